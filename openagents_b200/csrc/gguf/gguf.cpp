@@ -102,6 +102,8 @@ static void json_float(double v, std::string& out) {
   char buf[40];
   std::snprintf(buf, sizeof buf, "%.17g", v);
   out += buf;
+  // keep floats recognisable as floats after a JSON round trip
+  if (!std::strpbrk(buf, ".eE")) out += ".0";
 }
 
 static bool json_value(Cursor& c, uint32_t type, std::string& out) {

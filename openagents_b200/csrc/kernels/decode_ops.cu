@@ -1,0 +1,364 @@
+// Memory-bound decode-path operators: embedding gather with dequant, RMSNorm with fused activation
+// quantization, RoPE fused with the paged KV-cache write, SwiGLU, residual add and greedy / top-k
+// sampling.  The math follows the reference CPU workload
+// (apps/openagents.com/workers/api/src/cs336-a1-real-gradient-workload.ts:351-375 RMSNorm,
+// :532-549 SwiGLU, cs336-a2-benchmark-workload.ts:212-249 greedy arg-max decode).
+#include "common.cuh"
+
+using namespace b200;
+
+// ------------------------------------------------------------------ embedding gather
+
+// Weight types of the embedding table.
+enum { EMB_F32 = 0, EMB_BF16 = 1, EMB_Q8R = 2, EMB_Q6KR = 3 };
+
+// ids [T]; out fp32 [T][D].  `w` is the main plane, `w2` the scale plane (fp16) where one exists.
+// vocab_lo / vocab_n select a vocabulary shard: rows outside it produce zeros (tensor-parallel
+// embedding; the all-reduce that follows adds the one non-zero shard).
+__global__ void embedding_kernel(const int* __restrict__ ids, float* __restrict__ out, int D, int type,
+                                 const uint8_t* __restrict__ w, const __half* __restrict__ w2,
+                                 int vocab_lo, int vocab_n) {
+  const int t = blockIdx.x;
+  const int id = ids[t] - vocab_lo;
+  float* o = out + (size_t)t * D;
+  if (id < 0 || id >= vocab_n) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = 0.f;
+    return;
+  }
+  if (type == EMB_F32) {
+    const float* r = (const float*)w + (size_t)id * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = r[i];
+  } else if (type == EMB_BF16) {
+    const __nv_bfloat16* r = (const __nv_bfloat16*)w + (size_t)id * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = __bfloat162float(r[i]);
+  } else if (type == EMB_Q8R) {
+    const int8_t* r = (const int8_t*)w + (size_t)id * D;
+    const __half* d = w2 + (size_t)id * (D / 32);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+      int slot = (i & ~7) | x8_slot(i & 7);
+      o[i] = __half2float(d[i >> 5]) * (float)r[slot];
+    }
+  } else {  // EMB_Q6KR: 208-byte superblocks [lo words 128][T words 64][scales 16] + d plane
+    const int nsb = D / 256;
+    const uint8_t* r = w + (size_t)id * nsb * 208;
+    const __half* dp = w2 + (size_t)id * nsb;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+      const int sb = i >> 8, e = i & 255;
+      const uint8_t* blk = r + sb * 208;
+      const int word = e >> 3, ei = e & 7;
+      const uint32_t lo = ((const uint32_t*)blk)[word];
+      const uint32_t tw = ((const uint32_t*)(blk + 128))[word >> 1];
+      const int nib = (lo >> (4 * (ei >> 1) + 16 * (ei & 1))) & 0xF;
+      // 2-bit field: lane = slot & 3, half = slot >> 2 of the x8 slot, word parity selects +4
+      const int slot = x8_slot(ei);
+      const int hi = (tw >> (8 * (slot & 3) + 2 * (slot >> 2) + 4 * (word & 1))) & 3;
+      const int q = (nib | (hi << 4)) - 32;
+      const float sc = (float)((const int8_t*)(blk + 192))[e >> 4];
+      o[i] = __half2float(dp[sb]) * sc * (float)q;
+    }
+  }
+}
+
+B200_API int b200_embedding(const int* ids, float* out, int T, int D, int type, const void* w,
+                            const void* w2, int vocab_lo, int vocab_n, cudaStream_t st) {
+  embedding_kernel<<<T, 256, 0, st>>>(ids, out, D, type, (const uint8_t*)w, (const __half*)w2, vocab_lo,
+                                      vocab_n);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ RMSNorm (+ quantize)
+
+// x fp32 [T][D] -> any of: quantized activations (xq int8 x8-order, xd [T][D/32], xs16 [T][D/16]),
+// bf16 h [T][D], fp32 h [T][D].  One block per token; each warp owns 32-element blocks.
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ g, float eps, int D,
+                               int8_t* __restrict__ xq, float* __restrict__ xd, float* __restrict__ xs16,
+                               __nv_bfloat16* __restrict__ hb, float* __restrict__ hf) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const float* xr = x + (size_t)t * D;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float v = xr[i];
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / (float)D + eps);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int blk = w; blk < D / 32; blk += nw) {
+    const int i = blk * 32 + lane;
+    const float v = xr[i] * rstd * (g ? g[i] : 1.f);
+    if (hb) hb[(size_t)t * D + i] = __float2bfloat16(v);
+    if (hf) hf[(size_t)t * D + i] = v;
+    if (xq)
+      quantize_block32(v, lane, xq + (size_t)t * D + blk * 32, xd + (size_t)t * (D / 32) + blk,
+                       xs16 + (size_t)t * (D / 16) + blk * 2);
+  }
+}
+
+B200_API int b200_rmsnorm(const float* x, const float* g, float eps, int T, int D, void* xq, float* xd,
+                          float* xs16, void* hb, float* hf, cudaStream_t st) {
+  if (D % 32) return B200_ERR_BAD_ARG;
+  rmsnorm_kernel<<<T, 256, 0, st>>>(x, g, eps, D, (int8_t*)xq, xd, xs16, (__nv_bfloat16*)hb, hf);
+  return (int)cudaGetLastError();
+}
+
+// Plain activation quantization of fp32 rows (used where no norm precedes a quantized matvec).
+__global__ void quantize_x_kernel(const float* __restrict__ x, int D, int8_t* __restrict__ xq,
+                                  float* __restrict__ xd, float* __restrict__ xs16) {
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int blk = w; blk < D / 32; blk += nw) {
+    const float v = x[(size_t)t * D + blk * 32 + lane];
+    quantize_block32(v, lane, xq + (size_t)t * D + blk * 32, xd + (size_t)t * (D / 32) + blk,
+                     xs16 + (size_t)t * (D / 16) + blk * 2);
+  }
+}
+B200_API int b200_quantize_x(const float* x, int T, int D, void* xq, float* xd, float* xs16, cudaStream_t st) {
+  if (D % 32) return B200_ERR_BAD_ARG;
+  quantize_x_kernel<<<T, 256, 0, st>>>(x, D, (int8_t*)xq, xd, xs16);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ RoPE + paged KV write
+
+// qkv fp32 [T][(Hq + 2 Hkv) * hd] (q heads, then k heads, then v heads).
+// pos [T] absolute positions; slot [T] = physical token slot in the cache (page * page_size + offset).
+// Cache layout: [page][Hkv][page_size][hd] fp16, so one (page, head) is one contiguous tile.
+// q_out fp32 and/or q_out_h fp16 [T][Hq*hd] receive the rotated queries scaled by `q_scale`.
+// style 0: pairs (2i, 2i+1); style 1: halves (i, i + hd/2).
+__global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
+                               const int* __restrict__ slot, float* __restrict__ q_out, __half* __restrict__ q_out_h,
+                               __half* __restrict__ kc, __half* __restrict__ vc, int Hq, int Hkv, int hd,
+                               int page_size, float theta, int style, float q_scale) {
+  const int t = blockIdx.x;
+  const int row = (Hq + 2 * Hkv) * hd;
+  const float* in = qkv + (size_t)t * row;
+  const float p = (float)pos[t];
+  const int s = slot[t];
+  const int page = s / page_size, off = s % page_size;
+  const int half = hd >> 1;
+  // rotate q and k: one thread per (head, pair)
+  for (int i = threadIdx.x; i < (Hq + Hkv) * half; i += blockDim.x) {
+    const int h = i / half, j = i % half;
+    // Double precision on purpose: fast-math sine loses accuracy at angles of thousands of radians.
+    const double inv = exp2(-2.0 * (double)j / (double)hd * log2((double)theta));
+    double snd, csd;
+    sincos((double)p * inv, &snd, &csd);
+    const float sn = (float)snd, cs = (float)csd;
+    const int i0 = style == 0 ? 2 * j : j;
+    const int i1 = style == 0 ? 2 * j + 1 : j + half;
+    const float a = in[h * hd + i0], b = in[h * hd + i1];
+    const float r0 = a * cs - b * sn, r1 = a * sn + b * cs;
+    if (h < Hq) {
+      const size_t qi = (size_t)t * Hq * hd + h * hd;
+      if (q_out) {
+        q_out[qi + i0] = r0 * q_scale;
+        q_out[qi + i1] = r1 * q_scale;
+      }
+      if (q_out_h) {
+        q_out_h[qi + i0] = __float2half(r0 * q_scale);
+        q_out_h[qi + i1] = __float2half(r1 * q_scale);
+      }
+    } else if (s >= 0) {
+      const int kh = h - Hq;
+      __half* dst = kc + (((size_t)page * Hkv + kh) * page_size + off) * hd;
+      dst[i0] = __float2half(r0);
+      dst[i1] = __float2half(r1);
+    }
+  }
+  if (s >= 0) {
+    const float* vin = in + (Hq + Hkv) * hd;
+    for (int i = threadIdx.x; i < Hkv * hd; i += blockDim.x) {
+      const int kh = i / hd, e = i % hd;
+      vc[(((size_t)page * Hkv + kh) * page_size + off) * hd + e] = __float2half(vin[i]);
+    }
+  }
+}
+
+B200_API int b200_rope_kv(const float* qkv, const int* pos, const int* slot, float* q_out, void* q_out_h, void* kc,
+                          void* vc, int T, int Hq, int Hkv, int hd, int page_size, float theta,
+                          int style, float q_scale, cudaStream_t st) {
+  rope_kv_kernel<<<T, 256, 0, st>>>(qkv, pos, slot, q_out, (__half*)q_out_h, (__half*)kc, (__half*)vc, Hq, Hkv, hd,
+                                    page_size, theta, style, q_scale);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ SwiGLU / add / bias
+
+// gu fp32 [T][2F] (gate then up) -> bf16 and/or fp32 act [T][F]
+__global__ void swiglu_kernel(const float* __restrict__ gu, int F, __nv_bfloat16* __restrict__ ob,
+                              float* __restrict__ of) {
+  const size_t t = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= F) return;
+  const float v = silu(gu[t * 2 * F + i]) * gu[t * 2 * F + F + i];
+  if (ob) ob[t * F + i] = __float2bfloat16(v);
+  if (of) of[t * F + i] = v;
+}
+B200_API int b200_swiglu(const float* gu, int T, int F, void* ob, float* of, cudaStream_t st) {
+  dim3 grid((F + 255) / 256, T);
+  swiglu_kernel<<<grid, 256, 0, st>>>(gu, F, (__nv_bfloat16*)ob, of);
+  return (int)cudaGetLastError();
+}
+
+__global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] += y[i];
+}
+B200_API int b200_add_inplace(float* x, const float* y, size_t n, cudaStream_t st) {
+  add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, y, n);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ sampling
+
+// Greedy arg-max over logits [T][V] with the lowest index winning ties (matches torch.argmax on
+// the first maximal element).  Optional vocab_offset for a tensor-parallel shard; writes the max
+// value too so shards can be merged.
+__global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out_id,
+                              float* __restrict__ out_val, int vocab_offset) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int t = blockIdx.x;
+  const float* l = logits + (size_t)t * V;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float v = l[i];
+    if (v > best) {
+      best = v;
+      bi = i;
+    }
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (lane == 0) {
+    sv[w] = best;
+    si[w] = bi;
+  }
+  __syncthreads();
+  if (w == 0) {
+    const int nw = blockDim.x >> 5;
+    best = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      out_id[t] = bi + vocab_offset;
+      if (out_val) out_val[t] = best;
+    }
+  }
+}
+B200_API int b200_argmax(const float* logits, int T, int V, int* out_id, float* out_val,
+                         int vocab_offset, cudaStream_t st) {
+  argmax_kernel<<<T, 1024, 0, st>>>(logits, V, out_id, out_val, vocab_offset);
+  return (int)cudaGetLastError();
+}
+
+// Temperature / top-k / top-p sampling of one token per row.  One block per row.  The candidate
+// set is the top-k (k <= 64) found by repeated block arg-max, which is exact and cheap for the
+// small k that serving uses; top-p then trims the sorted candidates.  `u` holds one uniform random
+// number per row, supplied by the host so runs are reproducible.
+__global__ void sample_topk_kernel(const float* __restrict__ logits, int V, float temperature, int top_k,
+                                   float top_p, const float* __restrict__ u, int* __restrict__ out_id,
+                                   float* __restrict__ scratch) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ float cand_v[64];
+  __shared__ int cand_i[64];
+  const int t = blockIdx.x;
+  const float* l = logits + (size_t)t * V;
+  float* mask = scratch + (size_t)t * V;  // copy we can knock entries out of
+  for (int i = threadIdx.x; i < V; i += blockDim.x) mask[i] = l[i];
+  __syncthreads();
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int k = 0; k < top_k; k++) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      float v = mask[i];
+      if (v > best) {
+        best = v;
+        bi = i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      sv[w] = best;
+      si[w] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int j = 1; j < nw; j++)
+        if (sv[j] > sv[0] || (sv[j] == sv[0] && si[j] < si[0])) {
+          sv[0] = sv[j];
+          si[0] = si[j];
+        }
+      cand_v[k] = sv[0];
+      cand_i[k] = si[0];
+      if (si[0] < V) mask[si[0]] = -INFINITY;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const float inv_t = 1.f / fmaxf(temperature, 1e-6f);
+    const float m = cand_v[0];
+    float p[64];
+    float z = 0.f;
+    for (int k = 0; k < top_k; k++) {
+      p[k] = __expf((cand_v[k] - m) * inv_t);
+      z += p[k];
+    }
+    // top-p: keep the shortest prefix whose mass reaches top_p
+    int keep = top_k;
+    float acc = 0.f;
+    for (int k = 0; k < top_k; k++) {
+      acc += p[k] / z;
+      if (acc >= top_p) {
+        keep = k + 1;
+        break;
+      }
+    }
+    float z2 = 0.f;
+    for (int k = 0; k < keep; k++) z2 += p[k];
+    float r = u[t] * z2, c = 0.f;
+    int pick = cand_i[keep - 1];
+    for (int k = 0; k < keep; k++) {
+      c += p[k];
+      if (r < c) {
+        pick = cand_i[k];
+        break;
+      }
+    }
+    out_id[t] = pick;
+  }
+}
+B200_API int b200_sample_topk(const float* logits, int T, int V, float temperature, int top_k, float top_p,
+                              const float* u, int* out_id, float* scratch, cudaStream_t st) {
+  if (top_k < 1 || top_k > 64) return B200_ERR_BAD_ARG;
+  sample_topk_kernel<<<T, 1024, 0, st>>>(logits, V, temperature, top_k, top_p, u, out_id, scratch);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,278 @@
+// bf16 GEMM on the 5th-generation tensor cores: D[M][N] = A[M][K] * B[N][K]^T (+ epilogue).
+//
+// One CTA computes a 128 x BN output tile.  Warp 0 feeds shared memory with TMA tile loads
+// (128-byte swizzle), one elected thread of warp 1 issues tcgen05.mma with the accumulator in
+// tensor memory, and warps 2..5 read the accumulator back with tcgen05.ld and run the epilogue
+// (bias, GELU, residual, fp32 or bf16 store).  Stages hand over through mbarriers; every wait is
+// bounded and a timeout is reported through the status word instead of hanging.
+//
+// Both operands are K-major ("TN"), which is the natural layout of y = x W^T with W stored
+// [out][in]; the GEMM-shaped reference case is cs336-a2-benchmark-workload.ts:251-292.
+#include "tc05.cuh"
+
+using namespace b200;
+using namespace b200::tc;
+
+namespace b200 {
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+int make_tmap_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
+                 uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return -1;
+  if (((uintptr_t)base & 15) || (row_stride_bytes & 15)) return -2;
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                             : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+}  // namespace b200
+
+enum { ACT_NONE = 0, ACT_GELU = 1 };
+
+struct GemmEpi {
+  float* out_f32;            // either or both outputs
+  __nv_bfloat16* out_bf16;
+  const float* bias;         // [N] or null
+  const float* resid_f32;    // [M][ldc] or null, added after the activation
+  const __nv_bfloat16* resid_bf16;
+  int ldc;
+  int act;
+  int accumulate;            // out_f32 += value
+};
+
+constexpr int BM = 128, BK = 64;
+
+__device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, int M, int N, const uint32_t (&r)[32]) {
+  if (m >= M) return;
+  const size_t base = (size_t)m * e.ldc + n0;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+  const bool full = n0 + 32 <= N;
+  if (full) {
+    if (e.bias) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 b = *(const float4*)(e.bias + n0 + j);
+        v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+      }
+    }
+    if (e.act == ACT_GELU) {
+#pragma unroll
+      for (int j = 0; j < 32; j++) v[j] = gelu_tanh(v[j]);
+    }
+    if (e.resid_f32) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 b = *(const float4*)(e.resid_f32 + base + j);
+        v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+      }
+    }
+    if (e.resid_bf16) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        const uint4 b = *(const uint4*)(e.resid_bf16 + base + j);
+        const __nv_bfloat162* p = (const __nv_bfloat162*)&b;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const float2 f = __bfloat1622float2(p[q]);
+          v[j + 2 * q] += f.x;
+          v[j + 2 * q + 1] += f.y;
+        }
+      }
+    }
+    if (e.out_f32) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (e.accumulate) {
+          const float4 p = *(const float4*)(e.out_f32 + base + j);
+          o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+        }
+        *(float4*)(e.out_f32 + base + j) = o;
+      }
+    }
+    if (e.out_bf16) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 o;
+        __nv_bfloat162* p = (__nv_bfloat162*)&o;
+#pragma unroll
+        for (int q = 0; q < 4; q++) p[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+        *(uint4*)(e.out_bf16 + base + j) = o;
+      }
+    }
+  } else {
+    for (int j = 0; j < 32 && n0 + j < N; j++) {
+      float x = v[j];
+      if (e.bias) x += e.bias[n0 + j];
+      if (e.act == ACT_GELU) x = gelu_tanh(x);
+      if (e.resid_f32) x += e.resid_f32[base + j];
+      if (e.resid_bf16) x += __bfloat162float(e.resid_bf16[base + j]);
+      if (e.out_f32) e.out_f32[base + j] = e.accumulate ? e.out_f32[base + j] + x : x;
+      if (e.out_bf16) e.out_bf16[base + j] = __float2bfloat16(x);
+    }
+  }
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                         const __grid_constant__ CUtensorMap tmB,
+                                                         const GemmEpi epi, int M, int N, int K,
+                                                         int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint64_t* bars = (uint64_t*)(sB + STAGES * B_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint32_t* tmem_holder = (uint32_t*)(bars + 2 * STAGES + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int KB = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(smem_u32(full + s), 1);
+      mbar_init(smem_u32(empty + s), 1);
+    }
+    mbar_init(smem_u32(tfull), 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < KB; kb++) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        if (!mbar_wait(smem_u32(empty + s), ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(smem_u32(full + s), A_BYTES + B_BYTES);
+        tma_load_2d(smem_u32(sA + s * A_BYTES), &tmA, smem_u32(full + s), kb * BK, m0);
+        tma_load_2d(smem_u32(sB + s * B_BYTES), &tmB, smem_u32(full + s), kb * BK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16(BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < KB && ok; kb++) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        ok = mbar_wait(smem_u32(full + s), ph, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t ad = smem_desc_sw128(smem_u32(sA + s * A_BYTES));
+        const uint64_t bd = smem_desc_sw128(smem_u32(sB + s * B_BYTES));
+#pragma unroll
+        for (int k = 0; k < BK / 16; k++)
+          umma_bf16(tmem_base, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+        umma_commit(smem_u32(empty + s));
+      }
+      // Always commit to the accumulator barrier so the epilogue is released (with an abort flag
+      // set it will skip the read-back).
+      umma_commit(smem_u32(tfull));
+    }
+  } else {
+    bool ok = mbar_wait(smem_u32(tfull), 0, abort_flag);
+    ok = __all_sync(0xffffffffu, ok && !*abort_flag);  // tcgen05.ld needs the whole warp
+    tc_fence_after();
+    if (ok) {
+      const int q = warp & 3;
+      const int m = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        if (n0 + c * 32 < N) epilogue_row(epi, m, n0 + c * 32, M, N, r);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, BN);
+  if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, (int)B200_ERR_TIMEOUT_MMA);
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpi& e, int M, int N, int K,
+                       int* status, cudaStream_t st) {
+  constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16;
+  auto kern = gemm_bf16_kernel<BN, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  kern<<<grid, 192, smem, st>>>(ta, tb, e, M, N, K, status);
+  return (int)cudaGetLastError();
+}
+
+// A [M][K] (row stride lda), B [N][K] (row stride ldb), bf16, K-major.  Strides in elements and
+// multiples of 8; base pointers 16-byte aligned.  tile_n: 0 = choose, else 64 / 128 / 256.
+// `status` is a device int the kernel sets non-zero if one of its waits ran out.
+B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, int lda, int ldb, float* out_f32,
+                            void* out_bf16, int ldc, const float* bias, const float* resid_f32,
+                            const void* resid_bf16, int act, int accumulate, int tile_n, int* status,
+                            cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0 || (lda % 8) || (ldb % 8) || (K % 8)) return B200_ERR_BAD_ARG;
+  if ((out_bf16 && (ldc % 8)) || (out_f32 && (ldc % 4))) return B200_ERR_BAD_ARG;
+  if (tile_n == 0) {
+    const long tiles256 = (long)((N + 255) / 256) * ((M + 127) / 128);
+    tile_n = (N >= 256 && tiles256 >= 148) ? 256 : (N >= 128 && (long)((N + 127) / 128) * ((M + 127) / 128) >= 148) ? 128 : (N > 64 ? 128 : 64);
+  }
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tb, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, (uint32_t)tile_n, BK, true);
+  if (rc) return rc;
+  GemmEpi e;
+  e.out_f32 = out_f32; e.out_bf16 = (__nv_bfloat16*)out_bf16; e.bias = bias; e.resid_f32 = resid_f32;
+  e.resid_bf16 = (const __nv_bfloat16*)resid_bf16; e.ldc = ldc; e.act = act; e.accumulate = accumulate;
+  switch (tile_n) {
+    case 256: return launch_gemm<256, 4>(ta, tb, e, M, N, K, status, st);
+    case 128: return launch_gemm<128, 6>(ta, tb, e, M, N, K, status, st);
+    case 64: return launch_gemm<64, 8>(ta, tb, e, M, N, K, status, st);
+  }
+  return B200_ERR_BAD_ARG;
+}

@@ -1,0 +1,351 @@
+// Small-batch (1..8 tokens) quantized mat-vec: y[b][n] = sum_k W[n][k] * x[b][k], the decode-time
+// projection of a GGUF-quantized weight.  Weights stream from HBM exactly once in their packed
+// form; activations are pre-quantized to int8 (32-element blocks) so the inner product runs on
+// dp4a and a whole CTA's activations fit in shared memory.  One CTA owns 32 output rows so the
+// epilogue can emit a complete 32-element quantized block for the next mat-vec (fused SwiGLU +
+// requantize), add the residual, or add a bias.
+//
+// Reference math: per-position projections of
+// apps/openagents.com/workers/api/src/cs336-a1-real-gradient-workload.ts:459-475 (QKV),
+// :520-528 (output projection + residual), :532-559 (SwiGLU FFN).
+#include "common.cuh"
+
+using namespace b200;
+
+enum { WT_Q4KR = 0, WT_Q6KR = 1, WT_Q8R = 2, WT_BF16 = 3 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU_Q8 = 2, EPI_SWIGLU_F32 = 3 };
+
+struct MatvecArgs {
+  const uint8_t* w;     // main plane
+  const __half* w2;     // scale plane (Q6K-R: d per superblock; Q8-R: d per block)
+  int N, K;             // output rows (per matrix when dual), reduction length
+  int nb;               // live tokens (<= template B)
+  const int8_t* xq;     // [nb][K] int8, x8 order
+  const float* xd;      // [nb][K/32]
+  const float* xs16;    // [nb][K/16]
+  const float* xf;      // [nb][K] fp32 (bf16-weight path only)
+  int epi;
+  const float* bias;    // [N] or null (dual: [2N])
+  const float* resid;   // [nb][ldy] (EPI_RESID)
+  float* y;             // [nb][ldy]
+  int ldy;
+  int8_t* oq;           // EPI_SWIGLU_Q8 outputs
+  float* od;
+  float* os16;
+};
+
+__device__ __forceinline__ int dp4a(uint32_t a, uint32_t b, int c) {
+  return __dp4a((int)a, (int)b, c);
+}
+
+template <int WT>
+__device__ __forceinline__ size_t row_bytes(int K) {
+  if (WT == WT_Q4KR) return (size_t)(K / 256) * 144;
+  if (WT == WT_Q6KR) return (size_t)(K / 256) * 208;
+  return (size_t)K;  // Q8R
+}
+
+// Dot of one 32-element unit of one weight row against all B tokens.
+template <int WT, int B>
+__device__ __forceinline__ void unit_dot(const uint8_t* __restrict__ wrow, const __half* __restrict__ w2row,
+                                         int u, int U, const uint4* __restrict__ xp0,
+                                         const uint4* __restrict__ xp1, const float* __restrict__ sxd,
+                                         const float2* __restrict__ sxs, float (&acc)[B]) {
+  const int sb = u >> 3, j = u & 7;
+  if constexpr (WT == WT_Q4KR) {
+    const uint8_t* blk = wrow + (size_t)sb * 144;
+    const uint4 hdr = __ldg((const uint4*)blk);
+    const uint4 q = ldg_stream(blk + 16 + j * 16);
+    const int sh = 8 * (j & 3);
+    const uint32_t b0 = (hdr.y >> sh) & 0xFF, b1 = (hdr.z >> sh) & 0xFF, b2 = (hdr.w >> sh) & 0xFF;
+    const uint32_t sc = j < 4 ? (b0 & 63) : ((b2 & 0xF) | ((b0 >> 6) << 4));
+    const uint32_t mn = j < 4 ? (b1 & 63) : ((b2 >> 4) | ((b1 >> 6) << 4));
+    const __half2 dd = *reinterpret_cast<const __half2*>(&hdr.x);
+    const float a = __low2float(dd) * (float)sc, m = __high2float(dd) * (float)mn;
+    const uint32_t l0 = q.x & 0x0F0F0F0Fu, h0 = (q.x >> 4) & 0x0F0F0F0Fu;
+    const uint32_t l1 = q.y & 0x0F0F0F0Fu, h1 = (q.y >> 4) & 0x0F0F0F0Fu;
+    const uint32_t l2 = q.z & 0x0F0F0F0Fu, h2 = (q.z >> 4) & 0x0F0F0F0Fu;
+    const uint32_t l3 = q.w & 0x0F0F0F0Fu, h3 = (q.w >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+    for (int b = 0; b < B; b++) {
+      const uint4 x0 = xp0[b * U + u], x1 = xp1[b * U + u];
+      int s = dp4a(l0, x0.x, 0);
+      s = dp4a(h0, x0.y, s);
+      s = dp4a(l1, x0.z, s);
+      s = dp4a(h1, x0.w, s);
+      s = dp4a(l2, x1.x, s);
+      s = dp4a(h2, x1.y, s);
+      s = dp4a(l3, x1.z, s);
+      s = dp4a(h3, x1.w, s);
+      const float2 xs = sxs[b * U + u];
+      acc[b] += a * sxd[b * U + u] * (float)s - m * (xs.x + xs.y);
+    }
+  } else if constexpr (WT == WT_Q6KR) {
+    const uint8_t* blk = wrow + (size_t)sb * 208;
+    const uint4 lo = ldg_stream(blk + j * 16);
+    const uint2 tw = ldg_stream2(blk + 128 + j * 8);
+    const uint32_t scw = ((const uint16_t*)(blk + 192))[j];
+    const float d = __half2float(w2row[sb]);
+    const float sc0 = d * (float)(int8_t)(scw & 0xFF), sc1 = d * (float)(int8_t)(scw >> 8);
+    const uint32_t m4 = 0x0F0F0F0Fu, m2 = 0x03030303u;
+    const uint32_t a0 = (lo.x & m4) | ((tw.x & m2) << 4), a1 = ((lo.x >> 4) & m4) | (((tw.x >> 2) & m2) << 4);
+    const uint32_t a2 = (lo.y & m4) | (((tw.x >> 4) & m2) << 4), a3 = ((lo.y >> 4) & m4) | (((tw.x >> 6) & m2) << 4);
+    const uint32_t c0 = (lo.z & m4) | ((tw.y & m2) << 4), c1 = ((lo.z >> 4) & m4) | (((tw.y >> 2) & m2) << 4);
+    const uint32_t c2 = (lo.w & m4) | (((tw.y >> 4) & m2) << 4), c3 = ((lo.w >> 4) & m4) | (((tw.y >> 6) & m2) << 4);
+#pragma unroll
+    for (int b = 0; b < B; b++) {
+      const uint4 x0 = xp0[b * U + u], x1 = xp1[b * U + u];
+      int s0 = dp4a(a0, x0.x, 0);
+      s0 = dp4a(a1, x0.y, s0);
+      s0 = dp4a(a2, x0.z, s0);
+      s0 = dp4a(a3, x0.w, s0);
+      int s1 = dp4a(c0, x1.x, 0);
+      s1 = dp4a(c1, x1.y, s1);
+      s1 = dp4a(c2, x1.z, s1);
+      s1 = dp4a(c3, x1.w, s1);
+      const float2 xs = sxs[b * U + u];
+      const float xd = sxd[b * U + u];
+      acc[b] += sc0 * (xd * (float)s0 - 32.f * xs.x) + sc1 * (xd * (float)s1 - 32.f * xs.y);
+    }
+  } else {  // WT_Q8R
+    const uint4 q0 = ldg_stream(wrow + (size_t)u * 32), q1 = ldg_stream(wrow + (size_t)u * 32 + 16);
+    const float d = __half2float(w2row[u]);
+#pragma unroll
+    for (int b = 0; b < B; b++) {
+      const uint4 x0 = xp0[b * U + u], x1 = xp1[b * U + u];
+      int s = dp4a(q0.x, x0.x, 0);
+      s = dp4a(q0.y, x0.y, s);
+      s = dp4a(q0.z, x0.z, s);
+      s = dp4a(q0.w, x0.w, s);
+      s = dp4a(q1.x, x1.x, s);
+      s = dp4a(q1.y, x1.y, s);
+      s = dp4a(q1.z, x1.z, s);
+      s = dp4a(q1.w, x1.w, s);
+      acc[b] += d * sxd[b * U + u] * (float)s;
+    }
+  }
+}
+
+// Shared epilogue: res[m][r][b] holds the 32 x B results of matrix m (m = 1 only when dual).
+template <int B>
+__device__ __forceinline__ void matvec_epilogue(const MatvecArgs& a, const float* res, bool dual) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (w >= a.nb) return;
+  const int b = w;
+  const int n = blockIdx.x * 32 + lane;
+  const bool live = n < a.N;
+  float v = res[lane * B + b];
+  if (a.bias && live) v += a.bias[n];
+  if (a.epi == EPI_STORE) {
+    if (live) a.y[(size_t)b * a.ldy + n] = v;
+    if (dual && live) {
+      float v2 = res[32 * B + lane * B + b] + (a.bias ? a.bias[a.N + n] : 0.f);
+      a.y[(size_t)b * a.ldy + a.N + n] = v2;
+    }
+  } else if (a.epi == EPI_RESID) {
+    if (live) a.y[(size_t)b * a.ldy + n] = a.resid[(size_t)b * a.ldy + n] + v;
+  } else {
+    float u = res[32 * B + lane * B + b];
+    if (a.bias && live) u += a.bias[a.N + n];
+    const float act = live ? silu(v) * u : 0.f;
+    if (a.epi == EPI_SWIGLU_F32) {
+      if (live) a.y[(size_t)b * a.ldy + n] = act;
+    } else {
+      quantize_block32(act, lane, a.oq + (size_t)b * a.N + blockIdx.x * 32,
+                       a.od + (size_t)b * (a.N / 32) + blockIdx.x,
+                       a.os16 + (size_t)b * (a.N / 16) + blockIdx.x * 2);
+    }
+  }
+}
+
+template <int WT, int B, bool DUAL>
+__global__ void __launch_bounds__(256) matvec_q_kernel(const MatvecArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int U = a.K / 32;
+  uint4* xp0 = (uint4*)smem;                  // [B][U]
+  uint4* xp1 = xp0 + B * U;                   // [B][U]
+  float* sxd = (float*)(xp1 + B * U);         // [B][U]
+  float2* sxs = (float2*)(sxd + B * U);       // [B][U]
+  float* res = (float*)(sxs + B * U);         // [2][32][B]
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+
+  // Stage the quantized activations (a few KB per token) into shared memory, split into two
+  // 16-byte planes so a warp's reads are conflict-free.
+  for (int i = tid; i < B * U; i += 256) {
+    const int b = i / U, u = i - b * U;
+    if (b < a.nb) {
+      const uint4* src = (const uint4*)(a.xq + (size_t)b * a.K + (size_t)u * 32);
+      xp0[i] = src[0];
+      xp1[i] = src[1];
+      sxd[i] = a.xd[(size_t)b * U + u];
+      sxs[i] = ((const float2*)a.xs16)[(size_t)b * U + u];
+    } else {
+      xp0[i] = make_uint4(0, 0, 0, 0);
+      xp1[i] = make_uint4(0, 0, 0, 0);
+      sxd[i] = 0.f;
+      sxs[i] = make_float2(0.f, 0.f);
+    }
+  }
+  __syncthreads();
+
+  const size_t rb = row_bytes<WT>(a.K);
+  const int w2_per_row = (WT == WT_Q6KR) ? a.K / 256 : U;
+#pragma unroll 1
+  for (int i = 0; i < 4; i++) {
+    const int r = w + 8 * i;
+    const int n = blockIdx.x * 32 + r;
+    float acc0[B], acc1[B];
+#pragma unroll
+    for (int b = 0; b < B; b++) acc0[b] = acc1[b] = 0.f;
+    if (n < a.N) {
+      const uint8_t* wr0 = a.w + (size_t)n * rb;
+      const __half* w20 = a.w2 ? a.w2 + (size_t)n * w2_per_row : nullptr;
+      const uint8_t* wr1 = a.w + (size_t)(n + a.N) * rb;
+      const __half* w21 = a.w2 ? a.w2 + (size_t)(n + a.N) * w2_per_row : nullptr;
+#pragma unroll 4
+      for (int u = lane; u < U; u += 32) {
+        unit_dot<WT, B>(wr0, w20, u, U, xp0, xp1, sxd, sxs, acc0);
+        if (DUAL) unit_dot<WT, B>(wr1, w21, u, U, xp0, xp1, sxd, sxs, acc1);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < B; b++) {
+      float v0 = warp_sum(acc0[b]);
+      if (lane == 0) res[r * B + b] = v0;
+      if (DUAL) {
+        float v1 = warp_sum(acc1[b]);
+        if (lane == 0) res[32 * B + r * B + b] = v1;
+      }
+    }
+  }
+  __syncthreads();
+  matvec_epilogue<B>(a, res, DUAL);
+}
+
+// bf16 weights [N][K] against fp32 activations.
+template <int B, bool DUAL>
+__global__ void __launch_bounds__(256) matvec_bf16_kernel(const MatvecArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  float* xs = (float*)smem;            // [B][K]
+  float* res = xs + (size_t)B * a.K;   // [2][32][B]
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  for (int i = tid; i < B * a.K; i += 256) {
+    const int b = i / a.K;
+    xs[i] = b < a.nb ? a.xf[i] : 0.f;
+  }
+  __syncthreads();
+  const __nv_bfloat16* W = (const __nv_bfloat16*)a.w;
+#pragma unroll 1
+  for (int i = 0; i < 4; i++) {
+    const int r = w + 8 * i;
+    const int n = blockIdx.x * 32 + r;
+    float acc0[B], acc1[B];
+#pragma unroll
+    for (int b = 0; b < B; b++) acc0[b] = acc1[b] = 0.f;
+    if (n < a.N) {
+      const __nv_bfloat16* wr0 = W + (size_t)n * a.K;
+      const __nv_bfloat16* wr1 = W + (size_t)(n + a.N) * a.K;
+#pragma unroll 2
+      for (int k = lane * 8; k < a.K; k += 256) {
+        const uint4 q0 = ldg_stream(wr0 + k);
+        uint4 q1 = make_uint4(0, 0, 0, 0);
+        if (DUAL) q1 = ldg_stream(wr1 + k);
+        const __nv_bfloat162* p0 = (const __nv_bfloat162*)&q0;
+        const __nv_bfloat162* p1 = (const __nv_bfloat162*)&q1;
+#pragma unroll
+        for (int b = 0; b < B; b++) {
+          const float4 xa = *(const float4*)(xs + (size_t)b * a.K + k);
+          const float4 xb = *(const float4*)(xs + (size_t)b * a.K + k + 4);
+          float2 f;
+          f = __bfloat1622float2(p0[0]); acc0[b] += f.x * xa.x + f.y * xa.y;
+          f = __bfloat1622float2(p0[1]); acc0[b] += f.x * xa.z + f.y * xa.w;
+          f = __bfloat1622float2(p0[2]); acc0[b] += f.x * xb.x + f.y * xb.y;
+          f = __bfloat1622float2(p0[3]); acc0[b] += f.x * xb.z + f.y * xb.w;
+          if (DUAL) {
+            f = __bfloat1622float2(p1[0]); acc1[b] += f.x * xa.x + f.y * xa.y;
+            f = __bfloat1622float2(p1[1]); acc1[b] += f.x * xa.z + f.y * xa.w;
+            f = __bfloat1622float2(p1[2]); acc1[b] += f.x * xb.x + f.y * xb.y;
+            f = __bfloat1622float2(p1[3]); acc1[b] += f.x * xb.z + f.y * xb.w;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < B; b++) {
+      float v0 = warp_sum(acc0[b]);
+      if (lane == 0) res[r * B + b] = v0;
+      if (DUAL) {
+        float v1 = warp_sum(acc1[b]);
+        if (lane == 0) res[32 * B + r * B + b] = v1;
+      }
+    }
+  }
+  __syncthreads();
+  matvec_epilogue<B>(a, res, DUAL);
+}
+
+template <int WT, int B, bool DUAL>
+static int launch_q(const MatvecArgs& a, cudaStream_t st) {
+  const int U = a.K / 32;
+  const size_t smem = (size_t)B * U * (16 + 16 + 4 + 8) + 2 * 32 * B * sizeof(float);
+  auto kern = matvec_q_kernel<WT, B, DUAL>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kern<<<(a.N + 31) / 32, 256, smem, st>>>(a);
+  return (int)cudaGetLastError();
+}
+template <int B, bool DUAL>
+static int launch_bf16(const MatvecArgs& a, cudaStream_t st) {
+  const size_t smem = (size_t)B * a.K * 4 + 2 * 32 * B * sizeof(float);
+  auto kern = matvec_bf16_kernel<B, DUAL>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kern<<<(a.N + 31) / 32, 256, smem, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
+template <int B, bool DUAL>
+static int dispatch_wt(int wt, const MatvecArgs& a, cudaStream_t st) {
+  switch (wt) {
+    case WT_Q4KR: return launch_q<WT_Q4KR, B, DUAL>(a, st);
+    case WT_Q6KR: return launch_q<WT_Q6KR, B, DUAL>(a, st);
+    case WT_Q8R: return launch_q<WT_Q8R, B, DUAL>(a, st);
+    case WT_BF16: return launch_bf16<B, DUAL>(a, st);
+  }
+  return B200_ERR_BAD_ARG;
+}
+
+// wt: weight layout; nb: tokens (1..8).  For the SwiGLU epilogues `w` holds 2N rows (gate rows
+// first, then up rows) and N is the width of one of them.
+B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, int nb, const void* xq,
+                         const float* xd, const float* xs16, const float* xf, int epi, const float* bias,
+                         const float* resid, float* y, int ldy, void* oq, float* od, float* os16,
+                         cudaStream_t st) {
+  if (nb < 1 || nb > 8) return B200_ERR_BAD_ARG;
+  if (wt == WT_BF16 ? (K % 8 != 0) : (K % 256 != 0 && !(wt == WT_Q8R && K % 32 == 0))) return B200_ERR_BAD_ARG;
+  if (epi == EPI_SWIGLU_Q8 && N % 32) return B200_ERR_BAD_ARG;
+  MatvecArgs a;
+  a.w = (const uint8_t*)w; a.w2 = (const __half*)w2; a.N = N; a.K = K; a.nb = nb;
+  a.xq = (const int8_t*)xq; a.xd = xd; a.xs16 = xs16; a.xf = xf; a.epi = epi; a.bias = bias;
+  a.resid = resid; a.y = y; a.ldy = ldy; a.oq = (int8_t*)oq; a.od = od; a.os16 = os16;
+  const bool dual = epi >= EPI_SWIGLU_Q8;
+  const int B = nb <= 1 ? 1 : nb <= 2 ? 2 : nb <= 4 ? 4 : 8;
+  if (dual) {
+    switch (B) {
+      case 1: return dispatch_wt<1, true>(wt, a, st);
+      case 2: return dispatch_wt<2, true>(wt, a, st);
+      case 4: return dispatch_wt<4, true>(wt, a, st);
+      default: return dispatch_wt<8, true>(wt, a, st);
+    }
+  }
+  switch (B) {
+    case 1: return dispatch_wt<1, false>(wt, a, st);
+    case 2: return dispatch_wt<2, false>(wt, a, st);
+    case 4: return dispatch_wt<4, false>(wt, a, st);
+    default: return dispatch_wt<8, false>(wt, a, st);
+  }
+}

@@ -1,0 +1,183 @@
+// Paged KV-cache bookkeeping on the host: a page free-list with reference counts, per-sequence
+// page lists, and a prefix index keyed by a hash chain over full pages of token ids so a new
+// request can share the pages of an earlier one with the same prefix.
+//
+// The reference lists "KV and prefix caches, continuous batching" as model-server infrastructure
+// (docs/muse/muse-glimmer.md:113-114) and derives a cache-affinity key from a canonical prompt
+// prefix (apps/openagents.com/workers/api/src/inference/prompt-prefix-cache.ts:324); the page
+// mechanics here are this framework's own.
+#include <cstdint>
+#include <cstring>
+#include <unordered_map>
+#include <vector>
+
+namespace {
+
+struct Seq {
+  std::vector<int32_t> pages;
+  int64_t n_tokens = 0;
+  std::vector<uint64_t> chain;  // hash of each full page's prefix chain, parallel to pages
+};
+
+struct Pool {
+  int32_t n_pages, page_size;
+  std::vector<int32_t> free_list;
+  std::vector<int32_t> refcnt;
+  std::vector<uint64_t> page_hash;     // chain hash a page is registered under (0 = none)
+  std::unordered_map<uint64_t, int32_t> prefix;  // chain hash -> page
+  std::unordered_map<int64_t, Seq> seqs;
+  uint64_t hits = 0, lookups = 0;
+};
+
+uint64_t mix(uint64_t h, uint64_t v) {
+  h ^= v + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+  h *= 0xff51afd7ed558ccdull;
+  h ^= h >> 33;
+  return h;
+}
+
+uint64_t page_chain_hash(uint64_t prev, const int32_t* toks, int n) {
+  uint64_t h = prev ? prev : 0x243F6A8885A308D3ull;
+  for (int i = 0; i < n; i++) h = mix(h, (uint64_t)(uint32_t)toks[i] + 1);
+  return h ? h : 1;
+}
+
+void release_page(Pool* p, int32_t pg) {
+  if (--p->refcnt[pg] == 0) {
+    if (p->page_hash[pg]) {
+      auto it = p->prefix.find(p->page_hash[pg]);
+      if (it != p->prefix.end() && it->second == pg) p->prefix.erase(it);
+      p->page_hash[pg] = 0;
+    }
+    p->free_list.push_back(pg);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+void* b200_kv_create(int32_t n_pages, int32_t page_size) {
+  Pool* p = new Pool();
+  p->n_pages = n_pages;
+  p->page_size = page_size;
+  p->refcnt.assign(n_pages, 0);
+  p->page_hash.assign(n_pages, 0);
+  p->free_list.reserve(n_pages);
+  for (int32_t i = n_pages - 1; i >= 0; i--) p->free_list.push_back(i);
+  return p;
+}
+void b200_kv_destroy(void* h) { delete (Pool*)h; }
+int32_t b200_kv_free_pages(void* h) { return (int32_t)((Pool*)h)->free_list.size(); }
+int32_t b200_kv_total_pages(void* h) { return ((Pool*)h)->n_pages; }
+uint64_t b200_kv_prefix_hits(void* h) { return ((Pool*)h)->hits; }
+uint64_t b200_kv_prefix_lookups(void* h) { return ((Pool*)h)->lookups; }
+
+// Start a sequence.  If `tokens` is given, full pages whose prefix chain is already cached are
+// shared; returns the number of tokens covered by shared pages (a multiple of the page size, and
+// always less than n_tokens so at least one token is left to compute), or -1 if the id is in use.
+int64_t b200_kv_seq_begin(void* h, int64_t seq_id, const int32_t* tokens, int64_t n_tokens) {
+  Pool* p = (Pool*)h;
+  if (p->seqs.count(seq_id)) return -1;
+  Seq& s = p->seqs[seq_id];
+  if (!tokens) return 0;
+  uint64_t chain = 0;
+  int64_t full = (n_tokens - 1) / p->page_size;  // leave the last token uncached
+  for (int64_t i = 0; i < full; i++) {
+    chain = page_chain_hash(chain, tokens + i * p->page_size, p->page_size);
+    p->lookups++;
+    auto it = p->prefix.find(chain);
+    if (it == p->prefix.end()) break;
+    p->hits++;
+    p->refcnt[it->second]++;
+    s.pages.push_back(it->second);
+    s.chain.push_back(chain);
+    s.n_tokens += p->page_size;
+  }
+  return s.n_tokens;
+}
+
+// Grow the sequence to hold n_new more tokens.  Returns 0, -1 (unknown sequence) or -2 (out of
+// pages; nothing is allocated in that case).
+int32_t b200_kv_seq_extend(void* h, int64_t seq_id, int64_t n_new) {
+  Pool* p = (Pool*)h;
+  auto it = p->seqs.find(seq_id);
+  if (it == p->seqs.end()) return -1;
+  Seq& s = it->second;
+  int64_t need = (s.n_tokens + n_new + p->page_size - 1) / p->page_size - (int64_t)s.pages.size();
+  if (need > (int64_t)p->free_list.size()) return -2;
+  for (int64_t i = 0; i < need; i++) {
+    int32_t pg = p->free_list.back();
+    p->free_list.pop_back();
+    p->refcnt[pg] = 1;
+    s.pages.push_back(pg);
+  }
+  s.n_tokens += n_new;
+  return 0;
+}
+
+// Register the sequence's full pages in the prefix index (call once their K/V are written).
+// `tokens` are all n_tokens ids of the sequence so far.
+void b200_kv_seq_publish(void* h, int64_t seq_id, const int32_t* tokens, int64_t n_tokens) {
+  Pool* p = (Pool*)h;
+  auto it = p->seqs.find(seq_id);
+  if (it == p->seqs.end()) return;
+  Seq& s = it->second;
+  int64_t full = n_tokens / p->page_size;
+  if (full > (int64_t)s.pages.size()) full = (int64_t)s.pages.size();
+  uint64_t chain = s.chain.empty() ? 0 : s.chain.back();
+  for (int64_t i = (int64_t)s.chain.size(); i < full; i++) {
+    chain = page_chain_hash(chain, tokens + i * p->page_size, p->page_size);
+    s.chain.push_back(chain);
+    int32_t pg = s.pages[i];
+    if (!p->prefix.count(chain) && p->page_hash[pg] == 0) {
+      p->prefix[chain] = pg;
+      p->page_hash[pg] = chain;
+    }
+  }
+}
+
+int64_t b200_kv_seq_len(void* h, int64_t seq_id) {
+  Pool* p = (Pool*)h;
+  auto it = p->seqs.find(seq_id);
+  return it == p->seqs.end() ? -1 : it->second.n_tokens;
+}
+int32_t b200_kv_seq_n_pages(void* h, int64_t seq_id) {
+  Pool* p = (Pool*)h;
+  auto it = p->seqs.find(seq_id);
+  return it == p->seqs.end() ? -1 : (int32_t)it->second.pages.size();
+}
+// Copies up to `cap` page ids; returns the number of pages of the sequence.
+int32_t b200_kv_seq_pages(void* h, int64_t seq_id, int32_t* out, int32_t cap) {
+  Pool* p = (Pool*)h;
+  auto it = p->seqs.find(seq_id);
+  if (it == p->seqs.end()) return -1;
+  const auto& pg = it->second.pages;
+  int32_t n = (int32_t)pg.size();
+  std::memcpy(out, pg.data(), sizeof(int32_t) * (size_t)(n < cap ? n : cap));
+  return n;
+}
+// Drop the last n tokens (a rejected speculative tail or a cancelled turn).
+int32_t b200_kv_seq_truncate(void* h, int64_t seq_id, int64_t new_len) {
+  Pool* p = (Pool*)h;
+  auto it = p->seqs.find(seq_id);
+  if (it == p->seqs.end() || new_len < 0 || new_len > it->second.n_tokens) return -1;
+  Seq& s = it->second;
+  size_t keep = (size_t)((new_len + p->page_size - 1) / p->page_size);
+  while (s.pages.size() > keep) {
+    release_page(p, s.pages.back());
+    s.pages.pop_back();
+  }
+  if (s.chain.size() > (size_t)(new_len / p->page_size)) s.chain.resize((size_t)(new_len / p->page_size));
+  s.n_tokens = new_len;
+  return 0;
+}
+void b200_kv_seq_end(void* h, int64_t seq_id) {
+  Pool* p = (Pool*)h;
+  auto it = p->seqs.find(seq_id);
+  if (it == p->seqs.end()) return;
+  for (int32_t pg : it->second.pages) release_page(p, pg);
+  p->seqs.erase(it);
+}
+
+}  // extern "C"

@@ -1,0 +1,513 @@
+"""Decoder engine for dense llama-family models on one GPU (or one tensor-parallel rank).
+
+The engine owns the device weights, the paged fp16 KV cache and the activation workspaces, and
+exposes two operations over packed token batches: ``forward_tokens`` (prefill chunks, many tokens
+per sequence) and ``decode`` (one token per sequence, replayed from a CUDA graph).  Small decode
+batches (<= 8 tokens) take the quantized mat-vec kernels, which read the packed weights once;
+larger batches and prefill take the tcgen05 GEMM.
+
+The serve-side contract this implements is the reference's model-server description: GGUF load,
+KV and prefix caches, continuous batching (docs/muse/muse-glimmer.md:110-126).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .. import _native
+from ..ops import cuda_ops as ops
+from .config import ModelConfig
+from .qweight import QWeight, RawTensor, WeightSource
+
+PAGE = 16
+MATVEC_MAX_TOKENS = 8
+
+
+class KVPool:
+    """Host-side page bookkeeping (C++), shared by every layer's device cache."""
+
+    def __init__(self, n_pages: int, page_size: int = PAGE):
+        L = _native.host()
+        if not getattr(L, "_b200_kv_ready", False):
+            vp, i64, i32, u64 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_uint64
+            P32 = ctypes.POINTER(ctypes.c_int32)
+            sig = {"b200_kv_create": ([i32, i32], vp), "b200_kv_destroy": ([vp], None),
+                   "b200_kv_free_pages": ([vp], i32), "b200_kv_total_pages": ([vp], i32),
+                   "b200_kv_prefix_hits": ([vp], u64), "b200_kv_prefix_lookups": ([vp], u64),
+                   "b200_kv_seq_begin": ([vp, i64, P32, i64], i64), "b200_kv_seq_extend": ([vp, i64, i64], i32),
+                   "b200_kv_seq_publish": ([vp, i64, P32, i64], None), "b200_kv_seq_len": ([vp, i64], i64),
+                   "b200_kv_seq_n_pages": ([vp, i64], i32), "b200_kv_seq_pages": ([vp, i64, P32, i32], i32),
+                   "b200_kv_seq_truncate": ([vp, i64, i64], i32), "b200_kv_seq_end": ([vp, i64], None)}
+            for n, (a, r) in sig.items():
+                f = getattr(L, n)
+                f.argtypes, f.restype = a, r
+            L._b200_kv_ready = True
+        self.L = L
+        self.h = L.b200_kv_create(n_pages, page_size)
+        self.page_size = page_size
+        self.n_pages = n_pages
+
+    @staticmethod
+    def _arr(tokens):
+        if tokens is None:
+            return None, 0
+        a = (ctypes.c_int32 * len(tokens))(*tokens)
+        return a, len(tokens)
+
+    def begin(self, seq_id: int, tokens=None) -> int:
+        a, n = self._arr(tokens)
+        r = self.L.b200_kv_seq_begin(self.h, seq_id, a, n)
+        if r < 0:
+            raise KeyError(f"sequence {seq_id} already exists")
+        return r
+
+    def extend(self, seq_id: int, n_new: int):
+        r = self.L.b200_kv_seq_extend(self.h, seq_id, n_new)
+        if r == -1:
+            raise KeyError(f"unknown sequence {seq_id}")
+        if r == -2:
+            raise MemoryError("KV cache is out of pages")
+
+    def publish(self, seq_id: int, tokens):
+        a, n = self._arr(tokens)
+        self.L.b200_kv_seq_publish(self.h, seq_id, a, n)
+
+    def length(self, seq_id: int) -> int:
+        return self.L.b200_kv_seq_len(self.h, seq_id)
+
+    def pages(self, seq_id: int) -> list[int]:
+        n = self.L.b200_kv_seq_n_pages(self.h, seq_id)
+        if n < 0:
+            raise KeyError(f"unknown sequence {seq_id}")
+        buf = (ctypes.c_int32 * max(n, 1))()
+        self.L.b200_kv_seq_pages(self.h, seq_id, buf, n)
+        return list(buf[:n])
+
+    def truncate(self, seq_id: int, new_len: int):
+        if self.L.b200_kv_seq_truncate(self.h, seq_id, new_len) != 0:
+            raise ValueError("bad truncate")
+
+    def end(self, seq_id: int):
+        self.L.b200_kv_seq_end(self.h, seq_id)
+
+    @property
+    def free_pages(self) -> int:
+        return self.L.b200_kv_free_pages(self.h)
+
+    @property
+    def prefix_stats(self) -> tuple[int, int]:
+        return self.L.b200_kv_prefix_hits(self.h), self.L.b200_kv_prefix_lookups(self.h)
+
+    def __del__(self):
+        try:
+            self.L.b200_kv_destroy(self.h)
+        except Exception:
+            pass
+
+
+@dataclass
+class _Layer:
+    attn_norm: torch.Tensor
+    wqkv: QWeight
+    bqkv: torch.Tensor | None
+    wo: QWeight
+    bo: torch.Tensor | None
+    sinks: torch.Tensor | None
+    ffn_norm: torch.Tensor
+    wgu: QWeight | None
+    wdown: QWeight | None
+    window: int
+
+
+def _f32(src: WeightSource, name: str) -> torch.Tensor | None:
+    if not src.has(name):
+        return None
+    return src.get(name).to_float().contiguous()
+
+
+class LlamaEngine:
+    def __init__(self, cfg: ModelConfig, src: WeightSource, device="cuda", max_batch: int = 64,
+                 max_ctx: int = 4096, n_pages: int | None = None, tp_rank: int = 0, tp_world: int = 1,
+                 max_tokens: int = 4096, comm=None):
+        if cfg.arch != "llama":
+            raise ValueError("LlamaEngine serves dense llama-family models")
+        self.cfg, self.device = cfg, torch.device(device)
+        self.rank, self.world, self.comm = tp_rank, tp_world, comm
+        if cfg.n_kv_heads % tp_world or cfg.ffn % tp_world:
+            raise ValueError("tensor-parallel degree must divide the KV heads and the FFN width")
+        self.Hq, self.Hkv, self.hd = cfg.n_heads // tp_world, cfg.n_kv_heads // tp_world, cfg.head_dim
+        self.F = cfg.ffn // tp_world
+        self.d = cfg.d_model
+        self.max_batch, self.max_tokens = max_batch, max_tokens
+        self.max_pages = (max_ctx + PAGE - 1) // PAGE
+        self.n_pages = n_pages if n_pages is not None else max_batch * self.max_pages + 1
+        self.pool = KVPool(self.n_pages)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._load(src)
+        self._alloc()
+        self._graphs: dict[int, tuple] = {}
+        self.launches_per_decode = 0
+
+    # ------------------------------------------------------------------ weights
+    def _shard_rows(self, r: RawTensor, per_head_rows: int | None = None) -> RawTensor:
+        n = r.shape[0] // self.world
+        return r.rows(self.rank * n, (self.rank + 1) * n)
+
+    def _shard_cols(self, r: RawTensor) -> RawTensor:
+        k = r.shape[1] // self.world
+        return r.cols(self.rank * k, (self.rank + 1) * k) if self.world > 1 else r
+
+    def _load(self, src: WeightSource):
+        cfg, dev = self.cfg, self.device
+        emb = src.get("token_embd.weight")
+        self.emb = QWeight.from_raw(emb)
+        self.emb_type = {ops.WT_Q6KR: ops.EMB_Q6KR, ops.WT_Q8R: ops.EMB_Q8R, ops.WT_BF16: ops.EMB_BF16}.get(self.emb.wt)
+        if self.emb_type is None:
+            # Q4_K / MXFP4 tables are not gathered directly; keep them as bf16.
+            x = emb.to_float().to(torch.bfloat16).contiguous()
+            self.emb = QWeight(ops.WT_BF16, x.shape[0], x.shape[1], x, None, emb.type, shadow=x)
+            self.emb_type = ops.EMB_BF16
+        self.layers: list[_Layer] = []
+        for i in range(cfg.n_layers):
+            p = f"blk.{i}."
+            q, k, v = (self._shard_rows(src.get(p + n + ".weight")) for n in ("attn_q", "attn_k", "attn_v"))
+            wqkv = QWeight.from_raw(RawTensor.cat_rows([q, k, v]))
+            bqkv = None
+            if src.has(p + "attn_q.bias"):
+                bqkv = torch.cat([self._shard_rows(src.get(p + n + ".bias")).to_float() for n in ("attn_q", "attn_k", "attn_v")]).contiguous()
+            wo = QWeight.from_raw(self._shard_cols(src.get(p + "attn_output.weight")))
+            bo = _f32(src, p + "attn_output.bias")
+            sinks = _f32(src, p + "attn_sinks.weight")
+            if sinks is not None and self.world > 1:
+                sinks = sinks[self.rank * self.Hq:(self.rank + 1) * self.Hq].contiguous()
+            g = self._shard_rows(src.get(p + "ffn_gate.weight"))
+            u = self._shard_rows(src.get(p + "ffn_up.weight"))
+            wgu = QWeight.from_raw(RawTensor.cat_rows([g, u]))
+            wdown = QWeight.from_raw(self._shard_cols(src.get(p + "ffn_down.weight")))
+            self.layers.append(_Layer(_f32(src, p + "attn_norm.weight"), wqkv, bqkv, wo, bo, sinks,
+                                      _f32(src, p + "ffn_norm.weight"), wgu, wdown,
+                                      cfg.sliding_window if cfg.layer_uses_window(i) else 0))
+        self.out_norm = _f32(src, "output_norm.weight")
+        out = src.get("token_embd.weight" if cfg.tied_embeddings else "output.weight")
+        self.V_local = out.shape[0] // self.world if out.shape[0] % self.world == 0 else out.shape[0]
+        self.vocab_sharded = self.world > 1 and out.shape[0] % self.world == 0
+        if self.vocab_sharded:
+            out = out.rows(self.rank * self.V_local, (self.rank + 1) * self.V_local)
+        self.wout = QWeight.from_raw(out)
+        torch.cuda.synchronize(dev)
+
+    def weight_bytes(self) -> int:
+        n = self.wout.nbytes()
+        for l in self.layers:
+            n += l.wqkv.nbytes() + l.wo.nbytes() + l.wgu.nbytes() + l.wdown.nbytes()
+        return n
+
+    # ------------------------------------------------------------------ workspaces
+    def _alloc(self):
+        dev, T = self.device, self.max_tokens
+        f32 = dict(dtype=torch.float32, device=dev)
+        d, qd, kvd, F = self.d, self.Hq * self.hd, self.Hkv * self.hd, self.F
+        self.qkv_dim = qd + 2 * kvd
+        self.kc = [torch.zeros((self.n_pages, self.Hkv, PAGE, self.hd), dtype=torch.float16, device=dev) for _ in self.layers]
+        self.vc = [torch.zeros_like(k) for k in self.kc]
+        self.x = torch.empty((T, d), **f32)
+        self.qkv = torch.empty((T, self.qkv_dim), **f32)
+        self.q32 = torch.empty((max(self.max_batch, 1), qd), **f32)
+        self.q16 = torch.empty((T, qd), dtype=torch.float16, device=dev)
+        self.hb = torch.empty((T, max(d, qd, F)), dtype=torch.bfloat16, device=dev)
+        self.gu = torch.empty((T, 2 * F), **f32)
+        self.logits = torch.empty((self.max_batch, self.V_local), **f32)
+        kmax = max(d, qd, F)
+        nb = MATVEC_MAX_TOKENS
+        self.xq = torch.empty((nb, kmax), dtype=torch.int8, device=dev)
+        self.xd = torch.empty((nb, kmax // 32 + 1), **f32)
+        self.xs = torch.empty((nb, kmax // 16 + 2), **f32)
+        self.xf = torch.empty((nb, kmax), **f32)
+        # second activation set: a kernel never writes the buffers it is still reading
+        self.fq = torch.empty((nb, kmax), dtype=torch.int8, device=dev)
+        self.fd = torch.empty((nb, kmax // 32 + 1), **f32)
+        self.fs = torch.empty((nb, kmax // 16 + 2), **f32)
+        self.ids = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.pos = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.slot = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.page_table = torch.zeros((self.max_batch, self.max_pages), dtype=torch.int32, device=dev)
+        self.seq_lens = torch.zeros(self.max_batch, dtype=torch.int32, device=dev)
+        self.q_start = torch.zeros(self.max_batch, dtype=torch.int32, device=dev)
+        self.q_len = torch.zeros(self.max_batch, dtype=torch.int32, device=dev)
+        self.out_ids = torch.zeros(self.max_batch, dtype=torch.int32, device=dev)
+        self.out_val = torch.zeros(self.max_batch, **f32)
+        self.max_splits = 64
+        self.attn_scratch = torch.empty(ops.attn_decode_scratch_floats(self.max_batch, self.Hq, self.Hkv, self.hd, self.max_splits), **f32)
+        self.attn_counters = torch.zeros(self.max_batch * self.Hkv, dtype=torch.int32, device=dev)
+        wmax = max(max(l.wqkv.N * l.wqkv.K, l.wgu.N * l.wgu.K, l.wo.N * l.wo.K, l.wdown.N * l.wdown.K) for l in self.layers)
+        self._wscratch_elems = wmax
+        self._wscratch = None
+        self.use_shadow = True
+
+    def _dense(self, w: QWeight) -> torch.Tensor:
+        """bf16 [N][K] form of a weight for the tensor-core GEMM."""
+        if w.wt == ops.WT_BF16:
+            return w.main
+        if self.use_shadow:
+            return w.ensure_shadow()
+        if self._wscratch is None:
+            self._wscratch = torch.empty(self._wscratch_elems, dtype=torch.bfloat16, device=self.device)
+        out = self._wscratch[: w.N * w.K].view(w.N, w.K)
+        return w.dequant_into(out)
+
+    # ------------------------------------------------------------------ building blocks
+    def _splits(self, B: int, ctx_pages: int) -> int:
+        want = max(1, (2 * 148 + B * self.Hkv - 1) // (B * self.Hkv))
+        return max(1, min(self.max_splits, want, ctx_pages))
+
+    def _all_reduce(self, t: torch.Tensor):
+        if self.world > 1:
+            self.comm.all_reduce(t)
+
+    def _layers_small(self, nb: int, max_ctx_pages: int):
+        """<= 8 tokens, one per sequence: quantized mat-vec path."""
+        cfg, x = self.cfg, self.x[:nb]
+        S = self._splits(nb, max_ctx_pages)
+        qd = self.Hq * self.hd
+        style = 0 if cfg.rope_style == "pairs" else 1
+        n = 0
+        for li, L in enumerate(self.layers):
+            q8 = L.wqkv.quantized
+            ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, xq=self.xq if q8 else None, xd=self.xd, xs16=self.xs,
+                        hf=None if q8 else self.xf)
+            ops.matvec(L.wqkv.wt, L.wqkv.main, L.wqkv.plane2, L.wqkv.N, L.wqkv.K, nb, xq=self.xq, xd=self.xd,
+                       xs16=self.xs, xf=self.xf, epi=ops.EPI_STORE, bias=L.bqkv, y=self.qkv, ldy=self.qkv_dim)
+            ops.rope_kv(self.qkv[:nb], self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv,
+                        self.hd, PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd))
+            oq8 = L.wo.quantized
+            ops.attn_decode(self.q32, self.kc[li], self.vc[li], self.page_table, self.seq_lens, nb, self.Hq, self.Hkv,
+                            self.hd, window=L.window, S=S, sinks=L.sinks, out_f32=None if oq8 else self.xf,
+                            oq=self.xq if oq8 else None, od=self.xd, os16=self.xs, scratch=self.attn_scratch,
+                            counters=self.attn_counters)
+            if self.world == 1:
+                ops.matvec(L.wo.wt, L.wo.main, L.wo.plane2, L.wo.N, L.wo.K, nb, xq=self.xq, xd=self.xd, xs16=self.xs,
+                           xf=self.xf, epi=ops.EPI_RESID, bias=L.bo, resid=x, y=x, ldy=self.d)
+            else:
+                self.comm.matvec_allreduce(L.wo, nb, self.xq, self.xd, self.xs, self.xf, x, self.d, bias=L.bo)
+            g8 = L.wgu.quantized
+            ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, xq=self.xq if g8 else None, xd=self.xd, xs16=self.xs,
+                        hf=None if g8 else self.xf)
+            d8 = L.wdown.quantized and self.F % 32 == 0
+            ops.matvec(L.wgu.wt, L.wgu.main, L.wgu.plane2, self.F, L.wgu.K, nb, xq=self.xq, xd=self.xd, xs16=self.xs,
+                       xf=self.xf, epi=ops.EPI_SWIGLU_Q8 if d8 else ops.EPI_SWIGLU_F32, y=self.gu, ldy=self.F,
+                       oq=self.fq, od=self.fd, os16=self.fs)
+            if not d8 and L.wdown.quantized:
+                ops.quantize_x(self.gu.view(-1)[: nb * self.F].view(nb, self.F), self.fq, self.fd, self.fs)
+                n += 1
+            if self.world == 1:
+                ops.matvec(L.wdown.wt, L.wdown.main, L.wdown.plane2, L.wdown.N, L.wdown.K, nb, xq=self.fq, xd=self.fd,
+                           xs16=self.fs, xf=self.gu, epi=ops.EPI_RESID, resid=x, y=x, ldy=self.d)
+            else:
+                self.comm.matvec_allreduce(L.wdown, nb, self.fq, self.fd, self.fs, self.gu, x, self.d)
+            n += 8
+        return n
+
+    def _gemm(self, a_bf16, w: QWeight, M, out_f32=None, out_bf16=None, bias=None, resid_f32=None, ldc=None):
+        ops.gemm_bf16(a_bf16, self._dense(w), M, w.N, w.K, lda=a_bf16.stride(0), ldb=w.K, out_f32=out_f32,
+                      out_bf16=out_bf16, ldc=ldc or w.N, bias=bias, resid_f32=resid_f32, status=self.status)
+
+    def _layers_dense(self, T: int, decode: bool, n_seqs: int, max_q: int, max_ctx_pages: int):
+        """Any token count: tcgen05 GEMM path (prefill chunks and large decode batches)."""
+        cfg, x = self.cfg, self.x[:T]
+        qd = self.Hq * self.hd
+        style = 0 if cfg.rope_style == "pairs" else 1
+        hb_d = self.hb.view(-1)[: T * self.d].view(T, self.d)
+        hb_q = self.hb.view(-1)[: T * qd].view(T, qd)
+        hb_f = self.hb.view(-1)[: T * self.F].view(T, self.F)
+        qkv = self.qkv[:T]
+        gu = self.gu[:T]
+        S = self._splits(n_seqs, max_ctx_pages) if decode else 1
+        n = 0
+        for li, L in enumerate(self.layers):
+            ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, hb=hb_d)
+            self._gemm(hb_d, L.wqkv, T, out_f32=qkv, bias=L.bqkv)
+            if decode:
+                ops.rope_kv(qkv, self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv, self.hd,
+                            PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd))
+                ops.attn_decode(self.q32, self.kc[li], self.vc[li], self.page_table, self.seq_lens, n_seqs, self.Hq,
+                                self.Hkv, self.hd, window=L.window, S=S, sinks=L.sinks, out_bf16=hb_q,
+                                scratch=self.attn_scratch, counters=self.attn_counters)
+            else:
+                ops.rope_kv(qkv, self.pos, self.slot, None, self.q16, self.kc[li], self.vc[li], self.Hq, self.Hkv, self.hd,
+                            PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd))
+                ops.attn_prefill(self.q16, self.kc[li], self.vc[li], self.page_table, self.max_pages, self.q_start,
+                                 self.q_len, self.seq_lens, n_seqs, max_q, self.Hq, self.Hkv, self.hd, window=L.window,
+                                 sinks=L.sinks, out_bf16=hb_q)
+            if self.world == 1:
+                self._gemm(hb_q, L.wo, T, out_f32=x, bias=L.bo, resid_f32=x, ldc=self.d)
+            else:
+                self.comm.gemm_allreduce(hb_q, self._dense(L.wo), T, x, bias=L.bo)
+            ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, hb=hb_d)
+            self._gemm(hb_d, L.wgu, T, out_f32=gu)
+            ops.swiglu(gu, self.F, ob=hb_f)
+            if self.world == 1:
+                self._gemm(hb_f, L.wdown, T, out_f32=x, resid_f32=x, ldc=self.d)
+            else:
+                self.comm.gemm_allreduce(hb_f, self._dense(L.wdown), T, x)
+            n += 9
+        return n
+
+    def _head(self, rows: torch.Tensor, nb: int, greedy: bool = True):
+        """Final norm + LM head on ``nb`` rows of fp32 hidden state -> logits (and arg-max ids)."""
+        cfg = self.cfg
+        n = 2
+        if nb <= MATVEC_MAX_TOKENS:
+            q8 = self.wout.quantized
+            ops.rmsnorm(rows, self.out_norm, cfg.norm_eps, xq=self.xq if q8 else None, xd=self.xd, xs16=self.xs,
+                        hf=None if q8 else self.xf)
+            ops.matvec(self.wout.wt, self.wout.main, self.wout.plane2, self.wout.N, self.wout.K, nb, xq=self.xq,
+                       xd=self.xd, xs16=self.xs, xf=self.xf, epi=ops.EPI_STORE, y=self.logits, ldy=self.V_local)
+        else:
+            hb = self.hb.view(-1)[: nb * self.d].view(nb, self.d)
+            ops.rmsnorm(rows, self.out_norm, cfg.norm_eps, hb=hb)
+            self._gemm(hb, self.wout, nb, out_f32=self.logits)
+        if greedy:
+            ops.argmax(self.logits[:nb], self.out_ids, self.out_val,
+                       vocab_offset=self.rank * self.V_local if self.vocab_sharded else 0)
+            n += 1
+            if self.vocab_sharded:
+                self.comm.argmax_merge(self.out_ids, self.out_val, nb)
+        return n
+
+    def _embed(self, T: int):
+        ops.embedding(self.ids, self.x[:T], self.emb_type, self.emb.main, self.emb.plane2)
+
+    # ------------------------------------------------------------------ host-side batch assembly
+    def _stage_batch(self, seq_ids, new_tokens: list[list[int]]):
+        """Extend the sequences' page lists and build ids/pos/slot/page-table for the new tokens."""
+        ids, pos, slot, q_start, q_len, ctx = [], [], [], [], [], []
+        table = torch.zeros((len(seq_ids), self.max_pages), dtype=torch.int32)
+        for b, (sid, toks) in enumerate(zip(seq_ids, new_tokens)):
+            p0 = self.pool.length(sid)
+            self.pool.extend(sid, len(toks))
+            pages = self.pool.pages(sid)
+            if len(pages) > self.max_pages:
+                raise ValueError("sequence exceeds the engine's max context")
+            table[b, : len(pages)] = torch.tensor(pages, dtype=torch.int32)
+            q_start.append(len(ids))
+            q_len.append(len(toks))
+            ctx.append(p0 + len(toks))
+            for i, t in enumerate(toks):
+                p = p0 + i
+                ids.append(t)
+                pos.append(p)
+                slot.append(pages[p // PAGE] * PAGE + p % PAGE)
+        return ids, pos, slot, q_start, q_len, ctx, table
+
+    def _upload(self, ids, pos, slot, q_start, q_len, ctx, table):
+        T, B = len(ids), len(ctx)
+        pin = lambda v: torch.tensor(v, dtype=torch.int32).pin_memory()
+        self.ids[:T].copy_(pin(ids), non_blocking=True)
+        self.pos[:T].copy_(pin(pos), non_blocking=True)
+        self.slot[:T].copy_(pin(slot), non_blocking=True)
+        self.q_start[:B].copy_(pin(q_start), non_blocking=True)
+        self.q_len[:B].copy_(pin(q_len), non_blocking=True)
+        self.seq_lens[:B].copy_(pin(ctx), non_blocking=True)
+        self.page_table[:B].copy_(table.pin_memory(), non_blocking=True)
+
+    # ------------------------------------------------------------------ public operations
+    def begin(self, seq_id: int, prompt=None) -> int:
+        """Open a sequence; returns how many prompt tokens are already cached (prefix reuse)."""
+        return self.pool.begin(seq_id, list(prompt) if prompt is not None else None)
+
+    def end(self, seq_id: int):
+        self.pool.end(seq_id)
+
+    @torch.no_grad()
+    def forward_tokens(self, seq_ids: list[int], new_tokens: list[list[int]], greedy: bool = True):
+        """Append ``new_tokens[b]`` to sequence ``seq_ids[b]`` and return the logits of each
+        sequence's last new token ([B, V] view, valid until the next call) and their arg-max."""
+        B = len(seq_ids)
+        staged = self._stage_batch(seq_ids, new_tokens)
+        ids, pos, slot, q_start, q_len, ctx, table = staged
+        T = len(ids)
+        if T > self.max_tokens or B > self.max_batch:
+            raise ValueError("batch exceeds the engine's workspace")
+        self._upload(*staged)
+        self._embed(T)
+        decode = all(n == 1 for n in q_len)
+        pages = max((c + PAGE - 1) // PAGE for c in ctx)
+        if decode and T <= MATVEC_MAX_TOKENS:
+            self._layers_small(T, pages)
+        else:
+            self._layers_dense(T, decode, B, max(q_len), pages)
+        if decode:
+            rows = self.x[:B]
+        else:
+            last = torch.tensor([s + n - 1 for s, n in zip(q_start, q_len)], device=self.device)
+            rows = self.x[:T].index_select(0, last).contiguous()
+        self._head(rows, B, greedy)
+        return self.logits[:B], self.out_ids[:B]
+
+    # ---- graph-replayed decode
+    def _capture(self, B: int, pages: int):
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream())
+
+        def body():
+            self._embed(B)
+            n = 1
+            if B <= MATVEC_MAX_TOKENS:
+                n += self._layers_small(B, pages)
+            else:
+                n += self._layers_dense(B, True, B, 1, pages)
+            n += self._head(self.x[:B], B, True)
+            return n
+
+        with torch.cuda.stream(s):
+            body()  # warm-up outside capture: sets kernel attributes, builds shadows
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            n = body()
+        return g, n
+
+    @torch.no_grad()
+    def decode(self, seq_ids: list[int], tokens: list[int], use_graph: bool = True):
+        """One decode step: append one token per sequence, return (logits view, arg-max ids)."""
+        if not use_graph:
+            return self.forward_tokens(seq_ids, [[t] for t in tokens])
+        B = len(seq_ids)
+        staged = self._stage_batch(seq_ids, [[t] for t in tokens])
+        ctx = staged[5]
+        pages = max((c + PAGE - 1) // PAGE for c in ctx)
+        # Split count is baked into the captured launch; bucket the context length so a graph is
+        # reused while the sequence grows.
+        bucket = 1 << max(0, (pages - 1)).bit_length()
+        key = (B, bucket)
+        if key not in self._graphs:
+            self._upload(*staged)
+            self._graphs[key] = self._capture(B, bucket)
+        self._upload(*staged)
+        g, n = self._graphs[key]
+        g.replay()
+        self.launches_per_decode = n
+        return self.logits[:B], self.out_ids[:B]
+
+    def check_status(self):
+        s = int(self.status.item())
+        if s:
+            raise RuntimeError(f"a kernel wait timed out (status {s})")
+
+    @torch.no_grad()
+    def generate(self, prompt: list[int], n_new: int, seq_id: int = 0, use_graph: bool = True):
+        """Greedy generation for one sequence.  Returns (ids, per-step logits [n_new, V] on CPU)."""
+        cached = self.begin(seq_id, prompt)
+        logits, nxt = self.forward_tokens([seq_id], [list(prompt[cached:])])
+        out, all_logits = [], []
+        for _ in range(n_new):
+            all_logits.append(logits[0].float().cpu().clone())
+            tok = int(nxt[0].item())
+            out.append(tok)
+            logits, nxt = self.decode([seq_id], [tok], use_graph=use_graph)
+        self.pool.publish(seq_id, list(prompt) + out)
+        return out, torch.stack(all_logits)

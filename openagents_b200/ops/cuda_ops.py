@@ -1,0 +1,154 @@
+"""Python faces of the sm_100a kernels (ctypes over ``libb200_cuda.so``).
+
+Every function takes torch CUDA tensors, launches on the current torch stream and raises on a
+non-zero return code.  There is no fallback: on a machine with a GPU a missing library is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_size_t, c_void_p
+
+import torch
+
+from .. import _native
+
+WT_Q4KR, WT_Q6KR, WT_Q8R, WT_BF16, WT_MXFP4R = 0, 1, 2, 3, 4
+EPI_STORE, EPI_RESID, EPI_SWIGLU_Q8, EPI_SWIGLU_F32 = 0, 1, 2, 3
+EMB_F32, EMB_BF16, EMB_Q8R, EMB_Q6KR = 0, 1, 2, 3
+ACT_NONE, ACT_GELU = 0, 1
+
+_P = c_void_p
+_SIGS = {
+    "b200_embedding": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, c_int, _P],
+    "b200_rmsnorm": [_P, _P, c_float, c_int, c_int, _P, _P, _P, _P, _P, _P],
+    "b200_quantize_x": [_P, c_int, c_int, _P, _P, _P, _P],
+    "b200_rope_kv": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, _P],
+    "b200_swiglu": [_P, c_int, c_int, _P, _P, _P],
+    "b200_add_inplace": [_P, _P, c_size_t, _P],
+    "b200_argmax": [_P, c_int, c_int, _P, _P, c_int, _P],
+    "b200_sample_topk": [_P, c_int, c_int, c_float, c_int, c_float, _P, _P, _P, _P],
+    "b200_matvec": [c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, _P, _P],
+    "b200_attn_decode": [_P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P,
+                         _P, _P, _P],
+    "b200_attn_prefill": [_P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
+    "b200_gemm_bf16": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, _P, _P],
+    "b200_dequant_bf16": [c_int, _P, _P, _P, c_size_t, c_int, _P],
+    "b200_f32_to_bf16": [_P, _P, c_size_t, _P],
+    "b200_transpose_bf16": [_P, _P, c_int, c_int, _P],
+}
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        L = _native.cuda()
+        for name, args in _SIGS.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        L.b200_attn_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
+        L.b200_attn_decode_scratch_floats.restype = c_size_t
+        _lib = L
+    return _lib
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _st():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
+
+
+def embedding(ids, out, emb_type, w, w2=None, vocab_lo=0, vocab_n=None):
+    T, D = out.shape
+    _check(lib().b200_embedding(_p(ids), _p(out), T, D, emb_type, _p(w), _p(w2), vocab_lo,
+                                vocab_n if vocab_n is not None else 2 ** 31 - 1, _st()), "embedding")
+
+
+def rmsnorm(x, g, eps, xq=None, xd=None, xs16=None, hb=None, hf=None):
+    T, D = x.shape
+    _check(lib().b200_rmsnorm(_p(x), _p(g), eps, T, D, _p(xq), _p(xd), _p(xs16), _p(hb), _p(hf), _st()), "rmsnorm")
+
+
+def quantize_x(x, xq, xd, xs16):
+    T, D = x.shape
+    _check(lib().b200_quantize_x(_p(x), T, D, _p(xq), _p(xd), _p(xs16), _st()), "quantize_x")
+
+
+def rope_kv(qkv, pos, slot, q_out, q_out_h, kc, vc, Hq, Hkv, hd, page_size, theta, style, q_scale):
+    T = qkv.shape[0]
+    _check(lib().b200_rope_kv(_p(qkv), _p(pos), _p(slot), _p(q_out), _p(q_out_h), _p(kc), _p(vc), T, Hq, Hkv, hd,
+                              page_size, theta, style, q_scale, _st()), "rope_kv")
+
+
+def swiglu(gu, F, ob=None, of=None):
+    T = gu.shape[0]
+    _check(lib().b200_swiglu(_p(gu), T, F, _p(ob), _p(of), _st()), "swiglu")
+
+
+def add_inplace(x, y):
+    _check(lib().b200_add_inplace(_p(x), _p(y), x.numel(), _st()), "add_inplace")
+
+
+def argmax(logits, out_id, out_val=None, vocab_offset=0):
+    T, V = logits.shape
+    _check(lib().b200_argmax(_p(logits), T, V, _p(out_id), _p(out_val), vocab_offset, _st()), "argmax")
+
+
+def sample_topk(logits, temperature, top_k, top_p, u, out_id, scratch):
+    T, V = logits.shape
+    _check(lib().b200_sample_topk(_p(logits), T, V, temperature, top_k, top_p, _p(u), _p(out_id), _p(scratch), _st()),
+           "sample_topk")
+
+
+def matvec(wt, w, w2, N, K, nb, xq=None, xd=None, xs16=None, xf=None, epi=EPI_STORE, bias=None, resid=None, y=None,
+           ldy=0, oq=None, od=None, os16=None):
+    _check(lib().b200_matvec(wt, _p(w), _p(w2), N, K, nb, _p(xq), _p(xd), _p(xs16), _p(xf), epi, _p(bias), _p(resid),
+                             _p(y), ldy, _p(oq), _p(od), _p(os16), _st()), "matvec")
+
+
+def attn_decode_scratch_floats(B, Hq, Hkv, hd, S):
+    return lib().b200_attn_decode_scratch_floats(B, Hq, Hkv, hd, S)
+
+
+def attn_decode(q, kc, vc, page_table, seq_lens, B, Hq, Hkv, hd, window=0, S=1, sinks=None, out_f32=None, out_bf16=None,
+                oq=None, od=None, os16=None, scratch=None, counters=None):
+    _check(lib().b200_attn_decode(_p(q), _p(kc), _p(vc), _p(page_table), page_table.shape[1], _p(seq_lens), _p(sinks),
+                                  B, Hq, Hkv, hd, window, S, _p(out_f32), _p(out_bf16), _p(oq), _p(od), _p(os16),
+                                  _p(scratch), _p(counters), _st()), "attn_decode")
+
+
+def attn_prefill(q, kc, vc, page_table, max_pages, q_start, q_len, ctx_len, n_seqs, max_q_len, Hq, Hkv, hd, window=0,
+                 sinks=None, out_bf16=None, out_f32=None, lse=None):
+    _check(lib().b200_attn_prefill(_p(q), _p(kc), _p(vc), _p(page_table), max_pages, _p(q_start), _p(q_len),
+                                   _p(ctx_len), _p(sinks), n_seqs, max_q_len, Hq, Hkv, hd, window, _p(out_bf16),
+                                   _p(out_f32), _p(lse), _st()), "attn_prefill")
+
+
+def gemm_bf16(A, B, M, N, K, lda=None, ldb=None, out_f32=None, out_bf16=None, ldc=None, bias=None, resid_f32=None,
+              resid_bf16=None, act=ACT_NONE, accumulate=False, tile_n=0, status=None):
+    """D[M][N] = A[M][K] @ B[N][K]^T with fused epilogue (see ``gemm_tc05.cu``)."""
+    _check(lib().b200_gemm_bf16(_p(A), _p(B), M, N, K, lda or K, ldb or K, _p(out_f32), _p(out_bf16), ldc or N,
+                                _p(bias), _p(resid_f32), _p(resid_bf16), act, int(accumulate), tile_n, _p(status),
+                                _st()), "gemm_bf16")
+
+
+def dequant_bf16(wt, w, w2, out, N, K):
+    _check(lib().b200_dequant_bf16(wt, _p(w), _p(w2), _p(out), N, K, _st()), "dequant_bf16")
+
+
+def f32_to_bf16(x, y):
+    _check(lib().b200_f32_to_bf16(_p(x), _p(y), x.numel(), _st()), "f32_to_bf16")
+
+
+def transpose_bf16(x, out):
+    R, C = x.shape
+    _check(lib().b200_transpose_bf16(_p(x), _p(out), R, C, _st()), "transpose_bf16")

@@ -1,0 +1,51 @@
+"""Paged KV bookkeeping and prefix sharing (host C++)."""
+import pytest
+
+from openagents_b200.models.engine import KVPool
+
+
+def test_alloc_extend_free():
+    p = KVPool(8, 16)
+    assert p.free_pages == 8
+    assert p.begin(1) == 0
+    p.extend(1, 17)
+    assert p.length(1) == 17 and len(p.pages(1)) == 2 and p.free_pages == 6
+    p.extend(1, 15)
+    assert len(p.pages(1)) == 2
+    p.extend(1, 1)
+    assert len(p.pages(1)) == 3
+    with pytest.raises(MemoryError):
+        p.extend(1, 16 * 6)
+    assert p.length(1) == 33          # a failed extend allocates nothing
+    p.truncate(1, 16)
+    assert len(p.pages(1)) == 1 and p.free_pages == 7
+    p.end(1)
+    assert p.free_pages == 8
+    with pytest.raises(KeyError):
+        p.extend(1, 1)
+
+
+def test_prefix_sharing():
+    p = KVPool(16, 16)
+    toks = list(range(40))
+    assert p.begin(1, toks) == 0
+    p.extend(1, 40)
+    p.publish(1, toks)
+    pages1 = p.pages(1)
+    # same first 32 tokens, different tail: two full pages are shared
+    toks2 = toks[:32] + [999] * 10
+    cached = p.begin(2, toks2)
+    assert cached == 32
+    p.extend(2, len(toks2) - cached)
+    pages2 = p.pages(2)
+    assert pages2[:2] == pages1[:2] and pages2[2] != pages1[2]
+    # an identical prompt never reuses its last token's page: one token is always left to compute
+    assert p.begin(3, toks[:32]) == 16
+    hits, lookups = p.prefix_stats
+    assert hits == 3 and lookups >= 3
+    p.end(1)
+    assert p.pages(2)[:2] == pages1[:2]      # shared pages survive their first owner
+    p.end(2)
+    p.end(3)
+    assert p.free_pages == 16
+    assert p.begin(4, toks) == 0             # nothing cached once every owner is gone
