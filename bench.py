@@ -1,0 +1,236 @@
+#!/usr/bin/env python
+"""Headline benchmark: Llama-3-8B-shape Q4_K GGUF decode throughput (batch 64, plus batch 1 and the
+2048-token prefill TTFT as side metrics) on N B200 GPUs of one node, tensor-parallel for N > 1.
+
+    python bench.py --gpus N --steps K --warmup W
+
+Weights are seeded N(0, 0.02) quantized to Q4_K (embeddings / output Q6_K); prompts are uniform
+random ids; there is no dataset or checkpoint involved.  A "step" is one decode step of the whole
+batch.  The device-timed value replays the engine's self-advancing decode graph (real
+autoregression: each step consumes the previous step's arg-max); the end-to-end value calls the
+public ``engine.decode`` once per step with the step's inputs copied from pinned host memory and
+the sampled ids read back.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+MODEL = "llama-3-8b-shape"
+PROMPT_LEN = 2048
+BATCH = 64
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["not_measured"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def reference_arm():
+    # The reference tree is a TypeScript/Rust monorepo without a Python project or any ML engine:
+    # `pip install /root/reference` stops with "Neither 'setup.py' nor 'pyproject.toml' found".
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "reference has no installable Python package and no inference/training engine "
+                                     "(pip: neither setup.py nor pyproject.toml found)"}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    ap.add_argument("--model", default=MODEL)
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; marks the run invalid)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm()
+        return
+    K, W = args.steps, max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    comm = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        from openagents_b200.parallel.tp import TPComm
+        comm = TPComm(rank, world, dev)
+
+    from openagents_b200.models.config import PRESETS
+    from openagents_b200.models.engine import LlamaEngine, PAGE
+    from openagents_b200.models.qweight import RandomSource
+    from openagents_b200.models.weights import PLAN_Q4_K
+
+    cfg = PRESETS[args.model]
+    valid = True
+    if args.layers:
+        cfg = cfg.with_(n_layers=args.layers)
+        valid = False
+    B, P = args.batch, args.prompt_len
+    total_steps = 2 * (K + W) + 8
+    max_ctx = P + total_steps + PAGE
+    t0 = time.time()
+    eng = LlamaEngine(cfg, RandomSource(cfg, PLAN_Q4_K, 0, dev), device=dev, max_batch=B + 1, max_ctx=max_ctx,
+                      max_tokens=4 * P, tp_rank=rank, tp_world=world, comm=comm)
+    load_s = time.time() - t0
+
+    g = torch.Generator().manual_seed(1234)
+    prompts = torch.randint(0, cfg.vocab, (B + 1, P), generator=g)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- prefill TTFT: one 2048-token prompt, device time of the whole forward incl. first arg-max
+    eng.begin(B)
+    eng.forward_tokens([B], [prompts[B, :64].tolist()])      # warm kernels / shadows on a short chunk
+    eng.end(B)
+    ttft = []
+    for rep in range(3):
+        eng.begin(B)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _, nxt1 = eng.forward_tokens([B], [prompts[B].tolist()])
+        e1.record()
+        barrier()
+        ttft.append(max_over_ranks(e0.elapsed_time(e1)))
+        if rep < 2:
+            eng.end(B)
+    ttft_ms = min(ttft[1:])
+
+    # ---- batch prefill (untimed): 4 sequences per call
+    first = []
+    for b0 in range(0, B, 4):
+        ids = list(range(b0, min(B, b0 + 4)))
+        for i in ids:
+            eng.begin(i)
+        _, nxt = eng.forward_tokens(ids, [prompts[i].tolist() for i in ids])
+        first += nxt.tolist()
+    eng.check_status()
+
+    gpu_index = local
+    # ---- bs1 decode (sequence B, already prefilled)
+    tok1 = [int(nxt1[0].item())]
+    last = eng.decode_steps([B], tok1, W)[W - 1].clone()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = {0: e0}
+    eng.decode_steps([B], [int(last[0].item())], K, on_replay=lambda i: marks[i].record() if i in marks else None)
+    e1.record()
+    barrier()
+    bs1_ms = max_over_ranks(e0.elapsed_time(e1)) / K
+    launches_bs1 = eng.launches_per_decode
+
+    # ---- bs64 decode: device-timed, self-advancing graph
+    seqs = list(range(B))
+    hist = eng.decode_steps(seqs, first, W)
+    last = hist[W - 1].tolist()
+    sampler = ClockSampler(gpu_index)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = {0: e0}
+    hist = eng.decode_steps(seqs, last, K, on_replay=lambda i: marks[i].record() if i in marks else None)
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    dev_ms = max_over_ranks(e0.elapsed_time(e1)) / K
+    launches = eng.launches_per_decode * K
+    last = hist[K - 1].tolist()
+    eng.check_status()
+
+    # ---- bs64 decode end to end through engine.decode(): per step H2D of the inputs, D2H of the ids
+    for _ in range(W):
+        _, nxt = eng.decode(seqs, last)
+        last = nxt.tolist()
+    barrier()
+    t_start = time.perf_counter()
+    for _ in range(K):
+        _, nxt = eng.decode(seqs, last)
+        last = nxt.tolist()                    # device -> host read of the step's result
+    torch.cuda.synchronize()
+    e2e_ms = max_over_ranks((time.perf_counter() - t_start) * 1e3) / K
+    h2d = 4 * (3 * B + 3 * B + B * eng.max_pages)     # ids, pos, slot, q_start, q_len, seq_lens, page table
+    d2h = 4 * B
+    eng.check_status()
+
+    if rank == 0:
+        value = B / (dev_ms * 1e-3)
+        out = {
+            "metric": "llama3_8b_q4k_decode_tok_s_bs64", "value": round(value, 1), "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(dev_ms, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"model": cfg.name, "weights": "Q4_K (embeddings/output Q6_K), seeded N(0,0.02)",
+                       "global_batch": B, "seq_len": P, "decode_context": f"{P}+", "kv_cache": "paged fp16, 16-token pages",
+                       "parallelism": f"tp{world}", "l2": "inputs larger than L2 (weights + KV cache >> 126 MB)",
+                       "valid": valid},
+            "clocks": clocks,
+            "e2e": {"value": round(B / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches,
+            "extra": {"decode_tok_s_bs1": round(1.0 / (bs1_ms * 1e-3), 1), "ms_per_step_bs1": round(bs1_ms, 4),
+                      "launches_per_step_bs1": launches_bs1, "prefill_ttft_ms": round(ttft_ms, 3),
+                      "prefill_tok_s": round(P / (ttft_ms * 1e-3), 1), "load_s": round(load_s, 1),
+                      "weight_bytes_per_gpu": eng.weight_bytes()},
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

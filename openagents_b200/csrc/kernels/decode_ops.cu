@@ -362,3 +362,34 @@ B200_API int b200_sample_topk(const float* logits, int T, int V, float temperatu
   sample_topk_kernel<<<T, 1024, 0, st>>>(logits, V, temperature, top_k, top_p, u, out_id, scratch);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------ device-side autoregression
+
+// Turns a decode step's outputs into the next step's inputs without a host round trip: the
+// sampled id becomes the next input id, position and visible length grow by one, the cache slot
+// is looked up in the (pre-extended) page table, and the id is appended to a history buffer.
+__global__ void decode_advance_kernel(int* __restrict__ ids, const int* __restrict__ out_ids, int* __restrict__ pos,
+                                      int* __restrict__ slot, int* __restrict__ seq_lens,
+                                      const int* __restrict__ page_table, int max_pages, int page_size, int B,
+                                      int* __restrict__ hist, int* __restrict__ step_counter, int hist_cap) {
+  const int step = *step_counter;
+  for (int b = threadIdx.x; b < B; b += blockDim.x) {
+    const int id = out_ids[b];
+    ids[b] = id;
+    const int p = pos[b] + 1;
+    pos[b] = p;
+    seq_lens[b] = p + 1;
+    const int pg = p / page_size;
+    slot[b] = pg < max_pages ? page_table[(size_t)b * max_pages + pg] * page_size + p % page_size : -1;
+    if (hist && step < hist_cap) hist[(size_t)step * B + b] = id;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *step_counter = step + 1;
+}
+B200_API int b200_decode_advance(int* ids, const int* out_ids, int* pos, int* slot, int* seq_lens,
+                                 const int* page_table, int max_pages, int page_size, int B, int* hist,
+                                 int* step_counter, int hist_cap, cudaStream_t st) {
+  decode_advance_kernel<<<1, 256, 0, st>>>(ids, out_ids, pos, slot, seq_lens, page_table, max_pages, page_size, B,
+                                           hist, step_counter, hist_cap);
+  return (int)cudaGetLastError();
+}

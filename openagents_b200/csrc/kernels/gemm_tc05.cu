@@ -137,6 +137,9 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, in
   }
 }
 
+// Persistent kernel: each CTA walks output tiles (m fastest) with a shared-memory ring that keeps
+// running across tiles and two accumulator stages in tensor memory, so the epilogue of one tile
+// overlaps the main loop of the next.
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
                                                          const __grid_constant__ CUtensorMap tmB,
@@ -150,27 +153,32 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   uint64_t* bars = (uint64_t*)(sB + STAGES * B_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
-  uint64_t* tfull = bars + 2 * STAGES;
-  uint32_t* tmem_holder = (uint32_t*)(bars + 2 * STAGES + 1);
+  uint64_t* tfull = bars + 2 * STAGES;       // [2]
+  uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_holder = (uint32_t*)(bars + 2 * STAGES + 4);
   volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   const int KB = (K + BK - 1) / BK;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
       mbar_init(smem_u32(full + s), 1);
       mbar_init(smem_u32(empty + s), 1);
     }
-    mbar_init(smem_u32(tfull), 1);
+    for (int s = 0; s < 2; s++) {
+      mbar_init(smem_u32(tfull + s), 1);
+      mbar_init(smem_u32(tempty + s), 4);
+    }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_holder), BN);
+    tmem_alloc(smem_u32(tmem_holder), 2 * BN);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -180,62 +188,89 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < KB; kb++) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(smem_u32(empty + s), ph ^ 1, abort_flag)) break;
-        mbar_expect_tx(smem_u32(full + s), A_BYTES + B_BYTES);
-        tma_load_2d(smem_u32(sA + s * A_BYTES), &tmA, smem_u32(full + s), kb * BK, m0);
-        tma_load_2d(smem_u32(sB + s * B_BYTES), &tmB, smem_u32(full + s), kb * BK, n0);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < KB; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(smem_u32(empty + s), ph ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(smem_u32(full + s), A_BYTES + B_BYTES);
+          tma_load_2d(smem_u32(sA + s * A_BYTES), &tmA, smem_u32(full + s), kb * BK, m0);
+          tma_load_2d(smem_u32(sB + s * B_BYTES), &tmB, smem_u32(full + s), kb * BK, n0);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_bf16(BM, BN);
+      uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int kb = 0; kb < KB && ok; kb++) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        ok = mbar_wait(smem_u32(full + s), ph, abort_flag);
-        if (!ok) break;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, tcount++) {
+        const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+        if (!mbar_wait(smem_u32(tempty + acc), aph ^ 1, abort_flag)) break;
         tc_fence_after();
-        const uint64_t ad = smem_desc_sw128(smem_u32(sA + s * A_BYTES));
-        const uint64_t bd = smem_desc_sw128(smem_u32(sB + s * B_BYTES));
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < KB; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(smem_u32(full + s), ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t ad = smem_desc_sw128(smem_u32(sA + s * A_BYTES));
+          const uint64_t bd = smem_desc_sw128(smem_u32(sB + s * B_BYTES));
 #pragma unroll
-        for (int k = 0; k < BK / 16; k++)
-          umma_bf16(tmem_base, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-        umma_commit(smem_u32(empty + s));
+          for (int k = 0; k < BK / 16; k++)
+            umma_bf16(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(smem_u32(empty + s));
+        }
+        umma_commit(smem_u32(tfull + acc));   // released even after a failed wait; the flag says why
       }
-      // Always commit to the accumulator barrier so the epilogue is released (with an abort flag
-      // set it will skip the read-back).
-      umma_commit(smem_u32(tfull));
     }
   } else {
-    bool ok = mbar_wait(smem_u32(tfull), 0, abort_flag);
-    ok = __all_sync(0xffffffffu, ok && !*abort_flag);  // tcgen05.ld needs the whole warp
-    tc_fence_after();
-    if (ok) {
-      const int q = warp & 3;
+    const int q = warp & 3;
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, tcount++) {
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+      bool ok = mbar_wait(smem_u32(tfull + acc), aph, abort_flag);
+      ok = __all_sync(0xffffffffu, ok && !*abort_flag);  // tcgen05.ld needs the whole warp
+      if (!ok) break;
+      tc_fence_after();
       const int m = m0 + q * 32 + lane;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + (uint32_t)(c * 32), r);
         tmem_ld_wait();
         if (n0 + c * 32 < N) epilogue_row(epi, m, n0 + c * 32, M, N, r);
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(tempty + acc));
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, BN);
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
   if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, (int)B200_ERR_TIMEOUT_MMA);
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
 }
 
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpi& e, int M, int N, int K,
                        int* status, cudaStream_t st) {
-  constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16;
+  constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16;
   auto kern = gemm_bf16_kernel<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
@@ -243,7 +278,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmE
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  const int n_tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+  const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
   kern<<<grid, 192, smem, st>>>(ta, tb, e, M, N, K, status);
   return (int)cudaGetLastError();
 }

@@ -45,17 +45,50 @@ __device__ __forceinline__ size_t row_bytes(int K) {
   return (size_t)K;  // Q8R
 }
 
-// Dot of one 32-element unit of one weight row against all B tokens.
-template <int WT, int B>
-__device__ __forceinline__ void unit_dot(const uint8_t* __restrict__ wrow, const __half* __restrict__ w2row,
-                                         int u, int U, const uint4* __restrict__ xp0,
-                                         const uint4* __restrict__ xp1, const float* __restrict__ sxd,
-                                         const float2* __restrict__ sxs, float (&acc)[B]) {
+// Raw bytes of one 32-element unit of one weight row, fetched in a load phase that is kept apart
+// from the arithmetic so that many loads are in flight per lane.
+template <int WT>
+struct UnitRaw {
+  uint4 a;      // Q4K-R: header; Q6K-R: low nibbles; Q8-R: first 16 bytes
+  uint4 b;      // Q4K-R: quants; Q6K-R: {T words, scales, d}; Q8-R: second 16 bytes
+  uint32_t c;   // Q8-R: fp16 scale
+};
+
+template <int WT>
+__device__ __forceinline__ UnitRaw<WT> unit_load(const uint8_t* __restrict__ wrow, const __half* __restrict__ w2row,
+                                                 int u) {
+  UnitRaw<WT> r;
   const int sb = u >> 3, j = u & 7;
   if constexpr (WT == WT_Q4KR) {
     const uint8_t* blk = wrow + (size_t)sb * 144;
-    const uint4 hdr = __ldg((const uint4*)blk);
-    const uint4 q = ldg_stream(blk + 16 + j * 16);
+    r.a = __ldg((const uint4*)blk);
+    r.b = ldg_stream(blk + 16 + j * 16);
+    r.c = 0;
+  } else if constexpr (WT == WT_Q6KR) {
+    const uint8_t* blk = wrow + (size_t)sb * 208;
+    r.a = ldg_stream(blk + j * 16);
+    const uint2 tw = ldg_stream2(blk + 128 + j * 8);
+    r.b.x = tw.x;
+    r.b.y = tw.y;
+    r.b.z = ((const uint16_t*)(blk + 192))[j];
+    r.b.w = __half_as_ushort(w2row[sb]);
+    r.c = 0;
+  } else {
+    r.a = ldg_stream(wrow + (size_t)u * 32);
+    r.b = ldg_stream(wrow + (size_t)u * 32 + 16);
+    r.c = __half_as_ushort(w2row[u]);
+  }
+  return r;
+}
+
+// Dot of one loaded unit against all B tokens.
+template <int WT, int B>
+__device__ __forceinline__ void unit_dot(const UnitRaw<WT>& r, int u, int U, const uint4* __restrict__ xp0,
+                                         const uint4* __restrict__ xp1, const float* __restrict__ sxd,
+                                         const float2* __restrict__ sxs, float (&acc)[B]) {
+  const int j = u & 7;
+  if constexpr (WT == WT_Q4KR) {
+    const uint4 hdr = r.a, q = r.b;
     const int sh = 8 * (j & 3);
     const uint32_t b0 = (hdr.y >> sh) & 0xFF, b1 = (hdr.z >> sh) & 0xFF, b2 = (hdr.w >> sh) & 0xFF;
     const uint32_t sc = j < 4 ? (b0 & 63) : ((b2 & 0xF) | ((b0 >> 6) << 4));
@@ -81,11 +114,10 @@ __device__ __forceinline__ void unit_dot(const uint8_t* __restrict__ wrow, const
       acc[b] += a * sxd[b * U + u] * (float)s - m * (xs.x + xs.y);
     }
   } else if constexpr (WT == WT_Q6KR) {
-    const uint8_t* blk = wrow + (size_t)sb * 208;
-    const uint4 lo = ldg_stream(blk + j * 16);
-    const uint2 tw = ldg_stream2(blk + 128 + j * 8);
-    const uint32_t scw = ((const uint16_t*)(blk + 192))[j];
-    const float d = __half2float(w2row[sb]);
+    const uint4 lo = r.a;
+    const uint2 tw = make_uint2(r.b.x, r.b.y);
+    const uint32_t scw = r.b.z;
+    const float d = __half2float(__ushort_as_half((unsigned short)r.b.w));
     const float sc0 = d * (float)(int8_t)(scw & 0xFF), sc1 = d * (float)(int8_t)(scw >> 8);
     const uint32_t m4 = 0x0F0F0F0Fu, m2 = 0x03030303u;
     const uint32_t a0 = (lo.x & m4) | ((tw.x & m2) << 4), a1 = ((lo.x >> 4) & m4) | (((tw.x >> 2) & m2) << 4);
@@ -108,8 +140,8 @@ __device__ __forceinline__ void unit_dot(const uint8_t* __restrict__ wrow, const
       acc[b] += sc0 * (xd * (float)s0 - 32.f * xs.x) + sc1 * (xd * (float)s1 - 32.f * xs.y);
     }
   } else {  // WT_Q8R
-    const uint4 q0 = ldg_stream(wrow + (size_t)u * 32), q1 = ldg_stream(wrow + (size_t)u * 32 + 16);
-    const float d = __half2float(w2row[u]);
+    const uint4 q0 = r.a, q1 = r.b;
+    const float d = __half2float(__ushort_as_half((unsigned short)r.c));
 #pragma unroll
     for (int b = 0; b < B; b++) {
       const uint4 x0 = xp0[b * U + u], x1 = xp1[b * U + u];
@@ -190,31 +222,52 @@ __global__ void __launch_bounds__(256) matvec_q_kernel(const MatvecArgs a) {
 
   const size_t rb = row_bytes<WT>(a.K);
   const int w2_per_row = (WT == WT_Q6KR) ? a.K / 256 : U;
-#pragma unroll 1
-  for (int i = 0; i < 4; i++) {
-    const int r = w + 8 * i;
-    const int n = blockIdx.x * 32 + r;
-    float acc0[B], acc1[B];
+  constexpr int RW = 4;             // rows per warp
+  constexpr int NM = DUAL ? 2 : 1;  // matrices
+  float acc[NM][RW][B];
 #pragma unroll
-    for (int b = 0; b < B; b++) acc0[b] = acc1[b] = 0.f;
-    if (n < a.N) {
-      const uint8_t* wr0 = a.w + (size_t)n * rb;
-      const __half* w20 = a.w2 ? a.w2 + (size_t)n * w2_per_row : nullptr;
-      const uint8_t* wr1 = a.w + (size_t)(n + a.N) * rb;
-      const __half* w21 = a.w2 ? a.w2 + (size_t)(n + a.N) * w2_per_row : nullptr;
-#pragma unroll 4
-      for (int u = lane; u < U; u += 32) {
-        unit_dot<WT, B>(wr0, w20, u, U, xp0, xp1, sxd, sxs, acc0);
-        if (DUAL) unit_dot<WT, B>(wr1, w21, u, U, xp0, xp1, sxd, sxs, acc1);
-      }
+  for (int mi = 0; mi < NM; mi++)
+#pragma unroll
+    for (int i = 0; i < RW; i++)
+#pragma unroll
+      for (int b = 0; b < B; b++) acc[mi][i][b] = 0.f;
+  const uint8_t* wr[NM][RW];
+  const __half* w2r[NM][RW];
+  bool live[RW];
+#pragma unroll
+  for (int i = 0; i < RW; i++) {
+    const int n = blockIdx.x * 32 + w + 8 * i;
+    live[i] = n < a.N;
+    const int nn = live[i] ? n : 0;
+#pragma unroll
+    for (int mi = 0; mi < NM; mi++) {
+      wr[mi][i] = a.w + (size_t)(nn + mi * a.N) * rb;
+      w2r[mi][i] = a.w2 ? a.w2 + (size_t)(nn + mi * a.N) * w2_per_row : nullptr;
     }
+  }
+  // Load phase (all rows of the warp, both matrices) then compute phase, per 32-unit column block.
+#pragma unroll 2
+  for (int u = lane; u < U; u += 32) {
+    UnitRaw<WT> raw[NM][RW];
+#pragma unroll
+    for (int mi = 0; mi < NM; mi++)
+#pragma unroll
+      for (int i = 0; i < RW; i++) raw[mi][i] = unit_load<WT>(wr[mi][i], w2r[mi][i], u);
+#pragma unroll
+    for (int mi = 0; mi < NM; mi++)
+#pragma unroll
+      for (int i = 0; i < RW; i++) unit_dot<WT, B>(raw[mi][i], u, U, xp0, xp1, sxd, sxs, acc[mi][i]);
+  }
+#pragma unroll
+  for (int i = 0; i < RW; i++) {
+    const int r = w + 8 * i;
 #pragma unroll
     for (int b = 0; b < B; b++) {
-      float v0 = warp_sum(acc0[b]);
-      if (lane == 0) res[r * B + b] = v0;
+      float v0 = warp_sum(acc[0][i][b]);
+      if (lane == 0) res[r * B + b] = live[i] ? v0 : 0.f;
       if (DUAL) {
-        float v1 = warp_sum(acc1[b]);
-        if (lane == 0) res[32 * B + r * B + b] = v1;
+        float v1 = warp_sum(acc[NM - 1][i][b]);
+        if (lane == 0) res[32 * B + r * B + b] = live[i] ? v1 : 0.f;
       }
     }
   }

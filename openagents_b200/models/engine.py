@@ -286,7 +286,7 @@ class LlamaEngine:
             ops.attn_decode(self.q32, self.kc[li], self.vc[li], self.page_table, self.seq_lens, nb, self.Hq, self.Hkv,
                             self.hd, window=L.window, S=S, sinks=L.sinks, out_f32=None if oq8 else self.xf,
                             oq=self.xq if oq8 else None, od=self.xd, os16=self.xs, scratch=self.attn_scratch,
-                            counters=self.attn_counters)
+                            counters=self.attn_counters, status=self.status)
             if self.world == 1:
                 ops.matvec(L.wo.wt, L.wo.main, L.wo.plane2, L.wo.N, L.wo.K, nb, xq=self.xq, xd=self.xd, xs16=self.xs,
                            xf=self.xf, epi=ops.EPI_RESID, bias=L.bo, resid=x, y=x, ldy=self.d)
@@ -334,7 +334,7 @@ class LlamaEngine:
                             PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd))
                 ops.attn_decode(self.q32, self.kc[li], self.vc[li], self.page_table, self.seq_lens, n_seqs, self.Hq,
                                 self.Hkv, self.hd, window=L.window, S=S, sinks=L.sinks, out_bf16=hb_q,
-                                scratch=self.attn_scratch, counters=self.attn_counters)
+                                scratch=self.attn_scratch, counters=self.attn_counters, status=self.status)
             else:
                 ops.rope_kv(qkv, self.pos, self.slot, None, self.q16, self.kc[li], self.vc[li], self.Hq, self.Hkv, self.hd,
                             PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd))
@@ -448,7 +448,7 @@ class LlamaEngine:
         return self.logits[:B], self.out_ids[:B]
 
     # ---- graph-replayed decode
-    def _capture(self, B: int, pages: int):
+    def _capture(self, B: int, pages: int, advance: bool = False):
         g = torch.cuda.CUDAGraph()
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream())
@@ -461,10 +461,20 @@ class LlamaEngine:
             else:
                 n += self._layers_dense(B, True, B, 1, pages)
             n += self._head(self.x[:B], B, True)
+            if advance:
+                ops.decode_advance(self.ids, self.out_ids, self.pos, self.slot, self.seq_lens, self.page_table, PAGE, B,
+                                   self._hist, self._step, self._hist.numel() // B)
+                n += 1
             return n
 
+        if advance:   # the warm-up run must not move the real state: save and restore it
+            saved = [t.clone() for t in (self.ids, self.pos, self.slot, self.seq_lens, self._step)]
         with torch.cuda.stream(s):
             body()  # warm-up outside capture: sets kernel attributes, builds shadows
+        if advance:
+            torch.cuda.synchronize()
+            for t, v in zip((self.ids, self.pos, self.slot, self.seq_lens, self._step), saved):
+                t.copy_(v)
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         with torch.cuda.graph(g, stream=s):
@@ -492,6 +502,42 @@ class LlamaEngine:
         g.replay()
         self.launches_per_decode = n
         return self.logits[:B], self.out_ids[:B]
+
+    @torch.no_grad()
+    def decode_steps(self, seq_ids: list[int], tokens: list[int], n_steps: int, on_replay=None):
+        """``n_steps`` greedy decode steps with the autoregression kept on the device: one upload,
+        ``n_steps`` graph replays (each ends by turning its arg-max into the next step's input),
+        one read-back.  Returns the generated ids as an int32 tensor [n_steps, B] (on the device).
+        ``on_replay(i)`` is called before replay ``i`` (benchmarks place their events there)."""
+        B = len(seq_ids)
+        staged = self._stage_batch(seq_ids, [[t] for t in tokens])
+        ctx = staged[5]
+        table = staged[6]
+        for b, sid in enumerate(seq_ids):        # pages for every later step up front
+            self.pool.extend(sid, n_steps - 1)
+            pages = self.pool.pages(sid)
+            if len(pages) > self.max_pages:
+                raise ValueError("sequence exceeds the engine's max context")
+            table[b, : len(pages)] = torch.tensor(pages, dtype=torch.int32)
+        pages = max((c + n_steps + PAGE - 1) // PAGE for c in ctx)
+        bucket = 1 << max(0, (pages - 1)).bit_length()
+        key = ("loop", B, bucket)
+        if getattr(self, "_hist", None) is None or self._hist.numel() < n_steps * B:
+            self._hist = torch.zeros(max(n_steps * B, 4096), dtype=torch.int32, device=self.device)
+            self._step = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self._graphs = {k: v for k, v in self._graphs.items() if not (isinstance(k, tuple) and k[0] == "loop")}
+        if key not in self._graphs:
+            self._upload(*staged)
+            self._graphs[key] = self._capture(B, bucket, advance=True)
+        self._upload(*staged)
+        self._step.zero_()
+        g, n = self._graphs[key]
+        for i in range(n_steps):
+            if on_replay is not None:
+                on_replay(i)
+            g.replay()
+        self.launches_per_decode = n
+        return self._hist[: n_steps * B].view(n_steps, B)
 
     def check_status(self):
         s = int(self.status.item())

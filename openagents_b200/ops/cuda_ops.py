@@ -28,13 +28,14 @@ _SIGS = {
     "b200_argmax": [_P, c_int, c_int, _P, _P, c_int, _P],
     "b200_sample_topk": [_P, c_int, c_int, c_float, c_int, c_float, _P, _P, _P, _P],
     "b200_matvec": [c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, _P, _P],
-    "b200_attn_decode": [_P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P,
-                         _P, _P, _P],
+    "b200_attn_decode": [_P, _P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
+                         _P, _P, _P, _P, _P],
     "b200_attn_prefill": [_P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
     "b200_gemm_bf16": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, _P, _P],
     "b200_dequant_bf16": [c_int, _P, _P, _P, c_size_t, c_int, _P],
     "b200_f32_to_bf16": [_P, _P, c_size_t, _P],
     "b200_transpose_bf16": [_P, _P, c_int, c_int, _P],
+    "b200_decode_advance": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, _P, c_int, _P],
 }
 
 _lib = None
@@ -120,10 +121,10 @@ def attn_decode_scratch_floats(B, Hq, Hkv, hd, S):
 
 
 def attn_decode(q, kc, vc, page_table, seq_lens, B, Hq, Hkv, hd, window=0, S=1, sinks=None, out_f32=None, out_bf16=None,
-                oq=None, od=None, os16=None, scratch=None, counters=None):
-    _check(lib().b200_attn_decode(_p(q), _p(kc), _p(vc), _p(page_table), page_table.shape[1], _p(seq_lens), _p(sinks),
+                oq=None, od=None, os16=None, scratch=None, counters=None, status=None):
+    _check(lib().b200_attn_decode(_p(q), _p(kc), _p(vc), _p(page_table), page_table.shape[1], kc.shape[0], _p(seq_lens), _p(sinks),
                                   B, Hq, Hkv, hd, window, S, _p(out_f32), _p(out_bf16), _p(oq), _p(od), _p(os16),
-                                  _p(scratch), _p(counters), _st()), "attn_decode")
+                                  _p(scratch), _p(counters), _p(status), _st()), "attn_decode")
 
 
 def attn_prefill(q, kc, vc, page_table, max_pages, q_start, q_len, ctx_len, n_seqs, max_q_len, Hq, Hkv, hd, window=0,
@@ -152,3 +153,9 @@ def f32_to_bf16(x, y):
 def transpose_bf16(x, out):
     R, C = x.shape
     _check(lib().b200_transpose_bf16(_p(x), _p(out), R, C, _st()), "transpose_bf16")
+
+
+def decode_advance(ids, out_ids, pos, slot, seq_lens, page_table, page_size, B, hist, step_counter, hist_cap):
+    _check(lib().b200_decode_advance(_p(ids), _p(out_ids), _p(pos), _p(slot), _p(seq_lens), _p(page_table),
+                                     page_table.shape[1], page_size, B, _p(hist), _p(step_counter), hist_cap, _st()),
+           "decode_advance")

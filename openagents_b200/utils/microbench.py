@@ -1,0 +1,161 @@
+"""Per-kernel timing against the measured roofline.
+
+    python -m openagents_b200.utils.microbench [matvec|attn|gemm|all]
+
+Each case is timed with CUDA events after warm-up, with a buffer larger than L2 written between
+iterations so operands are read from HBM.  Fractions are "of measured": achieved bytes/s over the
+copy bandwidth and achieved FLOP/s over the cuBLAS bf16 throughput recorded in MEASURED_PEAKS.json
+(fallback 6650 GB/s and 1590 TFLOP/s when the file is absent).
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import sys
+
+import torch
+
+from ..gguf import GgmlType
+from ..gguf import torch_codecs as tc
+from ..models.qweight import QWeight, RawTensor
+from ..ops import cuda_ops as ops
+
+DEV = "cuda"
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    _flush.fill_(1)
+
+
+def timeit(fn, iters=20, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2] * 1e-3
+
+
+def _rand_q(N, K, t):
+    x = torch.randn(N, K, device=DEV) * 0.02
+    return QWeight.from_raw(RawTensor(t, (N, K), tc.quantize(x, t)))
+
+
+def bench_matvec(rows):
+    hbm, _, tag = peaks()
+    a = torch.zeros(32, device=DEV)
+    b = torch.zeros(32, device=DEV)
+    rows.append(f"event-pair floor (32-element add kernel): {timeit(lambda: ops.add_inplace(a, b))*1e6:6.1f} us")
+    shapes = [("qkv", 6144, 4096, GgmlType.Q4_K, False), ("o", 4096, 4096, GgmlType.Q4_K, False),
+              ("gate_up", 14336, 4096, GgmlType.Q4_K, True), ("down", 4096, 14336, GgmlType.Q4_K, False),
+              ("lm_head", 128256, 4096, GgmlType.Q6_K, False)]
+    for name, N, K, t, dual in shapes:
+        w = _rand_q(N * (2 if dual else 1), K, t)
+        for nb in (1, 4, 8):
+            x = torch.randn(nb, K, device=DEV)
+            xq = torch.empty((nb, K), dtype=torch.int8, device=DEV)
+            xd = torch.empty((nb, K // 32), device=DEV)
+            xs = torch.empty((nb, K // 16), device=DEV)
+            ops.quantize_x(x, xq, xd, xs)
+            y = torch.zeros((nb, N), device=DEV)
+            oq, od, os16 = torch.empty((nb, N), dtype=torch.int8, device=DEV), torch.empty((nb, N // 32), device=DEV), torch.empty((nb, N // 16), device=DEV)
+            if dual:
+                fn = lambda: ops.matvec(w.wt, w.main, w.plane2, N, K, nb, xq=xq, xd=xd, xs16=xs, epi=ops.EPI_SWIGLU_Q8, oq=oq, od=od, os16=os16)
+            else:
+                fn = lambda: ops.matvec(w.wt, w.main, w.plane2, N, K, nb, xq=xq, xd=xd, xs16=xs, epi=ops.EPI_STORE, y=y, ldy=N)
+            s = timeit(fn)
+            gbs = w.nbytes() / s / 1e9
+            rows.append(f"matvec {name:8s} N={N:6d} K={K:5d} {t.name} nb={nb}: {s*1e6:8.1f} us  {gbs:7.0f} GB/s  {gbs/hbm:5.2f} of {tag} HBM")
+
+
+def bench_attn(rows):
+    hbm, _, tag = peaks()
+    Hq, Hkv, hd = 32, 8, 128
+    for B, ctx in ((1, 2304), (8, 2304), (64, 2304)):
+        pages = (ctx + 15) // 16
+        n_pages = B * pages + 1
+        kc = torch.randn((n_pages, Hkv, 16, hd), device=DEV).half()
+        vc = torch.randn((n_pages, Hkv, 16, hd), device=DEV).half()
+        table = (torch.arange(B * pages, dtype=torch.int32, device=DEV).view(B, pages) + 1)
+        lens = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
+        q = torch.randn(B, Hq * hd, device=DEV) / math.sqrt(hd)
+        out = torch.empty((B, Hq * hd), dtype=torch.bfloat16, device=DEV)
+        for S in ((1, 4, 9, 18, 36) if B == 1 else (1, 2, 5) if B == 8 else (1, 2, 4)):
+            scratch = torch.empty(ops.attn_decode_scratch_floats(B, Hq, Hkv, hd, S), device=DEV)
+            counters = torch.zeros(B * Hkv, dtype=torch.int32, device=DEV)
+            fn = lambda: ops.attn_decode(q, kc, vc, table, lens, B, Hq, Hkv, hd, S=S, out_bf16=out, scratch=scratch, counters=counters)
+            s = timeit(fn)
+            byts = 2 * B * ctx * Hkv * hd * 2
+            rows.append(f"attn_decode B={B:3d} ctx={ctx} S={S:2d}: {s*1e6:8.1f} us  {byts/s/1e9:7.0f} GB/s  {byts/s/1e9/hbm:5.2f} of {tag} HBM")
+    # prefill
+    for T in (2048,):
+        pages = (T + 15) // 16
+        kc = torch.randn((pages + 1, Hkv, 16, hd), device=DEV).half()
+        vc = torch.randn((pages + 1, Hkv, 16, hd), device=DEV).half()
+        table = (torch.arange(pages, dtype=torch.int32, device=DEV).view(1, pages) + 1)
+        q = (torch.randn(T, Hq * hd, device=DEV) / math.sqrt(hd)).half()
+        out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=DEV)
+        z = torch.zeros(1, dtype=torch.int32, device=DEV)
+        tl = torch.full((1,), T, dtype=torch.int32, device=DEV)
+        fn = lambda: ops.attn_prefill(q, kc, vc, table, pages, z, tl, tl, 1, T, Hq, Hkv, hd, out_bf16=out)
+        s = timeit(fn)
+        fl = 4 * T * T * Hq * hd / 2
+        _, tf, tag2 = peaks()
+        rows.append(f"attn_prefill T={T}: {s*1e6:8.1f} us  {fl/s/1e12:6.1f} TFLOP/s (causal)  {fl/s/1e12/tf:5.2f} of {tag2} bf16")
+
+
+def bench_gemm(rows):
+    _, tf, tag = peaks()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for M, N, K in ((2048, 6144, 4096), (2048, 28672, 4096), (2048, 4096, 14336), (8192, 8192, 8192), (64, 6144, 4096),
+                    (64, 28672, 4096), (16384, 2304, 768), (16384, 768, 3072), (16384, 3072, 768)):
+        A = torch.randn(M, K, device=DEV).bfloat16()
+        B = torch.randn(N, K, device=DEV).bfloat16()
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+        for tile in (64, 128, 256):
+            fn = lambda: ops.gemm_bf16(A, B, M, N, K, out_bf16=out, tile_n=tile, status=status)
+            s = timeit(fn, iters=10)
+            fl = 2.0 * M * N * K
+            rows.append(f"gemm M={M:5d} N={N:5d} K={K:5d} tile_n={tile:3d}: {s*1e6:9.1f} us  {fl/s/1e12:7.1f} TFLOP/s  {fl/s/1e12/tf:5.2f} of {tag} bf16")
+        ref = timeit(lambda: torch.matmul(A, B.t(), out=out), iters=10)
+        rows.append(f"     torch.matmul (library reference)       : {ref*1e6:9.1f} us  {2.0*M*N*K/ref/1e12:7.1f} TFLOP/s")
+    assert int(status.item()) == 0
+
+
+def main():
+    which = sys.argv[1] if len(sys.argv) > 1 else "all"
+    rows = []
+    if which in ("matvec", "all"):
+        bench_matvec(rows)
+    if which in ("attn", "all"):
+        bench_attn(rows)
+    if which in ("gemm", "all"):
+        bench_gemm(rows)
+    print("\n".join(rows))
+
+
+if __name__ == "__main__":
+    main()

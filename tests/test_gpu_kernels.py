@@ -1,0 +1,339 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same op."""
+import math
+
+import pytest
+import torch
+
+from openagents_b200.gguf import GgmlType
+from openagents_b200.gguf import torch_codecs as tc
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _ops():
+    from openagents_b200.ops import cuda_ops
+    return cuda_ops
+
+
+def _qweight(x, t):
+    from openagents_b200.models.qweight import QWeight, RawTensor
+    return QWeight.from_raw(RawTensor(t, tuple(x.shape), tc.quantize(x, t)))
+
+
+def _randn(*shape, seed=0, scale=1.0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return torch.randn(*shape, generator=g, device=DEV) * scale
+
+
+def _quant_x(x):
+    """Reference of the activation quantizer: per-32 int8 with fp32 scale."""
+    xb = x.reshape(x.shape[0], -1, 32)
+    d = xb.abs().amax(-1, keepdim=True) / 127.0
+    q = torch.where(d > 0, torch.round(xb / d), torch.zeros_like(xb))
+    return (q * d).reshape(x.shape), q, d
+
+
+def _alloc_q(nb, K):
+    return (torch.empty((nb, K), dtype=torch.int8, device=DEV), torch.empty((nb, K // 32), device=DEV),
+            torch.empty((nb, K // 16), device=DEV))
+
+
+def test_rmsnorm_and_quant():
+    ops = _ops()
+    T, D = 5, 1024
+    x, g = _randn(T, D, seed=1), _randn(D, seed=2) * 0.1 + 1.0
+    xq, xd, xs = _alloc_q(T, D)
+    hf = torch.empty((T, D), device=DEV)
+    hb = torch.empty((T, D), dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm(x, g, 1e-5, xq=xq, xd=xd, xs16=xs, hb=hb, hf=hf)
+    ref = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * g
+    assert torch.allclose(hf, ref, atol=1e-5, rtol=1e-5)
+    assert torch.allclose(hb.float(), ref, atol=2e-2, rtol=1e-2)
+    deq_ref, q_ref, d_ref = _quant_x(ref)
+    # undo the byte order and compare the dequantized activations
+    inv = torch.tensor(tc.X8_POS, device=DEV)
+    q = xq.view(T, D // 8, 8)[:, :, inv].reshape(T, D // 32, 32).float()
+    assert torch.allclose(q * xd[..., None], deq_ref.reshape(T, D // 32, 32), atol=float(d_ref.max()) * 1.01)
+    s16 = (q.reshape(T, D // 16, 16).sum(-1) * xd.repeat_interleave(2, dim=1))
+    assert torch.allclose(xs, s16, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("t", [GgmlType.Q4_K, GgmlType.Q6_K, GgmlType.Q8_0, GgmlType.MXFP4])
+def test_dequant_matches_codec(t):
+    ops = _ops()
+    N, K = 96, 1024
+    x = _randn(N, K, seed=3, scale=0.02)
+    w = _qweight(x, t)
+    out = torch.empty((N, K), dtype=torch.bfloat16, device=DEV)
+    ops.dequant_bf16(w.wt, w.main, w.plane2, out, N, K)
+    ref = tc.dequantize(tc.quantize(x, t), t, (N, K))
+    assert torch.allclose(out.float(), ref, atol=1e-4, rtol=8e-3)
+
+
+@pytest.mark.parametrize("t", [GgmlType.Q4_K, GgmlType.Q6_K, GgmlType.Q8_0, GgmlType.BF16])
+@pytest.mark.parametrize("nb", [1, 3, 8])
+def test_matvec_store_and_resid(t, nb):
+    ops = _ops()
+    N, K = 200, 1024   # N not a multiple of 32: exercises the row tail
+    W = _randn(N, K, seed=4, scale=0.02)
+    w = _qweight(W, t)
+    Wd = tc.dequantize(tc.quantize(W, t), t, (N, K)) if t != GgmlType.BF16 else W.bfloat16().float()
+    x = _randn(nb, K, seed=5)
+    bias = _randn(N, seed=6)
+    xq, xd, xs = _alloc_q(nb, K)
+    ops.quantize_x(x, xq, xd, xs)
+    y = torch.zeros((nb, N), device=DEV)
+    ops.matvec(w.wt, w.main, w.plane2, N, K, nb, xq=xq, xd=xd, xs16=xs, xf=x, epi=ops.EPI_STORE, bias=bias, y=y, ldy=N)
+    ref = x @ Wd.t() + bias
+    tol = 0.02 * ref.std().item()
+    assert (y - ref).abs().max().item() < 4 * tol, (y - ref).abs().max().item()
+    # exact against the same quantized activations
+    if t != GgmlType.BF16:
+        xdq, _, _ = _quant_x(x)
+        ref_q = xdq @ Wd.t() + bias
+        assert torch.allclose(y, ref_q, atol=2e-3 * ref.std().item() + 1e-5, rtol=1e-4)
+    r = _randn(nb, N, seed=7)
+    y2 = r.clone()
+    ops.matvec(w.wt, w.main, w.plane2, N, K, nb, xq=xq, xd=xd, xs16=xs, xf=x, epi=ops.EPI_RESID, resid=y2, y=y2, ldy=N)
+    assert torch.allclose(y2, r + (y - bias), atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("t", [GgmlType.Q4_K, GgmlType.BF16])
+@pytest.mark.parametrize("nb", [1, 4])
+def test_matvec_swiglu(t, nb):
+    ops = _ops()
+    F, K = 256, 512
+    W = _randn(2 * F, K, seed=8, scale=0.05)
+    w = _qweight(W, t)
+    Wd = tc.dequantize(tc.quantize(W, t), t, (2 * F, K)) if t != GgmlType.BF16 else W.bfloat16().float()
+    x = _randn(nb, K, seed=9)
+    xq, xd, xs = _alloc_q(nb, K)
+    ops.quantize_x(x, xq, xd, xs)
+    xin = _quant_x(x)[0] if t != GgmlType.BF16 else x
+    gu = xin @ Wd.t()
+    ref = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    y = torch.zeros((nb, F), device=DEV)
+    ops.matvec(w.wt, w.main, w.plane2, F, K, nb, xq=xq, xd=xd, xs16=xs, xf=x, epi=ops.EPI_SWIGLU_F32, y=y, ldy=F)
+    assert torch.allclose(y, ref, atol=2e-3 * ref.std().item() + 1e-5, rtol=1e-3)
+    oq, od, os16 = _alloc_q(nb, F)
+    ops.matvec(w.wt, w.main, w.plane2, F, K, nb, xq=xq, xd=xd, xs16=xs, xf=x, epi=ops.EPI_SWIGLU_Q8, oq=oq, od=od, os16=os16)
+    inv = torch.tensor(tc.X8_POS, device=DEV)
+    q = oq.view(nb, F // 8, 8)[:, :, inv].reshape(nb, F // 32, 32).float()
+    deq = (q * od[..., None]).reshape(nb, F)
+    assert (deq - ref).abs().max().item() <= ref.abs().max().item() / 127.0 * 0.6 + 2e-3 * ref.std().item()
+
+
+def test_embedding_types():
+    ops = _ops()
+    V, D = 300, 512
+    E = _randn(V, D, seed=10, scale=0.02)
+    ids = torch.tensor([0, 5, 299, 17], dtype=torch.int32, device=DEV)
+    for t, et in ((GgmlType.Q6_K, ops.EMB_Q6KR), (GgmlType.Q8_0, ops.EMB_Q8R), (GgmlType.BF16, ops.EMB_BF16)):
+        w = _qweight(E, t)
+        ref = tc.dequantize(tc.quantize(E, t), t, (V, D))[ids.long()]
+        out = torch.empty((4, D), device=DEV)
+        ops.embedding(ids, out, et, w.main, w.plane2)
+        assert torch.allclose(out, ref, atol=1e-6, rtol=1e-5)
+    out = torch.ones((4, D), device=DEV)
+    w = _qweight(E, GgmlType.BF16)
+    ops.embedding(ids, out, ops.EMB_BF16, w.main, None, vocab_lo=100, vocab_n=100)
+    assert out.abs().sum().item() == 0.0
+
+
+@pytest.mark.parametrize("style", ["pairs", "half"])
+def test_rope_kv_write(style):
+    from openagents_b200.oracle import nn
+    ops = _ops()
+    T, Hq, Hkv, hd = 6, 4, 2, 64
+    qkv = _randn(T, (Hq + 2 * Hkv) * hd, seed=11)
+    pos = torch.tensor([0, 1, 2, 700, 3000, 8191], dtype=torch.int32, device=DEV)
+    slot = torch.tensor([16, 17, 18, 3, 40, 5], dtype=torch.int32, device=DEV)
+    kc = torch.zeros((4, Hkv, 16, hd), dtype=torch.float16, device=DEV)
+    vc = torch.zeros_like(kc)
+    q32 = torch.empty((T, Hq * hd), device=DEV)
+    q16 = torch.empty((T, Hq * hd), dtype=torch.float16, device=DEV)
+    ops.rope_kv(qkv, pos, slot, q32, q16, kc, vc, Hq, Hkv, hd, 16, 500000.0, 0 if style == "pairs" else 1, 0.125)
+    q, k, v = qkv.cpu().split([Hq * hd, Hkv * hd, Hkv * hd], dim=-1)
+    qr = nn.rope(q.view(T, Hq, hd), pos.cpu(), 500000.0, style) * 0.125
+    kr = nn.rope(k.view(T, Hkv, hd), pos.cpu(), 500000.0, style)
+    assert torch.allclose(q32.cpu().view(T, Hq, hd), qr, atol=2e-5)
+    assert torch.allclose(q16.cpu().float().view(T, Hq, hd), qr, atol=2e-3)
+    for i in range(T):
+        s = int(slot[i])
+        assert torch.allclose(kc[s // 16, :, s % 16].cpu().float(), kr[i], atol=4e-3)
+        assert torch.allclose(vc[s // 16, :, s % 16].cpu().float(), v.view(T, Hkv, hd)[i], atol=4e-3)
+
+
+def _paged_kv(B, Hkv, hd, lens, seed):
+    """Random K/V for B sequences scattered over shuffled pages.  Returns caches, table, dense K/V."""
+    max_pages = (max(lens) + 15) // 16
+    n_pages = B * max_pages + 3
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g)
+    table = torch.zeros((B, max_pages), dtype=torch.int32)
+    kc = torch.zeros((n_pages, Hkv, 16, hd), dtype=torch.float16)
+    vc = torch.zeros_like(kc)
+    Ks, Vs = [], []
+    for b in range(B):
+        K = torch.randn(lens[b], Hkv, hd, generator=g).half()
+        V = torch.randn(lens[b], Hkv, hd, generator=g).half()
+        Ks.append(K.float())
+        Vs.append(V.float())
+        for p in range((lens[b] + 15) // 16):
+            pid = int(perm[b * max_pages + p])
+            table[b, p] = pid
+            n = min(16, lens[b] - p * 16)
+            kc[pid, :, :n] = K[p * 16: p * 16 + n].transpose(0, 1)
+            vc[pid, :, :n] = V[p * 16: p * 16 + n].transpose(0, 1)
+    return kc.to(DEV), vc.to(DEV), table.to(DEV), Ks, Vs
+
+
+@pytest.mark.parametrize("hd,Hq,Hkv", [(128, 8, 2), (64, 16, 2), (128, 4, 4)])
+@pytest.mark.parametrize("S", [1, 5])
+@pytest.mark.parametrize("window,use_sinks", [(0, False), (40, True)])
+def test_attn_decode(hd, Hq, Hkv, S, window, use_sinks):
+    from openagents_b200.oracle import nn
+    ops = _ops()
+    lens = [1, 17, 130, 333]
+    B = len(lens)
+    kc, vc, table, Ks, Vs = _paged_kv(B, Hkv, hd, lens, seed=12)
+    q = _randn(B, Hq * hd, seed=13) * (1.0 / math.sqrt(hd))
+    sinks = _randn(Hq, seed=14) if use_sinks else None
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = torch.empty((B, Hq * hd), device=DEV)
+    oq, od, os16 = _alloc_q(B, Hq * hd)
+    scratch = torch.empty(ops.attn_decode_scratch_floats(B, Hq, Hkv, hd, S), device=DEV)
+    counters = torch.zeros(B * Hkv, dtype=torch.int32, device=DEV)
+    for _ in range(2):   # second run checks the counters were left at zero
+        ops.attn_decode(q, kc, vc, table, seq_lens, B, Hq, Hkv, hd, window=window, S=S, sinks=sinks, out_f32=out,
+                        oq=oq, od=od, os16=os16, scratch=scratch, counters=counters)
+        for b in range(B):
+            L = lens[b]
+            ref = nn.attention(q[b].cpu().view(1, Hq, hd), Ks[b], Vs[b], torch.tensor([L - 1]), torch.arange(L),
+                               window=window, sinks=sinks.cpu() if use_sinks else None, scale=1.0).reshape(-1)
+            assert torch.allclose(out[b].cpu(), ref, atol=2e-3, rtol=2e-3), (b, (out[b].cpu() - ref).abs().max())
+    assert int(counters.abs().sum()) == 0
+    inv = torch.tensor(tc.X8_POS, device=DEV)
+    deq = (oq.view(B, -1, 8)[:, :, inv].reshape(B, -1, 32).float() * od[..., None]).reshape(B, -1)
+    assert (deq - out).abs().max().item() <= out.abs().max().item() / 127 * 0.6
+
+
+@pytest.mark.parametrize("hd,Hq,Hkv", [(128, 4, 2), (64, 4, 1)])
+@pytest.mark.parametrize("window,use_sinks", [(0, False), (50, True)])
+def test_attn_prefill(hd, Hq, Hkv, window, use_sinks):
+    from openagents_b200.oracle import nn
+    ops = _ops()
+    ctx = [70, 200, 129]        # keys in cache after the chunk
+    qlen = [70, 64, 1]          # new query tokens (second sequence has 136 cached tokens)
+    B = len(ctx)
+    kc, vc, table, Ks, Vs = _paged_kv(B, Hkv, hd, ctx, seed=15)
+    T = sum(qlen)
+    q = (_randn(T, Hq * hd, seed=16) * (1.0 / math.sqrt(hd))).half()
+    sinks = _randn(Hq, seed=17) if use_sinks else None
+    q_start = torch.tensor([0, 70, 134], dtype=torch.int32, device=DEV)
+    out = torch.empty((T, Hq * hd), device=DEV)
+    outb = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=DEV)
+    lse = torch.empty((T, Hq), device=DEV)
+    ops.attn_prefill(q, kc, vc, table, table.shape[1], q_start, torch.tensor(qlen, dtype=torch.int32, device=DEV),
+                     torch.tensor(ctx, dtype=torch.int32, device=DEV), B, max(qlen), Hq, Hkv, hd, window=window,
+                     sinks=sinks, out_bf16=outb, out_f32=out, lse=lse)
+    for b in range(B):
+        s, n = int(q_start[b]), qlen[b]
+        qpos = torch.arange(ctx[b] - n, ctx[b])
+        ref = nn.attention(q[s:s + n].float().cpu().view(n, Hq, hd), Ks[b], Vs[b], qpos, torch.arange(ctx[b]),
+                           window=window, sinks=sinks.cpu() if use_sinks else None, scale=1.0).reshape(n, -1)
+        assert torch.allclose(out[s:s + n].cpu(), ref, atol=3e-3, rtol=3e-3), (b, (out[s:s + n].cpu() - ref).abs().max())
+        assert torch.allclose(outb[s:s + n].float().cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 520, 200), (64, 768, 768), (1024, 2304, 768), (257, 64, 4096)])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
+def test_gemm_bf16(M, N, K, tile_n):
+    ops = _ops()
+    A = _randn(M, K, seed=18).bfloat16()
+    B = _randn(N, K, seed=19).bfloat16()
+    bias = _randn(N, seed=20)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.zeros((M, N), device=DEV)
+    outb = torch.zeros((M, N), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_bf16(A, B, M, N, K, out_f32=out, out_bf16=outb, bias=bias, tile_n=tile_n, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ref = A.float() @ B.float().t() + bias
+    err = (out - ref).abs().max().item()
+    assert err < 2e-3 * math.sqrt(K), err
+    assert torch.allclose(outb.float(), ref, atol=0.05 * ref.abs().max().item() / 4, rtol=2e-2)
+
+
+def test_gemm_epilogues():
+    ops = _ops()
+    M, N, K = 200, 384, 256
+    A = _randn(M, K, seed=21).bfloat16()
+    B = _randn(N, K, seed=22, scale=0.05).bfloat16()
+    bias = _randn(N, seed=23)
+    resid = _randn(M, N, seed=24)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    base = A.float() @ B.float().t()
+    out = resid.clone()
+    ops.gemm_bf16(A, B, M, N, K, out_f32=out, resid_f32=out, bias=bias, status=status)   # in-place residual
+    assert torch.allclose(out, base + bias + resid, atol=2e-2, rtol=1e-3)
+    out = torch.zeros((M, N), device=DEV)
+    ops.gemm_bf16(A, B, M, N, K, out_f32=out, bias=bias, act=ops.ACT_GELU, status=status)
+    assert torch.allclose(out, torch.nn.functional.gelu(base + bias, approximate="tanh"), atol=2e-2, rtol=1e-3)
+    acc = resid.clone()
+    ops.gemm_bf16(A, B, M, N, K, out_f32=acc, accumulate=True, status=status)
+    assert torch.allclose(acc, resid + base, atol=2e-2, rtol=1e-3)
+    rb = resid.bfloat16()
+    outb = torch.zeros((M, N), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_bf16(A, B, M, N, K, out_bf16=outb, resid_bf16=rb, status=status)
+    assert torch.allclose(outb.float(), base + rb.float(), atol=0.1, rtol=2e-2)
+    assert int(status.item()) == 0
+
+
+def test_argmax_and_sampling():
+    ops = _ops()
+    T, V = 5, 50257
+    logits = _randn(T, V, seed=25)
+    logits[1, 777] = 50.0
+    logits[2, 3] = logits[2, 9] = 60.0     # tie: lowest index wins
+    ids = torch.zeros(T, dtype=torch.int32, device=DEV)
+    vals = torch.zeros(T, device=DEV)
+    ops.argmax(logits, ids, vals)
+    assert torch.equal(ids.long().cpu(), logits.argmax(-1).cpu())
+    assert int(ids[2]) == 3 and float(vals[1]) == 50.0
+    # top-1 sampling is arg-max whatever the random number
+    u = torch.rand(T, device=DEV)
+    scratch = torch.empty((T, V), device=DEV)
+    out = torch.zeros(T, dtype=torch.int32, device=DEV)
+    ops.sample_topk(logits, 1.0, 1, 1.0, u, out, scratch)
+    assert torch.equal(out, ids)
+    # with k=8 every draw must come from the 8 largest logits, and a tiny top-p collapses to arg-max
+    ops.sample_topk(logits, 0.8, 8, 1.0, u, out, scratch)
+    top8 = logits.topk(8, dim=-1).indices
+    assert all(int(out[t]) in top8[t].tolist() for t in range(T))
+    ops.sample_topk(logits, 1.0, 8, 1e-6, u, out, scratch)
+    assert torch.equal(out, ids)
+
+
+def test_swiglu_add_cast_transpose():
+    ops = _ops()
+    T, F = 7, 300
+    gu = _randn(T, 2 * F, seed=26)
+    of = torch.empty((T, F), device=DEV)
+    ob = torch.empty((T, F), dtype=torch.bfloat16, device=DEV)
+    ops.swiglu(gu, F, ob=ob, of=of)
+    ref = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    assert torch.allclose(of, ref, atol=1e-5, rtol=1e-5) and torch.allclose(ob.float(), ref, atol=2e-2, rtol=1e-2)
+    a, b = _randn(1001, seed=27), _randn(1001, seed=28)
+    c = a.clone()
+    ops.add_inplace(c, b)
+    assert torch.equal(c, a + b)
+    y = torch.empty(1001, dtype=torch.bfloat16, device=DEV)
+    ops.f32_to_bf16(a, y)
+    assert torch.equal(y, a.bfloat16())
+    m = _randn(70, 45, seed=29).bfloat16()
+    mt = torch.empty((45, 70), dtype=torch.bfloat16, device=DEV)
+    ops.transpose_bf16(m, mt)
+    assert torch.equal(mt, m.t().contiguous())
