@@ -9,6 +9,7 @@
 // Both operands are K-major ("TN"), which is the natural layout of y = x W^T with W stored
 // [out][in]; the GEMM-shaped reference case is cs336-a2-benchmark-workload.ts:251-292.
 #include "tc05.cuh"
+#include "../comm/sym.cuh"
 
 using namespace b200;
 using namespace b200::tc;
@@ -60,7 +61,17 @@ struct GemmEpi {
   int ldc;
   int act;
   int accumulate;            // out_f32 += value
+  // Fused collective epilogue (tensor-parallel row-parallel GEMMs): instead of storing, add the tile
+  // into an fp32 tensor [*, ldc] at byte offset sym_off of the symmetric heap.
+  //   SYM_ALLREDUCE : into every rank's replica (multimem.red through the switch where available)
+  //   SYM_RSCATTER  : row m goes to rank m / rows_per_rank, local row m % rows_per_rank
+  // The kernel then ends with a cross-rank barrier.
+  int sym_mode;
+  int rows_per_rank;
+  size_t sym_off;
+  SymTable sym;
 };
+enum { SYM_NONE = 0, SYM_ALLREDUCE = 1, SYM_RSCATTER = 2 };
 
 constexpr int BM = 128, BK = 64;
 
@@ -71,6 +82,31 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, in
 #pragma unroll
   for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
   const bool full = n0 + 32 <= N;
+  if (e.sym_mode != SYM_NONE) {
+    const bool add_bias = e.bias && e.sym.rank == 0;
+    const int owner = e.sym_mode == SYM_RSCATTER ? m / e.rows_per_rank : 0;
+    const int lrow = e.sym_mode == SYM_RSCATTER ? m % e.rows_per_rank : m;
+    const size_t off = e.sym_off + ((size_t)lrow * e.ldc + n0) * 4;
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (add_bias) {
+          const float4 b = *(const float4*)(e.bias + n0 + j);
+          o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+        }
+        if (e.sym_mode == SYM_ALLREDUCE) sym_red_all_f32x4(e.sym, off + j * 4, o);
+        else sym_red_to_f32x4(e.sym, owner, off + j * 4, o);
+      }
+    } else {
+      for (int j = 0; j < 32 && n0 + j < N; j++) {
+        const float x = v[j] + (add_bias ? e.bias[n0 + j] : 0.f);
+        if (e.sym_mode == SYM_ALLREDUCE) sym_red_all_f32(e.sym, off + j * 4, x);
+        else sym_red_to_f32(e.sym, owner, off + j * 4, x);
+      }
+    }
+    return;
+  }
   if (full) {
     if (e.bias) {
 #pragma unroll
@@ -254,6 +290,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
   if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, (int)B200_ERR_TIMEOUT_MMA);
+  if (epi.sym_mode != SYM_NONE) sym_kernel_end_barrier(epi.sym, 0, gridDim.x);
 }
 
 static int sm_count() {
@@ -290,9 +327,11 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmE
 B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, int lda, int ldb, float* out_f32,
                             void* out_bf16, int ldc, const float* bias, const float* resid_f32,
                             const void* resid_bf16, int act, int accumulate, int tile_n, int* status,
+                            int sym_mode, const SymTable* sym, size_t sym_off, int rows_per_rank,
                             cudaStream_t st) {
   if (M <= 0 || N <= 0 || K <= 0 || (lda % 8) || (ldb % 8) || (K % 8)) return B200_ERR_BAD_ARG;
   if ((out_bf16 && (ldc % 8)) || (out_f32 && (ldc % 4))) return B200_ERR_BAD_ARG;
+  if (N % 4) return B200_ERR_BAD_ARG;
   if (tile_n == 0) {
     const long tiles256 = (long)((N + 255) / 256) * ((M + 127) / 128);
     tile_n = (N >= 256 && tiles256 >= 148) ? 256 : (N >= 128 && (long)((N + 127) / 128) * ((M + 127) / 128) >= 148) ? 128 : (N > 64 ? 128 : 64);
@@ -305,6 +344,13 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   GemmEpi e;
   e.out_f32 = out_f32; e.out_bf16 = (__nv_bfloat16*)out_bf16; e.bias = bias; e.resid_f32 = resid_f32;
   e.resid_bf16 = (const __nv_bfloat16*)resid_bf16; e.ldc = ldc; e.act = act; e.accumulate = accumulate;
+  e.sym_mode = sym_mode; e.rows_per_rank = rows_per_rank > 0 ? rows_per_rank : 1; e.sym_off = sym_off;
+  if (sym_mode != SYM_NONE) {
+    if (!sym || (ldc % 4) || (sym_off % 16)) return B200_ERR_BAD_ARG;
+    e.sym = *sym;
+  } else {
+    e.sym = SymTable{};
+  }
   switch (tile_n) {
     case 256: return launch_gemm<256, 4>(ta, tb, e, M, N, K, status, st);
     case 128: return launch_gemm<128, 6>(ta, tb, e, M, N, K, status, st);

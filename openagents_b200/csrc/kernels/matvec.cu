@@ -8,12 +8,12 @@
 // Reference math: per-position projections of
 // apps/openagents.com/workers/api/src/cs336-a1-real-gradient-workload.ts:459-475 (QKV),
 // :520-528 (output projection + residual), :532-559 (SwiGLU FFN).
-#include "common.cuh"
+#include "../comm/sym.cuh"
 
 using namespace b200;
 
 enum { WT_Q4KR = 0, WT_Q6KR = 1, WT_Q8R = 2, WT_BF16 = 3 };
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU_Q8 = 2, EPI_SWIGLU_F32 = 3 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU_Q8 = 2, EPI_SWIGLU_F32 = 3, EPI_ALLREDUCE = 4 };
 
 struct MatvecArgs {
   const uint8_t* w;     // main plane
@@ -32,6 +32,11 @@ struct MatvecArgs {
   int8_t* oq;           // EPI_SWIGLU_Q8 outputs
   float* od;
   float* os16;
+  // EPI_ALLREDUCE: this rank's partial products are added into the fp32 tensor at byte offset
+  // sym_off ([nb][ldy]) of EVERY rank's symmetric heap, and the kernel ends with a cross-rank
+  // barrier, so on completion each replica holds resid + sum of all ranks' partials.
+  SymTable sym;
+  size_t sym_off;
 };
 
 __device__ __forceinline__ int dp4a(uint32_t a, uint32_t b, int c) {
@@ -167,7 +172,7 @@ __device__ __forceinline__ void matvec_epilogue(const MatvecArgs& a, const float
   const int n = blockIdx.x * 32 + lane;
   const bool live = n < a.N;
   float v = res[lane * B + b];
-  if (a.bias && live) v += a.bias[n];
+  if (a.bias && live && (a.epi != EPI_ALLREDUCE || a.sym.rank == 0)) v += a.bias[n];
   if (a.epi == EPI_STORE) {
     if (live) a.y[(size_t)b * a.ldy + n] = v;
     if (dual && live) {
@@ -176,6 +181,8 @@ __device__ __forceinline__ void matvec_epilogue(const MatvecArgs& a, const float
     }
   } else if (a.epi == EPI_RESID) {
     if (live) a.y[(size_t)b * a.ldy + n] = a.resid[(size_t)b * a.ldy + n] + v;
+  } else if (a.epi == EPI_ALLREDUCE) {
+    if (live) sym_red_all_f32(a.sym, a.sym_off + ((size_t)b * a.ldy + n) * 4, v);
   } else {
     float u = res[32 * B + lane * B + b];
     if (a.bias && live) u += a.bias[a.N + n];
@@ -273,6 +280,7 @@ __global__ void __launch_bounds__(256) matvec_q_kernel(const MatvecArgs a) {
   }
   __syncthreads();
   matvec_epilogue<B>(a, res, DUAL);
+  if (a.epi == EPI_ALLREDUCE) sym_kernel_end_barrier(a.sym, 0, gridDim.x);
 }
 
 // bf16 weights [N][K] against fp32 activations.
@@ -335,6 +343,7 @@ __global__ void __launch_bounds__(256) matvec_bf16_kernel(const MatvecArgs a) {
   }
   __syncthreads();
   matvec_epilogue<B>(a, res, DUAL);
+  if (a.epi == EPI_ALLREDUCE) sym_kernel_end_barrier(a.sym, 0, gridDim.x);
 }
 
 template <int WT, int B, bool DUAL>
@@ -377,7 +386,7 @@ static int dispatch_wt(int wt, const MatvecArgs& a, cudaStream_t st) {
 B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, int nb, const void* xq,
                          const float* xd, const float* xs16, const float* xf, int epi, const float* bias,
                          const float* resid, float* y, int ldy, void* oq, float* od, float* os16,
-                         cudaStream_t st) {
+                         const SymTable* sym, size_t sym_off, cudaStream_t st) {
   if (nb < 1 || nb > 8) return B200_ERR_BAD_ARG;
   if (wt == WT_BF16 ? (K % 8 != 0) : (K % 256 != 0 && !(wt == WT_Q8R && K % 32 == 0))) return B200_ERR_BAD_ARG;
   if (epi == EPI_SWIGLU_Q8 && N % 32) return B200_ERR_BAD_ARG;
@@ -385,6 +394,14 @@ B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, in
   a.w = (const uint8_t*)w; a.w2 = (const __half*)w2; a.N = N; a.K = K; a.nb = nb;
   a.xq = (const int8_t*)xq; a.xd = xd; a.xs16 = xs16; a.xf = xf; a.epi = epi; a.bias = bias;
   a.resid = resid; a.y = y; a.ldy = ldy; a.oq = (int8_t*)oq; a.od = od; a.os16 = os16;
+  if (epi == EPI_ALLREDUCE) {
+    if (!sym) return B200_ERR_BAD_ARG;
+    a.sym = *sym;
+    a.sym_off = sym_off;
+  } else {
+    a.sym = SymTable{};
+    a.sym_off = 0;
+  }
   const bool dual = epi >= EPI_SWIGLU_Q8;
   const int B = nb <= 1 ? 1 : nb <= 2 ? 2 : nb <= 4 ? 4 : 8;
   if (dual) {

@@ -213,7 +213,10 @@ class LlamaEngine:
         self.qkv_dim = qd + 2 * kvd
         self.kc = [torch.zeros((self.n_pages, self.Hkv, PAGE, self.hd), dtype=torch.float16, device=dev) for _ in self.layers]
         self.vc = [torch.zeros_like(k) for k in self.kc]
-        self.x = torch.empty((T, d), **f32)
+        if self.world > 1:   # the replicated residual stream receives peers' partial sums: symmetric heap
+            self.x, self.x_off = self.comm.alloc_tensor((T, d), torch.float32)
+        else:
+            self.x = torch.empty((T, d), **f32)
         self.qkv = torch.empty((T, self.qkv_dim), **f32)
         self.q32 = torch.empty((max(self.max_batch, 1), qd), **f32)
         self.q16 = torch.empty((T, qd), dtype=torch.float16, device=dev)
@@ -263,9 +266,12 @@ class LlamaEngine:
         want = max(1, (2 * 148 + B * self.Hkv - 1) // (B * self.Hkv))
         return max(1, min(self.max_splits, want, ctx_pages))
 
-    def _all_reduce(self, t: torch.Tensor):
+    def _fence_reads(self):
+        """Tensor-parallel only: peers add into this rank's residual stream from inside their
+        kernels, so every rank must have finished reading (or overwriting) it before anyone starts
+        the next row-parallel projection."""
         if self.world > 1:
-            self.comm.all_reduce(t)
+            self.comm.heap.barrier(ch=2)
 
     def _layers_small(self, nb: int, max_ctx_pages: int):
         """<= 8 tokens, one per sequence: quantized mat-vec path."""
@@ -278,6 +284,7 @@ class LlamaEngine:
             q8 = L.wqkv.quantized
             ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, xq=self.xq if q8 else None, xd=self.xd, xs16=self.xs,
                         hf=None if q8 else self.xf)
+            self._fence_reads()
             ops.matvec(L.wqkv.wt, L.wqkv.main, L.wqkv.plane2, L.wqkv.N, L.wqkv.K, nb, xq=self.xq, xd=self.xd,
                        xs16=self.xs, xf=self.xf, epi=ops.EPI_STORE, bias=L.bqkv, y=self.qkv, ldy=self.qkv_dim)
             ops.rope_kv(self.qkv[:nb], self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv,
@@ -295,6 +302,7 @@ class LlamaEngine:
             g8 = L.wgu.quantized
             ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, xq=self.xq if g8 else None, xd=self.xd, xs16=self.xs,
                         hf=None if g8 else self.xf)
+            self._fence_reads()
             d8 = L.wdown.quantized and self.F % 32 == 0
             ops.matvec(L.wgu.wt, L.wgu.main, L.wgu.plane2, self.F, L.wgu.K, nb, xq=self.xq, xd=self.xd, xs16=self.xs,
                        xf=self.xf, epi=ops.EPI_SWIGLU_Q8 if d8 else ops.EPI_SWIGLU_F32, y=self.gu, ldy=self.F,
@@ -328,6 +336,7 @@ class LlamaEngine:
         n = 0
         for li, L in enumerate(self.layers):
             ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, hb=hb_d)
+            self._fence_reads()
             self._gemm(hb_d, L.wqkv, T, out_f32=qkv, bias=L.bqkv)
             if decode:
                 ops.rope_kv(qkv, self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv, self.hd,
@@ -344,14 +353,15 @@ class LlamaEngine:
             if self.world == 1:
                 self._gemm(hb_q, L.wo, T, out_f32=x, bias=L.bo, resid_f32=x, ldc=self.d)
             else:
-                self.comm.gemm_allreduce(hb_q, self._dense(L.wo), T, x, bias=L.bo)
+                self.comm.gemm_allreduce(hb_q, self._dense(L.wo), T, x, bias=L.bo, status=self.status)
             ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, hb=hb_d)
+            self._fence_reads()
             self._gemm(hb_d, L.wgu, T, out_f32=gu)
             ops.swiglu(gu, self.F, ob=hb_f)
             if self.world == 1:
                 self._gemm(hb_f, L.wdown, T, out_f32=x, resid_f32=x, ldc=self.d)
             else:
-                self.comm.gemm_allreduce(hb_f, self._dense(L.wdown), T, x)
+                self.comm.gemm_allreduce(hb_f, self._dense(L.wdown), T, x, status=self.status)
             n += 9
         return n
 
@@ -379,6 +389,7 @@ class LlamaEngine:
 
     def _embed(self, T: int):
         ops.embedding(self.ids, self.x[:T], self.emb_type, self.emb.main, self.emb.plane2)
+        self._fence_reads()
 
     # ------------------------------------------------------------------ host-side batch assembly
     def _stage_batch(self, seq_ids, new_tokens: list[list[int]]):

@@ -13,7 +13,8 @@ import torch
 from .. import _native
 
 WT_Q4KR, WT_Q6KR, WT_Q8R, WT_BF16, WT_MXFP4R = 0, 1, 2, 3, 4
-EPI_STORE, EPI_RESID, EPI_SWIGLU_Q8, EPI_SWIGLU_F32 = 0, 1, 2, 3
+EPI_STORE, EPI_RESID, EPI_SWIGLU_Q8, EPI_SWIGLU_F32, EPI_ALLREDUCE = 0, 1, 2, 3, 4
+SYM_NONE, SYM_ALLREDUCE, SYM_RSCATTER = 0, 1, 2
 EMB_F32, EMB_BF16, EMB_Q8R, EMB_Q6KR = 0, 1, 2, 3
 ACT_NONE, ACT_GELU = 0, 1
 
@@ -27,11 +28,13 @@ _SIGS = {
     "b200_add_inplace": [_P, _P, c_size_t, _P],
     "b200_argmax": [_P, c_int, c_int, _P, _P, c_int, _P],
     "b200_sample_topk": [_P, c_int, c_int, c_float, c_int, c_float, _P, _P, _P, _P],
-    "b200_matvec": [c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, _P, _P],
+    "b200_matvec": [c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, _P, _P,
+                    c_size_t, _P],
     "b200_attn_decode": [_P, _P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                          _P, _P, _P, _P, _P],
     "b200_attn_prefill": [_P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
-    "b200_gemm_bf16": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, _P, _P],
+    "b200_gemm_bf16": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, _P,
+                       c_int, _P, c_size_t, c_int, _P],
     "b200_dequant_bf16": [c_int, _P, _P, _P, c_size_t, c_int, _P],
     "b200_f32_to_bf16": [_P, _P, c_size_t, _P],
     "b200_transpose_bf16": [_P, _P, c_int, c_int, _P],
@@ -57,6 +60,11 @@ def lib():
 
 def _p(t):
     return None if t is None else t.data_ptr()
+
+
+def _sym(table):
+    """ctypes pointer to a SymTable structure (or None)."""
+    return None if table is None else ctypes.addressof(table)
 
 
 def _st():
@@ -111,9 +119,9 @@ def sample_topk(logits, temperature, top_k, top_p, u, out_id, scratch):
 
 
 def matvec(wt, w, w2, N, K, nb, xq=None, xd=None, xs16=None, xf=None, epi=EPI_STORE, bias=None, resid=None, y=None,
-           ldy=0, oq=None, od=None, os16=None):
+           ldy=0, oq=None, od=None, os16=None, sym=None, sym_off=0):
     _check(lib().b200_matvec(wt, _p(w), _p(w2), N, K, nb, _p(xq), _p(xd), _p(xs16), _p(xf), epi, _p(bias), _p(resid),
-                             _p(y), ldy, _p(oq), _p(od), _p(os16), _st()), "matvec")
+                             _p(y), ldy, _p(oq), _p(od), _p(os16), _sym(sym), sym_off, _st()), "matvec")
 
 
 def attn_decode_scratch_floats(B, Hq, Hkv, hd, S):
@@ -135,11 +143,12 @@ def attn_prefill(q, kc, vc, page_table, max_pages, q_start, q_len, ctx_len, n_se
 
 
 def gemm_bf16(A, B, M, N, K, lda=None, ldb=None, out_f32=None, out_bf16=None, ldc=None, bias=None, resid_f32=None,
-              resid_bf16=None, act=ACT_NONE, accumulate=False, tile_n=0, status=None):
+              resid_bf16=None, act=ACT_NONE, accumulate=False, tile_n=0, status=None, sym_mode=SYM_NONE, sym=None,
+              sym_off=0, rows_per_rank=0):
     """D[M][N] = A[M][K] @ B[N][K]^T with fused epilogue (see ``gemm_tc05.cu``)."""
     _check(lib().b200_gemm_bf16(_p(A), _p(B), M, N, K, lda or K, ldb or K, _p(out_f32), _p(out_bf16), ldc or N,
                                 _p(bias), _p(resid_f32), _p(resid_bf16), act, int(accumulate), tile_n, _p(status),
-                                _st()), "gemm_bf16")
+                                sym_mode, _sym(sym), sym_off, rows_per_rank, _st()), "gemm_bf16")
 
 
 def dequant_bf16(wt, w, w2, out, N, K):

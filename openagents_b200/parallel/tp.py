@@ -1,0 +1,58 @@
+"""Tensor-parallel communicator of the serving engine.
+
+The residual stream is replicated on every rank and lives in the symmetric heap.  A row-parallel
+projection (attention output, FFN down) adds its partial result straight into every replica from
+inside the kernel that computed it (``multimem.red`` through NVSwitch, or one ``red`` per peer), and
+the same kernel ends with the cross-rank barrier: there is no separate all-reduce launch.
+
+Topology naming follows the reference's serving contracts, which list ``tensor_sharded`` among the
+typed topologies (docs/teardowns/2026-07-21-buzz-teardown.md:660-681).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import cuda_ops as ops
+from .symm import SymmHeap
+
+
+class TPComm:
+    def __init__(self, rank: int, world: int, device, heap_bytes: int = 1 << 30, multicast: bool | None = None,
+                 wait_s: float = 2.0):
+        self.rank, self.world, self.device = rank, world, torch.device(device)
+        self.heap = SymmHeap(heap_bytes, device, wait_s=wait_s, multicast=multicast)
+        self._merge = None
+
+    def alloc_tensor(self, shape, dtype):
+        return self.heap.alloc_tensor(shape, dtype)
+
+    def offset_of(self, t: torch.Tensor) -> int:
+        return t.data_ptr() - self.heap.buf.data_ptr()
+
+    # row-parallel mat-vec with the all-reduce fused into its epilogue
+    def matvec_allreduce(self, w, nb, xq, xd, xs, xf, x, ldy, bias=None):
+        ops.matvec(w.wt, w.main, w.plane2, w.N, w.K, nb, xq=xq, xd=xd, xs16=xs, xf=xf, epi=ops.EPI_ALLREDUCE,
+                   bias=bias, y=x, ldy=ldy, sym=self.heap.table, sym_off=self.offset_of(x))
+
+    # row-parallel GEMM with the all-reduce fused into its epilogue
+    def gemm_allreduce(self, a_bf16, w_dense, M, x, bias=None, status=None):
+        N, K = w_dense.shape
+        ops.gemm_bf16(a_bf16, w_dense, M, N, K, lda=a_bf16.stride(0), ldb=K, ldc=x.stride(0), bias=bias, status=status,
+                      sym_mode=ops.SYM_ALLREDUCE, sym=self.heap.table, sym_off=self.offset_of(x))
+
+    def argmax_merge(self, out_ids: torch.Tensor, out_val: torch.Tensor, nb: int):
+        """Global arg-max over vocabulary shards: every rank publishes (value, id) per row to every
+        rank, then each picks the best (lowest id on ties) from identical data."""
+        if self._merge is None:
+            self._merge, self._merge_off = self.heap.alloc_tensor((self.world, 2, 1024), torch.float32)
+            self._stage, self._stage_off = self.heap.alloc_tensor((2, 1024), torch.float32)
+        if nb > 1024:
+            raise ValueError("argmax_merge handles up to 1024 rows")
+        self._stage[0, :nb].copy_(out_val[:nb])
+        self._stage[1, :nb].copy_(out_ids[:nb].view(torch.float32) if out_ids.dtype == torch.int32 else out_ids[:nb])
+        self.heap.all_gather(self._stage_off, self._merge_off, 2 * 1024 * 4)
+        vals = self._merge[:, 0, :nb]
+        ids = self._merge[:, 1, :nb].view(torch.int32)
+        best = vals.max(dim=0).values
+        cand = torch.where(vals == best[None], ids, torch.full_like(ids, 2 ** 31 - 1))
+        out_ids[:nb].copy_(cand.min(dim=0).values)

@@ -1,0 +1,178 @@
+"""Multi-GPU checks, run as child processes (one per GPU) over NCCL for the bootstrap.
+
+Skipped on a single-GPU box.  The failure-path test needs only one GPU: a kernel waits on a flag
+nothing sets, gives up after the heap's limit and reports it through the control block, leaving the
+context usable.
+"""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _run(fn, world, *args):
+    import torch.multiprocessing as mp
+    port = _free_port()
+    mp.spawn(_entry, args=(world, port, fn, args), nprocs=world, join=True)
+
+
+def _entry(rank, world, port, fn, args):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    try:
+        fn(rank, world, *args)
+        torch.cuda.synchronize()
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def _need(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+# ---------------------------------------------------------------- collectives
+
+def _collectives(rank, world, multicast):
+    import torch.distributed as dist
+    from openagents_b200.parallel.symm import SymmHeap
+    dev = torch.device("cuda", rank)
+    heap = SymmHeap(64 << 20, dev, multicast=multicast)
+    n = 1 << 18
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    # all-reduce, twice (second round checks the epoch bookkeeping)
+    x, off = heap.alloc_tensor((n,), torch.float32)
+    for rep in range(2):
+        mine = torch.randn(n, generator=g, device=dev)
+        x.copy_(mine)
+        ref = mine.clone()
+        dist.all_reduce(ref)
+        heap.barrier()
+        heap.all_reduce_f32(off, n)
+        torch.cuda.synchronize()
+        assert torch.allclose(x, ref, atol=1e-5, rtol=1e-5), (rep, (x - ref).abs().max())
+    # all-gather
+    src, soff = heap.alloc_tensor((n,), torch.float32)
+    dst, doff = heap.alloc_tensor((world, n), torch.float32)
+    src.copy_(torch.randn(n, generator=g, device=dev))
+    ref = [torch.empty(n, device=dev) for _ in range(world)]
+    dist.all_gather(ref, src.clone())
+    heap.barrier()
+    heap.all_gather(soff, doff, n * 4)
+    torch.cuda.synchronize()
+    assert torch.equal(dst, torch.stack(ref))
+    # reduce-scatter
+    inp, ioff = heap.alloc_tensor((world, n), torch.float32)
+    out, ooff = heap.alloc_tensor((n,), torch.float32)
+    inp.copy_(torch.randn(world, n, generator=g, device=dev))
+    ref = torch.empty(n, device=dev)
+    dist.reduce_scatter_tensor(ref, inp.clone())
+    heap.barrier()
+    heap.reduce_scatter_f32(ioff, ooff, n)
+    torch.cuda.synchronize()
+    assert torch.allclose(out, ref, atol=1e-5, rtol=1e-5)
+    # all-to-all
+    a2a, aoff = heap.alloc_tensor((world, n), torch.float32)
+    a2o, boff = heap.alloc_tensor((world, n), torch.float32)
+    a2a.copy_(torch.randn(world, n, generator=g, device=dev))
+    ref = torch.empty(world, n, device=dev)
+    dist.all_to_all_single(ref, a2a.clone())
+    heap.barrier()
+    heap.all_to_all(aoff, boff, n * 4)
+    torch.cuda.synchronize()
+    assert torch.equal(a2o, ref)
+    assert heap.status() == (0, 0)
+    if multicast is None and rank == 0:
+        print("multicast in use:", heap.uses_multicast)
+
+
+@pytest.mark.parametrize("multicast", [None, False])
+def test_collectives_two_gpus(multicast):
+    _need(2)
+    _run(_collectives, 2, multicast)
+
+
+# ---------------------------------------------------------------- tensor-parallel engine
+
+def _tp_engine(rank, world, path):
+    import torch.distributed as dist
+    from openagents_b200.models.engine import LlamaEngine
+    from openagents_b200.models.qweight import GGUFSource
+    from openagents_b200.models.weights import load_gguf_float
+    from openagents_b200.oracle.models import KVCacheRef, llama_forward
+    from openagents_b200.parallel.tp import TPComm
+    dev = torch.device("cuda", rank)
+    comm = TPComm(rank, world, dev, heap_bytes=64 << 20)
+    src = GGUFSource(path, dev)
+    eng = LlamaEngine(src.cfg, src, device=dev, max_batch=16, max_ctx=128, max_tokens=256, tp_rank=rank, tp_world=world,
+                      comm=comm)
+    cfg, W = load_gguf_float(path)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in (40, 17, 33)]
+
+    def full_logits(local):   # gather the vocabulary shards
+        parts = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(parts, local.contiguous())
+        return torch.cat(parts, dim=-1).cpu()
+
+    for b in range(3):
+        eng.begin(b)
+    logits, nxt = eng.forward_tokens([0, 1, 2], [p.tolist() for p in prompts])     # dense path + fused all-reduce
+    caches = [KVCacheRef(cfg.n_layers) for _ in range(3)]
+    ref = torch.stack([llama_forward(cfg, W, prompts[b], caches[b])[-1] for b in range(3)])
+    scale = ref.std().item()
+    got = full_logits(logits)
+    assert (got - ref).abs().max().item() < 0.08 * scale, (got - ref).abs().max().item()
+    assert nxt.tolist() == got.argmax(-1).tolist()
+    toks = ref.argmax(-1).tolist()
+    for step in range(4):                                                          # mat-vec path + fused all-reduce
+        logits, nxt = eng.decode([0, 1, 2], toks, use_graph=(step > 1))
+        ref = torch.stack([llama_forward(cfg, W, torch.tensor([toks[b]]), caches[b])[-1] for b in range(3)])
+        got = full_logits(logits)
+        assert (got - ref).abs().max().item() < 0.08 * scale, (step, (got - ref).abs().max().item())
+        assert nxt.tolist() == got.argmax(-1).tolist()
+        toks = ref.argmax(-1).tolist()
+    eng.check_status()
+    assert comm.heap.status() == (0, 0)
+
+
+def test_tp2_engine_matches_oracle(tmp_path):
+    _need(2)
+    from openagents_b200.models.config import TINY_LLAMA
+    from openagents_b200.models.weights import PLAN_Q4_K, random_weights, save_gguf
+    cfg = TINY_LLAMA.with_(d_model=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1024, vocab=4096, n_layers=3)
+    p = str(tmp_path / "q4k.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 3), PLAN_Q4_K)
+    _run(_tp_engine, 2, p)
+
+
+# ---------------------------------------------------------------- failure path (one GPU)
+
+def test_wait_times_out_and_context_survives():
+    from openagents_b200.parallel.symm import SymmHeap
+    heap = SymmHeap(1 << 20, "cuda:0", wait_s=0.2)
+    assert heap.status() == (0, 0)
+    heap.wait_unset_flag()
+    torch.cuda.synchronize()
+    code, n = heap.status()
+    assert code == 3 and n == 1          # B200_ERR_TIMEOUT_PEER, one wait gave up
+    x = torch.ones(8, device="cuda:0") * 2   # the context still works
+    assert float(x.sum()) == 16.0
+    heap.barrier()                        # a one-rank barrier completes at once
+    torch.cuda.synchronize()
+    assert heap.status()[1] == 1
