@@ -34,7 +34,7 @@ def llama_forward(cfg: ModelConfig, W: dict, tokens: torch.Tensor, cache: KVCach
     cache = cache if cache is not None else KVCacheRef(cfg.n_layers)
     p0 = cache.length
     T = tokens.shape[0]
-    pos = torch.arange(p0, p0 + T)
+    pos = torch.arange(p0, p0 + T, device=tokens.device)
     x = W["token_embd.weight"][tokens]
     for i in range(cfg.n_layers):
         pre = f"blk.{i}."
@@ -45,7 +45,7 @@ def llama_forward(cfg: ModelConfig, W: dict, tokens: torch.Tensor, cache: KVCach
         q = nn.rope(q, pos, cfg.rope_theta, cfg.rope_style)
         k = nn.rope(k, pos, cfg.rope_theta, cfg.rope_style)
         K, V = cache.append(i, k, v)
-        kpos = torch.arange(K.shape[0])
+        kpos = torch.arange(K.shape[0], device=tokens.device)
         window = cfg.sliding_window if cfg.layer_uses_window(i) else 0
         sinks = W.get(pre + "attn_sinks.weight") if cfg.attn_sinks else None
         a = nn.attention(q, K, V, pos, kpos, window=window, sinks=sinks).reshape(T, cfg.q_dim)
@@ -84,7 +84,7 @@ def gpt2_forward(cfg: ModelConfig, W: dict, tokens: torch.Tensor) -> torch.Tenso
     """tokens: [B, T].  Pre-LN GPT-2 with tied embeddings.  Returns logits [B, T, V]."""
     B, T = tokens.shape
     x = W["token_embd.weight"][tokens] + W["position_embd.weight"][:T]
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=tokens.device)
     for i in range(cfg.n_layers):
         pre = f"blk.{i}."
         h = nn.layernorm(x, W[pre + "attn_norm.weight"], W[pre + "attn_norm.bias"], cfg.norm_eps)

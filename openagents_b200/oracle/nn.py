@@ -34,7 +34,7 @@ def swiglu(gate, up):
 def rope(x: torch.Tensor, pos: torch.Tensor, theta: float, style: str = "pairs") -> torch.Tensor:
     """x: [..., T, H, D]; pos: [T] (or broadcastable to x[..., :, 0, 0])."""
     D = x.shape[-1]
-    inv = theta ** (-torch.arange(0, D, 2, dtype=torch.float64) / D)
+    inv = theta ** (-torch.arange(0, D, 2, dtype=torch.float64, device=x.device) / D)
     ang = pos.to(torch.float64)[..., None] * inv          # [T, D/2]
     cos, sin = ang.cos().to(x.dtype)[..., None, :], ang.sin().to(x.dtype)[..., None, :]
     if style == "pairs":

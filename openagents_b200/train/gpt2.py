@@ -1,0 +1,229 @@
+"""GPT-2-shape causal LM for training: explicit forward and backward over the hand-written kernels.
+
+Parameters live in one flat bf16 buffer (the working copy the GEMMs read) with one flat fp32
+gradient buffer beside it; both sit in the symmetric heap so the sharded optimizer's collectives
+can address them by offset.  Weight-decayed tensors (matrices, embeddings) come first in the flat
+order, so "decay or not" is a single index comparison inside the optimizer kernel.
+
+Linear layers run on the tcgen05 GEMM in its K-major x K-major form:
+    forward   y  = x  W^T         A = x [M,K],     B = W  [N,K]
+    backward  dx = dy W           A = dy [M,N],    B = W^T [K,N]   (transposed copy, refreshed per step)
+              dW += dy^T x        A = dy^T [N,M],  B = x^T [K,M]   (accumulated in fp32 in the epilogue)
+The attention core currently calls torch's fused scaled-dot-product attention for its forward and
+backward inside training; the serving path uses this package's own attention kernels.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from ..models.config import ModelConfig
+from ..models.weights import TensorSpec, init_tensor, tensor_specs
+from ..ops import cuda_ops as ops
+from ..ops import train_ops as tops
+
+VOCAB_PAD = 128
+
+
+def padded_vocab(v: int) -> int:
+    return (v + VOCAB_PAD - 1) // VOCAB_PAD * VOCAB_PAD
+
+
+@dataclass
+class ParamSlot:
+    name: str
+    shape: tuple[int, ...]
+    offset: int          # element offset into the flat buffers
+    decay: bool
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+
+def param_layout(cfg: ModelConfig, align: int = 64) -> tuple[list[ParamSlot], int, int]:
+    """Flat layout: decayed tensors first.  Returns (slots, total elements, decay_end)."""
+    specs = tensor_specs(cfg)
+    Vp = padded_vocab(cfg.vocab)
+
+    def shape_of(s: TensorSpec):
+        return (Vp, cfg.d_model) if s.name == "token_embd.weight" else tuple(s.shape)
+
+    decayed = [s for s in specs if s.kind in ("matrix", "embed", "pos")]
+    plain = [s for s in specs if s.kind not in ("matrix", "embed", "pos")]
+    slots, off = [], 0
+    for group, dec in ((decayed, True), (plain, False)):
+        for s in group:
+            sh = shape_of(s)
+            n = 1
+            for d in sh:
+                n *= d
+            slots.append(ParamSlot(s.name, sh, off, dec))
+            off += (n + align - 1) // align * align
+        if dec:
+            decay_end = off
+    return slots, off, decay_end
+
+
+class GPT2Model:
+    """Holds views into the flat buffers and runs forward/backward for one micro-batch."""
+
+    def __init__(self, cfg: ModelConfig, params_bf16: torch.Tensor, grads_f32: torch.Tensor, slots: list[ParamSlot],
+                 micro_batch: int, seq_len: int):
+        self.cfg, self.B, self.T = cfg, micro_batch, seq_len
+        self.M = micro_batch * seq_len
+        self.dev = params_bf16.device
+        self.Vp = padded_vocab(cfg.vocab)
+        self.p, self.g = {}, {}
+        for s in slots:
+            self.p[s.name] = params_bf16[s.offset: s.offset + s.numel].view(*s.shape)
+            self.g[s.name] = grads_f32[s.offset: s.offset + s.numel].view(*s.shape)
+        self.slots = slots
+        d, f, M = cfg.d_model, cfg.ffn, self.M
+        bf = dict(dtype=torch.bfloat16, device=self.dev)
+        f32 = dict(dtype=torch.float32, device=self.dev)
+        # fp32 copies of the small vectors the kernels read in fp32 (LayerNorm gains, biases)
+        self.vec = {n: torch.empty(s.shape, **f32) for n, s in ((s.name, s) for s in slots) if len(s.shape) == 1}
+        # transposed weight copies for dx = dy W
+        self.wT = {s.name: torch.empty((s.shape[1], s.shape[0]), **bf) for s in slots
+                   if len(s.shape) == 2 and s.name.startswith("blk.")}
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        L = cfg.n_layers
+        self.act = [dict(x_in=torch.empty((M, d), **bf), ln1=torch.empty((M, d), **bf), mean1=torch.empty(M, **f32),
+                         rstd1=torch.empty(M, **f32), qkv=torch.empty((M, 3 * d), **bf), attn=torch.empty((M, d), **bf),
+                         x_mid=torch.empty((M, d), **bf), ln2=torch.empty((M, d), **bf), mean2=torch.empty(M, **f32),
+                         rstd2=torch.empty(M, **f32), h=torch.empty((M, f), **bf), a=torch.empty((M, f), **bf))
+                    for _ in range(L)]
+        self.x_out = torch.empty((M, d), **bf)
+        self.lnf = torch.empty((M, d), **bf)
+        self.meanf, self.rstdf = torch.empty(M, **f32), torch.empty(M, **f32)
+        self.logits = torch.empty((M, self.Vp), **bf)
+        self.loss_rows = torch.empty(M, **f32)
+        # backward scratch
+        self.dx = torch.empty((M, d), **bf)
+        self.d_a = torch.empty((M, f), **bf)
+        self.d_d = torch.empty((M, d), **bf)
+        self.d_qkv = torch.empty((M, 3 * d), **bf)
+        self.tA = torch.empty(max(f, 3 * d, self.Vp) * M, **bf)     # transposed dy
+        self.tB = torch.empty(max(max(f, 3 * d) * M, d * self.Vp), **bf)   # transposed activation / tied embedding
+        self.kernel_launches = 0
+
+    # ---- helpers
+    def refresh_param_views(self):
+        """Call after every optimizer step: fp32 vector copies and transposed matrices."""
+        for n, v in self.vec.items():
+            v.copy_(self.p[n])
+        for n, t in self.wT.items():
+            ops.transpose_bf16(self.p[n], t)
+            self.kernel_launches += 1
+
+    def _gemm(self, A, B, M, N, K, **kw):
+        ops.gemm_bf16(A, B, M, N, K, status=self.status, **kw)
+        self.kernel_launches += 1
+
+    def _linear_fwd(self, x, wname, bname, out, resid=None):
+        W = self.p[wname]
+        N, K = W.shape
+        self._gemm(x, W, x.shape[0], N, K, out_bf16=out, bias=self.vec[bname] if bname else None, resid_bf16=resid)
+
+    def _linear_bwd(self, dy, x, wname, bname, dx_out):
+        """dW += dy^T x, db += colsum(dy), dx_out = dy W (if requested)."""
+        W = self.p[wname]
+        N, K = W.shape
+        M = dy.shape[0]
+        dyT = self.tA[: N * M].view(N, M)
+        xT = self.tB[: K * M].view(K, M)
+        ops.transpose_bf16(dy, dyT)
+        ops.transpose_bf16(x, xT)
+        self.kernel_launches += 2
+        self._gemm(dyT, xT, N, K, M, out_f32=self.g[wname], accumulate=True)
+        if bname:
+            tops.bias_grad(dy, self.g[bname])
+            self.kernel_launches += 1
+        if dx_out is not None:
+            self._gemm(dy, self.wT[wname], M, K, N, out_bf16=dx_out)
+
+    # ---- forward + backward of one micro-batch; returns the mean loss (device scalar)
+    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, loss_scale: float = 1.0):
+        cfg, M, T, d = self.cfg, self.M, self.T, self.cfg.d_model
+        H, hd = cfg.n_heads, cfg.head_dim
+        ids = tokens.reshape(-1).to(torch.int32)
+        tg = targets.reshape(-1).to(torch.int32)
+        x = self.act[0]["x_in"]
+        tops.embed_fwd(ids, self.p["token_embd.weight"], self.p["position_embd.weight"], x, T)
+        self.kernel_launches += 1
+        attn_saved = []
+        for i, a in enumerate(self.act):
+            pre = f"blk.{i}."
+            x = a["x_in"]
+            tops.layernorm_fwd(x, self.vec[pre + "attn_norm.weight"], self.vec[pre + "attn_norm.bias"], cfg.norm_eps,
+                               a["ln1"], a["mean1"], a["rstd1"])
+            self._linear_fwd(a["ln1"], pre + "attn_qkv.weight", pre + "attn_qkv.bias", a["qkv"])
+            qkv = a["qkv"].view(self.B, T, 3, H, hd).permute(2, 0, 3, 1, 4)       # [3, B, H, T, hd]
+            q, k, v = (t.detach().requires_grad_(True) for t in (qkv[0], qkv[1], qkv[2]))
+            with torch.enable_grad():
+                o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+            attn_saved.append((q, k, v, o))
+            a["attn"].view(self.B, T, H, hd).copy_(o.detach().permute(0, 2, 1, 3))
+            self._linear_fwd(a["attn"], pre + "attn_output.weight", pre + "attn_output.bias", a["x_mid"], resid=x)
+            tops.layernorm_fwd(a["x_mid"], self.vec[pre + "ffn_norm.weight"], self.vec[pre + "ffn_norm.bias"],
+                               cfg.norm_eps, a["ln2"], a["mean2"], a["rstd2"])
+            self._linear_fwd(a["ln2"], pre + "ffn_up.weight", pre + "ffn_up.bias", a["h"])
+            tops.gelu_fwd(a["h"], a["a"])
+            nxt = self.act[i + 1]["x_in"] if i + 1 < len(self.act) else self.x_out
+            self._linear_fwd(a["a"], pre + "ffn_down.weight", pre + "ffn_down.bias", nxt, resid=a["x_mid"])
+            self.kernel_launches += 3
+        tops.layernorm_fwd(self.x_out, self.vec["output_norm.weight"], self.vec["output_norm.bias"], cfg.norm_eps,
+                           self.lnf, self.meanf, self.rstdf)
+        wte = self.p["token_embd.weight"]
+        self._gemm(self.lnf, wte, M, self.Vp, d, out_bf16=self.logits)
+        tops.ce_fused(self.logits, tg, self.loss_rows, loss_scale / M, cfg.vocab)     # logits now hold dlogits
+        self.kernel_launches += 2
+        loss = self.loss_rows.mean()
+
+        # ---- backward
+        dlog = self.logits
+        # tied embedding: d wte += dlogits^T lnf ; d lnf = dlogits wte
+        dlT = self.tA[: self.Vp * M].view(self.Vp, M)
+        lnfT = self.tB[: d * M].view(d, M)
+        ops.transpose_bf16(dlog, dlT)
+        ops.transpose_bf16(self.lnf, lnfT)
+        self._gemm(dlT, lnfT, self.Vp, d, M, out_f32=self.g["token_embd.weight"], accumulate=True)
+        wteT = self.tB[: d * self.Vp].view(d, self.Vp)
+        ops.transpose_bf16(wte, wteT)
+        self._gemm(dlog, wteT, M, d, self.Vp, out_bf16=self.d_d)
+        tops.layernorm_bwd(self.d_d, self.x_out, self.vec["output_norm.weight"], self.meanf, self.rstdf, self.dx, False,
+                           self.g["output_norm.weight"], self.g["output_norm.bias"])
+        self.kernel_launches += 4
+        for i in reversed(range(len(self.act))):
+            a = self.act[i]
+            pre = f"blk.{i}."
+            # FFN branch: x_out = x_mid + down(gelu(up(ln2(x_mid))))
+            self._linear_bwd(self.dx, a["a"], pre + "ffn_down.weight", pre + "ffn_down.bias", self.d_a)
+            tops.gelu_bwd(a["h"], self.d_a)
+            self._linear_bwd(self.d_a, a["ln2"], pre + "ffn_up.weight", pre + "ffn_up.bias", self.d_d)
+            tops.layernorm_bwd(self.d_d, a["x_mid"], self.vec[pre + "ffn_norm.weight"], a["mean2"], a["rstd2"], self.dx,
+                               True, self.g[pre + "ffn_norm.weight"], self.g[pre + "ffn_norm.bias"])
+            # attention branch: x_mid = x_in + proj(attn(qkv(ln1(x_in))))
+            self._linear_bwd(self.dx, a["attn"], pre + "attn_output.weight", pre + "attn_output.bias", self.d_d)
+            q, k, v, o = attn_saved[i]
+            do = self.d_d.view(self.B, T, H, hd).permute(0, 2, 1, 3)
+            dq, dk, dv = torch.autograd.grad(o, (q, k, v), do)
+            dqkv = self.d_qkv.view(self.B, T, 3, H, hd)
+            dqkv[:, :, 0].copy_(dq.permute(0, 2, 1, 3))
+            dqkv[:, :, 1].copy_(dk.permute(0, 2, 1, 3))
+            dqkv[:, :, 2].copy_(dv.permute(0, 2, 1, 3))
+            self._linear_bwd(self.d_qkv, a["ln1"], pre + "attn_qkv.weight", pre + "attn_qkv.bias", self.d_d)
+            tops.layernorm_bwd(self.d_d, a["x_in"], self.vec[pre + "attn_norm.weight"], a["mean1"], a["rstd1"], self.dx,
+                               True, self.g[pre + "attn_norm.weight"], self.g[pre + "attn_norm.bias"])
+            attn_saved[i] = None
+            self.kernel_launches += 3
+        tops.embed_bwd(ids, self.dx, self.g["token_embd.weight"], self.g["position_embd.weight"], T)
+        self.kernel_launches += 1
+        return loss

@@ -337,3 +337,69 @@ def test_swiglu_add_cast_transpose():
     mt = torch.empty((45, 70), dtype=torch.bfloat16, device=DEV)
     ops.transpose_bf16(m, mt)
     assert torch.equal(mt, m.t().contiguous())
+
+
+def test_train_ops_match_torch():
+    from openagents_b200.ops import train_ops as tops
+    M, D, F_, V = 96, 256, 512, 1000
+    x = _randn(M, D, seed=30).bfloat16()
+    g, b = (_randn(D, seed=31) * 0.1 + 1.0), _randn(D, seed=32) * 0.1
+    y = torch.empty_like(x)
+    mean, rstd = torch.empty(M, device=DEV), torch.empty(M, device=DEV)
+    tops.layernorm_fwd(x, g, b, 1e-5, y, mean, rstd)
+    xr = x.float().requires_grad_(True)
+    gr, br = g.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    ref = torch.nn.functional.layer_norm(xr, (D,), gr, br, 1e-5)
+    assert torch.allclose(y.float(), ref, atol=3e-2, rtol=2e-2)
+    dy = _randn(M, D, seed=33).bfloat16()
+    ref.backward(dy.float())
+    dx = torch.full((M, D), 0.5, dtype=torch.bfloat16, device=DEV)
+    dg, db = torch.zeros(D, device=DEV), torch.zeros(D, device=DEV)
+    tops.layernorm_bwd(dy, x, g, mean, rstd, dx, True, dg, db)
+    assert torch.allclose(dx.float(), xr.grad + 0.5, atol=6e-2, rtol=3e-2)
+    assert torch.allclose(dg, gr.grad, atol=0.15, rtol=2e-2) and torch.allclose(db, br.grad, atol=0.15, rtol=2e-2)
+    # GELU
+    h = _randn(M, F_, seed=34).bfloat16()
+    a = torch.empty_like(h)
+    tops.gelu_fwd(h, a)
+    hr = h.float().requires_grad_(True)
+    ar = torch.nn.functional.gelu(hr, approximate="tanh")
+    assert torch.allclose(a.float(), ar, atol=2e-2, rtol=2e-2)
+    da = _randn(M, F_, seed=35).bfloat16()
+    ar.backward(da.float())
+    dh = da.clone()
+    tops.gelu_bwd(h, dh)
+    assert torch.allclose(dh.float(), hr.grad, atol=3e-2, rtol=3e-2)
+    # bias gradient
+    gb = torch.zeros(F_, device=DEV)
+    tops.bias_grad(da, gb)
+    assert torch.allclose(gb, da.float().sum(0), atol=1e-2, rtol=1e-3)
+    # fused cross-entropy (vocabulary padded to 1024 columns; one masked row)
+    ldl = 1024
+    logits = (_randn(M, ldl, seed=36) * 2).bfloat16()
+    tgt = torch.randint(0, V, (M,), device=DEV, dtype=torch.int32)
+    tgt[5] = -1
+    lr_ = logits[:, :V].float().requires_grad_(True)
+    keep = tgt >= 0
+    lref = torch.nn.functional.cross_entropy(lr_[keep], tgt[keep].long(), reduction="none")
+    (lref.sum() / M).backward()
+    loss = torch.empty(M, device=DEV)
+    work = logits.clone()
+    tops.ce_fused(work, tgt, loss, 1.0 / M, V)
+    assert torch.allclose(loss[keep], lref, atol=2e-2, rtol=1e-2) and float(loss[5]) == 0.0
+    assert torch.allclose(work[:, :V].float(), lr_.grad, atol=2e-4 + 1e-2 * lr_.grad.abs().max().item(), rtol=2e-2)
+    assert float(work[:, V:].abs().sum()) == 0.0
+    # embedding forward / backward
+    Vv, T = 50, 8
+    wte, wpe = _randn(Vv, D, seed=37).bfloat16(), _randn(T, D, seed=38).bfloat16()
+    ids = torch.randint(0, Vv, (3 * T,), device=DEV, dtype=torch.int32)
+    e = torch.empty((3 * T, D), dtype=torch.bfloat16, device=DEV)
+    tops.embed_fwd(ids, wte, wpe, e, T)
+    pos = torch.arange(3 * T, device=DEV) % T
+    assert torch.allclose(e.float(), (wte[ids.long()].float() + wpe[pos].float()), atol=2e-2, rtol=1e-2)
+    de = _randn(3 * T, D, seed=39).bfloat16()
+    gte, gpe = torch.zeros(Vv, D, device=DEV), torch.zeros(T, D, device=DEV)
+    tops.embed_bwd(ids, de, gte, gpe, T)
+    rte = torch.zeros(Vv, D, device=DEV).index_add_(0, ids.long(), de.float())
+    rpe = torch.zeros(T, D, device=DEV).index_add_(0, pos, de.float())
+    assert torch.allclose(gte, rte, atol=1e-3) and torch.allclose(gpe, rpe, atol=1e-3)
