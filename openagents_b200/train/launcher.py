@@ -1,0 +1,136 @@
+"""``b200-train``: the distributed-training launcher.
+
+    python -m openagents_b200.train.launcher --nproc 8 --steps 20 [--ckpt-dir DIR] [--resume DIR]
+
+With ``--nproc N > 1`` it re-executes itself under ``torch.distributed.run`` (one process per GPU,
+rendezvous on 127.0.0.1); each worker then builds the trainer, walks the run/window state machine
+(plan -> active -> seal -> reconcile) around its steps and, at the end of a window, writes a
+checkpoint whose seal descriptor goes through the durable-seal predicate.
+
+Flags follow the trainer contract (``--zero-stage --global-batch --seq-len --lr --betas --wd --clip
+--ckpt-dir --resume``); the run/window semantics are the reference's
+(apps/openagents.com/workers/api/src/training-run-window-authority.ts:43-56, 219-231).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+
+def parse(argv=None):
+    ap = argparse.ArgumentParser(prog="b200-train")
+    ap.add_argument("--nproc", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--window-steps", type=int, default=0, help="optimizer steps per window (0 = one window)")
+    ap.add_argument("--model", default="gpt2-small-shape")
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--zero-stage", type=int, default=2)
+    ap.add_argument("--global-batch", type=int, default=512)
+    ap.add_argument("--micro-batch", type=int, default=16)
+    ap.add_argument("--seq-len", type=int, default=1024)
+    ap.add_argument("--lr", type=float, default=6e-4)
+    ap.add_argument("--betas", type=float, nargs=2, default=(0.9, 0.95))
+    ap.add_argument("--wd", type=float, default=0.1)
+    ap.add_argument("--clip", type=float, default=1.0)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--ckpt-dir", default="")
+    ap.add_argument("--resume", default="")
+    ap.add_argument("--max-allowed-stale", type=int, default=5)
+    ap.add_argument("--master-port", type=int, default=29517)
+    ap.add_argument("--log-jsonl", default="")
+    return ap.parse_args(argv)
+
+
+def worker(args):
+    import torch
+    import torch.distributed as dist
+    from ..control import run_window as rw
+    from ..models.config import PRESETS
+    from .checkpoint import seal_descriptor
+    from .trainer import TrainConfig, Trainer, synthetic_batch
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    model = PRESETS[args.model]
+    if args.layers:
+        model = model.with_(n_layers=args.layers)
+    cfg = TrainConfig(model=model, global_batch=args.global_batch, micro_batch=args.micro_batch, seq_len=args.seq_len,
+                      lr=args.lr, betas=tuple(args.betas), weight_decay=args.wd, grad_clip=args.clip, seed=args.seed,
+                      zero_stage=args.zero_stage)
+    tr = Trainer(cfg, dev, rank, world)
+    if args.resume:
+        man = tr.load_checkpoint(args.resume)
+        if rank == 0:
+            print(json.dumps({"event": "resumed", "step": man["step"], "checkpointDigestRef": man["checkpointDigestRef"]}))
+    auth = rw.Authority()
+    run = auth.plan_run("promise.local.train", max_allowed_stale=args.max_allowed_stale)
+    auth.advance_run(run.run_ref, "active")
+    wsteps = args.window_steps or args.steps
+    log = open(args.log_jsonl, "a") if (args.log_jsonl and rank == 0) else None
+    step0 = tr.step_count
+    done = 0
+    while done < args.steps:
+        n = min(wsteps, args.steps - done)
+        w = auth.plan_window(run.run_ref, step0 + done, step0 + done + n)
+        auth.activate_window(w.window_ref)
+        auth.claim_lease(w.window_ref, f"worker.rank{rank}")
+        t_train = 0.0
+        for _ in range(n):
+            tok, tgt = synthetic_batch(cfg, tr.accum, tr.step_count, rank, dev)
+            tok, tgt = tok.pin_memory().to(dev, non_blocking=True), tgt.pin_memory().to(dev, non_blocking=True)
+            t0 = time.perf_counter()
+            loss = tr.train_step(tok, tgt)
+            lv = float(loss.item())
+            dt = time.perf_counter() - t0
+            t_train += dt
+            rec = {"event": "step", "step": tr.step_count, "loss": round(lv, 5), "grad_norm": round(tr.grad_norm(), 5),
+                   "step_s": round(dt, 4), "tokens_per_s": round(cfg.global_batch * cfg.seq_len / dt, 1), "lr": tr.lr_at(tr.step_count - 1)}
+            if rank == 0:
+                print(json.dumps(rec), flush=True)
+                if log:
+                    log.write(json.dumps(rec) + "\n")
+        tr.check_status()
+        done += n
+        meta = rw.SealMetadata(verification_overhead={"verificationSeconds": 0.0, "trainingSeconds": t_train})
+        if args.ckpt_dir:
+            d = os.path.join(args.ckpt_dir, f"step{tr.step_count:08d}")
+            man = tr.save_checkpoint(d, run_ref=run.run_ref, window_ref=w.window_ref, term=run.term)
+            if rank == 0:
+                meta.checkpoint_digest_ref = man["checkpointDigestRef"]
+                meta.durable_checkpoint_seal = seal_descriptor(man, d)
+        _, gate = auth.seal_window(w.window_ref, meta)
+        if rank == 0:
+            print(json.dumps({"event": "window", "windowRef": w.window_ref, "state": auth._window(w.window_ref).state,
+                              "sealDecision": gate.decision if gate else None, "reasons": list(gate.reasons) if gate else []}))
+        if auth._window(w.window_ref).state == "sealed":
+            auth.reconcile_window(w.window_ref)
+        else:
+            # HOLD: the checkpoint is not durable (one local replica).  Training goes on; the window
+            # stays open for an operator to seal once a replicated store has confirmed the copy.
+            pass
+    if log:
+        log.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main(argv=None):
+    args = parse(argv)
+    if args.nproc > 1 and "RANK" not in os.environ:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.nproc}",
+               "--master-addr", "127.0.0.1", "--master-port", str(args.master_port), "-m", "openagents_b200.train.launcher"]
+        cmd += sys.argv[1:] if argv is None else list(argv)
+        raise SystemExit(subprocess.call(cmd))
+    worker(args)
+
+
+if __name__ == "__main__":
+    main()

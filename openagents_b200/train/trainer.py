@@ -156,6 +156,58 @@ class Trainer:
         return out
 
 
+    # ---- checkpoints
+    def save_checkpoint(self, ckpt_dir: str, run_ref: str = "run.local", window_ref: str = "run.local.w0", term: int = 0):
+        """Every rank writes its shard files; rank 0 (the commit authority) writes the manifest."""
+        import dataclasses
+        from . import checkpoint as ck
+        torch.cuda.synchronize(self.device)
+        mine = ck.save_shard(ckpt_dir, self.rank, self.master, self.m, self.v)
+        files = dict(mine)
+        if self.world > 1:
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, mine)
+            files = {}
+            for g in gathered:
+                files.update(g)
+        man = None
+        if self.rank == 0:
+            tc_ = dataclasses.asdict(self.cfg)
+            man = ck.write_manifest(ckpt_dir, files, run_ref=run_ref, window_ref=window_ref, step=self.step_count,
+                                    world_size=self.world, zero_stage=self.cfg.zero_stage, n_total=self.n_total,
+                                    shard=self.shard, term=term, train_config=tc_, model_config=self.cfg.model.as_dict())
+        if self.world > 1:
+            dist.barrier()
+        return man
+
+    def load_checkpoint(self, ckpt_dir: str) -> dict:
+        """Verify digests, re-shard if the world size differs, restore master/moments/step and the
+        bf16 working parameters."""
+        from . import checkpoint as ck
+        man, master, m, v = ck.load_full(ckpt_dir)
+        self.master.copy_(ck.reshard(master, self.n_total, self.world, self.rank))
+        self.m.copy_(ck.reshard(m, self.n_total, self.world, self.rank))
+        self.v.copy_(ck.reshard(v, self.n_total, self.world, self.rank))
+        full = master
+        if full.numel() < self.n_total:
+            full = torch.cat((full, torch.zeros(self.n_total - full.numel())))
+        self.params.copy_(full[: self.n_total].to(self.device).to(torch.bfloat16))
+        self.step_count = int(man["step"])
+        self.grads.zero_()
+        self.model.refresh_param_views()
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier()
+        return man
+
+    def export_gguf(self, path: str, plan=None):
+        """Save the trained model through the same GGUF writer the serving loader reads."""
+        from ..models.weights import PLAN_BF16, save_gguf
+        named = self.named_master()
+        if self.rank == 0:
+            save_gguf(path, self.cfg.model, {k: v.cpu() for k, v in named.items()}, plan or PLAN_BF16)
+
+
 def synthetic_batch(cfg: TrainConfig, accum: int, step: int, rank: int, device):
     """Uniform random token ids of the training shape (seeded per step and rank)."""
     g = torch.Generator(device="cpu").manual_seed(cfg.seed * 7919 + step * 104729 + rank)
