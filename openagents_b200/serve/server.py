@@ -1,0 +1,368 @@
+"""``b200-serve``: OpenAI-compatible model server.
+
+    python -m openagents_b200.serve.server -m model.gguf --backend cuda --host 127.0.0.1 --port 8080
+
+Flags and routes follow the reference's description of its model server
+(apps/pylon/docs/2026-06-09-pylon-qwen35-local-inference-roadmap.md:137-160, 232-236):
+``-m`` (repeatable), ``--backend cpu|cuda``, ``--host``, ``--port``, ``--reasoning-budget``,
+``--mesh-coordination enabled|disabled``; ``GET /health`` (reports ``execution_engine`` and the
+endpoints), ``GET /v1/models``, ``POST /v1/chat/completions`` (streaming and not), ``POST
+/v1/responses`` (with ``previous_response_id`` replay), ``GET /psionic/management/status``; plus
+``/v1/sessions`` in the shape of the one in-tree local model server with session semantics
+(packages/apple-fm-runtime/native/foundation-bridge/Sources/foundation-bridge/main.swift:472-494)
+and a Prometheus ``/metrics``.  ``POST /v1/serve`` answers the gateway's serve wire contract
+(apps/openagents.com/workers/api/src/inference/psionic-fabric-serve.ts:116-164) including the
+exact-greedy parity check: the request is decoded a second time on the same engine and the two
+token streams must be identical.
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import json
+import threading
+import time
+import uuid
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+from .. import ENGINE_NAME, __version__
+from ..utils.telemetry import Histogram, measured, not_measured
+from .generation import (CHAT_TEMPLATE_DIGEST, ByteTokenizer, Request, SamplingParams, Scheduler, VocabTokenizer,
+                         render_chat)
+
+ENDPOINTS = ["/health", "/v1/models", "/v1/chat/completions", "/v1/responses", "/v1/sessions", "/v1/serve",
+             "/psionic/management/status", "/metrics"]
+
+
+class ServedModel:
+    def __init__(self, model_id: str, backend, artifact_digest: str | None, tokenizer=None, max_num_seqs: int = 64,
+                 prefill_chunk: int = 2048):
+        self.id, self.backend, self.artifact_digest = model_id, backend, artifact_digest
+        self.tok = tokenizer or ByteTokenizer(backend.cfg.vocab)
+        self.sched = Scheduler(backend, self.tok, max_num_seqs=max_num_seqs, prefill_chunk=prefill_chunk)
+        self.lock = threading.Lock()      # one engine, one scheduling thread at a time
+        self.created = int(time.time())
+
+    def generate(self, prompt_ids, params, seq_id=None, keep=False, on_token=None) -> Request:
+        with self.lock:
+            r = self.sched.submit(prompt_ids, params, seq_id=seq_id, keep_sequence=keep, on_token=on_token)
+            self.sched.run_until_done([r])
+        return r
+
+
+class Session:
+    def __init__(self, sid: str, model: ServedModel):
+        self.id, self.model = sid, model
+        self.seq_id: int | None = None
+        self.tokens: list[int] = []       # everything the sequence's KV covers, plus the pending tail
+        self.pending: list[int] = []      # generated tokens whose K/V have not been written yet
+        self.responses: list[str] = []
+        self.created = time.time()
+
+
+class ServerState:
+    def __init__(self, models: list[ServedModel], reasoning_budget: int = 0, mesh_coordination: str = "disabled"):
+        self.models = {m.id: m for m in models}
+        self.default = models[0]
+        self.sessions: dict[str, Session] = {}
+        self.responses: dict[str, tuple[str, str]] = {}     # response id -> (session id, text)
+        self.reasoning_budget, self.mesh_coordination = reasoning_budget, mesh_coordination
+        self.started = time.time()
+        self.ttft = Histogram([0.005, 0.01, 0.025, 0.05, 0.1, 0.25, 0.5, 1, 2.5, 5, 10])
+        self.itl = Histogram([0.0005, 0.001, 0.002, 0.005, 0.01, 0.02, 0.05, 0.1, 0.25])
+        self.lock = threading.Lock()
+
+    def model(self, name: str | None) -> ServedModel:
+        if not name:
+            return self.default
+        if name not in self.models:
+            raise KeyError(name)
+        return self.models[name]
+
+    # ---- one completion, with or without a session
+    def complete(self, model: ServedModel, messages: list[dict], body: dict, session: Session | None = None,
+                 on_token=None) -> tuple[Request, dict]:
+        params = SamplingParams(max_tokens=int(body.get("max_tokens") or body.get("max_output_tokens") or 128),
+                                temperature=float(body.get("temperature") or 0.0), top_p=float(body.get("top_p") or 1.0),
+                                top_k=int(body.get("top_k") or 0),
+                                stop=tuple(body["stop"]) if isinstance(body.get("stop"), list) else ((body["stop"],) if body.get("stop") else ()),
+                                seed=body.get("seed"))
+        ids = model.tok.encode(render_chat(messages))
+        if session is None:
+            r = model.generate(ids, params, on_token=on_token)
+        else:
+            feed = session.pending + ids
+            if session.seq_id is None:
+                r = model.generate(feed, params, keep=True, on_token=on_token)
+                session.seq_id = r.seq_id
+            else:
+                r = model.generate(feed, params, seq_id=session.seq_id, keep=True, on_token=on_token)
+            session.tokens += feed + r.output[:-1] if r.output else feed
+            session.pending = r.output[-1:] if r.output else []
+        usage = {"prompt_tokens": len(ids), "completion_tokens": len(r.output), "total_tokens": len(ids) + len(r.output),
+                 "prompt_tokens_details": {"cached_tokens": r.cached_prompt_tokens}}
+        with self.lock:
+            if r.ttft_s is not None:
+                self.ttft.observe(r.ttft_s)
+            if r.t_done and r.t_first_token and len(r.output) > 1:
+                self.itl.observe((r.t_done - r.t_first_token) / (len(r.output) - 1))
+        return r, usage
+
+    def serve_contract(self, model: ServedModel, body: dict) -> dict:
+        """The gateway's serve request: greedy decode twice on this engine; parity = same tokens."""
+        msgs = body.get("messages") or []
+        pp = dict(body.get("passthroughParams") or {})
+        pp["temperature"] = 0.0
+        r1, usage = self.complete(model, msgs, pp)
+        parity = False
+        if body.get("requireExactGreedyParity", True):
+            r2, _ = self.complete(model, msgs, pp)
+            parity = r1.output == r2.output
+        topo = model.backend.topology()
+        run_ref = "serve." + hashlib.sha256(json.dumps([model.id, msgs, r1.output]).encode()).hexdigest()[:24]
+        return {"content": model.tok.decode(r1.output), "finishReason": r1.finish_reason or "stop",
+                "usage": {"promptTokens": usage["prompt_tokens"], "completionTokens": usage["completion_tokens"],
+                          "totalTokens": usage["total_tokens"], "cachedPromptTokens": r1.cached_prompt_tokens},
+                "servedModel": model.id, "servingRunRef": run_ref, "stages": topo["stages"],
+                "parityMode": "exact_greedy_parity" if body.get("requireExactGreedyParity", True) else "none",
+                "parityVerified": parity,
+                "tokenHash": "sha256:" + hashlib.sha256(json.dumps(r1.output).encode()).hexdigest()}
+
+    def status(self) -> dict:
+        return {"execution_engine": ENGINE_NAME, "version": __version__, "uptime_s": round(time.time() - self.started, 1),
+                "mesh_coordination": self.mesh_coordination, "reasoning_budget": self.reasoning_budget,
+                "models": [{"id": m.id, "backend": m.backend.name, "architecture": m.backend.cfg.arch,
+                            "artifact_digest": m.artifact_digest, "kv": m.backend.kv_stats(),
+                            "topology": m.backend.topology(), "scheduler": dict(m.sched.stats)} for m in self.models.values()],
+                "sessions": len(self.sessions)}
+
+    def metrics_text(self) -> str:
+        out = []
+        for m in self.models.values():
+            s, lab = m.sched.stats, f'{{model="{m.id}"}}'
+            out += [f"b200_requests_total{lab} {s['requests']}", f"b200_prompt_tokens_total{lab} {s['prompt_tokens']}",
+                    f"b200_completion_tokens_total{lab} {s['completion_tokens']}",
+                    f"b200_prefix_cache_hit_tokens_total{lab} {s['cached_prompt_tokens']}",
+                    f"b200_decode_steps_total{lab} {s['steps']}",
+                    f"b200_decode_batch_size_avg{lab} {s['batch_size_sum'] / s['steps'] if s['steps'] else 0}"]
+            for k, v in m.backend.kv_stats().items():
+                out.append(f"b200_kv_{k}{lab} {v}")
+        out += self.ttft.prometheus("b200_ttft_seconds") + self.itl.prometheus("b200_inter_token_latency_seconds")
+        return "\n".join(out) + "\n"
+
+
+def make_handler(state: ServerState):
+    class H(BaseHTTPRequestHandler):
+        protocol_version = "HTTP/1.1"
+
+        def log_message(self, *a):
+            pass
+
+        def _json(self, code: int, obj):
+            data = json.dumps(obj).encode()
+            self.send_response(code)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
+
+        def _err(self, code: int, msg: str, kind: str = "invalid_request_error"):
+            self._json(code, {"error": {"message": msg, "type": kind}})
+
+        def _body(self):
+            n = int(self.headers.get("Content-Length") or 0)
+            raw = self.rfile.read(n) if n else b"{}"
+            try:
+                obj = json.loads(raw)
+            except json.JSONDecodeError:
+                return None
+            return obj if isinstance(obj, dict) else None
+
+        def do_GET(self):
+            path = self.path.split("?")[0]
+            if path == "/health":
+                return self._json(200, {"status": "ok", "execution_engine": ENGINE_NAME, "endpoints": ENDPOINTS,
+                                        "models": list(state.models)})
+            if path == "/v1/models":
+                return self._json(200, {"object": "list", "data": [
+                    {"id": m.id, "object": "model", "created": m.created, "owned_by": ENGINE_NAME,
+                     "artifact_digest": m.artifact_digest, "architecture": m.backend.cfg.arch,
+                     "chat_template_digest": CHAT_TEMPLATE_DIGEST, "context_length": m.backend.cfg.context}
+                    for m in state.models.values()]})
+            if path == "/psionic/management/status":
+                return self._json(200, state.status())
+            if path == "/metrics":
+                data = state.metrics_text().encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/plain; version=0.0.4")
+                self.send_header("Content-Length", str(len(data)))
+                self.end_headers()
+                return self.wfile.write(data)
+            if path == "/v1/sessions":
+                return self._json(200, {"sessions": [{"id": s.id, "model": s.model.id, "tokens": len(s.tokens),
+                                                      "responses": s.responses} for s in state.sessions.values()]})
+            self._err(404, f"no route {path}", "not_found")
+
+        def do_DELETE(self):
+            parts = self.path.strip("/").split("/")
+            if len(parts) == 3 and parts[:2] == ["v1", "sessions"] and parts[2] in state.sessions:
+                s = state.sessions.pop(parts[2])
+                if s.seq_id is not None:
+                    with s.model.lock:
+                        s.model.backend.end(s.seq_id)
+                return self._json(200, {"deleted": s.id})
+            self._err(404, "no such session", "not_found")
+
+        def do_POST(self):
+            path = self.path.split("?")[0]
+            body = self._body()
+            if body is None:
+                return self._err(400, "request body must be a JSON object")
+            try:
+                model = state.model(body.get("model"))
+            except KeyError:
+                return self._err(404, f"model {body.get('model')!r} is not served", "model_not_found")
+            try:
+                if path == "/v1/chat/completions":
+                    return self._chat(model, body)
+                if path == "/v1/responses":
+                    return self._responses(model, body)
+                if path == "/v1/serve":
+                    return self._json(200, state.serve_contract(model, body))
+                if path == "/v1/sessions":
+                    s = Session("sess-" + uuid.uuid4().hex[:16], model)
+                    state.sessions[s.id] = s
+                    return self._json(200, {"id": s.id, "model": model.id})
+                parts = path.strip("/").split("/")
+                if len(parts) == 4 and parts[:2] == ["v1", "sessions"] and parts[3] == "responses":
+                    s = state.sessions.get(parts[2])
+                    if s is None:
+                        return self._err(404, "no such session", "not_found")
+                    msgs = body.get("messages") or [{"role": "user", "content": str(body.get("input", ""))}]
+                    r, usage = state.complete(s.model, msgs, body, session=s)
+                    rid = "resp-" + uuid.uuid4().hex[:16]
+                    s.responses.append(rid)
+                    return self._json(200, {"id": rid, "session": s.id, "output_text": s.model.tok.decode(r.output),
+                                            "usage": usage})
+            except MemoryError as e:
+                return self._err(503, str(e), "kv_cache_exhausted")
+            except Exception as e:      # surface engine errors as a typed, non-retryable failure
+                return self._err(500, f"{type(e).__name__}: {e}", "engine_error")
+            self._err(404, f"no route {path}", "not_found")
+
+        def _chat(self, model, body):
+            msgs = body.get("messages")
+            if not isinstance(msgs, list) or not msgs:
+                return self._err(400, "messages must be a non-empty list")
+            cid = "chatcmpl-" + uuid.uuid4().hex[:24]
+            created = int(time.time())
+            if body.get("stream"):
+                self.send_response(200)
+                self.send_header("Content-Type", "text/event-stream")
+                self.send_header("Cache-Control", "no-cache")
+                self.send_header("Transfer-Encoding", "chunked")
+                self.end_headers()
+
+                def chunk(obj):
+                    data = ("data: " + (obj if isinstance(obj, str) else json.dumps(obj)) + "\n\n").encode()
+                    self.wfile.write(f"{len(data):x}\r\n".encode() + data + b"\r\n")
+                    self.wfile.flush()
+
+                base = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model.id}
+                chunk({**base, "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]})
+                pending: list[int] = []
+
+                def on_token(t):
+                    pending.append(t)
+                    text = model.tok.decode(pending)
+                    if text and not text.endswith("�"):       # hold back incomplete UTF-8 sequences
+                        chunk({**base, "choices": [{"index": 0, "delta": {"content": text}, "finish_reason": None}]})
+                        pending.clear()
+
+                r, usage = state.complete(model, msgs, body, on_token=on_token)
+                chunk({**base, "choices": [{"index": 0, "delta": {}, "finish_reason": r.finish_reason}], "usage": usage})
+                chunk("[DONE]")
+                self.wfile.write(b"0\r\n\r\n")
+                return
+            r, usage = state.complete(model, msgs, body)
+            msg = {"role": "assistant", "content": model.tok.decode(r.output)}
+            self._json(200, {"id": cid, "object": "chat.completion", "created": created, "model": model.id,
+                             "choices": [{"index": 0, "message": msg, "finish_reason": r.finish_reason}], "usage": usage,
+                             "timings": {"ttft_ms": None if r.ttft_s is None else round(r.ttft_s * 1e3, 3),
+                                         "predicted_per_second": (len(r.output) - 1) / (r.t_done - r.t_first_token)
+                                         if r.t_done and r.t_first_token and len(r.output) > 1 and r.t_done > r.t_first_token else None}})
+
+        def _responses(self, model, body):
+            inp = body.get("input")
+            msgs = inp if isinstance(inp, list) else [{"role": "user", "content": str(inp or "")}]
+            prev = body.get("previous_response_id")
+            if prev is not None:
+                if prev not in state.responses:
+                    return self._err(404, f"previous_response_id {prev!r} is unknown", "not_found")
+                sess = state.sessions[state.responses[prev][0]]
+            else:
+                sess = Session("sess-" + uuid.uuid4().hex[:16], model)
+                state.sessions[sess.id] = sess
+            r, usage = state.complete(sess.model, msgs, body, session=sess)
+            rid = "resp-" + uuid.uuid4().hex[:16]
+            text = sess.model.tok.decode(r.output)
+            state.responses[rid] = (sess.id, text)
+            sess.responses.append(rid)
+            self._json(200, {"id": rid, "object": "response", "model": sess.model.id, "previous_response_id": prev,
+                             "status": "completed", "output_text": text,
+                             "output": [{"type": "message", "role": "assistant", "content": [{"type": "output_text", "text": text}]}],
+                             "usage": {"input_tokens": usage["prompt_tokens"], "output_tokens": usage["completion_tokens"],
+                                       "total_tokens": usage["total_tokens"],
+                                       "input_tokens_details": {"cached_tokens": r.cached_prompt_tokens}}})
+
+    return H
+
+
+def build_state(model_paths: list[str], backend: str = "cuda", max_num_seqs: int = 64, kv_page_size: int = 16,
+                max_ctx: int = 4096, reasoning_budget: int = 0, mesh_coordination: str = "disabled") -> ServerState:
+    from ..receipts.manifests import artifact_digest
+    from .backend import CpuBackend, CudaBackend
+    if backend not in ("cpu", "cuda"):
+        raise ValueError("--backend accepts cpu or cuda")
+    if kv_page_size != 16:
+        raise ValueError("the paged KV cache uses 16-token pages")
+    models = []
+    for p in model_paths:
+        b = CpuBackend.from_gguf(p) if backend == "cpu" else CudaBackend.from_gguf(p, max_num_seqs=max_num_seqs, max_ctx=max_ctx)
+        mid = p.rsplit("/", 1)[-1].removesuffix(".gguf")
+        models.append(ServedModel(mid, b, artifact_digest(p), max_num_seqs=max_num_seqs))
+    return ServerState(models, reasoning_budget, mesh_coordination)
+
+
+def serve(state: ServerState, host: str = "127.0.0.1", port: int = 8080) -> ThreadingHTTPServer:
+    httpd = ThreadingHTTPServer((host, port), make_handler(state))
+    httpd.daemon_threads = True
+    return httpd
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="b200-serve")
+    ap.add_argument("-m", "--model", action="append", required=True)
+    ap.add_argument("--backend", default="cuda", choices=["cpu", "cuda"])
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8080)
+    ap.add_argument("--reasoning-budget", type=int, default=0)
+    ap.add_argument("--mesh-coordination", default="disabled", choices=["enabled", "disabled"])
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--ep", type=int, default=1)
+    ap.add_argument("--kv-page-size", type=int, default=16)
+    ap.add_argument("--max-num-seqs", type=int, default=64)
+    ap.add_argument("--max-ctx", type=int, default=4096)
+    a = ap.parse_args(argv)
+    state = build_state(a.model, a.backend, a.max_num_seqs, a.kv_page_size, a.max_ctx, a.reasoning_budget, a.mesh_coordination)
+    httpd = serve(state, a.host, a.port)
+    print(json.dumps({"event": "listening", "host": a.host, "port": a.port, "models": list(state.models),
+                      "execution_engine": ENGINE_NAME}), flush=True)
+    try:
+        httpd.serve_forever()
+    except KeyboardInterrupt:
+        pass
+
+
+if __name__ == "__main__":
+    main()

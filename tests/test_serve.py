@@ -1,0 +1,184 @@
+"""Model server on the CPU backend: real HTTP round trips against a tiny GGUF model, the serve wire
+contract with its parity gate, sessions and ``previous_response_id``, the scheduler, the node CLI
+and the receipts (CPU)."""
+import json
+import subprocess
+import threading
+import urllib.error
+import urllib.request
+
+import pytest
+import torch
+
+from openagents_b200.models.config import TINY_LLAMA
+from openagents_b200.models.weights import PLAN_Q8_0, random_weights, save_gguf
+from openagents_b200.receipts import manifests as mf
+from openagents_b200.serve.backend import CpuBackend
+from openagents_b200.serve.generation import ByteTokenizer, SamplingParams, Scheduler
+from openagents_b200.serve.server import ServedModel, ServerState, serve
+
+
+@pytest.fixture(scope="module")
+def gguf_path(tmp_path_factory):
+    cfg = TINY_LLAMA.with_(vocab=512, d_model=64, n_heads=2, n_kv_heads=1, head_dim=32, ffn=128)
+    p = str(tmp_path_factory.mktemp("m") / "tiny.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 0), PLAN_Q8_0)
+    return p
+
+
+@pytest.fixture(scope="module")
+def server(gguf_path):
+    model = ServedModel("tiny", CpuBackend.from_gguf(gguf_path), mf.artifact_digest(gguf_path), max_num_seqs=4)
+    state = ServerState([model])
+    httpd = serve(state, "127.0.0.1", 0)
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    yield f"http://127.0.0.1:{httpd.server_address[1]}", state
+    httpd.shutdown()
+
+
+def _get(url):
+    with urllib.request.urlopen(url, timeout=60) as r:
+        return r.status, r.read()
+
+
+def _post(url, obj):
+    req = urllib.request.Request(url, data=json.dumps(obj).encode(), headers={"Content-Type": "application/json"})
+    try:
+        with urllib.request.urlopen(req, timeout=120) as r:
+            return r.status, r.read()
+    except urllib.error.HTTPError as e:
+        return e.code, e.read()
+
+
+def test_health_models_status_metrics(server):
+    base, _ = server
+    code, body = _get(base + "/health")
+    h = json.loads(body)
+    assert code == 200 and h["execution_engine"] == "b200" and "/v1/chat/completions" in h["endpoints"]
+    m = json.loads(_get(base + "/v1/models")[1])["data"][0]
+    assert m["id"] == "tiny" and m["artifact_digest"].startswith("sha256:") and m["chat_template_digest"].startswith("sha256:")
+    st = json.loads(_get(base + "/psionic/management/status")[1])
+    assert st["models"][0]["backend"] == "cpu" and st["models"][0]["topology"]["stages"][0]["layerEnd"] == 2
+    assert b"b200_requests_total" in _get(base + "/metrics")[1]
+
+
+def test_chat_completion_and_stream_agree(server):
+    base, _ = server
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 12, "temperature": 0}
+    code, raw = _post(base + "/v1/chat/completions", body)
+    r = json.loads(raw)
+    assert code == 200 and r["choices"][0]["finish_reason"] in ("length", "stop")
+    assert r["usage"]["completion_tokens"] <= 12 and r["usage"]["total_tokens"] == r["usage"]["prompt_tokens"] + r["usage"]["completion_tokens"]
+    code, raw = _post(base + "/v1/chat/completions", {**body, "stream": True})
+    events = [l[6:] for l in raw.decode().split("\n") if l.startswith("data: ")]
+    assert events[-1] == "[DONE]"
+    text = "".join(json.loads(e)["choices"][0]["delta"].get("content", "") for e in events[:-1])
+    assert text == r["choices"][0]["message"]["content"]
+    assert _post(base + "/v1/chat/completions", {"model": "nope", "messages": [{"role": "user", "content": "x"}]})[0] == 404
+    assert _post(base + "/v1/chat/completions", {"messages": []})[0] == 400
+
+
+def test_serve_contract_parity_and_receipt(server):
+    base, _ = server
+    code, raw = _post(base + "/v1/serve", {"model": "tiny", "messages": [{"role": "user", "content": "abc"}],
+                                           "passthroughParams": {"max_tokens": 8}, "requireExactGreedyParity": True})
+    s = json.loads(raw)
+    assert code == 200 and s["parityMode"] == "exact_greedy_parity" and s["parityVerified"] is True
+    assert len(s["stages"]) == 1 and s["usage"]["totalTokens"] == s["usage"]["promptTokens"] + s["usage"]["completionTokens"]
+    rec = mf.serving_receipt(s)
+    assert rec["sharded"] is False and not mf.clears_paid_traffic(rec)        # no paid-traffic bundle: not cleared
+    rec["paidTrafficVerification"] = {"parityPassed": True, "canaryPassed": True, "replayPassed": True, "payoutEligible": True, "blockerRefs": []}
+    assert mf.clears_paid_traffic(rec)
+
+
+def test_responses_with_previous_response_id_reuses_the_sequence(server):
+    base, state = server
+    code, raw = _post(base + "/v1/responses", {"model": "tiny", "input": "first turn", "max_output_tokens": 6})
+    r1 = json.loads(raw)
+    assert code == 200 and r1["status"] == "completed"
+    code, raw = _post(base + "/v1/responses", {"model": "tiny", "input": "second", "previous_response_id": r1["id"], "max_output_tokens": 6})
+    r2 = json.loads(raw)
+    assert code == 200 and r2["previous_response_id"] == r1["id"]
+    sess = state.sessions[state.responses[r2["id"]][0]]
+    assert len(sess.responses) == 2
+    # the second turn ran only its own tokens: the cache already held the first turn
+    kv_tokens = state.default.backend.caches[sess.seq_id].length
+    assert kv_tokens == len(sess.tokens)
+    assert _post(base + "/v1/responses", {"input": "x", "previous_response_id": "resp-missing"})[0] == 404
+
+
+def test_continuous_batching_matches_sequential(gguf_path):
+    be = CpuBackend.from_gguf(gguf_path)
+    tok = ByteTokenizer(be.cfg.vocab)
+    prompts = [tok.encode(t) for t in ("alpha", "a much longer prompt than the others", "b")]
+    solo = []
+    for p in prompts:
+        s = Scheduler(be, tok, max_num_seqs=1)
+        r = s.submit(p, SamplingParams(max_tokens=6))
+        s.run_until_done([r])
+        solo.append(r.output)
+    s = Scheduler(be, tok, max_num_seqs=3, prefill_chunk=8)          # chunked prefill + batched decode
+    reqs = [s.submit(p, SamplingParams(max_tokens=6)) for p in prompts]
+    s.run_until_done(reqs)
+    assert [r.output for r in reqs] == solo
+    assert s.stats["steps"] > 0 and s.stats["batch_size_sum"] / s.stats["steps"] > 1.0
+    assert not be.caches                                              # finished sequences released their KV
+
+
+def test_node_cli_against_reference_fixture(tmp_path):
+    from openagents_b200 import _build
+    _build.build_node()
+    cli = str(_build.node_cli_path())
+    fx = "/root/reference/fixtures/cloud/psionic_worker_attachment_v1/mixed-readiness.json"
+    import os
+    if not os.path.exists(fx):
+        fx = str(tmp_path / "fx.json")
+        json.dump({"schema_version": "openagents.psionic_worker_attachment.v1", "updated_at_ms": 1, "workers": [
+            {"product_id": "psionic.managed.inference", "worker_id": "w.i", "worker_kind": "inference", "ready": True, "crashed": False,
+             "evidence_digest": "sha256:a", "detail": None},
+            {"product_id": "psionic.managed.training", "worker_id": "w.t", "worker_kind": "training", "ready": False, "crashed": True,
+             "evidence_digest": "sha256:b", "detail": None},
+            {"product_id": "psionic.managed.sandbox", "worker_id": "w.s", "worker_kind": "sandbox", "ready": False, "crashed": False,
+             "evidence_digest": "sha256:c", "detail": None}]}, open(fx, "w"))
+    d = str(tmp_path)
+    assert subprocess.run([cli, "psionic", "attach", "--file", fx, "--state-dir", d], capture_output=True).returncode == 0
+    st = json.loads(subprocess.run([cli, "status", "--json", "--state-dir", d], capture_output=True, text=True).stdout)
+    assert st["capabilities"]["inference_products"] == ["psionic.managed.inference"]
+    assert st["capabilities"]["training_products"] == [] and st["capabilities"]["sandbox_profiles"] == []   # crashed / not ready
+    r = subprocess.run([cli, "psionic", "receipt", "append", "--state-dir", d, "--assignment-id", "asg.1", "--product-id",
+                        "psionic.managed.inference", "--worker-id", "w.i", "--status", "succeeded", "--evidence-digest", "sha256:ev"],
+                       capture_output=True, text=True)
+    rec = json.loads(r.stdout)
+    assert r.returncode == 0 and rec["schema_version"] == "openagents.psionic_execution_receipt.v1" and rec["receipt_digest"].startswith("sha256:")
+    st = json.loads(subprocess.run([cli, "status", "--json", "--state-dir", d], capture_output=True, text=True).stdout)
+    assert st["psionic_execution_receipt_digests"] == [rec["receipt_digest"]]
+    # rejections: ready and crashed at once; sandbox receipt without a profile digest; bad digest
+    bad = json.load(open(fx))
+    bad["workers"][0]["crashed"] = True
+    json.dump(bad, open(tmp_path / "bad.json", "w"))
+    assert subprocess.run([cli, "psionic", "attach", "--file", str(tmp_path / "bad.json"), "--state-dir", d], capture_output=True).returncode == 3
+    assert subprocess.run([cli, "psionic", "receipt", "append", "--state-dir", d, "--assignment-id", "a", "--product-id", "sandbox.x",
+                           "--worker-id", "w", "--status", "succeeded", "--evidence-digest", "sha256:e"], capture_output=True).returncode == 3
+    assert subprocess.run([cli, "psionic", "receipt", "append", "--state-dir", d, "--assignment-id", "a", "--product-id", "p",
+                           "--worker-id", "w", "--status", "succeeded", "--evidence-digest", "md5:e"], capture_output=True).returncode == 3
+
+
+def test_manifests_and_payout_split(gguf_path):
+    mm = mf.model_artifact_manifest(gguf_path, "llama", "Q8_0", "sha256:" + "0" * 64)
+    assert mf.verify_manifest(mm) and mm["artifactDigest"] == mf.artifact_digest(gguf_path)
+    rm = mf.release_manifest("0.1.0", {"model": gguf_path}, [mm])
+    assert mf.verify_manifest(rm)
+    rm["version"] = "0.1.1"
+    assert not mf.verify_manifest(rm)
+    stages = [{"stageIndex": 0, "layerStart": 0, "layerEnd": 11, "gpuResident": True},
+              {"stageIndex": 1, "layerStart": 11, "layerEnd": 32, "gpuResident": True}]
+    rec = mf.sharded_run_receipt("sha256:m", 32, stages)
+    assert mf.structural_errors(rec) == []
+    split = mf.payout_split(rec, 1001)
+    assert sum(s["payoutSats"] for s in split) == 1001 and split[0]["payoutSats"] == 344 and split[1]["payoutSats"] == 657
+    gap = mf.sharded_run_receipt("sha256:m", 32, [stages[0], {**stages[1], "layerStart": 12}])
+    assert any("gap" in e for e in mf.structural_errors(gap))
+    whole = mf.sharded_run_receipt("sha256:m", 32, [{"stageIndex": 0, "layerStart": 0, "layerEnd": 32, "gpuResident": True}])
+    assert len(mf.structural_errors(whole)) >= 2
+    with pytest.raises(ValueError):
+        mf.payout_split(mf.sharded_run_receipt("sha256:m", 32, stages, "mismatch"), 10)
