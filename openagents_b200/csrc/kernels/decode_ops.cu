@@ -393,3 +393,49 @@ B200_API int b200_decode_advance(int* ids, const int* out_ids, int* pos, int* sl
                                            hist, step_counter, hist_cap);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------ allocation-free sampling
+// See no_alloc.h.  The scratch lives in this translation unit; host code may not use the array's
+// name as a pointer (on the host it is only a stand-in for the symbol), so the device address is
+// fetched once per device with cudaGetSymbolAddress and handed to the kernel as an argument.
+#include <cstdio>
+#include <mutex>
+
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[B200_SAMPLE_NOALLOC_MAX_ELEMS];
+
+static float* noalloc_scratch_for_current_device(cudaError_t* err) {
+  static std::mutex mu;
+  static float* ptr[64] = {nullptr};
+  int dev = 0;
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess) return nullptr;
+  if (dev < 0 || dev >= 64) {
+    *err = cudaErrorInvalidDevice;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptr[dev]) {
+    float* p = nullptr;
+    *err = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);   // device `dev` is current here
+    if (*err != cudaSuccess) return nullptr;
+    ptr[dev] = p;
+  }
+  return ptr[dev];
+}
+
+B200_API int b200_sample_topk_noalloc(const float* logits, int T, int V, float temperature, int top_k, float top_p,
+                                      const float* u, int* out_id, cudaStream_t stream) {
+  if (T < 1 || V < 1 || top_k < 1 || top_k > 64) return B200_NOALLOC_ERR_BAD_ARG;
+  if ((unsigned long long)T * (unsigned long long)V > (unsigned long long)B200_SAMPLE_NOALLOC_MAX_ELEMS) {
+    std::fprintf(stderr, "b200_sample_topk_noalloc: T*V = %llu exceeds the built-in scratch of %u floats\n",
+                 (unsigned long long)T * (unsigned long long)V, (unsigned)B200_SAMPLE_NOALLOC_MAX_ELEMS);
+    return B200_NOALLOC_ERR_TOO_LARGE;
+  }
+  cudaError_t err;
+  float* scratch = noalloc_scratch_for_current_device(&err);
+  if (!scratch) return (int)err;
+  sample_topk_kernel<<<T, 1024, 0, stream>>>(logits, V, temperature, top_k, top_p, u, out_id, scratch);
+  return (int)cudaGetLastError();
+}
