@@ -124,6 +124,8 @@ class QWeight:
     plane2: torch.Tensor | None
     src_type: GgmlType
     shadow: torch.Tensor | None = None   # bf16 [N][K] copy for the dense tensor-core path
+    tiled: torch.Tensor | None = None    # tile-major packed copy for the fused-dequant GEMM
+    tiled2: torch.Tensor | None = None
 
     @staticmethod
     def from_raw(r: RawTensor) -> "QWeight":
@@ -158,6 +160,41 @@ class QWeight:
             ops.dequant_bf16(self.wt, self.main, self.plane2, out, self.N, self.K)
             self.shadow = out
         return self.shadow
+
+    def ensure_tiled(self):
+        """Tile-major form for the fused-dequant GEMM: [N/128][K/256][128 rows][bytes], rows
+        zero-padded to a multiple of 128, with the per-sub-block scale arithmetic done once here:
+
+        * Q4_K: 160 bytes per row and superblock = 8 x (a, c) bf16 pairs + 128 quant bytes, where a
+          32-element sub-block dequantizes as ``a * (16 + q) + c`` (c = -16 a - min).
+        * Q6_K: 224 bytes = 16 bf16 scales (d * sc, one per 16 elements) + 128 nibble bytes + 64
+          bytes of high bit pairs; values are ``s * (q - 32)``.
+        """
+        if self.tiled is None:
+            nsb = self.K // 256
+            Np = (self.N + 127) // 128 * 128
+            if self.wt == ops.WT_Q4KR:
+                m = self.main.view(self.N * nsb, 144)
+                d = m[:, 0:2].contiguous().view(torch.float16).float()
+                dmin = m[:, 2:4].contiguous().view(torch.float16).float()
+                ls, lm = tc._unpack_scale_min(m[:, 4:16])
+                a_bf = (d * ls.float()).to(torch.bfloat16)
+                c_bf = (-16.0 * a_bf.float() - dmin * lm.float()).to(torch.bfloat16)
+                head = torch.stack((a_bf, c_bf), dim=-1).reshape(self.N * nsb, 16).view(torch.uint8)
+                rows = torch.cat((head, m[:, 16:]), dim=1)                      # [N*nsb, 160]
+            elif self.wt == ops.WT_Q6KR:
+                m = self.main.view(self.N * nsb, 208)
+                sc = m[:, 192:208].contiguous().view(torch.int8).float()
+                s_bf = (self.plane2.view(self.N * nsb, 1).float() * sc).to(torch.bfloat16)
+                rows = torch.cat((s_bf.view(torch.uint8), m[:, :192]), dim=1)   # [N*nsb, 224]
+            else:
+                raise ValueError("only Q4_K and Q6_K weights have a tile-major form")
+            raw = rows.shape[1]
+            rows = rows.view(self.N, nsb, raw)
+            if Np != self.N:
+                rows = torch.cat((rows, torch.zeros((Np - self.N, nsb, raw), dtype=rows.dtype, device=rows.device)))
+            self.tiled = rows.view(Np // 128, 128, nsb, raw).permute(0, 2, 1, 3).contiguous()
+        return self.tiled, None
 
     def dequant_into(self, out: torch.Tensor) -> torch.Tensor:
         if self.wt == ops.WT_BF16:

@@ -38,6 +38,7 @@ _SIGS = {
     "b200_dequant_bf16": [c_int, _P, _P, _P, c_size_t, c_int, _P],
     "b200_f32_to_bf16": [_P, _P, c_size_t, _P],
     "b200_transpose_bf16": [_P, _P, c_int, c_int, _P],
+    "b200_qgemm": [c_int, _P, _P, c_int, c_int, _P, c_int, c_int, _P, c_int, _P, c_int, c_int, _P, _P, _P],
     "b200_decode_advance": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, _P, c_int, _P],
 }
 
@@ -168,3 +169,15 @@ def decode_advance(ids, out_ids, pos, slot, seq_lens, page_table, page_size, B, 
     _check(lib().b200_decode_advance(_p(ids), _p(out_ids), _p(pos), _p(slot), _p(seq_lens), _p(page_table),
                                      page_table.shape[1], page_size, B, _p(hist), _p(step_counter), hist_cap, _st()),
            "decode_advance")
+
+
+QEPI_STORE, QEPI_ADD = 0, 1
+
+
+def qgemm(w, x_bf16, T, y, ldy, bias=None, epi=QEPI_STORE, split_k=0, status=None, dbg=None):
+    """y[T][N] (+)= x[T][K] @ dequant(W)[N][K]^T with the dequantization inside the tcgen05 pipeline.
+    ``w`` is a QWeight in Q4_K-R or Q6_K-R."""
+    wt = {WT_Q4KR: 0, WT_Q6KR: 1}[w.wt]
+    tiled, tiled2 = w.ensure_tiled()
+    _check(lib().b200_qgemm(wt, _p(tiled), _p(tiled2), w.N, w.K, _p(x_bf16), x_bf16.stride(0), T, _p(y), ldy, _p(bias),
+                            epi, split_k, _p(status), _p(dbg), _st()), "qgemm")

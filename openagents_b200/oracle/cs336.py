@@ -1,0 +1,382 @@
+"""CPU restatement of the reference's contributor workloads ("homework"): the only executable ML
+semantics in the reference tree, kept here as oracles and as the CPU side of the multi-rank tests.
+
+A1 real-gradient workload (apps/openagents.com/workers/api/src/cs336-a1-real-gradient-workload.ts):
+a tiny LM — embedding, RMSNorm, single-head causal softmax attention, residual, RMSNorm, SwiGLU,
+residual, RMSNorm, unembedding, cross-entropy — in float64 with a hand-derived backward pass
+(:417-596 forward, :602-784 backward), per-shard full-batch gradients (:816-866), synchronous
+data-parallel SGD averaging (:872-891), validation loss (:899-927) and SHA-256 state commitments
+(:801-809).  Parameter layout and run configuration follow :30-60 and :199-226 (2,244 parameters).
+"""
+from __future__ import annotations
+
+import hashlib
+import struct
+from dataclasses import dataclass
+
+import numpy as np
+
+RMS_EPS = 1e-5
+
+
+@dataclass(frozen=True)
+class A1Config:
+    d_ff: int = 24
+    d_model: int = 12
+    learning_rate: float = 1.5
+    sequence_length: int = 16
+    shard_count: int = 2
+    step_count: int = 6
+    structure_bias: float = 0.85
+    train_sequences_per_shard: int = 48
+    validation_sequence_count: int = 32
+    vocabulary_size: int = 32
+
+
+NAMES = ("emb", "g1", "wq", "wk", "wv", "wo", "g2", "w1", "w3", "w2", "g3", "wu")
+
+
+def parameter_layout(c: A1Config) -> dict:
+    d, h, v = c.d_model, c.d_ff, c.vocabulary_size
+    shapes = {"emb": (v, d), "g1": (d,), "wq": (d, d), "wk": (d, d), "wv": (d, d), "wo": (d, d), "g2": (d,),
+              "w1": (d, h), "w3": (d, h), "w2": (h, d), "g3": (d,), "wu": (d, v)}
+    out, off = {}, 0
+    for n in NAMES:
+        size = int(np.prod(shapes[n]))
+        out[n] = (off, shapes[n])
+        off += size
+    out["size"] = off
+    return out
+
+
+def unpack(c: A1Config, params: np.ndarray) -> dict:
+    lay = parameter_layout(c)
+    return {n: params[lay[n][0]: lay[n][0] + int(np.prod(lay[n][1]))].reshape(lay[n][1]) for n in NAMES}
+
+
+def _stream(seed: str, n: int) -> np.ndarray:
+    """Deterministic uniform [0,1) stream from a SHA-256 counter (the reference seeds its data and
+    parameters the same way: :151-173)."""
+    out, i = np.empty(n), 0
+    ctr = 0
+    while i < n:
+        h = hashlib.sha256(f"{seed}:{ctr}".encode()).digest()
+        for k in range(0, 32, 4):
+            if i < n:
+                out[i] = struct.unpack(">I", h[k:k + 4])[0] / 2 ** 32
+                i += 1
+        ctr += 1
+    return out
+
+
+def init_params(c: A1Config, seed: str = "cs336.a1.params") -> np.ndarray:
+    lay = parameter_layout(c)
+    p = np.zeros(lay["size"])
+    u = _stream(seed, lay["size"])
+    for n in NAMES:
+        off, shape = lay[n]
+        size = int(np.prod(shape))
+        if n in ("g1", "g2", "g3"):
+            p[off: off + size] = 1.0
+        else:
+            fan = shape[0] if n != "emb" else c.d_model
+            p[off: off + size] = (u[off: off + size] * 2 - 1) / np.sqrt(fan)
+    return p
+
+
+def make_sequences(c: A1Config, seed: str, count: int) -> np.ndarray:
+    """Token sequences with learnable structure: with probability ``structure_bias`` the next token
+    is (prev * 3 + 1) mod V, otherwise uniform."""
+    V, T = c.vocabulary_size, c.sequence_length + 1
+    u = _stream(seed, count * T * 2).reshape(count, T, 2)
+    seq = np.zeros((count, T), dtype=np.int64)
+    seq[:, 0] = (u[:, 0, 0] * V).astype(np.int64)
+    for t in range(1, T):
+        follow = u[:, t, 0] < c.structure_bias
+        seq[:, t] = np.where(follow, (seq[:, t - 1] * 3 + 1) % V, (u[:, t, 1] * V).astype(np.int64))
+    return seq
+
+
+def rmsnorm_fwd(x, g):
+    r = 1.0 / np.sqrt((x * x).mean(-1, keepdims=True) + RMS_EPS)
+    return x * r * g, r
+
+
+def rmsnorm_bwd(dy, x, g, r):
+    d = x.shape[-1]
+    dg = (dy * x * r).sum(0)
+    dxh = dy * g
+    dx = r * dxh - x * (r ** 3) * (dxh * x).sum(-1, keepdims=True) / d
+    return dx, dg
+
+
+def sequence_pass(c: A1Config, P: dict, seq: np.ndarray, need_grad: bool = True):
+    """Forward (and backward) over one sequence.  Returns (mean loss, grads dict or None)."""
+    d, T = c.d_model, c.sequence_length
+    tok, tgt = seq[:T], seq[1: T + 1]
+    x0 = P["emb"][tok]                                       # [T, d]
+    h1, r1 = rmsnorm_fwd(x0, P["g1"])
+    q, k, v = h1 @ P["wq"], h1 @ P["wk"], h1 @ P["wv"]
+    s = (q @ k.T) / np.sqrt(d)
+    mask = np.triu(np.ones((T, T), dtype=bool), 1)
+    s = np.where(mask, -np.inf, s)
+    s = s - s.max(-1, keepdims=True)
+    a = np.exp(s)
+    a = a / a.sum(-1, keepdims=True)
+    ctx = a @ v
+    x1 = x0 + ctx @ P["wo"]
+    h2, r2 = rmsnorm_fwd(x1, P["g2"])
+    gate, val = h2 @ P["w1"], h2 @ P["w3"]
+    sig = 1.0 / (1.0 + np.exp(-gate))
+    act = gate * sig * val
+    x2 = x1 + act @ P["w2"]
+    h3, r3 = rmsnorm_fwd(x2, P["g3"])
+    logits = h3 @ P["wu"]
+    z = logits - logits.max(-1, keepdims=True)
+    lse = np.log(np.exp(z).sum(-1, keepdims=True))
+    logp = z - lse
+    loss = -logp[np.arange(T), tgt].mean()
+    if not need_grad:
+        return loss, None
+    G = {}
+    dlogits = np.exp(logp)
+    dlogits[np.arange(T), tgt] -= 1.0
+    dlogits /= T
+    G["wu"] = h3.T @ dlogits
+    dh3 = dlogits @ P["wu"].T
+    dx2, G["g3"] = rmsnorm_bwd(dh3, x2, P["g3"], r3)
+    G["w2"] = act.T @ dx2
+    dact = dx2 @ P["w2"].T
+    dval = dact * gate * sig
+    dgate = dact * val * (sig + gate * sig * (1 - sig))
+    G["w1"], G["w3"] = h2.T @ dgate, h2.T @ dval
+    dh2 = dgate @ P["w1"].T + dval @ P["w3"].T
+    dx1_n, G["g2"] = rmsnorm_bwd(dh2, x1, P["g2"], r2)
+    dx1 = dx2 + dx1_n
+    G["wo"] = ctx.T @ dx1
+    dctx = dx1 @ P["wo"].T
+    da = dctx @ v.T
+    dv = a.T @ dctx
+    ds = a * (da - (da * a).sum(-1, keepdims=True)) / np.sqrt(d)
+    dq, dk = ds @ k, ds.T @ q
+    G["wq"], G["wk"], G["wv"] = h1.T @ dq, h1.T @ dk, h1.T @ dv
+    dh1 = dq @ P["wq"].T + dk @ P["wk"].T + dv @ P["wv"].T
+    dx0_n, G["g1"] = rmsnorm_bwd(dh1, x0, P["g1"], r1)
+    dx0 = dx1 + dx0_n
+    G["emb"] = np.zeros_like(P["emb"])
+    np.add.at(G["emb"], tok, dx0)
+    return loss, G
+
+
+def shard_gradient(c: A1Config, params: np.ndarray, shard_index: int) -> tuple[np.ndarray, float]:
+    """Full-batch mean gradient of one shard."""
+    P = unpack(c, params)
+    seqs = make_sequences(c, f"cs336.a1.train.shard{shard_index}", c.train_sequences_per_shard)
+    lay = parameter_layout(c)
+    g, total = np.zeros(lay["size"]), 0.0
+    for s in seqs:
+        loss, G = sequence_pass(c, P, s)
+        total += loss
+        for n in NAMES:
+            off = lay[n][0]
+            g[off: off + G[n].size] += G[n].reshape(-1)
+    return g / len(seqs), total / len(seqs)
+
+
+def apply_aggregated_sgd_step(c: A1Config, params: np.ndarray, shard_grads: list[np.ndarray]) -> np.ndarray:
+    return params - c.learning_rate * np.sum(shard_grads, axis=0) / len(shard_grads)
+
+
+def validation_loss(c: A1Config, params: np.ndarray) -> float:
+    P = unpack(c, params)
+    seqs = make_sequences(c, "cs336.a1.validation", c.validation_sequence_count)
+    return float(np.mean([sequence_pass(c, P, s, need_grad=False)[0] for s in seqs]))
+
+
+def state_digest(params: np.ndarray) -> str:
+    return hashlib.sha256(np.ascontiguousarray(params, dtype="<f8").tobytes()).hexdigest()
+
+
+def run_training(c: A1Config = A1Config()) -> dict:
+    """The in-process reference trajectory every multi-device run must match digest for digest."""
+    params = init_params(c)
+    steps = [{"step": 0, "validationLoss": validation_loss(c, params), "stateDigest": state_digest(params)}]
+    for step in range(1, c.step_count + 1):
+        grads = [shard_gradient(c, params, s)[0] for s in range(c.shard_count)]
+        params = apply_aggregated_sgd_step(c, params, grads)
+        steps.append({"step": step, "validationLoss": validation_loss(c, params), "stateDigest": state_digest(params),
+                      "gradientDigests": [state_digest(g) for g in grads]})
+    return {"parameterCount": int(params.size), "steps": steps, "finalParams": params}
+
+
+# ---------------------------------------------------------------- A1 homework: BPE + committed mod-p matmul
+# (cs336-a1-homework-workload.ts:20 modulus, :132-169 tokenizer shard, :209-221 product, :232-290 commitments)
+FIELD_MODULUS = 2 ** 31 - 1
+
+
+def bpe_train(data: bytes, n_merges: int = 24) -> dict:
+    """Byte-level BPE: repeatedly merge the most frequent adjacent pair (ties: lowest pair)."""
+    ids = list(data)
+    merges = []
+    for k in range(n_merges):
+        counts = {}
+        for a, b in zip(ids, ids[1:]):
+            counts[(a, b)] = counts.get((a, b), 0) + 1
+        if not counts:
+            break
+        best = max(counts.items(), key=lambda kv: (kv[1], -kv[0][0], -kv[0][1]))[0]
+        new_id = 256 + k
+        merges.append((best[0], best[1], new_id))
+        out, i = [], 0
+        while i < len(ids):
+            if i + 1 < len(ids) and (ids[i], ids[i + 1]) == best:
+                out.append(new_id)
+                i += 2
+            else:
+                out.append(ids[i])
+                i += 1
+        ids = out
+    digest = hashlib.sha256(json_bytes({"merges": merges, "tokenCount": len(ids)})).hexdigest()
+    return {"merges": merges, "tokenIds": ids, "digestHex": digest}
+
+
+def json_bytes(obj) -> bytes:
+    import json
+    return json.dumps(obj, sort_keys=True, separators=(",", ":")).encode()
+
+
+def seeded_matrix(seed: str, rows: int, cols: int, bound: int = FIELD_MODULUS) -> np.ndarray:
+    return (np.floor(_stream(seed, rows * cols) * bound)).astype(np.int64).reshape(rows, cols)
+
+
+def matrix_product_mod(a: np.ndarray, b: np.ndarray, p: int = FIELD_MODULUS) -> np.ndarray:
+    out = np.zeros((a.shape[0], b.shape[1]), dtype=np.int64)
+    for i in range(a.shape[0]):
+        for j in range(b.shape[1]):
+            out[i, j] = sum(int(x) * int(y) for x, y in zip(a[i], b[:, j])) % p
+    return out
+
+
+def merkle_root(leaves: list[str]) -> str:
+    level = [bytes.fromhex(h) for h in leaves]
+    if not level:
+        return hashlib.sha256(b"").hexdigest()
+    while len(level) > 1:
+        if len(level) % 2:
+            level.append(level[-1])
+        level = [hashlib.sha256(level[i] + level[i + 1]).digest() for i in range(0, len(level), 2)]
+    return level[0].hex()
+
+
+def training_step_matrix(tokenizer_digest: str, rows: int = 8, inner: int = 16, cols: int = 8) -> dict:
+    """One committed forward matmul: left matrix from the tokenizer digest, seeded right matrix, product
+    mod p, row digests, Merkle root, and a challenge vector derived after the commitment."""
+    left = seeded_matrix("left:" + tokenizer_digest, rows, inner)
+    right = seeded_matrix("right:weights", inner, cols)
+    prod = matrix_product_mod(left, right)
+    row_digests = [hashlib.sha256(json_bytes([int(v) for v in r])).hexdigest() for r in prod]
+    root = merkle_root(row_digests)
+    challenge = (np.floor(_stream("challenge:" + root, cols) * FIELD_MODULUS)).astype(np.int64)
+    return {"fieldModulus": FIELD_MODULUS, "leftMatrix": left.tolist(), "rightMatrix": right.tolist(),
+            "claimedProductMatrix": prod.tolist(), "rowDigests": row_digests, "merkleRoot": root,
+            "challengeVector": challenge.tolist(), "rowOpenings": [{"rowRef": f"row.{i}", "digest": d} for i, d in enumerate(row_digests)],
+            "merkleProofValid": True}
+
+
+# ---------------------------------------------------------------- A2 device micro-benchmarks
+# (cs336-a2-benchmark-workload.ts:35-44 shapes, :141-191 attention, :193-210 STREAM triad, :212-249 greedy
+# row decode, :251-292 one training step, :338-370 suite with an injectable clock, :497-509 agreement score)
+def mulberry32(seed: int):
+    state = seed & 0xFFFFFFFF
+
+    def nxt() -> float:
+        nonlocal state
+        state = (state + 0x6D2B79F5) & 0xFFFFFFFF
+        t = state
+        t = ((t ^ (t >> 15)) * (t | 1)) & 0xFFFFFFFF
+        t ^= (t + (((t ^ (t >> 7)) * (t | 61)) & 0xFFFFFFFF)) & 0xFFFFFFFF
+        return ((t ^ (t >> 14)) & 0xFFFFFFFF) / 4294967296.0
+    return nxt
+
+
+def _rand(seed: int, *shape) -> np.ndarray:
+    r = mulberry32(seed)
+    return np.array([r() * 2 - 1 for _ in range(int(np.prod(shape)))]).reshape(shape)
+
+
+def a2_attention(seq: int = 64, dim: int = 32, seed: int = 1) -> np.ndarray:
+    q, k, v = _rand(seed, seq, dim), _rand(seed + 1, seq, dim), _rand(seed + 2, seq, dim)
+    s = q @ k.T / np.sqrt(dim)
+    s = np.exp(s - s.max(-1, keepdims=True))
+    return (s / s.sum(-1, keepdims=True)) @ v
+
+
+def a2_stream_triad(n: int = 2_000_000, passes: int = 8, scalar: float = 3.0) -> float:
+    b, c = np.arange(n, dtype=np.float64) * 1e-6, np.ones(n)
+    a = np.zeros(n)
+    for _ in range(passes):
+        a = b + scalar * c
+        b, c = c, a
+    return float(a[::max(1, n // 1000)].sum())
+
+
+def a2_row_decode(vocab: int = 96, hidden: int = 48, steps: int = 48, seed: int = 7) -> list[int]:
+    W, state = _rand(seed, vocab, hidden), _rand(seed + 1, hidden)
+    out = []
+    for _ in range(steps):
+        tok = int(np.argmax(W @ state))
+        out.append(tok)
+        state = np.tanh(0.5 * state + 0.5 * W[tok])
+    return out
+
+
+def a2_training_step(rows: int = 32, inner: int = 64, cols: int = 32, lr: float = 0.01, seed: int = 11) -> tuple[np.ndarray, float]:
+    A, W, T = _rand(seed, rows, inner), _rand(seed + 1, inner, cols), _rand(seed + 2, rows, cols)
+    E = A @ W - T
+    return W - lr * (A.T @ E) / rows, float((E * E).mean())
+
+
+def nearest_rank(samples: list[float], q: float) -> float:
+    s = sorted(samples)
+    return s[max(0, min(len(s) - 1, int(np.ceil(q * len(s))) - 1))]
+
+
+def a2_suite(now, repetitions: int = 5) -> dict:
+    """Times the four kernels with the injected clock ``now()`` (seconds); p50/p90 by nearest rank."""
+    out = {}
+    for name, fn in (("attention", a2_attention), ("memory_bandwidth", lambda: a2_stream_triad(200_000, 2)),
+                     ("decode", a2_row_decode), ("training_step", a2_training_step)):
+        ts, digest = [], None
+        for _ in range(repetitions):
+            t0 = now()
+            r = fn()
+            ts.append(now() - t0)
+            digest = hashlib.sha256(repr(np.asarray(r[0] if isinstance(r, tuple) else r).round(9).tolist()).encode()).hexdigest()
+        out[name] = {"p50": nearest_rank(ts, 0.5), "p90": nearest_rank(ts, 0.9), "outputDigest": digest}
+    return out
+
+
+def cross_device_agreement(median_a: float, median_b: float) -> float:
+    lo, hi = min(median_a, median_b), max(median_a, median_b)
+    return 0.0 if hi <= 0 else lo / hi
+
+
+# ---------------------------------------------------------------- A3 IsoFLOP grid, A5 DPO
+# (cs336-a3-sweep-workload.ts:141 grid planner with D = C / (6 N); cs336-a5-dpo-preference-workload.ts:85-122)
+def plan_isoflop_grid(compute_budgets: list[float], param_counts: list[int]) -> list[dict]:
+    return [{"computeBudget": C, "paramCount": N, "tokenBudget": int(C // (6 * N))} for C in compute_budgets for N in param_counts
+            if C // (6 * N) >= 1]
+
+
+def softplus(x: float) -> float:
+    return float(np.log1p(np.exp(-abs(x))) + max(x, 0.0))
+
+
+def dpo_implicit_reward(beta: float, logp_policy: float, logp_ref: float) -> float:
+    return beta * (logp_policy - logp_ref)
+
+
+def dpo_pair_loss(beta: float, pol_chosen: float, pol_rejected: float, ref_chosen: float, ref_rejected: float) -> float:
+    """-log sigmoid(r_chosen - r_rejected) written with softplus."""
+    margin = dpo_implicit_reward(beta, pol_chosen, ref_chosen) - dpo_implicit_reward(beta, pol_rejected, ref_rejected)
+    return softplus(-margin)

@@ -145,6 +145,24 @@ def bench_gemm(rows):
     assert int(status.item()) == 0
 
 
+def bench_qgemm(rows):
+    hbm, tf, tag = peaks()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for name, N, K, t in (("qkv", 6144, 4096, GgmlType.Q4_K), ("o", 4096, 4096, GgmlType.Q4_K), ("gate_up", 28672, 4096, GgmlType.Q4_K),
+                          ("down", 4096, 14336, GgmlType.Q4_K), ("lm_head", 128256, 4096, GgmlType.Q6_K)):
+        w = _rand_q(N, K, t)
+        for T in (64, 2048):
+            if T == 2048 and name == "lm_head":
+                continue
+            x = torch.randn(T, K, device=DEV).bfloat16()
+            y = torch.zeros((T, N), device=DEV)
+            fn = lambda: ops.qgemm(w, x, T, y, N, epi=ops.QEPI_ADD, split_k=0, status=status)
+            s = timeit(fn, iters=10)
+            gbs, fl = w.nbytes() / s / 1e9, 2.0 * T * N * K / s / 1e12
+            rows.append(f"qgemm {name:8s} N={N:6d} K={K:5d} {t.name} T={T:4d}: {s*1e6:8.1f} us  {gbs:6.0f} GB/s ({gbs/hbm:4.2f} of {tag} HBM)  {fl:7.1f} TFLOP/s ({fl/tf:4.2f} of {tag} bf16)")
+    assert int(status.item()) == 0
+
+
 def main():
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
     rows = []
@@ -154,6 +172,8 @@ def main():
         bench_attn(rows)
     if which in ("gemm", "all"):
         bench_gemm(rows)
+    if which in ("qgemm", "all"):
+        bench_qgemm(rows)
     print("\n".join(rows))
 
 

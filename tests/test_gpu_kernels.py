@@ -403,3 +403,29 @@ def test_train_ops_match_torch():
     rte = torch.zeros(Vv, D, device=DEV).index_add_(0, ids.long(), de.float())
     rpe = torch.zeros(T, D, device=DEV).index_add_(0, pos, de.float())
     assert torch.allclose(gte, rte, atol=1e-3) and torch.allclose(gpe, rpe, atol=1e-3)
+
+
+@pytest.mark.parametrize("t", [GgmlType.Q4_K, GgmlType.Q6_K])
+@pytest.mark.parametrize("T,N,K,split", [(64, 384, 1024, 1), (40, 200, 512, 2), (130, 256, 768, 1), (300, 128, 2048, 4)])
+def test_qgemm_fused_dequant(t, T, N, K, split):
+    ops = _ops()
+    W = _randn(N, K, seed=40, scale=0.02)
+    w = _qweight(W, t)
+    Wd = tc.dequantize(tc.quantize(W, t), t, (N, K))
+    x = _randn(T, K, seed=41).bfloat16()
+    bias = _randn(N, seed=42)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ref = x.float() @ Wd.t() + bias
+    tol = 0.02 * ref.std().item()
+    if split == 1:
+        y = torch.full((T, N), 7.0, device=DEV)
+        ops.qgemm(w, x, T, y, N, bias=bias, epi=ops.QEPI_STORE, split_k=1, status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert (y - ref).abs().max().item() < 4 * tol, (y - ref).abs().max().item()
+    r = _randn(T, N, seed=43)
+    y = r.clone()
+    ops.qgemm(w, x, T, y, N, bias=bias, epi=ops.QEPI_ADD, split_k=split, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert (y - r - ref).abs().max().item() < 4 * tol, (y - r - ref).abs().max().item()
