@@ -69,28 +69,57 @@ B200_API int b200_embedding(const int* ids, float* out, int T, int D, int type, 
 // ------------------------------------------------------------------ RMSNorm (+ quantize)
 
 // x fp32 [T][D] -> any of: quantized activations (xq int8 x8-order, xd [T][D/32], xs16 [T][D/16]),
-// bf16 h [T][D], fp32 h [T][D].  One block per token; each warp owns 32-element blocks.
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ g, float eps, int D,
-                               int8_t* __restrict__ xq, float* __restrict__ xd, float* __restrict__ xs16,
-                               __nv_bfloat16* __restrict__ hb, float* __restrict__ hf) {
+// bf16 h [T][D], fp32 h [T][D].  One block per token; each warp owns 32-element blocks.  A decode
+// step runs this on the critical path with one token, so the row and the gain are read once with
+// all loads in flight together and kept in registers; only rows longer than kRmsRegs * 1024 fall
+// back to re-reading.
+constexpr int kRmsRegs = 8;
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ g, float eps,
+                                                       int D, int8_t* __restrict__ xq, float* __restrict__ xd,
+                                                       float* __restrict__ xs16, __nv_bfloat16* __restrict__ hb,
+                                                       float* __restrict__ hf) {
   __shared__ float red[32];
   const int t = blockIdx.x;
   const float* xr = x + (size_t)t * D;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int nblk = D / 32;
+  float v[kRmsRegs], gg[kRmsRegs];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) {
-    float v = xr[i];
-    ss += v * v;
+#pragma unroll
+  for (int k = 0; k < kRmsRegs; k++) {
+    const int blk = w + k * nw;
+    const bool in = blk < nblk;
+    v[k] = in ? xr[blk * 32 + lane] : 0.f;
+    gg[k] = (in && g) ? g[blk * 32 + lane] : 1.f;
+  }
+#pragma unroll
+  for (int k = 0; k < kRmsRegs; k++) ss += v[k] * v[k];
+  for (int blk = w + kRmsRegs * nw; blk < nblk; blk += nw) {
+    const float e = xr[blk * 32 + lane];
+    ss += e * e;
   }
   ss = block_sum(ss, red);
   const float rstd = rsqrtf(ss / (float)D + eps);
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int blk = w; blk < D / 32; blk += nw) {
+#pragma unroll
+  for (int k = 0; k < kRmsRegs; k++) {
+    const int blk = w + k * nw;
+    if (blk < nblk) {
+      const int i = blk * 32 + lane;
+      const float o = v[k] * rstd * gg[k];
+      if (hb) hb[(size_t)t * D + i] = __float2bfloat16(o);
+      if (hf) hf[(size_t)t * D + i] = o;
+      if (xq)
+        quantize_block32(o, lane, xq + (size_t)t * D + blk * 32, xd + (size_t)t * (D / 32) + blk,
+                         xs16 + (size_t)t * (D / 16) + blk * 2);
+    }
+  }
+  for (int blk = w + kRmsRegs * nw; blk < nblk; blk += nw) {
     const int i = blk * 32 + lane;
-    const float v = xr[i] * rstd * (g ? g[i] : 1.f);
-    if (hb) hb[(size_t)t * D + i] = __float2bfloat16(v);
-    if (hf) hf[(size_t)t * D + i] = v;
+    const float o = xr[i] * rstd * (g ? g[i] : 1.f);
+    if (hb) hb[(size_t)t * D + i] = __float2bfloat16(o);
+    if (hf) hf[(size_t)t * D + i] = o;
     if (xq)
-      quantize_block32(v, lane, xq + (size_t)t * D + blk * 32, xd + (size_t)t * (D / 32) + blk,
+      quantize_block32(o, lane, xq + (size_t)t * D + blk * 32, xd + (size_t)t * (D / 32) + blk,
                        xs16 + (size_t)t * (D / 16) + blk * 2);
   }
 }
@@ -98,7 +127,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 B200_API int b200_rmsnorm(const float* x, const float* g, float eps, int T, int D, void* xq, float* xd,
                           float* xs16, void* hb, float* hf, cudaStream_t st) {
   if (D % 32) return B200_ERR_BAD_ARG;
-  rmsnorm_kernel<<<T, 256, 0, st>>>(x, g, eps, D, (int8_t*)xq, xd, xs16, (__nv_bfloat16*)hb, hf);
+  const int threads = D >= 4096 ? 1024 : D >= 1024 ? 512 : 256;
+  rmsnorm_kernel<<<T, threads, 0, st>>>(x, g, eps, D, (int8_t*)xq, xd, xs16, (__nv_bfloat16*)hb, hf);
   return (int)cudaGetLastError();
 }
 
@@ -126,60 +156,95 @@ B200_API int b200_quantize_x(const float* x, int T, int D, void* xq, float* xd, 
 // Cache layout: [page][Hkv][page_size][hd] fp16, so one (page, head) is one contiguous tile.
 // q_out fp32 and/or q_out_h fp16 [T][Hq*hd] receive the rotated queries scaled by `q_scale`.
 // style 0: pairs (2i, 2i+1); style 1: halves (i, i + hd/2).
+// tab [tab_len][hd/2] holds (cos, sin) of pos * theta^(-2j/hd), computed once in double precision
+// by b200_rope_table; positions beyond the table (or a null table) are computed here in double,
+// because fast-math sine loses accuracy at angles of thousands of radians.
+// One thread per (head, pair) and per pair of V elements: a decode step has one token per
+// sequence, so the work is spread over grid.y instead of looping inside one block.
 __global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
                                const int* __restrict__ slot, float* __restrict__ q_out, __half* __restrict__ q_out_h,
                                __half* __restrict__ kc, __half* __restrict__ vc, int Hq, int Hkv, int hd,
-                               int page_size, float theta, int style, float q_scale) {
+                               int page_size, float theta, int style, float q_scale,
+                               const float2* __restrict__ tab, int tab_len) {
   const int t = blockIdx.x;
   const int row = (Hq + 2 * Hkv) * hd;
   const float* in = qkv + (size_t)t * row;
-  const float p = (float)pos[t];
-  const int s = slot[t];
-  const int page = s / page_size, off = s % page_size;
   const int half = hd >> 1;
-  // rotate q and k: one thread per (head, pair)
-  for (int i = threadIdx.x; i < (Hq + Hkv) * half; i += blockDim.x) {
-    const int h = i / half, j = i % half;
-    // Double precision on purpose: fast-math sine loses accuracy at angles of thousands of radians.
+  const int n_rot = (Hq + Hkv) * half, n_v = Hkv * half;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= n_rot + n_v) return;
+  const int s = slot[t];
+  const int page = s >= 0 ? s / page_size : 0, off = s >= 0 ? s % page_size : 0;
+  if (i >= n_rot) {
+    if (s < 0) return;
+    const int e = (i - n_rot) * 2, kh = e / hd, c = e % hd;
+    const float2 v = *(const float2*)(in + (Hq + Hkv) * hd + e);
+    *(__half2*)(vc + (((size_t)page * Hkv + kh) * page_size + off) * hd + c) = __floats2half2_rn(v.x, v.y);
+    return;
+  }
+  const int h = i / half, j = i % half;
+  const int p = pos[t];
+  float sn, cs;
+  if (tab && p >= 0 && p < tab_len) {
+    const float2 e = tab[(size_t)p * half + j];
+    cs = e.x;
+    sn = e.y;
+  } else {
     const double inv = exp2(-2.0 * (double)j / (double)hd * log2((double)theta));
     double snd, csd;
     sincos((double)p * inv, &snd, &csd);
-    const float sn = (float)snd, cs = (float)csd;
-    const int i0 = style == 0 ? 2 * j : j;
-    const int i1 = style == 0 ? 2 * j + 1 : j + half;
-    const float a = in[h * hd + i0], b = in[h * hd + i1];
-    const float r0 = a * cs - b * sn, r1 = a * sn + b * cs;
-    if (h < Hq) {
-      const size_t qi = (size_t)t * Hq * hd + h * hd;
-      if (q_out) {
-        q_out[qi + i0] = r0 * q_scale;
-        q_out[qi + i1] = r1 * q_scale;
-      }
-      if (q_out_h) {
-        q_out_h[qi + i0] = __float2half(r0 * q_scale);
-        q_out_h[qi + i1] = __float2half(r1 * q_scale);
-      }
-    } else if (s >= 0) {
-      const int kh = h - Hq;
-      __half* dst = kc + (((size_t)page * Hkv + kh) * page_size + off) * hd;
-      dst[i0] = __float2half(r0);
-      dst[i1] = __float2half(r1);
-    }
+    sn = (float)snd;
+    cs = (float)csd;
   }
-  if (s >= 0) {
-    const float* vin = in + (Hq + Hkv) * hd;
-    for (int i = threadIdx.x; i < Hkv * hd; i += blockDim.x) {
-      const int kh = i / hd, e = i % hd;
-      vc[(((size_t)page * Hkv + kh) * page_size + off) * hd + e] = __float2half(vin[i]);
+  const int i0 = style == 0 ? 2 * j : j;
+  const int i1 = style == 0 ? 2 * j + 1 : j + half;
+  const float a = in[h * hd + i0], b = in[h * hd + i1];
+  const float r0 = a * cs - b * sn, r1 = a * sn + b * cs;
+  if (h < Hq) {
+    const size_t qi = (size_t)t * Hq * hd + h * hd;
+    if (q_out) {
+      q_out[qi + i0] = r0 * q_scale;
+      q_out[qi + i1] = r1 * q_scale;
     }
+    if (q_out_h) {
+      q_out_h[qi + i0] = __float2half(r0 * q_scale);
+      q_out_h[qi + i1] = __float2half(r1 * q_scale);
+    }
+  } else if (s >= 0) {
+    const int kh = h - Hq;
+    __half* dst = kc + (((size_t)page * Hkv + kh) * page_size + off) * hd;
+    dst[i0] = __float2half(r0);
+    dst[i1] = __float2half(r1);
   }
+}
+
+__global__ void rope_table_kernel(float2* __restrict__ tab, int n_pos, int hd, float theta) {
+  const int half = hd >> 1;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pos * half) return;
+  const int p = i / half, j = i % half;
+  const double inv = exp2(-2.0 * (double)j / (double)hd * log2((double)theta));
+  double sn, cs;
+  sincos((double)p * inv, &sn, &cs);
+  tab[i] = make_float2((float)cs, (float)sn);
+}
+
+// (cos, sin) table [n_pos][hd/2] for b200_rope_kv; built once per engine.
+B200_API int b200_rope_table(void* tab, int n_pos, int hd, float theta, cudaStream_t st) {
+  if (hd % 2 || n_pos < 1) return B200_ERR_BAD_ARG;
+  const int n = n_pos * (hd / 2);
+  rope_table_kernel<<<(n + 255) / 256, 256, 0, st>>>((float2*)tab, n_pos, hd, theta);
+  return (int)cudaGetLastError();
 }
 
 B200_API int b200_rope_kv(const float* qkv, const int* pos, const int* slot, float* q_out, void* q_out_h, void* kc,
                           void* vc, int T, int Hq, int Hkv, int hd, int page_size, float theta,
-                          int style, float q_scale, cudaStream_t st) {
-  rope_kv_kernel<<<T, 256, 0, st>>>(qkv, pos, slot, q_out, (__half*)q_out_h, (__half*)kc, (__half*)vc, Hq, Hkv, hd,
-                                    page_size, theta, style, q_scale);
+                          int style, float q_scale, const void* tab, int tab_len, cudaStream_t st) {
+  if (hd % 2) return B200_ERR_BAD_ARG;
+  const int items = (Hq + 2 * Hkv) * (hd / 2);
+  rope_kv_kernel<<<dim3(T, (items + 255) / 256), 256, 0, st>>>(qkv, pos, slot, q_out, (__half*)q_out_h, (__half*)kc,
+                                                               (__half*)vc, Hq, Hkv, hd, page_size, theta, style,
+                                                               q_scale, (const float2*)tab, tab_len);
   return (int)cudaGetLastError();
 }
 
@@ -215,58 +280,61 @@ B200_API int b200_add_inplace(float* x, const float* y, size_t n, cudaStream_t s
 // Greedy arg-max over logits [T][V] with the lowest index winning ties (matches torch.argmax on
 // the first maximal element).  Optional vocab_offset for a tensor-parallel shard; writes the max
 // value too so shards can be merged.
-__global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out_id,
-                              float* __restrict__ out_val, int vocab_offset) {
-  __shared__ float sv[32];
-  __shared__ int si[32];
+// A row is split over gridDim.y blocks.  Each block folds its part into a 64-bit key
+// (order-preserving float bits, then ~index so that ties go to the lowest index) with atomicMax on
+// keys[t]; the block that arrives last (tickets[t]) decodes the key, writes the result and zeroes
+// both words again, so the scratch needs zeroing only once, when it is allocated.
+__device__ __forceinline__ unsigned long long argmax_key(float v, int i) {
+  uint32_t u = __float_as_uint(v);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i);
+}
+__global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out_id,
+                                                     float* __restrict__ out_val, int vocab_offset,
+                                                     unsigned long long* __restrict__ keys, int* __restrict__ tickets) {
+  __shared__ unsigned long long sk[8];
   const int t = blockIdx.x;
   const float* l = logits + (size_t)t * V;
-  float best = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float v = l[i];
-    if (v > best) {
-      best = v;
-      bi = i;
-    }
+  const int per = (V + gridDim.y - 1) / gridDim.y;
+  const int lo = blockIdx.y * per, hi = min(V, lo + per);
+  unsigned long long best = 0;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const unsigned long long k = argmax_key(l[i], i);
+    best = k > best ? k : best;
   }
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) {
-      best = ov;
-      bi = oi;
-    }
+    const unsigned long long ok = __shfl_xor_sync(0xffffffffu, best, o);
+    best = ok > best ? ok : best;
   }
-  if (lane == 0) {
-    sv[w] = best;
-    si[w] = bi;
-  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) sk[w] = best;
   __syncthreads();
-  if (w == 0) {
-    const int nw = blockDim.x >> 5;
-    best = lane < nw ? sv[lane] : -INFINITY;
-    bi = lane < nw ? si[lane] : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) {
-        best = ov;
-        bi = oi;
-      }
+  if (threadIdx.x == 0) {
+    for (int k = 1; k < (int)(blockDim.x >> 5); k++) best = sk[k] > best ? sk[k] : best;
+    if (gridDim.y > 1) {
+      atomicMax(&keys[t], best);
+      __threadfence();
+      if (atomicAdd(&tickets[t], 1) != (int)gridDim.y - 1) return;
+      __threadfence();
+      best = atomicExch(&keys[t], 0ull);
+      tickets[t] = 0;
     }
-    if (lane == 0) {
-      out_id[t] = bi + vocab_offset;
-      if (out_val) out_val[t] = best;
-    }
+    uint32_t u = (uint32_t)(best >> 32);
+    u = (u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u;
+    out_id[t] = (int)(0xFFFFFFFFu - (uint32_t)best) + vocab_offset;
+    if (out_val) out_val[t] = __uint_as_float(u);
   }
 }
+// scratch: T * 16 bytes, zeroed once by the caller (T 64-bit keys, then T tickets, then padding);
+// null runs one block per row.
 B200_API int b200_argmax(const float* logits, int T, int V, int* out_id, float* out_val,
-                         int vocab_offset, cudaStream_t st) {
-  argmax_kernel<<<T, 1024, 0, st>>>(logits, V, out_id, out_val, vocab_offset);
+                         int vocab_offset, void* scratch, cudaStream_t st) {
+  int chunks = 1;
+  if (scratch) chunks = max(1, min(64, V / 2048));
+  unsigned long long* keys = (unsigned long long*)scratch;
+  int* tickets = scratch ? (int*)(keys + T) : nullptr;
+  argmax_kernel<<<dim3(T, chunks), 256, 0, st>>>(logits, V, out_id, out_val, vocab_offset, keys, tickets);
   return (int)cudaGetLastError();
 }
 

@@ -61,6 +61,9 @@ struct GemmEpi {
   int ldc;
   int act;
   int accumulate;            // out_f32 += value
+  // Split-K (small M): each split adds its partial product into out_f32 with a vector `red`, so
+  // out_f32 must already hold the residual (or zeros); bias comes from split 0 only.
+  int splitk_red;
   // Fused collective epilogue (tensor-parallel row-parallel GEMMs): instead of storing, add the tile
   // into an fp32 tensor [*, ldc] at byte offset sym_off of the symmetric heap.
   //   SYM_ALLREDUCE : into every rank's replica (multimem.red through the switch where available)
@@ -75,15 +78,29 @@ enum { SYM_NONE = 0, SYM_ALLREDUCE = 1, SYM_RSCATTER = 2 };
 
 constexpr int BM = 128, BK = 64;
 
-__device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, int M, int N, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, int M, int N, const uint32_t (&r)[32],
+                                             bool first_split) {
   if (m >= M) return;
   const size_t base = (size_t)m * e.ldc + n0;
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
   const bool full = n0 + 32 <= N;
+  if (e.splitk_red && e.sym_mode == SYM_NONE) {
+    const bool add_bias = e.bias && first_split;
+    for (int j = 0; j < 32 && n0 + j < N; j += 4) {
+      float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      if (add_bias) {
+        const float4 b = *(const float4*)(e.bias + n0 + j);
+        o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+      }
+      asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(e.out_f32 + base + j), "f"(o.x),
+                   "f"(o.y), "f"(o.z), "f"(o.w) : "memory");
+    }
+    return;
+  }
   if (e.sym_mode != SYM_NONE) {
-    const bool add_bias = e.bias && e.sym.rank == 0;
+    const bool add_bias = e.bias && e.sym.rank == 0 && first_split;
     const int owner = e.sym_mode == SYM_RSCATTER ? m / e.rows_per_rank : 0;
     const int lrow = e.sym_mode == SYM_RSCATTER ? m % e.rows_per_rank : m;
     const size_t off = e.sym_off + ((size_t)lrow * e.ldc + n0) * 4;
@@ -179,7 +196,7 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, in
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
                                                          const __grid_constant__ CUtensorMap tmB,
-                                                         const GemmEpi epi, int M, int N, int K,
+                                                         const GemmEpi epi, int M, int N, int K, int splits,
                                                          int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -197,7 +214,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = (K + BK - 1) / BK;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  const int n_tiles = tiles_m * tiles_n;
+  const int n_tiles = tiles_m * tiles_n * splits;   // work items: (output tile, K split), split fastest
+  const int kps = (KB + splits - 1) / splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -226,9 +244,11 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < n_tiles && ok; item += gridDim.x) {
+        const int tile = item / splits, sp = item - tile * splits;
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-        for (int kb = 0; kb < KB; kb++, it++) {
+        const int kb0 = sp * kps, kb1 = min(KB, kb0 + kps);
+        for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(smem_u32(empty + s), ph ^ 1, abort_flag)) { ok = false; break; }
@@ -243,12 +263,14 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       constexpr uint32_t idesc = idesc_bf16(BM, BN);
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, tcount++) {
+      for (int item = blockIdx.x; item < n_tiles && ok; item += gridDim.x, tcount++) {
+        const int sp = item % splits;
+        const int kb0 = sp * kps, kb1 = min(KB, kb0 + kps);
         const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
         if (!mbar_wait(smem_u32(tempty + acc), aph ^ 1, abort_flag)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < KB; kb++, it++) {
+        for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(smem_u32(full + s), ph, abort_flag)) { ok = false; break; }
@@ -257,7 +279,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
           const uint64_t bd = smem_desc_sw128(smem_u32(sB + s * B_BYTES));
 #pragma unroll
           for (int k = 0; k < BK / 16; k++)
-            umma_bf16(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           umma_commit(smem_u32(empty + s));
         }
         umma_commit(smem_u32(tfull + acc));   // released even after a failed wait; the flag says why
@@ -266,7 +288,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   } else {
     const int q = warp & 3;
     uint32_t tcount = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, tcount++) {
+    for (int item = blockIdx.x; item < n_tiles; item += gridDim.x, tcount++) {
+      const int tile = item / splits, sp = item - tile * splits;
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
       bool ok = mbar_wait(smem_u32(tfull + acc), aph, abort_flag);
@@ -279,7 +302,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + (uint32_t)(c * 32), r);
         tmem_ld_wait();
-        if (n0 + c * 32 < N) epilogue_row(epi, m, n0 + c * 32, M, N, r);
+        if (n0 + c * 32 < N) epilogue_row(epi, m, n0 + c * 32, M, N, r, sp == 0);
       }
       tc_fence_before();
       __syncwarp();
@@ -306,7 +329,7 @@ static int sm_count() {
 
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpi& e, int M, int N, int K,
-                       int* status, cudaStream_t st) {
+                       int splits, int* status, cudaStream_t st) {
   constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16;
   auto kern = gemm_bf16_kernel<BN, STAGES>;
   static bool configured = false;
@@ -315,9 +338,9 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmE
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
-  const int n_tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+  const int n_tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM) * splits;
   const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
-  kern<<<grid, 192, smem, st>>>(ta, tb, e, M, N, K, status);
+  kern<<<grid, 192, smem, st>>>(ta, tb, e, M, N, K, splits, status);
   return (int)cudaGetLastError();
 }
 
@@ -326,15 +349,18 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmE
 // `status` is a device int the kernel sets non-zero if one of its waits ran out.
 B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, int lda, int ldb, float* out_f32,
                             void* out_bf16, int ldc, const float* bias, const float* resid_f32,
-                            const void* resid_bf16, int act, int accumulate, int tile_n, int* status,
+                            const void* resid_bf16, int act, int accumulate, int tile_n, int split_k, int* status,
                             int sym_mode, const SymTable* sym, size_t sym_off, int rows_per_rank,
                             cudaStream_t st) {
   if (M <= 0 || N <= 0 || K <= 0 || (lda % 8) || (ldb % 8) || (K % 8)) return B200_ERR_BAD_ARG;
   if ((out_bf16 && (ldc % 8)) || (out_f32 && (ldc % 4))) return B200_ERR_BAD_ARG;
   if (N % 4) return B200_ERR_BAD_ARG;
+  const long tiles_m = (M + 127) / 128;
   if (tile_n == 0) {
-    const long tiles256 = (long)((N + 255) / 256) * ((M + 127) / 128);
-    tile_n = (N >= 256 && tiles256 >= 148) ? 256 : (N >= 128 && (long)((N + 127) / 128) * ((M + 127) / 128) >= 148) ? 128 : (N > 64 ? 128 : 64);
+    const long tiles256 = (long)((N + 255) / 256) * tiles_m, tiles128 = (long)((N + 127) / 128) * tiles_m;
+    tile_n = (N >= 256 && tiles256 >= 148) ? 256 : (N >= 128 && tiles128 >= 148) ? 128 : (N > 64 ? 128 : 64);
+    // Few tiles (decode batches): narrower tiles put more SMs on the weight stream.
+    if (tile_n == 128 && tiles128 <= 74) tile_n = 64;
   }
   CUtensorMap ta, tb;
   int rc = make_tmap_2d(&ta, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK, true);
@@ -345,6 +371,25 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   e.out_f32 = out_f32; e.out_bf16 = (__nv_bfloat16*)out_bf16; e.bias = bias; e.resid_f32 = resid_f32;
   e.resid_bf16 = (const __nv_bfloat16*)resid_bf16; e.ldc = ldc; e.act = act; e.accumulate = accumulate;
   e.sym_mode = sym_mode; e.rows_per_rank = rows_per_rank > 0 ? rows_per_rank : 1; e.sym_off = sym_off;
+  // Split K when the output tiles alone would leave most SMs idle and the epilogue is (or can be
+  // turned into) a pure accumulation: the fused collectives already add into their destination, and
+  // an in-place fp32 residual add (resid_f32 == out_f32) is the same thing as adding into out_f32.
+  const bool red_ok = sym_mode != SYM_NONE ||
+                      (out_f32 && !out_bf16 && !resid_bf16 && act == 0 &&
+                       ((accumulate && !resid_f32) || (!accumulate && resid_f32 == out_f32)));
+  const long n_out_tiles = (long)((N + tile_n - 1) / tile_n) * tiles_m;
+  const int KBt = (K + BK - 1) / BK;
+  int splits = 1;
+  if (split_k > 0) splits = split_k;
+  else if (red_ok && n_out_tiles <= 74) splits = (int)(148 / n_out_tiles);
+  if (splits > 1) {
+    if (!red_ok) return B200_ERR_BAD_ARG;
+    if (splits > 16) splits = 16;
+    while (splits > 1 && KBt / splits < 8) splits--;           // keep at least 8 K blocks per split
+    const int kps = (KBt + splits - 1) / splits;
+    splits = (KBt + kps - 1) / kps;                            // no empty split
+  }
+  e.splitk_red = (splits > 1 && sym_mode == SYM_NONE) ? 1 : 0;
   if (sym_mode != SYM_NONE) {
     if (!sym || (ldc % 4) || (sym_off % 16)) return B200_ERR_BAD_ARG;
     e.sym = *sym;
@@ -352,9 +397,9 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
     e.sym = SymTable{};
   }
   switch (tile_n) {
-    case 256: return launch_gemm<256, 4>(ta, tb, e, M, N, K, status, st);
-    case 128: return launch_gemm<128, 6>(ta, tb, e, M, N, K, status, st);
-    case 64: return launch_gemm<64, 8>(ta, tb, e, M, N, K, status, st);
+    case 256: return launch_gemm<256, 4>(ta, tb, e, M, N, K, splits, status, st);
+    case 128: return launch_gemm<128, 6>(ta, tb, e, M, N, K, splits, status, st);
+    case 64: return launch_gemm<64, 8>(ta, tb, e, M, N, K, splits, status, st);
   }
   return B200_ERR_BAD_ARG;
 }

@@ -402,7 +402,7 @@ B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, in
     a.sym = SymTable{};
     a.sym_off = 0;
   }
-  const bool dual = epi >= EPI_SWIGLU_Q8;
+  const bool dual = epi == EPI_SWIGLU_Q8 || epi == EPI_SWIGLU_F32;
   const int B = nb <= 1 ? 1 : nb <= 2 ? 2 : nb <= 4 ? 4 : 8;
   if (dual) {
     switch (B) {

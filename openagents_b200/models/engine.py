@@ -245,6 +245,8 @@ class LlamaEngine:
         self.max_splits = 64
         self.attn_scratch = torch.empty(ops.attn_decode_scratch_floats(self.max_batch, self.Hq, self.Hkv, self.hd, self.max_splits), **f32)
         self.attn_counters = torch.zeros(self.max_batch * self.Hkv, dtype=torch.int32, device=dev)
+        self.argmax_scratch = ops.argmax_scratch(self.max_batch, dev)
+        self.rope_tab = ops.rope_table(self.max_pages * PAGE, self.hd, self.cfg.rope_theta, dev)
         wmax = max(max(l.wqkv.N * l.wqkv.K, l.wgu.N * l.wgu.K, l.wo.N * l.wo.K, l.wdown.N * l.wdown.K) for l in self.layers)
         self._wscratch_elems = wmax
         self._wscratch = None
@@ -288,7 +290,7 @@ class LlamaEngine:
             ops.matvec(L.wqkv.wt, L.wqkv.main, L.wqkv.plane2, L.wqkv.N, L.wqkv.K, nb, xq=self.xq, xd=self.xd,
                        xs16=self.xs, xf=self.xf, epi=ops.EPI_STORE, bias=L.bqkv, y=self.qkv, ldy=self.qkv_dim)
             ops.rope_kv(self.qkv[:nb], self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv,
-                        self.hd, PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd))
+                        self.hd, PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd), table=self.rope_tab)
             oq8 = L.wo.quantized
             ops.attn_decode(self.q32, self.kc[li], self.vc[li], self.page_table, self.seq_lens, nb, self.Hq, self.Hkv,
                             self.hd, window=L.window, S=S, sinks=L.sinks, out_f32=None if oq8 else self.xf,
@@ -340,13 +342,13 @@ class LlamaEngine:
             self._gemm(hb_d, L.wqkv, T, out_f32=qkv, bias=L.bqkv)
             if decode:
                 ops.rope_kv(qkv, self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv, self.hd,
-                            PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd))
+                            PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd), table=self.rope_tab)
                 ops.attn_decode(self.q32, self.kc[li], self.vc[li], self.page_table, self.seq_lens, n_seqs, self.Hq,
                                 self.Hkv, self.hd, window=L.window, S=S, sinks=L.sinks, out_bf16=hb_q,
                                 scratch=self.attn_scratch, counters=self.attn_counters, status=self.status)
             else:
                 ops.rope_kv(qkv, self.pos, self.slot, None, self.q16, self.kc[li], self.vc[li], self.Hq, self.Hkv, self.hd,
-                            PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd))
+                            PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd), table=self.rope_tab)
                 ops.attn_prefill(self.q16, self.kc[li], self.vc[li], self.page_table, self.max_pages, self.q_start,
                                  self.q_len, self.seq_lens, n_seqs, max_q, self.Hq, self.Hkv, self.hd, window=L.window,
                                  sinks=L.sinks, out_bf16=hb_q)
@@ -381,7 +383,7 @@ class LlamaEngine:
             self._gemm(hb, self.wout, nb, out_f32=self.logits)
         if greedy:
             ops.argmax(self.logits[:nb], self.out_ids, self.out_val,
-                       vocab_offset=self.rank * self.V_local if self.vocab_sharded else 0)
+                       vocab_offset=self.rank * self.V_local if self.vocab_sharded else 0, scratch=self.argmax_scratch)
             n += 1
             if self.vocab_sharded:
                 self.comm.argmax_merge(self.out_ids, self.out_val, nb)

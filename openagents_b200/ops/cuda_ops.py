@@ -23,18 +23,19 @@ _SIGS = {
     "b200_embedding": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, c_int, _P],
     "b200_rmsnorm": [_P, _P, c_float, c_int, c_int, _P, _P, _P, _P, _P, _P],
     "b200_quantize_x": [_P, c_int, c_int, _P, _P, _P, _P],
-    "b200_rope_kv": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, _P],
+    "b200_rope_kv": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, _P, c_int, _P],
+    "b200_rope_table": [_P, c_int, c_int, c_float, _P],
     "b200_swiglu": [_P, c_int, c_int, _P, _P, _P],
     "b200_add_inplace": [_P, _P, c_size_t, _P],
-    "b200_argmax": [_P, c_int, c_int, _P, _P, c_int, _P],
+    "b200_argmax": [_P, c_int, c_int, _P, _P, c_int, _P, _P],
     "b200_sample_topk": [_P, c_int, c_int, c_float, c_int, c_float, _P, _P, _P, _P],
     "b200_matvec": [c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, _P, _P,
                     c_size_t, _P],
     "b200_attn_decode": [_P, _P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                          _P, _P, _P, _P, _P],
     "b200_attn_prefill": [_P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
-    "b200_gemm_bf16": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, _P,
-                       c_int, _P, c_size_t, c_int, _P],
+    "b200_gemm_bf16": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int,
+                       _P, c_int, _P, c_size_t, c_int, _P],
     "b200_dequant_bf16": [c_int, _P, _P, _P, c_size_t, c_int, _P],
     "b200_f32_to_bf16": [_P, _P, c_size_t, _P],
     "b200_transpose_bf16": [_P, _P, c_int, c_int, _P],
@@ -93,10 +94,19 @@ def quantize_x(x, xq, xd, xs16):
     _check(lib().b200_quantize_x(_p(x), T, D, _p(xq), _p(xd), _p(xs16), _st()), "quantize_x")
 
 
-def rope_kv(qkv, pos, slot, q_out, q_out_h, kc, vc, Hq, Hkv, hd, page_size, theta, style, q_scale):
+def rope_kv(qkv, pos, slot, q_out, q_out_h, kc, vc, Hq, Hkv, hd, page_size, theta, style, q_scale, table=None):
+    """``table``: optional (cos, sin) table from :func:`rope_table`; without it the angles are computed per call."""
     T = qkv.shape[0]
     _check(lib().b200_rope_kv(_p(qkv), _p(pos), _p(slot), _p(q_out), _p(q_out_h), _p(kc), _p(vc), T, Hq, Hkv, hd,
-                              page_size, theta, style, q_scale, _st()), "rope_kv")
+                              page_size, theta, style, q_scale, _p(table), 0 if table is None else table.shape[0], _st()),
+           "rope_kv")
+
+
+def rope_table(n_pos, hd, theta, device):
+    """fp32 [n_pos][hd/2][2] table of (cos, sin), computed in double precision on the device."""
+    tab = torch.empty((n_pos, hd // 2, 2), dtype=torch.float32, device=device)
+    _check(lib().b200_rope_table(_p(tab), n_pos, hd, theta, _st()), "rope_table")
+    return tab
 
 
 def swiglu(gu, F, ob=None, of=None):
@@ -108,9 +118,14 @@ def add_inplace(x, y):
     _check(lib().b200_add_inplace(_p(x), _p(y), x.numel(), _st()), "add_inplace")
 
 
-def argmax(logits, out_id, out_val=None, vocab_offset=0):
+def argmax(logits, out_id, out_val=None, vocab_offset=0, scratch=None):
     T, V = logits.shape
-    _check(lib().b200_argmax(_p(logits), T, V, _p(out_id), _p(out_val), vocab_offset, _st()), "argmax")
+    _check(lib().b200_argmax(_p(logits), T, V, _p(out_id), _p(out_val), vocab_offset, _p(scratch), _st()), "argmax")
+
+
+def argmax_scratch(T, device):
+    """Zeroed scratch that lets :func:`argmax` split each row over many blocks."""
+    return torch.zeros(T * 4, dtype=torch.int32, device=device)
 
 
 def sample_topk(logits, temperature, top_k, top_p, u, out_id, scratch):
@@ -145,10 +160,10 @@ def attn_prefill(q, kc, vc, page_table, max_pages, q_start, q_len, ctx_len, n_se
 
 def gemm_bf16(A, B, M, N, K, lda=None, ldb=None, out_f32=None, out_bf16=None, ldc=None, bias=None, resid_f32=None,
               resid_bf16=None, act=ACT_NONE, accumulate=False, tile_n=0, status=None, sym_mode=SYM_NONE, sym=None,
-              sym_off=0, rows_per_rank=0):
+              sym_off=0, rows_per_rank=0, split_k=0):
     """D[M][N] = A[M][K] @ B[N][K]^T with fused epilogue (see ``gemm_tc05.cu``)."""
     _check(lib().b200_gemm_bf16(_p(A), _p(B), M, N, K, lda or K, ldb or K, _p(out_f32), _p(out_bf16), ldc or N,
-                                _p(bias), _p(resid_f32), _p(resid_bf16), act, int(accumulate), tile_n, _p(status),
+                                _p(bias), _p(resid_f32), _p(resid_bf16), act, int(accumulate), tile_n, split_k, _p(status),
                                 sym_mode, _sym(sym), sym_off, rows_per_rank, _st()), "gemm_bf16")
 
 

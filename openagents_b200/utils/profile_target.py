@@ -4,7 +4,9 @@
 
 Each case sets up one kernel on a problem that is larger than L2 but holds well under a gigabyte on
 the device, launches it a few times and exits, so a capture with ``ncu -k regex:<kernel> -c 1`` ends
-by itself in seconds.  Cases: qgemm64, qgemm_lm, gemm, matvec, attn_decode, attn_prefill.
+by itself in seconds.  Cases: qgemm64, qgemm_lm, gemm, matvec, attn_decode, attn_prefill, and
+``step64`` / ``step1``: whole decode steps (batch 64 / 1, context 2048) of a 4-layer Llama-3-8B-shape
+engine without graphs, for a per-kernel launch list.
 """
 from __future__ import annotations
 
@@ -64,11 +66,30 @@ def main():
         out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=DEV)
         z, tl = torch.zeros(1, dtype=torch.int32, device=DEV), torch.full((1,), T, dtype=torch.int32, device=DEV)
         fn = lambda: ops.attn_prefill(q, kc, vc, table, pages, z, tl, tl, 1, T, Hq, Hkv, hd, out_bf16=out)
+    elif case in ("step64", "step1"):
+        from ..models.config import LLAMA3_8B
+        from ..models.engine import LlamaEngine
+        from ..models.qweight import RandomSource
+        from ..models.weights import PLAN_Q4_K
+        B, ctx = (64, 2048) if case == "step64" else (1, 2048)
+        cfg = LLAMA3_8B.with_(n_layers=4)
+        eng = LlamaEngine(cfg, RandomSource(cfg, PLAN_Q4_K, 0, DEV), device=DEV, max_batch=B, max_ctx=ctx + 64, max_tokens=2048)
+        g = torch.Generator().manual_seed(1)
+        for b in range(B):
+            eng.begin(b)
+            eng.forward_tokens([b], [torch.randint(0, cfg.vocab, (ctx,), generator=g).tolist()])
+        ids = list(range(B))
+        status = eng.status
+        fn = lambda: eng.decode(ids, [5] * B, use_graph=False)
     else:
         raise SystemExit(f"unknown case {case}")
+    fn()                                  # warm-up outside the profiled range
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()           # honoured by `ncu --profile-from-start off`
     for _ in range(n):
         fn()
     torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     assert int(status.item()) == 0
     print("ok", case)
 

@@ -166,6 +166,42 @@ def test_rope_kv_write(style):
         assert torch.allclose(vc[s // 16, :, s % 16].cpu().float(), v.view(T, Hkv, hd)[i], atol=4e-3)
 
 
+def test_rope_table_matches_direct():
+    ops = _ops()
+    T, Hq, Hkv, hd = 5, 4, 2, 128
+    qkv = _randn(T, (Hq + 2 * Hkv) * hd, seed=12)
+    pos = torch.tensor([0, 5, 1023, 4000, 9000], dtype=torch.int32, device=DEV)   # last one is beyond the table
+    slot = torch.tensor([0, 1, 2, 3, -1], dtype=torch.int32, device=DEV)            # last one writes no KV
+    tab = ops.rope_table(8192, hd, 500000.0, DEV)
+    outs = []
+    for table in (None, tab):
+        kc = torch.zeros((2, Hkv, 16, hd), dtype=torch.float16, device=DEV)
+        vc = torch.zeros_like(kc)
+        q32 = torch.empty((T, Hq * hd), device=DEV)
+        ops.rope_kv(qkv, pos, slot, q32, None, kc, vc, Hq, Hkv, hd, 16, 500000.0, 0, 1.0, table=table)
+        outs.append((q32, kc, vc))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    assert outs[1][1][0, :, 4:].abs().sum().item() == 0.0
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 14336), (8, 512, 4096), (64, 192, 1024)])
+def test_gemm_split_k_inplace_residual(M, N, K):
+    """Few output tiles: the in-place residual add runs split over K with vector reductions."""
+    ops = _ops()
+    A = _randn(M, K, seed=31).bfloat16()
+    B = _randn(N, K, seed=32, scale=0.05).bfloat16()
+    bias = _randn(N, seed=33)
+    x0 = _randn(M, N, seed=34)
+    ref = x0 + bias + A.float() @ B.float().t()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for split_k in (0, 1, 3):
+        x = x0.clone()
+        ops.gemm_bf16(A, B, M, N, K, out_f32=x, resid_f32=x, bias=bias, status=status, split_k=split_k)
+        assert (x - ref).abs().max().item() < 2e-3 * math.sqrt(K) * 0.05 + 1e-3, split_k
+    assert int(status.item()) == 0
+
+
 def _paged_kv(B, Hkv, hd, lens, seed):
     """Random K/V for B sequences scattered over shuffled pages.  Returns caches, table, dense K/V."""
     max_pages = (max(lens) + 15) // 16
@@ -303,6 +339,18 @@ def test_argmax_and_sampling():
     ops.argmax(logits, ids, vals)
     assert torch.equal(ids.long().cpu(), logits.argmax(-1).cpu())
     assert int(ids[2]) == 3 and float(vals[1]) == 50.0
+    # rows split over many blocks: same answer, twice in a row (the scratch resets itself)
+    sc = ops.argmax_scratch(T, DEV)
+    for _ in range(2):
+        ids2 = torch.zeros(T, dtype=torch.int32, device=DEV)
+        vals2 = torch.zeros(T, device=DEV)
+        ops.argmax(logits, ids2, vals2, vocab_offset=7, scratch=sc)
+        assert torch.equal(ids2, ids + 7) and torch.equal(vals2, vals)
+    assert int(sc.abs().sum()) == 0
+    neg = -torch.rand(3, 40000, device=DEV) - 1.0
+    ids3 = torch.zeros(3, dtype=torch.int32, device=DEV)
+    ops.argmax(neg, ids3, None, scratch=sc)
+    assert torch.equal(ids3.long().cpu(), neg.argmax(-1).cpu())
     # top-1 sampling is arg-max whatever the random number
     u = torch.rand(T, device=DEV)
     scratch = torch.empty((T, V), device=DEV)
