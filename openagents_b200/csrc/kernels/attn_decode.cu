@@ -97,6 +97,17 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
 
   const int split = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g4 = lane >> 2, t4 = lane & 3;
+  if (tid == 0) {
+    for (int s = 0; s < kStages; s++) tc::mbar_init(tc::smem_u32(bars + s), 1);
+    s_abort = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_desc(&tmK);
+    tc::tma_prefetch_desc(&tmV);
+  }
+  // Everything above touches only this CTA's shared memory; lengths, page table, queries and the
+  // cache come from earlier kernels.
+  pdl_trigger();
+  pdl_wait();
   const int len = a.seq_lens[b];
   const int first = (a.window > 0 && len > a.window) ? len - a.window : 0;
   const int p_first = first >> 4, p_last = (len + 15) >> 4;
@@ -108,13 +119,6 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
 
   const int* pt = a.page_table + (size_t)b * a.max_pages;
   for (int i = tid; i < np; i += 128) s_pid[i] = pt[pa + i];
-  if (tid == 0) {
-    for (int s = 0; s < kStages; s++) tc::mbar_init(tc::smem_u32(bars + s), 1);
-    s_abort = 0;
-    tc::fence_barrier_init();
-    tc::tma_prefetch_desc(&tmK);
-    tc::tma_prefetch_desc(&tmV);
-  }
   __syncthreads();
 
   auto issue = [&](int i) {   // one lane: fetch page i of the range into ring slot i % kStages
@@ -353,8 +357,7 @@ static int launch(const AttnDecArgs& a, int B, int n_pages, cudaStream_t st) {
   if (rc) return rc;
   rc = make_tmap_2d(&tv, a.vc, 2, rows, HD, (uint64_t)HD * 2, 16, 64, true);
   if (rc) return rc;
-  attn_decode_kernel<HD, G><<<grid, 128, smem, st>>>(tk, tv, a);
-  return (int)cudaGetLastError();
+  return launch_pdl(attn_decode_kernel<HD, G>, grid, dim3(128), smem, st, tk, tv, a);
 }
 
 // Floats of scratch the split-merge needs: part_acc then part_ml, plus B*Hkv ints of counters.

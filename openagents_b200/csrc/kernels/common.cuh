@@ -18,7 +18,39 @@ enum B200Status : int {
   B200_ERR_BAD_ARG = 5,
 };
 
+// Programmatic dependent launch.  A kernel launched through launch_pdl may start while the kernel
+// before it in the stream is still running; it must call pdl_wait() before it reads anything an
+// earlier kernel wrote and before it writes anything at all.  What comes before the wait (barrier
+// and tensor-memory set-up, L2 prefetch of weights, which no kernel writes) overlaps the previous
+// kernel.  pdl_trigger() lets the NEXT kernel in the stream start its own preamble.
+// b200_set_pdl(0) turns the attribute off, so every launch is then fully serialised.
+extern "C" int b200_pdl_enabled();
+extern "C" int b200_prefetch_enabled();
+
 namespace b200 {
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Ask for `bytes` (multiple of 16) at 16-byte aligned `p` to be brought into L2; nothing waits for it.
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = b200_pdl_enabled() ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -7,6 +7,22 @@
 
 using namespace b200;
 
+static int g_pdl = 1;
+extern "C" __attribute__((visibility("default"))) int b200_pdl_enabled() { return g_pdl; }
+// on = 0: launch every kernel fully serialised (no programmatic dependent launch).
+B200_API int b200_set_pdl(int on) {
+  g_pdl = on ? 1 : 0;
+  return 0;
+}
+static int g_prefetch = 1;
+extern "C" __attribute__((visibility("default"))) int b200_prefetch_enabled() { return g_prefetch; }
+// on = 0: kernels do not prefetch their weights into L2 ahead of the dependency wait.
+B200_API int b200_set_prefetch(int on) {
+  g_prefetch = on ? 1 : 0;
+  return 0;
+}
+
+
 // ------------------------------------------------------------------ embedding gather
 
 // Weight types of the embedding table.
@@ -18,6 +34,8 @@ enum { EMB_F32 = 0, EMB_BF16 = 1, EMB_Q8R = 2, EMB_Q6KR = 3 };
 __global__ void embedding_kernel(const int* __restrict__ ids, float* __restrict__ out, int D, int type,
                                  const uint8_t* __restrict__ w, const __half* __restrict__ w2,
                                  int vocab_lo, int vocab_n) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t] - vocab_lo;
   float* o = out + (size_t)t * D;
@@ -61,9 +79,8 @@ __global__ void embedding_kernel(const int* __restrict__ ids, float* __restrict_
 
 B200_API int b200_embedding(const int* ids, float* out, int T, int D, int type, const void* w,
                             const void* w2, int vocab_lo, int vocab_n, cudaStream_t st) {
-  embedding_kernel<<<T, 256, 0, st>>>(ids, out, D, type, (const uint8_t*)w, (const __half*)w2, vocab_lo,
-                                      vocab_n);
-  return (int)cudaGetLastError();
+  return launch_pdl(embedding_kernel, dim3(T), dim3(256), 0, st, ids, out, D, type, (const uint8_t*)w,
+                    (const __half*)w2, vocab_lo, vocab_n);
 }
 
 // ------------------------------------------------------------------ RMSNorm (+ quantize)
@@ -85,12 +102,17 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
   const int nblk = D / 32;
   float v[kRmsRegs], gg[kRmsRegs];
   float ss = 0.f;
+  pdl_trigger();
+#pragma unroll
+  for (int k = 0; k < kRmsRegs; k++) {   // the gain is a weight: read it while the producer of x still runs
+    const int blk = w + k * nw;
+    gg[k] = (blk < nblk && g) ? g[blk * 32 + lane] : 1.f;
+  }
+  pdl_wait();
 #pragma unroll
   for (int k = 0; k < kRmsRegs; k++) {
     const int blk = w + k * nw;
-    const bool in = blk < nblk;
-    v[k] = in ? xr[blk * 32 + lane] : 0.f;
-    gg[k] = (in && g) ? g[blk * 32 + lane] : 1.f;
+    v[k] = blk < nblk ? xr[blk * 32 + lane] : 0.f;
   }
 #pragma unroll
   for (int k = 0; k < kRmsRegs; k++) ss += v[k] * v[k];
@@ -128,13 +150,15 @@ B200_API int b200_rmsnorm(const float* x, const float* g, float eps, int T, int 
                           float* xs16, void* hb, float* hf, cudaStream_t st) {
   if (D % 32) return B200_ERR_BAD_ARG;
   const int threads = D >= 4096 ? 1024 : D >= 1024 ? 512 : 256;
-  rmsnorm_kernel<<<T, threads, 0, st>>>(x, g, eps, D, (int8_t*)xq, xd, xs16, (__nv_bfloat16*)hb, hf);
-  return (int)cudaGetLastError();
+  return launch_pdl(rmsnorm_kernel, dim3(T), dim3(threads), 0, st, x, g, eps, D, (int8_t*)xq, xd, xs16,
+                    (__nv_bfloat16*)hb, hf);
 }
 
 // Plain activation quantization of fp32 rows (used where no norm precedes a quantized matvec).
 __global__ void quantize_x_kernel(const float* __restrict__ x, int D, int8_t* __restrict__ xq,
                                   float* __restrict__ xd, float* __restrict__ xs16) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int blk = w; blk < D / 32; blk += nw) {
@@ -145,8 +169,7 @@ __global__ void quantize_x_kernel(const float* __restrict__ x, int D, int8_t* __
 }
 B200_API int b200_quantize_x(const float* x, int T, int D, void* xq, float* xd, float* xs16, cudaStream_t st) {
   if (D % 32) return B200_ERR_BAD_ARG;
-  quantize_x_kernel<<<T, 256, 0, st>>>(x, D, (int8_t*)xq, xd, xs16);
-  return (int)cudaGetLastError();
+  return launch_pdl(quantize_x_kernel, dim3(T), dim3(256), 0, st, x, D, (int8_t*)xq, xd, xs16);
 }
 
 // ------------------------------------------------------------------ RoPE + paged KV write
@@ -166,6 +189,8 @@ __global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restr
                                __half* __restrict__ kc, __half* __restrict__ vc, int Hq, int Hkv, int hd,
                                int page_size, float theta, int style, float q_scale,
                                const float2* __restrict__ tab, int tab_len) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int row = (Hq + 2 * Hkv) * hd;
   const float* in = qkv + (size_t)t * row;
@@ -242,10 +267,9 @@ B200_API int b200_rope_kv(const float* qkv, const int* pos, const int* slot, flo
                           int style, float q_scale, const void* tab, int tab_len, cudaStream_t st) {
   if (hd % 2) return B200_ERR_BAD_ARG;
   const int items = (Hq + 2 * Hkv) * (hd / 2);
-  rope_kv_kernel<<<dim3(T, (items + 255) / 256), 256, 0, st>>>(qkv, pos, slot, q_out, (__half*)q_out_h, (__half*)kc,
-                                                               (__half*)vc, Hq, Hkv, hd, page_size, theta, style,
-                                                               q_scale, (const float2*)tab, tab_len);
-  return (int)cudaGetLastError();
+  return launch_pdl(rope_kv_kernel, dim3(T, (items + 255) / 256), dim3(256), 0, st, qkv, pos, slot, q_out,
+                    (__half*)q_out_h, (__half*)kc, (__half*)vc, Hq, Hkv, hd, page_size, theta, style, q_scale,
+                    (const float2*)tab, tab_len);
 }
 
 // ------------------------------------------------------------------ SwiGLU / add / bias
@@ -253,6 +277,8 @@ B200_API int b200_rope_kv(const float* qkv, const int* pos, const int* slot, flo
 // gu fp32 [T][2F] (gate then up) -> bf16 and/or fp32 act [T][F]
 __global__ void swiglu_kernel(const float* __restrict__ gu, int F, __nv_bfloat16* __restrict__ ob,
                               float* __restrict__ of) {
+  pdl_trigger();
+  pdl_wait();
   const size_t t = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= F) return;
@@ -262,17 +288,17 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, int F, __nv_bfloat16
 }
 B200_API int b200_swiglu(const float* gu, int T, int F, void* ob, float* of, cudaStream_t st) {
   dim3 grid((F + 255) / 256, T);
-  swiglu_kernel<<<grid, 256, 0, st>>>(gu, F, (__nv_bfloat16*)ob, of);
-  return (int)cudaGetLastError();
+  return launch_pdl(swiglu_kernel, grid, dim3(256), 0, st, gu, F, (__nv_bfloat16*)ob, of);
 }
 
 __global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, size_t n) {
+  pdl_trigger();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) x[i] += y[i];
 }
 B200_API int b200_add_inplace(float* x, const float* y, size_t n, cudaStream_t st) {
-  add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, y, n);
-  return (int)cudaGetLastError();
+  return launch_pdl(add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, x, y, n);
 }
 
 // ------------------------------------------------------------------ sampling
@@ -293,6 +319,8 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ l
                                                      float* __restrict__ out_val, int vocab_offset,
                                                      unsigned long long* __restrict__ keys, int* __restrict__ tickets) {
   __shared__ unsigned long long sk[8];
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const float* l = logits + (size_t)t * V;
   const int per = (V + gridDim.y - 1) / gridDim.y;
@@ -334,8 +362,8 @@ B200_API int b200_argmax(const float* logits, int T, int V, int* out_id, float* 
   if (scratch) chunks = max(1, min(64, V / 2048));
   unsigned long long* keys = (unsigned long long*)scratch;
   int* tickets = scratch ? (int*)(keys + T) : nullptr;
-  argmax_kernel<<<dim3(T, chunks), 256, 0, st>>>(logits, V, out_id, out_val, vocab_offset, keys, tickets);
-  return (int)cudaGetLastError();
+  return launch_pdl(argmax_kernel, dim3(T, chunks), dim3(256), 0, st, logits, V, out_id, out_val, vocab_offset, keys,
+                    tickets);
 }
 
 // Temperature / top-k / top-p sampling of one token per row.  One block per row.  The candidate
@@ -440,6 +468,8 @@ __global__ void decode_advance_kernel(int* __restrict__ ids, const int* __restri
                                       int* __restrict__ slot, int* __restrict__ seq_lens,
                                       const int* __restrict__ page_table, int max_pages, int page_size, int B,
                                       int* __restrict__ hist, int* __restrict__ step_counter, int hist_cap) {
+  pdl_trigger();
+  pdl_wait();
   const int step = *step_counter;
   for (int b = threadIdx.x; b < B; b += blockDim.x) {
     const int id = out_ids[b];
@@ -457,9 +487,8 @@ __global__ void decode_advance_kernel(int* __restrict__ ids, const int* __restri
 B200_API int b200_decode_advance(int* ids, const int* out_ids, int* pos, int* slot, int* seq_lens,
                                  const int* page_table, int max_pages, int page_size, int B, int* hist,
                                  int* step_counter, int hist_cap, cudaStream_t st) {
-  decode_advance_kernel<<<1, 256, 0, st>>>(ids, out_ids, pos, slot, seq_lens, page_table, max_pages, page_size, B,
-                                           hist, step_counter, hist_cap);
-  return (int)cudaGetLastError();
+  return launch_pdl(decode_advance_kernel, dim3(1), dim3(256), 0, st, ids, out_ids, pos, slot, seq_lens, page_table,
+                    max_pages, page_size, B, hist, step_counter, hist_cap);
 }
 
 // ------------------------------------------------------------------ allocation-free sampling

@@ -64,6 +64,9 @@ struct GemmEpi {
   // Split-K (small M): each split adds its partial product into out_f32 with a vector `red`, so
   // out_f32 must already hold the residual (or zeros); bias comes from split 0 only.
   int splitk_red;
+  // Swapped operands (few tokens): the kernel computes W X^T, so an accumulator row is an output
+  // COLUMN; the epilogue then writes out[col][row] and takes the bias by row.
+  int transposed;
   // Fused collective epilogue (tensor-parallel row-parallel GEMMs): instead of storing, add the tile
   // into an fp32 tensor [*, ldc] at byte offset sym_off of the symmetric heap.
   //   SYM_ALLREDUCE : into every rank's replica (multimem.red through the switch where available)
@@ -78,8 +81,83 @@ enum { SYM_NONE = 0, SYM_ALLREDUCE = 1, SYM_RSCATTER = 2 };
 
 constexpr int BM = 128, BK = 64;
 
+// Accumulating epilogues (fused collectives, split K) go through shared memory so that one warp
+// instruction adds 4 rows x 128 contiguous bytes instead of 32 rows x 16 bytes: reductions that
+// cross NVLink are sent as full packets, and local ones touch whole sectors.  `stage` is this warp's
+// 32 x 32 fp32 patch; lane = accumulator row on the way in, (row group, float4 column) on the way out.
+__device__ __forceinline__ void epilogue_chunk_red(const GemmEpi& e, float* stage, int m_warp0, int n0, int M, int N,
+                                                   const uint32_t (&r)[32], bool first_split) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int c4 = 0; c4 < 8; c4++)
+    *(float4*)(stage + lane * 32 + ((c4 ^ (lane & 7)) << 2)) =
+        make_float4(__uint_as_float(r[4 * c4]), __uint_as_float(r[4 * c4 + 1]), __uint_as_float(r[4 * c4 + 2]),
+                    __uint_as_float(r[4 * c4 + 3]));
+  __syncwarp();
+  const int c4 = lane & 7, n = n0 + c4 * 4;
+  if (n < N) {
+    const bool sym = e.sym_mode != SYM_NONE;
+    float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (e.bias && first_split && (!sym || e.sym.rank == 0)) b = *(const float4*)(e.bias + n);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int row = (lane >> 3) + 4 * i, m = m_warp0 + row;
+      if (m >= M) break;
+      float4 o = *(const float4*)(stage + row * 32 + ((c4 ^ (row & 7)) << 2));
+      o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+      if (!sym) {
+        asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(e.out_f32 + (size_t)m * e.ldc + n),
+                     "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w) : "memory");
+      } else if (e.sym_mode == SYM_ALLREDUCE) {
+        sym_red_all_f32x4(e.sym, e.sym_off + ((size_t)m * e.ldc + n) * 4, o);
+      } else {
+        sym_red_to_f32x4(e.sym, m / e.rows_per_rank, e.sym_off + ((size_t)(m % e.rows_per_rank) * e.ldc + n) * 4, o);
+      }
+    }
+  }
+  __syncwarp();
+}
+
+// Transposed epilogue: this thread holds, for output column `n` (a weight row), the values of the 32
+// output rows t0..t0+31 (tokens).  Consecutive lanes hold consecutive columns, so each of the 32
+// stores of a warp covers 128 contiguous bytes.
+__device__ __forceinline__ void epilogue_col(const GemmEpi& e, int n, int t0, int n_cols, int n_rows,
+                                             const uint32_t (&r)[32], bool first_split) {
+  if (n >= n_cols) return;
+  const bool sym = e.sym_mode != SYM_NONE;
+  const float b = (e.bias && first_split && (!sym || e.sym.rank == 0)) ? e.bias[n] : 0.f;
+#pragma unroll 4
+  for (int j = 0; j < 32; j++) {
+    const int t = t0 + j;
+    if (t >= n_rows) break;
+    float x = __uint_as_float(r[j]) + b;
+    if (sym) {
+      const int owner = e.sym_mode == SYM_RSCATTER ? t / e.rows_per_rank : 0;
+      const int lrow = e.sym_mode == SYM_RSCATTER ? t % e.rows_per_rank : t;
+      const size_t off = e.sym_off + ((size_t)lrow * e.ldc + n) * 4;
+      if (e.sym_mode == SYM_ALLREDUCE) sym_red_all_f32(e.sym, off, x);
+      else sym_red_to_f32(e.sym, owner, off, x);
+      continue;
+    }
+    const size_t idx = (size_t)t * e.ldc + n;
+    if (e.splitk_red) {
+      asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(e.out_f32 + idx), "f"(x) : "memory");
+      continue;
+    }
+    if (e.act == ACT_GELU) x = gelu_tanh(x);
+    if (e.resid_f32) x += e.resid_f32[idx];
+    if (e.resid_bf16) x += __bfloat162float(e.resid_bf16[idx]);
+    if (e.out_f32) e.out_f32[idx] = e.accumulate ? e.out_f32[idx] + x : x;
+    if (e.out_bf16) e.out_bf16[idx] = __float2bfloat16(x);
+  }
+}
+
 __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, int M, int N, const uint32_t (&r)[32],
                                              bool first_split) {
+  if (e.transposed) {
+    epilogue_col(e, m, n0, M, N, r, first_split);
+    return;
+  }
   if (m >= M) return;
   const size_t base = (size_t)m * e.ldc + n0;
   float v[32];
@@ -210,6 +288,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]
   uint32_t* tmem_holder = (uint32_t*)(bars + 2 * STAGES + 4);
   volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+  float* stage_all = (float*)(bars + 2 * STAGES + 6);   // 4 epilogue warps x 32 x 32 fp32, 16-byte aligned
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = (K + BK - 1) / BK;
@@ -239,6 +318,10 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+
+  // Set-up above touches only this CTA's shared and tensor memory; the operands come from earlier kernels.
+  pdl_trigger();
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -287,6 +370,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     }
   } else {
     const int q = warp & 3;
+    float* stage = stage_all + q * 1024;
+    const bool red_path = !epi.transposed && (epi.sym_mode != SYM_NONE || epi.splitk_red);
     uint32_t tcount = 0;
     for (int item = blockIdx.x; item < n_tiles; item += gridDim.x, tcount++) {
       const int tile = item / splits, sp = item - tile * splits;
@@ -302,7 +387,10 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + (uint32_t)(c * 32), r);
         tmem_ld_wait();
-        if (n0 + c * 32 < N) epilogue_row(epi, m, n0 + c * 32, M, N, r, sp == 0);
+        if (n0 + c * 32 < N) {
+          if (red_path) epilogue_chunk_red(epi, stage, m0 + q * 32, n0 + c * 32, M, N, r, sp == 0);
+          else epilogue_row(epi, m, n0 + c * 32, M, N, r, sp == 0);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -330,7 +418,7 @@ static int sm_count() {
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpi& e, int M, int N, int K,
                        int splits, int* status, cudaStream_t st) {
-  constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16;
+  constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 6) * 8 + 4 * 32 * 32 * 4;
   auto kern = gemm_bf16_kernel<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
@@ -340,8 +428,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmE
   }
   const int n_tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM) * splits;
   const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
-  kern<<<grid, 192, smem, st>>>(ta, tb, e, M, N, K, splits, status);
-  return (int)cudaGetLastError();
+  return launch_pdl(kern, dim3(grid), dim3(192), smem, st, ta, tb, e, M, N, K, splits, status);
 }
 
 // A [M][K] (row stride lda), B [N][K] (row stride ldb), bf16, K-major.  Strides in elements and
@@ -355,6 +442,18 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   if (M <= 0 || N <= 0 || K <= 0 || (lda % 8) || (ldb % 8) || (K % 8)) return B200_ERR_BAD_ARG;
   if ((out_bf16 && (ldc % 8)) || (out_f32 && (ldc % 4))) return B200_ERR_BAD_ARG;
   if (N % 4) return B200_ERR_BAD_ARG;
+  if (sym_mode != SYM_NONE && (!sym || (ldc % 4) || (sym_off % 16))) return B200_ERR_BAD_ARG;
+  // Few tokens: stream the weights as the 128-row operand and the tokens as the narrow one, so that
+  // most of every pipeline stage is weight bytes from HBM and none of the tile is padding.
+  // Measured on the decode shapes (64 tokens), the swapped form is only faster for long K with few
+  // rows, so it is opt-in: tile_n = -1.
+  const bool swap = tile_n == -1 && M <= 256 && N >= 128;
+  if (swap) {
+    tile_n = M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    const void* tp = A; A = B; B = tp;
+    const int ti = lda; lda = ldb; ldb = ti;
+    const int tm = M; M = N; N = tm;
+  }
   const long tiles_m = (M + 127) / 128;
   if (tile_n == 0) {
     const long tiles256 = (long)((N + 255) / 256) * tiles_m, tiles128 = (long)((N + 127) / 128) * tiles_m;
@@ -382,6 +481,7 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   int splits = 1;
   if (split_k > 0) splits = split_k;
   else if (red_ok && n_out_tiles <= 74) splits = (int)(148 / n_out_tiles);
+  if (split_k <= 0 && sym_mode != SYM_NONE && splits > 2) splits = 2;   // every split's tile crosses NVLink
   if (splits > 1) {
     if (!red_ok) return B200_ERR_BAD_ARG;
     if (splits > 16) splits = 16;
@@ -390,6 +490,7 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
     splits = (KBt + kps - 1) / kps;                            // no empty split
   }
   e.splitk_red = (splits > 1 && sym_mode == SYM_NONE) ? 1 : 0;
+  e.transposed = swap ? 1 : 0;
   if (sym_mode != SYM_NONE) {
     if (!sym || (ldc % 4) || (sym_off % 16)) return B200_ERR_BAD_ARG;
     e.sym = *sym;

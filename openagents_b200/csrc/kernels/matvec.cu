@@ -37,6 +37,7 @@ struct MatvecArgs {
   // barrier, so on completion each replica holds resid + sum of all ranks' partials.
   SymTable sym;
   size_t sym_off;
+  int prefetch;         // bring this CTA's weight rows into L2 before waiting for the previous kernel
 };
 
 __device__ __forceinline__ int dp4a(uint32_t a, uint32_t b, int c) {
@@ -163,14 +164,15 @@ __device__ __forceinline__ void unit_dot(const UnitRaw<WT>& r, int u, int U, con
   }
 }
 
-// Shared epilogue: res[m][r][b] holds the 32 x B results of matrix m (m = 1 only when dual).
-template <int B>
+// Shared epilogue: res[m][r][b] holds the R x B results of matrix m (m = 1 only when dual); R is the
+// number of rows a CTA owns (32, or fewer for small matrices so that more CTAs share the stream).
+template <int B, int R = 32>
 __device__ __forceinline__ void matvec_epilogue(const MatvecArgs& a, const float* res, bool dual) {
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   if (w >= a.nb) return;
   const int b = w;
-  const int n = blockIdx.x * 32 + lane;
-  const bool live = n < a.N;
+  const int n = blockIdx.x * R + lane;
+  const bool live = lane < R && n < a.N;
   float v = res[lane * B + b];
   if (a.bias && live && (a.epi != EPI_ALLREDUCE || a.sym.rank == 0)) v += a.bias[n];
   if (a.epi == EPI_STORE) {
@@ -197,10 +199,31 @@ __device__ __forceinline__ void matvec_epilogue(const MatvecArgs& a, const float
   }
 }
 
-template <int WT, int B, bool DUAL>
+template <int WT, int B, bool DUAL, int RW>
 __global__ void __launch_bounds__(256) matvec_q_kernel(const MatvecArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
+  constexpr int R = 8 * RW;   // rows per CTA
+  static_assert(!DUAL || RW == 4, "the SwiGLU epilogue quantizes 32-row blocks");
   const int U = a.K / 32;
+  {
+    // This CTA's weight rows are one contiguous range (two when dual).  Ask for them in L2 now: the
+    // kernel before this one in the stream may still be running, and the weights do not depend on it.
+    const size_t rbp = row_bytes<WT>(a.K);
+    const int r0 = blockIdx.x * R;
+    const int nr = min(R, a.N - r0);
+    if (nr > 0 && a.prefetch) {
+      const size_t bytes = (size_t)nr * rbp;     // multiple of 16: every row is
+      constexpr uint32_t CH = 16384;
+      const int nch = (int)((bytes + CH - 1) / CH);
+      for (int c = threadIdx.x; c < nch * (DUAL ? 2 : 1); c += 256) {
+        const int m = c / nch, cc = c - m * nch;
+        const size_t off = (size_t)cc * CH;
+        prefetch_l2(a.w + ((size_t)r0 + (size_t)m * a.N) * rbp + off, (uint32_t)min((size_t)CH, bytes - off));
+      }
+    }
+  }
+  pdl_trigger();
+  pdl_wait();
   uint4* xp0 = (uint4*)smem;                  // [B][U]
   uint4* xp1 = xp0 + B * U;                   // [B][U]
   float* sxd = (float*)(xp1 + B * U);         // [B][U]
@@ -229,7 +252,6 @@ __global__ void __launch_bounds__(256) matvec_q_kernel(const MatvecArgs a) {
 
   const size_t rb = row_bytes<WT>(a.K);
   const int w2_per_row = (WT == WT_Q6KR) ? a.K / 256 : U;
-  constexpr int RW = 4;             // rows per warp
   constexpr int NM = DUAL ? 2 : 1;  // matrices
   float acc[NM][RW][B];
 #pragma unroll
@@ -243,7 +265,7 @@ __global__ void __launch_bounds__(256) matvec_q_kernel(const MatvecArgs a) {
   bool live[RW];
 #pragma unroll
   for (int i = 0; i < RW; i++) {
-    const int n = blockIdx.x * 32 + w + 8 * i;
+    const int n = blockIdx.x * R + w + 8 * i;
     live[i] = n < a.N;
     const int nn = live[i] ? n : 0;
 #pragma unroll
@@ -279,7 +301,7 @@ __global__ void __launch_bounds__(256) matvec_q_kernel(const MatvecArgs a) {
     }
   }
   __syncthreads();
-  matvec_epilogue<B>(a, res, DUAL);
+  matvec_epilogue<B, R>(a, res, DUAL);
   if (a.epi == EPI_ALLREDUCE) sym_kernel_end_barrier(a.sym, 0, gridDim.x);
 }
 
@@ -290,6 +312,8 @@ __global__ void __launch_bounds__(256) matvec_bf16_kernel(const MatvecArgs a) {
   float* xs = (float*)smem;            // [B][K]
   float* res = xs + (size_t)B * a.K;   // [2][32][B]
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  pdl_trigger();
+  pdl_wait();
   for (int i = tid; i < B * a.K; i += 256) {
     const int b = i / a.K;
     xs[i] = b < a.nb ? a.xf[i] : 0.f;
@@ -346,17 +370,26 @@ __global__ void __launch_bounds__(256) matvec_bf16_kernel(const MatvecArgs a) {
   if (a.epi == EPI_ALLREDUCE) sym_kernel_end_barrier(a.sym, 0, gridDim.x);
 }
 
-template <int WT, int B, bool DUAL>
-static int launch_q(const MatvecArgs& a, cudaStream_t st) {
+template <int WT, int B, bool DUAL, int RW>
+static int launch_q_rw(const MatvecArgs& a, cudaStream_t st) {
   const int U = a.K / 32;
   const size_t smem = (size_t)B * U * (16 + 16 + 4 + 8) + 2 * 32 * B * sizeof(float);
-  auto kern = matvec_q_kernel<WT, B, DUAL>;
+  auto kern = matvec_q_kernel<WT, B, DUAL, RW>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kern<<<(a.N + 31) / 32, 256, smem, st>>>(a);
-  return (int)cudaGetLastError();
+  constexpr int R = 8 * RW;
+  return launch_pdl(kern, dim3((a.N + R - 1) / R), dim3(256), smem, st, a);
+}
+template <int WT, int B, bool DUAL>
+static int launch_q(const MatvecArgs& a, cudaStream_t st) {
+  // One or two tokens and a matrix of a few thousand rows: 32-row CTAs would leave SMs idle and too
+  // few loads in flight, so a CTA takes 8 rows instead.
+  if constexpr (!DUAL && B <= 2) {
+    if ((a.N + 31) / 32 < 3 * 148) return launch_q_rw<WT, B, DUAL, 1>(a, st);
+  }
+  return launch_q_rw<WT, B, DUAL, 4>(a, st);
 }
 template <int B, bool DUAL>
 static int launch_bf16(const MatvecArgs& a, cudaStream_t st) {
@@ -366,8 +399,7 @@ static int launch_bf16(const MatvecArgs& a, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kern<<<(a.N + 31) / 32, 256, smem, st>>>(a);
-  return (int)cudaGetLastError();
+  return launch_pdl(kern, dim3((a.N + 31) / 32), dim3(256), smem, st, a);
 }
 
 template <int B, bool DUAL>
@@ -402,6 +434,7 @@ B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, in
     a.sym = SymTable{};
     a.sym_off = 0;
   }
+  a.prefetch = b200_prefetch_enabled();
   const bool dual = epi == EPI_SWIGLU_Q8 || epi == EPI_SWIGLU_F32;
   const int B = nb <= 1 ? 1 : nb <= 2 ? 2 : nb <= 4 ? 4 : 8;
   if (dual) {

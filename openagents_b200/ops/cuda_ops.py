@@ -6,6 +6,7 @@ non-zero return code.  There is no fallback: on a machine with a GPU a missing l
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_size_t, c_void_p
 
 import torch
@@ -36,6 +37,8 @@ _SIGS = {
     "b200_attn_prefill": [_P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
     "b200_gemm_bf16": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int,
                        _P, c_int, _P, c_size_t, c_int, _P],
+    "b200_set_pdl": [c_int],
+    "b200_set_prefetch": [c_int],
     "b200_dequant_bf16": [c_int, _P, _P, _P, c_size_t, c_int, _P],
     "b200_f32_to_bf16": [_P, _P, c_size_t, _P],
     "b200_transpose_bf16": [_P, _P, c_int, c_int, _P],
@@ -57,6 +60,10 @@ def lib():
         L.b200_attn_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
         L.b200_attn_decode_scratch_floats.restype = c_size_t
         _lib = L
+        if os.environ.get("B200_PDL", "1") == "0":      # debugging aid: fully serialised launches
+            L.b200_set_pdl(0)
+        if os.environ.get("B200_PREFETCH", "1") == "0":
+            L.b200_set_prefetch(0)
     return _lib
 
 
@@ -165,6 +172,11 @@ def gemm_bf16(A, B, M, N, K, lda=None, ldb=None, out_f32=None, out_bf16=None, ld
     _check(lib().b200_gemm_bf16(_p(A), _p(B), M, N, K, lda or K, ldb or K, _p(out_f32), _p(out_bf16), ldc or N,
                                 _p(bias), _p(resid_f32), _p(resid_bf16), act, int(accumulate), tile_n, split_k, _p(status),
                                 sym_mode, _sym(sym), sym_off, rows_per_rank, _st()), "gemm_bf16")
+
+
+def set_pdl(on: bool):
+    """Turn programmatic dependent launch of the decode-path kernels on or off (on by default)."""
+    _check(lib().b200_set_pdl(int(on)), "set_pdl")
 
 
 def dequant_bf16(wt, w, w2, out, N, K):

@@ -195,10 +195,15 @@ def test_gemm_split_k_inplace_residual(M, N, K):
     x0 = _randn(M, N, seed=34)
     ref = x0 + bias + A.float() @ B.float().t()
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    for split_k in (0, 1, 3):
+    for split_k, tile_n in ((0, 0), (1, 0), (3, 0), (0, -1), (1, -1)):      # tile_n -1: weights as the 128-row operand
         x = x0.clone()
-        ops.gemm_bf16(A, B, M, N, K, out_f32=x, resid_f32=x, bias=bias, status=status, split_k=split_k)
-        assert (x - ref).abs().max().item() < 2e-3 * math.sqrt(K) * 0.05 + 1e-3, split_k
+        ops.gemm_bf16(A, B, M, N, K, out_f32=x, resid_f32=x, bias=bias, status=status, split_k=split_k, tile_n=tile_n)
+        assert (x - ref).abs().max().item() < 2e-3 * math.sqrt(K) * 0.05 + 1e-3, (split_k, tile_n)
+    out = torch.zeros((M, N), device=DEV)
+    outb = torch.zeros((M, N), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_bf16(A, B, M, N, K, out_f32=out, out_bf16=outb, bias=bias, act=ops.ACT_GELU, tile_n=-1, status=status)
+    g = torch.nn.functional.gelu(ref - x0, approximate="tanh")
+    assert torch.allclose(out, g, atol=2e-2, rtol=1e-3) and torch.allclose(outb.float(), g, atol=5e-2, rtol=2e-2)
     assert int(status.item()) == 0
 
 
