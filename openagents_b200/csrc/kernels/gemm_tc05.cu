@@ -67,6 +67,18 @@ struct GemmEpi {
   // Swapped operands (few tokens): the kernel computes W X^T, so an accumulator row is an output
   // COLUMN; the epilogue then writes out[col][row] and takes the bias by row.
   int transposed;
+  // Grouped GEMM (mixture-of-experts): rows of A and of the output come in groups of `group_rows`
+  // (one expert each, a multiple of 128); group g multiplies B rows [g * group_n, (g + 1) * group_n)
+  // and only its first group_counts[g] rows are live (tiles beyond them are skipped).
+  //   moe_mode 1: columns are (gate, up) pairs; writes silu(gate) * up to out_bf16[m][n / 2]
+  //   moe_mode 2: combine: row m is token meta[2m+1] of rank meta[2m]; adds gate_w[m] * value into
+  //               that rank's fp32 tensor at heap offset sym_off ([token][ldc]); ends with a barrier
+  int group_rows;
+  int group_n;
+  const int* group_counts;
+  int moe_mode;
+  const int* meta;
+  const float* gate_w;
   // Fused collective epilogue (tensor-parallel row-parallel GEMMs): instead of storing, add the tile
   // into an fp32 tensor [*, ldc] at byte offset sym_off of the symmetric heap.
   //   SYM_ALLREDUCE : into every rank's replica (multimem.red through the switch where available)
@@ -113,6 +125,47 @@ __device__ __forceinline__ void epilogue_chunk_red(const GemmEpi& e, float* stag
       } else {
         sym_red_to_f32x4(e.sym, m / e.rows_per_rank, e.sym_off + ((size_t)(m % e.rows_per_rank) * e.ldc + n) * 4, o);
       }
+    }
+  }
+  __syncwarp();
+}
+
+// moe_mode 1: 32 accumulator columns are 16 (gate, up) pairs of one row.
+__device__ __forceinline__ void epilogue_row_swiglu(const GemmEpi& e, int m, int n0, const uint32_t (&r)[32]) {
+  uint4 o[2];
+  __nv_bfloat162* p = (__nv_bfloat162*)o;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const float g0 = __uint_as_float(r[4 * j]), u0 = __uint_as_float(r[4 * j + 1]);
+    const float g1 = __uint_as_float(r[4 * j + 2]), u1 = __uint_as_float(r[4 * j + 3]);
+    p[j] = __floats2bfloat162_rn(silu(g0) * u0, silu(g1) * u1);
+  }
+  uint4* dst = (uint4*)(e.out_bf16 + (size_t)m * e.ldc + (n0 >> 1));
+  dst[0] = o[0];
+  dst[1] = o[1];
+}
+
+// moe_mode 2: like epilogue_chunk_red, but every row has its own destination (rank, token) and weight.
+__device__ __forceinline__ void epilogue_chunk_combine(const GemmEpi& e, float* stage, int m_warp0, int live_end,
+                                                       int n0, int N, const uint32_t (&r)[32]) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int c4 = 0; c4 < 8; c4++)
+    *(float4*)(stage + lane * 32 + ((c4 ^ (lane & 7)) << 2)) =
+        make_float4(__uint_as_float(r[4 * c4]), __uint_as_float(r[4 * c4 + 1]), __uint_as_float(r[4 * c4 + 2]),
+                    __uint_as_float(r[4 * c4 + 3]));
+  __syncwarp();
+  const int c4 = lane & 7, n = n0 + c4 * 4;
+  if (n < N) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int row = (lane >> 3) + 4 * i, m = m_warp0 + row;
+      if (m >= live_end) break;
+      const int dst = e.meta[2 * m], tok = e.meta[2 * m + 1];
+      const float w = e.gate_w[m];
+      float4 o = *(const float4*)(stage + row * 32 + ((c4 ^ (row & 7)) << 2));
+      o.x *= w; o.y *= w; o.z *= w; o.w *= w;
+      sym_red_to_f32x4(e.sym, dst, e.sym_off + ((size_t)tok * e.ldc + n) * 4, o);
     }
   }
   __syncwarp();
@@ -330,6 +383,12 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       for (int item = blockIdx.x; item < n_tiles && ok; item += gridDim.x) {
         const int tile = item / splits, sp = item - tile * splits;
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        int b_row = n0;
+        if (epi.group_rows) {
+          const int g = m0 / epi.group_rows;
+          if (m0 - g * epi.group_rows >= epi.group_counts[g]) continue;   // every role skips the same tiles
+          b_row += g * epi.group_n;
+        }
         const int kb0 = sp * kps, kb1 = min(KB, kb0 + kps);
         for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
@@ -337,7 +396,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
           if (!mbar_wait(smem_u32(empty + s), ph ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(smem_u32(full + s), A_BYTES + B_BYTES);
           tma_load_2d(smem_u32(sA + s * A_BYTES), &tmA, smem_u32(full + s), kb * BK, m0);
-          tma_load_2d(smem_u32(sB + s * B_BYTES), &tmB, smem_u32(full + s), kb * BK, n0);
+          tma_load_2d(smem_u32(sB + s * B_BYTES), &tmB, smem_u32(full + s), kb * BK, b_row);
         }
       }
     }
@@ -346,10 +405,15 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       constexpr uint32_t idesc = idesc_bf16(BM, BN);
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_tiles && ok; item += gridDim.x, tcount++) {
-        const int sp = item % splits;
+      for (int item = blockIdx.x; item < n_tiles && ok; item += gridDim.x) {
+        const int tile = item / splits, sp = item - tile * splits;
+        if (epi.group_rows) {
+          const int m0 = (tile % tiles_m) * BM, g = m0 / epi.group_rows;
+          if (m0 - g * epi.group_rows >= epi.group_counts[g]) continue;
+        }
         const int kb0 = sp * kps, kb1 = min(KB, kb0 + kps);
         const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+        tcount++;
         if (!mbar_wait(smem_u32(tempty + acc), aph ^ 1, abort_flag)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -373,10 +437,17 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     float* stage = stage_all + q * 1024;
     const bool red_path = !epi.transposed && (epi.sym_mode != SYM_NONE || epi.splitk_red);
     uint32_t tcount = 0;
-    for (int item = blockIdx.x; item < n_tiles; item += gridDim.x, tcount++) {
+    for (int item = blockIdx.x; item < n_tiles; item += gridDim.x) {
       const int tile = item / splits, sp = item - tile * splits;
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      int live_end = M;                       // rows below this index are written
+      if (epi.group_rows) {
+        const int g = m0 / epi.group_rows, cnt = epi.group_counts[g];
+        if (m0 - g * epi.group_rows >= cnt) continue;
+        live_end = g * epi.group_rows + cnt;
+      }
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+      tcount++;
       bool ok = mbar_wait(smem_u32(tfull + acc), aph, abort_flag);
       ok = __all_sync(0xffffffffu, ok && !*abort_flag);  // tcgen05.ld needs the whole warp
       if (!ok) break;
@@ -388,8 +459,10 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + (uint32_t)(c * 32), r);
         tmem_ld_wait();
         if (n0 + c * 32 < N) {
-          if (red_path) epilogue_chunk_red(epi, stage, m0 + q * 32, n0 + c * 32, M, N, r, sp == 0);
-          else epilogue_row(epi, m, n0 + c * 32, M, N, r, sp == 0);
+          if (epi.moe_mode == 2) epilogue_chunk_combine(epi, stage, m0 + q * 32, live_end, n0 + c * 32, N, r);
+          else if (epi.moe_mode == 1) { if (m < live_end) epilogue_row_swiglu(epi, m, n0 + c * 32, r); }
+          else if (red_path) epilogue_chunk_red(epi, stage, m0 + q * 32, n0 + c * 32, live_end, N, r, sp == 0);
+          else epilogue_row(epi, m, n0 + c * 32, live_end, N, r, sp == 0);
         }
       }
       tc_fence_before();
@@ -491,6 +564,7 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   }
   e.splitk_red = (splits > 1 && sym_mode == SYM_NONE) ? 1 : 0;
   e.transposed = swap ? 1 : 0;
+  e.group_rows = 0; e.group_n = 0; e.group_counts = nullptr; e.moe_mode = 0; e.meta = nullptr; e.gate_w = nullptr;
   if (sym_mode != SYM_NONE) {
     if (!sym || (ldc % 4) || (sym_off % 16)) return B200_ERR_BAD_ARG;
     e.sym = *sym;
@@ -503,4 +577,37 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
     case 64: return launch_gemm<64, 8>(ta, tb, e, M, N, K, splits, status, st);
   }
   return B200_ERR_BAD_ARG;
+}
+
+// Grouped GEMM of a mixture-of-experts layer (see GemmEpi).  A [groups * group_rows][K] bf16 (row
+// stride lda) holds each expert's gathered tokens, B [groups * N][K] bf16 its weights, counts[g] the
+// live rows of group g (device memory, final before this kernel starts).
+//   mode 1: B rows are interleaved (gate_0, up_0, gate_1, ...), N = 2 * ffn; out_bf16 [rows][ldc] gets
+//           silu(gate) * up, N / 2 columns per row.
+//   mode 2: N = d_model; row m is added, scaled by gate_w[m], into token meta[2m+1] of rank meta[2m]:
+//           fp32 [tokens][ldc] at byte offset sym_off of that rank's symmetric heap.  The kernel ends
+//           with the cross-rank barrier, so afterwards every rank's residual stream is complete.
+B200_API int b200_moe_gemm(const void* A, const void* B, int groups, int group_rows, int N, int K, int lda, int ldb,
+                           const int* counts, int mode, void* out_bf16, int ldc, const int* meta, const float* gate_w,
+                           const SymTable* sym, size_t sym_off, int* status, cudaStream_t st) {
+  if (groups <= 0 || group_rows <= 0 || group_rows % BM || N <= 0 || K <= 0 || (lda % 8) || (ldb % 8) || (K % 8) || (N % 4))
+    return B200_ERR_BAD_ARG;
+  if (mode == 1 ? (!out_bf16 || (ldc % 8) || (N % 32)) : (mode != 2 || !meta || !gate_w || !sym || (ldc % 4) || (sym_off % 16)))
+    return B200_ERR_BAD_ARG;
+  const int M = groups * group_rows;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tb, B, 2, (uint64_t)groups * N, (uint64_t)K, (uint64_t)ldb * 2, 128, BK, true);
+  if (rc) return rc;
+  GemmEpi e = {};
+  e.out_bf16 = (__nv_bfloat16*)out_bf16; e.ldc = ldc;
+  e.group_rows = group_rows; e.group_n = N; e.group_counts = counts; e.moe_mode = mode; e.meta = meta; e.gate_w = gate_w;
+  e.rows_per_rank = 1;
+  if (mode == 2) {
+    e.sym_mode = SYM_ALLREDUCE;   // only so that the kernel ends with the cross-rank barrier
+    e.sym = *sym;
+    e.sym_off = sym_off;
+  }
+  return launch_gemm<128, 6>(ta, tb, e, M, N, K, 1, status, st);
 }

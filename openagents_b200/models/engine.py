@@ -129,11 +129,13 @@ def _f32(src: WeightSource, name: str) -> torch.Tensor | None:
 
 
 class LlamaEngine:
+    ARCHS = ("llama",)
+
     def __init__(self, cfg: ModelConfig, src: WeightSource, device="cuda", max_batch: int = 64,
                  max_ctx: int = 4096, n_pages: int | None = None, tp_rank: int = 0, tp_world: int = 1,
                  max_tokens: int = 4096, comm=None):
-        if cfg.arch != "llama":
-            raise ValueError("LlamaEngine serves dense llama-family models")
+        if cfg.arch not in self.ARCHS:
+            raise ValueError(f"{type(self).__name__} serves {self.ARCHS} models, not {cfg.arch!r}")
         self.cfg, self.device = cfg, torch.device(device)
         self.rank, self.world, self.comm = tp_rank, tp_world, comm
         if cfg.n_kv_heads % tp_world or cfg.ffn % tp_world:
@@ -150,6 +152,7 @@ class LlamaEngine:
         self._alloc()
         self._graphs: dict[int, tuple] = {}
         self.launches_per_decode = 0
+        self.small_path_tokens = MATVEC_MAX_TOKENS      # up to this many decode tokens take the mat-vec path
 
     # ------------------------------------------------------------------ weights
     def _shard_rows(self, r: RawTensor, per_head_rows: int | None = None) -> RawTensor:
@@ -183,10 +186,7 @@ class LlamaEngine:
             sinks = _f32(src, p + "attn_sinks.weight")
             if sinks is not None and self.world > 1:
                 sinks = sinks[self.rank * self.Hq:(self.rank + 1) * self.Hq].contiguous()
-            g = self._shard_rows(src.get(p + "ffn_gate.weight"))
-            u = self._shard_rows(src.get(p + "ffn_up.weight"))
-            wgu = QWeight.from_raw(RawTensor.cat_rows([g, u]))
-            wdown = QWeight.from_raw(self._shard_cols(src.get(p + "ffn_down.weight")))
+            wgu, wdown = self._load_ffn(src, p, i)
             self.layers.append(_Layer(_f32(src, p + "attn_norm.weight"), wqkv, bqkv, wo, bo, sinks,
                                       _f32(src, p + "ffn_norm.weight"), wgu, wdown,
                                       cfg.sliding_window if cfg.layer_uses_window(i) else 0))
@@ -199,10 +199,15 @@ class LlamaEngine:
         self.wout = QWeight.from_raw(out)
         torch.cuda.synchronize(dev)
 
+    def _load_ffn(self, src: WeightSource, p: str, layer: int):
+        g = self._shard_rows(src.get(p + "ffn_gate.weight"))
+        u = self._shard_rows(src.get(p + "ffn_up.weight"))
+        return QWeight.from_raw(RawTensor.cat_rows([g, u])), QWeight.from_raw(self._shard_cols(src.get(p + "ffn_down.weight")))
+
     def weight_bytes(self) -> int:
         n = self.wout.nbytes()
         for l in self.layers:
-            n += l.wqkv.nbytes() + l.wo.nbytes() + l.wgu.nbytes() + l.wdown.nbytes()
+            n += l.wqkv.nbytes() + l.wo.nbytes() + (l.wgu.nbytes() + l.wdown.nbytes() if l.wgu is not None else 0)
         return n
 
     # ------------------------------------------------------------------ workspaces
@@ -247,7 +252,8 @@ class LlamaEngine:
         self.attn_counters = torch.zeros(self.max_batch * self.Hkv, dtype=torch.int32, device=dev)
         self.argmax_scratch = ops.argmax_scratch(self.max_batch, dev)
         self.rope_tab = ops.rope_table(self.max_pages * PAGE, self.hd, self.cfg.rope_theta, dev)
-        wmax = max(max(l.wqkv.N * l.wqkv.K, l.wgu.N * l.wgu.K, l.wo.N * l.wo.K, l.wdown.N * l.wdown.K) for l in self.layers)
+        wmax = max(max(l.wqkv.N * l.wqkv.K, l.wo.N * l.wo.K, *((l.wgu.N * l.wgu.K, l.wdown.N * l.wdown.K) if l.wgu is not None else ()))
+                   for l in self.layers)
         self._wscratch_elems = wmax
         self._wscratch = None
         self.use_shadow = True
@@ -356,16 +362,24 @@ class LlamaEngine:
                 self._gemm(hb_q, L.wo, T, out_f32=x, bias=L.bo, resid_f32=x, ldc=self.d)
             else:
                 self.comm.gemm_allreduce(hb_q, self._dense(L.wo), T, x, bias=L.bo, status=self.status)
-            ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, hb=hb_d)
+            ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, hb=hb_d, hf=self._ffn_hf(T))
             self._fence_reads()
-            self._gemm(hb_d, L.wgu, T, out_f32=gu)
-            ops.swiglu(gu, self.F, ob=hb_f)
-            if self.world == 1:
-                self._gemm(hb_f, L.wdown, T, out_f32=x, resid_f32=x, ldc=self.d)
-            else:
-                self.comm.gemm_allreduce(hb_f, self._dense(L.wdown), T, x, status=self.status)
-            n += 9
+            n += 6 + self._ffn_dense(li, L, T, x, hb_d, hb_f, gu)
         return n
+
+    def _ffn_hf(self, T: int):
+        """fp32 copy of the normalised hidden state, for feed-forward blocks that want one."""
+        return None
+
+    def _ffn_dense(self, li: int, L: _Layer, T: int, x, hb_d, hb_f, gu) -> int:
+        """Feed-forward block on ``hb_d`` (normalised hidden, bf16); adds its output into ``x``."""
+        self._gemm(hb_d, L.wgu, T, out_f32=gu)
+        ops.swiglu(gu, self.F, ob=hb_f)
+        if self.world == 1:
+            self._gemm(hb_f, L.wdown, T, out_f32=x, resid_f32=x, ldc=self.d)
+        else:
+            self.comm.gemm_allreduce(hb_f, self._dense(L.wdown), T, x, status=self.status)
+        return 3
 
     def _head(self, rows: torch.Tensor, nb: int, greedy: bool = True):
         """Final norm + LM head on ``nb`` rows of fp32 hidden state -> logits (and arg-max ids)."""
@@ -448,7 +462,7 @@ class LlamaEngine:
         self._embed(T)
         decode = all(n == 1 for n in q_len)
         pages = max((c + PAGE - 1) // PAGE for c in ctx)
-        if decode and T <= MATVEC_MAX_TOKENS:
+        if decode and T <= self.small_path_tokens:
             self._layers_small(T, pages)
         else:
             self._layers_dense(T, decode, B, max(q_len), pages)
@@ -469,7 +483,7 @@ class LlamaEngine:
         def body():
             self._embed(B)
             n = 1
-            if B <= MATVEC_MAX_TOKENS:
+            if B <= self.small_path_tokens:
                 n += self._layers_small(B, pages)
             else:
                 n += self._layers_dense(B, True, B, 1, pages)

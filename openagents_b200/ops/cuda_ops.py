@@ -37,6 +37,10 @@ _SIGS = {
     "b200_attn_prefill": [_P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
     "b200_gemm_bf16": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int,
                        _P, c_int, _P, c_size_t, c_int, _P],
+    "b200_moe_gemm": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P, c_int, _P, _P, _P, c_size_t, _P, _P],
+    "b200_moe_route_dispatch": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_size_t, c_size_t, c_size_t, c_size_t,
+                                _P, _P, _P, _P, _P],
+    "b200_moe_zero": [_P, c_int, _P],
     "b200_set_pdl": [c_int],
     "b200_set_prefetch": [c_int],
     "b200_dequant_bf16": [c_int, _P, _P, _P, c_size_t, c_int, _P],
@@ -208,3 +212,27 @@ def qgemm(w, x_bf16, T, y, ldy, bias=None, epi=QEPI_STORE, split_k=0, status=Non
     tiled, tiled2 = w.ensure_tiled()
     _check(lib().b200_qgemm(wt, _p(tiled), _p(tiled2), w.N, w.K, _p(x_bf16), x_bf16.stride(0), T, _p(y), ldy, _p(bias),
                             epi, split_k, _p(status), _p(dbg), _st()), "qgemm")
+
+
+# ---------------------------------------------------------------- mixture of experts
+def moe_route_dispatch(h_bf16, h_f32, router_w, router_b, top_k, E_local, C, recv_x_off, recv_meta_off, recv_w_off, counts_off,
+                       sym, topk_ids=None, topk_w=None, status=None):
+    """Router + top-k + softmax + expert-parallel dispatch of ``h_bf16`` [T][d] (see ``moe.cu``); the router
+    (fp32 weights) reads ``h_f32`` when given."""
+    T, d = h_bf16.shape
+    E = router_w.shape[0]
+    _check(lib().b200_moe_route_dispatch(_p(h_bf16), _p(h_f32), _p(router_w), _p(router_b), T, d, E, top_k, E_local, C, recv_x_off,
+                                         recv_meta_off, recv_w_off, counts_off, _p(topk_ids), _p(topk_w), _sym(sym),
+                                         _p(status), _st()), "moe_route_dispatch")
+
+
+def moe_gemm(A, B, groups, group_rows, N, K, counts, mode, out_bf16=None, ldc=0, meta=None, gate_w=None, sym=None,
+             sym_off=0, status=None, lda=None, ldb=None):
+    """Grouped expert GEMM (see ``gemm_tc05.cu``): mode 1 = gate/up with fused SwiGLU, mode 2 = down
+    projection fused with the weighted combine into the source ranks' residual streams."""
+    _check(lib().b200_moe_gemm(_p(A), _p(B), groups, group_rows, N, K, lda or K, ldb or K, _p(counts), mode, _p(out_bf16),
+                               ldc, _p(meta), _p(gate_w), _sym(sym), sym_off, _p(status), _st()), "moe_gemm")
+
+
+def moe_zero(t):
+    _check(lib().b200_moe_zero(_p(t), t.numel(), _st()), "moe_zero")
