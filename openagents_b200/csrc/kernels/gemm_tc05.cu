@@ -92,6 +92,7 @@ struct GemmEpi {
 enum { SYM_NONE = 0, SYM_ALLREDUCE = 1, SYM_RSCATTER = 2 };
 
 constexpr int BM = 128, BK = 64;
+constexpr int kMaxLiveTiles = 2048;   // grouped mode: 128-row tiles with live rows, listed in shared memory
 
 // Accumulating epilogues (fused collectives, split K) go through shared memory so that one warp
 // instruction adds 4 rows x 128 contiguous bytes instead of 32 rows x 16 bytes: reductions that
@@ -342,11 +343,14 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   uint32_t* tmem_holder = (uint32_t*)(bars + 2 * STAGES + 4);
   volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
   float* stage_all = (float*)(bars + 2 * STAGES + 6);   // 4 epilogue warps x 32 x 32 fp32, 16-byte aligned
+  int* live_m = (int*)(stage_all + 4 * 1024);            // grouped mode: first row of every live 128-row tile
+  __shared__ int s_n_live;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = (K + BK - 1) / BK;
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  const int n_tiles = tiles_m * tiles_n * splits;   // work items: (output tile, K split), split fastest
+  int tiles_m = (M + BM - 1) / BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  int n_tiles = tiles_m * tiles_n * splits;   // work items: (output tile, K split), split fastest
   const int kps = (KB + splits - 1) / splits;
 
   if (threadIdx.x == 0) {
@@ -376,19 +380,31 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   pdl_trigger();
   pdl_wait();
 
+  if (epi.group_rows) {
+    // Only the tiles that hold live rows are work items: list them once (the counts are final now).
+    if (threadIdx.x == 0) {
+      int n = 0;
+      const int groups = M / epi.group_rows;
+      for (int g = 0; g < groups; g++) {
+        const int cnt = min(epi.group_counts[g], epi.group_rows);
+        for (int r = 0; r < cnt && n < kMaxLiveTiles; r += BM) live_m[n++] = g * epi.group_rows + r;
+      }
+      s_n_live = n;
+    }
+    __syncthreads();
+    tiles_m = s_n_live;
+    n_tiles = tiles_m * tiles_n;
+  }
+
   if (warp == 0) {
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < n_tiles && ok; item += gridDim.x) {
         const int tile = item / splits, sp = item - tile * splits;
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        const int m0 = epi.group_rows ? live_m[tile % tiles_m] : (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
         int b_row = n0;
-        if (epi.group_rows) {
-          const int g = m0 / epi.group_rows;
-          if (m0 - g * epi.group_rows >= epi.group_counts[g]) continue;   // every role skips the same tiles
-          b_row += g * epi.group_n;
-        }
+        if (epi.group_rows) b_row += (m0 / epi.group_rows) * epi.group_n;
         const int kb0 = sp * kps, kb1 = min(KB, kb0 + kps);
         for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
@@ -407,10 +423,6 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       bool ok = true;
       for (int item = blockIdx.x; item < n_tiles && ok; item += gridDim.x) {
         const int tile = item / splits, sp = item - tile * splits;
-        if (epi.group_rows) {
-          const int m0 = (tile % tiles_m) * BM, g = m0 / epi.group_rows;
-          if (m0 - g * epi.group_rows >= epi.group_counts[g]) continue;
-        }
         const int kb0 = sp * kps, kb1 = min(KB, kb0 + kps);
         const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
         tcount++;
@@ -439,12 +451,11 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     uint32_t tcount = 0;
     for (int item = blockIdx.x; item < n_tiles; item += gridDim.x) {
       const int tile = item / splits, sp = item - tile * splits;
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int m0 = epi.group_rows ? live_m[tile % tiles_m] : (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
       int live_end = M;                       // rows below this index are written
       if (epi.group_rows) {
-        const int g = m0 / epi.group_rows, cnt = epi.group_counts[g];
-        if (m0 - g * epi.group_rows >= cnt) continue;
-        live_end = g * epi.group_rows + cnt;
+        const int g = m0 / epi.group_rows;
+        live_end = g * epi.group_rows + min(epi.group_counts[g], epi.group_rows);
       }
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
       tcount++;
@@ -491,7 +502,8 @@ static int sm_count() {
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpi& e, int M, int N, int K,
                        int splits, int* status, cudaStream_t st) {
-  constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 6) * 8 + 4 * 32 * 32 * 4;
+  constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 6) * 8 + 4 * 32 * 32 * 4 +
+                          kMaxLiveTiles * 4;
   auto kern = gemm_bf16_kernel<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
@@ -595,6 +607,7 @@ B200_API int b200_moe_gemm(const void* A, const void* B, int groups, int group_r
   if (mode == 1 ? (!out_bf16 || (ldc % 8) || (N % 32)) : (mode != 2 || !meta || !gate_w || !sym || (ldc % 4) || (sym_off % 16)))
     return B200_ERR_BAD_ARG;
   const int M = groups * group_rows;
+  if ((long)groups * (group_rows / BM) > kMaxLiveTiles) return B200_ERR_BAD_ARG;
   CUtensorMap ta, tb;
   int rc = make_tmap_2d(&ta, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK, true);
   if (rc) return rc;

@@ -6,7 +6,8 @@ Each case sets up one kernel on a problem that is larger than L2 but holds well 
 the device, launches it a few times and exits, so a capture with ``ncu -k regex:<kernel> -c 1`` ends
 by itself in seconds.  Cases: qgemm64, qgemm_lm, gemm, matvec, attn_decode, attn_prefill, and
 ``step64`` / ``step1``: whole decode steps (batch 64 / 1, context 2048) of a 4-layer Llama-3-8B-shape
-engine without graphs, for a per-kernel launch list.
+engine without graphs, for a per-kernel launch list; ``moe_step``: the same for a 2-layer gpt-oss-20b-shape
+expert engine at batch 256.
 """
 from __future__ import annotations
 
@@ -78,6 +79,23 @@ def main():
         for b in range(B):
             eng.begin(b)
             eng.forward_tokens([b], [torch.randint(0, cfg.vocab, (ctx,), generator=g).tolist()])
+        ids = list(range(B))
+        status = eng.status
+        fn = lambda: eng.decode(ids, [5] * B, use_graph=False)
+    elif case == "moe_step":
+        from ..models.config import GPT_OSS_20B
+        from ..models.moe_engine import MoEEngine
+        from ..models.qweight import RandomSource
+        from ..models.weights import PLAN_MOE
+        B, ctx = 256, 128
+        cfg = GPT_OSS_20B.with_(n_layers=2)
+        eng = MoEEngine(cfg, RandomSource(cfg, PLAN_MOE, 0, DEV), device=DEV, max_batch=B, max_ctx=ctx + 64, max_tokens=4096)
+        g = torch.Generator().manual_seed(1)
+        for b0 in range(0, B, 32):
+            ids = list(range(b0, b0 + 32))
+            for b in ids:
+                eng.begin(b)
+            eng.forward_tokens(ids, [torch.randint(0, cfg.vocab, (ctx,), generator=g).tolist() for _ in ids])
         ids = list(range(B))
         status = eng.status
         fn = lambda: eng.decode(ids, [5] * B, use_graph=False)
