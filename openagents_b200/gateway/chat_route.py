@@ -1,0 +1,207 @@
+"""The gateway's chat-completions route: the request path from an API key to a metered, receipted answer.
+
+Order of work for ``POST /v1/chat/completions`` (the reference's ``handleChatCompletions``,
+inference/chat-completions-routes.ts:2550, wired at index.ts:16272):
+
+1. authenticate the bearer key; 2. fair share: a key may hold only so many requests in flight;
+3. decode and validate the body; 4. model gating (the key's allowed models); 5. stable-first prompt
+layout and the cache-affinity hash; 6. lane plan from the router; 7. dispatch with overflow across the
+registered adapters; 8. re-frame the answer (JSON, or server-sent events for ``stream``); 9. meter the
+usage against the pricing table and the key's balance; 10. build the telemetry record and return the
+compact telemetry block on the response.
+
+Adapters here: ``LocalEngineAdapter`` answers from an in-process ``ServerState`` (this engine, whole-model
+lane) and produces the serving receipt with exact-greedy parity itself; the ``openagents-network`` adapter
+from ``fabric`` does the same over HTTP to a node.
+"""
+from __future__ import annotations
+
+import json
+import threading
+import time
+import uuid
+
+from . import prompt_cache as pc
+from . import request_telemetry as rt
+from .fabric import InferenceAdapterError, InferenceRequest, InferenceResult, InferenceUsage, ProviderRegistry, normalize_serve_response
+from .metadata import engine_quantization
+from .router import PricingTable, dispatch_with_overflow, select_adapter_plan
+
+
+class GatewayError(Exception):
+    def __init__(self, status: int, code: str, message: str):
+        super().__init__(message)
+        self.status, self.code, self.message = status, code, message
+
+    def body(self) -> dict:
+        return {"error": {"message": self.message, "type": self.code, "code": self.code}}
+
+
+class ApiKey:
+    def __init__(self, key: str, account: str, balance_msat: int = 0, allowed_models: tuple | None = None, max_inflight: int = 4,
+                 byok: dict | None = None):
+        self.key, self.account, self.balance_msat, self.allowed_models = key, account, balance_msat, allowed_models
+        self.max_inflight, self.inflight, self.byok = max_inflight, 0, byok or {}
+
+
+class LocalEngineAdapter:
+    """Serves from an in-process ``openagents_b200.serve.server.ServerState``."""
+
+    def __init__(self, state, adapter_id: str = "openagents-network", model_alias: dict | None = None):
+        self.id, self.state, self.alias = adapter_id, state, model_alias or {}
+
+    def complete(self, request: InferenceRequest):
+        try:
+            model = self.state.model(self.alias.get(request.model, request.model))
+        except KeyError:
+            raise InferenceAdapterError(self.id, "request_rejected", f"model {request.model!r} is not served here", False, 404)
+        greedy = float(request.passthrough_params.get("temperature") or 0.0) == 0.0
+        raw = self.state.serve_contract(model, {"messages": [dict(m) for m in request.messages],
+                                                "passthroughParams": dict(request.passthrough_params),
+                                                "requireExactGreedyParity": greedy})
+        serve = normalize_serve_response(raw)
+        if serve is None:
+            raise InferenceAdapterError(self.id, "malformed_response", "engine returned a malformed serve response")
+        if greedy and not serve["parityVerified"]:
+            raise InferenceAdapterError(self.id, "fabric_parity_unverified", "greedy decode was not reproducible")
+        result = InferenceResult(serve["content"], serve["finishReason"], serve["servedModel"], serve["usage"])
+        receipt = {k: serve[k] for k in ("servingRunRef", "servedModel", "stages", "parityMode", "parityVerified")}
+        receipt["sharded"] = len(serve["stages"]) > 1
+        return result, receipt
+
+
+class ChatGateway:
+    def __init__(self, registry: ProviderRegistry, keys: list[ApiKey], pricing: PricingTable | None = None, plan=None, now=time.time,
+                 sleep=lambda ms: None, default_price_msat_per_token: tuple[int, int] = (1, 4)):
+        self.registry, self.pricing, self.plan, self.now, self.sleep = registry, pricing, plan, now, sleep
+        self.keys = {k.key: k for k in keys}
+        self.default_price = default_price_msat_per_token
+        self.lock = threading.Lock()
+        self.telemetry: list[dict] = []
+
+    # ---- steps
+    def authenticate(self, authorization: str | None) -> ApiKey:
+        if not authorization or not authorization.lower().startswith("bearer "):
+            raise GatewayError(401, "missing_api_key", "send Authorization: Bearer <key>")
+        k = self.keys.get(authorization[7:].strip())
+        if k is None:
+            raise GatewayError(401, "invalid_api_key", "unknown API key")
+        return k
+
+    @staticmethod
+    def decode_body(body) -> dict:
+        if isinstance(body, (bytes, str)):
+            try:
+                body = json.loads(body)
+            except json.JSONDecodeError:
+                raise GatewayError(400, "invalid_json", "request body is not JSON")
+        if not isinstance(body, dict):
+            raise GatewayError(400, "invalid_request", "request body must be an object")
+        if not isinstance(body.get("model"), str) or not body["model"].strip():
+            raise GatewayError(400, "invalid_request", "model is required")
+        msgs = body.get("messages")
+        if not isinstance(msgs, list) or not msgs or not all(isinstance(m, dict) and isinstance(m.get("role"), str) and isinstance(m.get("content"), str) for m in msgs):
+            raise GatewayError(400, "invalid_request", "messages must be a non-empty list of {role, content}")
+        mt = body.get("max_tokens")
+        if mt is not None and not (isinstance(mt, int) and 1 <= mt <= 131072):
+            raise GatewayError(400, "invalid_request", "max_tokens out of range")
+        return body
+
+    def price_msat(self, model: str, usage: InferenceUsage) -> int:
+        e = self.pricing.lookup(model) if self.pricing else None
+        if e is not None:     # USD per million tokens -> msat at a fixed planning rate of 1 USD = 1,000,000 msat
+            return int(round(usage.prompt_tokens * e.input_usd_per_mtok + usage.completion_tokens * e.output_usd_per_mtok))
+        pi, po = self.default_price
+        return usage.prompt_tokens * pi + usage.completion_tokens * po
+
+    # ---- the route
+    def handle(self, authorization: str | None, body, session: str | None = None) -> tuple[int, dict | list[str]]:
+        """Returns (status, JSON object) or, for ``stream``, (200, list of SSE frames)."""
+        t0 = self.now()
+        try:
+            key = self.authenticate(authorization)
+            with self.lock:
+                if key.inflight >= key.max_inflight:
+                    raise GatewayError(429, "fair_share_exceeded", "too many requests in flight for this key")
+                key.inflight += 1
+            try:
+                return self._handle(key, body, session, t0)
+            finally:
+                with self.lock:
+                    key.inflight -= 1
+        except GatewayError as e:
+            return e.status, e.body()
+
+    def _handle(self, key: ApiKey, body, session, t0):
+        body = self.decode_body(body)
+        model = body["model"].strip()
+        if key.allowed_models is not None and model not in key.allowed_models:
+            raise GatewayError(403, "model_not_allowed", f"this key may not use {model!r}")
+        if key.balance_msat <= 0 and not key.byok:
+            raise GatewayError(402, "insufficient_balance", "the key has no balance")
+        layout = pc.assemble_stable_prompt_layout([(m, m.get("stable_kind")) for m in body["messages"]])
+        messages = tuple({"role": m["role"], "content": m["content"]} for m in layout["messages"])
+        affinity_raw = pc.derive_cache_affinity_key(key.account, session)
+        passthrough = {k: body[k] for k in ("max_tokens", "temperature", "top_p", "top_k", "stop", "seed") if k in body}
+        passthrough.update(pc.session_affinity_params(pc.hash_cache_affinity_key(affinity_raw)))
+        request = InferenceRequest(model, messages, bool(body.get("stream")), passthrough)
+        plan = self.plan(model) if self.plan else select_adapter_plan(model, self.pricing)
+        events = []
+        t_dispatch = self.now()
+        try:
+            d = dispatch_with_overflow(request, lambda a, r: a.complete(r), self.registry, plan=plan, sleep=self.sleep, telemetry=events.append)
+        except InferenceAdapterError as e:
+            status = e.http_status if e.http_status in (400, 404, 429) else (503 if e.retryable else 502)
+            raise GatewayError(status, e.kind, e.reason)
+        t_done = self.now()
+        out = d.value
+        result, receipt = out[0], out[1]
+        paid = out[2] if len(out) > 2 else None
+        price = self.price_msat(result.served_model if self.pricing and self.pricing.lookup(result.served_model) else model, result.usage)
+        if not key.byok:
+            with self.lock:
+                key.balance_msat -= price
+        rid = "chatcmpl-" + uuid.uuid4().hex[:24]
+        record = rt.build_record(
+            request_id=rid, requested_model=model, served_model=result.served_model, route=d.adapter_id, provider=d.adapter_id,
+            request_class="interactive_stream" if request.stream else "async_job", prompt_tokens=result.usage.prompt_tokens,
+            completion_tokens=result.usage.completion_tokens, total_tokens=result.usage.total_tokens,
+            cached_input_tokens=result.usage.cached_prompt_tokens, total_wall_clock_ms=(t_done - t0) * 1000,
+            provider_time_ms=(t_done - t_dispatch) * 1000, gateway_overhead_ms=(t_dispatch - t0) * 1000,
+            cache_affinity_key_raw=affinity_raw, fallback_reason=d.fallback_reason, price_msat=price,
+            verification_class="exact_trace_replay" if receipt.get("parityVerified") else "unverified",
+            executed_verdict="passed" if receipt.get("parityVerified") else "not_executed",
+            quantization=None, speculation={"mode": "none"}, settlement_state="not_applicable")
+        if d.adapter_id == "openagents-network":
+            record["quantization"] = engine_quantization("Q4_K") if "q4" in result.served_model.lower() else record["quantization"]
+        with self.lock:
+            self.telemetry.append(record)
+        usage = {"prompt_tokens": result.usage.prompt_tokens, "completion_tokens": result.usage.completion_tokens,
+                 "total_tokens": result.usage.total_tokens}
+        if result.usage.cached_prompt_tokens is not None:
+            usage["prompt_tokens_details"] = {"cached_tokens": result.usage.cached_prompt_tokens}
+        ext = {"telemetry": rt.block_from_record(record, f"telemetry.{rid}"), "receipt": receipt, "route": d.adapter_id,
+               "overflow_count": d.overflow_count, "stable_prefix_hash": layout["stablePrefixHash"], "price_msat": price,
+               "clears_paid_traffic": paid}
+        created = int(t_done)
+        if request.stream:
+            frames = []
+            head = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": result.served_model}
+            frames.append("data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}) + "\n\n")
+            text = result.content
+            for i in range(0, len(text), 16):        # the upstream answer is re-framed into OpenAI delta chunks
+                frames.append("data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {"content": text[i:i + 16]}, "finish_reason": None}]}) + "\n\n")
+            frames.append("data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {}, "finish_reason": result.finish_reason}], "usage": usage,
+                                                 "openagents": ext}) + "\n\n")
+            frames.append("data: [DONE]\n\n")
+            return 200, frames
+        return 200, {"id": rid, "object": "chat.completion", "created": created, "model": result.served_model,
+                     "choices": [{"index": 0, "message": {"role": "assistant", "content": result.content}, "finish_reason": result.finish_reason}],
+                     "usage": usage, "openagents": ext}
+
+    def models(self) -> dict:
+        return {"object": "list", "data": [{"id": i, "object": "model", "owned_by": "openagents"} for i in self.registry.ids()]}
+
+    def quote(self, model: str, prompt_tokens: int, max_tokens: int) -> dict:
+        """``/v1/quote``: worst-case price of a request."""
+        return {"model": model, "maxPriceMsat": self.price_msat(model, InferenceUsage(prompt_tokens, max_tokens, prompt_tokens + max_tokens))}

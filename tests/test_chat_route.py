@@ -1,0 +1,95 @@
+"""The gateway's chat-completions route end to end on CPU: key -> fair share -> plan -> overflow -> local engine -> metering -> telemetry."""
+import json
+
+import pytest
+
+from openagents_b200.gateway import chat_route as cr
+from openagents_b200.gateway import fabric as fb
+from openagents_b200.gateway import router as rt
+from openagents_b200.models.config import TINY_LLAMA
+from openagents_b200.models.weights import PLAN_Q8_0, random_weights, save_gguf
+from openagents_b200.receipts import manifests as mf
+from openagents_b200.serve.backend import CpuBackend
+from openagents_b200.serve.server import ServedModel, ServerState
+
+
+@pytest.fixture(scope="module")
+def state(tmp_path_factory):
+    cfg = TINY_LLAMA.with_(vocab=512, d_model=64, n_heads=2, n_kv_heads=1, head_dim=32, ffn=128)
+    p = str(tmp_path_factory.mktemp("m") / "tiny.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 0), PLAN_Q8_0)
+    return ServerState([ServedModel("tiny", CpuBackend.from_gguf(p), mf.artifact_digest(p), max_num_seqs=4)])
+
+
+class _Failing:
+    def __init__(self, id, err):
+        self.id, self.err, self.calls = id, err, 0
+
+    def complete(self, request):
+        self.calls += 1
+        raise self.err
+
+
+def _gateway(state, keys=None, fireworks_error=None):
+    reg = fb.ProviderRegistry()
+    fw = _Failing(rt.FIREWORKS, fireworks_error or fb.InferenceAdapterError(rt.FIREWORKS, "rate_limited", "429", True, 429))
+    reg.register(fw)
+    reg.register(cr.LocalEngineAdapter(state, model_alias={"qwen-tiny": "tiny"}))
+    keys = keys or [cr.ApiKey("k1", "acct1", balance_msat=10_000, max_inflight=1), cr.ApiKey("k2", "acct2", 10_000, allowed_models=("other",)),
+                    cr.ApiKey("k3", "acct3", 0)]
+    return cr.ChatGateway(reg, keys), fw
+
+
+BODY = {"model": "qwen-tiny", "messages": [{"role": "user", "content": "hello"}, {"role": "system", "content": "be brief"}], "max_tokens": 8}
+
+
+def test_route_overflows_to_local_engine_and_meters(state):
+    gw, fw = _gateway(state)
+    status, out = gw.handle("Bearer k1", json.dumps(BODY), session="s1")
+    assert status == 200 and out["object"] == "chat.completion" and out["choices"][0]["message"]["role"] == "assistant"
+    ext = out["openagents"]
+    assert fw.calls == 1 and ext["route"] == "openagents-network" and ext["overflow_count"] == 1
+    assert ext["receipt"]["parityVerified"] is True and ext["receipt"]["sharded"] is False
+    u = out["usage"]
+    assert u["completion_tokens"] == 8 and ext["price_msat"] == u["prompt_tokens"] * 1 + 8 * 4
+    assert gw.keys["k1"].balance_msat == 10_000 - ext["price_msat"] and gw.keys["k1"].inflight == 0
+    rec = gw.telemetry[-1]
+    assert rec["fallbackReason"] == "rate_limited" and rec["verificationClass"] == "exact_trace_replay" and rec["executedVerdict"] == "passed"
+    assert rec["cacheAffinityKeyHash"].startswith("cacheaff:fnv1a32:") and ext["telemetry"]["detailRef"].startswith("telemetry.chatcmpl-")
+    assert ext["stable_prefix_hash"].startswith("prefix:fnv1a32:")
+    # same request again: same content (greedy) and the stable prefix hash is unchanged
+    _, out2 = gw.handle("Bearer k1", BODY)
+    assert out2["choices"][0]["message"]["content"] == out["choices"][0]["message"]["content"]
+    assert out2["openagents"]["stable_prefix_hash"] == ext["stable_prefix_hash"]
+
+
+def test_stream_is_reframed_as_sse(state):
+    gw, _ = _gateway(state)
+    status, frames = gw.handle("Bearer k1", dict(BODY, stream=True))
+    assert status == 200 and frames[-1] == "data: [DONE]\n\n" and all(f.startswith("data: ") and f.endswith("\n\n") for f in frames)
+    chunks = [json.loads(f[6:]) for f in frames[:-1]]
+    assert chunks[0]["choices"][0]["delta"] == {"role": "assistant"} and chunks[-1]["choices"][0]["finish_reason"] in ("length", "stop")
+    text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks)
+    _, plain = gw.handle("Bearer k1", BODY)
+    assert text == plain["choices"][0]["message"]["content"] and chunks[-1]["usage"]["completion_tokens"] == 8
+
+
+def test_refusals(state):
+    gw, fw = _gateway(state)
+    assert gw.handle(None, BODY)[0] == 401 and gw.handle("Bearer nope", BODY)[1]["error"]["code"] == "invalid_api_key"
+    assert gw.handle("Bearer k2", BODY)[1]["error"]["code"] == "model_not_allowed"
+    assert gw.handle("Bearer k3", BODY)[0] == 402
+    assert gw.handle("Bearer k1", "{not json")[1]["error"]["code"] == "invalid_json"
+    assert gw.handle("Bearer k1", {"model": "qwen-tiny", "messages": []})[0] == 400
+    assert gw.handle("Bearer k1", dict(BODY, max_tokens=0))[0] == 400
+    gw.keys["k1"].inflight = 1
+    assert gw.handle("Bearer k1", BODY) == (429, {"error": {"message": "too many requests in flight for this key", "type": "fair_share_exceeded", "code": "fair_share_exceeded"}})
+    gw.keys["k1"].inflight = 0
+    # a non-retryable failure on the first lane surfaces instead of overflowing
+    gw2, fw2 = _gateway(state, fireworks_error=fb.InferenceAdapterError(rt.FIREWORKS, "request_rejected", "bad request", False, 400))
+    status, out = gw2.handle("Bearer k1", BODY)
+    assert status == 400 and out["error"]["code"] == "request_rejected" and gw2.keys["k1"].balance_msat == 10_000
+    # an unknown model on every lane
+    status, out = gw.handle("Bearer k1", dict(BODY, model="qwen-unknown"))
+    assert status in (404, 502, 503) and gw.keys["k1"].inflight == 0
+    assert gw.quote("qwen-tiny", 100, 50) == {"model": "qwen-tiny", "maxPriceMsat": 300} and rt.FIREWORKS in [m["id"] for m in gw.models()["data"]]
