@@ -213,13 +213,15 @@ def main():
         _, nxt = eng.decode(seqs, last)
         last = nxt.tolist()
     barrier()
+    h2d_before = eng.h2d_bytes
     t_start = time.perf_counter()
     for _ in range(K):
         _, nxt = eng.decode(seqs, last)
         last = nxt.tolist()                    # device -> host read of the step's result
     torch.cuda.synchronize()
     e2e_ms = max_over_ranks((time.perf_counter() - t_start) * 1e3) / K
-    h2d = 4 * (3 * B + 3 * B + B * eng.max_pages)     # ids, pos, slot, q_start, q_len, seq_lens, page table
+    h2d = (eng.h2d_bytes - h2d_before) // K        # counted by the engine from the tensors it copies: ids, pos, slot,
+                                                   # lengths every step, page-table rows when a sequence takes a new page
     d2h = 4 * B
     eng.check_status()
 

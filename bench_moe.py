@@ -120,6 +120,7 @@ def main():
         _, nxt = eng.decode(seqs, last)
         last = nxt.tolist()
     barrier()
+    h2d_before = eng.h2d_bytes
     t0 = time.perf_counter()
     for _ in range(K):
         _, nxt = eng.decode(seqs, last)
@@ -127,7 +128,8 @@ def main():
     torch.cuda.synchronize()
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1000) / K
     eng.check_status()
-    h2d = 4 * (3 * B + 3 * B) + B * eng.max_pages * 4
+    h2d = (eng.h2d_bytes - h2d_before) // K        # counted by the engine from the tensors it copies: ids, pos, slot,
+                                                   # lengths every step, page-table rows when a sequence takes a new page
     if rank == 0:
         print(json.dumps({
             "metric": "gpt_oss_20b_moe_decode_tok_s_bs256", "value": round(args.batch / dev_ms * 1000, 1), "unit": "tokens/s",

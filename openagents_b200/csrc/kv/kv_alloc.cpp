@@ -157,6 +157,48 @@ int32_t b200_kv_seq_pages(void* h, int64_t seq_id, int32_t* out, int32_t cap) {
   std::memcpy(out, pg.data(), sizeof(int32_t) * (size_t)(n < cap ? n : cap));
   return n;
 }
+// One decode step for a whole batch in a single call: every sequence grows by one token and the
+// per-sequence launch metadata is written straight into the caller's (pinned) staging arrays:
+// pos[b] = position of the new token, slot[b] = its physical cache slot, ctx[b] = new length,
+// table[b][0..max_pages) = page list (rows are rewritten only when `full_table` is set or the
+// sequence just took a new page).  Returns 0, or -1 unknown sequence / -2 out of pages / -3 sequence
+// longer than max_pages pages (with nothing changed for the failing and later sequences);
+// *table_dirty is set when any table row was written.
+int32_t b200_kv_stage_decode(void* h, const int64_t* seq_ids, int32_t B, int32_t max_pages, int32_t full_table,
+                             int32_t* pos, int32_t* slot, int32_t* ctx, int32_t* table, int32_t* table_dirty) {
+  Pool* p = (Pool*)h;
+  const int64_t ps = p->page_size;
+  int32_t dirty = 0;
+  for (int32_t b = 0; b < B; b++) {
+    auto it = p->seqs.find(seq_ids[b]);
+    if (it == p->seqs.end()) return -1;
+    Seq& s = it->second;
+    const int64_t p0 = s.n_tokens;
+    const bool new_page = (p0 + 1 + ps - 1) / ps > (int64_t)s.pages.size();
+    if (new_page) {
+      if ((int64_t)s.pages.size() + 1 > max_pages) return -3;
+      if (p->free_list.empty()) return -2;
+      int32_t pg = p->free_list.back();
+      p->free_list.pop_back();
+      p->refcnt[pg] = 1;
+      s.pages.push_back(pg);
+    }
+    if ((int64_t)s.pages.size() > max_pages) return -3;
+    s.n_tokens = p0 + 1;
+    pos[b] = (int32_t)p0;
+    slot[b] = (int32_t)(s.pages[p0 / ps] * ps + p0 % ps);
+    ctx[b] = (int32_t)(p0 + 1);
+    if (full_table || new_page) {
+      int32_t* row = table + (size_t)b * max_pages;
+      std::memcpy(row, s.pages.data(), sizeof(int32_t) * s.pages.size());
+      std::memset(row + s.pages.size(), 0, sizeof(int32_t) * (size_t)(max_pages - (int64_t)s.pages.size()));
+      dirty = 1;
+    }
+  }
+  *table_dirty = dirty;
+  return 0;
+}
+
 // Drop the last n tokens (a rejected speculative tail or a cancelled turn).
 int32_t b200_kv_seq_truncate(void* h, int64_t seq_id, int64_t new_len) {
   Pool* p = (Pool*)h;

@@ -40,7 +40,8 @@ class KVPool:
                    "b200_kv_seq_begin": ([vp, i64, P32, i64], i64), "b200_kv_seq_extend": ([vp, i64, i64], i32),
                    "b200_kv_seq_publish": ([vp, i64, P32, i64], None), "b200_kv_seq_len": ([vp, i64], i64),
                    "b200_kv_seq_n_pages": ([vp, i64], i32), "b200_kv_seq_pages": ([vp, i64, P32, i32], i32),
-                   "b200_kv_seq_truncate": ([vp, i64, i64], i32), "b200_kv_seq_end": ([vp, i64], None)}
+                   "b200_kv_seq_truncate": ([vp, i64, i64], i32), "b200_kv_seq_end": ([vp, i64], None),
+                   "b200_kv_stage_decode": ([vp, vp, i32, i32, i32, vp, vp, vp, vp, vp], i32)}
             for n, (a, r) in sig.items():
                 f = getattr(L, n)
                 f.argtypes, f.restype = a, r
@@ -85,6 +86,21 @@ class KVPool:
         buf = (ctypes.c_int32 * max(n, 1))()
         self.L.b200_kv_seq_pages(self.h, seq_id, buf, n)
         return list(buf[:n])
+
+    def stage_decode(self, seq_ids_ptr: int, B: int, max_pages: int, full_table: bool, pos_ptr: int, slot_ptr: int, ctx_ptr: int,
+                     table_ptr: int) -> bool:
+        """Grow ``B`` sequences by one token and fill the staging arrays (raw host pointers); returns
+        whether any page-table row was rewritten."""
+        dirty = ctypes.c_int32(0)
+        r = self.L.b200_kv_stage_decode(self.h, seq_ids_ptr, B, max_pages, int(full_table), pos_ptr, slot_ptr, ctx_ptr, table_ptr,
+                                        ctypes.addressof(dirty))
+        if r == -1:
+            raise KeyError("unknown sequence in the decode batch")
+        if r == -2:
+            raise MemoryError("KV cache is out of pages")
+        if r == -3:
+            raise ValueError("sequence exceeds the engine's max context")
+        return bool(dirty.value)
 
     def truncate(self, seq_id: int, new_len: int):
         if self.L.b200_kv_seq_truncate(self.h, seq_id, new_len) != 0:
@@ -153,6 +169,7 @@ class LlamaEngine:
         self._graphs: dict[int, tuple] = {}
         self.launches_per_decode = 0
         self.small_path_tokens = MATVEC_MAX_TOKENS      # up to this many decode tokens take the mat-vec path
+        self.h2d_bytes = 0                              # host-to-device bytes copied by decode() so far
 
     # ------------------------------------------------------------------ weights
     def _shard_rows(self, r: RawTensor, per_head_rows: int | None = None) -> RawTensor:
@@ -431,6 +448,8 @@ class LlamaEngine:
 
     def _upload(self, ids, pos, slot, q_start, q_len, ctx, table):
         T, B = len(ids), len(ctx)
+        if getattr(self, "_stg", None) is not None:
+            self._stg["last_batch"] = None        # the decode fast path must resend its page-table rows
         pin = lambda v: torch.tensor(v, dtype=torch.int32).pin_memory()
         self.ids[:T].copy_(pin(ids), non_blocking=True)
         self.pos[:T].copy_(pin(pos), non_blocking=True)
@@ -508,23 +527,55 @@ class LlamaEngine:
             n = body()
         return g, n
 
+    def _decode_staging(self):
+        """Pinned host staging for decode steps, allocated once: per-step metadata goes from the page
+        allocator (one native call for the whole batch) into these arrays and from there to the device
+        in four small asynchronous copies; the page table moves only when a sequence took a new page
+        or the batch changed."""
+        if getattr(self, "_stg", None) is None:
+            B, P = self.max_batch, self.max_pages
+            pin = lambda *shape, dt=torch.int32: torch.zeros(shape, dtype=dt).pin_memory() if torch.cuda.is_available() else torch.zeros(shape, dtype=dt)
+            self._stg = {"seq": pin(B, dt=torch.int64), "ids": pin(B), "pos": pin(B), "slot": pin(B), "ctx": pin(B), "table": pin(B, P),
+                         "out": pin(B), "last_batch": None}
+        return self._stg
+
     @torch.no_grad()
     def decode(self, seq_ids: list[int], tokens: list[int], use_graph: bool = True):
         """One decode step: append one token per sequence, return (logits view, arg-max ids)."""
         if not use_graph:
             return self.forward_tokens(seq_ids, [[t] for t in tokens])
         B = len(seq_ids)
-        staged = self._stage_batch(seq_ids, [[t] for t in tokens])
-        ctx = staged[5]
-        pages = max((c + PAGE - 1) // PAGE for c in ctx)
+        if B > self.max_batch:
+            raise ValueError("batch exceeds the engine's workspace")
+        st = self._decode_staging()
+        batch = tuple(seq_ids)
+        same = st["last_batch"] == batch
+        if not same:
+            st["seq"][:B] = torch.tensor(seq_ids, dtype=torch.int64)
+        st["ids"][:B] = torch.tensor(tokens, dtype=torch.int32)
+        dirty = self.pool.stage_decode(st["seq"].data_ptr(), B, self.max_pages, not same, st["pos"].data_ptr(), st["slot"].data_ptr(),
+                                       st["ctx"].data_ptr(), st["table"].data_ptr())
+        st["last_batch"] = batch
+        pages = (int(st["ctx"][:B].max()) + PAGE - 1) // PAGE
         # Split count is baked into the captured launch; bucket the context length so a graph is
         # reused while the sequence grows.
         bucket = 1 << max(0, (pages - 1)).bit_length()
         key = (B, bucket)
+
+        def upload():
+            self.ids[:B].copy_(st["ids"][:B], non_blocking=True)
+            self.pos[:B].copy_(st["pos"][:B], non_blocking=True)
+            self.slot[:B].copy_(st["slot"][:B], non_blocking=True)
+            self.seq_lens[:B].copy_(st["ctx"][:B], non_blocking=True)
+            self.h2d_bytes += 16 * B
+            if dirty or not same:     # otherwise the device rows are still those of the previous step
+                self.page_table[:B].copy_(st["table"][:B], non_blocking=True)
+                self.h2d_bytes += 4 * B * self.max_pages
+
         if key not in self._graphs:
-            self._upload(*staged)
+            upload()
             self._graphs[key] = self._capture(B, bucket)
-        self._upload(*staged)
+        upload()
         g, n = self._graphs[key]
         g.replay()
         self.launches_per_decode = n

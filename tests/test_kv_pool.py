@@ -49,3 +49,30 @@ def test_prefix_sharing():
     p.end(3)
     assert p.free_pages == 16
     assert p.begin(4, toks) == 0             # nothing cached once every owner is gone
+
+
+def test_stage_decode_batch():
+    """One native call grows a whole decode batch and fills the launch metadata."""
+    import torch
+    from openagents_b200.models.engine import KVPool
+    pool = KVPool(64)
+    for sid, n in ((7, 15), (9, 33)):
+        pool.begin(sid)
+        pool.extend(sid, n)
+    seq = torch.tensor([7, 9], dtype=torch.int64)
+    pos, slot, ctx = (torch.zeros(2, dtype=torch.int32) for _ in range(3))
+    table = torch.full((2, 8), -1, dtype=torch.int32)
+    args = (seq.data_ptr(), 2, 8)
+    ptrs = (pos.data_ptr(), slot.data_ptr(), ctx.data_ptr(), table.data_ptr())
+    assert pool.stage_decode(*args, True, *ptrs) is True
+    assert pos.tolist() == [15, 33] and ctx.tolist() == [16, 34]
+    assert table[0].tolist() == pool.pages(7) + [0] * 7 and table[1, :3].tolist() == pool.pages(9)
+    assert slot.tolist() == [pool.pages(7)[0] * 16 + 15, pool.pages(9)[2] * 16 + 1]
+    assert pool.stage_decode(*args, False, *ptrs) is True          # sequence 7 crossed into a new page
+    assert len(pool.pages(7)) == 2 and table[0, :2].tolist() == pool.pages(7) and slot[0].item() == pool.pages(7)[1] * 16
+    assert pool.stage_decode(*args, False, *ptrs) is False and pool.length(7) == 18
+    import pytest
+    with pytest.raises(KeyError):
+        pool.stage_decode(torch.tensor([1234], dtype=torch.int64).data_ptr(), 1, 8, True, *ptrs)
+    with pytest.raises(ValueError):
+        pool.stage_decode(*args[:2], 1, True, *ptrs)
