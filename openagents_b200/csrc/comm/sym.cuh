@@ -164,10 +164,60 @@ __device__ __forceinline__ bool sym_barrier_thread(const SymTable& T, int ch) {
   return ok;
 }
 
+// ---- "ready" handshake ---------------------------------------------------------------------
+// A kernel that adds into a tensor of every rank (a fused all-reduce) may only start adding once every
+// rank has finished reading that tensor's previous contents.  Instead of a stand-alone barrier
+// launch between reader and writer, the READER signals when it is done (sym_signal_ready, no wait) and
+// the WRITER checks the signals just before its first remote add (sym_wait_ready), by which time they
+// have normally long arrived.  One signal per rank per phase; the writer's last CTA closes the phase
+// (see sym_kernel_end_barrier).  Channel kSymReadyCh of the control block is reserved for this.
+constexpr int kSymReadyCh = 4;
+
+// Call from every thread of every CTA at the end of the reading kernel.
+__device__ __forceinline__ void sym_signal_ready(const SymTable& T, int n_ctas) {
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    SymControl* me = sym_ctl(T, T.rank);
+    const int done = atomicAdd(&me->ticket[kSymReadyCh], 1);
+    if (done == n_ctas - 1) {
+      me->ticket[kSymReadyCh] = 0;
+      __threadfence_system();
+      if (T.use_mc) {
+        asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(T.mc_base + offsetof(SymControl, flag) + 4 * kSymReadyCh),
+                     "r"(1u) : "memory");
+      } else {
+        for (int p = 0; p < T.world; p++)
+          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(&sym_ctl(T, p)->flag[kSymReadyCh]), "r"(1u) : "memory");
+      }
+    }
+  }
+}
+
+// One thread: wait until every rank has signalled the current phase.  Returns false (and records the
+// time-out) if the wait ran out; the caller goes on either way, as after a timed-out barrier.
+__device__ __forceinline__ bool sym_wait_ready(const SymTable& T) {
+  SymControl* me = sym_ctl(T, T.rank);
+  const int e = *(volatile int*)&me->epoch[kSymReadyCh];
+  const uint32_t target = (uint32_t)T.world * (uint32_t)(e + 1);
+  const unsigned long long t0 = sym_now_ns();
+  for (uint32_t spin = 0;; ++spin) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(&me->flag[kSymReadyCh]) : "memory");
+    if ((int32_t)(v - target) >= 0) return true;
+    if ((spin & 63u) == 63u && sym_now_ns() - t0 > T.wait_ns) {
+      me->status = (int)B200_ERR_TIMEOUT_PEER;
+      atomicAdd(&me->timeouts, 1);
+      return false;
+    }
+  }
+}
+
 // Call from every thread of every CTA at the end of a kernel that pushed data to peers: the CTA that
 // finishes last runs the cross-rank barrier, so when the kernel completes, every rank's pushes have
-// landed everywhere.  No CTA waits for another CTA.
-__device__ __forceinline__ void sym_kernel_end_barrier(const SymTable& T, int ch, int n_ctas) {
+// landed everywhere.  No CTA waits for another CTA.  `close_ready_phase`: this kernel consumed one
+// phase of the ready handshake (every CTA has read the phase number by now).
+__device__ __forceinline__ void sym_kernel_end_barrier(const SymTable& T, int ch, int n_ctas, bool close_ready_phase = false) {
   __shared__ int s_is_last;
   __threadfence_system();
   __syncthreads();
@@ -177,6 +227,7 @@ __device__ __forceinline__ void sym_kernel_end_barrier(const SymTable& T, int ch
     s_is_last = (done == n_ctas - 1);
     if (s_is_last) {
       me->ticket[ch] = 0;
+      if (close_ready_phase) me->epoch[kSymReadyCh] += 1;
       __threadfence();
       sym_barrier_thread(T, ch);
     }

@@ -3,7 +3,7 @@
 // sampling.  The math follows the reference CPU workload
 // (apps/openagents.com/workers/api/src/cs336-a1-real-gradient-workload.ts:351-375 RMSNorm,
 // :532-549 SwiGLU, cs336-a2-benchmark-workload.ts:212-249 greedy arg-max decode).
-#include "common.cuh"
+#include "../comm/sym.cuh"
 
 using namespace b200;
 
@@ -94,7 +94,7 @@ constexpr int kRmsRegs = 8;
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ g, float eps,
                                                        int D, int8_t* __restrict__ xq, float* __restrict__ xd,
                                                        float* __restrict__ xs16, __nv_bfloat16* __restrict__ hb,
-                                                       float* __restrict__ hf) {
+                                                       float* __restrict__ hf, const SymTable sym, int signal_ready) {
   __shared__ float red[32];
   const int t = blockIdx.x;
   const float* xr = x + (size_t)t * D;
@@ -144,14 +144,19 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
       quantize_block32(o, lane, xq + (size_t)t * D + blk * 32, xd + (size_t)t * (D / 32) + blk,
                        xs16 + (size_t)t * (D / 16) + blk * 2);
   }
+  // Tensor parallel: x is replicated and peers add into it from their row-parallel kernels; tell them
+  // this rank has finished reading the values it needed.
+  if (signal_ready) sym_signal_ready(sym, gridDim.x);
 }
 
+// sym non-null: x lives in the symmetric heap and the next row-parallel kernel of every rank will add
+// into it; this kernel then ends by signalling that this rank has read x (see sym.cuh).
 B200_API int b200_rmsnorm(const float* x, const float* g, float eps, int T, int D, void* xq, float* xd,
-                          float* xs16, void* hb, float* hf, cudaStream_t st) {
+                          float* xs16, void* hb, float* hf, const SymTable* sym, cudaStream_t st) {
   if (D % 32) return B200_ERR_BAD_ARG;
   const int threads = D >= 4096 ? 1024 : D >= 1024 ? 512 : 256;
   return launch_pdl(rmsnorm_kernel, dim3(T), dim3(threads), 0, st, x, g, eps, D, (int8_t*)xq, xd, xs16,
-                    (__nv_bfloat16*)hb, hf);
+                    (__nv_bfloat16*)hb, hf, sym ? *sym : SymTable{}, sym ? 1 : 0);
 }
 
 // Plain activation quantization of fp32 rows (used where no norm precedes a quantized matvec).

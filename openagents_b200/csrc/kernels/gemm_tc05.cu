@@ -79,6 +79,7 @@ struct GemmEpi {
   int moe_mode;
   const int* meta;
   const float* gate_w;
+  int wait_ready;            // fused all-reduce: check the peers' "finished reading" signals before the first add
   // Fused collective epilogue (tensor-parallel row-parallel GEMMs): instead of storing, add the tile
   // into an fp32 tensor [*, ldc] at byte offset sym_off of the symmetric heap.
   //   SYM_ALLREDUCE : into every rank's replica (multimem.red through the switch where available)
@@ -448,6 +449,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     const int q = warp & 3;
     float* stage = stage_all + q * 1024;
     const bool red_path = !epi.transposed && (epi.sym_mode != SYM_NONE || epi.splitk_red);
+    bool ready_checked = !(epi.sym_mode != SYM_NONE && epi.wait_ready);
     uint32_t tcount = 0;
     for (int item = blockIdx.x; item < n_tiles; item += gridDim.x) {
       const int tile = item / splits, sp = item - tile * splits;
@@ -463,6 +465,11 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       ok = __all_sync(0xffffffffu, ok && !*abort_flag);  // tcgen05.ld needs the whole warp
       if (!ok) break;
       tc_fence_after();
+      if (!ready_checked) {          // once per warp, before its first remote add
+        if (lane == 0) sym_wait_ready(epi.sym);
+        __syncwarp();
+        ready_checked = true;
+      }
       const int m = m0 + q * 32 + lane;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
@@ -485,7 +492,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
   if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, (int)B200_ERR_TIMEOUT_MMA);
-  if (epi.sym_mode != SYM_NONE) sym_kernel_end_barrier(epi.sym, 0, gridDim.x);
+  if (epi.sym_mode != SYM_NONE) sym_kernel_end_barrier(epi.sym, 0, gridDim.x, epi.wait_ready != 0);
 }
 
 static int sm_count() {
@@ -522,7 +529,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmE
 B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, int lda, int ldb, float* out_f32,
                             void* out_bf16, int ldc, const float* bias, const float* resid_f32,
                             const void* resid_bf16, int act, int accumulate, int tile_n, int split_k, int* status,
-                            int sym_mode, const SymTable* sym, size_t sym_off, int rows_per_rank,
+                            int sym_mode, const SymTable* sym, size_t sym_off, int rows_per_rank, int wait_ready,
                             cudaStream_t st) {
   if (M <= 0 || N <= 0 || K <= 0 || (lda % 8) || (ldb % 8) || (K % 8)) return B200_ERR_BAD_ARG;
   if ((out_bf16 && (ldc % 8)) || (out_f32 && (ldc % 4))) return B200_ERR_BAD_ARG;
@@ -577,6 +584,7 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   e.splitk_red = (splits > 1 && sym_mode == SYM_NONE) ? 1 : 0;
   e.transposed = swap ? 1 : 0;
   e.group_rows = 0; e.group_n = 0; e.group_counts = nullptr; e.moe_mode = 0; e.meta = nullptr; e.gate_w = nullptr;
+  e.wait_ready = (sym_mode != SYM_NONE) ? wait_ready : 0;
   if (sym_mode != SYM_NONE) {
     if (!sym || (ldc % 4) || (sym_off % 16)) return B200_ERR_BAD_ARG;
     e.sym = *sym;

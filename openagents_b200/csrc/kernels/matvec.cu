@@ -38,6 +38,7 @@ struct MatvecArgs {
   SymTable sym;
   size_t sym_off;
   int prefetch;         // bring this CTA's weight rows into L2 before waiting for the previous kernel
+  int wait_ready;       // EPI_ALLREDUCE: check the peers' "finished reading" signals before the first add
 };
 
 __device__ __forceinline__ int dp4a(uint32_t a, uint32_t b, int c) {
@@ -300,9 +301,10 @@ __global__ void __launch_bounds__(256) matvec_q_kernel(const MatvecArgs a) {
       }
     }
   }
+  if (a.epi == EPI_ALLREDUCE && a.wait_ready && threadIdx.x == 0) sym_wait_ready(a.sym);
   __syncthreads();
   matvec_epilogue<B, R>(a, res, DUAL);
-  if (a.epi == EPI_ALLREDUCE) sym_kernel_end_barrier(a.sym, 0, gridDim.x);
+  if (a.epi == EPI_ALLREDUCE) sym_kernel_end_barrier(a.sym, 0, gridDim.x, a.wait_ready != 0);
 }
 
 // bf16 weights [N][K] against fp32 activations.
@@ -365,9 +367,10 @@ __global__ void __launch_bounds__(256) matvec_bf16_kernel(const MatvecArgs a) {
       }
     }
   }
+  if (a.epi == EPI_ALLREDUCE && a.wait_ready && threadIdx.x == 0) sym_wait_ready(a.sym);
   __syncthreads();
   matvec_epilogue<B>(a, res, DUAL);
-  if (a.epi == EPI_ALLREDUCE) sym_kernel_end_barrier(a.sym, 0, gridDim.x);
+  if (a.epi == EPI_ALLREDUCE) sym_kernel_end_barrier(a.sym, 0, gridDim.x, a.wait_ready != 0);
 }
 
 template <int WT, int B, bool DUAL, int RW>
@@ -418,7 +421,7 @@ static int dispatch_wt(int wt, const MatvecArgs& a, cudaStream_t st) {
 B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, int nb, const void* xq,
                          const float* xd, const float* xs16, const float* xf, int epi, const float* bias,
                          const float* resid, float* y, int ldy, void* oq, float* od, float* os16,
-                         const SymTable* sym, size_t sym_off, cudaStream_t st) {
+                         const SymTable* sym, size_t sym_off, int wait_ready, cudaStream_t st) {
   if (nb < 1 || nb > 8) return B200_ERR_BAD_ARG;
   if (wt == WT_BF16 ? (K % 8 != 0) : (K % 256 != 0 && !(wt == WT_Q8R && K % 32 == 0))) return B200_ERR_BAD_ARG;
   if (epi == EPI_SWIGLU_Q8 && N % 32) return B200_ERR_BAD_ARG;
@@ -435,6 +438,7 @@ B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, in
     a.sym_off = 0;
   }
   a.prefetch = b200_prefetch_enabled();
+  a.wait_ready = wait_ready;
   const bool dual = epi == EPI_SWIGLU_Q8 || epi == EPI_SWIGLU_F32;
   const int B = nb <= 1 ? 1 : nb <= 2 ? 2 : nb <= 4 ? 4 : 8;
   if (dual) {

@@ -12,6 +12,7 @@ KV and prefix caches, continuous batching (docs/muse/muse-glimmer.md:110-126).
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from dataclasses import dataclass
 
@@ -154,6 +155,7 @@ class LlamaEngine:
             raise ValueError(f"{type(self).__name__} serves {self.ARCHS} models, not {cfg.arch!r}")
         self.cfg, self.device = cfg, torch.device(device)
         self.rank, self.world, self.comm = tp_rank, tp_world, comm
+        self._use_fence = os.environ.get("B200_TP_FENCE", "0") == "1"
         if cfg.n_kv_heads % tp_world or cfg.ffn % tp_world:
             raise ValueError("tensor-parallel degree must divide the KV heads and the FFN width")
         self.Hq, self.Hkv, self.hd = cfg.n_heads // tp_world, cfg.n_kv_heads // tp_world, cfg.head_dim
@@ -291,12 +293,16 @@ class LlamaEngine:
         want = max(1, (2 * 148 + B * self.Hkv - 1) // (B * self.Hkv))
         return max(1, min(self.max_splits, want, ctx_pages))
 
-    def _fence_reads(self):
-        """Tensor-parallel only: peers add into this rank's residual stream from inside their
-        kernels, so every rank must have finished reading (or overwriting) it before anyone starts
-        the next row-parallel projection."""
-        if self.world > 1:
+    @property
+    def _sig(self):
+        """Tensor-parallel only: peers add into this rank's residual stream from inside their row-parallel
+        kernels, so every rank must have finished reading (or overwriting) it before anyone adds.  The
+        RMSNorm that reads it signals when it is done and the row-parallel kernels check the signals just
+        before their first remote add: a handshake inside kernels that run anyway, not a barrier launch."""
+        if self.world > 1 and self._use_fence:      # measurement aid: the stand-alone barrier the handshake replaces
             self.comm.heap.barrier(ch=2)
+            return None
+        return self.comm.heap.table if self.world > 1 else None
 
     def _layers_small(self, nb: int, max_ctx_pages: int):
         """<= 8 tokens, one per sequence: quantized mat-vec path."""
@@ -308,8 +314,7 @@ class LlamaEngine:
         for li, L in enumerate(self.layers):
             q8 = L.wqkv.quantized
             ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, xq=self.xq if q8 else None, xd=self.xd, xs16=self.xs,
-                        hf=None if q8 else self.xf)
-            self._fence_reads()
+                        hf=None if q8 else self.xf, signal_sym=self._sig)
             ops.matvec(L.wqkv.wt, L.wqkv.main, L.wqkv.plane2, L.wqkv.N, L.wqkv.K, nb, xq=self.xq, xd=self.xd,
                        xs16=self.xs, xf=self.xf, epi=ops.EPI_STORE, bias=L.bqkv, y=self.qkv, ldy=self.qkv_dim)
             ops.rope_kv(self.qkv[:nb], self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv,
@@ -323,11 +328,10 @@ class LlamaEngine:
                 ops.matvec(L.wo.wt, L.wo.main, L.wo.plane2, L.wo.N, L.wo.K, nb, xq=self.xq, xd=self.xd, xs16=self.xs,
                            xf=self.xf, epi=ops.EPI_RESID, bias=L.bo, resid=x, y=x, ldy=self.d)
             else:
-                self.comm.matvec_allreduce(L.wo, nb, self.xq, self.xd, self.xs, self.xf, x, self.d, bias=L.bo)
+                self.comm.matvec_allreduce(L.wo, nb, self.xq, self.xd, self.xs, self.xf, x, self.d, bias=L.bo, wait_ready=not self._use_fence)
             g8 = L.wgu.quantized
             ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, xq=self.xq if g8 else None, xd=self.xd, xs16=self.xs,
-                        hf=None if g8 else self.xf)
-            self._fence_reads()
+                        hf=None if g8 else self.xf, signal_sym=self._sig)
             d8 = L.wdown.quantized and self.F % 32 == 0
             ops.matvec(L.wgu.wt, L.wgu.main, L.wgu.plane2, self.F, L.wgu.K, nb, xq=self.xq, xd=self.xd, xs16=self.xs,
                        xf=self.xf, epi=ops.EPI_SWIGLU_Q8 if d8 else ops.EPI_SWIGLU_F32, y=self.gu, ldy=self.F,
@@ -339,7 +343,7 @@ class LlamaEngine:
                 ops.matvec(L.wdown.wt, L.wdown.main, L.wdown.plane2, L.wdown.N, L.wdown.K, nb, xq=self.fq, xd=self.fd,
                            xs16=self.fs, xf=self.gu, epi=ops.EPI_RESID, resid=x, y=x, ldy=self.d)
             else:
-                self.comm.matvec_allreduce(L.wdown, nb, self.fq, self.fd, self.fs, self.gu, x, self.d)
+                self.comm.matvec_allreduce(L.wdown, nb, self.fq, self.fd, self.fs, self.gu, x, self.d, wait_ready=not self._use_fence)
             n += 8
         return n
 
@@ -360,8 +364,7 @@ class LlamaEngine:
         S = self._splits(n_seqs, max_ctx_pages) if decode else 1
         n = 0
         for li, L in enumerate(self.layers):
-            ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, hb=hb_d)
-            self._fence_reads()
+            ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, hb=hb_d, signal_sym=self._sig)
             self._gemm(hb_d, L.wqkv, T, out_f32=qkv, bias=L.bqkv)
             if decode:
                 ops.rope_kv(qkv, self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv, self.hd,
@@ -378,9 +381,8 @@ class LlamaEngine:
             if self.world == 1:
                 self._gemm(hb_q, L.wo, T, out_f32=x, bias=L.bo, resid_f32=x, ldc=self.d)
             else:
-                self.comm.gemm_allreduce(hb_q, self._dense(L.wo), T, x, bias=L.bo, status=self.status)
-            ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, hb=hb_d, hf=self._ffn_hf(T))
-            self._fence_reads()
+                self.comm.gemm_allreduce(hb_q, self._dense(L.wo), T, x, bias=L.bo, status=self.status, wait_ready=not self._use_fence)
+            ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, hb=hb_d, hf=self._ffn_hf(T), signal_sym=self._sig)
             n += 6 + self._ffn_dense(li, L, T, x, hb_d, hb_f, gu)
         return n
 
@@ -395,7 +397,7 @@ class LlamaEngine:
         if self.world == 1:
             self._gemm(hb_f, L.wdown, T, out_f32=x, resid_f32=x, ldc=self.d)
         else:
-            self.comm.gemm_allreduce(hb_f, self._dense(L.wdown), T, x, status=self.status)
+            self.comm.gemm_allreduce(hb_f, self._dense(L.wdown), T, x, status=self.status, wait_ready=not self._use_fence)
         return 3
 
     def _head(self, rows: torch.Tensor, nb: int, greedy: bool = True):
@@ -422,7 +424,6 @@ class LlamaEngine:
 
     def _embed(self, T: int):
         ops.embedding(self.ids, self.x[:T], self.emb_type, self.emb.main, self.emb.plane2)
-        self._fence_reads()
 
     # ------------------------------------------------------------------ host-side batch assembly
     def _stage_batch(self, seq_ids, new_tokens: list[list[int]]):

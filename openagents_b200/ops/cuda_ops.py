@@ -22,7 +22,7 @@ ACT_NONE, ACT_GELU = 0, 1
 _P = c_void_p
 _SIGS = {
     "b200_embedding": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, c_int, _P],
-    "b200_rmsnorm": [_P, _P, c_float, c_int, c_int, _P, _P, _P, _P, _P, _P],
+    "b200_rmsnorm": [_P, _P, c_float, c_int, c_int, _P, _P, _P, _P, _P, _P, _P],
     "b200_quantize_x": [_P, c_int, c_int, _P, _P, _P, _P],
     "b200_rope_kv": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, _P, c_int, _P],
     "b200_rope_table": [_P, c_int, c_int, c_float, _P],
@@ -31,12 +31,12 @@ _SIGS = {
     "b200_argmax": [_P, c_int, c_int, _P, _P, c_int, _P, _P],
     "b200_sample_topk": [_P, c_int, c_int, c_float, c_int, c_float, _P, _P, _P, _P],
     "b200_matvec": [c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, _P, _P,
-                    c_size_t, _P],
+                    c_size_t, c_int, _P],
     "b200_attn_decode": [_P, _P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                          _P, _P, _P, _P, _P],
     "b200_attn_prefill": [_P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
     "b200_gemm_bf16": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int,
-                       _P, c_int, _P, c_size_t, c_int, _P],
+                       _P, c_int, _P, c_size_t, c_int, c_int, _P],
     "b200_moe_gemm": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P, c_int, _P, _P, _P, c_size_t, _P, _P],
     "b200_moe_route_dispatch": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_size_t, c_size_t, c_size_t, c_size_t,
                                 _P, _P, _P, _P, _P],
@@ -95,9 +95,11 @@ def embedding(ids, out, emb_type, w, w2=None, vocab_lo=0, vocab_n=None):
                                 vocab_n if vocab_n is not None else 2 ** 31 - 1, _st()), "embedding")
 
 
-def rmsnorm(x, g, eps, xq=None, xd=None, xs16=None, hb=None, hf=None):
+def rmsnorm(x, g, eps, xq=None, xd=None, xs16=None, hb=None, hf=None, signal_sym=None):
+    """``signal_sym``: symmetric-heap table; the kernel then ends by telling every rank that this rank has
+    finished reading ``x`` (the handshake the fused all-reduce kernels check with ``wait_ready``)."""
     T, D = x.shape
-    _check(lib().b200_rmsnorm(_p(x), _p(g), eps, T, D, _p(xq), _p(xd), _p(xs16), _p(hb), _p(hf), _st()), "rmsnorm")
+    _check(lib().b200_rmsnorm(_p(x), _p(g), eps, T, D, _p(xq), _p(xd), _p(xs16), _p(hb), _p(hf), _sym(signal_sym), _st()), "rmsnorm")
 
 
 def quantize_x(x, xq, xd, xs16):
@@ -146,9 +148,9 @@ def sample_topk(logits, temperature, top_k, top_p, u, out_id, scratch):
 
 
 def matvec(wt, w, w2, N, K, nb, xq=None, xd=None, xs16=None, xf=None, epi=EPI_STORE, bias=None, resid=None, y=None,
-           ldy=0, oq=None, od=None, os16=None, sym=None, sym_off=0):
+           ldy=0, oq=None, od=None, os16=None, sym=None, sym_off=0, wait_ready=False):
     _check(lib().b200_matvec(wt, _p(w), _p(w2), N, K, nb, _p(xq), _p(xd), _p(xs16), _p(xf), epi, _p(bias), _p(resid),
-                             _p(y), ldy, _p(oq), _p(od), _p(os16), _sym(sym), sym_off, _st()), "matvec")
+                             _p(y), ldy, _p(oq), _p(od), _p(os16), _sym(sym), sym_off, int(wait_ready), _st()), "matvec")
 
 
 def attn_decode_scratch_floats(B, Hq, Hkv, hd, S):
@@ -171,11 +173,11 @@ def attn_prefill(q, kc, vc, page_table, max_pages, q_start, q_len, ctx_len, n_se
 
 def gemm_bf16(A, B, M, N, K, lda=None, ldb=None, out_f32=None, out_bf16=None, ldc=None, bias=None, resid_f32=None,
               resid_bf16=None, act=ACT_NONE, accumulate=False, tile_n=0, status=None, sym_mode=SYM_NONE, sym=None,
-              sym_off=0, rows_per_rank=0, split_k=0):
+              sym_off=0, rows_per_rank=0, split_k=0, wait_ready=False):
     """D[M][N] = A[M][K] @ B[N][K]^T with fused epilogue (see ``gemm_tc05.cu``)."""
     _check(lib().b200_gemm_bf16(_p(A), _p(B), M, N, K, lda or K, ldb or K, _p(out_f32), _p(out_bf16), ldc or N,
                                 _p(bias), _p(resid_f32), _p(resid_bf16), act, int(accumulate), tile_n, split_k, _p(status),
-                                sym_mode, _sym(sym), sym_off, rows_per_rank, _st()), "gemm_bf16")
+                                sym_mode, _sym(sym), sym_off, rows_per_rank, int(wait_ready), _st()), "gemm_bf16")
 
 
 def set_pdl(on: bool):

@@ -30,15 +30,17 @@ class TPComm:
         return t.data_ptr() - self.heap.buf.data_ptr()
 
     # row-parallel mat-vec with the all-reduce fused into its epilogue
-    def matvec_allreduce(self, w, nb, xq, xd, xs, xf, x, ldy, bias=None):
+    def matvec_allreduce(self, w, nb, xq, xd, xs, xf, x, ldy, bias=None, wait_ready=False):
+        """``wait_ready``: every rank's reader of ``x`` signals when it is done (``ops.rmsnorm(..., signal_sym=)``)
+        and this kernel checks the signals before its first remote add, instead of a barrier launch in between."""
         ops.matvec(w.wt, w.main, w.plane2, w.N, w.K, nb, xq=xq, xd=xd, xs16=xs, xf=xf, epi=ops.EPI_ALLREDUCE,
-                   bias=bias, y=x, ldy=ldy, sym=self.heap.table, sym_off=self.offset_of(x))
+                   bias=bias, y=x, ldy=ldy, sym=self.heap.table, sym_off=self.offset_of(x), wait_ready=wait_ready)
 
     # row-parallel GEMM with the all-reduce fused into its epilogue
-    def gemm_allreduce(self, a_bf16, w_dense, M, x, bias=None, status=None):
+    def gemm_allreduce(self, a_bf16, w_dense, M, x, bias=None, status=None, wait_ready=False):
         N, K = w_dense.shape
         ops.gemm_bf16(a_bf16, w_dense, M, N, K, lda=a_bf16.stride(0), ldb=K, ldc=x.stride(0), bias=bias, status=status,
-                      sym_mode=ops.SYM_ALLREDUCE, sym=self.heap.table, sym_off=self.offset_of(x))
+                      sym_mode=ops.SYM_ALLREDUCE, sym=self.heap.table, sym_off=self.offset_of(x), wait_ready=wait_ready)
 
     def argmax_merge(self, out_ids: torch.Tensor, out_val: torch.Tensor, nb: int):
         """Global arg-max over vocabulary shards: every rank publishes (value, id) per row to every
