@@ -172,6 +172,7 @@ class LlamaEngine:
         self.launches_per_decode = 0
         self.small_path_tokens = MATVEC_MAX_TOKENS      # up to this many decode tokens take the mat-vec path
         self.h2d_bytes = 0                              # host-to-device bytes copied by decode() so far
+        self.attn_target_ctas = int(os.environ.get("B200_ATTN_CTAS", 0))   # split-K attention: CTAs to aim for (0: built-in rule)
 
     # ------------------------------------------------------------------ weights
     def _shard_rows(self, r: RawTensor, per_head_rows: int | None = None) -> RawTensor:
@@ -290,7 +291,17 @@ class LlamaEngine:
 
     # ------------------------------------------------------------------ building blocks
     def _splits(self, B: int, ctx_pages: int) -> int:
-        want = max(1, (2 * 148 + B * self.Hkv - 1) // (B * self.Hkv))
+        """Split-K factor of decode attention.  Measured on the 8B shape: a CTA should keep at least ~24
+        pages (the merge of the partial results and each CTA's set-up are a fixed cost), small batches
+        want just enough CTAs to cover the SMs once, and large batches run best at ~2000 CTAs (several
+        waves even out the tail)."""
+        if self.attn_target_ctas:                      # explicit override (benchmark sweeps)
+            want = max(1, (self.attn_target_ctas + B * self.Hkv - 1) // (B * self.Hkv))
+        else:
+            rows = B * self.Hkv
+            fill = (148 + rows - 1) // rows
+            big = (2048 + rows - 1) // rows if rows >= 148 else 0
+            want = min(max(1, ctx_pages // 24), max(fill, big))
         return max(1, min(self.max_splits, want, ctx_pages))
 
     @property
