@@ -50,7 +50,9 @@ int make_tmap_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t ro
 
 }  // namespace b200
 
-enum { ACT_NONE = 0, ACT_GELU = 1 };
+// ACT_SWIGLU_PAIR: B rows are interleaved (gate_0, up_0, gate_1, ...); the epilogue writes
+// silu(gate) * up as bf16, N / 2 values per row of out_bf16 (row stride ldc), nothing else.
+enum { ACT_NONE = 0, ACT_GELU = 1, ACT_SWIGLU_PAIR = 2 };
 
 struct GemmEpi {
   float* out_f32;            // either or both outputs
@@ -478,7 +480,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         tmem_ld_wait();
         if (n0 + c * 32 < N) {
           if (epi.moe_mode == 2) epilogue_chunk_combine(epi, stage, m0 + q * 32, live_end, n0 + c * 32, N, r);
-          else if (epi.moe_mode == 1) { if (m < live_end) epilogue_row_swiglu(epi, m, n0 + c * 32, r); }
+          else if (epi.moe_mode == 1 || epi.act == ACT_SWIGLU_PAIR) { if (m < live_end) epilogue_row_swiglu(epi, m, n0 + c * 32, r); }
           else if (red_path) epilogue_chunk_red(epi, stage, m0 + q * 32, n0 + c * 32, live_end, N, r, sp == 0);
           else epilogue_row(epi, m, n0 + c * 32, live_end, N, r, sp == 0);
         }
@@ -535,6 +537,9 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   if ((out_bf16 && (ldc % 8)) || (out_f32 && (ldc % 4))) return B200_ERR_BAD_ARG;
   if (N % 4) return B200_ERR_BAD_ARG;
   if (sym_mode != SYM_NONE && (!sym || (ldc % 4) || (sym_off % 16))) return B200_ERR_BAD_ARG;
+  if (act == ACT_SWIGLU_PAIR && (!out_bf16 || out_f32 || bias || resid_f32 || resid_bf16 || accumulate || sym_mode != SYM_NONE ||
+                                 tile_n == -1 || (N % 32) || (ldc % 8)))
+    return B200_ERR_BAD_ARG;
   // Few tokens: stream the weights as the 128-row operand and the tokens as the narrow one, so that
   // most of every pipeline stage is weight bytes from HBM and none of the tile is padding.
   // Measured on the decode shapes (64 tokens), the swapped form is only faster for long K with few

@@ -246,6 +246,7 @@ class LlamaEngine:
         self.q32 = torch.empty((max(self.max_batch, 1), qd), **f32)
         self.q16 = torch.empty((T, qd), dtype=torch.float16, device=dev)
         self.hb = torch.empty((T, max(d, qd, F)), dtype=torch.bfloat16, device=dev)
+        self.hb2 = torch.empty((T, F), dtype=torch.bfloat16, device=dev)
         self.gu = torch.empty((T, 2 * F), **f32)
         self.logits = torch.empty((self.max_batch, self.V_local), **f32)
         kmax = max(d, qd, F)
@@ -369,7 +370,7 @@ class LlamaEngine:
         style = 0 if cfg.rope_style == "pairs" else 1
         hb_d = self.hb.view(-1)[: T * self.d].view(T, self.d)
         hb_q = self.hb.view(-1)[: T * qd].view(T, qd)
-        hb_f = self.hb.view(-1)[: T * self.F].view(T, self.F)
+        hb_f = self.hb2[:T]                           # its own buffer: the fused gate/up GEMM reads hb_d while writing it
         qkv = self.qkv[:T]
         gu = self.gu[:T]
         S = self._splits(n_seqs, max_ctx_pages) if decode else 1
@@ -403,13 +404,17 @@ class LlamaEngine:
 
     def _ffn_dense(self, li: int, L: _Layer, T: int, x, hb_d, hb_f, gu) -> int:
         """Feed-forward block on ``hb_d`` (normalised hidden, bf16); adds its output into ``x``."""
-        self._gemm(hb_d, L.wgu, T, out_f32=gu)
-        ops.swiglu(gu, self.F, ob=hb_f)
+        if self.use_shadow:       # gate/up projection with SwiGLU in the epilogue: no fp32 [T][2F] round trip
+            ops.gemm_bf16(hb_d, L.wgu.ensure_pair_shadow(), T, 2 * self.F, L.wgu.K, lda=hb_d.stride(0), ldb=L.wgu.K, out_bf16=hb_f,
+                          ldc=self.F, act=ops.ACT_SWIGLU_PAIR, status=self.status)
+        else:
+            self._gemm(hb_d, L.wgu, T, out_f32=gu)
+            ops.swiglu(gu, self.F, ob=hb_f)
         if self.world == 1:
             self._gemm(hb_f, L.wdown, T, out_f32=x, resid_f32=x, ldc=self.d)
         else:
             self.comm.gemm_allreduce(hb_f, self._dense(L.wdown), T, x, status=self.status, wait_ready=not self._use_fence)
-        return 3
+        return 2 if self.use_shadow else 3
 
     def _head(self, rows: torch.Tensor, nb: int, greedy: bool = True):
         """Final norm + LM head on ``nb`` rows of fp32 hidden state -> logits (and arg-max ids)."""

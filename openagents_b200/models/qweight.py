@@ -161,6 +161,18 @@ class QWeight:
             self.shadow = out
         return self.shadow
 
+    def ensure_pair_shadow(self) -> torch.Tensor:
+        """bf16 [N][K] copy of a stacked (gate rows, then up rows) matrix with the rows interleaved
+        (gate_0, up_0, gate_1, ...), the order the GEMM's SwiGLU epilogue pairs columns in.  Replaces the
+        plain shadow: the dense path needs only this one."""
+        if getattr(self, "pair_shadow", None) is None:
+            sh = self.ensure_shadow()
+            half = self.N // 2
+            self.pair_shadow = sh.view(2, half, self.K).transpose(0, 1).reshape(self.N, self.K).contiguous()
+            if self.wt != ops.WT_BF16:
+                self.shadow = None
+        return self.pair_shadow
+
     def ensure_tiled(self):
         """Tile-major form for the fused-dequant GEMM: [N/128][K/256][128 rows][bytes], rows
         zero-padded to a multiple of 128, with the per-sub-block scale arithmetic done once here:

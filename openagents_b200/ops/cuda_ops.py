@@ -17,7 +17,7 @@ WT_Q4KR, WT_Q6KR, WT_Q8R, WT_BF16, WT_MXFP4R = 0, 1, 2, 3, 4
 EPI_STORE, EPI_RESID, EPI_SWIGLU_Q8, EPI_SWIGLU_F32, EPI_ALLREDUCE = 0, 1, 2, 3, 4
 SYM_NONE, SYM_ALLREDUCE, SYM_RSCATTER = 0, 1, 2
 EMB_F32, EMB_BF16, EMB_Q8R, EMB_Q6KR = 0, 1, 2, 3
-ACT_NONE, ACT_GELU = 0, 1
+ACT_NONE, ACT_GELU, ACT_SWIGLU_PAIR = 0, 1, 2
 
 _P = c_void_p
 _SIGS = {
