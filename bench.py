@@ -228,7 +228,7 @@ def main():
     if rank == 0:
         value = B / (dev_ms * 1e-3)
         out = {
-            "metric": "llama3_8b_q4k_decode_tok_s_bs64", "value": round(value, 1), "unit": "tokens/s",
+            "metric": f"{cfg.name.replace('-shape', '').replace('-', '_').replace('llama_3', 'llama3')}_q4k_decode_tok_s_bs{B}", "value": round(value, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(dev_ms, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"model": cfg.name, "weights": "Q4_K (embeddings/output Q6_K), seeded N(0,0.02)",

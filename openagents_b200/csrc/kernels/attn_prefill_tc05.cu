@@ -1,0 +1,332 @@
+// Causal grouped-query flash attention for prefill on the 5th-generation tensor cores (head dim 128).
+//
+// One CTA = 128 query rows of one head.  Roles: warp 0 is the TMA producer (Q once, then a ring of
+// K/V blocks of 64 keys gathered page by page from the paged fp16 cache), warp 1 issues tcgen05.mma,
+// warps 2..5 (128 threads, one query row each) do the online softmax and keep the output row in
+// registers.  Per key block j:
+//   S_j = Q K_j^T        tcgen05.mma 128 x 64 x 128 into one of two S accumulators in tensor memory
+//   softmax              S_j -> registers (tcgen05.ld), mask, running max / sum, P_j (fp16) -> shared
+//                        memory in the 128-byte-swizzled K-major layout the next MMA reads
+//   PV_j = P_j V_j       tcgen05.mma 128 x 128 x 64 into one of two O accumulators, V taken as it lies
+//                        in the cache ([key][dim], i.e. the MN-major form of the B operand)
+//   O += rescaled PV_j   PV_j -> registers, one iteration later, so that S_{j+1} and PV_j overlap the
+//                        softmax arithmetic
+// Sliding windows, learned sink logits and a context that is longer than the chunk (chunked prefill,
+// prefix reuse) are handled by the mask and the block range.  Math as in the reference's attention
+// (apps/openagents.com/workers/api/src/cs336-a1-real-gradient-workload.ts:478-518: max-subtract,
+// exp, normalise).  Every wait is bounded; a wait that runs out sets the status word and the CTA
+// leaves through the common exit, which frees its tensor memory.
+#include "tc05.cuh"
+
+using namespace b200;
+using namespace b200::tc;
+
+namespace {
+
+constexpr int QB = 128, KB = 64, HD = 128, KV_STAGES = 3;
+constexpr int Q_BYTES = QB * HD * 2;            // 32 KB: two halves of [128 rows][64 dims]
+constexpr int K_BYTES = KB * HD * 2;            // 16 KB: two halves of [64 keys][64 dims]
+constexpr int P_BYTES = QB * KB * 2;            // 16 KB: [128 rows][64 keys]
+constexpr uint32_t TMEM_COLS = 512;             // S: 2 x 64, O: 2 x 128
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct PrefillArgs {
+  const int* page_table;   // [n_seqs][max_pages]
+  const int* q_start;      // [n_seqs]
+  const int* q_len;        // [n_seqs]
+  const int* ctx_len;      // [n_seqs]
+  const float* sinks;      // [Hq] or null
+  __nv_bfloat16* out;      // [T_total][Hq * HD]
+  int* status;
+  int max_pages, Hq, Hkv, window;
+};
+
+// fp16 x fp16 -> fp32 instruction descriptor; b_mn: the B operand is MN-major.
+__host__ __device__ constexpr uint32_t idesc_f16(int M, int N, bool b_mn) {
+  return (1u << 4) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// MN-major operand in 128-byte-swizzled rows of 64 elements: `lbo` bytes from one 64-element column
+// block to the next, 8-row groups along K 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint32_t lbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                    const __grid_constant__ CUtensorMap tmK,
+                                                                    const __grid_constant__ CUtensorMap tmV,
+                                                                    const PrefillArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + Q_BYTES;                           // KV_STAGES x (K, V)
+  uint8_t* sP = sKV + KV_STAGES * 2 * K_BYTES;           // 2 x P
+  uint64_t* bars = (uint64_t*)(sP + 2 * P_BYTES);
+  uint64_t* q_full = bars;                                // [1]
+  uint64_t* kv_full = bars + 1;                           // [KV_STAGES]
+  uint64_t* kv_empty = kv_full + KV_STAGES;               // [KV_STAGES]
+  uint64_t* s_full = kv_empty + KV_STAGES;                // [2]
+  uint64_t* s_empty = s_full + 2;                         // [2]
+  uint64_t* p_full = s_empty + 2;                         // [2]
+  uint64_t* o_full = p_full + 2;                          // [2]
+  uint64_t* o_empty = o_full + 2;                         // [2]
+  uint32_t* tmem_holder = (uint32_t*)(o_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+
+  const int seq = blockIdx.z, h = blockIdx.y, qb = gridDim.x - 1 - blockIdx.x;   // longest (latest) query blocks first
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(q_full), 1);
+    for (int s = 0; s < KV_STAGES; s++) {
+      mbar_init(smem_u32(kv_full + s), 1);
+      mbar_init(smem_u32(kv_empty + s), 1);
+    }
+    for (int s = 0; s < 2; s++) {
+      mbar_init(smem_u32(s_full + s), 1);
+      mbar_init(smem_u32(s_empty + s), 4);
+      mbar_init(smem_u32(p_full + s), 4);
+      mbar_init(smem_u32(o_full + s), 1);
+      mbar_init(smem_u32(o_empty + s), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  pdl_trigger();
+  pdl_wait();
+
+  const int qlen = a.q_len[seq];
+  const int q0 = qb * QB;
+  const bool live = q0 < qlen;            // a dead CTA still goes through the common exit (it holds tensor memory)
+  const int ctx = a.ctx_len[seq], qs = a.q_start[seq];
+  const int kh = h / (a.Hq / a.Hkv);
+  const int pos0 = ctx - qlen + q0;       // absolute position of this CTA's first query row
+  const int k_hi = min(ctx, pos0 + QB);   // keys [k_lo, k_hi) can matter to some row
+  const int k_lo = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+  const int jb0 = k_lo / KB, jb1 = live ? (k_hi + KB - 1) / KB : jb0;   // key blocks [jb0, jb1)
+  const int nb = jb1 - jb0;
+  const uint32_t S_T = tmem_base, O_T = tmem_base + 128;   // S buffers at +0, +64; O buffers at +128, +256
+
+  if (warp == 0) {
+    if (lane == 0 && nb > 0) {
+      mbar_expect_tx(smem_u32(q_full), Q_BYTES);
+      tma_load_2d(smem_u32(sQ), &tmQ, smem_u32(q_full), h * HD, qs + q0);
+      tma_load_2d(smem_u32(sQ + Q_BYTES / 2), &tmQ, smem_u32(q_full), h * HD + 64, qs + q0);
+      const int* pt = a.page_table + (size_t)seq * a.max_pages;
+      for (int j = 0; j < nb; j++) {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        if (!mbar_wait(smem_u32(kv_empty + s), ph ^ 1, abort_flag)) break;
+        const uint32_t bar = smem_u32(kv_full + s);
+        mbar_expect_tx(bar, 2 * K_BYTES);
+        uint8_t* sK = sKV + (size_t)s * 2 * K_BYTES;
+        uint8_t* sV = sK + K_BYTES;
+#pragma unroll
+        for (int p = 0; p < KB / 16; p++) {
+          const int pi = (jb0 + j) * (KB / 16) + p;
+          const int page = (pi * 16 < ctx) ? pt[pi] : 0;          // pages past the context are masked anyway
+          const int row = (page * a.Hkv + kh) * 16;
+#pragma unroll
+          for (int hf = 0; hf < 2; hf++) {
+            tma_load_2d(smem_u32(sK + hf * (K_BYTES / 2) + p * 2048), &tmK, bar, hf * 64, row);
+            tma_load_2d(smem_u32(sV + hf * (K_BYTES / 2) + p * 2048), &tmV, bar, hf * 64, row);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && nb > 0) {
+      constexpr uint32_t idesc_s = idesc_f16(QB, KB, false);
+      constexpr uint32_t idesc_o = idesc_f16(QB, HD, true);
+      bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag);
+      auto issue_pv = [&](int j) -> bool {        // O[j & 1] = P_j V_j, then release K/V stage of block j
+        const int s = j % KV_STAGES, b = j & 1;
+        const uint32_t ph2 = (j >> 1) & 1;
+        if (!mbar_wait(smem_u32(p_full + b), ph2, abort_flag)) return false;
+        if (!mbar_wait(smem_u32(o_empty + b), ph2 ^ 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t pa = smem_u32(sP + b * P_BYTES);
+        const uint32_t va = smem_u32(sKV + (size_t)s * 2 * K_BYTES + K_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < KB / 16; kk++)
+          umma_bf16(O_T + b * 128, smem_desc_sw128(pa) + 2 * kk, smem_desc_sw128_mn(va + kk * 2048, K_BYTES / 2), idesc_o,
+                    kk != 0 ? 1u : 0u);
+        umma_commit(smem_u32(o_full + b));
+        umma_commit(smem_u32(kv_empty + s));
+        return true;
+      };
+      for (int j = 0; j < nb && ok; j++) {
+        const int s = j % KV_STAGES, b = j & 1;
+        if (!mbar_wait(smem_u32(kv_full + s), (j / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(s_empty + b), ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sKV + (size_t)s * 2 * K_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; kk++)
+          umma_bf16(S_T + b * 64, smem_desc_sw128(qa + (kk >> 2) * (Q_BYTES / 2)) + 2 * (kk & 3),
+                    smem_desc_sw128(ka + (kk >> 2) * (K_BYTES / 2)) + 2 * (kk & 3), idesc_s, kk != 0 ? 1u : 0u);
+        umma_commit(smem_u32(s_full + b));
+        if (j > 0) ok = issue_pv(j - 1);
+      }
+      if (ok) issue_pv(nb - 1);
+    }
+  } else if (nb > 0) {
+    const int q = warp & 3;                      // tensor-memory lane quarter this warp may read
+    const int row = q * 32 + lane;               // query row of this thread
+    const int qpos = pos0 + row;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
+    float o[HD];
+#pragma unroll
+    for (int i = 0; i < HD; i++) o[i] = 0.f;
+    bool ok = true;
+
+    auto accumulate = [&](int j, float alpha) {   // O = O * alpha + PV_j
+      const int b = j & 1;
+      ok = mbar_wait(smem_u32(o_full + b), (j >> 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok && !*abort_flag);
+      if (!ok) return;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < HD / 32; c++) {
+        uint32_t r[32];
+        tmem_ld32(O_T + b * 128 + lane_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(r[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(o_empty + b));
+    };
+
+    for (int j = 0; j < nb; j++) {
+      const int b = j & 1;
+      ok = mbar_wait(smem_u32(s_full + b), (j >> 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok && !*abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      float sv[KB];
+      {
+        uint32_t r[32];
+        tmem_ld32(S_T + b * 64 + lane_addr, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) sv[i] = __uint_as_float(r[i]);
+        tmem_ld32(S_T + b * 64 + lane_addr + 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) sv[32 + i] = __uint_as_float(r[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(s_empty + b));
+      // mask and running max
+      const int kb0 = (jb0 + j) * KB;
+      const bool edge = kb0 + KB - 1 > pos0 || kb0 + KB > ctx || (a.window > 0 && kb0 < pos0 + QB - a.window);
+      float mx = m;
+#pragma unroll
+      for (int i = 0; i < KB; i++) {
+        if (edge) {
+          const int kp = kb0 + i;
+          if (kp > qpos || kp >= ctx || (a.window > 0 && kp <= qpos - a.window)) sv[i] = -INFINITY;
+        }
+        mx = fmaxf(mx, sv[i]);
+      }
+      const float alpha = (mx == -INFINITY) ? 1.f : exp2f((m - mx) * kLog2e);
+      const float mref = (mx == -INFINITY) ? 0.f : mx;
+      float sum = 0.f;
+      // P row: 64 fp16 = 8 chunks of 16 bytes, chunk c of row r at r * 128 + ((c ^ (r & 7)) * 16)
+      uint8_t* prow = sP + b * P_BYTES + row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; c++) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const float p0 = exp2f((sv[c * 8 + 2 * i] - mref) * kLog2e), p1 = exp2f((sv[c * 8 + 2 * i + 1] - mref) * kLog2e);
+          const __half2 hh = __floats2half2_rn(p0, p1);
+          // sum what the tensor core will actually multiply (the rounded values)
+          sum += __low2float(hh) + __high2float(hh);
+          w[i] = *(const uint32_t*)&hh;
+        }
+        *(uint4*)(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      l = l * alpha + sum;
+      m = mx;
+      fence_proxy_async_smem();                  // P must be visible to the tensor core's (async proxy) reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(p_full + b));
+      if (j > 0) {
+        accumulate(j - 1, alpha_prev);
+        if (!ok) break;
+      }
+      alpha_prev = alpha;
+    }
+    if (ok) accumulate(nb - 1, alpha_prev);
+    if (ok && row < qlen - q0) {
+      if (a.sinks && m != -INFINITY) l += exp2f((a.sinks[h] - m) * kLog2e);
+      else if (a.sinks && m == -INFINITY) l += 1.f;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = a.out + (size_t)(qs + q0 + row) * a.Hq * HD + (size_t)h * HD;
+#pragma unroll
+      for (int i = 0; i < HD; i += 8) {
+        uint4 v;
+        __nv_bfloat162* p = (__nv_bfloat162*)&v;
+#pragma unroll
+        for (int k = 0; k < 4; k++) p[k] = __floats2bfloat162_rn(o[i + 2 * k] * inv, o[i + 2 * k + 1] * inv);
+        *(uint4*)(dst + i) = v;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (threadIdx.x == 0 && *abort_flag && a.status) atomicExch(a.status, (int)B200_ERR_TIMEOUT_MMA);
+}
+
+}  // namespace
+
+// q fp16 [T_total][Hq * 128] (rotated, pre-scaled by 1/sqrt(128)); kc / vc fp16 [n_pages][Hkv][16][128];
+// out bf16 [T_total][Hq * 128].  Sequences as in b200_attn_prefill; max_q = longest chunk.
+B200_API int b200_attn_prefill_tc05(const void* q, const void* kc, const void* vc, const int* page_table, int max_pages,
+                                    int n_pages, const int* q_start, const int* q_len, const int* ctx_len, int n_seqs,
+                                    int max_q, int T_total, int Hq, int Hkv, int window, const float* sinks, void* out,
+                                    int* status, cudaStream_t st) {
+  if (Hq % Hkv || n_seqs < 1 || max_q < 1 || !page_table) return B200_ERR_BAD_ARG;
+  CUtensorMap tq, tk, tv;
+  int rc = make_tmap_2d(&tq, q, 2, (uint64_t)T_total, (uint64_t)Hq * HD, (uint64_t)Hq * HD * 2, QB, 64, true);
+  if (rc) return rc;
+  const uint64_t rows = (uint64_t)n_pages * Hkv * 16;
+  rc = make_tmap_2d(&tk, kc, 2, rows, HD, (uint64_t)HD * 2, 16, 64, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tv, vc, 2, rows, HD, (uint64_t)HD * 2, 16, 64, true);
+  if (rc) return rc;
+  PrefillArgs a;
+  a.page_table = page_table; a.q_start = q_start; a.q_len = q_len; a.ctx_len = ctx_len; a.sinks = sinks;
+  a.out = (__nv_bfloat16*)out; a.status = status; a.max_pages = max_pages; a.Hq = Hq; a.Hkv = Hkv; a.window = window;
+  constexpr size_t smem = 1024 + Q_BYTES + KV_STAGES * 2 * K_BYTES + 2 * P_BYTES + 32 * 8;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((max_q + QB - 1) / QB, Hq, n_seqs);
+  return launch_pdl(attn_prefill_tc05_kernel, grid, dim3(192), smem, st, tq, tk, tv, a);
+}

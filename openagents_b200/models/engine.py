@@ -172,6 +172,7 @@ class LlamaEngine:
         self.launches_per_decode = 0
         self.small_path_tokens = MATVEC_MAX_TOKENS      # up to this many decode tokens take the mat-vec path
         self.h2d_bytes = 0                              # host-to-device bytes copied by decode() so far
+        self.prefill_tc05 = os.environ.get("B200_PREFILL_TC05", "0") == "1"     # off until verified on a GPU
         self.attn_target_ctas = int(os.environ.get("B200_ATTN_CTAS", 0))   # split-K attention: CTAs to aim for (0: built-in rule)
 
     # ------------------------------------------------------------------ weights
@@ -387,9 +388,14 @@ class LlamaEngine:
             else:
                 ops.rope_kv(qkv, self.pos, self.slot, None, self.q16, self.kc[li], self.vc[li], self.Hq, self.Hkv, self.hd,
                             PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd), table=self.rope_tab)
-                ops.attn_prefill(self.q16, self.kc[li], self.vc[li], self.page_table, self.max_pages, self.q_start,
-                                 self.q_len, self.seq_lens, n_seqs, max_q, self.Hq, self.Hkv, self.hd, window=L.window,
-                                 sinks=L.sinks, out_bf16=hb_q)
+                if self.hd == 128 and self.prefill_tc05:     # 5th-generation tensor-core path
+                    ops.attn_prefill_tc05(self.q16, self.kc[li], self.vc[li], self.page_table, self.q_start, self.q_len,
+                                          self.seq_lens, n_seqs, max_q, self.Hq, self.Hkv, window=L.window, sinks=L.sinks,
+                                          out_bf16=hb_q, status=self.status)
+                else:
+                    ops.attn_prefill(self.q16, self.kc[li], self.vc[li], self.page_table, self.max_pages, self.q_start,
+                                     self.q_len, self.seq_lens, n_seqs, max_q, self.Hq, self.Hkv, self.hd, window=L.window,
+                                     sinks=L.sinks, out_bf16=hb_q)
             if self.world == 1:
                 self._gemm(hb_q, L.wo, T, out_f32=x, bias=L.bo, resid_f32=x, ldc=self.d)
             else:

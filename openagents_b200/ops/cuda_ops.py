@@ -35,6 +35,7 @@ _SIGS = {
     "b200_attn_decode": [_P, _P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                          _P, _P, _P, _P, _P],
     "b200_attn_prefill": [_P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
+    "b200_attn_prefill_tc05": [_P, _P, _P, _P, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
     "b200_gemm_bf16": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int,
                        _P, c_int, _P, c_size_t, c_int, c_int, _P],
     "b200_moe_gemm": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P, c_int, _P, _P, _P, c_size_t, _P, _P],
@@ -169,6 +170,14 @@ def attn_prefill(q, kc, vc, page_table, max_pages, q_start, q_len, ctx_len, n_se
     _check(lib().b200_attn_prefill(_p(q), _p(kc), _p(vc), _p(page_table), max_pages, _p(q_start), _p(q_len),
                                    _p(ctx_len), _p(sinks), n_seqs, max_q_len, Hq, Hkv, hd, window, _p(out_bf16),
                                    _p(out_f32), _p(lse), _st()), "attn_prefill")
+
+
+def attn_prefill_tc05(q16, kc, vc, page_table, q_start, q_len, ctx_len, n_seqs, max_q_len, Hq, Hkv, window=0, sinks=None,
+                      out_bf16=None, status=None):
+    """Prefill attention on tcgen05 (head dim 128, fp16 q / cache, bf16 out); see ``attn_prefill_tc05.cu``."""
+    _check(lib().b200_attn_prefill_tc05(_p(q16), _p(kc), _p(vc), _p(page_table), page_table.shape[1], kc.shape[0], _p(q_start),
+                                        _p(q_len), _p(ctx_len), n_seqs, max_q_len, q16.shape[0], Hq, Hkv, window, _p(sinks),
+                                        _p(out_bf16), _p(status), _st()), "attn_prefill_tc05")
 
 
 def gemm_bf16(A, B, M, N, K, lda=None, ldb=None, out_f32=None, out_bf16=None, ldc=None, bias=None, resid_f32=None,

@@ -7,7 +7,8 @@ the device, launches it a few times and exits, so a capture with ``ncu -k regex:
 by itself in seconds.  Cases: qgemm64, qgemm_lm, gemm, matvec, attn_decode, attn_prefill, and
 ``step64`` / ``step1``: whole decode steps (batch 64 / 1, context 2048) of a 4-layer Llama-3-8B-shape
 engine without graphs, for a per-kernel launch list; ``moe_step``: the same for a 2-layer gpt-oss-20b-shape
-expert engine at batch 256.
+expert engine at batch 256; ``moe_ffn``: one expert layer at 4096 tokens; ``gemm_ar64`` / ``gemm_ar2048``: the
+row-parallel GEMM with its fused all-reduce epilogue; ``zero_adamw``: the sharded optimizer step.
 """
 from __future__ import annotations
 
@@ -99,6 +100,51 @@ def main():
         ids = list(range(B))
         status = eng.status
         fn = lambda: eng.decode(ids, [5] * B, use_graph=False)
+    elif case == "moe_ffn":
+        # one gpt-oss-20b-shape expert layer at 4096 tokens: fused router+dispatch, then the two grouped GEMMs
+        from ..models.config import GPT_OSS_20B
+        from ..models.moe_engine import MoEEngine
+        from ..models.qweight import RandomSource
+        from ..models.weights import PLAN_MOE
+        cfg = GPT_OSS_20B.with_(n_layers=1, vocab=2048)
+        eng = MoEEngine(cfg, RandomSource(cfg, PLAN_MOE, 0, DEV), device=DEV, max_batch=8, max_ctx=256, max_tokens=4096)
+        T = 4096
+        hb = torch.randn(T, cfg.d_model, device=DEV).bfloat16()
+        eng.hf32[:T].copy_(hb.float())
+        x = eng.x[:T]
+        status = eng.status
+
+        def fn():
+            ops.moe_zero(eng.counts)
+            eng._ffn_dense(0, eng.layers[0], T, x, hb, None, None)
+    elif case in ("gemm_ar64", "gemm_ar2048"):
+        # row-parallel down projection with the all-reduce fused into the epilogue (one-rank heap: the
+        # reductions land in this GPU's own replica; on N ranks the same instructions go through NVSwitch)
+        from ..parallel.tp import TPComm
+        M = 64 if case == "gemm_ar64" else 2048
+        N, K = 4096, 14336
+        comm = TPComm(0, 1, DEV, heap_bytes=M * N * 4 + (1 << 20))
+        xh, _ = comm.alloc_tensor((M, N), torch.float32)
+        A, B = torch.randn(M, K, device=DEV).bfloat16(), torch.randn(N, K, device=DEV).bfloat16()
+        fn = lambda: comm.gemm_allreduce(A, B, M, xh, status=status)
+    elif case == "zero_adamw":
+        # sharded AdamW step on GPT-2-small's 124M parameters, one-rank heap: reduce-scatter + norm, then
+        # clip + AdamW + bf16 cast + all-gather push
+        from ..ops import train_ops as tops
+        from ..parallel.symm import SymmHeap
+        n = 124_475_904
+        heap = SymmHeap(n * 6 + (1 << 20), DEV)
+        grads, goff = heap.alloc_tensor((n,), torch.float32)
+        params, poff = heap.alloc_tensor((n,), torch.bfloat16)
+        grads.normal_(0, 1e-3)
+        gsh, master, m, v = (torch.zeros(n, device=DEV) for _ in range(4))
+        master.normal_(0, 0.02)
+        norm2 = torch.zeros(4, device=DEV)
+
+        def fn():
+            norm2.zero_()
+            tops.zero_reduce_norm(heap.table, goff, 0, n, gsh, norm2)
+            tops.zero_adamw_gather(heap.table, poff, 0, n, gsh, master, m, v, norm2, 6e-4, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0, n)
     else:
         raise SystemExit(f"unknown case {case}")
     fn()                                  # warm-up outside the profiled range

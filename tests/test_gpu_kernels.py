@@ -289,6 +289,38 @@ def test_attn_prefill(hd, Hq, Hkv, window, use_sinks):
         assert torch.allclose(outb[s:s + n].float().cpu(), ref, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("Hq,Hkv,window,use_sinks", [(4, 2, 0, False), (8, 2, 96, True), (2, 2, 0, True)])
+def test_attn_prefill_tc05(Hq, Hkv, window, use_sinks):
+    """tcgen05 prefill attention (head dim 128) against the fp32 oracle: cold prefill longer than one query
+    tile, a chunk on top of cached context, a one-token chunk, and a sequence that ends mid key block."""
+    from openagents_b200.oracle import nn
+    ops = _ops()
+    hd = 128
+    ctx = [300, 200, 129, 513]
+    qlen = [300, 64, 1, 257]
+    B = len(ctx)
+    kc, vc, table, Ks, Vs = _paged_kv(B, Hkv, hd, ctx, seed=35)
+    T = sum(qlen)
+    q = (_randn(T, Hq * hd, seed=36) * (1.0 / math.sqrt(hd))).half()
+    sinks = _randn(Hq, seed=37) if use_sinks else None
+    starts = [sum(qlen[:b]) for b in range(B)]
+    q_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    outb = torch.zeros((T, Hq * hd), dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.attn_prefill_tc05(q, kc, vc, table, q_start, torch.tensor(qlen, dtype=torch.int32, device=DEV),
+                          torch.tensor(ctx, dtype=torch.int32, device=DEV), B, max(qlen), Hq, Hkv, window=window, sinks=sinks,
+                          out_bf16=outb, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for b in range(B):
+        s, n = starts[b], qlen[b]
+        qpos = torch.arange(ctx[b] - n, ctx[b])
+        ref = nn.attention(q[s:s + n].float().cpu().view(n, Hq, hd), Ks[b], Vs[b], qpos, torch.arange(ctx[b]),
+                           window=window, sinks=sinks.cpu() if use_sinks else None, scale=1.0).reshape(n, -1)
+        err = (outb[s:s + n].float().cpu() - ref).abs().max().item()
+        assert err < 2e-2, (b, err)
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 520, 200), (64, 768, 768), (1024, 2304, 768), (257, 64, 4096)])
 @pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
 def test_gemm_bf16(M, N, K, tile_n):
