@@ -27,6 +27,7 @@ from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 
 from .. import ENGINE_NAME, __version__
 from ..utils.telemetry import Histogram, measured, not_measured
+from . import tools as tooling
 from .generation import (CHAT_TEMPLATE_DIGEST, ByteTokenizer, Request, SamplingParams, Scheduler, VocabTokenizer,
                          render_chat)
 
@@ -254,6 +255,17 @@ def make_handler(state: ServerState):
             msgs = body.get("messages")
             if not isinstance(msgs, list) or not msgs:
                 return self._err(400, "messages must be a non-empty list")
+            tools = body.get("tools") or []
+            try:
+                mode, fname = tooling.normalize_tool_choice(body.get("tool_choice"), tools)
+            except tooling.ToolCallError as e:
+                return self._err(400, str(e), e.kind)
+            tool_msg = tooling.render_tools_system_message(tools, mode, fname)
+            if tool_msg is not None:         # stable position: ahead of the conversation, after other system text
+                head = [m for m in msgs if m.get("role") == "system"]
+                msgs = head + [{"role": "system", "content": tool_msg["content"]}] + [m for m in msgs if m.get("role") != "system"]
+            msgs = [{"role": m["role"], "content": m.get("content") if isinstance(m.get("content"), str) else
+                     json.dumps(m.get("tool_calls") or m.get("content") or "")} for m in msgs]
             cid = "chatcmpl-" + uuid.uuid4().hex[:24]
             created = int(time.time())
             if body.get("stream"):
@@ -271,23 +283,40 @@ def make_handler(state: ServerState):
                 base = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model.id}
                 chunk({**base, "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]})
                 pending: list[int] = []
+                splitter = tooling.ToolCallStreamSplitter(tools) if mode != "none" else None
+
+                def emit(text):
+                    for d in (splitter.feed(text) if splitter else [{"content": text}]):
+                        chunk({**base, "choices": [{"index": 0, "delta": d, "finish_reason": None}]})
 
                 def on_token(t):
                     pending.append(t)
                     text = model.tok.decode(pending)
-                    if text and not text.endswith("�"):       # hold back incomplete UTF-8 sequences
-                        chunk({**base, "choices": [{"index": 0, "delta": {"content": text}, "finish_reason": None}]})
+                    if text and not text.endswith("\ufffd"):       # hold back incomplete UTF-8 sequences
+                        emit(text)
                         pending.clear()
 
                 r, usage = state.complete(model, msgs, body, on_token=on_token)
-                chunk({**base, "choices": [{"index": 0, "delta": {}, "finish_reason": r.finish_reason}], "usage": usage})
+                finish = r.finish_reason
+                if splitter:
+                    for d in splitter.flush():
+                        chunk({**base, "choices": [{"index": 0, "delta": d, "finish_reason": None}]})
+                    if splitter.n_calls:
+                        finish = "tool_calls"
+                chunk({**base, "choices": [{"index": 0, "delta": {}, "finish_reason": finish}], "usage": usage})
                 chunk("[DONE]")
                 self.wfile.write(b"0\r\n\r\n")
                 return
             r, usage = state.complete(model, msgs, body)
-            msg = {"role": "assistant", "content": model.tok.decode(r.output)}
+            text = model.tok.decode(r.output)
+            try:
+                msg, finish = tooling.finish_with_tools(text, tools, mode, fname)
+            except tooling.ToolCallError as e:
+                return self._err(422, str(e), e.kind)
+            if finish == "stop":
+                finish = r.finish_reason
             self._json(200, {"id": cid, "object": "chat.completion", "created": created, "model": model.id,
-                             "choices": [{"index": 0, "message": msg, "finish_reason": r.finish_reason}], "usage": usage,
+                             "choices": [{"index": 0, "message": msg, "finish_reason": finish}], "usage": usage,
                              "timings": {"ttft_ms": None if r.ttft_s is None else round(r.ttft_s * 1e3, 3),
                                          "predicted_per_second": (len(r.output) - 1) / (r.t_done - r.t_first_token)
                                          if r.t_done and r.t_first_token and len(r.output) > 1 and r.t_done > r.t_first_token else None}})
