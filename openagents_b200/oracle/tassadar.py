@@ -25,6 +25,7 @@ from __future__ import annotations
 
 import hashlib
 import math
+import re
 import struct
 
 EXACT_WINDOW = 9_007_199_254_740_992           # 2^53
@@ -367,3 +368,92 @@ def verify_linked_composition(composed_model: dict, banks: list[dict], steps, ex
     blockers += [r for v in verdicts for r in v["blockerRefs"]]
     return {"replayVerificationCleared": not blockers, "blockerRefs": blockers, "composedTraceDigest": ct["traceDigest"],
             "constituentVerifications": verdicts, "verifierId": "tassadar.linked_dense.replay_verifier.b200.v1"}
+
+
+# ---------------------------------------------------------------- capability envelope and self-test
+# A node may only advertise the executor capability together with a receipt that its own executor replayed the
+# digest-pinned fixture to the expected trace digest (packages/tassadar-executor/src/capability-envelope.ts:109-160
+# self-test, :187-222 declaration, :241-266 matrix row, :286-349 row decoder, :351-388 ref filter).
+CAPABILITY_REF = "capability.tassadar_poc.numeric_model_executor"     # packages/tassadar-executor/src/lane.ts:7
+SELF_TEST_RECEIPT_SCHEMA = "openagents.tassadar_executor.self_test_receipt.v1"
+CAPABILITY_ENVELOPE_SCHEMA = "openagents.pylon.tassadar_capability_envelope.v1"
+CAPABILITY_MATRIX_ROW_SCHEMA = "openagents.tassadar_executor.capability_matrix_row.v1"
+WINDOW_VERSION_REF = "window.tassadar_executor.exact_2p53.v1"
+WORKLOAD_FAMILY_REF = "workload.tassadar_executor.alm_numeric_trace.v1"
+LEG_REFS = ("leg.tassadar_executor.alm_numeric_execute.v1", "leg.tassadar_executor.exact_trace_replay_full.v1",
+            "leg.tassadar_executor.exact_trace_replay_window.v1")
+_SELF_TEST_PREFIX = "receipt.tassadar_executor.self_test.v1"
+_COMPILE_PREFIX = "receipt.tassadar_compile.model_digest"
+_SELF_TEST_REF = re.compile(r"^receipt\.tassadar_executor\.self_test\.v1\.[0-9a-f]{16}$")
+_COMPILE_REF = re.compile(r"^receipt\.tassadar_compile\.model_digest\.[0-9a-f]{16}$")
+
+
+class CapabilityShapeError(Exception):
+    pass
+
+
+def run_self_test(workload: dict, observed_at: str = "1970-01-01T00:00:00Z") -> dict:
+    """workload = {fixtureId, expectedModelDigest, expectedTraceDigest, model, steps}.  The receipt carries digests only."""
+    v = verify_full_replay(workload["model"], workload["steps"], workload["expectedTraceDigest"], "device.self_test.local")
+    ok = v["outcome"] == "verified"
+    rej = v["rejection"]
+    detail = None if ok else ("self-test replay rejected without a named rejection" if rej is None else
+                              f"execution_refused: {rej['detail']}" if rej["reason"] == "execution_refused" else rej["reason"])
+    return {"schema": SELF_TEST_RECEIPT_SCHEMA, "capabilityRef": CAPABILITY_REF, "executorId": EXECUTOR_ID, "fixtureId": workload["fixtureId"],
+            "graphDigest": workload["model"]["graph_digest"], "modelDigest": workload["expectedModelDigest"],
+            "expectedTraceDigest": workload["expectedTraceDigest"], "replayedTraceDigest": v["replayedTraceDigest"],
+            "stepCount": v["replayedSteps"], "replayClassId": REPLAY_CLASS_ID, "observedAt": observed_at,
+            "outcome": "verified" if ok else "failed", "refusalDetail": detail,
+            "receiptRef": f"{_SELF_TEST_PREFIX}.{v['replayedTraceDigest'][:16]}" if ok and v["replayedTraceDigest"] else None}
+
+
+def capability_matrix_row(envelope: dict) -> dict:
+    r = envelope["selfTestReceipt"]
+    if r["receiptRef"] is None:
+        raise CapabilityShapeError("capability matrix row requires a verified self-test receipt ref")
+    return {"schema": CAPABILITY_MATRIX_ROW_SCHEMA, "capabilityRef": CAPABILITY_REF, "workloadFamilyRef": WORKLOAD_FAMILY_REF,
+            "windowVersionRef": WINDOW_VERSION_REF, "legRefs": list(envelope["legRefs"]), "replayClassId": envelope["replayClassId"],
+            "compileReceiptRef": f"{_COMPILE_PREFIX}.{r['modelDigest'][:16]}", "replayReceiptRef": r["receiptRef"],
+            "posture": "execute_exact_or_refuse"}
+
+
+def build_capability_declaration(receipt: dict) -> dict:
+    """A failed or receipt-less self-test yields a typed refusal, never a declaration."""
+    if receipt["outcome"] != "verified" or receipt["receiptRef"] is None:
+        return {"declared": False, "refusal": {
+            "kind": "self_test_receipt_missing" if receipt["outcome"] == "verified" else "self_test_failed",
+            "refusalRef": "refusal.tassadar_executor.capability_undeclarable",
+            "detail": receipt.get("refusalDetail") or "executor self-test did not verify the pinned trace digest"}}
+    env = {"schema": CAPABILITY_ENVELOPE_SCHEMA, "capabilityRef": CAPABILITY_REF, "windowVersionRef": WINDOW_VERSION_REF,
+           "exactnessWindowLabel": "2^53", "exactnessWindow": EXACT_WINDOW, "legRefs": list(LEG_REFS), "replayClassId": receipt["replayClassId"],
+           "executorId": receipt["executorId"], "selfTestReceipt": receipt}
+    return {"declared": True, "envelope": env, "matrixRow": capability_matrix_row(env), "capabilityRefs": [CAPABILITY_REF, receipt["receiptRef"]]}
+
+
+def decode_capability_matrix_row(row) -> dict:
+    """Every fixed field must equal its constant and every receipt field its receipt-derived pattern."""
+    if not isinstance(row, dict):
+        raise CapabilityShapeError("capability matrix row must be an object")
+    for k, want in (("schema", CAPABILITY_MATRIX_ROW_SCHEMA), ("capabilityRef", CAPABILITY_REF), ("workloadFamilyRef", WORKLOAD_FAMILY_REF),
+                    ("windowVersionRef", WINDOW_VERSION_REF), ("replayClassId", REPLAY_CLASS_ID), ("posture", "execute_exact_or_refuse")):
+        if row.get(k) != want:
+            raise CapabilityShapeError(f"capability matrix row field {k} must be {want}, got {row.get(k)}")
+    legs = row.get("legRefs")
+    if not isinstance(legs, list) or not legs or any(l not in LEG_REFS for l in legs):
+        raise CapabilityShapeError("legRefs must be a non-empty subset of the known executor legs")
+    if not isinstance(row.get("compileReceiptRef"), str) or not _COMPILE_REF.match(row["compileReceiptRef"]):
+        raise CapabilityShapeError("compileReceiptRef must derive from a model digest")
+    if not isinstance(row.get("replayReceiptRef"), str) or not _SELF_TEST_REF.match(row["replayReceiptRef"]):
+        raise CapabilityShapeError("replayReceiptRef must derive from a verified self-test receipt")
+    return {k: row[k] for k in ("schema", "capabilityRef", "workloadFamilyRef", "windowVersionRef", "legRefs", "replayClassId",
+                                "compileReceiptRef", "replayReceiptRef", "posture")}
+
+
+def has_receipted_capability(refs) -> bool:
+    return CAPABILITY_REF in refs and any(_SELF_TEST_REF.match(r) for r in refs)
+
+
+def strip_unreceipted_capability(refs) -> list:
+    """Drop a configuration-asserted capability claim (and orphaned receipt refs) that has no self-test receipt beside it."""
+    refs = list(refs)
+    return refs if has_receipted_capability(refs) else [r for r in refs if r != CAPABILITY_REF and not _SELF_TEST_REF.match(r)]

@@ -88,3 +88,26 @@ def test_linked_composition():
     assert not v["replayVerificationCleared"]
     assert set(v["blockerRefs"]) == {"blocker.public.tassadar_compiled_module.composed_trace_mismatch",
                                      "blocker.public.tassadar_compiled_module.source_trace_mismatch"}
+
+
+def test_capability_envelope_needs_a_verified_self_test():
+    wl = {"fixtureId": "fixture.loop_sum", "expectedModelDigest": "ab" * 32, "expectedTraceDigest": GOLD["expectedTraceDigest"],
+          "model": GOLD["model"], "steps": GOLD["steps"]}
+    r = ts.run_self_test(wl)
+    assert r["outcome"] == "verified" and r["receiptRef"] == "receipt.tassadar_executor.self_test.v1." + GOLD["expectedTraceDigest"][:16]
+    assert "stepOutputs" not in r and "model" not in r
+    d = ts.build_capability_declaration(r)
+    assert d["declared"] and d["capabilityRefs"] == [ts.CAPABILITY_REF, r["receiptRef"]]
+    row = ts.decode_capability_matrix_row(json.loads(json.dumps(d["matrixRow"])))
+    assert row["compileReceiptRef"] == "receipt.tassadar_compile.model_digest." + "ab" * 8 and row["posture"] == "execute_exact_or_refuse"
+    for k, v in (("posture", "best_effort"), ("compileReceiptRef", "free form"), ("legRefs", ["leg.unknown"]), ("replayReceiptRef", "receipt.x")):
+        with pytest.raises(ts.CapabilityShapeError):
+            ts.decode_capability_matrix_row({**row, k: v})
+    bad = ts.run_self_test({**wl, "expectedTraceDigest": "00" * 32})
+    assert bad["outcome"] == "failed" and bad["receiptRef"] is None and bad["refusalDetail"] == "trace_digest_mismatch"
+    ref = ts.build_capability_declaration(bad)
+    assert not ref["declared"] and ref["refusal"]["kind"] == "self_test_failed"
+    refs = [ts.CAPABILITY_REF, "capability.other"]
+    assert ts.strip_unreceipted_capability(refs) == ["capability.other"]
+    assert ts.strip_unreceipted_capability(["capability.other", r["receiptRef"]]) == ["capability.other"]
+    assert ts.strip_unreceipted_capability(refs + [r["receiptRef"]]) == refs + [r["receiptRef"]]
