@@ -203,3 +203,54 @@ class ModelRegistry:
         if tpl is not None and template_digest(tpl) not in self.allowed:
             return {"admitted": False, "reason": "chat_template_digest_not_allowlisted", "architecture": arch, "templateDigest": template_digest(tpl)}
         return {"admitted": True, "architecture": arch, "family": ADMITTED_ARCHITECTURES[arch], "templateDigest": template_digest(tpl) if tpl else None}
+
+
+# ---------------------------------------------------------------- assignment leases that ask for local inference
+# A lease may carry local-inference requirements {workClass, mode, requiredModelRef?, receiptRefs?}.  The runner admits
+# the lease only if a served model row satisfies the mode, and attaches the backend ref, the selected model ref and the
+# lease's receipt refs to the closeout.  In the reference the selector is an archived stub that always refuses with
+# ``blocker.psionic_qwen35.archived_to_backroom``; here it is live against the rows the model server reports.
+# Reference: apps/pylon/src/assignment.ts:112-119 (requirements), :1334-1347 (admission), :2437-2461 (closeout refs);
+# apps/pylon/packages/runtime/src/backends/psionic-qwen/model-admission.ts:1-24, contract.ts:1-6.
+BACKEND_REF = "backend.psionic.qwen35"
+MODEL_REFS = {"small": "model.psionic.qwen35.0_8b.q8_0", "large": "model.psionic.qwen35.2b.q8_0"}
+TASK_MODES = ("coding_agent", "requires_2b")
+
+
+def admission_from_model_rows(rows) -> dict:
+    """rows: [{modelRef, ready}] as listed by the model server (``/v1/models``)."""
+    observed = [r["modelRef"] for r in rows]
+    admitted = [r["modelRef"] for r in rows if r.get("ready", True)]
+    return {"rows": list(rows), "observedModelRefs": observed, "admittedModelRefs": admitted,
+            "blockerRefs": [] if admitted else ["blocker.psionic_qwen35.qwen35_model_missing"]}
+
+
+def select_model(admission: dict, mode: str) -> dict:
+    if mode not in TASK_MODES:
+        raise ValueError(f"mode must be one of {TASK_MODES}")
+    if admission["blockerRefs"]:
+        return {"admitted": False, "selectedModelRef": None, "blockerRefs": list(admission["blockerRefs"])}
+    adm = admission["admittedModelRefs"]
+    if mode == "requires_2b":
+        if MODEL_REFS["large"] not in adm:
+            return {"admitted": False, "selectedModelRef": None, "blockerRefs": ["blocker.psionic_qwen35.model_2b_missing"]}
+        return {"admitted": True, "selectedModelRef": MODEL_REFS["large"], "blockerRefs": []}
+    pick = MODEL_REFS["large"] if MODEL_REFS["large"] in adm else adm[0]       # the stronger row when it is there
+    return {"admitted": True, "selectedModelRef": pick, "blockerRefs": []}
+
+
+def admit_inference_lease(requirements: dict, admission: dict) -> dict:
+    sel = select_model(admission, requirements["mode"])
+    blockers = list(sel["blockerRefs"])
+    need = requirements.get("requiredModelRef")
+    if need and sel["selectedModelRef"] != need:
+        blockers.append("blocker.psionic_qwen35.model_2b_missing" if need == MODEL_REFS["large"] else "blocker.psionic_qwen35.required_model_missing")
+    return {"admitted": not blockers, "selectedModelRef": sel["selectedModelRef"], "blockerRefs": sorted(set(blockers))}
+
+
+def closeout_receipt_refs(requirements: dict | None, admission: dict) -> list[str]:
+    if not requirements:
+        return []
+    refs = [BACKEND_REF] + list(requirements.get("receiptRefs") or [])
+    sel = select_model(admission, requirements["mode"])["selectedModelRef"]
+    return list(dict.fromkeys(refs + ([sel] if sel else [])))

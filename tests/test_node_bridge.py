@@ -84,3 +84,21 @@ def test_model_registry_template_allowlist():
     ok = reg.admit({"general.architecture": "gpt-oss", "tokenizer.chat_template": tpl})
     assert ok["admitted"] and ok["family"] == "moe" and ok["templateDigest"] == d
     assert not reg.admit({"general.architecture": "llama", "tokenizer.chat_template": tpl + " "})["admitted"]
+
+
+def test_inference_lease_admission_and_closeout_refs():
+    small, large = nb.MODEL_REFS["small"], nb.MODEL_REFS["large"]
+    none = nb.admission_from_model_rows([])
+    assert nb.select_model(none, "coding_agent")["blockerRefs"] == ["blocker.psionic_qwen35.qwen35_model_missing"]
+    only_small = nb.admission_from_model_rows([{"modelRef": small}, {"modelRef": large, "ready": False}])
+    assert nb.select_model(only_small, "coding_agent") == {"admitted": True, "selectedModelRef": small, "blockerRefs": []}
+    assert nb.select_model(only_small, "requires_2b")["blockerRefs"] == ["blocker.psionic_qwen35.model_2b_missing"]
+    both = nb.admission_from_model_rows([{"modelRef": small}, {"modelRef": large}])
+    assert nb.select_model(both, "coding_agent")["selectedModelRef"] == large
+    req = {"workClass": "local_inference", "mode": "coding_agent", "requiredModelRef": large, "receiptRefs": ["receipt.a", "receipt.a"]}
+    assert nb.admit_inference_lease(req, only_small) == {"admitted": False, "selectedModelRef": small, "blockerRefs": ["blocker.psionic_qwen35.model_2b_missing"]}
+    assert nb.admit_inference_lease(req, both)["admitted"]
+    assert nb.closeout_receipt_refs(req, both) == [nb.BACKEND_REF, "receipt.a", large]
+    assert nb.closeout_receipt_refs(None, both) == []
+    with pytest.raises(ValueError):
+        nb.select_model(both, "chat")
