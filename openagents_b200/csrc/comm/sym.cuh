@@ -213,6 +213,51 @@ __device__ __forceinline__ bool sym_wait_ready(const SymTable& T) {
   }
 }
 
+// ---- all-gather by push, consumed tile by tile --------------------------------------------------
+// Rank r writes its rows of a row-sharded tensor into every rank's full copy (sym_st_all_v4) and then
+// bumps counter kSymAgCh0 + r on every rank (sym_signal_rows, called by every thread of every CTA of
+// the pushing kernel).  A consumer that needs rows owned by rank r waits until that counter has
+// reached the number of all-gathers issued so far (`epoch`, counted by the host, the same on all
+// ranks), so it can start on the rows that are already there while the others are still in flight.
+constexpr int kSymAgCh0 = 8;   // channels 8 .. 8 + kMaxRanks - 1
+
+__device__ __forceinline__ void sym_signal_rows(const SymTable& T, int n_ctas) {
+  __threadfence_system();        // this thread's pushes are visible system-wide before the counter moves
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    SymControl* me = sym_ctl(T, T.rank);
+    const int done = atomicAdd(&me->ticket[kSymAgCh0], 1);
+    if (done == n_ctas - 1) {
+      me->ticket[kSymAgCh0] = 0;
+      __threadfence_system();
+      const size_t off = offsetof(SymControl, flag) + 4 * (kSymAgCh0 + T.rank);
+      if (T.use_mc) {
+        asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(T.mc_base + off), "r"(1u) : "memory");
+      } else {
+        for (int p = 0; p < T.world; p++)
+          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(T.base[p] + off), "r"(1u) : "memory");
+      }
+    }
+  }
+}
+
+// One thread: wait until rank `owner` has pushed its rows of all-gather number `epoch`.  Returns false
+// (and records the time-out) if the wait ran out.
+__device__ __forceinline__ bool sym_wait_rows(const SymTable& T, int owner, uint32_t epoch) {
+  SymControl* me = sym_ctl(T, T.rank);
+  const unsigned long long t0 = sym_now_ns();
+  for (uint32_t spin = 0;; ++spin) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(&me->flag[kSymAgCh0 + owner]) : "memory");
+    if ((int32_t)(v - epoch) >= 0) return true;
+    if ((spin & 63u) == 63u && sym_now_ns() - t0 > T.wait_ns) {
+      me->status = (int)B200_ERR_TIMEOUT_PEER;
+      atomicAdd(&me->timeouts, 1);
+      return false;
+    }
+  }
+}
+
 // Call from every thread of every CTA at the end of a kernel that pushed data to peers: the CTA that
 // finishes last runs the cross-rank barrier, so when the kernel completes, every rank's pushes have
 // landed everywhere.  No CTA waits for another CTA.  `close_ready_phase`: this kernel consumed one

@@ -159,6 +159,56 @@ B200_API int b200_rmsnorm(const float* x, const float* g, float eps, int T, int 
                     (__nv_bfloat16*)hb, hf, sym ? *sym : SymTable{}, sym ? 1 : 0);
 }
 
+// Sequence-sharded tensor-parallel prefill: this rank owns rows [row0, row0 + T) of the residual
+// stream.  Normalise them and push the bf16 result into EVERY rank's full [rows][D] tensor at byte
+// offset hb_off of the symmetric heap (one multimem store per 16 bytes through NVSwitch, or one store
+// per peer), then bump this rank's all-gather counter: the column-parallel GEMM that follows on each
+// rank starts on the rows that have arrived (see sym_wait_rows).  This is the all-gather, fused into
+// the kernel that produces the data.
+__global__ void __launch_bounds__(512) rmsnorm_allgather_kernel(const float* __restrict__ x, const float* __restrict__ g,
+                                                                float eps, int D, int row0, int n_rows, size_t hb_off,
+                                                                const SymTable sym) {
+  __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (t >= n_rows) {              // a rank without rows still counts as having pushed (one CTA, no data)
+    sym_signal_rows(sym, gridDim.x);
+    return;
+  }
+  const float4* xr = (const float4*)(x + (size_t)(row0 + t) * D);
+  const int chunks = D / 8;                       // 8 elements = 32 bytes in, 16 bytes out
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    const float4 a = xr[2 * c], b = xr[2 * c + 1];
+    ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / (float)D + eps);
+  const float4* gr = (const float4*)g;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    const float4 a = xr[2 * c], b = xr[2 * c + 1];                 // second read of the row: L1 / L2
+    const float4 ga = g ? gr[2 * c] : make_float4(1.f, 1.f, 1.f, 1.f), gb = g ? gr[2 * c + 1] : make_float4(1.f, 1.f, 1.f, 1.f);
+    uint4 o;
+    __nv_bfloat162* p = (__nv_bfloat162*)&o;
+    p[0] = __floats2bfloat162_rn(a.x * rstd * ga.x, a.y * rstd * ga.y);
+    p[1] = __floats2bfloat162_rn(a.z * rstd * ga.z, a.w * rstd * ga.w);
+    p[2] = __floats2bfloat162_rn(b.x * rstd * gb.x, b.y * rstd * gb.y);
+    p[3] = __floats2bfloat162_rn(b.z * rstd * gb.z, b.w * rstd * gb.w);
+    sym_st_all_v4(sym, hb_off + ((size_t)(row0 + t) * D + (size_t)c * 8) * 2, o);
+  }
+  sym_signal_rows(sym, gridDim.x);
+}
+
+// x: this rank's full-size fp32 residual tensor [*][D] (only rows [row0, row0 + T) are read); the bf16
+// result goes to rows [row0, row0 + T) of the [*][D] tensor at heap offset hb_off on every rank.
+B200_API int b200_rmsnorm_allgather(const float* x, const float* g, float eps, int row0, int T, int D, size_t hb_off,
+                                    const SymTable* sym, cudaStream_t st) {
+  if (!sym || (D % 8) || (hb_off % 16) || T < 0) return B200_ERR_BAD_ARG;
+  return launch_pdl(rmsnorm_allgather_kernel, dim3(T > 0 ? T : 1), dim3(D >= 4096 ? 512 : 256), 0, st, x, g, eps, D, row0, T,
+                    hb_off, *sym);
+}
+
 // Plain activation quantization of fp32 rows (used where no norm precedes a quantized matvec).
 __global__ void quantize_x_kernel(const float* __restrict__ x, int D, int8_t* __restrict__ xq,
                                   float* __restrict__ xd, float* __restrict__ xs16) {

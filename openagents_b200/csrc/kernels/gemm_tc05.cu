@@ -86,13 +86,22 @@ struct GemmEpi {
   // into an fp32 tensor [*, ldc] at byte offset sym_off of the symmetric heap.
   //   SYM_ALLREDUCE : into every rank's replica (multimem.red through the switch where available)
   //   SYM_RSCATTER  : row m goes to rank m / rows_per_rank, local row m % rows_per_rank
+  //   SYM_RSCATTER_ROWS : row m goes to rank m / rows_per_rank, same row m (the owner keeps its rows in
+  //                   place in a full-size tensor: the sequence-sharded residual stream of prefill)
   // The kernel then ends with a cross-rank barrier.
   int sym_mode;
   int rows_per_rank;
   size_t sym_off;
+  // All-gather fused into the A operand (sequence-sharded prefill): rows of A are pushed into this
+  // rank's memory by their owners (rank m / ag_rows_per_rank, see rmsnorm_allgather_kernel); the
+  // producer warp waits for the owner's counter to reach ag_epoch before it loads a tile, and the walk
+  // over m tiles starts at this rank's own rows, which need no transfer.  0 = off.
+  int ag_rows_per_rank;
+  uint32_t ag_epoch;
   SymTable sym;
 };
-enum { SYM_NONE = 0, SYM_ALLREDUCE = 1, SYM_RSCATTER = 2 };
+enum { SYM_NONE = 0, SYM_ALLREDUCE = 1, SYM_RSCATTER = 2, SYM_RSCATTER_ROWS = 3 };
+__device__ __forceinline__ int rs_row(const GemmEpi& e, int m) { return e.sym_mode == SYM_RSCATTER ? m % e.rows_per_rank : m; }
 
 constexpr int BM = 128, BK = 64;
 constexpr int kMaxLiveTiles = 2048;   // grouped mode: 128-row tiles with live rows, listed in shared memory
@@ -127,7 +136,7 @@ __device__ __forceinline__ void epilogue_chunk_red(const GemmEpi& e, float* stag
       } else if (e.sym_mode == SYM_ALLREDUCE) {
         sym_red_all_f32x4(e.sym, e.sym_off + ((size_t)m * e.ldc + n) * 4, o);
       } else {
-        sym_red_to_f32x4(e.sym, m / e.rows_per_rank, e.sym_off + ((size_t)(m % e.rows_per_rank) * e.ldc + n) * 4, o);
+        sym_red_to_f32x4(e.sym, m / e.rows_per_rank, e.sym_off + ((size_t)rs_row(e, m) * e.ldc + n) * 4, o);
       }
     }
   }
@@ -189,8 +198,8 @@ __device__ __forceinline__ void epilogue_col(const GemmEpi& e, int n, int t0, in
     if (t >= n_rows) break;
     float x = __uint_as_float(r[j]) + b;
     if (sym) {
-      const int owner = e.sym_mode == SYM_RSCATTER ? t / e.rows_per_rank : 0;
-      const int lrow = e.sym_mode == SYM_RSCATTER ? t % e.rows_per_rank : t;
+      const int owner = e.sym_mode != SYM_ALLREDUCE ? t / e.rows_per_rank : 0;
+      const int lrow = rs_row(e, t);
       const size_t off = e.sym_off + ((size_t)lrow * e.ldc + n) * 4;
       if (e.sym_mode == SYM_ALLREDUCE) sym_red_all_f32(e.sym, off, x);
       else sym_red_to_f32(e.sym, owner, off, x);
@@ -236,8 +245,8 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, in
   }
   if (e.sym_mode != SYM_NONE) {
     const bool add_bias = e.bias && e.sym.rank == 0 && first_split;
-    const int owner = e.sym_mode == SYM_RSCATTER ? m / e.rows_per_rank : 0;
-    const int lrow = e.sym_mode == SYM_RSCATTER ? m % e.rows_per_rank : m;
+    const int owner = e.sym_mode != SYM_ALLREDUCE ? m / e.rows_per_rank : 0;
+    const int lrow = rs_row(e, m);
     const size_t off = e.sym_off + ((size_t)lrow * e.ldc + n0) * 4;
     if (full) {
 #pragma unroll
@@ -355,6 +364,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   const int tiles_n = (N + BN - 1) / BN;
   int n_tiles = tiles_m * tiles_n * splits;   // work items: (output tile, K split), split fastest
   const int kps = (KB + splits - 1) / splits;
+  // fused all-gather: start the walk over m tiles at this rank's own rows
+  const int m_rot = epi.ag_rows_per_rank ? ((epi.sym.rank * epi.ag_rows_per_rank) / BM) % tiles_m : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -401,11 +412,24 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, ag_seen = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < n_tiles && ok; item += gridDim.x) {
         const int tile = item / splits, sp = item - tile * splits;
-        const int m0 = epi.group_rows ? live_m[tile % tiles_m] : (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        const int m0 = epi.group_rows ? live_m[tile % tiles_m] : ((tile % tiles_m + m_rot) % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        if (epi.ag_rows_per_rank) {       // rows of this tile come from their owners' all-gather pushes
+          const int o0 = m0 / epi.ag_rows_per_rank, o1 = min(m0 + BM - 1, M - 1) / epi.ag_rows_per_rank;
+          for (int o = o0; o <= o1 && ok; o++) {
+            if (ag_seen & (1u << o)) continue;
+            if (!sym_wait_rows(epi.sym, o, epi.ag_epoch)) {
+              *abort_flag = 1;
+              ok = false;
+            }
+            ag_seen |= 1u << o;
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");   // peers' stores -> this CTA's TMA reads
+        }
         int b_row = n0;
         if (epi.group_rows) b_row += (m0 / epi.group_rows) * epi.group_n;
         const int kb0 = sp * kps, kb1 = min(KB, kb0 + kps);
@@ -455,7 +479,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     uint32_t tcount = 0;
     for (int item = blockIdx.x; item < n_tiles; item += gridDim.x) {
       const int tile = item / splits, sp = item - tile * splits;
-      const int m0 = epi.group_rows ? live_m[tile % tiles_m] : (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int m0 = epi.group_rows ? live_m[tile % tiles_m] : ((tile % tiles_m + m_rot) % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
       int live_end = M;                       // rows below this index are written
       if (epi.group_rows) {
         const int g = m0 / epi.group_rows;
@@ -532,11 +556,12 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
                             void* out_bf16, int ldc, const float* bias, const float* resid_f32,
                             const void* resid_bf16, int act, int accumulate, int tile_n, int split_k, int* status,
                             int sym_mode, const SymTable* sym, size_t sym_off, int rows_per_rank, int wait_ready,
-                            cudaStream_t st) {
+                            int ag_rows_per_rank, int ag_epoch, cudaStream_t st) {
   if (M <= 0 || N <= 0 || K <= 0 || (lda % 8) || (ldb % 8) || (K % 8)) return B200_ERR_BAD_ARG;
   if ((out_bf16 && (ldc % 8)) || (out_f32 && (ldc % 4))) return B200_ERR_BAD_ARG;
   if (N % 4) return B200_ERR_BAD_ARG;
   if (sym_mode != SYM_NONE && (!sym || (ldc % 4) || (sym_off % 16))) return B200_ERR_BAD_ARG;
+  if (ag_rows_per_rank < 0 || (ag_rows_per_rank > 0 && (!sym || tile_n == -1))) return B200_ERR_BAD_ARG;
   if (act == ACT_SWIGLU_PAIR && (!out_bf16 || out_f32 || bias || resid_f32 || resid_bf16 || accumulate || sym_mode != SYM_NONE ||
                                  tile_n == -1 || (N % 32) || (ldc % 8)))
     return B200_ERR_BAD_ARG;
@@ -590,8 +615,8 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   e.transposed = swap ? 1 : 0;
   e.group_rows = 0; e.group_n = 0; e.group_counts = nullptr; e.moe_mode = 0; e.meta = nullptr; e.gate_w = nullptr;
   e.wait_ready = (sym_mode != SYM_NONE) ? wait_ready : 0;
-  if (sym_mode != SYM_NONE) {
-    if (!sym || (ldc % 4) || (sym_off % 16)) return B200_ERR_BAD_ARG;
+  e.ag_rows_per_rank = ag_rows_per_rank; e.ag_epoch = (uint32_t)ag_epoch;
+  if (sym_mode != SYM_NONE || ag_rows_per_rank > 0) {
     e.sym = *sym;
   } else {
     e.sym = SymTable{};

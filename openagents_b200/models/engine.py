@@ -172,7 +172,8 @@ class LlamaEngine:
         self.launches_per_decode = 0
         self.small_path_tokens = MATVEC_MAX_TOKENS      # up to this many decode tokens take the mat-vec path
         self.h2d_bytes = 0                              # host-to-device bytes copied by decode() so far
-        self.prefill_tc05 = os.environ.get("B200_PREFILL_TC05", "0") == "1"     # off until verified on a GPU
+        self.prefill_tc05 = os.environ.get("B200_PREFILL_TC05", "1") == "1"     # tcgen05 prefill attention (head size 128)
+        self.seq_shard = os.environ.get("B200_TP_SEQ_SHARD", "1") == "1"        # sequence-sharded tensor-parallel prefill
         self.attn_target_ctas = int(os.environ.get("B200_ATTN_CTAS", 0))   # split-K attention: CTAs to aim for (0: built-in rule)
 
     # ------------------------------------------------------------------ weights
@@ -240,7 +241,10 @@ class LlamaEngine:
         self.kc = [torch.zeros((self.n_pages, self.Hkv, PAGE, self.hd), dtype=torch.float16, device=dev) for _ in self.layers]
         self.vc = [torch.zeros_like(k) for k in self.kc]
         if self.world > 1:   # the replicated residual stream receives peers' partial sums: symmetric heap
-            self.x, self.x_off = self.comm.alloc_tensor((T, d), torch.float32)
+            # (+ world rows: the in-place all-gather that ends a sequence-sharded prefill moves whole row blocks)
+            self.x, self.x_off = self.comm.alloc_tensor((T + self.world, d), torch.float32)
+            self.hbfull, self.hbfull_off = self.comm.alloc_tensor((T + self.world, d), torch.bfloat16)
+            self._ag_epoch = 0
         else:
             self.x = torch.empty((T, d), **f32)
         self.qkv = torch.empty((T, self.qkv_dim), **f32)
@@ -364,8 +368,17 @@ class LlamaEngine:
         ops.gemm_bf16(a_bf16, self._dense(w), M, w.N, w.K, lda=a_bf16.stride(0), ldb=w.K, out_f32=out_f32,
                       out_bf16=out_bf16, ldc=ldc or w.N, bias=bias, resid_f32=resid_f32, status=self.status)
 
+    def _seq_sharded(self, T: int, decode: bool) -> bool:
+        """Tensor-parallel prefill keeps the residual stream sharded by rows (sequence parallel): each
+        row-parallel GEMM reduce-scatters its partial sums to the rows' owners and each norm all-gathers the
+        normalised rows into the next column-parallel GEMM, instead of all-reducing the whole stream twice
+        a layer (an all-reduce delivers world x [T, d] fp32 to every GPU; the pair delivers about 1.5 x)."""
+        return self.world > 1 and not decode and self.seq_shard and T >= 128 * self.world
+
     def _layers_dense(self, T: int, decode: bool, n_seqs: int, max_q: int, max_ctx_pages: int):
         """Any token count: tcgen05 GEMM path (prefill chunks and large decode batches)."""
+        if self._seq_sharded(T, decode):
+            return self._layers_seq_sharded(T, n_seqs, max_q)
         cfg, x = self.cfg, self.x[:T]
         qd = self.Hq * self.hd
         style = 0 if cfg.rope_style == "pairs" else 1
@@ -403,6 +416,65 @@ class LlamaEngine:
             ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, hb=hb_d, hf=self._ffn_hf(T), signal_sym=self._sig)
             n += 6 + self._ffn_dense(li, L, T, x, hb_d, hb_f, gu)
         return n
+
+    def _layers_seq_sharded(self, T: int, n_seqs: int, max_q: int):
+        """Prefill with the residual stream sharded by rows over the tensor-parallel ranks.  Per layer:
+        norm + all-gather push -> QKV GEMM (waits tile by tile for the rows' owners) -> attention on this
+        rank's heads -> output GEMM with the reduce-scatter in its epilogue; the same pair around the
+        feed-forward block.  Ends with an in-place all-gather of the residual rows, so that the caller
+        finds the replicated stream the decode path works on."""
+        cfg, W, table = self.cfg, self.world, self.comm.heap.table
+        Tr = (T + W - 1) // W
+        row0 = min(T, self.rank * Tr)
+        nloc = min(T, row0 + Tr) - row0
+        qd = self.Hq * self.hd
+        style = 0 if cfg.rope_style == "pairs" else 1
+        hbf = self.hbfull[:T]
+        hb_q = self.hb.view(-1)[: T * qd].view(T, qd)
+        hb_f = self.hb2[:T]
+        qkv = self.qkv[:T]
+        n = 0
+
+        def norm_gather(gain):
+            ops.rmsnorm_allgather(self.x, gain, cfg.norm_eps, row0, nloc, self.hbfull_off, table)
+            self._ag_epoch += 1
+
+        def gemm_scatter(a, w, bias=None):
+            N, K = w.shape
+            ops.gemm_bf16(a, w, T, N, K, lda=a.stride(0), ldb=K, ldc=self.d, bias=bias, status=self.status,
+                          sym_mode=ops.SYM_RSCATTER_ROWS, sym=table, sym_off=self.x_off, rows_per_rank=Tr)
+
+        for li, L in enumerate(self.layers):
+            norm_gather(L.attn_norm)
+            wq = self._dense(L.wqkv)
+            ops.gemm_bf16(hbf, wq, T, L.wqkv.N, L.wqkv.K, lda=self.d, ldb=L.wqkv.K, out_f32=qkv, ldc=L.wqkv.N, bias=L.bqkv,
+                          status=self.status, sym=table, ag_rows_per_rank=Tr, ag_epoch=self._ag_epoch)
+            ops.rope_kv(qkv, self.pos, self.slot, None, self.q16, self.kc[li], self.vc[li], self.Hq, self.Hkv, self.hd,
+                        PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd), table=self.rope_tab)
+            if self.hd == 128 and self.prefill_tc05:
+                ops.attn_prefill_tc05(self.q16, self.kc[li], self.vc[li], self.page_table, self.q_start, self.q_len,
+                                      self.seq_lens, n_seqs, max_q, self.Hq, self.Hkv, window=L.window, sinks=L.sinks,
+                                      out_bf16=hb_q, status=self.status)
+            else:
+                ops.attn_prefill(self.q16, self.kc[li], self.vc[li], self.page_table, self.max_pages, self.q_start,
+                                 self.q_len, self.seq_lens, n_seqs, max_q, self.Hq, self.Hkv, self.hd, window=L.window,
+                                 sinks=L.sinks, out_bf16=hb_q)
+            gemm_scatter(hb_q, self._dense(L.wo), bias=L.bo)
+            norm_gather(L.ffn_norm)
+            if self.use_shadow:
+                ops.gemm_bf16(hbf, L.wgu.ensure_pair_shadow(), T, 2 * self.F, L.wgu.K, lda=self.d, ldb=L.wgu.K, out_bf16=hb_f,
+                              ldc=self.F, act=ops.ACT_SWIGLU_PAIR, status=self.status, sym=table, ag_rows_per_rank=Tr,
+                              ag_epoch=self._ag_epoch)
+                n += 8
+            else:
+                ops.gemm_bf16(hbf, self._dense(L.wgu), T, L.wgu.N, L.wgu.K, lda=self.d, ldb=L.wgu.K, out_f32=self.gu[:T],
+                              ldc=L.wgu.N, status=self.status, sym=table, ag_rows_per_rank=Tr, ag_epoch=self._ag_epoch)
+                ops.swiglu(self.gu[:T], self.F, ob=hb_f)
+                n += 9
+            gemm_scatter(hb_f, self._dense(L.wdown))
+        # every rank's rows back into every replica (whole blocks of Tr rows; the tensor has world spare rows)
+        self.comm.heap.all_gather(self.x_off + self.rank * Tr * self.d * 4, self.x_off, Tr * self.d * 4)
+        return n + 1
 
     def _ffn_hf(self, T: int):
         """fp32 copy of the normalised hidden state, for feed-forward blocks that want one."""

@@ -15,7 +15,7 @@ from .. import _native
 
 WT_Q4KR, WT_Q6KR, WT_Q8R, WT_BF16, WT_MXFP4R = 0, 1, 2, 3, 4
 EPI_STORE, EPI_RESID, EPI_SWIGLU_Q8, EPI_SWIGLU_F32, EPI_ALLREDUCE = 0, 1, 2, 3, 4
-SYM_NONE, SYM_ALLREDUCE, SYM_RSCATTER = 0, 1, 2
+SYM_NONE, SYM_ALLREDUCE, SYM_RSCATTER, SYM_RSCATTER_ROWS = 0, 1, 2, 3
 EMB_F32, EMB_BF16, EMB_Q8R, EMB_Q6KR = 0, 1, 2, 3
 ACT_NONE, ACT_GELU, ACT_SWIGLU_PAIR = 0, 1, 2
 
@@ -23,6 +23,7 @@ _P = c_void_p
 _SIGS = {
     "b200_embedding": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, c_int, _P],
     "b200_rmsnorm": [_P, _P, c_float, c_int, c_int, _P, _P, _P, _P, _P, _P, _P],
+    "b200_rmsnorm_allgather": [_P, _P, c_float, c_int, c_int, c_int, c_size_t, _P, _P],
     "b200_quantize_x": [_P, c_int, c_int, _P, _P, _P, _P],
     "b200_rope_kv": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, _P, c_int, _P],
     "b200_rope_table": [_P, c_int, c_int, c_float, _P],
@@ -37,7 +38,7 @@ _SIGS = {
     "b200_attn_prefill": [_P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
     "b200_attn_prefill_tc05": [_P, _P, _P, _P, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
     "b200_gemm_bf16": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int,
-                       _P, c_int, _P, c_size_t, c_int, c_int, _P],
+                       _P, c_int, _P, c_size_t, c_int, c_int, c_int, c_int, _P],
     "b200_moe_gemm": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P, c_int, _P, _P, _P, c_size_t, _P, _P],
     "b200_moe_route_dispatch": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_size_t, c_size_t, c_size_t, c_size_t,
                                 _P, _P, _P, _P, _P],
@@ -101,6 +102,12 @@ def rmsnorm(x, g, eps, xq=None, xd=None, xs16=None, hb=None, hf=None, signal_sym
     finished reading ``x`` (the handshake the fused all-reduce kernels check with ``wait_ready``)."""
     T, D = x.shape
     _check(lib().b200_rmsnorm(_p(x), _p(g), eps, T, D, _p(xq), _p(xd), _p(xs16), _p(hb), _p(hf), _sym(signal_sym), _st()), "rmsnorm")
+
+
+def rmsnorm_allgather(x, g, eps, row0, n_rows, hb_off, sym):
+    """Normalise rows [row0, row0 + n_rows) of ``x`` (fp32 [*, D]) and push them as bf16 into every rank's
+    [*, D] tensor at byte offset ``hb_off`` of the symmetric heap; ends by bumping this rank's all-gather counter."""
+    _check(lib().b200_rmsnorm_allgather(_p(x), _p(g), eps, row0, n_rows, x.shape[1], hb_off, _sym(sym), _st()), "rmsnorm_allgather")
 
 
 def quantize_x(x, xq, xd, xs16):
@@ -182,11 +189,12 @@ def attn_prefill_tc05(q16, kc, vc, page_table, q_start, q_len, ctx_len, n_seqs, 
 
 def gemm_bf16(A, B, M, N, K, lda=None, ldb=None, out_f32=None, out_bf16=None, ldc=None, bias=None, resid_f32=None,
               resid_bf16=None, act=ACT_NONE, accumulate=False, tile_n=0, status=None, sym_mode=SYM_NONE, sym=None,
-              sym_off=0, rows_per_rank=0, split_k=0, wait_ready=False):
-    """D[M][N] = A[M][K] @ B[N][K]^T with fused epilogue (see ``gemm_tc05.cu``)."""
+              sym_off=0, rows_per_rank=0, split_k=0, wait_ready=False, ag_rows_per_rank=0, ag_epoch=0):
+    """D[M][N] = A[M][K] @ B[N][K]^T with fused epilogue (see ``gemm_tc05.cu``).  ``ag_rows_per_rank`` > 0: the rows
+    of A are all-gathered by push (``rmsnorm_allgather``) and each tile waits for its owners' counter to reach ``ag_epoch``."""
     _check(lib().b200_gemm_bf16(_p(A), _p(B), M, N, K, lda or K, ldb or K, _p(out_f32), _p(out_bf16), ldc or N,
                                 _p(bias), _p(resid_f32), _p(resid_bf16), act, int(accumulate), tile_n, split_k, _p(status),
-                                sym_mode, _sym(sym), sym_off, rows_per_rank, int(wait_ready), _st()), "gemm_bf16")
+                                sym_mode, _sym(sym), sym_off, rows_per_rank, int(wait_ready), ag_rows_per_rank, ag_epoch, _st()), "gemm_bf16")
 
 
 def set_pdl(on: bool):

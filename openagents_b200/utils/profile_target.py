@@ -4,11 +4,12 @@
 
 Each case sets up one kernel on a problem that is larger than L2 but holds well under a gigabyte on
 the device, launches it a few times and exits, so a capture with ``ncu -k regex:<kernel> -c 1`` ends
-by itself in seconds.  Cases: qgemm64, qgemm_lm, gemm, matvec, attn_decode, attn_prefill, and
+by itself in seconds.  Cases: qgemm64, qgemm_lm, gemm, matvec, attn_decode, attn_prefill, attn_prefill_tc05, and
 ``step64`` / ``step1``: whole decode steps (batch 64 / 1, context 2048) of a 4-layer Llama-3-8B-shape
 engine without graphs, for a per-kernel launch list; ``moe_step``: the same for a 2-layer gpt-oss-20b-shape
 expert engine at batch 256; ``moe_ffn``: one expert layer at 4096 tokens; ``gemm_ar64`` / ``gemm_ar2048``: the
-row-parallel GEMM with its fused all-reduce epilogue; ``zero_adamw``: the sharded optimizer step.
+row-parallel GEMM with its fused all-reduce epilogue; ``gemm_ag2048`` / ``gemm_rs2048``: the sequence-sharded prefill
+pair (norm + all-gather push -> GEMM, GEMM -> reduce-scatter); ``zero_adamw``: the sharded optimizer step.
 """
 from __future__ import annotations
 
@@ -58,7 +59,7 @@ def main():
         scratch = torch.empty(ops.attn_decode_scratch_floats(B, Hq, Hkv, hd, S), device=DEV)
         counters = torch.zeros(B * Hkv, dtype=torch.int32, device=DEV)
         fn = lambda: ops.attn_decode(q, kc, vc, table, lens, B, Hq, Hkv, hd, S=S, out_bf16=out, scratch=scratch, counters=counters)
-    elif case == "attn_prefill":
+    elif case in ("attn_prefill", "attn_prefill_tc05"):
         T, Hq, Hkv, hd = 2048, 32, 8, 128
         pages = T // 16
         kc = torch.randn((pages + 1, Hkv, 16, hd), device=DEV).half()
@@ -67,7 +68,10 @@ def main():
         q = (torch.randn(T, Hq * hd, device=DEV) / math.sqrt(hd)).half()
         out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=DEV)
         z, tl = torch.zeros(1, dtype=torch.int32, device=DEV), torch.full((1,), T, dtype=torch.int32, device=DEV)
-        fn = lambda: ops.attn_prefill(q, kc, vc, table, pages, z, tl, tl, 1, T, Hq, Hkv, hd, out_bf16=out)
+        if case == "attn_prefill":
+            fn = lambda: ops.attn_prefill(q, kc, vc, table, pages, z, tl, tl, 1, T, Hq, Hkv, hd, out_bf16=out)
+        else:
+            fn = lambda: ops.attn_prefill_tc05(q, kc, vc, table, z, tl, tl, 1, T, Hq, Hkv, out_bf16=out, status=status)
     elif case in ("step64", "step1"):
         from ..models.config import LLAMA3_8B
         from ..models.engine import LlamaEngine
@@ -127,6 +131,32 @@ def main():
         xh, _ = comm.alloc_tensor((M, N), torch.float32)
         A, B = torch.randn(M, K, device=DEV).bfloat16(), torch.randn(N, K, device=DEV).bfloat16()
         fn = lambda: comm.gemm_allreduce(A, B, M, xh, status=status)
+    elif case in ("gemm_ag2048", "gemm_rs2048"):
+        # sequence-sharded prefill pair on a one-rank heap: norm + all-gather push -> QKV GEMM that waits for the
+        # rows' owners tile by tile; output GEMM with the reduce-scatter in its epilogue
+        from ..parallel.tp import TPComm
+        M, d = 2048, 4096
+        comm = TPComm(0, 1, DEV, heap_bytes=M * d * 8 + (1 << 20))
+        xh, x_off = comm.alloc_tensor((M, d), torch.float32)
+        hbf, hb_off = comm.alloc_tensor((M, d), torch.bfloat16)
+        xh.normal_()
+        gain = torch.ones(d, device=DEV)
+        table = comm.heap.table
+        if case == "gemm_ag2048":
+            N = 6144
+            B = torch.randn(N, d, device=DEV).bfloat16()
+            out = torch.empty((M, N), device=DEV)
+            epoch = [0]
+
+            def fn():
+                ops.rmsnorm_allgather(xh, gain, 1e-5, 0, M, hb_off, table)
+                epoch[0] += 1
+                ops.gemm_bf16(hbf, B, M, N, d, out_f32=out, status=status, sym=table, ag_rows_per_rank=M, ag_epoch=epoch[0])
+        else:
+            K = 4096
+            A, B = torch.randn(M, K, device=DEV).bfloat16(), torch.randn(d, K, device=DEV).bfloat16()
+            fn = lambda: ops.gemm_bf16(A, B, M, d, K, ldc=d, status=status, sym_mode=ops.SYM_RSCATTER_ROWS, sym=table,
+                                       sym_off=x_off, rows_per_rank=M)
     elif case == "zero_adamw":
         # sharded AdamW step on GPT-2-small's 124M parameters, one-rank heap: reduce-scatter + norm, then
         # clip + AdamW + bf16 cast + all-gather push
@@ -149,13 +179,16 @@ def main():
         raise SystemExit(f"unknown case {case}")
     fn()                                  # warm-up outside the profiled range
     torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.profiler.start()           # honoured by `ncu --profile-from-start off`
+    e0.record()
     for _ in range(n):
         fn()
+    e1.record()
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
     assert int(status.item()) == 0
-    print("ok", case)
+    print("ok", case, f"{e0.elapsed_time(e1) * 1000 / n:.1f} us per call (CUDA events, {n} calls back to back; not valid under a profiler)")
 
 
 if __name__ == "__main__":

@@ -289,10 +289,13 @@ def test_attn_prefill(hd, Hq, Hkv, window, use_sinks):
         assert torch.allclose(outb[s:s + n].float().cpu(), ref, atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("Hq,Hkv,window,use_sinks", [(4, 2, 0, False), (8, 2, 96, True), (2, 2, 0, True)])
-def test_attn_prefill_tc05(Hq, Hkv, window, use_sinks):
+@pytest.mark.parametrize("Hq,Hkv,window,use_sinks,qk_gain", [(4, 2, 0, False, 1.0), (8, 2, 96, True, 1.0), (2, 2, 0, True, 1.0),
+                                                             (4, 2, 0, True, 6.0), (4, 4, 160, False, 5.0)])
+def test_attn_prefill_tc05(Hq, Hkv, window, use_sinks, qk_gain):
     """tcgen05 prefill attention (head dim 128) against the fp32 oracle: cold prefill longer than one query
-    tile, a chunk on top of cached context, a one-token chunk, and a sequence that ends mid key block."""
+    tile, a chunk on top of cached context, a one-token chunk, and a sequence that ends mid key block.
+    ``qk_gain`` > 1 spreads the scores (standard deviation ~ gain), so that row maxima keep jumping by more
+    than the kernel's rescale step and the in-tensor-memory rescale of the output rows runs many times."""
     from openagents_b200.oracle import nn
     ops = _ops()
     hd = 128
@@ -301,7 +304,7 @@ def test_attn_prefill_tc05(Hq, Hkv, window, use_sinks):
     B = len(ctx)
     kc, vc, table, Ks, Vs = _paged_kv(B, Hkv, hd, ctx, seed=35)
     T = sum(qlen)
-    q = (_randn(T, Hq * hd, seed=36) * (1.0 / math.sqrt(hd))).half()
+    q = (_randn(T, Hq * hd, seed=36) * (qk_gain / math.sqrt(hd))).half()
     sinks = _randn(Hq, seed=37) if use_sinks else None
     starts = [sum(qlen[:b]) for b in range(B)]
     q_start = torch.tensor(starts, dtype=torch.int32, device=DEV)

@@ -119,7 +119,7 @@ def _tp_engine(rank, world, path):
     dev = torch.device("cuda", rank)
     comm = TPComm(rank, world, dev, heap_bytes=64 << 20)
     src = GGUFSource(path, dev)
-    eng = LlamaEngine(src.cfg, src, device=dev, max_batch=16, max_ctx=128, max_tokens=256, tp_rank=rank, tp_world=world,
+    eng = LlamaEngine(src.cfg, src, device=dev, max_batch=16, max_ctx=320, max_tokens=320, tp_rank=rank, tp_world=world,
                       comm=comm)
     cfg, W = load_gguf_float(path)
     g = torch.Generator().manual_seed(2)
@@ -146,6 +146,25 @@ def _tp_engine(rank, world, path):
         got = full_logits(logits)
         assert (got - ref).abs().max().item() < 0.08 * scale, (step, (got - ref).abs().max().item())
         assert nxt.tolist() == got.argmax(-1).tolist()
+        toks = ref.argmax(-1).tolist()
+    # long prompts: sequence-sharded prefill (norm + all-gather push -> GEMM, GEMM -> reduce-scatter), an odd total
+    # so that the ranks own different numbers of rows, then decode on the replicated stream again
+    long = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in (201, 78)]
+    assert eng._seq_sharded(sum(len(p) for p in long), False)
+    for b in (3, 4):
+        eng.begin(b)
+    logits, nxt = eng.forward_tokens([3, 4], [p.tolist() for p in long])
+    caches = [KVCacheRef(cfg.n_layers) for _ in range(2)]
+    ref = torch.stack([llama_forward(cfg, W, long[b], caches[b])[-1] for b in range(2)])
+    got = full_logits(logits)
+    assert (got - ref).abs().max().item() < 0.08 * scale, (got - ref).abs().max().item()
+    assert nxt.tolist() == got.argmax(-1).tolist()
+    toks = ref.argmax(-1).tolist()
+    for step in range(2):
+        logits, nxt = eng.decode([3, 4], toks, use_graph=False)
+        ref = torch.stack([llama_forward(cfg, W, torch.tensor([toks[b]]), caches[b])[-1] for b in range(2)])
+        got = full_logits(logits)
+        assert (got - ref).abs().max().item() < 0.08 * scale, (step, (got - ref).abs().max().item())
         toks = ref.argmax(-1).tolist()
     eng.check_status()
     assert comm.heap.status() == (0, 0)
