@@ -7,10 +7,13 @@
 //   S_j = Q K_j^T        tcgen05.mma 128 x 64 x 128 into one of two S accumulators in tensor memory
 //   softmax              S_j -> registers (tcgen05.ld), mask, running max / sum, P_j (fp16) -> shared
 //                        memory in the 128-byte-swizzled K-major layout the next MMA reads
-//   PV_j = P_j V_j       tcgen05.mma 128 x 128 x 64 into one of two O accumulators, V taken as it lies
-//                        in the cache ([key][dim], i.e. the MN-major form of the B operand)
-//   O += rescaled PV_j   PV_j -> registers, one iteration later, so that S_{j+1} and PV_j overlap the
-//                        softmax arithmetic
+//   O += P_j V_j         tcgen05.mma 128 x 128 x 64 accumulating in ONE O tile that stays in tensor memory
+//                        for the whole row block, V taken as it lies in the cache ([key][dim], i.e. the
+//                        MN-major form of the B operand)
+// The exponent offset of a row (its running maximum) is only moved when the maximum has grown by more
+// than 8 (a factor 256, well inside fp16 for P and fp32 for O and the row sum); then the row's owner
+// thread rescales the O row in tensor memory (tcgen05.ld / st) between two PV products.  After the
+// first key blocks of a causal row that is rare, so the steady state has no O traffic at all.
 // Sliding windows, learned sink logits and a context that is longer than the chunk (chunked prefill,
 // prefix reuse) are handled by the mask and the block range.  Math as in the reference's attention
 // (apps/openagents.com/workers/api/src/cs336-a1-real-gradient-workload.ts:478-518: max-subtract,
@@ -27,7 +30,8 @@ constexpr int QB = 128, KB = 64, HD = 128, KV_STAGES = 3;
 constexpr int Q_BYTES = QB * HD * 2;            // 32 KB: two halves of [128 rows][64 dims]
 constexpr int K_BYTES = KB * HD * 2;            // 16 KB: two halves of [64 keys][64 dims]
 constexpr int P_BYTES = QB * KB * 2;            // 16 KB: [128 rows][64 keys]
-constexpr uint32_t TMEM_COLS = 512;             // S: 2 x 64, O: 2 x 128
+constexpr uint32_t TMEM_COLS = 256;             // S: 2 x 64, O: 128
+constexpr float kRescaleStep = 8.f;             // log2 units
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct PrefillArgs {
@@ -57,6 +61,29 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint3
   return d;
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                     const __grid_constant__ CUtensorMap tmK,
                                                                     const __grid_constant__ CUtensorMap tmV,
@@ -73,9 +100,8 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
   uint64_t* s_full = kv_empty + KV_STAGES;                // [2]
   uint64_t* s_empty = s_full + 2;                         // [2]
   uint64_t* p_full = s_empty + 2;                         // [2]
-  uint64_t* o_full = p_full + 2;                          // [2]
-  uint64_t* o_empty = o_full + 2;                         // [2]
-  uint32_t* tmem_holder = (uint32_t*)(o_empty + 2);
+  uint64_t* o_done = p_full + 2;                          // [1]: one phase per PV product
+  uint32_t* tmem_holder = (uint32_t*)(o_done + 2);
   volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
 
   const int seq = blockIdx.z, h = blockIdx.y, qb = gridDim.x - 1 - blockIdx.x;   // longest (latest) query blocks first
@@ -91,9 +117,8 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
       mbar_init(smem_u32(s_full + s), 1);
       mbar_init(smem_u32(s_empty + s), 4);
       mbar_init(smem_u32(p_full + s), 4);
-      mbar_init(smem_u32(o_full + s), 1);
-      mbar_init(smem_u32(o_empty + s), 4);
     }
+    mbar_init(smem_u32(o_done), 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmQ);
@@ -121,7 +146,7 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
   const int k_lo = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
   const int jb0 = k_lo / KB, jb1 = live ? (k_hi + KB - 1) / KB : jb0;   // key blocks [jb0, jb1)
   const int nb = jb1 - jb0;
-  const uint32_t S_T = tmem_base, O_T = tmem_base + 128;   // S buffers at +0, +64; O buffers at +128, +256
+  const uint32_t S_T = tmem_base, O_T = tmem_base + 128;   // S buffers at +0, +64; O at +128
 
   if (warp == 0) {
     if (lane == 0 && nb > 0) {
@@ -155,19 +180,18 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
       constexpr uint32_t idesc_s = idesc_f16(QB, KB, false);
       constexpr uint32_t idesc_o = idesc_f16(QB, HD, true);
       bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag);
-      auto issue_pv = [&](int j) -> bool {        // O[j & 1] = P_j V_j, then release K/V stage of block j
+      auto issue_pv = [&](int j) -> bool {        // O += P_j V_j, then release K/V stage of block j
         const int s = j % KV_STAGES, b = j & 1;
         const uint32_t ph2 = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(p_full + b), ph2, abort_flag)) return false;
-        if (!mbar_wait(smem_u32(o_empty + b), ph2 ^ 1, abort_flag)) return false;
+        if (!mbar_wait(smem_u32(p_full + b), ph2, abort_flag)) return false;   // P_j written, O row rescaled if needed
         tc_fence_after();
         const uint32_t pa = smem_u32(sP + b * P_BYTES);
         const uint32_t va = smem_u32(sKV + (size_t)s * 2 * K_BYTES + K_BYTES);
 #pragma unroll
         for (int kk = 0; kk < KB / 16; kk++)
-          umma_bf16(O_T + b * 128, smem_desc_sw128(pa) + 2 * kk, smem_desc_sw128_mn(va + kk * 2048, K_BYTES / 2), idesc_o,
-                    kk != 0 ? 1u : 0u);
-        umma_commit(smem_u32(o_full + b));
+          umma_bf16(O_T, smem_desc_sw128(pa) + 2 * kk, smem_desc_sw128_mn(va + kk * 2048, K_BYTES / 2), idesc_o,
+                    (j != 0 || kk != 0) ? 1u : 0u);
+        umma_commit(smem_u32(o_done));
         umma_commit(smem_u32(kv_empty + s));
         return true;
       };
@@ -191,30 +215,8 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
     const int row = q * 32 + lane;               // query row of this thread
     const int qpos = pos0 + row;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
-    float o[HD];
-#pragma unroll
-    for (int i = 0; i < HD; i++) o[i] = 0.f;
+    float m_used = -INFINITY, l = 0.f;     // exponent offset of this row (log2 units) and the row sum under it
     bool ok = true;
-
-    auto accumulate = [&](int j, float alpha) {   // O = O * alpha + PV_j
-      const int b = j & 1;
-      ok = mbar_wait(smem_u32(o_full + b), (j >> 1) & 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok && !*abort_flag);
-      if (!ok) return;
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < HD / 32; c++) {
-        uint32_t r[32];
-        tmem_ld32(O_T + b * 128 + lane_addr + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(r[i]);
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(o_empty + b));
-    };
 
     for (int j = 0; j < nb; j++) {
       const int b = j & 1;
@@ -237,21 +239,50 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(s_empty + b));
-      // mask and running max
+      // mask, block maximum
       const int kb0 = (jb0 + j) * KB;
       const bool edge = kb0 + KB - 1 > pos0 || kb0 + KB > ctx || (a.window > 0 && kb0 < pos0 + QB - a.window);
-      float mx = m;
+      if (edge) {
 #pragma unroll
-      for (int i = 0; i < KB; i++) {
-        if (edge) {
+        for (int i = 0; i < KB; i++) {
           const int kp = kb0 + i;
           if (kp > qpos || kp >= ctx || (a.window > 0 && kp <= qpos - a.window)) sv[i] = -INFINITY;
         }
-        mx = fmaxf(mx, sv[i]);
       }
-      const float alpha = (mx == -INFINITY) ? 1.f : exp2f((m - mx) * kLog2e);
-      const float mref = (mx == -INFINITY) ? 0.f : mx;
-      float sum = 0.f;
+      float bmax = fmaxf(sv[0], sv[1]);
+#pragma unroll
+      for (int i = 2; i < KB; i += 2) bmax = max3(bmax, sv[i], sv[i + 1]);
+      bmax *= kLog2e;
+      // move the exponent offset only when it is far behind (or not set yet)
+      const bool unset = m_used == -INFINITY;
+      const bool behind = bmax > m_used + kRescaleStep;          // false while bmax is -inf
+      if (j > 0 && __any_sync(0xffffffffu, behind && !unset)) {
+        // some row of this warp has O and l under an offset that is too small: rescale (all lanes take part,
+        // tcgen05.ld / st are warp-wide; a lane that is not behind multiplies by one or, if unset, by zero its zero row)
+        const float m_new = fmaxf(m_used, bmax);
+        const float scale = (m_new == -INFINITY) ? 1.f : ex2_approx(m_used - m_new);
+        ok = mbar_wait(smem_u32(o_done), (j - 1) & 1, abort_flag);       // PV_{j-1} has finished
+        ok = __all_sync(0xffffffffu, ok && !*abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < HD / 32; c++) {
+          uint32_t r[32];
+          tmem_ld32(O_T + lane_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * scale);
+          tmem_st32(O_T + lane_addr + c * 32, r);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        l *= scale;
+        m_used = m_new;
+      } else if (unset) {
+        m_used = bmax;                             // nothing accumulated yet under the old offset (O row and l are zero)
+      }
+      const float off = (m_used == -INFINITY) ? 0.f : m_used;
+      float sum0 = 0.f, sum1 = 0.f;
       // P row: 64 fp16 = 8 chunks of 16 bytes, chunk c of row r at r * 128 + ((c ^ (r & 7)) * 16)
       uint8_t* prow = sP + b * P_BYTES + row * 128;
 #pragma unroll
@@ -259,38 +290,45 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
         uint32_t w[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-          const float p0 = exp2f((sv[c * 8 + 2 * i] - mref) * kLog2e), p1 = exp2f((sv[c * 8 + 2 * i + 1] - mref) * kLog2e);
+          const float p0 = ex2_approx(fmaf(sv[c * 8 + 2 * i], kLog2e, -off)), p1 = ex2_approx(fmaf(sv[c * 8 + 2 * i + 1], kLog2e, -off));
+          sum0 += p0;
+          sum1 += p1;
           const __half2 hh = __floats2half2_rn(p0, p1);
-          // sum what the tensor core will actually multiply (the rounded values)
-          sum += __low2float(hh) + __high2float(hh);
           w[i] = *(const uint32_t*)&hh;
         }
         *(uint4*)(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      l = l * alpha + sum;
-      m = mx;
+      l += sum0 + sum1;
       fence_proxy_async_smem();                  // P must be visible to the tensor core's (async proxy) reads
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(p_full + b));
-      if (j > 0) {
-        accumulate(j - 1, alpha_prev);
-        if (!ok) break;
-      }
-      alpha_prev = alpha;
     }
-    if (ok) accumulate(nb - 1, alpha_prev);
-    if (ok && row < qlen - q0) {
-      if (a.sinks && m != -INFINITY) l += exp2f((a.sinks[h] - m) * kLog2e);
-      else if (a.sinks && m == -INFINITY) l += 1.f;
+    if (ok) {
+      ok = mbar_wait(smem_u32(o_done), (nb - 1) & 1, abort_flag);          // last PV product
+      ok = __all_sync(0xffffffffu, ok && !*abort_flag);
+    }
+    if (ok) {
+      tc_fence_after();
+      if (a.sinks) l += (m_used == -INFINITY) ? 1.f : ex2_approx(a.sinks[h] * kLog2e - m_used);
       const float inv = l > 0.f ? 1.f / l : 0.f;
+      const bool wr = row < qlen - q0;
       __nv_bfloat16* dst = a.out + (size_t)(qs + q0 + row) * a.Hq * HD + (size_t)h * HD;
 #pragma unroll
-      for (int i = 0; i < HD; i += 8) {
-        uint4 v;
-        __nv_bfloat162* p = (__nv_bfloat162*)&v;
+      for (int c = 0; c < HD / 32; c++) {
+        uint32_t r[32];
+        tmem_ld32(O_T + lane_addr + c * 32, r);
+        tmem_ld_wait();
+        if (wr) {
 #pragma unroll
-        for (int k = 0; k < 4; k++) p[k] = __floats2bfloat162_rn(o[i + 2 * k] * inv, o[i + 2 * k + 1] * inv);
-        *(uint4*)(dst + i) = v;
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            __nv_bfloat162* p = (__nv_bfloat162*)&v;
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+              p[k] = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * k]) * inv, __uint_as_float(r[i + 2 * k + 1]) * inv);
+            *(uint4*)(dst + c * 32 + i) = v;
+          }
+        }
       }
     }
   }
