@@ -222,7 +222,9 @@ __device__ __forceinline__ bool sym_wait_ready(const SymTable& T) {
 constexpr int kSymAgCh0 = 8;   // channels 8 .. 8 + kMaxRanks - 1
 
 __device__ __forceinline__ void sym_signal_rows(const SymTable& T, int n_ctas) {
-  __threadfence_system();        // this thread's pushes are visible system-wide before the counter moves
+  // The CTA barrier orders every thread's pushes before thread 0's system-scope fence and release below
+  // (release is cumulative), so the threads need no system fence of their own, which would cost each of
+  // them a round trip to the peers.
   __syncthreads();
   if (threadIdx.x == 0) {
     SymControl* me = sym_ctl(T, T.rank);

@@ -2,8 +2,10 @@
 //
 // One CTA = 128 query rows of one head.  Roles: warp 0 is the TMA producer (Q once, then a ring of
 // K/V blocks of 64 keys gathered page by page from the paged fp16 cache), warp 1 issues tcgen05.mma,
-// warps 2..5 (128 threads, one query row each) do the online softmax and keep the output row in
-// registers.  Per key block j:
+// warps 2..9 do the online softmax: two warps per 32 query rows (the two share a tensor-memory lane
+// quarter), one taking keys 0..31 of a block and output columns 0..63, the other the rest; they swap
+// their partial row maxima through shared memory once per block.  Two warps per scheduler is what
+// hides the latencies of tensor-memory loads, exponentials and barriers.  Per key block j:
 //   S_j = Q K_j^T        tcgen05.mma 128 x 64 x 128 into one of two S accumulators in tensor memory
 //   softmax              S_j -> registers (tcgen05.ld), mask, running max / sum, P_j (fp16) -> shared
 //                        memory in the 128-byte-swizzled K-major layout the next MMA reads
@@ -84,7 +86,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-__global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
+__global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                     const __grid_constant__ CUtensorMap tmK,
                                                                     const __grid_constant__ CUtensorMap tmV,
                                                                     const PrefillArgs a) {
@@ -101,8 +103,10 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
   uint64_t* s_empty = s_full + 2;                         // [2]
   uint64_t* p_full = s_empty + 2;                         // [2]
   uint64_t* o_done = p_full + 2;                          // [1]: one phase per PV product
-  uint32_t* tmem_holder = (uint32_t*)(o_done + 2);
+  uint64_t* x_full = o_done + 2;                          // [4 quarters][2]: both warps of a pair have posted their half
+  uint32_t* tmem_holder = (uint32_t*)(x_full + 8);
   volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+  float* xch = (float*)(bars + 32);                       // [2 (block parity)][2 (half)][128 rows] partial row maxima / sums
 
   const int seq = blockIdx.z, h = blockIdx.y, qb = gridDim.x - 1 - blockIdx.x;   // longest (latest) query blocks first
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -115,10 +119,11 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(smem_u32(s_full + s), 1);
-      mbar_init(smem_u32(s_empty + s), 4);
-      mbar_init(smem_u32(p_full + s), 4);
+      mbar_init(smem_u32(s_empty + s), 8);
+      mbar_init(smem_u32(p_full + s), 8);
     }
     mbar_init(smem_u32(o_done), 1);
+    for (int s = 0; s < 8; s++) mbar_init(smem_u32(x_full + s), 2);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmQ);
@@ -212,11 +217,20 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
     }
   } else if (nb > 0) {
     const int q = warp & 3;                      // tensor-memory lane quarter this warp may read
-    const int row = q * 32 + lane;               // query row of this thread
+    const int hsel = (warp - 2) >> 2;            // 0: keys 0..31 of a block, output columns 0..63; 1: the other half
+    const int row = q * 32 + lane;               // query row of this thread (shared with the partner warp's same lane)
     const int qpos = pos0 + row;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    float m_used = -INFINITY, l = 0.f;     // exponent offset of this row (log2 units) and the row sum under it
+    constexpr int HK = KB / 2, HO = HD / 2;
+    float m_used = -INFINITY, l = 0.f;     // exponent offset of this row (log2 units) and this warp's part of the row sum
     bool ok = true;
+    // post this warp's half and wait (bounded, like every wait here) for the partner's; use number `u` of buffer `bb`
+    auto pair_sync = [&](int bb, int u) -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(x_full + q * 2 + bb));
+      bool k = mbar_wait(smem_u32(x_full + q * 2 + bb), (uint32_t)u & 1, abort_flag);
+      return __all_sync(0xffffffffu, k && !*abort_flag);
+    };
 
     for (int j = 0; j < nb; j++) {
       const int b = j & 1;
@@ -224,41 +238,42 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
       ok = __all_sync(0xffffffffu, ok && !*abort_flag);
       if (!ok) break;
       tc_fence_after();
-      float sv[KB];
+      float sv[HK];
       {
         uint32_t r[32];
-        tmem_ld32(S_T + b * 64 + lane_addr, r);
+        tmem_ld32(S_T + b * 64 + lane_addr + hsel * HK, r);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i++) sv[i] = __uint_as_float(r[i]);
-        tmem_ld32(S_T + b * 64 + lane_addr + 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i++) sv[32 + i] = __uint_as_float(r[i]);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(s_empty + b));
-      // mask, block maximum
+      // mask, maximum of this half, swap with the partner warp
       const int kb0 = (jb0 + j) * KB;
       const bool edge = kb0 + KB - 1 > pos0 || kb0 + KB > ctx || (a.window > 0 && kb0 < pos0 + QB - a.window);
       if (edge) {
 #pragma unroll
-        for (int i = 0; i < KB; i++) {
-          const int kp = kb0 + i;
+        for (int i = 0; i < HK; i++) {
+          const int kp = kb0 + hsel * HK + i;
           if (kp > qpos || kp >= ctx || (a.window > 0 && kp <= qpos - a.window)) sv[i] = -INFINITY;
         }
       }
-      float bmax = fmaxf(sv[0], sv[1]);
+      float mx0 = fmaxf(sv[0], sv[1]), mx1 = fmaxf(sv[2], sv[3]);
 #pragma unroll
-      for (int i = 2; i < KB; i += 2) bmax = max3(bmax, sv[i], sv[i + 1]);
-      bmax *= kLog2e;
-      // move the exponent offset only when it is far behind (or not set yet)
+      for (int i = 4; i < HK; i += 4) {
+        mx0 = max3(mx0, sv[i], sv[i + 1]);
+        mx1 = max3(mx1, sv[i + 2], sv[i + 3]);
+      }
+      float* xb = xch + b * 256;
+      xb[hsel * 128 + row] = fmaxf(mx0, mx1);
+      ok = pair_sync(b, j >> 1);
+      if (!ok) break;
+      const float bmax = fmaxf(fmaxf(mx0, mx1), xb[(hsel ^ 1) * 128 + row]) * kLog2e;
+      // move the exponent offset only when it is far behind (or not set yet); both warps of a pair decide alike
       const bool unset = m_used == -INFINITY;
       const bool behind = bmax > m_used + kRescaleStep;          // false while bmax is -inf
       if (j > 0 && __any_sync(0xffffffffu, behind && !unset)) {
-        // some row of this warp has O and l under an offset that is too small: rescale (all lanes take part,
-        // tcgen05.ld / st are warp-wide; a lane that is not behind multiplies by one or, if unset, by zero its zero row)
         const float m_new = fmaxf(m_used, bmax);
         const float scale = (m_new == -INFINITY) ? 1.f : ex2_approx(m_used - m_new);
         ok = mbar_wait(smem_u32(o_done), (j - 1) & 1, abort_flag);       // PV_{j-1} has finished
@@ -266,13 +281,13 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < HD / 32; c++) {
+        for (int c = 0; c < HO / 32; c++) {
           uint32_t r[32];
-          tmem_ld32(O_T + lane_addr + c * 32, r);
+          tmem_ld32(O_T + lane_addr + hsel * HO + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * scale);
-          tmem_st32(O_T + lane_addr + c * 32, r);
+          tmem_st32(O_T + lane_addr + hsel * HO + c * 32, r);
         }
         tmem_st_wait();
         tc_fence_before();
@@ -282,23 +297,22 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
         m_used = bmax;                             // nothing accumulated yet under the old offset (O row and l are zero)
       }
       const float off = (m_used == -INFINITY) ? 0.f : m_used;
-      float sum0 = 0.f, sum1 = 0.f;
-      // P row: 64 fp16 = 8 chunks of 16 bytes, chunk c of row r at r * 128 + ((c ^ (r & 7)) * 16)
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+      // P row: 64 fp16 = 8 chunks of 16 bytes, chunk c of row r at r * 128 + ((c ^ (r & 7)) * 16); this warp: 4 chunks
       uint8_t* prow = sP + b * P_BYTES + row * 128;
 #pragma unroll
-      for (int c = 0; c < 8; c++) {
+      for (int c = 0; c < 4; c++) {
         uint32_t w[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
           const float p0 = ex2_approx(fmaf(sv[c * 8 + 2 * i], kLog2e, -off)), p1 = ex2_approx(fmaf(sv[c * 8 + 2 * i + 1], kLog2e, -off));
-          sum0 += p0;
-          sum1 += p1;
+          if (i & 1) { sum2 += p0; sum3 += p1; } else { sum0 += p0; sum1 += p1; }
           const __half2 hh = __floats2half2_rn(p0, p1);
           w[i] = *(const uint32_t*)&hh;
         }
-        *(uint4*)(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *(uint4*)(prow + (((hsel * 4 + c) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      l += sum0 + sum1;
+      l += (sum0 + sum1) + (sum2 + sum3);
       fence_proxy_async_smem();                  // P must be visible to the tensor core's (async proxy) reads
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(p_full + b));
@@ -307,16 +321,22 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc05_kernel(const __grid_
       ok = mbar_wait(smem_u32(o_done), (nb - 1) & 1, abort_flag);          // last PV product
       ok = __all_sync(0xffffffffu, ok && !*abort_flag);
     }
-    if (ok) {
+    // row sum = both halves (the partner is at the same point: every exit above is taken by whole CTAs' worth of
+    // warps only through the abort flag, in which case nothing is written)
+    if (__all_sync(0xffffffffu, ok)) {
+      float* xl = xch + (nb & 1) * 256;            // the buffer the last block did not use
+      xl[hsel * 128 + row] = l;
+      ok = pair_sync(nb & 1, nb >> 1);
+      l += xl[(hsel ^ 1) * 128 + row];
       tc_fence_after();
       if (a.sinks) l += (m_used == -INFINITY) ? 1.f : ex2_approx(a.sinks[h] * kLog2e - m_used);
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      const bool wr = row < qlen - q0;
-      __nv_bfloat16* dst = a.out + (size_t)(qs + q0 + row) * a.Hq * HD + (size_t)h * HD;
+      const bool wr = ok && row < qlen - q0;
+      __nv_bfloat16* dst = a.out + (size_t)(qs + q0 + row) * a.Hq * HD + (size_t)h * HD + hsel * HO;
 #pragma unroll
-      for (int c = 0; c < HD / 32; c++) {
+      for (int c = 0; c < HO / 32; c++) {
         uint32_t r[32];
-        tmem_ld32(O_T + lane_addr + c * 32, r);
+        tmem_ld32(O_T + lane_addr + hsel * HO + c * 32, r);
         tmem_ld_wait();
         if (wr) {
 #pragma unroll
@@ -358,7 +378,7 @@ B200_API int b200_attn_prefill_tc05(const void* q, const void* kc, const void* v
   PrefillArgs a;
   a.page_table = page_table; a.q_start = q_start; a.q_len = q_len; a.ctx_len = ctx_len; a.sinks = sinks;
   a.out = (__nv_bfloat16*)out; a.status = status; a.max_pages = max_pages; a.Hq = Hq; a.Hkv = Hkv; a.window = window;
-  constexpr size_t smem = 1024 + Q_BYTES + KV_STAGES * 2 * K_BYTES + 2 * P_BYTES + 32 * 8;
+  constexpr size_t smem = 1024 + Q_BYTES + KV_STAGES * 2 * K_BYTES + 2 * P_BYTES + 32 * 8 + 2 * 2 * 128 * 4;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -366,5 +386,5 @@ B200_API int b200_attn_prefill_tc05(const void* q, const void* kc, const void* v
     configured = true;
   }
   dim3 grid((max_q + QB - 1) / QB, Hq, n_seqs);
-  return launch_pdl(attn_prefill_tc05_kernel, grid, dim3(192), smem, st, tq, tk, tv, a);
+  return launch_pdl(attn_prefill_tc05_kernel, grid, dim3(320), smem, st, tq, tk, tv, a);
 }

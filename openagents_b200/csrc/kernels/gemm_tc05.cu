@@ -337,14 +337,19 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, in
 // Persistent kernel: each CTA walks output tiles (m fastest) with a shared-memory ring that keeps
 // running across tiles and two accumulator stages in tensor memory, so the epilogue of one tile
 // overlaps the main loop of the next.
-template <int BN, int STAGES>
+// AROWS = 64 (at most 64 rows of A in all): the TMA box of A is 64 rows and a stage keeps only those
+// 8 KB; the MMA still reads a 128-row operand, whose upper half is whatever follows in shared memory
+// (the next stage); rows are independent and rows >= M are never written, so that is harmless, and the
+// 8 KB saved per stage buy more stages, i.e. more weight bytes in flight per SM, which is what bounds a
+// GEMM with few rows (bytes in flight = bandwidth x latency).
+template <int BN, int STAGES, int AROWS>
 __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
                                                          const __grid_constant__ CUtensorMap tmB,
                                                          const GemmEpi epi, int M, int N, int K, int splits,
                                                          int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+  constexpr int A_BYTES = AROWS * BK * 2, B_BYTES = BN * BK * 2;
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_BYTES;
   uint64_t* bars = (uint64_t*)(sB + STAGES * B_BYTES);
@@ -416,7 +421,11 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       bool ok = true;
       for (int item = blockIdx.x; item < n_tiles && ok; item += gridDim.x) {
         const int tile = item / splits, sp = item - tile * splits;
-        const int m0 = epi.group_rows ? live_m[tile % tiles_m] : ((tile % tiles_m + m_rot) % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        // Dense: m fastest (B tile shared by the CTAs of a wave).  Grouped: n fastest, so that the CTAs of a wave
+        // sweep the few row tiles of ONE expert across all its columns: that expert's weights and rows are
+        // read from HBM once and stay in L2, instead of every expert's rows being re-read for each column tile.
+        const int m0 = epi.group_rows ? live_m[tile / tiles_n] : ((tile % tiles_m + m_rot) % tiles_m) * BM;
+        const int n0 = epi.group_rows ? (tile % tiles_n) * BN : (tile / tiles_m) * BN;
         if (epi.ag_rows_per_rank) {       // rows of this tile come from their owners' all-gather pushes
           const int o0 = m0 / epi.ag_rows_per_rank, o1 = min(m0 + BM - 1, M - 1) / epi.ag_rows_per_rank;
           for (int o = o0; o <= o1 && ok; o++) {
@@ -479,7 +488,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     uint32_t tcount = 0;
     for (int item = blockIdx.x; item < n_tiles; item += gridDim.x) {
       const int tile = item / splits, sp = item - tile * splits;
-      const int m0 = epi.group_rows ? live_m[tile % tiles_m] : ((tile % tiles_m + m_rot) % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int m0 = epi.group_rows ? live_m[tile / tiles_n] : ((tile % tiles_m + m_rot) % tiles_m) * BM;
+      const int n0 = epi.group_rows ? (tile % tiles_n) * BN : (tile / tiles_m) * BN;
       int live_end = M;                       // rows below this index are written
       if (epi.group_rows) {
         const int g = m0 / epi.group_rows;
@@ -532,12 +542,24 @@ static int sm_count() {
   return n;
 }
 
-template <int BN, int STAGES>
+static bool gemm_deep_enabled() {      // B200_GEMM_DEEP=0: measurement aid, the 128-row box for every M
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("B200_GEMM_DEEP");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+template <int BN, int STAGES, int AROWS = 128>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpi& e, int M, int N, int K,
                        int splits, int* status, cudaStream_t st) {
-  constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 6) * 8 + 4 * 32 * 32 * 4 +
-                          kMaxLiveTiles * 4;
-  auto kern = gemm_bf16_kernel<BN, STAGES>;
+  // AROWS = 64: no tile list (never grouped); the last stage's 128-row operand read runs 8 KB past its A tile and
+  // lands in the B region, which follows the A region
+  constexpr size_t smem = 1024 + (size_t)STAGES * (AROWS * BK * 2 + BN * BK * 2) + (2 * STAGES + 6) * 8 + 4 * 32 * 32 * 4 +
+                          (AROWS == 128 ? kMaxLiveTiles * 4 : 0);
+  static_assert(smem <= 232448, "shared memory per CTA");
+  auto kern = gemm_bf16_kernel<BN, STAGES, AROWS>;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -584,7 +606,8 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
     if (tile_n == 128 && tiles128 <= 74) tile_n = 64;
   }
   CUtensorMap ta, tb;
-  int rc = make_tmap_2d(&ta, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK, true);
+  const bool few_rows = M <= 64 && gemm_deep_enabled();      // 64-row A box, deeper pipeline
+  int rc = make_tmap_2d(&ta, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, few_rows ? 64 : BM, BK, true);
   if (rc) return rc;
   rc = make_tmap_2d(&tb, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, (uint32_t)tile_n, BK, true);
   if (rc) return rc;
@@ -622,9 +645,12 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
     e.sym = SymTable{};
   }
   switch (tile_n) {
-    case 256: return launch_gemm<256, 4>(ta, tb, e, M, N, K, splits, status, st);
-    case 128: return launch_gemm<128, 6>(ta, tb, e, M, N, K, splits, status, st);
-    case 64: return launch_gemm<64, 8>(ta, tb, e, M, N, K, splits, status, st);
+    case 256: return few_rows ? launch_gemm<256, 5, 64>(ta, tb, e, M, N, K, splits, status, st)
+                              : launch_gemm<256, 4>(ta, tb, e, M, N, K, splits, status, st);
+    case 128: return few_rows ? launch_gemm<128, 8, 64>(ta, tb, e, M, N, K, splits, status, st)
+                              : launch_gemm<128, 6>(ta, tb, e, M, N, K, splits, status, st);
+    case 64: return few_rows ? launch_gemm<64, 13, 64>(ta, tb, e, M, N, K, splits, status, st)
+                             : launch_gemm<64, 8>(ta, tb, e, M, N, K, splits, status, st);
   }
   return B200_ERR_BAD_ARG;
 }

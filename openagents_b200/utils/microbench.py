@@ -163,6 +163,28 @@ def bench_qgemm(rows):
     assert int(status.item()) == 0
 
 
+def bench_gemm_small(rows):
+    """The four projections of a Llama-3-8B layer at a decode batch of 64 rows: weight-streaming GEMMs, judged
+    against the copy bandwidth.  ``store``: plain fp32 store (no split K); ``add``: accumulate into the output
+    (split K allowed)."""
+    hbm, _, tag = peaks()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    M = 64
+    for name, N, K in (("qkv", 6144, 4096), ("wo", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)):
+        A = torch.randn(M, K, device=DEV).bfloat16()
+        B = torch.randn(N, K, device=DEV).bfloat16()
+        out = torch.zeros((M, N), device=DEV)
+        for mode in ("store", "add"):
+            for tile in (0, 64, 128, 256):
+                fn = lambda: ops.gemm_bf16(A, B, M, N, K, out_f32=out, accumulate=(mode == "add"), tile_n=tile, status=status)
+                s = timeit(fn, iters=20)
+                gbs = N * K * 2 / s / 1e9
+                rows.append(f"gemm64 {name:8s} N={N:5d} K={K:5d} {mode:5s} tile_n={tile:3d}: {s*1e6:7.1f} us  {gbs:6.0f} GB/s  {gbs/hbm:4.2f} of {tag} HBM")
+        ref = timeit(lambda: torch.matmul(A, B.t()), iters=20)
+        rows.append(f"       torch.matmul (library reference)              : {ref*1e6:7.1f} us  {N*K*2/ref/1e9:6.0f} GB/s")
+    assert int(status.item()) == 0
+
+
 def main():
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
     rows = []
@@ -174,6 +196,8 @@ def main():
         bench_gemm(rows)
     if which in ("qgemm", "all"):
         bench_qgemm(rows)
+    if which in ("gemm64", "all"):
+        bench_gemm_small(rows)
     print("\n".join(rows))
 
 

@@ -162,19 +162,19 @@ def main():
         # clip + AdamW + bf16 cast + all-gather push
         from ..ops import train_ops as tops
         from ..parallel.symm import SymmHeap
-        n = 124_475_904
-        heap = SymmHeap(n * 6 + (1 << 20), DEV)
-        grads, goff = heap.alloc_tensor((n,), torch.float32)
-        params, poff = heap.alloc_tensor((n,), torch.bfloat16)
+        n_par = 124_475_904
+        heap = SymmHeap(n_par * 6 + (1 << 20), DEV)
+        grads, goff = heap.alloc_tensor((n_par,), torch.float32)
+        params, poff = heap.alloc_tensor((n_par,), torch.bfloat16)
         grads.normal_(0, 1e-3)
-        gsh, master, m, v = (torch.zeros(n, device=DEV) for _ in range(4))
+        gsh, master, m, v = (torch.zeros(n_par, device=DEV) for _ in range(4))
         master.normal_(0, 0.02)
         norm2 = torch.zeros(4, device=DEV)
 
         def fn():
             norm2.zero_()
-            tops.zero_reduce_norm(heap.table, goff, 0, n, gsh, norm2)
-            tops.zero_adamw_gather(heap.table, poff, 0, n, gsh, master, m, v, norm2, 6e-4, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0, n)
+            tops.zero_reduce_norm(heap.table, goff, 0, n_par, gsh, norm2)
+            tops.zero_adamw_gather(heap.table, poff, 0, n_par, gsh, master, m, v, norm2, 6e-4, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0, n_par)
     else:
         raise SystemExit(f"unknown case {case}")
     fn()                                  # warm-up outside the profiled range
