@@ -28,7 +28,7 @@ using namespace b200::tc;
 
 namespace {
 
-constexpr int QB = 128, KB = 64, HD = 128, KV_STAGES = 3;
+constexpr int QB = 128, KB = 64, HD = 128, KV_STAGES = 4;
 constexpr int Q_BYTES = QB * HD * 2;            // 32 KB: two halves of [128 rows][64 dims]
 constexpr int K_BYTES = KB * HD * 2;            // 16 KB: two halves of [64 keys][64 dims]
 constexpr int P_BYTES = QB * KB * 2;            // 16 KB: [128 rows][64 keys]

@@ -94,7 +94,8 @@ constexpr int kRmsRegs = 8;
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ g, float eps,
                                                        int D, int8_t* __restrict__ xq, float* __restrict__ xd,
                                                        float* __restrict__ xs16, __nv_bfloat16* __restrict__ hb,
-                                                       float* __restrict__ hf, const SymTable sym, int signal_ready) {
+                                                       float* __restrict__ hf, const SymTable sym, int signal_ready,
+                                                       float4* __restrict__ zero, int zero_n4) {
   __shared__ float red[32];
   const int t = blockIdx.x;
   const float* xr = x + (size_t)t * D;
@@ -114,6 +115,9 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
     const int blk = w + k * nw;
     v[k] = blk < nblk ? xr[blk * 32 + lane] : 0.f;
   }
+  // Clear the output of the split-K GEMM that consumes this norm (its splits add their partial sums).
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < zero_n4; i += gridDim.x * blockDim.x)
+    zero[i] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
   for (int k = 0; k < kRmsRegs; k++) ss += v[k] * v[k];
   for (int blk = w + kRmsRegs * nw; blk < nblk; blk += nw) {
@@ -151,12 +155,14 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
 
 // sym non-null: x lives in the symmetric heap and the next row-parallel kernel of every rank will add
 // into it; this kernel then ends by signalling that this rank has read x (see sym.cuh).
+// zero / zero_n: an fp32 buffer (16-byte aligned, zero_n a multiple of 4) that the kernel clears on the side.
 B200_API int b200_rmsnorm(const float* x, const float* g, float eps, int T, int D, void* xq, float* xd,
-                          float* xs16, void* hb, float* hf, const SymTable* sym, cudaStream_t st) {
-  if (D % 32) return B200_ERR_BAD_ARG;
+                          float* xs16, void* hb, float* hf, const SymTable* sym, float* zero, long zero_n,
+                          cudaStream_t st) {
+  if (D % 32 || (zero && ((zero_n % 4) || ((uintptr_t)zero % 16)))) return B200_ERR_BAD_ARG;
   const int threads = D >= 4096 ? 1024 : D >= 1024 ? 512 : 256;
   return launch_pdl(rmsnorm_kernel, dim3(T), dim3(threads), 0, st, x, g, eps, D, (int8_t*)xq, xd, xs16,
-                    (__nv_bfloat16*)hb, hf, sym ? *sym : SymTable{}, sym ? 1 : 0);
+                    (__nv_bfloat16*)hb, hf, sym ? *sym : SymTable{}, sym ? 1 : 0, (float4*)zero, zero ? (int)(zero_n / 4) : 0);
 }
 
 // Sequence-sharded tensor-parallel prefill: this rank owns rows [row0, row0 + T) of the residual

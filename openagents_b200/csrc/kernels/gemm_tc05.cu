@@ -599,11 +599,25 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
     const int tm = M; M = N; N = tm;
   }
   const long tiles_m = (M + 127) / 128;
+  // Split K when the output tiles alone would leave most SMs idle and the epilogue is (or can be
+  // turned into) a pure accumulation: the fused collectives already add into their destination, and
+  // an in-place fp32 residual add (resid_f32 == out_f32) is the same thing as adding into out_f32.
+  const bool red_ok = sym_mode != SYM_NONE ||
+                      (out_f32 && !out_bf16 && !resid_bf16 && act == 0 &&
+                       ((accumulate && !resid_f32) || (!accumulate && resid_f32 == out_f32)));
   if (tile_n == 0) {
     const long tiles256 = (long)((N + 255) / 256) * tiles_m, tiles128 = (long)((N + 127) / 128) * tiles_m;
-    tile_n = (N >= 256 && tiles256 >= 148) ? 256 : (N >= 128 && tiles128 >= 148) ? 128 : (N > 64 ? 128 : 64);
-    // Few tiles (decode batches): narrower tiles put more SMs on the weight stream.
-    if (tile_n == 128 && tiles128 <= 74) tile_n = 64;
+    if (M <= 64 && !swap) {
+      // One row tile, weight-streaming.  Measured inside CUDA graphs on the 8B decode shapes at 64 rows: where K may
+      // be split, 128-wide tiles with 3-4 splits win (QKV 17 us against 25, down 28 against 38); where it may
+      // not, the widest tile that still leaves about a hundred CTAs (gate/up 49 us at 256 against 54 at 128).
+      if (red_ok) tile_n = N >= 128 ? 128 : 64;
+      else tile_n = (N >= 256 && tiles256 >= 100) ? 256 : (N >= 128 && tiles128 >= 100) ? 128 : 64;
+    } else {
+      tile_n = (N >= 256 && tiles256 >= 148) ? 256 : (N >= 128 && tiles128 >= 148) ? 128 : (N > 64 ? 128 : 64);
+      // Few tiles (decode batches): narrower tiles put more SMs on the weight stream.
+      if (tile_n == 128 && tiles128 <= 74) tile_n = 64;
+    }
   }
   CUtensorMap ta, tb;
   const bool few_rows = M <= 64 && gemm_deep_enabled();      // 64-row A box, deeper pipeline
@@ -615,12 +629,6 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   e.out_f32 = out_f32; e.out_bf16 = (__nv_bfloat16*)out_bf16; e.bias = bias; e.resid_f32 = resid_f32;
   e.resid_bf16 = (const __nv_bfloat16*)resid_bf16; e.ldc = ldc; e.act = act; e.accumulate = accumulate;
   e.sym_mode = sym_mode; e.rows_per_rank = rows_per_rank > 0 ? rows_per_rank : 1; e.sym_off = sym_off;
-  // Split K when the output tiles alone would leave most SMs idle and the epilogue is (or can be
-  // turned into) a pure accumulation: the fused collectives already add into their destination, and
-  // an in-place fp32 residual add (resid_f32 == out_f32) is the same thing as adding into out_f32.
-  const bool red_ok = sym_mode != SYM_NONE ||
-                      (out_f32 && !out_bf16 && !resid_bf16 && act == 0 &&
-                       ((accumulate && !resid_f32) || (!accumulate && resid_f32 == out_f32)));
   const long n_out_tiles = (long)((N + tile_n - 1) / tile_n) * tiles_m;
   const int KBt = (K + BK - 1) / BK;
   int splits = 1;

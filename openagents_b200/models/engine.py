@@ -364,9 +364,9 @@ class LlamaEngine:
             n += 8
         return n
 
-    def _gemm(self, a_bf16, w: QWeight, M, out_f32=None, out_bf16=None, bias=None, resid_f32=None, ldc=None):
+    def _gemm(self, a_bf16, w: QWeight, M, out_f32=None, out_bf16=None, bias=None, resid_f32=None, ldc=None, accumulate=False):
         ops.gemm_bf16(a_bf16, self._dense(w), M, w.N, w.K, lda=a_bf16.stride(0), ldb=w.K, out_f32=out_f32,
-                      out_bf16=out_bf16, ldc=ldc or w.N, bias=bias, resid_f32=resid_f32, status=self.status)
+                      out_bf16=out_bf16, ldc=ldc or w.N, bias=bias, resid_f32=resid_f32, accumulate=accumulate, status=self.status)
 
     def _seq_sharded(self, T: int, decode: bool) -> bool:
         """Tensor-parallel prefill keeps the residual stream sharded by rows (sequence parallel): each
@@ -389,9 +389,10 @@ class LlamaEngine:
         gu = self.gu[:T]
         S = self._splits(n_seqs, max_ctx_pages) if decode else 1
         n = 0
+        split_qkv = T <= 64          # one row tile: let the QKV GEMM split K (the norm clears its output, the splits add)
         for li, L in enumerate(self.layers):
-            ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, hb=hb_d, signal_sym=self._sig)
-            self._gemm(hb_d, L.wqkv, T, out_f32=qkv, bias=L.bqkv)
+            ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, hb=hb_d, signal_sym=self._sig, zero=qkv if split_qkv else None)
+            self._gemm(hb_d, L.wqkv, T, out_f32=qkv, bias=L.bqkv, accumulate=split_qkv)
             if decode:
                 ops.rope_kv(qkv, self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv, self.hd,
                             PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd), table=self.rope_tab)

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_size_t, c_void_p
+from ctypes import c_float, c_int, c_long, c_size_t, c_void_p
 
 import torch
 
@@ -22,7 +22,7 @@ ACT_NONE, ACT_GELU, ACT_SWIGLU_PAIR = 0, 1, 2
 _P = c_void_p
 _SIGS = {
     "b200_embedding": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, c_int, _P],
-    "b200_rmsnorm": [_P, _P, c_float, c_int, c_int, _P, _P, _P, _P, _P, _P, _P],
+    "b200_rmsnorm": [_P, _P, c_float, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, c_long, _P],
     "b200_rmsnorm_allgather": [_P, _P, c_float, c_int, c_int, c_int, c_size_t, _P, _P],
     "b200_quantize_x": [_P, c_int, c_int, _P, _P, _P, _P],
     "b200_rope_kv": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, _P, c_int, _P],
@@ -97,11 +97,13 @@ def embedding(ids, out, emb_type, w, w2=None, vocab_lo=0, vocab_n=None):
                                 vocab_n if vocab_n is not None else 2 ** 31 - 1, _st()), "embedding")
 
 
-def rmsnorm(x, g, eps, xq=None, xd=None, xs16=None, hb=None, hf=None, signal_sym=None):
+def rmsnorm(x, g, eps, xq=None, xd=None, xs16=None, hb=None, hf=None, signal_sym=None, zero=None):
     """``signal_sym``: symmetric-heap table; the kernel then ends by telling every rank that this rank has
-    finished reading ``x`` (the handshake the fused all-reduce kernels check with ``wait_ready``)."""
+    finished reading ``x`` (the handshake the fused all-reduce kernels check with ``wait_ready``).
+    ``zero``: a contiguous fp32 tensor the kernel clears on the side (the output of a split-K GEMM that follows)."""
     T, D = x.shape
-    _check(lib().b200_rmsnorm(_p(x), _p(g), eps, T, D, _p(xq), _p(xd), _p(xs16), _p(hb), _p(hf), _sym(signal_sym), _st()), "rmsnorm")
+    _check(lib().b200_rmsnorm(_p(x), _p(g), eps, T, D, _p(xq), _p(xd), _p(xs16), _p(hb), _p(hf), _sym(signal_sym),
+                              _p(zero), zero.numel() if zero is not None else 0, _st()), "rmsnorm")
 
 
 def rmsnorm_allgather(x, g, eps, row0, n_rows, hb_off, sym):
