@@ -110,11 +110,8 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    comm = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-        from openagents_b200.parallel.tp import TPComm
-        comm = TPComm(rank, world, dev)
 
     from openagents_b200.models.config import PRESETS
     from openagents_b200.models.engine import LlamaEngine, PAGE
@@ -127,6 +124,10 @@ def main():
         cfg = cfg.with_(n_layers=args.layers)
         valid = False
     B, P = args.batch, args.prompt_len
+    comm = None
+    if world > 1:    # symmetric heap: the fp32 residual stream and the bf16 all-gathered activations of a prefill chunk
+        from openagents_b200.parallel.tp import TPComm
+        comm = TPComm(rank, world, dev, heap_bytes=(4 * P + world) * cfg.d_model * 6 + (64 << 20))
     total_steps = 2 * (K + W) + 8
     max_ctx = P + total_steps + PAGE
     t0 = time.time()
