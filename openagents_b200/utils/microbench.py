@@ -171,7 +171,10 @@ def bench_gemm_small(rows):
     hbm, _, tag = peaks()
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     M, R = 64, 8
-    for name, N, K in (("qkv", 6144, 4096), ("wo", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)):
+    shapes = (("qkv", 6144, 4096), ("wo", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336))
+    if len(sys.argv) > 2 and sys.argv[2] == "ksweep":      # time against K at fixed N: intercept = per-launch cost, slope = per K block
+        shapes = tuple((f"k{K}", 6144, K) for K in (64, 512, 1024, 2048, 4096, 8192))
+    for name, N, K in shapes:
         A = torch.randn(M, K, device=DEV).bfloat16()
         Bs = [torch.randn(N, K, device=DEV).bfloat16() for _ in range(R)]
         out = torch.zeros((M, N), device=DEV)
