@@ -29,10 +29,8 @@ using namespace b200::tc;
 namespace {
 
 constexpr int QB = 128, KB = 64, HD = 128, KV_STAGES = 4;
-constexpr int Q_BYTES = QB * HD * 2;            // 32 KB: two halves of [128 rows][64 dims]
 constexpr int K_BYTES = KB * HD * 2;            // 16 KB: two halves of [64 keys][64 dims]
-constexpr int P_BYTES = QB * KB * 2;            // 16 KB: [128 rows][64 keys]
-constexpr uint32_t TMEM_COLS = 256;             // S: 2 x 64, O: 128
+constexpr uint32_t TMEM_COLS = 512;             // S: 2 x 64, O: 128, Q: 64, P: 2 x 32 (384 used; the allocation is a power of two)
 constexpr float kRescaleStep = 8.f;             // log2 units
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -44,7 +42,8 @@ struct PrefillArgs {
   const float* sinks;      // [Hq] or null
   __nv_bfloat16* out;      // [T_total][Hq * HD]
   int* status;
-  int max_pages, Hq, Hkv, window;
+  const __half* q;         // [T_total][Hq * HD], rotated and scaled
+  int max_pages, Hq, Hkv, window, T_total;
 };
 
 // fp16 x fp16 -> fp32 instruction descriptor; b_mn: the B operand is MN-major.
@@ -84,18 +83,34 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// D (tensor memory) (+)= A (tensor memory: lane = row, 32-bit column j = elements 2j, 2j + 1 of the K slice) x B (shared
+// memory descriptor).  An A operand in shared memory costs a 128-row x 32-byte read per instruction whatever N
+// is, which is what bounds MMAs with a narrow N; from tensor memory it does not.
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-__global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
-                                                                    const __grid_constant__ CUtensorMap tmK,
+__global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(                                                                    const __grid_constant__ CUtensorMap tmK,
                                                                     const __grid_constant__ CUtensorMap tmV,
                                                                     const PrefillArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;
-  uint8_t* sKV = sQ + Q_BYTES;                           // KV_STAGES x (K, V)
-  uint8_t* sP = sKV + KV_STAGES * 2 * K_BYTES;           // 2 x P
-  uint64_t* bars = (uint64_t*)(sP + 2 * P_BYTES);
+  uint8_t* sKV = smem;                                    // KV_STAGES x (K, V)
+  uint64_t* bars = (uint64_t*)(sKV + KV_STAGES * 2 * K_BYTES);
   uint64_t* q_full = bars;                                // [1]
   uint64_t* kv_full = bars + 1;                           // [KV_STAGES]
   uint64_t* kv_empty = kv_full + KV_STAGES;               // [KV_STAGES]
@@ -112,7 +127,7 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(const __grid_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    mbar_init(smem_u32(q_full), 1);
+    mbar_init(smem_u32(q_full), 4);
     for (int s = 0; s < KV_STAGES; s++) {
       mbar_init(smem_u32(kv_full + s), 1);
       mbar_init(smem_u32(kv_empty + s), 1);
@@ -126,7 +141,6 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(const __grid_
     for (int s = 0; s < 8; s++) mbar_init(smem_u32(x_full + s), 2);
     *abort_flag = 0;
     fence_barrier_init();
-    tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
   }
@@ -152,12 +166,10 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(const __grid_
   const int jb0 = k_lo / KB, jb1 = live ? (k_hi + KB - 1) / KB : jb0;   // key blocks [jb0, jb1)
   const int nb = jb1 - jb0;
   const uint32_t S_T = tmem_base, O_T = tmem_base + 128;   // S buffers at +0, +64; O at +128
+  const uint32_t Q_T = tmem_base + 256, P_T = tmem_base + 320;   // Q (fp16 pairs, 64 columns); P buffers (32 columns each)
 
   if (warp == 0) {
     if (lane == 0 && nb > 0) {
-      mbar_expect_tx(smem_u32(q_full), Q_BYTES);
-      tma_load_2d(smem_u32(sQ), &tmQ, smem_u32(q_full), h * HD, qs + q0);
-      tma_load_2d(smem_u32(sQ + Q_BYTES / 2), &tmQ, smem_u32(q_full), h * HD + 64, qs + q0);
       const int* pt = a.page_table + (size_t)seq * a.max_pages;
       for (int j = 0; j < nb; j++) {
         const int s = j % KV_STAGES;
@@ -190,12 +202,11 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(const __grid_
         const uint32_t ph2 = (j >> 1) & 1;
         if (!mbar_wait(smem_u32(p_full + b), ph2, abort_flag)) return false;   // P_j written, O row rescaled if needed
         tc_fence_after();
-        const uint32_t pa = smem_u32(sP + b * P_BYTES);
         const uint32_t va = smem_u32(sKV + (size_t)s * 2 * K_BYTES + K_BYTES);
 #pragma unroll
         for (int kk = 0; kk < KB / 16; kk++)
-          umma_bf16(O_T, smem_desc_sw128(pa) + 2 * kk, smem_desc_sw128_mn(va + kk * 2048, K_BYTES / 2), idesc_o,
-                    (j != 0 || kk != 0) ? 1u : 0u);
+          umma_ts(O_T, P_T + b * 32 + 8 * kk, smem_desc_sw128_mn(va + kk * 2048, K_BYTES / 2), idesc_o,
+                  (j != 0 || kk != 0) ? 1u : 0u);
         umma_commit(smem_u32(o_done));
         umma_commit(smem_u32(kv_empty + s));
         return true;
@@ -205,11 +216,11 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(const __grid_
         if (!mbar_wait(smem_u32(kv_full + s), (j / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
         if (!mbar_wait(smem_u32(s_empty + b), ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sKV + (size_t)s * 2 * K_BYTES);
+        const uint32_t ka = smem_u32(sKV + (size_t)s * 2 * K_BYTES);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; kk++)
-          umma_bf16(S_T + b * 64, smem_desc_sw128(qa + (kk >> 2) * (Q_BYTES / 2)) + 2 * (kk & 3),
-                    smem_desc_sw128(ka + (kk >> 2) * (K_BYTES / 2)) + 2 * (kk & 3), idesc_s, kk != 0 ? 1u : 0u);
+          umma_ts(S_T + b * 64, Q_T + 8 * kk, smem_desc_sw128(ka + (kk >> 2) * (K_BYTES / 2)) + 2 * (kk & 3), idesc_s,
+                  kk != 0 ? 1u : 0u);
         umma_commit(smem_u32(s_full + b));
         if (j > 0) ok = issue_pv(j - 1);
       }
@@ -225,6 +236,25 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(const __grid_
     float m_used = -INFINITY, l = 0.f;     // exponent offset of this row (log2 units) and this warp's part of the row sum
     bool ok = true;
     // post this warp's half and wait (bounded, like every wait here) for the partner's; use number `u` of buffer `bb`
+    if (hsel == 0) {
+      // This row of Q (fp16, already rotated and scaled) goes to tensor memory once: column j = dims 2j, 2j + 1.
+      const bool in = qs + q0 + row < a.T_total;
+      const uint4* qrow = (const uint4*)(a.q + ((size_t)(qs + q0 + (in ? row : 0)) * a.Hq + h) * HD);
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        uint32_t r[32];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const uint4 v = in ? qrow[c * 8 + i] : make_uint4(0u, 0u, 0u, 0u);
+          r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
+        }
+        tmem_st32(Q_T + lane_addr + c * 32, r);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(q_full));
+    }
     auto pair_sync = [&](int bb, int u) -> bool {
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(x_full + q * 2 + bb));
@@ -298,22 +328,20 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(const __grid_
       }
       const float off = (m_used == -INFINITY) ? 0.f : m_used;
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-      // P row: 64 fp16 = 8 chunks of 16 bytes, chunk c of row r at r * 128 + ((c ^ (r & 7)) * 16); this warp: 4 chunks
-      uint8_t* prow = sP + b * P_BYTES + row * 128;
+      // P row (fp16 pairs) straight into tensor memory, where the PV product reads it as its A operand:
+      // this warp's 32 keys are columns [16 * hsel, 16 * hsel + 16) of P buffer b
+      uint32_t pw[16];
 #pragma unroll
-      for (int c = 0; c < 4; c++) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          const float p0 = ex2_approx(fmaf(sv[c * 8 + 2 * i], kLog2e, -off)), p1 = ex2_approx(fmaf(sv[c * 8 + 2 * i + 1], kLog2e, -off));
-          if (i & 1) { sum2 += p0; sum3 += p1; } else { sum0 += p0; sum1 += p1; }
-          const __half2 hh = __floats2half2_rn(p0, p1);
-          w[i] = *(const uint32_t*)&hh;
-        }
-        *(uint4*)(prow + (((hsel * 4 + c) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int i = 0; i < 16; i++) {
+        const float p0 = ex2_approx(fmaf(sv[2 * i], kLog2e, -off)), p1 = ex2_approx(fmaf(sv[2 * i + 1], kLog2e, -off));
+        if (i & 1) { sum2 += p0; sum3 += p1; } else { sum0 += p0; sum1 += p1; }
+        const __half2 hh = __floats2half2_rn(p0, p1);
+        pw[i] = *(const uint32_t*)&hh;
       }
+      tmem_st16(P_T + lane_addr + b * 32 + hsel * 16, pw);
+      tmem_st_wait();
       l += (sum0 + sum1) + (sum2 + sum3);
-      fence_proxy_async_smem();                  // P must be visible to the tensor core's (async proxy) reads
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(p_full + b));
     }
@@ -367,18 +395,18 @@ B200_API int b200_attn_prefill_tc05(const void* q, const void* kc, const void* v
                                     int max_q, int T_total, int Hq, int Hkv, int window, const float* sinks, void* out,
                                     int* status, cudaStream_t st) {
   if (Hq % Hkv || n_seqs < 1 || max_q < 1 || !page_table) return B200_ERR_BAD_ARG;
-  CUtensorMap tq, tk, tv;
-  int rc = make_tmap_2d(&tq, q, 2, (uint64_t)T_total, (uint64_t)Hq * HD, (uint64_t)Hq * HD * 2, QB, 64, true);
-  if (rc) return rc;
+  CUtensorMap tk, tv;
+  int rc;
   const uint64_t rows = (uint64_t)n_pages * Hkv * 16;
   rc = make_tmap_2d(&tk, kc, 2, rows, HD, (uint64_t)HD * 2, 16, 64, true);
   if (rc) return rc;
   rc = make_tmap_2d(&tv, vc, 2, rows, HD, (uint64_t)HD * 2, 16, 64, true);
   if (rc) return rc;
   PrefillArgs a;
+  a.q = (const __half*)q; a.T_total = T_total;
   a.page_table = page_table; a.q_start = q_start; a.q_len = q_len; a.ctx_len = ctx_len; a.sinks = sinks;
   a.out = (__nv_bfloat16*)out; a.status = status; a.max_pages = max_pages; a.Hq = Hq; a.Hkv = Hkv; a.window = window;
-  constexpr size_t smem = 1024 + Q_BYTES + KV_STAGES * 2 * K_BYTES + 2 * P_BYTES + 32 * 8 + 2 * 2 * 128 * 4;
+  constexpr size_t smem = 1024 + KV_STAGES * 2 * K_BYTES + 32 * 8 + 2 * 2 * 128 * 4;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -386,5 +414,5 @@ B200_API int b200_attn_prefill_tc05(const void* q, const void* kc, const void* v
     configured = true;
   }
   dim3 grid((max_q + QB - 1) / QB, Hq, n_seqs);
-  return launch_pdl(attn_prefill_tc05_kernel, grid, dim3(320), smem, st, tq, tk, tv, a);
+  return launch_pdl(attn_prefill_tc05_kernel, grid, dim3(320), smem, st, tk, tv, a);
 }
