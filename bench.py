@@ -80,7 +80,7 @@ class ClockSampler:
 
 def reference_arm():
     # The reference tree is a TypeScript/Rust monorepo without a Python project or any ML engine:
-    # `pip install /root/reference` stops with "Neither 'setup.py' nor 'pyproject.toml' found".
+    # a pip install of that tree stops with "Neither 'setup.py' nor 'pyproject.toml' found".
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference has no installable Python package and no inference/training engine "
                                      "(pip: neither setup.py nor pyproject.toml found)"}))

@@ -517,3 +517,9 @@ def test_qgemm_fused_dequant(t, T, N, K, split):
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     assert (y - r - ref).abs().max().item() < 4 * tol, (y - r - ref).abs().max().item()
+
+
+def test_stream_triad_probe():
+    """The bandwidth probe's triad kernel computes a = b + 3 c (checked inside) and reports a plausible rate."""
+    from openagents_b200.utils.bandwidth_probe import stream_triad_gbs
+    assert stream_triad_gbs(DEV, n=1 << 24) > 200.0

@@ -129,8 +129,9 @@ def test_node_cli_against_reference_fixture(tmp_path):
     from openagents_b200 import _build
     _build.build_node()
     cli = str(_build.node_cli_path())
-    fx = "/root/reference/fixtures/cloud/psionic_worker_attachment_v1/mixed-readiness.json"
     import os
+    # the reference's own fixture when its tree is at hand (OPENAGENTS_REFERENCE_DIR), else the same shape written here
+    fx = os.path.join(os.environ.get("OPENAGENTS_REFERENCE_DIR", "/nonexistent"), "fixtures/cloud/psionic_worker_attachment_v1/mixed-readiness.json")
     if not os.path.exists(fx):
         fx = str(tmp_path / "fx.json")
         json.dump({"schema_version": "openagents.psionic_worker_attachment.v1", "updated_at_ms": 1, "workers": [
