@@ -342,14 +342,19 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, in
 // (the next stage); rows are independent and rows >= M are never written, so that is harmless, and the
 // 8 KB saved per stage buy more stages, i.e. more weight bytes in flight per SM, which is what bounds a
 // GEMM with few rows (bytes in flight = bandwidth x latency).
-template <int BN, int STAGES, int AROWS>
+// KSUB = 2 (with AROWS = 64): a stage holds two 64-wide K blocks of each operand behind one barrier.  The thread
+// that issues the MMAs spends about 540 cycles per K block on a narrow tile (measured with clock64 stamps: some 55
+// per tcgen05.mma, the rest on the barrier wait, the fence and the commit), more than the tensor core needs for
+// four narrow MMAs (220 cycles at N = 64), and the producer thread 420; fewer, larger stages halve that overhead.
+template <int BN, int STAGES, int AROWS, int KSUB>
 __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
                                                          const __grid_constant__ CUtensorMap tmB,
                                                          const GemmEpi epi, int M, int N, int K, int splits,
                                                          int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int A_BYTES = AROWS * BK * 2, B_BYTES = BN * BK * 2;
+  constexpr int A_SUB = AROWS * BK * 2, B_SUB = BN * BK * 2;      // one 64-wide K block of each operand
+  constexpr int A_BYTES = KSUB * A_SUB, B_BYTES = KSUB * B_SUB, BKS = BK * KSUB;
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_BYTES;
   uint64_t* bars = (uint64_t*)(sB + STAGES * B_BYTES);
@@ -364,7 +369,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   __shared__ int s_n_live;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int KB = (K + BK - 1) / BK;
+  const int KB = (K + BKS - 1) / BKS;               // K in stage units
   int tiles_m = (M + BM - 1) / BM;
   const int tiles_n = (N + BN - 1) / BN;
   int n_tiles = tiles_m * tiles_n * splits;   // work items: (output tile, K split), split fastest
@@ -447,8 +452,11 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(smem_u32(empty + s), ph ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(smem_u32(full + s), A_BYTES + B_BYTES);
-          tma_load_2d(smem_u32(sA + s * A_BYTES), &tmA, smem_u32(full + s), kb * BK, m0);
-          tma_load_2d(smem_u32(sB + s * B_BYTES), &tmB, smem_u32(full + s), kb * BK, b_row);
+#pragma unroll
+          for (int u = 0; u < KSUB; u++) {      // a block past the end of K is filled with zeros by the TMA unit
+            tma_load_2d(smem_u32(sA + s * A_BYTES + u * A_SUB), &tmA, smem_u32(full + s), kb * BKS + u * BK, m0);
+            tma_load_2d(smem_u32(sB + s * B_BYTES + u * B_SUB), &tmB, smem_u32(full + s), kb * BKS + u * BK, b_row);
+          }
         }
       }
     }
@@ -470,11 +478,14 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(smem_u32(full + s), ph, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t ad = smem_desc_sw128(smem_u32(sA + s * A_BYTES));
-          const uint64_t bd = smem_desc_sw128(smem_u32(sB + s * B_BYTES));
 #pragma unroll
-          for (int k = 0; k < BK / 16; k++)
-            umma_bf16(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+          for (int u = 0; u < KSUB; u++) {
+            const uint64_t ad = smem_desc_sw128(smem_u32(sA + s * A_BYTES + u * A_SUB));
+            const uint64_t bd = smem_desc_sw128(smem_u32(sB + s * B_BYTES + u * B_SUB));
+#pragma unroll
+            for (int k = 0; k < BK / 16; k++)
+              umma_bf16(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb != kb0 || u != 0 || k != 0) ? 1u : 0u);
+          }
           umma_commit(smem_u32(empty + s));
         }
         umma_commit(smem_u32(tfull + acc));   // released even after a failed wait; the flag says why
@@ -730,15 +741,15 @@ static bool gemm_deep_enabled() {      // B200_GEMM_DEEP=0: measurement aid, the
   return on == 1;
 }
 
-template <int BN, int STAGES, int AROWS = 128>
+template <int BN, int STAGES, int AROWS = 128, int KSUB = 1>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpi& e, int M, int N, int K,
                        int splits, int* status, cudaStream_t st) {
   // AROWS = 64: no tile list (never grouped); the last stage's 128-row operand read runs 8 KB past its A tile and
   // lands in the B region, which follows the A region
-  constexpr size_t smem = 1024 + (size_t)STAGES * (AROWS * BK * 2 + BN * BK * 2) + (2 * STAGES + 6) * 8 + 4 * 32 * 32 * 4 +
+  constexpr size_t smem = 1024 + (size_t)STAGES * KSUB * (AROWS * BK * 2 + BN * BK * 2) + (2 * STAGES + 6) * 8 + 4 * 32 * 32 * 4 +
                           (AROWS == 128 ? kMaxLiveTiles * 4 : 0);
   static_assert(smem <= 232448, "shared memory per CTA");
-  auto kern = gemm_bf16_kernel<BN, STAGES, AROWS>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, AROWS, KSUB>;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -825,7 +836,9 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   e.resid_bf16 = (const __nv_bfloat16*)resid_bf16; e.ldc = ldc; e.act = act; e.accumulate = accumulate;
   e.sym_mode = sym_mode; e.rows_per_rank = rows_per_rank > 0 ? rows_per_rank : 1; e.sym_off = sym_off;
   const long n_out_tiles = (long)((N + tile_n - 1) / tile_n) * tiles_m;
-  const int KBt = (K + BK - 1) / BK;
+  const bool two_k = few_rows && !cluster_s && tile_n != 256;      // two K blocks per stage (narrow tiles)
+  const int k_unit = two_k ? 2 * BK : BK, min_per_split = two_k ? 4 : 8;
+  const int KBt = (K + k_unit - 1) / k_unit;                       // K in the kernel's stage units
   int splits = 1;
   if (split_k > 0) splits = split_k;
   else if (red_ok && n_out_tiles <= 74) splits = (int)(148 / n_out_tiles);
@@ -833,7 +846,7 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   if (splits > 1) {
     if (!red_ok) return B200_ERR_BAD_ARG;
     if (splits > 16) splits = 16;
-    while (splits > 1 && KBt / splits < 8) splits--;           // keep at least 8 K blocks per split
+    while (splits > 1 && KBt / splits < min_per_split) splits--;   // keep at least 8 K blocks (of 64) per split
     const int kps = (KBt + splits - 1) / splits;
     splits = (KBt + kps - 1) / kps;                            // no empty split
   }
@@ -858,9 +871,9 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   switch (tile_n) {
     case 256: return few_rows ? launch_gemm<256, 5, 64>(ta, tb, e, M, N, K, splits, status, st)
                               : launch_gemm<256, 4>(ta, tb, e, M, N, K, splits, status, st);
-    case 128: return few_rows ? launch_gemm<128, 8, 64>(ta, tb, e, M, N, K, splits, status, st)
+    case 128: return few_rows ? launch_gemm<128, 4, 64, 2>(ta, tb, e, M, N, K, splits, status, st)
                               : launch_gemm<128, 6>(ta, tb, e, M, N, K, splits, status, st);
-    case 64: return few_rows ? launch_gemm<64, 13, 64>(ta, tb, e, M, N, K, splits, status, st)
+    case 64: return few_rows ? launch_gemm<64, 6, 64, 2>(ta, tb, e, M, N, K, splits, status, st)
                              : launch_gemm<64, 8>(ta, tb, e, M, N, K, splits, status, st);
   }
   return B200_ERR_BAD_ARG;
