@@ -1,8 +1,8 @@
 // Causal grouped-query flash attention for prefill on the 5th-generation tensor cores (head dim 128).
 //
-// One CTA = 128 query rows of one head.  Roles: warp 0 is the TMA producer (Q once, then a ring of
-// K/V blocks of 64 keys gathered page by page from the paged fp16 cache), warp 1 issues tcgen05.mma,
-// warps 2..9 do the online softmax: two warps per 32 query rows (the two share a tensor-memory lane
+// One CTA = 128 query rows of one head.  Roles: warps 0 and 10 are the TMA producers (a ring of K / V
+// blocks of 64 keys gathered page by page from the paged fp16 cache), warps 1 and 11 issue the two
+// kinds of tcgen05.mma, warps 2..9 do the online softmax: two warps per 32 query rows (the two share a tensor-memory lane
 // quarter), one taking keys 0..31 of a block and output columns 0..63, the other the rest; they swap
 // their partial row maxima through shared memory once per block.  Two warps per scheduler is what
 // hides the latencies of tensor-memory loads, exponentials and barriers.  Per key block j:
@@ -104,7 +104,7 @@ __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-__global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(                                                                    const __grid_constant__ CUtensorMap tmK,
+__global__ void __launch_bounds__(384, 1) attn_prefill_tc05_kernel(                                                                    const __grid_constant__ CUtensorMap tmK,
                                                                     const __grid_constant__ CUtensorMap tmV,
                                                                     const PrefillArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -117,8 +117,8 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(             
   uint64_t* s_full = kv_empty + KV_STAGES;                // [2]
   uint64_t* s_empty = s_full + 2;                         // [2]
   uint64_t* p_full = s_empty + 2;                         // [2]
-  uint64_t* o_done = p_full + 2;                          // [1]: one phase per PV product
-  uint64_t* x_full = o_done + 2;                          // [4 quarters][2]: both warps of a pair have posted their half
+  uint64_t* pv_done = p_full + 2;                         // [2]: PV product of the blocks that used P buffer b
+  uint64_t* x_full = pv_done + 2;                          // [4 quarters][2]: both warps of a pair have posted their half
   uint32_t* tmem_holder = (uint32_t*)(x_full + 8);
   volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
   float* xch = (float*)(bars + 32);                       // [2 (block parity)][2 (half)][128 rows] partial row maxima / sums
@@ -137,7 +137,8 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(             
       mbar_init(smem_u32(s_empty + s), 8);
       mbar_init(smem_u32(p_full + s), 8);
     }
-    mbar_init(smem_u32(o_done), 1);
+    mbar_init(smem_u32(pv_done), 1);
+    mbar_init(smem_u32(pv_done + 1), 1);
     for (int s = 0; s < 8; s++) mbar_init(smem_u32(x_full + s), 2);
     *abort_flag = 0;
     fence_barrier_init();
@@ -168,53 +169,42 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(             
   const uint32_t S_T = tmem_base, O_T = tmem_base + 128;   // S buffers at +0, +64; O at +128
   const uint32_t Q_T = tmem_base + 256, P_T = tmem_base + 320;   // Q (fp16 pairs, 64 columns); P buffers (32 columns each)
 
-  if (warp == 0) {
+  // Four single-thread roles, each in a warp of its own, because what a thread can issue is the bound here:
+  // about 55 cycles per tcgen05.mma and 100-200 per TMA load, barrier wait, fence or commit.
+  //   warp 0: K loads (and the byte count of the whole stage)      warp 10: V loads
+  //   warp 1: S_j = Q K_j^T                                         warp 11: O += P_j V_j, releases the stage
+  if (warp == 0 || warp == 10) {
     if (lane == 0 && nb > 0) {
+      const bool is_k = warp == 0;
       const int* pt = a.page_table + (size_t)seq * a.max_pages;
       for (int j = 0; j < nb; j++) {
         const int s = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
         if (!mbar_wait(smem_u32(kv_empty + s), ph ^ 1, abort_flag)) break;
         const uint32_t bar = smem_u32(kv_full + s);
-        mbar_expect_tx(bar, 2 * K_BYTES);
-        uint8_t* sK = sKV + (size_t)s * 2 * K_BYTES;
-        uint8_t* sV = sK + K_BYTES;
+        // the barrier holds one pending arrival until this arrive.expect_tx, so V bytes that land first cannot
+        // complete the phase early
+        if (is_k) mbar_expect_tx(bar, 2 * K_BYTES);
+        uint8_t* dst = sKV + (size_t)s * 2 * K_BYTES + (is_k ? 0 : K_BYTES);
+        const CUtensorMap* tm = is_k ? &tmK : &tmV;
 #pragma unroll
         for (int p = 0; p < KB / 16; p++) {
           const int pi = (jb0 + j) * (KB / 16) + p;
           const int page = (pi * 16 < ctx) ? pt[pi] : 0;          // pages past the context are masked anyway
           const int row = (page * a.Hkv + kh) * 16;
 #pragma unroll
-          for (int hf = 0; hf < 2; hf++) {
-            tma_load_2d(smem_u32(sK + hf * (K_BYTES / 2) + p * 2048), &tmK, bar, hf * 64, row);
-            tma_load_2d(smem_u32(sV + hf * (K_BYTES / 2) + p * 2048), &tmV, bar, hf * 64, row);
-          }
+          for (int hf = 0; hf < 2; hf++) tma_load_2d(smem_u32(dst + hf * (K_BYTES / 2) + p * 2048), tm, bar, hf * 64, row);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && nb > 0) {
       constexpr uint32_t idesc_s = idesc_f16(QB, KB, false);
-      constexpr uint32_t idesc_o = idesc_f16(QB, HD, true);
       bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag);
-      auto issue_pv = [&](int j) -> bool {        // O += P_j V_j, then release K/V stage of block j
-        const int s = j % KV_STAGES, b = j & 1;
-        const uint32_t ph2 = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(p_full + b), ph2, abort_flag)) return false;   // P_j written, O row rescaled if needed
-        tc_fence_after();
-        const uint32_t va = smem_u32(sKV + (size_t)s * 2 * K_BYTES + K_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < KB / 16; kk++)
-          umma_ts(O_T, P_T + b * 32 + 8 * kk, smem_desc_sw128_mn(va + kk * 2048, K_BYTES / 2), idesc_o,
-                  (j != 0 || kk != 0) ? 1u : 0u);
-        umma_commit(smem_u32(o_done));
-        umma_commit(smem_u32(kv_empty + s));
-        return true;
-      };
       for (int j = 0; j < nb && ok; j++) {
         const int s = j % KV_STAGES, b = j & 1;
-        if (!mbar_wait(smem_u32(kv_full + s), (j / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
-        if (!mbar_wait(smem_u32(s_empty + b), ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(kv_full + s), (j / KV_STAGES) & 1, abort_flag)) break;
+        if (!mbar_wait(smem_u32(s_empty + b), ((j >> 1) & 1) ^ 1, abort_flag)) break;
         tc_fence_after();
         const uint32_t ka = smem_u32(sKV + (size_t)s * 2 * K_BYTES);
 #pragma unroll
@@ -222,11 +212,27 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(             
           umma_ts(S_T + b * 64, Q_T + 8 * kk, smem_desc_sw128(ka + (kk >> 2) * (K_BYTES / 2)) + 2 * (kk & 3), idesc_s,
                   kk != 0 ? 1u : 0u);
         umma_commit(smem_u32(s_full + b));
-        if (j > 0) ok = issue_pv(j - 1);
       }
-      if (ok) issue_pv(nb - 1);
     }
-  } else if (nb > 0) {
+  } else if (warp == 11) {
+    if (lane == 0 && nb > 0) {
+      constexpr uint32_t idesc_o = idesc_f16(QB, HD, true);
+      for (int j = 0; j < nb; j++) {
+        const int s = j % KV_STAGES, b = j & 1;
+        if (!mbar_wait(smem_u32(kv_full + s), (j / KV_STAGES) & 1, abort_flag)) break;       // V_j has landed
+        if (!mbar_wait(smem_u32(p_full + b), (j >> 1) & 1, abort_flag)) break;                // P_j written, O rows rescaled if needed
+        tc_fence_after();
+        const uint32_t va = smem_u32(sKV + (size_t)s * 2 * K_BYTES + K_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < KB / 16; kk++)
+          umma_ts(O_T, P_T + b * 32 + 8 * kk, smem_desc_sw128_mn(va + kk * 2048, K_BYTES / 2), idesc_o,
+                  (j != 0 || kk != 0) ? 1u : 0u);
+        // a commit covers this thread's MMAs only; S_j is known to be done because the softmax of block j needed it
+        umma_commit(smem_u32(pv_done + b));
+        umma_commit(smem_u32(kv_empty + s));
+      }
+    }
+  } else if (warp < 10 && nb > 0) {
     const int q = warp & 3;                      // tensor-memory lane quarter this warp may read
     const int hsel = (warp - 2) >> 2;            // 0: keys 0..31 of a block, output columns 0..63; 1: the other half
     const int row = q * 32 + lane;               // query row of this thread (shared with the partner warp's same lane)
@@ -306,7 +312,7 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(             
       if (j > 0 && __any_sync(0xffffffffu, behind && !unset)) {
         const float m_new = fmaxf(m_used, bmax);
         const float scale = (m_new == -INFINITY) ? 1.f : ex2_approx(m_used - m_new);
-        ok = mbar_wait(smem_u32(o_done), (j - 1) & 1, abort_flag);       // PV_{j-1} has finished
+        ok = mbar_wait(smem_u32(pv_done + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag);       // PV_{j-1} has finished
         ok = __all_sync(0xffffffffu, ok && !*abort_flag);
         if (!ok) break;
         tc_fence_after();
@@ -338,6 +344,11 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(             
         const __half2 hh = __floats2half2_rn(p0, p1);
         pw[i] = *(const uint32_t*)&hh;
       }
+      if (j >= 2) {      // P buffer b was last read by PV_{j-2}, issued by another thread than the one whose commit we saw for S_j
+        ok = mbar_wait(smem_u32(pv_done + b), ((j - 2) >> 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok && !*abort_flag);
+        if (!ok) break;
+      }
       tmem_st16(P_T + lane_addr + b * 32 + hsel * 16, pw);
       tmem_st_wait();
       l += (sum0 + sum1) + (sum2 + sum3);
@@ -346,7 +357,7 @@ __global__ void __launch_bounds__(320, 1) attn_prefill_tc05_kernel(             
       if (lane == 0) mbar_arrive(smem_u32(p_full + b));
     }
     if (ok) {
-      ok = mbar_wait(smem_u32(o_done), (nb - 1) & 1, abort_flag);          // last PV product
+      ok = mbar_wait(smem_u32(pv_done + ((nb - 1) & 1)), ((nb - 1) >> 1) & 1, abort_flag);          // last PV product
       ok = __all_sync(0xffffffffu, ok && !*abort_flag);
     }
     // row sum = both halves (the partner is at the same point: every exit above is taken by whole CTAs' worth of
@@ -414,5 +425,5 @@ B200_API int b200_attn_prefill_tc05(const void* q, const void* kc, const void* v
     configured = true;
   }
   dim3 grid((max_q + QB - 1) / QB, Hq, n_seqs);
-  return launch_pdl(attn_prefill_tc05_kernel, grid, dim3(320), smem, st, tk, tv, a);
+  return launch_pdl(attn_prefill_tc05_kernel, grid, dim3(384), smem, st, tk, tv, a);
 }
