@@ -226,6 +226,41 @@ def main():
     d2h = 4 * B
     eng.check_status()
 
+    # ---- N > 1, side measurement: the same global batch served by N independent replicas (whole model per GPU,
+    # B / N sequences each), the configuration a model that fits one GPU would be deployed in for throughput.
+    # The headline stays the tensor-parallel number; a failure here is reported, not raised.
+    replicas = None
+    if world > 1 and B % world == 0 and cfg.d_model <= 4096:
+        Bl, rep_ms, err = B // world, -1.0, ""
+        try:                       # local work only in here: a rank that fails must not leave the others in a collective
+            rep = LlamaEngine(cfg, RandomSource(cfg, PLAN_Q4_K, 0, dev), device=dev, max_batch=Bl, max_ctx=max_ctx,
+                              max_tokens=P, tp_rank=0, tp_world=1, comm=None)
+            firsts = []
+            for i in range(Bl):
+                rep.begin(i)
+                _, nx = rep.forward_tokens([i], [prompts[rank * Bl + i].tolist()])
+                firsts += nx.tolist()
+            ids_l = list(range(Bl))
+            h = rep.decode_steps(ids_l, firsts, W)
+            lastl = h[W - 1].tolist()
+            torch.cuda.synchronize()
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            marks = {0: r0}
+            rep.decode_steps(ids_l, lastl, K, on_replay=lambda i: marks[i].record() if i in marks else None)
+            r1.record()
+            torch.cuda.synchronize()
+            rep.check_status()
+            rep_ms = r0.elapsed_time(r1) / K
+            del rep
+        except Exception as e:      # noqa: BLE001 - a side measurement must not take the benchmark down
+            err = f"{type(e).__name__}: {e}"[:200]
+        t = torch.tensor([rep_ms, -rep_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)                 # slowest rank, and whether any rank failed
+        slowest, any_failed = float(t[0].item()), float(t[1].item()) > 0
+        replicas = ({"error": err or "a rank failed"} if any_failed else
+                    {"decode_tok_s": round(B / (slowest * 1e-3), 1), "ms_per_step": round(slowest, 4), "batch_per_gpu": Bl,
+                     "parallelism": f"dp{world} (independent replicas)"})
+
     if rank == 0:
         value = B / (dev_ms * 1e-3)
         out = {
@@ -243,7 +278,7 @@ def main():
             "extra": {"decode_tok_s_bs1": round(1.0 / (bs1_ms * 1e-3), 1), "ms_per_step_bs1": round(bs1_ms, 4),
                       "launches_per_step_bs1": launches_bs1, "prefill_ttft_ms": round(ttft_ms, 3),
                       "prefill_tok_s": round(P / (ttft_ms * 1e-3), 1), "load_s": round(load_s, 1),
-                      "weight_bytes_per_gpu": eng.weight_bytes()},
+                      "weight_bytes_per_gpu": eng.weight_bytes(), **({"replicas": replicas} if replicas else {})},
         }
         print(json.dumps(out))
     if world > 1:
