@@ -170,7 +170,10 @@ class LlamaEngine:
         self._alloc()
         self._graphs: dict[int, tuple] = {}
         self.launches_per_decode = 0
-        self.small_path_tokens = MATVEC_MAX_TOKENS      # up to this many decode tokens take the mat-vec path
+        # Up to this many decode tokens take the mat-vec path.  Measured on the 8B shape (ms per step, mat-vec / GEMM path):
+        # 2 tokens 2.9 / 4.3, 4 tokens 4.0 / 4.3, 8 tokens 5.7 / 4.4: the mat-vec kernels scale with the token count, the
+        # tensor-core path does not, and they cross between 4 and 5 tokens.
+        self.small_path_tokens = min(MATVEC_MAX_TOKENS, int(os.environ.get("B200_SMALL_PATH_TOKENS", 4)))
         self.h2d_bytes = 0                              # host-to-device bytes copied by decode() so far
         self.prefill_tc05 = os.environ.get("B200_PREFILL_TC05", "1") == "1"     # tcgen05 prefill attention (head size 128)
         self.seq_shard = os.environ.get("B200_TP_SEQ_SHARD", "1") == "1"        # sequence-sharded tensor-parallel prefill
