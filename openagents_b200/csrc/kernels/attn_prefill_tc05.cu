@@ -3,13 +3,13 @@
 // One CTA = 128 query rows of one head.  Roles: warps 0 and 10 are the TMA producers (a ring of K / V
 // blocks of 64 keys gathered page by page from the paged fp16 cache), warps 1 and 11 issue the two
 // kinds of tcgen05.mma, warps 2..9 do the online softmax: two warps per 32 query rows (the two share a tensor-memory lane
-// quarter), one taking keys 0..31 of a block and output columns 0..63, the other the rest; they swap
+// quarter), one taking keys 0..63 of a block and output columns 0..63, the other the rest; they swap
 // their partial row maxima through shared memory once per block.  Two warps per scheduler is what
 // hides the latencies of tensor-memory loads, exponentials and barriers.  Per key block j:
-//   S_j = Q K_j^T        tcgen05.mma 128 x 64 x 128 into one of two S accumulators in tensor memory
-//   softmax              S_j -> registers (tcgen05.ld), mask, running max / sum, P_j (fp16) -> shared
-//                        memory in the 128-byte-swizzled K-major layout the next MMA reads
-//   O += P_j V_j         tcgen05.mma 128 x 128 x 64 accumulating in ONE O tile that stays in tensor memory
+//   S_j = Q K_j^T        tcgen05.mma 128 x 128 x 128 into one of two S accumulators in tensor memory
+//   softmax              S_j -> registers (tcgen05.ld), mask, running max / sum, P_j (fp16 pairs) -> tensor
+//                        memory over the S columns it came from, where the next MMA reads it as its A operand
+//   O += P_j V_j         tcgen05.mma 128 x 128 x 128 accumulating in ONE O tile that stays in tensor memory
 //                        for the whole row block, V taken as it lies in the cache ([key][dim], i.e. the
 //                        MN-major form of the B operand)
 // The exponent offset of a row (its running maximum) is only moved when the maximum has grown by more
@@ -28,9 +28,9 @@ using namespace b200::tc;
 
 namespace {
 
-constexpr int QB = 128, KB = 64, HD = 128, KV_STAGES = 4;
+constexpr int QB = 128, KB = 128, HD = 128, KV_STAGES = 3;
 constexpr int K_BYTES = KB * HD * 2;            // 16 KB: two halves of [64 keys][64 dims]
-constexpr uint32_t TMEM_COLS = 512;             // S: 2 x 64, O: 128, Q: 64, P: 2 x 32 (384 used; the allocation is a power of two)
+constexpr uint32_t TMEM_COLS = 512;             // S: 2 x 128 (P is written over the S columns it came from), O: 128, Q: 64
 constexpr float kRescaleStep = 8.f;             // log2 units
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -166,8 +166,9 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc05_kernel(             
   const int k_lo = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
   const int jb0 = k_lo / KB, jb1 = live ? (k_hi + KB - 1) / KB : jb0;   // key blocks [jb0, jb1)
   const int nb = jb1 - jb0;
-  const uint32_t S_T = tmem_base, O_T = tmem_base + 128;   // S buffers at +0, +64; O at +128
-  const uint32_t Q_T = tmem_base + 256, P_T = tmem_base + 320;   // Q (fp16 pairs, 64 columns); P buffers (32 columns each)
+  const uint32_t S_T = tmem_base, O_T = tmem_base + 256;   // S buffers at +0, +128; O at +256
+  const uint32_t Q_T = tmem_base + 384;                    // Q (fp16 pairs, 64 columns)
+  // P_j (fp16 pairs) overwrites S_j: the warp that owns keys [64 h, 64 h + 64) of a block writes columns [64 h, 64 h + 32)
 
   // Four single-thread roles, each in a warp of its own, because what a thread can issue is the bound here:
   // about 55 cycles per tcgen05.mma and 100-200 per TMA load, barrier wait, fence or commit.
@@ -205,11 +206,12 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc05_kernel(             
         const int s = j % KV_STAGES, b = j & 1;
         if (!mbar_wait(smem_u32(kv_full + s), (j / KV_STAGES) & 1, abort_flag)) break;
         if (!mbar_wait(smem_u32(s_empty + b), ((j >> 1) & 1) ^ 1, abort_flag)) break;
+        if (j >= 2 && !mbar_wait(smem_u32(pv_done + b), ((j - 2) >> 1) & 1, abort_flag)) break;   // P_{j-2} sits in S buffer b
         tc_fence_after();
         const uint32_t ka = smem_u32(sKV + (size_t)s * 2 * K_BYTES);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; kk++)
-          umma_ts(S_T + b * 64, Q_T + 8 * kk, smem_desc_sw128(ka + (kk >> 2) * (K_BYTES / 2)) + 2 * (kk & 3), idesc_s,
+          umma_ts(S_T + b * KB, Q_T + 8 * kk, smem_desc_sw128(ka + (kk >> 2) * (K_BYTES / 2)) + 2 * (kk & 3), idesc_s,
                   kk != 0 ? 1u : 0u);
         umma_commit(smem_u32(s_full + b));
       }
@@ -225,7 +227,7 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc05_kernel(             
         const uint32_t va = smem_u32(sKV + (size_t)s * 2 * K_BYTES + K_BYTES);
 #pragma unroll
         for (int kk = 0; kk < KB / 16; kk++)
-          umma_ts(O_T, P_T + b * 32 + 8 * kk, smem_desc_sw128_mn(va + kk * 2048, K_BYTES / 2), idesc_o,
+          umma_ts(O_T, S_T + b * KB + (kk >> 2) * 64 + 8 * (kk & 3), smem_desc_sw128_mn(va + kk * 2048, K_BYTES / 2), idesc_o,
                   (j != 0 || kk != 0) ? 1u : 0u);
         // a commit covers this thread's MMAs only; S_j is known to be done because the softmax of block j needed it
         umma_commit(smem_u32(pv_done + b));
@@ -277,10 +279,13 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc05_kernel(             
       float sv[HK];
       {
         uint32_t r[32];
-        tmem_ld32(S_T + b * 64 + lane_addr + hsel * HK, r);
-        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i++) sv[i] = __uint_as_float(r[i]);
+        for (int c = 0; c < HK / 32; c++) {
+          tmem_ld32(S_T + b * KB + lane_addr + hsel * HK + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i++) sv[c * 32 + i] = __uint_as_float(r[i]);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -335,21 +340,17 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc05_kernel(             
       const float off = (m_used == -INFINITY) ? 0.f : m_used;
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
       // P row (fp16 pairs) straight into tensor memory, where the PV product reads it as its A operand:
-      // this warp's 32 keys are columns [16 * hsel, 16 * hsel + 16) of P buffer b
-      uint32_t pw[16];
+      // this warp's 64 keys become 32 columns at the start of its own half of S buffer b
+      uint32_t pw[HK / 2];
 #pragma unroll
-      for (int i = 0; i < 16; i++) {
+      for (int i = 0; i < HK / 2; i++) {
         const float p0 = ex2_approx(fmaf(sv[2 * i], kLog2e, -off)), p1 = ex2_approx(fmaf(sv[2 * i + 1], kLog2e, -off));
         if (i & 1) { sum2 += p0; sum3 += p1; } else { sum0 += p0; sum1 += p1; }
         const __half2 hh = __floats2half2_rn(p0, p1);
         pw[i] = *(const uint32_t*)&hh;
       }
-      if (j >= 2) {      // P buffer b was last read by PV_{j-2}, issued by another thread than the one whose commit we saw for S_j
-        ok = mbar_wait(smem_u32(pv_done + b), ((j - 2) >> 1) & 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok && !*abort_flag);
-        if (!ok) break;
-      }
-      tmem_st16(P_T + lane_addr + b * 32 + hsel * 16, pw);
+      // (S buffer b is free for P_j: S_j was only issued once PV_{j-2}, the last reader of these columns, had finished)
+      tmem_st32(S_T + b * KB + lane_addr + hsel * HK, pw);
       tmem_st_wait();
       l += (sum0 + sum1) + (sum2 + sum3);
       tc_fence_before();
