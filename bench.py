@@ -152,7 +152,7 @@ def main():
 
     # ---- prefill TTFT: one 2048-token prompt, device time of the whole forward incl. first arg-max
     eng.begin(B)
-    eng.forward_tokens([B], [prompts[B, :64].tolist()])      # warm kernels / shadows on a short chunk
+    eng.forward_tokens([B], [prompts[B, :64].tolist()])      # warm the kernels on a short chunk
     eng.end(B)
     ttft = []
     for rep in range(3):

@@ -183,6 +183,15 @@ def template_digest(template: str) -> str:
     return hashlib.sha256(template.encode()).hexdigest()
 
 
+def template_admitted(template: str, extra_digests=()) -> bool:
+    """Whether a GGUF chat template may be rendered by the server: its digest must be on the allowlist: the digests
+    given, plus those in ``B200_CHAT_TEMPLATE_ALLOW`` (comma-separated sha256 hex).  A template is code that runs on
+    every request, so an unknown one is never rendered; the server then uses its built-in template."""
+    import os
+    allowed = set(extra_digests) | {d.strip() for d in os.environ.get("B200_CHAT_TEMPLATE_ALLOW", "").split(",") if d.strip()}
+    return template_digest(template) in allowed
+
+
 class ModelRegistry:
     """Admission of a GGUF for GPU serving: a known ``general.architecture`` and, when the file carries a
     chat template, a digest on the allowlist (an unknown template is refused rather than rendered approximately)."""

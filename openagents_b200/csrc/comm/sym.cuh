@@ -14,7 +14,7 @@
 namespace b200 {
 
 constexpr int kMaxRanks = 8;
-constexpr int kSymChannels = 16;
+constexpr int kSymChannels = 32;
 constexpr size_t kSymControlBytes = 4096;
 
 struct SymControl {               // first kSymControlBytes of every heap
@@ -23,6 +23,8 @@ struct SymControl {               // first kSymControlBytes of every heap
   int ticket[kSymChannels];       // CTAs of the current launch that have finished (local)
   int status;                     // last error (B200Status), 0 if none
   int timeouts;                   // number of waits that ran out
+  uint32_t slot_seq;              // slot all-reduces this rank has issued so far (local; see sym_slots_*)
+  uint32_t merge_seq;             // arg-max merges this rank has issued so far (local)
 };
 
 struct SymTable {
@@ -67,6 +69,15 @@ __device__ __forceinline__ void sym_red_to_f32x4(const SymTable& T, int dst, siz
 }
 __device__ __forceinline__ void sym_red_to_f32(const SymTable& T, int dst, size_t off, float v) {
   asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(T.base[dst] + off), "f"(v) : "memory");
+}
+// Store one fp32 at `off` of every rank's heap.
+__device__ __forceinline__ void sym_st_all_f32(const SymTable& T, size_t off, float v) {
+  if (T.use_mc) {
+    asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(T.mc_base + off), "f"(v) : "memory");
+  } else {
+    for (int p = 0; p < T.world; p++)
+      asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(T.base[p] + off), "f"(v) : "memory");
+  }
 }
 // Store 16 bytes at `off` of every rank's heap (all-gather push).
 __device__ __forceinline__ void sym_st_all_v4(const SymTable& T, size_t off, uint4 v) {
@@ -252,6 +263,67 @@ __device__ __forceinline__ bool sym_wait_rows(const SymTable& T, int owner, uint
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(&me->flag[kSymAgCh0 + owner]) : "memory");
     if ((int32_t)(v - epoch) >= 0) return true;
+    if ((spin & 63u) == 63u && sym_now_ns() - t0 > T.wait_ns) {
+      me->status = (int)B200_ERR_TIMEOUT_PEER;
+      atomicAdd(&me->timeouts, 1);
+      return false;
+    }
+  }
+}
+
+// ---- one-shot all-reduce through per-rank slots -------------------------------------------------
+// Decode-time row-parallel projections (a few tokens to a batch of 64) do not add into a shared tensor:
+// every rank STORES its partial result into its own slot of a [2][world][rows][d] fp32 tensor on every
+// rank (multimem.st / peer stores) and bumps flag kSymSlotCh0 + rank everywhere; the kernel that needs
+// the sum (the next RMSNorm) waits for the world flags and adds the slots up in rank order, so every
+// replica computes bit-identical sums.  Nothing waits inside the producer, there is no barrier and no
+// "ready" handshake: slot parity alternates with the sequence number, and a rank can only start writing
+// parity p again after it has consumed the all-reduce in between, which every peer contributed to after
+// it had finished reading parity p.  The sequence number lives in device memory (slot_seq) and is
+// advanced by the producer's last CTA, so the scheme replays unchanged inside a CUDA graph.
+constexpr int kSymSlotCh0 = 16;    // channels 16 .. 16 + kMaxRanks - 1
+constexpr int kSymMergeCh0 = 24;   // channels 24 .. 24 + kMaxRanks - 1 (arg-max merge, same scheme)
+
+// Sequence number of the slot all-reduce this kernel is producing (read after the dependency wait).
+__device__ __forceinline__ uint32_t sym_slots_next_seq(const SymTable& T) {
+  return *(volatile uint32_t*)&sym_ctl(T, T.rank)->slot_seq + 1u;
+}
+// Sequence number of the latest completed producer kernel on this rank (what a consumer waits for).
+__device__ __forceinline__ uint32_t sym_slots_cur_seq(const SymTable& T) {
+  return *(volatile uint32_t*)&sym_ctl(T, T.rank)->slot_seq;
+}
+// Call from every thread of every CTA at the end of the producing kernel.  Each CTA's stores are ordered
+// before its ticket by a system-scope fence; the CTA that takes the last ticket advances the sequence
+// number and raises this rank's flag on every rank.
+__device__ __forceinline__ void sym_slots_signal(const SymTable& T, int n_ctas) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    SymControl* me = sym_ctl(T, T.rank);
+    __threadfence_system();
+    const int done = atomicAdd(&me->ticket[kSymSlotCh0], 1);
+    if (done == n_ctas - 1) {
+      me->ticket[kSymSlotCh0] = 0;
+      me->slot_seq = me->slot_seq + 1u;
+      __threadfence_system();
+      const size_t off = offsetof(SymControl, flag) + 4 * (kSymSlotCh0 + T.rank);
+      if (T.use_mc) {
+        asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(T.mc_base + off), "r"(1u) : "memory");
+      } else {
+        for (int p = 0; p < T.world; p++)
+          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(T.base[p] + off), "r"(1u) : "memory");
+      }
+    }
+  }
+}
+// One thread: wait until flag `ch` of this rank has reached `seq`.  Returns false (and records the
+// time-out) if the wait ran out.
+__device__ __forceinline__ bool sym_wait_flag(const SymTable& T, int ch, uint32_t seq) {
+  SymControl* me = sym_ctl(T, T.rank);
+  const unsigned long long t0 = sym_now_ns();
+  for (uint32_t spin = 0;; ++spin) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(&me->flag[ch]) : "memory");
+    if ((int32_t)(v - seq) >= 0) return true;
     if ((spin & 63u) == 63u && sym_now_ns() - t0 > T.wait_ns) {
       me->status = (int)B200_ERR_TIMEOUT_PEER;
       atomicAdd(&me->timeouts, 1);

@@ -13,6 +13,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <exception>
 #include <string>
 #include <vector>
 
@@ -170,6 +171,12 @@ static Reader* open_reader(const char* path) {
   }
   uint64_t n_tensors = c.get<uint64_t>();
   uint64_t n_kv = c.get<uint64_t>();
+  // A header cannot promise more entries than the file has room for: a key/value pair takes at least 12 bytes (empty
+  // key, type, one byte of value), a tensor record at least 24 (empty name, no dimensions, type, offset).
+  if (n_kv > r->size / 12 || n_tensors > r->size / 24) {
+    r->error = "header counts exceed the file size";
+    return r;
+  }
   std::string js = "{";
   for (uint64_t i = 0; i < n_kv && c.ok; i++) {
     std::string key = c.str();
@@ -204,9 +211,14 @@ static Reader* open_reader(const char* path) {
     }
     t.dims.resize(nd);
     uint64_t n = 1;
+    bool overflow = false;
     for (auto& d : t.dims) {
       d = c.get<uint64_t>();
-      n *= d;
+      overflow |= __builtin_mul_overflow(n, d, &n);
+    }
+    if (overflow || n > (uint64_t)1 << 48) {
+      r->error = "tensor " + t.name + " has an impossible element count";
+      return r;
     }
     t.type = c.get<uint32_t>();
     t.offset = c.get<uint64_t>();
@@ -223,8 +235,13 @@ static Reader* open_reader(const char* path) {
   }
   uint64_t pos = (uint64_t)(c.p - r->base);
   r->data_start = (pos + r->alignment - 1) / r->alignment * r->alignment;
+  if (r->data_start > r->size) {
+    r->error = "data section starts past the end of the file";
+    return r;
+  }
+  const uint64_t room = r->size - r->data_start;
   for (auto& t : r->tensors) {
-    if (r->data_start + t.offset + t.nbytes > r->size) {
+    if (t.offset > room || t.nbytes > room - t.offset) {      // written so that nothing can wrap around
       r->error = "tensor " + t.name + " runs past the end of the file";
       return r;
     }
@@ -283,7 +300,21 @@ int b200_quantize(uint32_t type, const float* src, void* dst, uint64_t n) {
 }
 
 // ---- reader
-void* b200_gguf_open(const char* path) { return open_reader(path); }
+// Never lets an exception cross the C boundary: a file whose header makes the parser run out of memory or trip a
+// length check comes back as a reader with an error message, like any other malformed file.
+void* b200_gguf_open(const char* path) {
+  try {
+    return open_reader(path);
+  } catch (const std::exception& e) {
+    Reader* r = new Reader();
+    r->error = std::string("malformed file: ") + e.what();
+    return r;
+  } catch (...) {
+    Reader* r = new Reader();
+    r->error = "malformed file";
+    return r;
+  }
+}
 const char* b200_gguf_error(void* h) {
   Reader* r = (Reader*)h;
   return r->error.empty() ? nullptr : r->error.c_str();

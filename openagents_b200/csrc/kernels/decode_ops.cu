@@ -91,14 +91,21 @@ B200_API int b200_embedding(const int* ids, float* out, int T, int D, int type, 
 // all loads in flight together and kept in registers; only rows longer than kRmsRegs * 1024 fall
 // back to re-reading.
 constexpr int kRmsRegs = 8;
-__global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ g, float eps,
+// sym_mode 1: tensor parallel, all-reduce form: x is replicated in the symmetric heap and peers add into it; the kernel
+//             ends by telling them that this rank has finished reading (see sym_signal_ready).
+// sym_mode 2: tensor parallel, slot form: the row-parallel projection before this norm left every rank's partial
+//             result in per-rank slots (see sym_slots_* in sym.cuh).  The kernel waits for the world flags, adds the
+//             slots to x in rank order (x <- x + sum, written back: x is this rank's private replica) and normalises
+//             the sum.  This is the consumer half of the all-reduce.
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ g, float eps,
                                                        int D, int8_t* __restrict__ xq, float* __restrict__ xd,
                                                        float* __restrict__ xs16, __nv_bfloat16* __restrict__ hb,
-                                                       float* __restrict__ hf, const SymTable sym, int signal_ready,
-                                                       float4* __restrict__ zero, int zero_n4) {
+                                                       float* __restrict__ hf, const SymTable sym, int sym_mode,
+                                                       float4* __restrict__ zero, int zero_n4, size_t slot_off,
+                                                       int slot_rows) {
   __shared__ float red[32];
   const int t = blockIdx.x;
-  const float* xr = x + (size_t)t * D;
+  float* xr = x + (size_t)t * D;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int nblk = D / 32;
   float v[kRmsRegs], gg[kRmsRegs];
@@ -110,10 +117,40 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
     gg[k] = (blk < nblk && g) ? g[blk * 32 + lane] : 1.f;
   }
   pdl_wait();
+  const float* slot0 = nullptr;
+  size_t slot_stride = 0;
+  if (sym_mode == 2) {
+    __shared__ uint32_t s_seq;
+    if (threadIdx.x < (unsigned)sym.world) {            // one thread per rank flag
+      const uint32_t seq = sym_slots_cur_seq(sym);
+      sym_wait_flag(sym, kSymSlotCh0 + threadIdx.x, seq);  // on a time-out the status word says so; the sum is then wrong, not hung
+      if (threadIdx.x == 0) s_seq = seq;
+    }
+    __syncthreads();
+    slot_stride = (size_t)slot_rows * D;
+    slot0 = (const float*)(sym.base[sym.rank] + slot_off) + (size_t)(s_seq & 1u) * sym.world * slot_stride + (size_t)t * D;
+  }
 #pragma unroll
   for (int k = 0; k < kRmsRegs; k++) {
     const int blk = w + k * nw;
     v[k] = blk < nblk ? xr[blk * 32 + lane] : 0.f;
+  }
+  if (sym_mode == 2) {
+#pragma unroll
+    for (int k = 0; k < kRmsRegs; k++) {
+      const int blk = w + k * nw;
+      if (blk < nblk) {
+        float acc = v[k];
+        for (int r = 0; r < sym.world; r++) acc += __ldcg(slot0 + (size_t)r * slot_stride + blk * 32 + lane);
+        v[k] = acc;
+        xr[blk * 32 + lane] = acc;
+      }
+    }
+    for (int blk = w + kRmsRegs * nw; blk < nblk; blk += nw) {     // long rows: the tail is re-read below, so sum it in place first
+      float acc = xr[blk * 32 + lane];
+      for (int r = 0; r < sym.world; r++) acc += __ldcg(slot0 + (size_t)r * slot_stride + blk * 32 + lane);
+      xr[blk * 32 + lane] = acc;
+    }
   }
   // Clear the output of the split-K GEMM that consumes this norm (its splits add their partial sums).
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < zero_n4; i += gridDim.x * blockDim.x)
@@ -148,21 +185,24 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
       quantize_block32(o, lane, xq + (size_t)t * D + blk * 32, xd + (size_t)t * (D / 32) + blk,
                        xs16 + (size_t)t * (D / 16) + blk * 2);
   }
-  // Tensor parallel: x is replicated and peers add into it from their row-parallel kernels; tell them
+  // Tensor parallel, all-reduce form: x is replicated and peers add into it from their row-parallel kernels; tell them
   // this rank has finished reading the values it needed.
-  if (signal_ready) sym_signal_ready(sym, gridDim.x);
+  if (sym_mode == 1) sym_signal_ready(sym, gridDim.x);
 }
 
-// sym non-null: x lives in the symmetric heap and the next row-parallel kernel of every rank will add
-// into it; this kernel then ends by signalling that this rank has read x (see sym.cuh).
+// sym_mode 0: plain.  1: x lives in the symmetric heap and the next row-parallel kernel of every rank will add into
+// it; this kernel then ends by signalling that this rank has read x (see sym.cuh).  2: add the per-rank slots at heap
+// offset slot_off ([2][world][slot_rows][D] fp32) into x first (see the kernel).
 // zero / zero_n: an fp32 buffer (16-byte aligned, zero_n a multiple of 4) that the kernel clears on the side.
-B200_API int b200_rmsnorm(const float* x, const float* g, float eps, int T, int D, void* xq, float* xd,
-                          float* xs16, void* hb, float* hf, const SymTable* sym, float* zero, long zero_n,
-                          cudaStream_t st) {
+B200_API int b200_rmsnorm(float* x, const float* g, float eps, int T, int D, void* xq, float* xd,
+                          float* xs16, void* hb, float* hf, const SymTable* sym, int sym_mode, float* zero, long zero_n,
+                          size_t slot_off, int slot_rows, cudaStream_t st) {
   if (D % 32 || (zero && ((zero_n % 4) || ((uintptr_t)zero % 16)))) return B200_ERR_BAD_ARG;
+  if ((sym_mode != 0 && !sym) || sym_mode < 0 || sym_mode > 2 || (sym_mode == 2 && (T > slot_rows || (slot_off % 16)))) return B200_ERR_BAD_ARG;
   const int threads = D >= 4096 ? 1024 : D >= 1024 ? 512 : 256;
   return launch_pdl(rmsnorm_kernel, dim3(T), dim3(threads), 0, st, x, g, eps, D, (int8_t*)xq, xd, xs16,
-                    (__nv_bfloat16*)hb, hf, sym ? *sym : SymTable{}, sym ? 1 : 0, (float4*)zero, zero ? (int)(zero_n / 4) : 0);
+                    (__nv_bfloat16*)hb, hf, sym ? *sym : SymTable{}, sym ? sym_mode : 0, (float4*)zero, zero ? (int)(zero_n / 4) : 0,
+                    slot_off, slot_rows);
 }
 
 // Sequence-sharded tensor-parallel prefill: this rank owns rows [row0, row0 + T) of the residual
@@ -427,6 +467,61 @@ B200_API int b200_argmax(const float* logits, int T, int V, int* out_id, float* 
                     tickets);
 }
 
+// Tensor-parallel arg-max merge: every rank holds, per row, the best (value, id) of its vocabulary shard.  Each
+// rank stores its pairs into its slot of a [2][world][rows][2] word tensor on every rank, raises its flag, waits for
+// the world flags and picks the best pair (highest value, lowest id on ties) from identical data, so all ranks
+// agree.  One CTA, one launch; slot parity and sequence number work as in the slot all-reduce (sym.cuh).
+__global__ void __launch_bounds__(1024) argmax_merge_kernel(int* __restrict__ out_id, const float* __restrict__ out_val, int nb,
+                                                            const SymTable sym, size_t merge_off, int rows) {
+  __shared__ uint32_t s_seq;
+  pdl_trigger();
+  pdl_wait();
+  SymControl* me = sym_ctl(sym, sym.rank);
+  const uint32_t seq = *(volatile uint32_t*)&me->merge_seq + 1u;
+  const size_t buf = seq & 1u;
+  for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+    const size_t off = merge_off + (((buf * sym.world + sym.rank) * rows + b) * 2) * 4;
+    sym_st_all_f32(sym, off, out_val[b]);
+    sym_st_all_f32(sym, off + 4, __int_as_float(out_id[b]));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    me->merge_seq = seq;
+    s_seq = seq;
+    __threadfence_system();
+    const size_t foff = offsetof(SymControl, flag) + 4 * (kSymMergeCh0 + sym.rank);
+    if (sym.use_mc) {
+      asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(sym.mc_base + foff), "r"(1u) : "memory");
+    } else {
+      for (int p = 0; p < sym.world; p++)
+        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(sym.base[p] + foff), "r"(1u) : "memory");
+    }
+  }
+  if (threadIdx.x < (unsigned)sym.world) sym_wait_flag(sym, kSymMergeCh0 + threadIdx.x, seq);
+  __syncthreads();
+  const float* slots = (const float*)(sym.base[sym.rank] + merge_off) + buf * sym.world * rows * 2;
+  for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int r = 0; r < sym.world; r++) {
+      const float v = __ldcg(slots + ((size_t)r * rows + b) * 2);
+      const int i = __float_as_int(__ldcg(slots + ((size_t)r * rows + b) * 2 + 1));
+      if (v > bv || (v == bv && i < bi)) {
+        bv = v;
+        bi = i;
+      }
+    }
+    if (bi != 0x7fffffff) out_id[b] = bi;
+  }
+}
+// out_id / out_val: this rank's per-row arg-max (global ids) and maxima; on return out_id holds the global winner.
+// merge_off: heap offset of [2][world][rows][2] 32-bit words; nb <= rows.
+B200_API int b200_argmax_merge(int* out_id, const float* out_val, int nb, const SymTable* sym, size_t merge_off, int rows,
+                               cudaStream_t st) {
+  if (!sym || nb < 1 || nb > rows || (merge_off % 16)) return B200_ERR_BAD_ARG;
+  return launch_pdl(argmax_merge_kernel, dim3(1), dim3(nb <= 256 ? 256 : 1024), 0, st, out_id, out_val, nb, *sym, merge_off, rows);
+}
+
 // Temperature / top-k / top-p sampling of one token per row.  One block per row.  The candidate
 // set is the top-k (k <= 64) found by repeated block arg-max, which is exact and cheap for the
 // small k that serving uses; top-p then trims the sorted candidates.  `u` holds one uniform random
@@ -438,6 +533,11 @@ __global__ void sample_topk_kernel(const float* __restrict__ logits, int V, floa
   __shared__ int si[32];
   __shared__ float cand_v[64];
   __shared__ int cand_i[64];
+  __shared__ int n_cand, s_stop;      // candidates found; set when no finite entry is left (NaN rows, -inf tails)
+  if (threadIdx.x == 0) {
+    n_cand = 0;
+    s_stop = 0;
+  }
   const int t = blockIdx.x;
   const float* l = logits + (size_t)t * V;
   float* mask = scratch + (size_t)t * V;  // copy we can knock entries out of
@@ -474,13 +574,24 @@ __global__ void sample_topk_kernel(const float* __restrict__ logits, int V, floa
           sv[0] = sv[j];
           si[0] = si[j];
         }
-      cand_v[k] = sv[0];
-      cand_i[k] = si[0];
-      if (si[0] < V) mask[si[0]] = -INFINITY;
+      if (si[0] >= 0 && si[0] < V) {
+        cand_v[k] = sv[0];
+        cand_i[k] = si[0];
+        n_cand = k + 1;
+        mask[si[0]] = -INFINITY;
+      } else {
+        s_stop = 1;          // nothing comparable left: every remaining entry is -inf or NaN
+      }
     }
     __syncthreads();
+    if (s_stop) break;
   }
   if (threadIdx.x == 0) {
+    top_k = n_cand;
+    if (top_k == 0) {        // a row without a single finite logit: a defined id instead of a sentinel
+      out_id[t] = 0;
+      return;
+    }
     const float inv_t = 1.f / fmaxf(temperature, 1e-6f);
     const float m = cand_v[0];
     float p[64];
@@ -515,7 +626,7 @@ __global__ void sample_topk_kernel(const float* __restrict__ logits, int V, floa
 }
 B200_API int b200_sample_topk(const float* logits, int T, int V, float temperature, int top_k, float top_p,
                               const float* u, int* out_id, float* scratch, cudaStream_t st) {
-  if (top_k < 1 || top_k > 64) return B200_ERR_BAD_ARG;
+  if (top_k < 1 || top_k > 64 || top_k > V) return B200_ERR_BAD_ARG;
   sample_topk_kernel<<<T, 1024, 0, st>>>(logits, V, temperature, top_k, top_p, u, out_id, scratch);
   return (int)cudaGetLastError();
 }
@@ -585,7 +696,7 @@ static float* noalloc_scratch_for_current_device(cudaError_t* err) {
 
 B200_API int b200_sample_topk_noalloc(const float* logits, int T, int V, float temperature, int top_k, float top_p,
                                       const float* u, int* out_id, cudaStream_t stream) {
-  if (T < 1 || V < 1 || top_k < 1 || top_k > 64) return B200_NOALLOC_ERR_BAD_ARG;
+  if (T < 1 || V < 1 || top_k < 1 || top_k > 64 || top_k > V) return B200_NOALLOC_ERR_BAD_ARG;
   if ((unsigned long long)T * (unsigned long long)V > (unsigned long long)B200_SAMPLE_NOALLOC_MAX_ELEMS) {
     std::fprintf(stderr, "b200_sample_topk_noalloc: T*V = %llu exceeds the built-in scratch of %u floats\n",
                  (unsigned long long)T * (unsigned long long)V, (unsigned)B200_SAMPLE_NOALLOC_MAX_ELEMS);

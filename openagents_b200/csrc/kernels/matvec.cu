@@ -13,7 +13,7 @@
 using namespace b200;
 
 enum { WT_Q4KR = 0, WT_Q6KR = 1, WT_Q8R = 2, WT_BF16 = 3 };
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU_Q8 = 2, EPI_SWIGLU_F32 = 3, EPI_ALLREDUCE = 4 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU_Q8 = 2, EPI_SWIGLU_F32 = 3, EPI_ALLREDUCE = 4, EPI_SLOTS = 5 };
 
 struct MatvecArgs {
   const uint8_t* w;     // main plane
@@ -35,8 +35,12 @@ struct MatvecArgs {
   // EPI_ALLREDUCE: this rank's partial products are added into the fp32 tensor at byte offset
   // sym_off ([nb][ldy]) of EVERY rank's symmetric heap, and the kernel ends with a cross-rank
   // barrier, so on completion each replica holds resid + sum of all ranks' partials.
+  // EPI_SLOTS: the partial products are STORED into this rank's slot of the fp32 tensor
+  // [2][world][slot_rows][ldy] at byte offset sym_off of every rank's heap and the kernel ends by raising this rank's
+  // flag; the RMSNorm that follows adds the slots up (see sym_slots_* in sym.cuh).  No barrier, no handshake.
   SymTable sym;
   size_t sym_off;
+  int slot_rows;
   int prefetch;         // bring this CTA's weight rows into L2 before waiting for the previous kernel
   int wait_ready;       // EPI_ALLREDUCE: check the peers' "finished reading" signals before the first add
 };
@@ -175,20 +179,23 @@ __device__ __forceinline__ void matvec_epilogue(const MatvecArgs& a, const float
   const int n = blockIdx.x * R + lane;
   const bool live = lane < R && n < a.N;
   float v = res[lane * B + b];
-  if (a.bias && live && (a.epi != EPI_ALLREDUCE || a.sym.rank == 0)) v += a.bias[n];
+  if (a.bias && live && ((a.epi != EPI_ALLREDUCE && a.epi != EPI_SLOTS) || a.sym.rank == 0)) v += a.bias[dual ? 2 * n : n];
   if (a.epi == EPI_STORE) {
     if (live) a.y[(size_t)b * a.ldy + n] = v;
     if (dual && live) {
-      float v2 = res[32 * B + lane * B + b] + (a.bias ? a.bias[a.N + n] : 0.f);
+      float v2 = res[32 * B + lane * B + b] + (a.bias ? a.bias[2 * n + 1] : 0.f);
       a.y[(size_t)b * a.ldy + a.N + n] = v2;
     }
   } else if (a.epi == EPI_RESID) {
     if (live) a.y[(size_t)b * a.ldy + n] = a.resid[(size_t)b * a.ldy + n] + v;
   } else if (a.epi == EPI_ALLREDUCE) {
     if (live) sym_red_all_f32(a.sym, a.sym_off + ((size_t)b * a.ldy + n) * 4, v);
+  } else if (a.epi == EPI_SLOTS) {
+    const size_t slot = (size_t)(sym_slots_next_seq(a.sym) & 1u) * a.sym.world + a.sym.rank;
+    if (live) sym_st_all_f32(a.sym, a.sym_off + ((slot * a.slot_rows + b) * a.ldy + n) * 4, v);
   } else {
     float u = res[32 * B + lane * B + b];
-    if (a.bias && live) u += a.bias[a.N + n];
+    if (a.bias && live) u += a.bias[2 * n + 1];
     const float act = live ? silu(v) * u : 0.f;
     if (a.epi == EPI_SWIGLU_F32) {
       if (live) a.y[(size_t)b * a.ldy + n] = act;
@@ -213,13 +220,14 @@ __global__ void __launch_bounds__(256) matvec_q_kernel(const MatvecArgs a) {
     const int r0 = blockIdx.x * R;
     const int nr = min(R, a.N - r0);
     if (nr > 0 && a.prefetch) {
-      const size_t bytes = (size_t)nr * rbp;     // multiple of 16: every row is
+      // dual: the (gate, up) rows of output row n are rows 2n and 2n + 1 of the matrix, so one range of 2 nr rows
+      const size_t total = (size_t)nr * rbp * (DUAL ? 2 : 1);     // multiple of 16: every row is
       constexpr uint32_t CH = 16384;
-      const int nch = (int)((bytes + CH - 1) / CH);
-      for (int c = threadIdx.x; c < nch * (DUAL ? 2 : 1); c += 256) {
-        const int m = c / nch, cc = c - m * nch;
-        const size_t off = (size_t)cc * CH;
-        prefetch_l2(a.w + ((size_t)r0 + (size_t)m * a.N) * rbp + off, (uint32_t)min((size_t)CH, bytes - off));
+      const int nch = (int)((total + CH - 1) / CH);
+      const uint8_t* base = a.w + (size_t)r0 * (DUAL ? 2 : 1) * rbp;
+      for (int c = threadIdx.x; c < nch; c += 256) {
+        const size_t off = (size_t)c * CH;
+        prefetch_l2(base + off, (uint32_t)min((size_t)CH, total - off));
       }
     }
   }
@@ -271,8 +279,9 @@ __global__ void __launch_bounds__(256) matvec_q_kernel(const MatvecArgs a) {
     const int nn = live[i] ? n : 0;
 #pragma unroll
     for (int mi = 0; mi < NM; mi++) {
-      wr[mi][i] = a.w + (size_t)(nn + mi * a.N) * rb;
-      w2r[mi][i] = a.w2 ? a.w2 + (size_t)(nn + mi * a.N) * w2_per_row : nullptr;
+      const size_t wrow = DUAL ? (size_t)(2 * nn + mi) : (size_t)nn;     // dual: rows interleaved (gate_n, up_n)
+      wr[mi][i] = a.w + wrow * rb;
+      w2r[mi][i] = a.w2 ? a.w2 + wrow * w2_per_row : nullptr;
     }
   }
   // Load phase (all rows of the warp, both matrices) then compute phase, per 32-unit column block.
@@ -305,6 +314,7 @@ __global__ void __launch_bounds__(256) matvec_q_kernel(const MatvecArgs a) {
   __syncthreads();
   matvec_epilogue<B, R>(a, res, DUAL);
   if (a.epi == EPI_ALLREDUCE) sym_kernel_end_barrier(a.sym, 0, gridDim.x, a.wait_ready != 0);
+  if (a.epi == EPI_SLOTS) sym_slots_signal(a.sym, gridDim.x);
 }
 
 // bf16 weights [N][K] against fp32 activations.
@@ -330,8 +340,8 @@ __global__ void __launch_bounds__(256) matvec_bf16_kernel(const MatvecArgs a) {
 #pragma unroll
     for (int b = 0; b < B; b++) acc0[b] = acc1[b] = 0.f;
     if (n < a.N) {
-      const __nv_bfloat16* wr0 = W + (size_t)n * a.K;
-      const __nv_bfloat16* wr1 = W + (size_t)(n + a.N) * a.K;
+      const __nv_bfloat16* wr0 = W + (size_t)(DUAL ? 2 * n : n) * a.K;     // dual: rows interleaved (gate_n, up_n)
+      const __nv_bfloat16* wr1 = W + (size_t)(2 * n + 1) * a.K;
 #pragma unroll 2
       for (int k = lane * 8; k < a.K; k += 256) {
         const uint4 q0 = ldg_stream(wr0 + k);
@@ -371,6 +381,7 @@ __global__ void __launch_bounds__(256) matvec_bf16_kernel(const MatvecArgs a) {
   __syncthreads();
   matvec_epilogue<B>(a, res, DUAL);
   if (a.epi == EPI_ALLREDUCE) sym_kernel_end_barrier(a.sym, 0, gridDim.x, a.wait_ready != 0);
+  if (a.epi == EPI_SLOTS) sym_slots_signal(a.sym, gridDim.x);
 }
 
 template <int WT, int B, bool DUAL, int RW>
@@ -416,12 +427,13 @@ static int dispatch_wt(int wt, const MatvecArgs& a, cudaStream_t st) {
   return B200_ERR_BAD_ARG;
 }
 
-// wt: weight layout; nb: tokens (1..8).  For the SwiGLU epilogues `w` holds 2N rows (gate rows
-// first, then up rows) and N is the width of one of them.
+// wt: weight layout; nb: tokens (1..8).  For the SwiGLU epilogues `w` holds 2N rows, interleaved
+// (gate_0, up_0, gate_1, ...: the order the GEMMs' SwiGLU epilogues pair rows in, so one copy of the matrix
+// serves every batch size) and N is the width of one of them; a bias is interleaved the same way.
 B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, int nb, const void* xq,
                          const float* xd, const float* xs16, const float* xf, int epi, const float* bias,
                          const float* resid, float* y, int ldy, void* oq, float* od, float* os16,
-                         const SymTable* sym, size_t sym_off, int wait_ready, cudaStream_t st) {
+                         const SymTable* sym, size_t sym_off, int wait_ready, int slot_rows, cudaStream_t st) {
   if (nb < 1 || nb > 8) return B200_ERR_BAD_ARG;
   if (wt == WT_BF16 ? (K % 8 != 0) : (K % 256 != 0 && !(wt == WT_Q8R && K % 32 == 0))) return B200_ERR_BAD_ARG;
   if (epi == EPI_SWIGLU_Q8 && N % 32) return B200_ERR_BAD_ARG;
@@ -429,8 +441,9 @@ B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, in
   a.w = (const uint8_t*)w; a.w2 = (const __half*)w2; a.N = N; a.K = K; a.nb = nb;
   a.xq = (const int8_t*)xq; a.xd = xd; a.xs16 = xs16; a.xf = xf; a.epi = epi; a.bias = bias;
   a.resid = resid; a.y = y; a.ldy = ldy; a.oq = (int8_t*)oq; a.od = od; a.os16 = os16;
-  if (epi == EPI_ALLREDUCE) {
-    if (!sym) return B200_ERR_BAD_ARG;
+  a.slot_rows = slot_rows;
+  if (epi == EPI_ALLREDUCE || epi == EPI_SLOTS) {
+    if (!sym || (epi == EPI_SLOTS && nb > slot_rows)) return B200_ERR_BAD_ARG;
     a.sym = *sym;
     a.sym_off = sym_off;
   } else {

@@ -20,13 +20,15 @@ extern "C" {
 
 // Return codes besides 0 (success) and positive cudaError_t values.
 #define B200_NOALLOC_ERR_TOO_LARGE (-1)   // T * V exceeds B200_SAMPLE_NOALLOC_MAX_ELEMS
-#define B200_NOALLOC_ERR_BAD_ARG (-2)     // T < 1, V < 1, or top_k outside 1..64
+#define B200_NOALLOC_ERR_BAD_ARG (-2)     // T < 1, V < 1, top_k outside 1..64, or top_k > V
 
 // Temperature / top-k / top-p sampling of one token per row of `logits` ([T][V] fp32, device
 // memory), exactly as b200_sample_topk does, but with the T * V floats of working space taken from
 // an array compiled into the library.  The caller still owns and passes every input and output:
 // `u` ([T] uniform random numbers in [0,1)) and `out_id` ([T] int32) are device pointers.
 //
+// * A row without a single finite logit (all NaN or -inf) yields token id 0; fewer than top_k finite
+//   entries means the candidates are the finite ones only.
 // * Calls no cudaMalloc, cudaFree or any other allocating routine.
 // * T * V larger than B200_SAMPLE_NOALLOC_MAX_ELEMS is refused with B200_NOALLOC_ERR_TOO_LARGE
 //   (and one line on stderr); nothing is launched.

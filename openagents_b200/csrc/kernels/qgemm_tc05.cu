@@ -1,54 +1,90 @@
-// Quantized-weight GEMM on tcgen05 with the dequantization inside the pipeline:
-//     Y[t][n] (+)= sum_k X[t][k] * W[n][k],   W in Q4_K-R or Q6_K-R, X bf16
-// used for decode batches above the mat-vec range and for prefill.  The packed weights are read
-// from HBM exactly once, in their 4.5- or 6.5-bit form.
+// Quantized-weight GEMM for decode batches (up to 64 tokens per tile) on tcgen05 with the
+// dequantization inside the pipeline:
+//     Y[t][n] (+)= sum_k X[t][k] * W[n][k],   W in Q4_K-R or Q6_K-R (row-major packed), X bf16.
+// The packed weights are read from HBM exactly once, in their 4.5- or 6.6-bit form; nothing keeps a
+// bf16 copy of them.
 //
-// The weight tile is the MMA's M operand (128 weight rows), the tokens are its N operand (BN), so a
-// 64-token decode batch still fills the 128-lane tensor-memory accumulator.  Roles in a CTA:
-//   warp 0      one thread: TMA loads of raw packed weight tiles (128 rows x one superblock)
-//   warp 1      one thread: tcgen05.mma issue; the warp owns the tensor-memory allocation
-//   warps 2-17  expand raw tiles into 128x64 bf16 operand tiles in the 128-byte-swizzled layout the MMA
-//               reads: a pair of warps owns one slot of an 8-slot operand ring and every eighth K
-//               block (one mask yields two adjacent bf16 mantissas, one fma applies the scale and
-//               offset precomputed at load); warps 2-9 then run the epilogue
-//   warp 18     one thread: TMA loads of the activation tiles
-// Rings hand over through mbarriers; every wait is bounded and reports through `status`.
-// Split-K (grid.z) adds partial tiles into fp32 output with `red.global.add`.
+// The weight tile is the MMA's M operand (128 weight rows), the tokens are its N operand (64), so a
+// decode batch fills the 128-lane accumulator without padding.  A persistent CTA (one per SM) walks
+// work items (128-row tile, K split) with a ring of stages of one superblock (256 of K) each:
+//   warp 0      one thread: TMA loads of the raw packed superblocks (128 rows x 144 / 208 bytes)
+//   warp 1      one thread: tcgen05.mma, TS form: the expanded weights are the A operand in TENSOR
+//               MEMORY, the activations the B operand in shared memory; owns the allocation
+//   warp 2      one thread: TMA loads of the activation tiles (from L2; they are a few hundred KB)
+//   warps 4-11  expansion: a thread owns one weight row (= one tensor-memory lane) and two 64-wide K
+//               blocks of every stage: one mask puts two adjacent 4-bit values into the mantissas of
+//               a bf16 pair, one subtraction and one fma apply the sub-block scale and offset, and
+//               tcgen05.st writes the 64 values where the MMA reads them, with no shared-memory round
+//               trip, no swizzle arithmetic and no proxy fence.  The same warps run the epilogue of
+//               item i after they have expanded the first stage of item i + 1 (two accumulators).
+// Each scheduler of the SM hosts one single-thread role warp and two expansion warps: the role threads run
+// dependent instruction chains and fall behind when they have to share their scheduler with more busy warps
+// (measured: with sixteen expansion warps the MMA thread needed 1400 cycles to issue a stage's sixteen MMAs),
+// which is also why the issuing loop below works on precomputed descriptor words.
+// Stages hand over through mbarriers; every wait is bounded and reports through `status`.
 //
-// GEMM-shaped reference math: cs336-a2-benchmark-workload.ts:251-292.
+// Epilogues: plain store (fp32 and/or bf16), accumulation with `red` (K may be split), SwiGLU over
+// interleaved (gate, up) rows, and the tensor-parallel form that stores the partial tile into this
+// rank's slot on every rank (see sym_slots_* in sym.cuh).
+//
+// GEMM-shaped reference math: apps/openagents.com/workers/api/src/cs336-a2-benchmark-workload.ts:251-292;
+// the quantized formats are the ones the reference serves (docs/muse/muse-glimmer.md:112).
 #include "tc05.cuh"
+#include "../comm/sym.cuh"
 
 using namespace b200;
 using namespace b200::tc;
 
 enum { QW_Q4KR = 0, QW_Q6KR = 1 };
-enum { QEPI_STORE = 0, QEPI_ADD = 1 };
+enum { QEPI_STORE = 0, QEPI_ADD = 1, QEPI_SWIGLU = 2, QEPI_SLOTS = 3 };
 
 struct QGemmArgs {
-  const uint8_t* w;      // tile-major packed weights: [N/128][K/256][128 rows][RAW bytes]
-  const __half* w2;      // unused (scales live in the tile-major rows)
-  float* y;              // [T][ldy] fp32
-  const float* bias;     // [N] or null (applied by split 0)
-  int ldy, T, N, K;
+  const __half* w2;      // Q6_K-R: fp16 d per (row, superblock); unused for Q4_K-R
+  float* out_f32;        // [T][ldo] (STORE / ADD), or null
+  __nv_bfloat16* out_bf16;   // [T][ldo] (STORE) or [T][ldo] with N / 2 live columns (SWIGLU), or null
+  const float* bias;     // [N] in the row order of W, or null (applied by K split 0; SLOTS: by rank 0)
+  int ldo, T, N, K;
   int epi;
-  int sb_per_split;      // superblocks per grid.z slice
+  int splits, sb_per_split, n_items;
   int* status;
-  long long* dbg;        // optional [grid][8] cycle counters (profiling builds of the caller only)
-};
-
-template <int WT>
-struct QTraits {
-  static constexpr int RAW = WT == QW_Q4KR ? 160 : 224;   // bytes per row per superblock (tile-major form)
+  SymTable sym;          // SLOTS only
+  size_t slot_off;       // heap offset of the slot tensor [2][world][slot_rows][ldo] fp32
+  int slot_rows;
 };
 
 __device__ __forceinline__ uint32_t bf162_as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 __device__ __forceinline__ __nv_bfloat162 u32_as_bf162(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
 
-// Expand 32 elements (one sub-block: 4 words) into four 16-byte chunks of bf16.
-// Q4_K: value = a * (16 + q) + c; the nibble sits in the mantissa of bf16 16.0.  `ac` = (a, c).
-__device__ __forceinline__ void expand_q4k(uint32_t ac, const uint4 q, uint4 (&out)[4]) {
-  const __nv_bfloat162 acv = u32_as_bf162(ac);
-  const __nv_bfloat162 A2 = __halves2bfloat162(acv.x, acv.x), C2 = __halves2bfloat162(acv.y, acv.y);
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D (tensor memory) (+)= A (tensor memory: lane = row, 32-bit column j = elements 2j, 2j + 1 of the K slice)
+// x B (shared-memory descriptor).
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Q4_K-R: one 32-element sub-block (4 words, word w = elements 8w .. 8w + 7, element i at bit
+// 4 (i / 2) + 16 (i % 2)) -> 16 words of bf16 pairs.  The nibble sits in the mantissa of bf16 16.0 (one shift and
+// one lop3 for two weights); (16 + q) - 24 = q - 8 is exact, and value = a * (q - 8) + c with c = 8 a - min keeps
+// the constant small (the sub-block's range is roughly centred on it), so rounding a and c to bf16 costs no more
+// than rounding the weight itself does.
+__device__ __forceinline__ void expand_q4k(__nv_bfloat162 A2, __nv_bfloat162 C2, const uint4 q, uint32_t* out) {
+  const __nv_bfloat162 off = __halves2bfloat162(__float2bfloat16(24.f), __float2bfloat16(24.f));
   const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
   for (int i = 0; i < 4; i++) {
@@ -57,16 +93,16 @@ __device__ __forceinline__ void expand_q4k(uint32_t ac, const uint4 q, uint4 (&o
     const uint32_t t1 = ((v >> 1) & 0x00780078u) | 0x41804180u;
     const uint32_t t2 = ((v >> 5) & 0x00780078u) | 0x41804180u;
     const uint32_t t3 = ((v >> 9) & 0x00780078u) | 0x41804180u;
-    out[i].x = bf162_as_u32(__hfma2(u32_as_bf162(t0), A2, C2));
-    out[i].y = bf162_as_u32(__hfma2(u32_as_bf162(t1), A2, C2));
-    out[i].z = bf162_as_u32(__hfma2(u32_as_bf162(t2), A2, C2));
-    out[i].w = bf162_as_u32(__hfma2(u32_as_bf162(t3), A2, C2));
+    out[4 * i + 0] = bf162_as_u32(__hfma2(__hsub2(u32_as_bf162(t0), off), A2, C2));
+    out[4 * i + 1] = bf162_as_u32(__hfma2(__hsub2(u32_as_bf162(t1), off), A2, C2));
+    out[4 * i + 2] = bf162_as_u32(__hfma2(__hsub2(u32_as_bf162(t2), off), A2, C2));
+    out[4 * i + 3] = bf162_as_u32(__hfma2(__hsub2(u32_as_bf162(t3), off), A2, C2));
   }
 }
 
-// Q6_K: 6-bit value = nibble | two high bits; (64 + q) - 96 = q - 32 is exact in bf16.  `ss` holds
+// Q6_K-R: 6-bit value = nibble | two high bits; (64 + q) - 96 = q - 32 is exact in bf16.  `ss` holds
 // the two bf16 scales of the sub-block (first and second 16 elements).
-__device__ __forceinline__ void expand_q6k(const uint4 lo, const uint2 tw, uint32_t ss, uint4 (&out)[4]) {
+__device__ __forceinline__ void expand_q6k(const uint4 lo, const uint2 tw, uint32_t ss, uint32_t* out) {
   const __nv_bfloat162 sv = u32_as_bf162(ss);
   const __nv_bfloat162 off = __halves2bfloat162(__float2bfloat16(96.f), __float2bfloat16(96.f));
   const uint32_t w[4] = {lo.x, lo.y, lo.z, lo.w};
@@ -79,250 +115,396 @@ __device__ __forceinline__ void expand_q6k(const uint4 lo, const uint2 tw, uint3
     const uint32_t q1 = ((v >> 4) & 0x000F000Fu) | (((T >> 2) & 0x00030003u) << 4);
     const uint32_t q2 = ((v >> 8) & 0x000F000Fu) | (((T >> 8) & 0x00030003u) << 4);
     const uint32_t q3 = ((v >> 12) & 0x000F000Fu) | (((T >> 10) & 0x00030003u) << 4);
-    out[i].x = bf162_as_u32(__hmul2(__hsub2(u32_as_bf162((q0 << 1) | 0x42804280u), off), S2));
-    out[i].y = bf162_as_u32(__hmul2(__hsub2(u32_as_bf162((q1 << 1) | 0x42804280u), off), S2));
-    out[i].z = bf162_as_u32(__hmul2(__hsub2(u32_as_bf162((q2 << 1) | 0x42804280u), off), S2));
-    out[i].w = bf162_as_u32(__hmul2(__hsub2(u32_as_bf162((q3 << 1) | 0x42804280u), off), S2));
+    out[4 * i + 0] = bf162_as_u32(__hmul2(__hsub2(u32_as_bf162((q0 << 1) | 0x42804280u), off), S2));
+    out[4 * i + 1] = bf162_as_u32(__hmul2(__hsub2(u32_as_bf162((q1 << 1) | 0x42804280u), off), S2));
+    out[4 * i + 2] = bf162_as_u32(__hmul2(__hsub2(u32_as_bf162((q2 << 1) | 0x42804280u), off), S2));
+    out[4 * i + 3] = bf162_as_u32(__hmul2(__hsub2(u32_as_bf162((q3 << 1) | 0x42804280u), off), S2));
   }
 }
 
-constexpr int QBM = 128, QBK = 64;
+constexpr int QBM = 128, QBN = 64, QSB = 256;      // weight rows per tile, tokens per tile, K per stage
+constexpr int kRoleWarps = 4;                      // raw loads, MMA, activation loads, one idle (keeps warp % 4 = lane quarter)
+constexpr int kDqWarps = 8;                        // expansion warps: lane quarter = warp & 3, K half = (warp - 4) >> 2
+constexpr int kQThreads = 32 * (kRoleWarps + kDqWarps);
+constexpr int kXStage = 4 * QBN * 64 * 2;          // four 64-wide K blocks of activations: 32 KB
+constexpr int kAS = 3;                             // operand stages in tensor memory (and activation stages in shared memory)
+// Every CTA walks the K range of its item from a different starting superblock (rotated by the CTA index): at any
+// moment the SMs then read different slices of the activations, instead of all of them pulling the same few L2 lines.
+__device__ __forceinline__ int rot_sb(int sb0, int sb1, int i) { const int n = sb1 - sb0; return sb0 + (i + (int)blockIdx.x) % n; }
 
-template <int WT, int BN, int RS, int AS, int XS>
-__global__ void __launch_bounds__(608) qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs a) {
-  constexpr int RAW = QTraits<WT>::RAW;
-  constexpr int RAW_BYTES = QBM * RAW, A_BYTES = QBM * QBK * 2, X_BYTES = BN * QBK * 2;
+template <int WT> struct QTraits { static constexpr int RAWB = WT == QW_Q4KR ? 144 : 208; static constexpr int RS = WT == QW_Q4KR ? 6 : 4; };
+
+// tcgen05.mma (TS form) with the shared-memory descriptor given as its two 32-bit halves: the issuing thread adds
+// block offsets to the low word only (the 14-bit address field cannot carry out of it), one instruction per MMA.
+__device__ __forceinline__ void umma_ts_lohi(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 bd, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <int WT>
+__global__ void __launch_bounds__(kQThreads, 1) qgemm_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                             const __grid_constant__ CUtensorMap tmX, const QGemmArgs a) {
+  constexpr int RAWB = QTraits<WT>::RAWB, RS = QTraits<WT>::RS;
+  constexpr int RAW_BYTES = QBM * RAWB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* sA = smem;                               // AS x 16 KB, swizzled operand tiles
-  uint8_t* sX = sA + AS * A_BYTES;                  // XS x BN*128 B, swizzled activation tiles
-  uint8_t* sR = sX + XS * X_BYTES;                  // RS raw packed tiles
-  uint64_t* bars = (uint64_t*)(sR + ((RS * RAW_BYTES + 127) & ~127));
-  uint64_t* raw_full = bars;
-  uint64_t* raw_empty = raw_full + RS;
-  uint64_t* a_full = raw_empty + RS;
-  uint64_t* a_empty = a_full + AS;
-  uint64_t* x_full = a_empty + AS;
-  uint64_t* x_empty = x_full + XS;
-  uint64_t* tfull = x_empty + XS;
-  uint32_t* tmem_holder = (uint32_t*)(tfull + 1);
+  uint8_t* sX = smem;                               // kAS stages of activations, 128-byte swizzle
+  uint8_t* sR = sX + kAS * kXStage;                 // RS raw packed stages
+  uint64_t* bars = (uint64_t*)(sR + RS * RAW_BYTES);
+  uint64_t* raw_full = bars;             // [RS]  TMA bytes landed
+  uint64_t* raw_empty = raw_full + RS;   // [RS]  every expansion warp has read the stage
+  uint64_t* x_full = raw_empty + RS;     // [kAS]
+  uint64_t* a_full = x_full + kAS;       // [kAS] every expansion warp has written its part of the operand
+  uint64_t* done = a_full + kAS;         // [kAS] the stage's MMAs have finished: its activation and operand slots are free
+  uint64_t* tfull = done + kAS;          // [2]   accumulator complete
+  uint64_t* tempty = tfull + 2;          // [2]   accumulator read back by every epilogue warp
+  uint32_t* tmem_holder = (uint32_t*)(tempty + 2);
   volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t0 = blockIdx.x * BN, n0 = blockIdx.y * QBM;
-  long long* dbg = a.dbg ? a.dbg + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 : nullptr;
-  const long long t_start = clock64();
-#define DBG_WAIT(slot_, expr_) do { long long _c = clock64(); expr_; if (dbg && lane == 0) atomicAdd((unsigned long long*)&dbg[slot_], (unsigned long long)(clock64() - _c)); } while (0)
-  const int nsb_total = a.K / 256;
-  const int sb0 = blockIdx.z * a.sb_per_split;
-  const int sb1 = min(nsb_total, sb0 + a.sb_per_split);
-  const int nsb = max(0, sb1 - sb0);
-  const int KB = nsb * 4;
+  const int nsb_total = a.K / QSB;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < RS; s++) {
       mbar_init(smem_u32(raw_full + s), 1);
-      mbar_init(smem_u32(raw_empty + s), 8);  // 4 K blocks x 2 warps
+      mbar_init(smem_u32(raw_empty + s), kDqWarps);
     }
-    for (int s = 0; s < AS; s++) {
-      mbar_init(smem_u32(a_full + s), 2);
-      mbar_init(smem_u32(a_empty + s), 1);
-    }
-    for (int s = 0; s < XS; s++) {
+    for (int s = 0; s < kAS; s++) {
       mbar_init(smem_u32(x_full + s), 1);
-      mbar_init(smem_u32(x_empty + s), 1);
+      mbar_init(smem_u32(a_full + s), kDqWarps);
+      mbar_init(smem_u32(done + s), 1);
     }
-    mbar_init(smem_u32(tfull), 1);
+    for (int s = 0; s < 2; s++) {
+      mbar_init(smem_u32(tfull + s), 1);
+      mbar_init(smem_u32(tempty + s), kDqWarps);
+    }
     *abort_flag = 0;
     fence_barrier_init();
+    tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_holder), BN);
+    tmem_alloc(smem_u32(tmem_holder), 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // tensor-memory columns: accumulators at +0 and +64, operand stages at +128, +256 and +384 (128 columns = 256 of K each)
+  pdl_trigger();
 
   if (warp == 0) {
-    if (lane == 0) {   // raw packed weight tiles, one superblock of 128 rows per stage
-      for (int i = 0; i < nsb; i++) {
-        const int s = i % RS;
-        bool okw; DBG_WAIT(0, okw = mbar_wait(smem_u32(raw_empty + s), ((i / RS) & 1) ^ 1, abort_flag));
-        if (!okw) break;
-        mbar_expect_tx(smem_u32(raw_full + s), RAW_BYTES);
-        // tile-major weights: the 128 rows of one superblock are one contiguous block
-        const uint8_t* src = a.w + ((size_t)blockIdx.y * nsb_total + sb0 + i) * RAW_BYTES;
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(smem_u32(sR + s * RAW_BYTES)), "l"(src), "r"((uint32_t)RAW_BYTES), "r"(smem_u32(raw_full + s))
-                     : "memory");
+    // The weights are not written by any kernel: this thread does not wait for the kernel before this one, so the
+    // first stages stream in while that kernel is still finishing.
+    if (lane == 0) {
+      uint32_t g = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x) {
+        const int tile = item / a.splits, sp = item - tile * a.splits;
+        const int sb0 = sp * a.sb_per_split, sb1 = min(nsb_total, sb0 + a.sb_per_split);
+        for (int sb = sb0; sb < sb1; sb++, g++) {
+          const uint32_t s = g % RS;
+          if (!mbar_wait(smem_u32(raw_empty + s), ((g / RS) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(smem_u32(raw_full + s), RAW_BYTES);
+          tma_load_2d(smem_u32(sR + s * RAW_BYTES), &tmW, smem_u32(raw_full + s), rot_sb(sb0, sb1, sb - sb0) * RAWB, tile * QBM);
+        }
       }
     }
-  } else if (warp == 2 + 2 * AS) {
-    if (lane == 0) {   // activation tiles, one 64-wide K block per stage
-      for (int kb = 0; kb < KB; kb++) {
-        const int s = kb % XS;
-        bool okw; DBG_WAIT(1, okw = mbar_wait(smem_u32(x_empty + s), ((kb / XS) & 1) ^ 1, abort_flag));
-        if (!okw) break;
-        mbar_expect_tx(smem_u32(x_full + s), X_BYTES);
-        tma_load_2d(smem_u32(sX + s * X_BYTES), &tmX, smem_u32(x_full + s), sb0 * 256 + kb * QBK, t0);
+  } else if (warp == 2) {
+    if (lane == 0) {
+      pdl_wait();
+      uint32_t g = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x) {
+        const int tile = item / a.splits, sp = item - tile * a.splits;
+        const int sb0 = sp * a.sb_per_split, sb1 = min(nsb_total, sb0 + a.sb_per_split);
+        for (int sb = sb0; sb < sb1; sb++, g++) {
+          const uint32_t s = g % kAS;
+          if (!mbar_wait(smem_u32(done + s), ((g / kAS) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(smem_u32(x_full + s), kXStage);
+          const int k0 = rot_sb(sb0, sb1, sb - sb0) * QSB;
+          const uint32_t dst = smem_u32(sX + s * kXStage), bar = smem_u32(x_full + s);
+#pragma unroll
+          for (int u = 0; u < 4; u++) tma_load_2d(dst + u * (QBN * 128), &tmX, bar, k0 + u * 64, 0);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = idesc_bf16(QBM, BN);
-      for (int kb = 0; kb < KB; kb++) {
-        const int sa = kb % AS, sx = kb % XS;
-        bool ok1, ok2;
-        DBG_WAIT(2, ok1 = mbar_wait(smem_u32(a_full + sa), (kb / AS) & 1, abort_flag));
-        DBG_WAIT(3, ok2 = mbar_wait(smem_u32(x_full + sx), (kb / XS) & 1, abort_flag));
-        if (!ok1 || !ok2) break;
+      constexpr uint32_t idesc = idesc_bf16(QBM, QBN);
+      const uint64_t bd0 = smem_desc_sw128(smem_u32(sX));
+      const uint32_t b_hi = (uint32_t)(bd0 >> 32), b_lo0 = (uint32_t)bd0;
+      uint32_t g = 0, tcount = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x, tcount++) {
+        const int tile = item / a.splits, sp = item - tile * a.splits;
+        const int n_st = min(nsb_total, (sp + 1) * a.sb_per_split) - sp * a.sb_per_split;
+        (void)tile;
+        const uint32_t acc = tcount & 1;
+        if (!mbar_wait(smem_u32(tempty + acc), ((tcount >> 1) & 1) ^ 1, abort_flag)) break;
         tc_fence_after();
-        const uint64_t ad = smem_desc_sw128(smem_u32(sA + sa * A_BYTES));
-        const uint64_t bd = smem_desc_sw128(smem_u32(sX + sx * X_BYTES));
+        const uint32_t d_tmem = tmem_base + acc * QBN;
+        for (int i = 0; i < n_st; i++, g++) {
+          const uint32_t s = g % kAS, ph = (g / kAS) & 1;
+          if (!mbar_wait(smem_u32(a_full + s), ph, abort_flag) || !mbar_wait(smem_u32(x_full + s), ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_tmem = tmem_base + 128 + s * 128;
+          const uint32_t b_lo = b_lo0 + s * (kXStage >> 4);
+          umma_ts_lohi(d_tmem, a_tmem, b_lo, b_hi, idesc, i != 0 ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < QBK / 16; k++) umma_bf16(tmem_base, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-        umma_commit(smem_u32(a_empty + sa));
-        umma_commit(smem_u32(x_empty + sx));
-      }
-      umma_commit(smem_u32(tfull));
-    }
-  } else {
-    // ---- expansion: sixteen warps; warps 2k and 2k+1 own operand slot k and the K blocks kb = k,
-    // k + 8, ..., each expanding 64 of the tile's 128 rows (a lane takes rows lane and lane + 32 of
-    // its half).  Eight K blocks are in flight and no two slots share a barrier.
-    const int dw = warp - 2, slot = dw >> 1, hh = dw & 1;
-    bool ok = true;
-    for (int kb = slot; kb < KB && ok; kb += AS) {
-      const int i = kb >> 2, g = kb & 3, rs = i % RS;
-      if (dw == 0) { DBG_WAIT(4, ok = mbar_wait(smem_u32(raw_full + rs), (i / RS) & 1, abort_flag)); }
-      else ok = mbar_wait(smem_u32(raw_full + rs), (i / RS) & 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (dw == 0) { DBG_WAIT(5, ok = mbar_wait(smem_u32(a_empty + slot), ((kb / AS) & 1) ^ 1, abort_flag)); }
-      else ok = mbar_wait(smem_u32(a_empty + slot), ((kb / AS) & 1) ^ 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      const long long t_exp = clock64();
-      uint8_t* tile = sA + slot * A_BYTES;
-#pragma unroll
-      for (int rr = 0; rr < 2; rr++) {
-        const int r = 64 * hh + lane + 32 * rr;
-        const uint8_t* rowp = sR + rs * RAW_BYTES + r * RAW;
-        uint8_t* dst = tile + r * 128;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-          const int j = 2 * g + h;
-          uint4 out[4];
-          if constexpr (WT == QW_Q4KR) {
-            expand_q4k(*(const uint32_t*)(rowp + 4 * j), *(const uint4*)(rowp + 32 + j * 16), out);
-          } else {
-            expand_q6k(*(const uint4*)(rowp + 32 + j * 16), *(const uint2*)(rowp + 160 + j * 8),
-                       *(const uint32_t*)(rowp + 4 * j), out);
-          }
-#pragma unroll
-          for (int c = 0; c < 4; c++) *(uint4*)(dst + (((4 * h + c) ^ (r & 7)) << 4)) = out[c];
+          for (int m = 1; m < 16; m++)     // K block m / 4 (8 KB apart in shared memory, 32 columns apart in tensor memory), K step m % 4
+            umma_ts_lohi(d_tmem, a_tmem + (m >> 2) * 32 + (m & 3) * 8, b_lo + (m >> 2) * ((QBN * 128) >> 4) + (m & 3) * 2, b_hi, idesc, 1u);
+          umma_commit(smem_u32(done + s));
         }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (dbg && dw == 0 && lane == 0) atomicAdd((unsigned long long*)&dbg[6], (unsigned long long)(clock64() - t_exp));
-      if (lane == 0) {
-        mbar_arrive(smem_u32(a_full + slot));
-        mbar_arrive(smem_u32(raw_empty + rs));     // this warp is done with its part of the raw tile
+        umma_commit(smem_u32(tfull + acc));      // released even after a failed wait; the flag says why
       }
     }
-    // ---- epilogue: lane quarter = warp % 4, column half = (warp - 2) / 4
-    bool tok = mbar_wait(smem_u32(tfull), 0, abort_flag);
-    tok = __all_sync(0xffffffffu, tok && ok && !*abort_flag);
-    if (tok && nsb > 0 && dw < 8) {
+  } else if (warp >= kRoleWarps) {
+    // ---- expansion + epilogue warps
+    const int dw = warp - kRoleWarps, q = warp & 3, khalf = dw >> 2;      // lane quarter; K blocks 2 khalf, 2 khalf + 1 of a stage
+    const int row = q * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    uint32_t g = 0, ecount = 0;
+    bool ok = true;
+    uint32_t slot_buf = 0;
+    bool waited = false;
+
+    // epilogue of the item with accumulator number `ec`: this warp takes its lane quarter and 32 of the 64 token columns
+    auto epilogue = [&](int item, uint32_t ec) {
+      const int tile = item / a.splits, sp = item - tile * a.splits;
+      const uint32_t acc = ec & 1;
+      bool tok = mbar_wait(smem_u32(tfull + acc), (ec >> 1) & 1, abort_flag);
+      tok = __all_sync(0xffffffffu, tok && !*abort_flag);
+      if (!tok) { ok = false; return; }
       tc_fence_after();
-      const int q = warp & 3, ch = dw >> 2;
-      const int n = n0 + q * 32 + lane;
-      const float bias = (a.bias && blockIdx.z == 0 && n < a.N) ? a.bias[n] : 0.f;
-#pragma unroll 1
-      for (int c = ch * (BN / 64); c < (ch + 1) * (BN / 64); c++) {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
-        tmem_ld_wait();
-        if (n < a.N) {
+      if (!waited) {                      // first global write of this thread: the kernel before this one must be complete
+        pdl_wait();
+        waited = true;
+        if (a.epi == QEPI_SLOTS) slot_buf = (sym_slots_next_seq(a.sym)) & 1u;
+      }
+      const int n = tile * QBM + row;
+      const int t0 = khalf * 32;
+      uint32_t v[32];
+      tmem_ld32(tmem_base + lane_addr + acc * QBN + (uint32_t)t0, v);
+      tmem_ld_wait();
+      const bool live = n < a.N;
+      if (a.epi == QEPI_SWIGLU) {
+        // rows are (gate_i, up_i) pairs in adjacent lanes; the even lane finishes the even tokens, the odd lane the odd ones
+        const float b = (a.bias && live) ? a.bias[n] : 0.f;
+        const bool odd = lane & 1;
 #pragma unroll
-          for (int e = 0; e < 32; e++) {
-            const int t = t0 + c * 32 + e;
-            if (t < a.T) {
-              float* p = a.y + (size_t)t * a.ldy + n;
-              const float val = __uint_as_float(v[e]) + bias;
-              if (a.epi == QEPI_ADD) atomicAdd(p, val);
-              else *p = val;
+        for (int j = 0; j < 32; j += 2) {
+          const float va = __uint_as_float(v[j]) + b, vb = __uint_as_float(v[j + 1]) + b;
+          const float pa = __shfl_xor_sync(0xffffffffu, va, 1), pb = __shfl_xor_sync(0xffffffffu, vb, 1);
+          const float gate = odd ? pb : va, up = odd ? vb : pa;
+          const int t = t0 + j + (odd ? 1 : 0);
+          if (live && t < a.T) a.out_bf16[(size_t)t * a.ldo + (n >> 1)] = __float2bfloat16(silu(gate) * up);
+        }
+      } else if (live) {
+        float b = 0.f;
+        if (a.bias && sp == 0 && (a.epi != QEPI_SLOTS || a.sym.rank == 0)) b = a.bias[n];
+        if (a.epi == QEPI_SLOTS) {
+          const size_t base = a.slot_off + ((((size_t)slot_buf * a.sym.world + a.sym.rank) * a.slot_rows) * a.ldo + n) * 4;
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const int t = t0 + j;
+            if (t < a.T) sym_st_all_f32(a.sym, base + (size_t)t * a.ldo * 4, __uint_as_float(v[j]) + b);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const int t = t0 + j;
+            if (t >= a.T) continue;
+            const float x = __uint_as_float(v[j]) + b;
+            const size_t idx = (size_t)t * a.ldo + n;
+            if (a.epi == QEPI_ADD) {
+              asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(a.out_f32 + idx), "f"(x) : "memory");
+            } else {
+              if (a.out_f32) a.out_f32[idx] = x;
+              if (a.out_bf16) a.out_bf16[idx] = __float2bfloat16(x);
             }
           }
         }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(tempty + acc));
+    };
+
+    int pending = -1;
+    for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x) {
+      const int tile = item / a.splits, sp = item - tile * a.splits;
+      const int sb0 = sp * a.sb_per_split, sb1 = min(nsb_total, sb0 + a.sb_per_split);
+      const int n = tile * QBM + row;
+      [[maybe_unused]] float d6 = 0.f;
+      if constexpr (WT == QW_Q6KR) d6 = (n < a.N) ? __half2float(a.w2[(size_t)n * nsb_total + rot_sb(sb0, sb1, 0)]) : 0.f;
+      for (int sb = sb0; sb < sb1 && ok; sb++, g++) {
+        [[maybe_unused]] float d6_next = 0.f;
+        if constexpr (WT == QW_Q6KR) {      // the next stage's d, fetched a stage ahead so that its latency is hidden
+          if (n < a.N && sb + 1 < sb1) d6_next = __half2float(a.w2[(size_t)n * nsb_total + rot_sb(sb0, sb1, sb + 1 - sb0)]);
+        }
+        const uint32_t rs = g % RS, s = g % kAS;
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(raw_full + rs), (g / RS) & 1, abort_flag));
+        if (!ok) break;
+        const uint8_t* rowp = sR + rs * RAW_BYTES + row * RAWB;
+        [[maybe_unused]] uint4 hdr;
+        [[maybe_unused]] float d4 = 0.f, dmin4 = 0.f;
+        if constexpr (WT == QW_Q4KR) {
+          hdr = *(const uint4*)rowp;
+          const __half2 dd = *reinterpret_cast<const __half2*>(&hdr.x);
+          d4 = __low2float(dd);
+          dmin4 = __high2float(dd);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+          const int kbu = 2 * khalf + u;               // K block of the stage
+          uint32_t r[32];
+          if constexpr (WT == QW_Q4KR) {
+            // sub-blocks 2 kbu and 2 kbu + 1: their 6-bit scale and min, byte-parallel
+            uint32_t S, Mn;
+            if (kbu < 2) {
+              S = hdr.y & 0x3F3F3F3Fu;
+              Mn = hdr.z & 0x3F3F3F3Fu;
+            } else {
+              S = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+              Mn = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+              const int j = 2 * kbu + h, sh = 8 * (j & 3);
+              const float av = d4 * (float)((S >> sh) & 0xFFu);
+              const __nv_bfloat16 ab = __float2bfloat16(av);
+              const __nv_bfloat16 cb = __float2bfloat16(8.f * __bfloat162float(ab) - dmin4 * (float)((Mn >> sh) & 0xFFu));
+              expand_q4k(__halves2bfloat162(ab, ab), __halves2bfloat162(cb, cb), *(const uint4*)(rowp + 16 + j * 16), r + 16 * h);
+            }
+          } else {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+              const int j = 2 * kbu + h;
+              const uint32_t scw = *(const uint16_t*)(rowp + 192 + 2 * j);
+              const __nv_bfloat162 ss = __floats2bfloat162_rn(d6 * (float)(int8_t)(scw & 0xFF), d6 * (float)(int8_t)(scw >> 8));
+              expand_q6k(*(const uint4*)(rowp + j * 16), *(const uint2*)(rowp + 128 + j * 8), bf162_as_u32(ss), r + 16 * h);
+            }
+          }
+          if (u == 0) {      // the first values are in registers: only now does this warp need the operand slot
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(done + s), ((g / kAS) & 1) ^ 1, abort_flag));
+            if (!ok) break;
+            tc_fence_after();
+          } else {           // everything this warp needs from the raw stage has been read
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(raw_empty + rs));
+            tmem_st_wait();  // the first store must have left the registers it reads: they are reused
+          }
+          tmem_st32(tmem_base + lane_addr + 128 + s * 128 + kbu * 32, r);
+        }
+        if (!ok) break;
+        if constexpr (WT == QW_Q6KR) d6 = d6_next;
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(a_full + s));
+        if (pending >= 0) {     // the MMA thread has a stage of the new item queued: finish the old item now
+          epilogue(pending, ecount++);
+          pending = -1;
+        }
+      }
+      pending = item;
     }
+    if (pending >= 0 && ok) epilogue(pending, ecount++);
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, BN);
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
   if (threadIdx.x == 0 && *abort_flag && a.status) atomicExch(a.status, (int)B200_ERR_TIMEOUT_MMA);
-  if (dbg && threadIdx.x == 0) dbg[7] = clock64() - t_start;
-#undef DBG_WAIT
+  if (a.epi == QEPI_SLOTS) {
+    if (threadIdx.x == 0) pdl_wait();       // a CTA without items must not signal before the kernel before this one is done
+    sym_slots_signal(a.sym, gridDim.x);
+  }
 }
 
-template <int WT, int BN, int RS, int AS, int XS>
-static int launch_q(const void* w, const void* w2, const void* x, int ldx, QGemmArgs a, int split_k, cudaStream_t st) {
-  constexpr int RAW = QTraits<WT>::RAW;
-  constexpr size_t smem = 1024 + (size_t)AS * QBM * QBK * 2 + (size_t)XS * BN * QBK * 2 + (((size_t)RS * QBM * RAW + 127) & ~127) +
-                          (2 * RS + 2 * AS + 2 * XS + 1) * 8 + 16;
-  static_assert(AS == 4 || AS == 8, "two expansion warps per operand slot");
+static int q_sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int WT>
+static int launch_q(const void* w, const void* x, int ldx, QGemmArgs a, cudaStream_t st) {
+  constexpr int RAWB = QTraits<WT>::RAWB, RS = QTraits<WT>::RS;
+  constexpr size_t smem = 1024 + kAS * (size_t)kXStage + (size_t)RS * QBM * RAWB + (2 * RS + 3 * kAS + 4) * 8 + 16;
   static_assert(smem <= 227 * 1024, "shared memory budget");
-  auto kern = qgemm_kernel<WT, BN, RS, AS, XS>;
+  auto kern = qgemm_kernel<WT>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  CUtensorMap tx;
-  a.w = (const uint8_t*)w;
-  int rc = make_tmap_2d(&tx, x, 2, (uint64_t)a.T, (uint64_t)a.K, (uint64_t)ldx * 2, BN, QBK, true);
+  const int nsb = a.K / QSB;
+  CUtensorMap tw, tx;
+  // packed rows as bytes: [N][nsb * RAWB], one box = 128 rows of one superblock; rows past N read as zeros (scale 0)
+  int rc = make_tmap_2d(&tw, w, 1, (uint64_t)a.N, (uint64_t)nsb * RAWB, (uint64_t)nsb * RAWB, QBM, RAWB, false);
   if (rc) return rc;
-  a.w2 = (const __half*)w2;
-  const int nsb = a.K / 256;
-  a.sb_per_split = (nsb + split_k - 1) / split_k;
-  dim3 grid((a.T + BN - 1) / BN, (a.N + QBM - 1) / QBM, (nsb + a.sb_per_split - 1) / a.sb_per_split);
-  kern<<<grid, 32 * (3 + 2 * AS), smem, st>>>(tx, a);
-  return (int)cudaGetLastError();
+  rc = make_tmap_2d(&tx, x, 2, (uint64_t)a.T, (uint64_t)a.K, (uint64_t)ldx * 2, QBN, 64, true);
+  if (rc) return rc;
+  const int grid = a.n_items < q_sm_count() ? a.n_items : q_sm_count();
+  return launch_pdl(kern, dim3(grid), dim3(kQThreads), smem, st, tw, tx, a);
 }
 
-// wt: QW_Q4KR / QW_Q6KR; `w` (and `w2`) in the tile-major form: rows padded to a multiple of 128 and
-// stored [N/128][K/256][128][bytes], so the 128 rows a CTA needs for one superblock are one
-// contiguous block (row-major packed weights make that a 144-byte gather per row, which wastes most
-// of every DRAM page).  x: bf16 [T][ldx].  y: fp32 [T][ldy].  split_k > 1 requires epi = QEPI_ADD
-// (y then already holds the residual, or zeros).  split_k = 0 chooses a split that fills the GPU.
-B200_API int b200_qgemm(int wt, const void* w, const void* w2, int N, int K, const void* x, int ldx, int T, float* y,
-                        int ldy, const float* bias, int epi, int split_k, int* status, long long* dbg, cudaStream_t st) {
-  if (K % 256 || (ldx % 8) || T < 1 || N < 1) return B200_ERR_BAD_ARG;
-  QGemmArgs a;
-  a.w = nullptr; a.w2 = nullptr; a.y = y; a.bias = bias; a.ldy = ldy; a.T = T; a.N = N; a.K = K; a.epi = epi; a.sb_per_split = 0;
-  a.status = status;
-  a.dbg = dbg;
-  const int bn = T <= 64 ? 64 : 128;
-  if (split_k == 0) {
-    const int tiles = ((T + bn - 1) / bn) * ((N + QBM - 1) / QBM);
-    split_k = 1;
-    if (epi == QEPI_ADD)
-      while (tiles * split_k < 120 && split_k * 2 <= K / 256 && split_k < 8) split_k *= 2;
+// wt: QW_Q4KR / QW_Q6KR; `w` the row-major packed plane the mat-vec kernels read as well ([N][K / 256][144 or 208
+// bytes]), `w2` the fp16 d plane of Q6_K-R.  x: bf16 [T][ldx].  Any T: tokens are taken 64 at a time.
+//   QEPI_STORE  out_f32 and/or out_bf16 [T][ldo] = result (+ bias)
+//   QEPI_ADD    out_f32 [T][ldo] += result (+ bias); split_k > 1 allowed (0 = choose)
+//   QEPI_SWIGLU rows of W are (gate_0, up_0, gate_1, ...); out_bf16 [T][ldo] gets silu(gate) * up, N / 2 columns
+//   QEPI_SLOTS  tensor parallel: the partial result goes to slot (parity of the sequence number, this rank) of the
+//               fp32 tensor [2][world][slot_rows][ldo] at heap offset slot_off on EVERY rank; the kernel ends by
+//               signalling, nothing waits (the consumer does: rmsnorm with slots).  T <= 64.
+B200_API int b200_qgemm(int wt, const void* w, const void* w2, int N, int K, const void* x, int ldx, int T, float* out_f32,
+                        void* out_bf16, int ldo, const float* bias, int epi, int split_k, const SymTable* sym,
+                        size_t slot_off, int slot_rows, int* status, cudaStream_t st) {
+  if (K % QSB || (ldx % 8) || T < 1 || N < 1 || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return B200_ERR_BAD_ARG;
+  if (wt != QW_Q4KR && wt != QW_Q6KR) return B200_ERR_BAD_ARG;
+  if (wt == QW_Q6KR && !w2) return B200_ERR_BAD_ARG;
+  if (epi == QEPI_SWIGLU ? (!out_bf16 || (N & 1)) : epi == QEPI_ADD ? !out_f32 : epi == QEPI_STORE ? (!out_f32 && !out_bf16)
+      : (epi != QEPI_SLOTS || !sym || T > QBN || T > slot_rows || (slot_off % 16)))
+    return B200_ERR_BAD_ARG;
+  QGemmArgs a = {};
+  a.w2 = (const __half*)w2; a.bias = bias; a.ldo = ldo; a.N = N; a.K = K; a.epi = epi; a.status = status;
+  if (epi == QEPI_SLOTS) { a.sym = *sym; a.slot_off = slot_off; a.slot_rows = slot_rows; }
+  const int nsb = K / QSB, tiles = (N + QBM - 1) / QBM;
+  int splits = 1;
+  if (epi == QEPI_ADD) {
+    if (split_k > 0) splits = split_k;
+    else if (tiles < q_sm_count()) {
+      splits = q_sm_count() / tiles;                 // fill the GPU once ...
+      while (splits > 1 && nsb / splits < 2) splits--;  // ... with at least two stages per item
+    }
+    if (splits > nsb) splits = nsb;
+  } else if (split_k > 1) {
+    return B200_ERR_BAD_ARG;
   }
-  if (split_k > 1 && epi != QEPI_ADD) return B200_ERR_BAD_ARG;
-  if (wt == QW_Q4KR) {
-    if (bn == 64) return launch_q<QW_Q4KR, 64, 3, 4, 12>(w, w2, x, ldx, a, split_k, st);
-    return launch_q<QW_Q4KR, 128, 3, 8, 2>(w, w2, x, ldx, a, split_k, st);
+  a.sb_per_split = (nsb + splits - 1) / splits;
+  a.splits = (nsb + a.sb_per_split - 1) / a.sb_per_split;     // no empty split
+  a.n_items = tiles * a.splits;
+  for (int t0 = 0; t0 < T; t0 += QBN) {
+    a.T = T - t0 < QBN ? T - t0 : QBN;
+    a.out_f32 = out_f32 ? out_f32 + (size_t)t0 * ldo : nullptr;
+    a.out_bf16 = out_bf16 ? (__nv_bfloat16*)out_bf16 + (size_t)t0 * ldo : nullptr;
+    const void* xs = (const __nv_bfloat16*)x + (size_t)t0 * ldx;
+    const int rc = wt == QW_Q4KR ? launch_q<QW_Q4KR>(w, xs, ldx, a, st) : launch_q<QW_Q6KR>(w, xs, ldx, a, st);
+    if (rc) return rc;
   }
-  if (wt == QW_Q6KR) {
-    if (bn == 64) return launch_q<QW_Q6KR, 64, 2, 4, 12>(w, w2, x, ldx, a, split_k, st);
-    return launch_q<QW_Q6KR, 128, 2, 8, 2>(w, w2, x, ldx, a, split_k, st);
-  }
-  return B200_ERR_BAD_ARG;
+  return 0;
 }

@@ -24,6 +24,8 @@ struct Pool {
   std::vector<int32_t> free_list;
   std::vector<int32_t> refcnt;
   std::vector<uint64_t> page_hash;     // chain hash a page is registered under (0 = none)
+  std::vector<int32_t> page_tokens;    // [n_pages][page_size] token ids of a registered page: a hit must match them,
+                                       // so a hash collision or a stale registration can never hand out wrong K/V
   std::unordered_map<uint64_t, int32_t> prefix;  // chain hash -> page
   std::unordered_map<int64_t, Seq> seqs;
   uint64_t hits = 0, lookups = 0;
@@ -42,13 +44,17 @@ uint64_t page_chain_hash(uint64_t prev, const int32_t* toks, int n) {
   return h ? h : 1;
 }
 
+void unregister_page(Pool* p, int32_t pg) {
+  if (p->page_hash[pg]) {
+    auto it = p->prefix.find(p->page_hash[pg]);
+    if (it != p->prefix.end() && it->second == pg) p->prefix.erase(it);
+    p->page_hash[pg] = 0;
+  }
+}
+
 void release_page(Pool* p, int32_t pg) {
   if (--p->refcnt[pg] == 0) {
-    if (p->page_hash[pg]) {
-      auto it = p->prefix.find(p->page_hash[pg]);
-      if (it != p->prefix.end() && it->second == pg) p->prefix.erase(it);
-      p->page_hash[pg] = 0;
-    }
+    unregister_page(p, pg);
     p->free_list.push_back(pg);
   }
 }
@@ -63,6 +69,7 @@ void* b200_kv_create(int32_t n_pages, int32_t page_size) {
   p->page_size = page_size;
   p->refcnt.assign(n_pages, 0);
   p->page_hash.assign(n_pages, 0);
+  p->page_tokens.assign((size_t)n_pages * (size_t)page_size, -1);
   p->free_list.reserve(n_pages);
   for (int32_t i = n_pages - 1; i >= 0; i--) p->free_list.push_back(i);
   return p;
@@ -88,6 +95,9 @@ int64_t b200_kv_seq_begin(void* h, int64_t seq_id, const int32_t* tokens, int64_
     p->lookups++;
     auto it = p->prefix.find(chain);
     if (it == p->prefix.end()) break;
+    if (std::memcmp(&p->page_tokens[(size_t)it->second * p->page_size], tokens + i * p->page_size,
+                    sizeof(int32_t) * (size_t)p->page_size) != 0)
+      break;                            // same hash, different tokens: not a hit
     p->hits++;
     p->refcnt[it->second]++;
     s.pages.push_back(it->second);
@@ -117,12 +127,14 @@ int32_t b200_kv_seq_extend(void* h, int64_t seq_id, int64_t n_new) {
 }
 
 // Register the sequence's full pages in the prefix index (call once their K/V are written).
-// `tokens` are all n_tokens ids of the sequence so far.
+// `tokens` are ALL n_tokens ids the sequence holds so far, from position 0 (for a continued session: the earlier
+// turns too, not just the new one); a list longer than the sequence is cut to the sequence's length.
 void b200_kv_seq_publish(void* h, int64_t seq_id, const int32_t* tokens, int64_t n_tokens) {
   Pool* p = (Pool*)h;
   auto it = p->seqs.find(seq_id);
   if (it == p->seqs.end()) return;
   Seq& s = it->second;
+  if (n_tokens > s.n_tokens) n_tokens = s.n_tokens;
   int64_t full = n_tokens / p->page_size;
   if (full > (int64_t)s.pages.size()) full = (int64_t)s.pages.size();
   uint64_t chain = s.chain.empty() ? 0 : s.chain.back();
@@ -133,6 +145,7 @@ void b200_kv_seq_publish(void* h, int64_t seq_id, const int32_t* tokens, int64_t
     if (!p->prefix.count(chain) && p->page_hash[pg] == 0) {
       p->prefix[chain] = pg;
       p->page_hash[pg] = chain;
+      std::memcpy(&p->page_tokens[(size_t)pg * p->page_size], tokens + i * p->page_size, sizeof(int32_t) * (size_t)p->page_size);
     }
   }
 }
@@ -162,13 +175,25 @@ int32_t b200_kv_seq_pages(void* h, int64_t seq_id, int32_t* out, int32_t cap) {
 // pos[b] = position of the new token, slot[b] = its physical cache slot, ctx[b] = new length,
 // table[b][0..max_pages) = page list (rows are rewritten only when `full_table` is set or the
 // sequence just took a new page).  Returns 0, or -1 unknown sequence / -2 out of pages / -3 sequence
-// longer than max_pages pages (with nothing changed for the failing and later sequences);
-// *table_dirty is set when any table row was written.
+// longer than max_pages pages; on an error NO sequence of the batch has changed (the batch is checked
+// before it is grown).  *table_dirty is set when any table row was written.
 int32_t b200_kv_stage_decode(void* h, const int64_t* seq_ids, int32_t B, int32_t max_pages, int32_t full_table,
                              int32_t* pos, int32_t* slot, int32_t* ctx, int32_t* table, int32_t* table_dirty) {
   Pool* p = (Pool*)h;
   const int64_t ps = p->page_size;
   int32_t dirty = 0;
+  {   // first pass: nothing is changed unless the whole batch can grow
+    int64_t need = 0;
+    for (int32_t b = 0; b < B; b++) {
+      auto it = p->seqs.find(seq_ids[b]);
+      if (it == p->seqs.end()) return -1;
+      const Seq& s = it->second;
+      const int64_t pages_after = (s.n_tokens + 1 + ps - 1) / ps;
+      if (pages_after > max_pages || (int64_t)s.pages.size() > max_pages) return -3;
+      if (pages_after > (int64_t)s.pages.size()) need++;
+    }
+    if (need > (int64_t)p->free_list.size()) return -2;
+  }
   for (int32_t b = 0; b < B; b++) {
     auto it = p->seqs.find(seq_ids[b]);
     if (it == p->seqs.end()) return -1;
@@ -199,20 +224,44 @@ int32_t b200_kv_stage_decode(void* h, const int64_t* seq_ids, int32_t B, int32_t
   return 0;
 }
 
-// Drop the last n tokens (a rejected speculative tail or a cancelled turn).
-int32_t b200_kv_seq_truncate(void* h, int64_t seq_id, int64_t new_len) {
+// Drop the tokens from position new_len on (a rejected speculative tail, a cancelled turn).  Pages that fall
+// away are released.  The page that stays partly filled will be written again from position new_len, so it leaves the
+// prefix index, and if another sequence shares it this sequence gets a page of its own: the call then returns 1 with
+// *cow_src / *cow_dst set, and the caller must copy the page's K/V (every layer) from src to dst before the next
+// write.  Returns 0 when no copy is needed, -1 for a bad sequence or length, -2 when a private page is needed and
+// none is free (nothing has changed in that case).
+int32_t b200_kv_seq_truncate(void* h, int64_t seq_id, int64_t new_len, int32_t* cow_src, int32_t* cow_dst) {
   Pool* p = (Pool*)h;
   auto it = p->seqs.find(seq_id);
   if (it == p->seqs.end() || new_len < 0 || new_len > it->second.n_tokens) return -1;
   Seq& s = it->second;
-  size_t keep = (size_t)((new_len + p->page_size - 1) / p->page_size);
+  const size_t keep = (size_t)((new_len + p->page_size - 1) / p->page_size);
+  const size_t full = (size_t)(new_len / p->page_size);
+  const bool partial = keep > full && keep <= s.pages.size();
+  int32_t rc = 0;
+  if (partial) {
+    const int32_t pg = s.pages[full];
+    if (p->refcnt[pg] > 1) {
+      if (p->free_list.empty()) return -2;
+      const int32_t fresh = p->free_list.back();
+      p->free_list.pop_back();
+      p->refcnt[fresh] = 1;
+      p->refcnt[pg]--;                  // the other holders keep the original (and its registration)
+      s.pages[full] = fresh;
+      if (cow_src) *cow_src = pg;
+      if (cow_dst) *cow_dst = fresh;
+      rc = 1;
+    } else {
+      unregister_page(p, pg);
+    }
+  }
   while (s.pages.size() > keep) {
     release_page(p, s.pages.back());
     s.pages.pop_back();
   }
-  if (s.chain.size() > (size_t)(new_len / p->page_size)) s.chain.resize((size_t)(new_len / p->page_size));
+  if (s.chain.size() > full) s.chain.resize(full);
   s.n_tokens = new_len;
-  return 0;
+  return rc;
 }
 void b200_kv_seq_end(void* h, int64_t seq_id) {
   Pool* p = (Pool*)h;

@@ -2,9 +2,11 @@
 
 The engine owns the device weights, the paged fp16 KV cache and the activation workspaces, and
 exposes two operations over packed token batches: ``forward_tokens`` (prefill chunks, many tokens
-per sequence) and ``decode`` (one token per sequence, replayed from a CUDA graph).  Small decode
-batches (<= 8 tokens) take the quantized mat-vec kernels, which read the packed weights once;
-larger batches and prefill take the tcgen05 GEMM.
+per sequence) and ``decode`` (one token per sequence, replayed from a CUDA graph).  The weights stay
+in their packed GGUF block formats in device memory, once: up to 4 decode tokens take the quantized
+mat-vec kernels (``dp4a``), up to 64 tokens the tcgen05 GEMM that expands the blocks inside its
+pipeline, and longer chunks (prefill) expand one matrix at a time into a scratch buffer for the
+bf16 tcgen05 GEMM.
 
 The serve-side contract this implements is the reference's model-server description: GGUF load,
 KV and prefix caches, continuous batching (docs/muse/muse-glimmer.md:110-126).
@@ -25,6 +27,7 @@ from .qweight import QWeight, RawTensor, WeightSource
 
 PAGE = 16
 MATVEC_MAX_TOKENS = 8
+QGEMM_MAX_TOKENS = 64      # token tile of the fused-dequant GEMM; also the row count of the tensor-parallel slots
 
 
 class KVPool:
@@ -41,7 +44,7 @@ class KVPool:
                    "b200_kv_seq_begin": ([vp, i64, P32, i64], i64), "b200_kv_seq_extend": ([vp, i64, i64], i32),
                    "b200_kv_seq_publish": ([vp, i64, P32, i64], None), "b200_kv_seq_len": ([vp, i64], i64),
                    "b200_kv_seq_n_pages": ([vp, i64], i32), "b200_kv_seq_pages": ([vp, i64, P32, i32], i32),
-                   "b200_kv_seq_truncate": ([vp, i64, i64], i32), "b200_kv_seq_end": ([vp, i64], None),
+                   "b200_kv_seq_truncate": ([vp, i64, i64, P32, P32], i32), "b200_kv_seq_end": ([vp, i64], None),
                    "b200_kv_stage_decode": ([vp, vp, i32, i32, i32, vp, vp, vp, vp, vp], i32)}
             for n, (a, r) in sig.items():
                 f = getattr(L, n)
@@ -80,6 +83,9 @@ class KVPool:
     def length(self, seq_id: int) -> int:
         return self.L.b200_kv_seq_len(self.h, seq_id)
 
+    def n_pages_of(self, seq_id: int) -> int:
+        return self.L.b200_kv_seq_n_pages(self.h, seq_id)
+
     def pages(self, seq_id: int) -> list[int]:
         n = self.L.b200_kv_seq_n_pages(self.h, seq_id)
         if n < 0:
@@ -104,8 +110,16 @@ class KVPool:
         return bool(dirty.value)
 
     def truncate(self, seq_id: int, new_len: int):
-        if self.L.b200_kv_seq_truncate(self.h, seq_id, new_len) != 0:
+        """Drop the tokens from ``new_len`` on.  Returns ``None``, or ``(src_page, dst_page)`` when the partly kept page
+        was shared with another sequence and this one was given a page of its own: the caller must copy that page's
+        K/V before writing to it."""
+        src, dst = ctypes.c_int32(-1), ctypes.c_int32(-1)
+        r = self.L.b200_kv_seq_truncate(self.h, seq_id, new_len, ctypes.byref(src), ctypes.byref(dst))
+        if r == -2:
+            raise MemoryError("KV cache is out of pages")
+        if r < 0:
             raise ValueError("bad truncate")
+        return (src.value, dst.value) if r == 1 else None
 
     def end(self, seq_id: int):
         self.L.b200_kv_seq_end(self.h, seq_id)
@@ -156,6 +170,10 @@ class LlamaEngine:
         self.cfg, self.device = cfg, torch.device(device)
         self.rank, self.world, self.comm = tp_rank, tp_world, comm
         self._use_fence = os.environ.get("B200_TP_FENCE", "0") == "1"
+        # Tensor-parallel decode: "slots" = one-shot all-reduce through per-rank slots, summed by the next norm (no
+        # barrier, no handshake); "allreduce" = the older form (multimem.red into every replica + barrier), kept as a
+        # measurement aid and for weight types the fused-dequant GEMM does not take.
+        self.tp_mode = os.environ.get("B200_TP_MODE", "slots")
         if cfg.n_kv_heads % tp_world or cfg.ffn % tp_world:
             raise ValueError("tensor-parallel degree must divide the KV heads and the FFN width")
         self.Hq, self.Hkv, self.hd = cfg.n_heads // tp_world, cfg.n_kv_heads // tp_world, cfg.head_dim
@@ -196,7 +214,7 @@ class LlamaEngine:
         if self.emb_type is None:
             # Q4_K / MXFP4 tables are not gathered directly; keep them as bf16.
             x = emb.to_float().to(torch.bfloat16).contiguous()
-            self.emb = QWeight(ops.WT_BF16, x.shape[0], x.shape[1], x, None, emb.type, shadow=x)
+            self.emb = QWeight(ops.WT_BF16, x.shape[0], x.shape[1], x, None, emb.type)
             self.emb_type = ops.EMB_BF16
         self.layers: list[_Layer] = []
         for i in range(cfg.n_layers):
@@ -225,9 +243,13 @@ class LlamaEngine:
         torch.cuda.synchronize(dev)
 
     def _load_ffn(self, src: WeightSource, p: str, layer: int):
+        """Gate and up projections as ONE matrix with interleaved rows (gate_0, up_0, gate_1, ...): every kernel that
+        fuses SwiGLU pairs adjacent rows, so a single packed copy serves the mat-vec, the fused-dequant GEMM and the
+        prefill GEMM."""
         g = self._shard_rows(src.get(p + "ffn_gate.weight"))
         u = self._shard_rows(src.get(p + "ffn_up.weight"))
-        return QWeight.from_raw(RawTensor.cat_rows([g, u])), QWeight.from_raw(self._shard_cols(src.get(p + "ffn_down.weight")))
+        return (QWeight.from_raw(RawTensor.interleave_rows(g, u)),
+                QWeight.from_raw(self._shard_cols(src.get(p + "ffn_down.weight"))))
 
     def weight_bytes(self) -> int:
         n = self.wout.nbytes()
@@ -283,20 +305,38 @@ class LlamaEngine:
         self.rope_tab = ops.rope_table(self.max_pages * PAGE, self.hd, self.cfg.rope_theta, dev)
         wmax = max(max(l.wqkv.N * l.wqkv.K, l.wo.N * l.wo.K, *((l.wgu.N * l.wgu.K, l.wdown.N * l.wdown.K) if l.wgu is not None else ()))
                    for l in self.layers)
-        self._wscratch_elems = wmax
+        self._wscratch_elems = max(wmax, self.wout.N * self.wout.K if self.wout.quantized else 0)
         self._wscratch = None
-        self.use_shadow = True
+        if self.world > 1:
+            # one-shot all-reduce slots [parity][rank][row][d] and arg-max merge slots [parity][rank][row][2]
+            self.slot_rows = QGEMM_MAX_TOKENS
+            self.slots, self.slots_off = self.comm.alloc_tensor((2, self.world, self.slot_rows, d), torch.float32)
+            row_par = [w for l in self.layers for w in (l.wo, l.wdown) if w is not None]
+            self.slots_small = self.tp_mode == "slots"
+            self.slots_dense = self.slots_small and all(self._qg(w) for w in row_par)
+        else:
+            self.slots_small = self.slots_dense = False
+        self._slots_pending = False
+
+    @staticmethod
+    def _qg(w: QWeight) -> bool:
+        """Whether the fused-dequant GEMM takes this weight."""
+        return w is not None and w.wt in (ops.WT_Q4KR, ops.WT_Q6KR) and w.K % 256 == 0
 
     def _dense(self, w: QWeight) -> torch.Tensor:
-        """bf16 [N][K] form of a weight for the tensor-core GEMM."""
+        """bf16 [N][K] form of a weight for the bf16 tensor-core GEMM (prefill): the matrix itself when it is stored
+        in bf16, else its expansion into the one scratch buffer all quantized matrices share.  The expansion kernel
+        and the GEMM run in stream order, so the buffer is free again when the next matrix needs it."""
         if w.wt == ops.WT_BF16:
             return w.main
-        if self.use_shadow:
-            return w.ensure_shadow()
         if self._wscratch is None:
             self._wscratch = torch.empty(self._wscratch_elems, dtype=torch.bfloat16, device=self.device)
         out = self._wscratch[: w.N * w.K].view(w.N, w.K)
         return w.dequant_into(out)
+
+    @property
+    def _slot_arg(self):
+        return (self.comm.heap.table, self.slots_off, self.slot_rows)
 
     # ------------------------------------------------------------------ building blocks
     def _splits(self, B: int, ctx_pages: int) -> int:
@@ -331,10 +371,13 @@ class LlamaEngine:
         qd = self.Hq * self.hd
         style = 0 if cfg.rope_style == "pairs" else 1
         n = 0
+        slots = self.slots_small
+        table = self.comm.heap.table if self.world > 1 else None
         for li, L in enumerate(self.layers):
             q8 = L.wqkv.quantized
             ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, xq=self.xq if q8 else None, xd=self.xd, xs16=self.xs,
-                        hf=None if q8 else self.xf, signal_sym=self._sig)
+                        hf=None if q8 else self.xf, signal_sym=None if slots else self._sig,
+                        slots=self._slot_arg if slots and li > 0 else None)
             ops.matvec(L.wqkv.wt, L.wqkv.main, L.wqkv.plane2, L.wqkv.N, L.wqkv.K, nb, xq=self.xq, xd=self.xd,
                        xs16=self.xs, xf=self.xf, epi=ops.EPI_STORE, bias=L.bqkv, y=self.qkv, ldy=self.qkv_dim)
             ops.rope_kv(self.qkv[:nb], self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv,
@@ -347,11 +390,16 @@ class LlamaEngine:
             if self.world == 1:
                 ops.matvec(L.wo.wt, L.wo.main, L.wo.plane2, L.wo.N, L.wo.K, nb, xq=self.xq, xd=self.xd, xs16=self.xs,
                            xf=self.xf, epi=ops.EPI_RESID, bias=L.bo, resid=x, y=x, ldy=self.d)
+            elif slots:
+                ops.matvec(L.wo.wt, L.wo.main, L.wo.plane2, L.wo.N, L.wo.K, nb, xq=self.xq, xd=self.xd, xs16=self.xs,
+                           xf=self.xf, epi=ops.EPI_SLOTS, bias=L.bo, ldy=self.d, sym=table, sym_off=self.slots_off,
+                           slot_rows=self.slot_rows)
             else:
                 self.comm.matvec_allreduce(L.wo, nb, self.xq, self.xd, self.xs, self.xf, x, self.d, bias=L.bo, wait_ready=not self._use_fence)
             g8 = L.wgu.quantized
             ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, xq=self.xq if g8 else None, xd=self.xd, xs16=self.xs,
-                        hf=None if g8 else self.xf, signal_sym=self._sig)
+                        hf=None if g8 else self.xf, signal_sym=None if slots else self._sig,
+                        slots=self._slot_arg if slots else None)
             d8 = L.wdown.quantized and self.F % 32 == 0
             ops.matvec(L.wgu.wt, L.wgu.main, L.wgu.plane2, self.F, L.wgu.K, nb, xq=self.xq, xd=self.xd, xs16=self.xs,
                        xf=self.xf, epi=ops.EPI_SWIGLU_Q8 if d8 else ops.EPI_SWIGLU_F32, y=self.gu, ldy=self.F,
@@ -362,9 +410,14 @@ class LlamaEngine:
             if self.world == 1:
                 ops.matvec(L.wdown.wt, L.wdown.main, L.wdown.plane2, L.wdown.N, L.wdown.K, nb, xq=self.fq, xd=self.fd,
                            xs16=self.fs, xf=self.gu, epi=ops.EPI_RESID, resid=x, y=x, ldy=self.d)
+            elif slots:
+                ops.matvec(L.wdown.wt, L.wdown.main, L.wdown.plane2, L.wdown.N, L.wdown.K, nb, xq=self.fq, xd=self.fd,
+                           xs16=self.fs, xf=self.gu, epi=ops.EPI_SLOTS, ldy=self.d, sym=table, sym_off=self.slots_off,
+                           slot_rows=self.slot_rows)
             else:
                 self.comm.matvec_allreduce(L.wdown, nb, self.fq, self.fd, self.fs, self.gu, x, self.d, wait_ready=not self._use_fence)
             n += 8
+        self._slots_pending = slots          # the last down projection's sum is taken by the final norm
         return n
 
     def _gemm(self, a_bf16, w: QWeight, M, out_f32=None, out_bf16=None, bias=None, resid_f32=None, ldc=None, accumulate=False):
@@ -379,7 +432,9 @@ class LlamaEngine:
         return self.world > 1 and not decode and self.seq_shard and T >= 128 * self.world
 
     def _layers_dense(self, T: int, decode: bool, n_seqs: int, max_q: int, max_ctx_pages: int):
-        """Any token count: tcgen05 GEMM path (prefill chunks and large decode batches)."""
+        """Any token count: tensor-core path.  Up to 64 tokens (decode batches, short chunks) the projections whose
+        weights are Q4_K / Q6_K run on the fused-dequant GEMM, which streams the packed blocks; beyond that (prefill)
+        every matrix is expanded into the shared scratch buffer and multiplied by the bf16 GEMM."""
         if self._seq_sharded(T, decode):
             return self._layers_seq_sharded(T, n_seqs, max_q)
         cfg, x = self.cfg, self.x[:T]
@@ -392,10 +447,18 @@ class LlamaEngine:
         gu = self.gu[:T]
         S = self._splits(n_seqs, max_ctx_pages) if decode else 1
         n = 0
+        fused = T <= QGEMM_MAX_TOKENS      # the fused-dequant GEMM's token tile
+        slots = self.slots_dense and fused
+        table = self.comm.heap.table if self.world > 1 else None
+        sig = None if slots else self._sig
         split_qkv = T <= 64          # one row tile: let the QKV GEMM split K (the norm clears its output, the splits add)
         for li, L in enumerate(self.layers):
-            ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, hb=hb_d, signal_sym=self._sig, zero=qkv if split_qkv else None)
-            self._gemm(hb_d, L.wqkv, T, out_f32=qkv, bias=L.bqkv, accumulate=split_qkv)
+            ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, hb=hb_d, signal_sym=sig, zero=qkv if split_qkv else None,
+                        slots=self._slot_arg if slots and li > 0 else None)
+            if fused and self._qg(L.wqkv):
+                ops.qgemm(L.wqkv, hb_d, T, out_f32=qkv, bias=L.bqkv, epi=ops.QEPI_ADD, status=self.status)
+            else:
+                self._gemm(hb_d, L.wqkv, T, out_f32=qkv, bias=L.bqkv, accumulate=split_qkv)
             if decode:
                 ops.rope_kv(qkv, self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv, self.hd,
                             PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd), table=self.rope_tab)
@@ -413,13 +476,30 @@ class LlamaEngine:
                     ops.attn_prefill(self.q16, self.kc[li], self.vc[li], self.page_table, self.max_pages, self.q_start,
                                      self.q_len, self.seq_lens, n_seqs, max_q, self.Hq, self.Hkv, self.hd, window=L.window,
                                      sinks=L.sinks, out_bf16=hb_q)
-            if self.world == 1:
-                self._gemm(hb_q, L.wo, T, out_f32=x, bias=L.bo, resid_f32=x, ldc=self.d)
-            else:
-                self.comm.gemm_allreduce(hb_q, self._dense(L.wo), T, x, bias=L.bo, status=self.status, wait_ready=not self._use_fence)
-            ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, hb=hb_d, hf=self._ffn_hf(T), signal_sym=self._sig)
-            n += 6 + self._ffn_dense(li, L, T, x, hb_d, hb_f, gu)
+            self._row_parallel(hb_q, L.wo, T, x, L.bo, fused, slots, table)
+            ops.rmsnorm(x, L.ffn_norm, cfg.norm_eps, hb=hb_d, hf=self._ffn_hf(T), signal_sym=sig,
+                        slots=self._slot_arg if slots else None)
+            n += 6 + self._ffn_dense(li, L, T, x, hb_d, hb_f, gu, fused, slots, table)
+        if slots and not decode:
+            # a short prefill chunk: the caller picks rows out of x, so fold the last all-reduce into it now
+            ops.rmsnorm(x, None, cfg.norm_eps, slots=self._slot_arg)
+            n += 1
+        else:
+            self._slots_pending = slots      # decode: the final norm takes the last sum
         return n
+
+    def _row_parallel(self, a_bf16, w: QWeight, T: int, x, bias, fused: bool, slots: bool, table):
+        """x += a W^T for a row-parallel projection (attention output, FFN down), summed over the tensor-parallel ranks."""
+        if slots:
+            ops.qgemm(w, a_bf16, T, ldo=self.d, bias=bias, epi=ops.QEPI_SLOTS, sym=table, slot_off=self.slots_off,
+                      slot_rows=self.slot_rows, status=self.status)
+        elif self.world == 1:
+            if fused and self._qg(w):
+                ops.qgemm(w, a_bf16, T, out_f32=x, ldo=self.d, bias=bias, epi=ops.QEPI_ADD, status=self.status)
+            else:
+                self._gemm(a_bf16, w, T, out_f32=x, bias=bias, resid_f32=x, ldc=self.d)
+        else:
+            self.comm.gemm_allreduce(a_bf16, self._dense(w), T, x, bias=bias, status=self.status, wait_ready=not self._use_fence)
 
     def _layers_seq_sharded(self, T: int, n_seqs: int, max_q: int):
         """Prefill with the residual stream sharded by rows over the tensor-parallel ranks.  Per layer:
@@ -465,16 +545,10 @@ class LlamaEngine:
                                  sinks=L.sinks, out_bf16=hb_q)
             gemm_scatter(hb_q, self._dense(L.wo), bias=L.bo)
             norm_gather(L.ffn_norm)
-            if self.use_shadow:
-                ops.gemm_bf16(hbf, L.wgu.ensure_pair_shadow(), T, 2 * self.F, L.wgu.K, lda=self.d, ldb=L.wgu.K, out_bf16=hb_f,
-                              ldc=self.F, act=ops.ACT_SWIGLU_PAIR, status=self.status, sym=table, ag_rows_per_rank=Tr,
-                              ag_epoch=self._ag_epoch)
-                n += 8
-            else:
-                ops.gemm_bf16(hbf, self._dense(L.wgu), T, L.wgu.N, L.wgu.K, lda=self.d, ldb=L.wgu.K, out_f32=self.gu[:T],
-                              ldc=L.wgu.N, status=self.status, sym=table, ag_rows_per_rank=Tr, ag_epoch=self._ag_epoch)
-                ops.swiglu(self.gu[:T], self.F, ob=hb_f)
-                n += 9
+            ops.gemm_bf16(hbf, self._dense(L.wgu), T, 2 * self.F, L.wgu.K, lda=self.d, ldb=L.wgu.K, out_bf16=hb_f,
+                          ldc=self.F, act=ops.ACT_SWIGLU_PAIR, status=self.status, sym=table, ag_rows_per_rank=Tr,
+                          ag_epoch=self._ag_epoch)
+            n += 8
             gemm_scatter(hb_f, self._dense(L.wdown))
         # every rank's rows back into every replica (whole blocks of Tr rows; the tensor has world spare rows)
         self.comm.heap.all_gather(self.x_off + self.rank * Tr * self.d * 4, self.x_off, Tr * self.d * 4)
@@ -484,34 +558,36 @@ class LlamaEngine:
         """fp32 copy of the normalised hidden state, for feed-forward blocks that want one."""
         return None
 
-    def _ffn_dense(self, li: int, L: _Layer, T: int, x, hb_d, hb_f, gu) -> int:
-        """Feed-forward block on ``hb_d`` (normalised hidden, bf16); adds its output into ``x``."""
-        if self.use_shadow:       # gate/up projection with SwiGLU in the epilogue: no fp32 [T][2F] round trip
-            ops.gemm_bf16(hb_d, L.wgu.ensure_pair_shadow(), T, 2 * self.F, L.wgu.K, lda=hb_d.stride(0), ldb=L.wgu.K, out_bf16=hb_f,
+    def _ffn_dense(self, li: int, L: _Layer, T: int, x, hb_d, hb_f, gu, fused: bool = False, slots: bool = False, table=None) -> int:
+        """Feed-forward block on ``hb_d`` (normalised hidden, bf16); adds its output into ``x``.  The gate/up matrix has
+        interleaved rows, so SwiGLU runs in the epilogue of its GEMM: no fp32 [T][2F] round trip."""
+        if fused and self._qg(L.wgu):
+            ops.qgemm(L.wgu, hb_d, T, out_bf16=hb_f, ldo=self.F, epi=ops.QEPI_SWIGLU, status=self.status)
+        else:
+            ops.gemm_bf16(hb_d, self._dense(L.wgu), T, 2 * self.F, L.wgu.K, lda=hb_d.stride(0), ldb=L.wgu.K, out_bf16=hb_f,
                           ldc=self.F, act=ops.ACT_SWIGLU_PAIR, status=self.status)
-        else:
-            self._gemm(hb_d, L.wgu, T, out_f32=gu)
-            ops.swiglu(gu, self.F, ob=hb_f)
-        if self.world == 1:
-            self._gemm(hb_f, L.wdown, T, out_f32=x, resid_f32=x, ldc=self.d)
-        else:
-            self.comm.gemm_allreduce(hb_f, self._dense(L.wdown), T, x, status=self.status, wait_ready=not self._use_fence)
-        return 2 if self.use_shadow else 3
+        self._row_parallel(hb_f, L.wdown, T, x, None, fused, slots, table)
+        return 2
 
     def _head(self, rows: torch.Tensor, nb: int, greedy: bool = True):
         """Final norm + LM head on ``nb`` rows of fp32 hidden state -> logits (and arg-max ids)."""
         cfg = self.cfg
         n = 2
+        slots = self._slot_arg if self._slots_pending else None     # tensor parallel: the last layer's sum is still in the slots
+        self._slots_pending = False
         if nb <= MATVEC_MAX_TOKENS:
             q8 = self.wout.quantized
             ops.rmsnorm(rows, self.out_norm, cfg.norm_eps, xq=self.xq if q8 else None, xd=self.xd, xs16=self.xs,
-                        hf=None if q8 else self.xf)
+                        hf=None if q8 else self.xf, slots=slots)
             ops.matvec(self.wout.wt, self.wout.main, self.wout.plane2, self.wout.N, self.wout.K, nb, xq=self.xq,
                        xd=self.xd, xs16=self.xs, xf=self.xf, epi=ops.EPI_STORE, y=self.logits, ldy=self.V_local)
         else:
             hb = self.hb.view(-1)[: nb * self.d].view(nb, self.d)
-            ops.rmsnorm(rows, self.out_norm, cfg.norm_eps, hb=hb)
-            self._gemm(hb, self.wout, nb, out_f32=self.logits)
+            ops.rmsnorm(rows, self.out_norm, cfg.norm_eps, hb=hb, slots=slots)
+            if nb <= QGEMM_MAX_TOKENS and self._qg(self.wout):
+                ops.qgemm(self.wout, hb, nb, out_f32=self.logits, ldo=self.V_local, epi=ops.QEPI_STORE, status=self.status)
+            else:
+                self._gemm(hb, self.wout, nb, out_f32=self.logits)
         if greedy:
             ops.argmax(self.logits[:nb], self.out_ids, self.out_val,
                        vocab_offset=self.rank * self.V_local if self.vocab_sharded else 0, scratch=self.argmax_scratch)
@@ -528,12 +604,24 @@ class LlamaEngine:
         """Extend the sequences' page lists and build ids/pos/slot/page-table for the new tokens."""
         ids, pos, slot, q_start, q_len, ctx = [], [], [], [], [], []
         table = torch.zeros((len(seq_ids), self.max_pages), dtype=torch.int32)
+        # Check the whole batch before any sequence grows: a refused batch must leave the page lists as they were.
+        if len(seq_ids) > self.max_batch or sum(len(t) for t in new_tokens) > self.max_tokens:
+            raise ValueError("batch exceeds the engine's workspace")
+        need = 0
+        for sid, toks in zip(seq_ids, new_tokens):
+            p0 = self.pool.length(sid)
+            if p0 < 0:
+                raise KeyError(f"unknown sequence {sid}")
+            after = (p0 + len(toks) + PAGE - 1) // PAGE
+            if after > self.max_pages:
+                raise ValueError("sequence exceeds the engine's max context")
+            need += max(0, after - self.pool.n_pages_of(sid))
+        if need > self.pool.free_pages:
+            raise MemoryError("KV cache is out of pages")
         for b, (sid, toks) in enumerate(zip(seq_ids, new_tokens)):
             p0 = self.pool.length(sid)
             self.pool.extend(sid, len(toks))
             pages = self.pool.pages(sid)
-            if len(pages) > self.max_pages:
-                raise ValueError("sequence exceeds the engine's max context")
             table[b, : len(pages)] = torch.tensor(pages, dtype=torch.int32)
             q_start.append(len(ids))
             q_len.append(len(toks))
@@ -565,6 +653,19 @@ class LlamaEngine:
 
     def end(self, seq_id: int):
         self.pool.end(seq_id)
+
+    def truncate(self, seq_id: int, new_len: int):
+        """Drop the sequence's tokens from position ``new_len`` on (a cancelled turn, a rejected speculative tail).
+        If the page that stays partly filled was shared through the prefix cache, the sequence gets a private copy of
+        it, so writing the next tokens cannot touch another sequence's K/V."""
+        cow = self.pool.truncate(seq_id, new_len)
+        if cow is not None:
+            src, dst = cow
+            for k, v in zip(self.kc, self.vc):
+                k[dst].copy_(k[src])
+                v[dst].copy_(v[src])
+        if getattr(self, "_stg", None) is not None:
+            self._stg["last_batch"] = None        # page lists changed: the decode fast path must resend its rows
 
     @torch.no_grad()
     def forward_tokens(self, seq_ids: list[int], new_tokens: list[list[int]], greedy: bool = True):
@@ -615,7 +716,7 @@ class LlamaEngine:
         if advance:   # the warm-up run must not move the real state: save and restore it
             saved = [t.clone() for t in (self.ids, self.pos, self.slot, self.seq_lens, self._step)]
         with torch.cuda.stream(s):
-            body()  # warm-up outside capture: sets kernel attributes, builds shadows
+            body()  # warm-up outside capture: sets kernel attributes, allocates the scratch
         if advance:
             torch.cuda.synchronize()
             for t, v in zip((self.ids, self.pos, self.slot, self.seq_lens, self._step), saved):
@@ -691,6 +792,8 @@ class LlamaEngine:
         ctx = staged[5]
         table = staged[6]
         for b, sid in enumerate(seq_ids):        # pages for every later step up front
+            if (self.pool.length(sid) + n_steps - 1 + PAGE - 1) // PAGE > self.max_pages:
+                raise ValueError("sequence exceeds the engine's max context")
             self.pool.extend(sid, n_steps - 1)
             pages = self.pool.pages(sid)
             if len(pages) > self.max_pages:

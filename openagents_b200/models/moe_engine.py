@@ -114,7 +114,7 @@ class MoEEngine(LlamaEngine):
         if self.ep_world > 1:
             self.ep.heap.barrier(ch=2)
 
-    def _ffn_dense(self, li: int, L: _Layer, T: int, x, hb_d, hb_f, gu) -> int:
+    def _ffn_dense(self, li: int, L: _Layer, T: int, x, hb_d, hb_f, gu, fused: bool = False, slots: bool = False, table=None) -> int:
         ex, heap = self.experts[li], self.ep.heap
         par = li & 1
         d, f = self.d, self.cfg.ffn

@@ -42,6 +42,16 @@ class RawTensor:
         return tc.dequantize(self.data, self.type, self.shape)
 
     @staticmethod
+    def interleave_rows(a: "RawTensor", b: "RawTensor") -> "RawTensor":
+        """Rows a_0, b_0, a_1, b_1, ... of two equally shaped matrices (exact for every block format: a row is a
+        whole number of blocks)."""
+        if a.type != b.type or a.shape != b.shape:
+            raise ValueError("row interleaving needs equal types and shapes")
+        n = a.shape[0]
+        d = torch.stack((a.data.reshape(n, -1), b.data.reshape(n, -1)), dim=1).reshape(-1)
+        return RawTensor(a.type, (2 * n,) + tuple(a.shape[1:]), d)
+
+    @staticmethod
     def cat_rows(parts: list["RawTensor"]) -> "RawTensor":
         t = parts[0].type
         if any(p.type != t or p.shape[1:] != parts[0].shape[1:] for p in parts):
@@ -123,9 +133,6 @@ class QWeight:
     main: torch.Tensor
     plane2: torch.Tensor | None
     src_type: GgmlType
-    shadow: torch.Tensor | None = None   # bf16 [N][K] copy for the dense tensor-core path
-    tiled: torch.Tensor | None = None    # tile-major packed copy for the fused-dequant GEMM
-    tiled2: torch.Tensor | None = None
 
     @staticmethod
     def from_raw(r: RawTensor) -> "QWeight":
@@ -145,7 +152,7 @@ class QWeight:
             q, e = tc.repack_mxfp4(r.data)
             return QWeight(ops.WT_MXFP4R, N, K, q, e, r.type)
         x = tc.dequantize(r.data, r.type, (N, K)).to(torch.bfloat16).contiguous()
-        return QWeight(ops.WT_BF16, N, K, x, None, r.type, shadow=x)
+        return QWeight(ops.WT_BF16, N, K, x, None, r.type)
 
     @property
     def quantized(self) -> bool:
@@ -153,60 +160,6 @@ class QWeight:
 
     def nbytes(self) -> int:
         return self.main.numel() * self.main.element_size() + (0 if self.plane2 is None else self.plane2.numel() * self.plane2.element_size())
-
-    def ensure_shadow(self) -> torch.Tensor:
-        if self.shadow is None:
-            out = torch.empty((self.N, self.K), dtype=torch.bfloat16, device=self.main.device)
-            ops.dequant_bf16(self.wt, self.main, self.plane2, out, self.N, self.K)
-            self.shadow = out
-        return self.shadow
-
-    def ensure_pair_shadow(self) -> torch.Tensor:
-        """bf16 [N][K] copy of a stacked (gate rows, then up rows) matrix with the rows interleaved
-        (gate_0, up_0, gate_1, ...), the order the GEMM's SwiGLU epilogue pairs columns in.  Replaces the
-        plain shadow: the dense path needs only this one."""
-        if getattr(self, "pair_shadow", None) is None:
-            sh = self.ensure_shadow()
-            half = self.N // 2
-            self.pair_shadow = sh.view(2, half, self.K).transpose(0, 1).reshape(self.N, self.K).contiguous()
-            if self.wt != ops.WT_BF16:
-                self.shadow = None
-        return self.pair_shadow
-
-    def ensure_tiled(self):
-        """Tile-major form for the fused-dequant GEMM: [N/128][K/256][128 rows][bytes], rows
-        zero-padded to a multiple of 128, with the per-sub-block scale arithmetic done once here:
-
-        * Q4_K: 160 bytes per row and superblock = 8 x (a, c) bf16 pairs + 128 quant bytes, where a
-          32-element sub-block dequantizes as ``a * (16 + q) + c`` (c = -16 a - min).
-        * Q6_K: 224 bytes = 16 bf16 scales (d * sc, one per 16 elements) + 128 nibble bytes + 64
-          bytes of high bit pairs; values are ``s * (q - 32)``.
-        """
-        if self.tiled is None:
-            nsb = self.K // 256
-            Np = (self.N + 127) // 128 * 128
-            if self.wt == ops.WT_Q4KR:
-                m = self.main.view(self.N * nsb, 144)
-                d = m[:, 0:2].contiguous().view(torch.float16).float()
-                dmin = m[:, 2:4].contiguous().view(torch.float16).float()
-                ls, lm = tc._unpack_scale_min(m[:, 4:16])
-                a_bf = (d * ls.float()).to(torch.bfloat16)
-                c_bf = (-16.0 * a_bf.float() - dmin * lm.float()).to(torch.bfloat16)
-                head = torch.stack((a_bf, c_bf), dim=-1).reshape(self.N * nsb, 16).view(torch.uint8)
-                rows = torch.cat((head, m[:, 16:]), dim=1)                      # [N*nsb, 160]
-            elif self.wt == ops.WT_Q6KR:
-                m = self.main.view(self.N * nsb, 208)
-                sc = m[:, 192:208].contiguous().view(torch.int8).float()
-                s_bf = (self.plane2.view(self.N * nsb, 1).float() * sc).to(torch.bfloat16)
-                rows = torch.cat((s_bf.view(torch.uint8), m[:, :192]), dim=1)   # [N*nsb, 224]
-            else:
-                raise ValueError("only Q4_K and Q6_K weights have a tile-major form")
-            raw = rows.shape[1]
-            rows = rows.view(self.N, nsb, raw)
-            if Np != self.N:
-                rows = torch.cat((rows, torch.zeros((Np - self.N, nsb, raw), dtype=rows.dtype, device=rows.device)))
-            self.tiled = rows.view(Np // 128, 128, nsb, raw).permute(0, 2, 1, 3).contiguous()
-        return self.tiled, None
 
     def dequant_into(self, out: torch.Tensor) -> torch.Tensor:
         if self.wt == ops.WT_BF16:

@@ -121,7 +121,7 @@ class SymmHeap:
         """(last error code, number of timed-out waits) from the local control block."""
         ctl = self.buf[:CONTROL_BYTES].view(torch.int32)
         torch.cuda.synchronize(self.device)
-        return int(ctl[48].item()), int(ctl[49].item())
+        return int(ctl[96].item()), int(ctl[97].item())   # after flag[32], epoch[32], ticket[32]
 
     def _stream(self):
         return torch.cuda.current_stream(self.device).cuda_stream

@@ -43,18 +43,12 @@ class TPComm:
                       sym_mode=ops.SYM_ALLREDUCE, sym=self.heap.table, sym_off=self.offset_of(x), wait_ready=wait_ready)
 
     def argmax_merge(self, out_ids: torch.Tensor, out_val: torch.Tensor, nb: int):
-        """Global arg-max over vocabulary shards: every rank publishes (value, id) per row to every
-        rank, then each picks the best (lowest id on ties) from identical data."""
+        """Global arg-max over vocabulary shards in one kernel: every rank stores its per-row (value, id) into its slot
+        on every rank, raises its flag, waits for the others' and picks the best pair (lowest id on ties) from identical
+        data."""
         if self._merge is None:
-            self._merge, self._merge_off = self.heap.alloc_tensor((self.world, 2, 1024), torch.float32)
-            self._stage, self._stage_off = self.heap.alloc_tensor((2, 1024), torch.float32)
-        if nb > 1024:
+            self._merge_rows = 1024
+            self._merge, self._merge_off = self.heap.alloc_tensor((2, self.world, self._merge_rows, 2), torch.float32)
+        if nb > self._merge_rows:
             raise ValueError("argmax_merge handles up to 1024 rows")
-        self._stage[0, :nb].copy_(out_val[:nb])
-        self._stage[1, :nb].copy_(out_ids[:nb].view(torch.float32) if out_ids.dtype == torch.int32 else out_ids[:nb])
-        self.heap.all_gather(self._stage_off, self._merge_off, 2 * 1024 * 4)
-        vals = self._merge[:, 0, :nb]
-        ids = self._merge[:, 1, :nb].view(torch.int32)
-        best = vals.max(dim=0).values
-        cand = torch.where(vals == best[None], ids, torch.full_like(ids, 2 ** 31 - 1))
-        out_ids[:nb].copy_(cand.min(dim=0).values)
+        ops.argmax_merge(out_ids, out_val, nb, self.heap.table, self._merge_off, self._merge_rows)

@@ -66,6 +66,110 @@ class VocabTokenizer:
         return "".join(self.tokens[i] for i in ids if 0 <= i < len(self.tokens))
 
 
+def _byte_alphabet() -> dict[int, str]:
+    """The printable stand-in for each byte that byte-level BPE vocabularies use (GPT-2 convention)."""
+    keep = list(range(ord("!"), ord("~") + 1)) + list(range(0xA1, 0xAD)) + list(range(0xAE, 0x100))
+    table, n = {}, 0
+    for b in range(256):
+        if b in keep:
+            table[b] = chr(b)
+        else:
+            table[b] = chr(256 + n)
+            n += 1
+    return table
+
+
+class BpeTokenizer:
+    """Byte-level BPE from a GGUF file's ``tokenizer.ggml.tokens`` and ``tokenizer.ggml.merges`` (model ``gpt2``, the
+    scheme of the llama-3, qwen and gpt-oss vocabularies): text is split into pre-token pieces, each piece's bytes are
+    mapped to the printable alphabet, and adjacent symbols are merged in rank order.  Special tokens
+    (``tokenizer.ggml.token_type`` 3 or 4, e.g. ``<|eot_id|>``) are matched verbatim before the split."""
+    _SPLIT = r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"
+
+    def __init__(self, tokens: list[str], merges: list[str], eos_id: int, bos_id: int | None = None,
+                 token_types: list[int] | None = None):
+        import regex
+        self.tokens, self.eos_id, self.bos_id, self.vocab_size = tokens, eos_id, bos_id, len(tokens)
+        self.index = {t: i for i, t in enumerate(tokens)}
+        self.rank = {tuple(m.split(" ", 1)): i for i, m in enumerate(merges)}
+        self.b2u = _byte_alphabet()
+        self.u2b = {u: b for b, u in self.b2u.items()}
+        self.split = regex.compile(self._SPLIT)
+        special = [t for i, t in enumerate(tokens) if token_types and i < len(token_types) and token_types[i] in (3, 4)]
+        self.special = sorted(special, key=len, reverse=True)
+        self.special_re = regex.compile("|".join(regex.escape(t) for t in self.special)) if self.special else None
+        self._cache: dict[str, list[int]] = {}
+
+    def _bpe(self, piece: str) -> list[int]:
+        hit = self._cache.get(piece)
+        if hit is not None:
+            return hit
+        sym = [self.b2u[b] for b in piece.encode("utf-8")]
+        while len(sym) > 1:
+            best, at = None, -1
+            for i in range(len(sym) - 1):
+                r = self.rank.get((sym[i], sym[i + 1]))
+                if r is not None and (best is None or r < best):
+                    best, at = r, i
+            if best is None:
+                break
+            sym[at: at + 2] = [sym[at] + sym[at + 1]]
+        ids = []
+        for t in sym:
+            i = self.index.get(t)
+            if i is None:                      # a symbol the vocabulary lacks: fall back to its single-byte tokens
+                ids += [self.index[c] for c in t if c in self.index]
+            else:
+                ids.append(i)
+        if len(self._cache) < 65536:
+            self._cache[piece] = ids
+        return ids
+
+    def _encode_plain(self, text: str) -> list[int]:
+        out: list[int] = []
+        for piece in self.split.findall(text):
+            out += self._bpe(piece)
+        return out
+
+    def encode(self, text: str) -> list[int]:
+        if not self.special_re:
+            return self._encode_plain(text)
+        out, pos = [], 0
+        for m in self.special_re.finditer(text):
+            out += self._encode_plain(text[pos: m.start()])
+            out.append(self.index[m.group(0)])
+            pos = m.end()
+        return out + self._encode_plain(text[pos:])
+
+    def decode(self, ids) -> str:
+        buf = bytearray()
+        for i in ids:
+            if 0 <= i < len(self.tokens):
+                t = self.tokens[i]
+                if t in self.special:
+                    buf += t.encode("utf-8")
+                else:
+                    buf += bytes(self.u2b[c] for c in t if c in self.u2b)
+        return buf.decode("utf-8", "replace")
+
+
+def tokenizer_from_metadata(meta: dict, vocab_size: int):
+    """The tokenizer a GGUF file describes: byte-level BPE when it carries merges, greedy longest match over the token
+    list when it only has tokens, raw bytes when it has neither (synthetic models)."""
+    tokens = meta.get("tokenizer.ggml.tokens")
+    if not tokens:
+        return ByteTokenizer(vocab_size)
+    tokens = [t if isinstance(t, str) else bytes(t).decode("utf-8", "replace") for t in tokens]
+    eos = int(meta.get("tokenizer.ggml.eos_token_id", len(tokens) - 1))
+    merges = meta.get("tokenizer.ggml.merges")
+    if merges:
+        bos = meta.get("tokenizer.ggml.bos_token_id")
+        types = meta.get("tokenizer.ggml.token_type")
+        return BpeTokenizer(tokens, [m if isinstance(m, str) else bytes(m).decode() for m in merges], eos,
+                            None if bos is None else int(bos), list(types) if types is not None else None)
+    return VocabTokenizer(tokens, eos)
+
+
 def render_chat(messages: list[dict]) -> str:
     return "".join(f"<|{m.get('role', 'user')}|>\n{m.get('content', '')}\n" for m in messages) + "<|assistant|>\n"
 
@@ -84,21 +188,6 @@ class SamplingParams:
         return self.temperature <= 0.0 or self.top_k == 1
 
 
-def sample(logits: torch.Tensor, p: SamplingParams, gen: torch.Generator | None) -> int:
-    """One token from a [V] logits row (host-side; the engine's device sampler serves the
-    graph-replayed greedy loop)."""
-    if p.greedy:
-        return int(torch.argmax(logits))
-    x = logits.float() / max(p.temperature, 1e-6)
-    k = p.top_k if p.top_k > 0 else min(64, x.numel())
-    vals, idx = torch.topk(x, min(k, x.numel()))
-    probs = torch.softmax(vals, dim=-1)
-    if p.top_p < 1.0:
-        keep = int((torch.cumsum(probs, 0) < p.top_p).sum().item()) + 1
-        probs, idx = probs[:keep] / probs[:keep].sum(), idx[:keep]
-    return int(idx[torch.multinomial(probs, 1, generator=gen)])
-
-
 @dataclass
 class Request:
     request_id: str
@@ -109,21 +198,41 @@ class Request:
     prefilled: int = 0
     cached_prompt_tokens: int = 0
     output: list[int] = field(default_factory=list)
-    finish_reason: str | None = None
+    finish_reason: str | None = None  # stop | length | error | cancelled
+    error: Exception | None = None    # what ended the request when finish_reason is "error"
     next_token: int | None = None
     t_arrival: float = 0.0
     t_first_token: float | None = None
     t_done: float | None = None
     keep_sequence: bool = False       # session turns keep their KV for the next turn
+    history: list[int] = field(default_factory=list)   # tokens the sequence already holds (a continued session)
+    opened: bool = False              # this request opened its sequence (and closes it if it fails)
     gen: torch.Generator | None = None
-    on_token: object = None           # callback(token_id) for streaming
+    on_token: object = None           # callback(token_id) for streaming (called from the scheduling thread)
+    on_done: object = None            # callback(request) when the request finishes, whatever the reason
 
     @property
     def ttft_s(self):
         return None if self.t_first_token is None else self.t_first_token - self.t_arrival
 
+    def uniform(self) -> float:
+        """The random number the sampler uses for this request's next token (seeded requests repeat)."""
+        return float(torch.rand(1, generator=self.gen).item())
+
+
+class RequestRejected(ValueError):
+    """A request that can never run on this server (longer than the context window, empty, ...)."""
+
 
 class Scheduler:
+    """Continuous batching over one backend.  ``step()`` admits waiting requests while sequence slots are free,
+    prefills their prompts in chunks (several requests share one forward call, up to ``prefill_chunk`` tokens), then
+    runs ONE decode step for every running sequence.  A request that fails (out of KV pages, a backend error) is
+    finished with ``finish_reason = "error"`` and leaves the queues, so it can never block the requests behind it.
+
+    The object is not thread-safe: one thread calls ``submit`` / ``step`` at a time (the server serialises them with
+    a lock and runs ``step`` on its scheduling thread)."""
+
     def __init__(self, backend: Backend, tokenizer, max_num_seqs: int = 64, prefill_chunk: int = 2048,
                  now=time.perf_counter):
         self.backend, self.tok, self.max_num_seqs, self.prefill_chunk, self.now = backend, tokenizer, max_num_seqs, prefill_chunk, now
@@ -132,13 +241,28 @@ class Scheduler:
         self._seq_ids = itertools.count(1)
         self._req_ids = itertools.count(1)
         self.stats = {"requests": 0, "prompt_tokens": 0, "completion_tokens": 0, "cached_prompt_tokens": 0, "steps": 0,
-                      "batch_size_sum": 0}
+                      "batch_size_sum": 0, "prefill_calls": 0, "prefill_seqs_sum": 0, "errors": 0, "rejected": 0,
+                      "d2h_bytes": 0}
+
+    @property
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
 
     def submit(self, prompt: list[int], params: SamplingParams, seq_id: int | None = None, keep_sequence: bool = False,
-               on_token=None) -> Request:
-        """``seq_id`` continues an existing sequence (a session turn): only the new tokens are run."""
+               on_token=None, on_done=None, history: list[int] | None = None) -> Request:
+        """``seq_id`` continues an existing sequence (a session turn): only the new tokens are run; ``history`` are the
+        tokens that sequence already holds (needed to publish its pages to the prefix cache under the right keys)."""
+        held = len(history) if history is not None else 0
+        limit = getattr(self.backend, "max_context", None)
+        if not prompt:
+            self.stats["rejected"] += 1
+            raise RequestRejected("the prompt is empty")
+        if limit is not None and held + len(prompt) + max(1, params.max_tokens) > limit:
+            self.stats["rejected"] += 1
+            raise RequestRejected(f"prompt of {held + len(prompt)} tokens plus max_tokens {params.max_tokens} exceeds the "
+                                  f"context window of {limit} tokens")
         r = Request(f"req-{next(self._req_ids)}", list(prompt), params, t_arrival=self.now(), keep_sequence=keep_sequence,
-                    on_token=on_token)
+                    on_token=on_token, on_done=on_done, history=list(history or []))
         if params.seed is not None:
             r.gen = torch.Generator().manual_seed(params.seed)
         if seq_id is not None:
@@ -148,16 +272,30 @@ class Scheduler:
         self.stats["prompt_tokens"] += len(r.prompt)
         return r
 
-    def _finish(self, r: Request, reason: str):
-        r.finish_reason, r.state, r.t_done = reason, "finished", self.now()
+    def cancel(self, r: Request):
+        """Drop a request (client went away); its sequence is closed unless a session keeps it."""
+        if r.state != "finished":
+            self._finish(r, "cancelled")
+
+    def _finish(self, r: Request, reason: str, error: Exception | None = None):
+        r.finish_reason, r.state, r.t_done, r.error = reason, "finished", self.now(), error
         if r in self.running:
             self.running.remove(r)
+        if r in self.waiting:
+            self.waiting.remove(r)
         self.stats["completion_tokens"] += len(r.output)
-        if not r.keep_sequence:
-            self.backend.end(r.seq_id)
+        if error is not None:
+            self.stats["errors"] += 1
+        # a failed or cancelled request gives its sequence back even inside a session: what the pages hold is unknown
+        if r.seq_id >= 0 and (not r.keep_sequence or (reason in ("error", "cancelled") and r.opened)):
+            try:
+                self.backend.end(r.seq_id)
+            except Exception:       # noqa: BLE001 - closing must not raise out of the scheduling loop
+                pass
+        if r.on_done:
+            r.on_done(r)
 
-    def _accept(self, r: Request, logits_row: torch.Tensor):
-        tok = sample(logits_row, r.params, r.gen)
+    def _accept(self, r: Request, tok: int):
         if r.t_first_token is None:
             r.t_first_token = self.now()
         if tok == self.tok.eos_id:
@@ -173,42 +311,87 @@ class Scheduler:
         if len(r.output) >= r.params.max_tokens:
             return self._finish(r, "length")
 
+    def _sample_batch(self, reqs: list[Request], seq_ids, new_tokens) -> list[int] | None:
+        """One backend call for ``reqs`` and one sampled token per request; on a backend error the requests are retried
+        one by one so that only the ones that really fail are finished with an error.  Returns ``None`` when every
+        request of the batch has been dealt with that way."""
+        try:
+            toks = self.backend.step(seq_ids, new_tokens, [r.params for r in reqs], [r.uniform() if not r.params.greedy else 0.0 for r in reqs])
+            self.stats["d2h_bytes"] += getattr(self.backend, "last_d2h_bytes", 0)
+            return toks
+        except Exception as e:       # noqa: BLE001 - any backend failure is turned into per-request errors
+            if len(reqs) == 1:
+                self._finish(reqs[0], "error", e)
+                return None
+            for r, s, t in zip(reqs, seq_ids, new_tokens):
+                one = self._sample_batch([r], [s], [t])
+                if one is not None:
+                    self._after_forward(r, len(t), one[0])
+            return None
+
+    def _after_forward(self, r: Request, n_fed: int, tok: int):
+        """Book ``n_fed`` tokens just run for ``r`` and, if that completed what it had to feed, take the sampled token."""
+        if r.state == "running":
+            return self._accept(r, tok)
+        r.prefilled += n_fed
+        if r.prefilled == len(r.prompt):
+            if r in self.waiting:
+                self.waiting.remove(r)
+            r.state = "running"
+            self.running.append(r)
+            try:
+                self.backend.publish(r.seq_id, r.history + r.prompt)
+            except Exception:      # noqa: BLE001 - the prefix index is an optimisation
+                pass
+            self._accept(r, tok)
+        else:
+            r.state = "prefill"
+
     def step(self) -> int:
         """One scheduling step: admit + prefill chunks, then one decode step.  Returns the number
         of sequences that made progress."""
         progressed = 0
-        # ---- admission and (chunked) prefill
+        # ---- admission and (chunked) prefill: several requests share the token budget of one forward call
         budget = self.prefill_chunk
-        while self.waiting and len(self.running) < self.max_num_seqs and budget > 0:
-            r = self.waiting[0]
+        batch: list[tuple[Request, int]] = []
+        slots = self.max_num_seqs - len(self.running)
+        for r in list(self.waiting):
+            if budget <= 0 or len(batch) >= slots:
+                break
             if r.seq_id < 0:
-                r.seq_id = next(self._seq_ids)
-                r.cached_prompt_tokens = self.backend.begin(r.seq_id, r.prompt)
+                try:
+                    r.seq_id = next(self._seq_ids)
+                    r.cached_prompt_tokens = self.backend.begin(r.seq_id, r.prompt)
+                    r.opened = True
+                except Exception as e:      # noqa: BLE001
+                    r.seq_id = -1
+                    self._finish(r, "error", e)
+                    continue
                 r.prefilled = r.cached_prompt_tokens
                 self.stats["cached_prompt_tokens"] += r.cached_prompt_tokens
             n = min(budget, len(r.prompt) - r.prefilled)
-            logits = self.backend.forward([r.seq_id], [r.prompt[r.prefilled: r.prefilled + n]])
-            r.prefilled += n
+            batch.append((r, n))
             budget -= n
-            progressed += 1
-            if r.prefilled == len(r.prompt):
-                self.waiting.pop(0)
-                r.state = "running"
-                self.running.append(r)
-                self.backend.publish(r.seq_id, r.prompt)
-                self._accept(r, logits[0])
-            else:
-                r.state = "prefill"
-                break
-        # ---- one decode step for everyone who has a token to feed
-        batch = [r for r in self.running if r.next_token is not None]
         if batch:
-            logits = self.backend.forward([r.seq_id for r in batch], [[r.next_token] for r in batch])
-            self.stats["steps"] += 1
-            self.stats["batch_size_sum"] += len(batch)
-            for i, r in enumerate(batch):
-                self._accept(r, logits[i])
+            reqs = [r for r, _ in batch]
+            feeds = [r.prompt[r.prefilled: r.prefilled + n] for r, n in batch]
+            toks = self._sample_batch(reqs, [r.seq_id for r in reqs], feeds)
+            self.stats["prefill_calls"] += 1
+            self.stats["prefill_seqs_sum"] += len(batch)
+            if toks is not None:
+                for (r, n), tok in zip(batch, toks):
+                    self._after_forward(r, n, tok)
             progressed += len(batch)
+        # ---- one decode step for everyone who has a token to feed
+        dec = [r for r in self.running if r.next_token is not None]
+        if dec:
+            toks = self._sample_batch(dec, [r.seq_id for r in dec], [[r.next_token] for r in dec])
+            self.stats["steps"] += 1
+            self.stats["batch_size_sum"] += len(dec)
+            if toks is not None:
+                for r, tok in zip(dec, toks):
+                    self._accept(r, tok)
+            progressed += len(dec)
         return progressed
 
     def run_until_done(self, reqs: list[Request], max_steps: int = 1_000_000):

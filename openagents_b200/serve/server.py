@@ -20,34 +20,89 @@ from __future__ import annotations
 import argparse
 import hashlib
 import json
+import os
+import queue
 import threading
 import time
 import uuid
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 
 from .. import ENGINE_NAME, __version__
+from ..gateway.observability import ChatTraceEmitter, RateMonitorConfig, ServedTokensLedger, ServingRateMonitor
+from ..utils.nvtx import nvtx_range
 from ..utils.telemetry import Histogram, measured, not_measured
 from . import tools as tooling
-from .generation import (CHAT_TEMPLATE_DIGEST, ByteTokenizer, Request, SamplingParams, Scheduler, VocabTokenizer,
-                         render_chat)
+from .generation import (CHAT_TEMPLATE_DIGEST, ByteTokenizer, Request, RequestRejected, SamplingParams, Scheduler,
+                         VocabTokenizer, render_chat, tokenizer_from_metadata)
 
 ENDPOINTS = ["/health", "/v1/models", "/v1/chat/completions", "/v1/responses", "/v1/sessions", "/v1/serve",
              "/psionic/management/status", "/metrics"]
 
 
 class ServedModel:
+    """One model, one engine, ONE scheduling thread.  HTTP handlers never run the engine: they ``submit`` (a short
+    critical section) and wait on the request's completion event or token queue, so requests that arrive while
+    others are decoding join the same decode batch (continuous batching across connections)."""
+
     def __init__(self, model_id: str, backend, artifact_digest: str | None, tokenizer=None, max_num_seqs: int = 64,
-                 prefill_chunk: int = 2048):
+                 prefill_chunk: int = 2048, chat_template: str | None = None):
         self.id, self.backend, self.artifact_digest = model_id, backend, artifact_digest
         self.tok = tokenizer or ByteTokenizer(backend.cfg.vocab)
+        self.chat_template = chat_template          # a GGUF chat template admitted by the digest allowlist, or None
         self.sched = Scheduler(backend, self.tok, max_num_seqs=max_num_seqs, prefill_chunk=prefill_chunk)
-        self.lock = threading.Lock()      # one engine, one scheduling thread at a time
+        self.cv = threading.Condition()              # guards the scheduler and the backend
         self.created = int(time.time())
+        self.closed = False
+        self.thread = threading.Thread(target=self._loop, name=f"sched-{model_id}", daemon=True)
+        self.thread.start()
 
-    def generate(self, prompt_ids, params, seq_id=None, keep=False, on_token=None) -> Request:
-        with self.lock:
-            r = self.sched.submit(prompt_ids, params, seq_id=seq_id, keep_sequence=keep, on_token=on_token)
-            self.sched.run_until_done([r])
+    # `lock` is what guards direct backend calls made outside the scheduling loop (closing a session's sequence)
+    @property
+    def lock(self):
+        return self.cv
+
+    def _loop(self):
+        while True:
+            with self.cv:
+                while not self.closed and not self.sched.has_work:
+                    self.cv.wait()
+                if self.closed:
+                    return
+                with nvtx_range("scheduler.step"):
+                    self.sched.step()
+
+    def close(self):
+        with self.cv:
+            self.closed = True
+            self.cv.notify_all()
+        self.thread.join(timeout=5)
+
+    def submit(self, prompt_ids, params, seq_id=None, keep=False, on_token=None, on_done=None, history=None) -> Request:
+        with self.cv:
+            r = self.sched.submit(prompt_ids, params, seq_id=seq_id, keep_sequence=keep, on_token=on_token, on_done=on_done,
+                                  history=history)
+            self.cv.notify_all()
+        return r
+
+    def generate(self, prompt_ids, params, seq_id=None, keep=False, on_token=None, history=None) -> Request:
+        """Blocking completion.  ``on_token`` is called on THIS thread (tokens cross from the scheduling thread through
+        a queue), so a slow client socket never stalls the decode loop."""
+        q: queue.SimpleQueue = queue.SimpleQueue()
+        r = self.submit(prompt_ids, params, seq_id=seq_id, keep=keep, on_token=q.put, on_done=lambda _r: q.put(None),
+                        history=history)
+        while True:
+            tok = q.get()
+            if tok is None:
+                break
+            if on_token:
+                try:
+                    on_token(tok)
+                except (BrokenPipeError, ConnectionError, OSError):      # client went away: stop generating for it
+                    with self.cv:
+                        self.sched.cancel(r)
+                    on_token = None
+        if r.finish_reason == "error" and r.error is not None:
+            raise r.error
         return r
 
 
@@ -72,6 +127,10 @@ class ServerState:
         self.ttft = Histogram([0.005, 0.01, 0.025, 0.05, 0.1, 0.25, 0.5, 1, 2.5, 5, 10])
         self.itl = Histogram([0.0005, 0.001, 0.002, 0.005, 0.01, 0.02, 0.05, 0.1, 0.25])
         self.lock = threading.Lock()
+        # served-token ledger (one idempotent row per completed request), rate monitor over it, opt-in trace emitter
+        self.ledger = ServedTokensLedger(os.environ.get("B200_SERVED_TOKENS_LEDGER") or None)
+        self.rate_monitor = ServingRateMonitor(self.ledger, RateMonitorConfig.from_env())
+        self.traces = ChatTraceEmitter(enabled=os.environ.get("B200_CHAT_TRACE_EMIT", "false").lower() == "true")
 
     def model(self, name: str | None) -> ServedModel:
         if not name:
@@ -89,19 +148,34 @@ class ServerState:
                                 stop=tuple(body["stop"]) if isinstance(body.get("stop"), list) else ((body["stop"],) if body.get("stop") else ()),
                                 seed=body.get("seed"))
         ids = model.tok.encode(render_chat(messages))
-        if session is None:
-            r = model.generate(ids, params, on_token=on_token)
-        else:
-            feed = session.pending + ids
-            if session.seq_id is None:
-                r = model.generate(feed, params, keep=True, on_token=on_token)
-                session.seq_id = r.seq_id
+        with nvtx_range("serve.complete"):
+            if session is None:
+                r = model.generate(ids, params, on_token=on_token)
             else:
-                r = model.generate(feed, params, seq_id=session.seq_id, keep=True, on_token=on_token)
-            session.tokens += feed + r.output[:-1] if r.output else feed
-            session.pending = r.output[-1:] if r.output else []
+                feed = session.pending + ids
+                try:
+                    if session.seq_id is None:
+                        r = model.generate(feed, params, keep=True, on_token=on_token)
+                        session.seq_id = r.seq_id
+                    else:
+                        r = model.generate(feed, params, seq_id=session.seq_id, keep=True, on_token=on_token,
+                                           history=session.tokens)
+                except RequestRejected:
+                    raise
+                except Exception:
+                    session.seq_id, session.tokens, session.pending = None, [], []     # the scheduler closed the sequence
+                    raise
+                session.tokens += feed + r.output[:-1] if r.output else feed
+                session.pending = r.output[-1:] if r.output else []
         usage = {"prompt_tokens": len(ids), "completion_tokens": len(r.output), "total_tokens": len(ids) + len(r.output),
                  "prompt_tokens_details": {"cached_tokens": r.cached_prompt_tokens}}
+        self.ledger.record(r.request_id + "." + uuid.uuid4().hex[:8], model.id, len(ids), len(r.output),
+                           account_ref=str(body.get("user") or "account.anonymous"), adapter_id=ENGINE_NAME,
+                           demand_kind=str(body.get("demand_kind") or "unlabeled"))
+        self.rate_monitor.lane_heartbeat(True)
+        trace = self.traces.emit(messages, model.tok.decode(r.output), opted_in=bool(body.get("emit_trace")))
+        if trace.get("emitted"):
+            usage["trace"] = trace["path"]
         with self.lock:
             if r.ttft_s is not None:
                 self.ttft.observe(r.ttft_s)
@@ -135,7 +209,8 @@ class ServerState:
                 "models": [{"id": m.id, "backend": m.backend.name, "architecture": m.backend.cfg.arch,
                             "artifact_digest": m.artifact_digest, "kv": m.backend.kv_stats(),
                             "topology": m.backend.topology(), "scheduler": dict(m.sched.stats)} for m in self.models.values()],
-                "sessions": len(self.sessions)}
+                "sessions": len(self.sessions), "tokens_served": self.ledger.public_projection(),
+                "serving_rate": self.rate_monitor.tick()["classification"]}
 
     def metrics_text(self) -> str:
         out = []
@@ -145,9 +220,12 @@ class ServerState:
                     f"b200_completion_tokens_total{lab} {s['completion_tokens']}",
                     f"b200_prefix_cache_hit_tokens_total{lab} {s['cached_prompt_tokens']}",
                     f"b200_decode_steps_total{lab} {s['steps']}",
-                    f"b200_decode_batch_size_avg{lab} {s['batch_size_sum'] / s['steps'] if s['steps'] else 0}"]
+                    f"b200_decode_batch_size_avg{lab} {s['batch_size_sum'] / s['steps'] if s['steps'] else 0}",
+                    f"b200_request_errors_total{lab} {s['errors']}", f"b200_requests_rejected_total{lab} {s['rejected']}",
+                    f"b200_sampled_ids_d2h_bytes_total{lab} {s['d2h_bytes']}"]
             for k, v in m.backend.kv_stats().items():
                 out.append(f"b200_kv_{k}{lab} {v}")
+        out.append(f"b200_tokens_served_total {self.ledger.total()}")
         out += self.ttft.prometheus("b200_ttft_seconds") + self.itl.prometheus("b200_inter_token_latency_seconds")
         return "\n".join(out) + "\n"
 
@@ -245,6 +323,8 @@ def make_handler(state: ServerState):
                     s.responses.append(rid)
                     return self._json(200, {"id": rid, "session": s.id, "output_text": s.model.tok.decode(r.output),
                                             "usage": usage})
+            except RequestRejected as e:
+                return self._err(400, str(e), "context_length_exceeded")
             except MemoryError as e:
                 return self._err(503, str(e), "kv_cache_exhausted")
             except Exception as e:      # surface engine errors as a typed, non-retryable failure
@@ -347,8 +427,23 @@ def make_handler(state: ServerState):
     return H
 
 
+def load_tokenizer(path: str, vocab_size: int):
+    """Tokenizer and chat template of a GGUF file.  The template is used only when its digest is on the allowlist of
+    ``control.node_bridge`` (a template is code that runs on every request); otherwise the built-in template applies."""
+    from ..control.node_bridge import template_admitted
+    from ..gguf import GGUFFile
+    meta = {k: v for k, v in GGUFFile(path).metadata.items() if k.startswith("tokenizer.")}
+    tok = tokenizer_from_metadata(meta, vocab_size)
+    tpl = meta.get("tokenizer.chat_template")
+    return tok, (tpl if isinstance(tpl, str) and template_admitted(tpl) else None)
+
+
 def build_state(model_paths: list[str], backend: str = "cuda", max_num_seqs: int = 64, kv_page_size: int = 16,
-                max_ctx: int = 4096, reasoning_budget: int = 0, mesh_coordination: str = "disabled") -> ServerState:
+                max_ctx: int = 4096, reasoning_budget: int = 0, mesh_coordination: str = "disabled",
+                device="cuda:0", tp_rank: int = 0, tp_world: int = 1, ep_rank: int = 0, ep_world: int = 1, comm=None,
+                control_group=None) -> ServerState:
+    """``tp_world`` / ``ep_world`` > 1: this process is rank 0 of a tensor- or expert-parallel group whose other ranks
+    run ``serve.distributed.follower_loop``; every engine call is first announced to them over ``control_group``."""
     from ..receipts.manifests import artifact_digest
     from .backend import CpuBackend, CudaBackend
     if backend not in ("cpu", "cuda"):
@@ -357,9 +452,17 @@ def build_state(model_paths: list[str], backend: str = "cuda", max_num_seqs: int
         raise ValueError("the paged KV cache uses 16-token pages")
     models = []
     for p in model_paths:
-        b = CpuBackend.from_gguf(p) if backend == "cpu" else CudaBackend.from_gguf(p, max_num_seqs=max_num_seqs, max_ctx=max_ctx)
+        if backend == "cpu":
+            b = CpuBackend.from_gguf(p)
+        else:
+            b = CudaBackend.from_gguf(p, device=device, max_num_seqs=max_num_seqs, max_ctx=max_ctx, tp_rank=tp_rank,
+                                      tp_world=tp_world, comm=comm, ep_rank=ep_rank, ep_world=ep_world)
+        if max(tp_world, ep_world) > 1:
+            from .distributed import LeaderBackend
+            b = LeaderBackend(b, control_group)
         mid = p.rsplit("/", 1)[-1].removesuffix(".gguf")
-        models.append(ServedModel(mid, b, artifact_digest(p), max_num_seqs=max_num_seqs))
+        tok, tpl = load_tokenizer(p, b.cfg.vocab)
+        models.append(ServedModel(mid, b, artifact_digest(p), tokenizer=tok, max_num_seqs=max_num_seqs, chat_template=tpl))
     return ServerState(models, reasoning_budget, mesh_coordination)
 
 
@@ -369,28 +472,54 @@ def serve(state: ServerState, host: str = "127.0.0.1", port: int = 8080) -> Thre
     return httpd
 
 
-def main(argv=None):
+def _flag_env(name: str, default):
+    """Flags are decoded once: the command line wins, then ``B200_SERVE_<FLAG>`` from the environment, then the default."""
+    v = os.environ.get("B200_SERVE_" + name.upper().replace("-", "_"))
+    return type(default)(v) if v is not None and default is not None else (v if v is not None else default)
+
+
+def parse_args(argv=None):
     ap = argparse.ArgumentParser(prog="b200-serve")
     ap.add_argument("-m", "--model", action="append", required=True)
-    ap.add_argument("--backend", default="cuda", choices=["cpu", "cuda"])
-    ap.add_argument("--host", default="127.0.0.1")
-    ap.add_argument("--port", type=int, default=8080)
-    ap.add_argument("--reasoning-budget", type=int, default=0)
-    ap.add_argument("--mesh-coordination", default="disabled", choices=["enabled", "disabled"])
-    ap.add_argument("--tp", type=int, default=1)
-    ap.add_argument("--ep", type=int, default=1)
-    ap.add_argument("--kv-page-size", type=int, default=16)
-    ap.add_argument("--max-num-seqs", type=int, default=64)
-    ap.add_argument("--max-ctx", type=int, default=4096)
+    ap.add_argument("--backend", default=_flag_env("backend", "cuda"), choices=["cpu", "cuda"])
+    ap.add_argument("--host", default=_flag_env("host", "127.0.0.1"))
+    ap.add_argument("--port", type=int, default=_flag_env("port", 8080))
+    ap.add_argument("--reasoning-budget", type=int, default=_flag_env("reasoning-budget", 0))
+    ap.add_argument("--mesh-coordination", default=_flag_env("mesh-coordination", "disabled"), choices=["enabled", "disabled"])
+    ap.add_argument("--tp", type=int, default=_flag_env("tp", 1), help="tensor-parallel ranks (one GPU each)")
+    ap.add_argument("--ep", type=int, default=_flag_env("ep", 1), help="expert-parallel ranks (models with experts)")
+    ap.add_argument("--kv-page-size", type=int, default=_flag_env("kv-page-size", 16))
+    ap.add_argument("--max-num-seqs", type=int, default=_flag_env("max-num-seqs", 64))
+    ap.add_argument("--max-ctx", type=int, default=_flag_env("max-ctx", 4096))
     a = ap.parse_args(argv)
-    state = build_state(a.model, a.backend, a.max_num_seqs, a.kv_page_size, a.max_ctx, a.reasoning_budget, a.mesh_coordination)
+    if a.tp > 1 and a.ep > 1:
+        ap.error("--tp and --ep cannot be combined")
+    if max(a.tp, a.ep) > 1 and a.backend != "cuda":
+        ap.error("--tp / --ep need --backend cuda")
+    return a
+
+
+def run_server(a, **parallel):
+    state = build_state(a.model, a.backend, a.max_num_seqs, a.kv_page_size, a.max_ctx, a.reasoning_budget, a.mesh_coordination,
+                        **parallel)
     httpd = serve(state, a.host, a.port)
     print(json.dumps({"event": "listening", "host": a.host, "port": a.port, "models": list(state.models),
-                      "execution_engine": ENGINE_NAME}), flush=True)
+                      "execution_engine": ENGINE_NAME, "tp": a.tp, "ep": a.ep}), flush=True)
     try:
         httpd.serve_forever()
     except KeyboardInterrupt:
         pass
+    finally:
+        for m in state.models.values():
+            m.close()
+
+
+def main(argv=None):
+    a = parse_args(argv)
+    if max(a.tp, a.ep) > 1:
+        from .distributed import launch_ranks
+        return launch_ranks(a)
+    run_server(a)
 
 
 if __name__ == "__main__":

@@ -146,20 +146,71 @@ def bench_gemm(rows):
 
 
 def bench_qgemm(rows):
-    hbm, tf, tag = peaks()
+    """The projections of a Llama-3-8B layer (and the LM head) on the fused-dequant GEMM at decode batch sizes, judged
+    against the copy bandwidth over the PACKED weight bytes.  Each timing is a CUDA graph over several different
+    weight matrices (together larger than L2), so neither the host launch path nor a warm L2 is in the number.
+    ``torch.matmul`` on a bf16 copy of the same matrix is the library reference (it reads 3.5x the bytes)."""
+    hbm, _, tag = peaks()
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    for name, N, K, t in (("qkv", 6144, 4096, GgmlType.Q4_K), ("o", 4096, 4096, GgmlType.Q4_K), ("gate_up", 28672, 4096, GgmlType.Q4_K),
-                          ("down", 4096, 14336, GgmlType.Q4_K), ("lm_head", 128256, 4096, GgmlType.Q6_K)):
-        w = _rand_q(N, K, t)
-        for T in (64, 2048):
-            if T == 2048 and name == "lm_head":
-                continue
+    shapes = (("qkv", 6144, 4096, GgmlType.Q4_K, "add", 8), ("wo", 4096, 4096, GgmlType.Q4_K, "add", 8),
+              ("gate_up", 28672, 4096, GgmlType.Q4_K, "swiglu", 4), ("down", 4096, 14336, GgmlType.Q4_K, "add", 6),
+              ("lm_head", 128256, 4096, GgmlType.Q6_K, "store", 2))
+    for name, N, K, t, mode, R in shapes:
+        ws = [_rand_q(N, K, t) for _ in range(R)]
+        for T in (16, 64):
             x = torch.randn(T, K, device=DEV).bfloat16()
-            y = torch.zeros((T, N), device=DEV)
-            fn = lambda: ops.qgemm(w, x, T, y, N, epi=ops.QEPI_ADD, split_k=0, status=status)
-            s = timeit(fn, iters=10)
-            gbs, fl = w.nbytes() / s / 1e9, 2.0 * T * N * K / s / 1e12
-            rows.append(f"qgemm {name:8s} N={N:6d} K={K:5d} {t.name} T={T:4d}: {s*1e6:8.1f} us  {gbs:6.0f} GB/s ({gbs/hbm:4.2f} of {tag} HBM)  {fl:7.1f} TFLOP/s ({fl/tf:4.2f} of {tag} bf16)")
+            out = torch.zeros((T, N), device=DEV)
+            outb = torch.zeros((T, N // 2), dtype=torch.bfloat16, device=DEV)
+
+            def launch(w):
+                if mode == "swiglu":
+                    ops.qgemm(w, x, T, out_bf16=outb, ldo=N // 2, epi=ops.QEPI_SWIGLU, status=status)
+                elif mode == "add":
+                    ops.qgemm(w, x, T, out_f32=out, epi=ops.QEPI_ADD, status=status)
+                else:
+                    ops.qgemm(w, x, T, out_f32=out, epi=ops.QEPI_STORE, status=status)
+
+            for w in ws[:2]:
+                launch(w)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for w in ws:
+                    launch(w)
+            g.replay()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) * 1e-3 / R)
+            s_ = sorted(ts)[len(ts) // 2]
+            gbs = ws[0].nbytes() / s_ / 1e9
+            rows.append(f"qgemm {name:8s} N={N:6d} K={K:5d} {t.name} {mode:6s} T={T:3d}: {s_*1e6:8.1f} us  {gbs:6.0f} GB/s packed "
+                        f"({gbs/hbm:4.2f} of {tag} HBM)")
+        if name != "lm_head":
+            Bs = [torch.randn(N, K, device=DEV).bfloat16() for _ in range(R)]
+            A = torch.randn(64, K, device=DEV).bfloat16()
+            ob = torch.empty((64, N), dtype=torch.bfloat16, device=DEV)
+            g = torch.cuda.CUDAGraph()
+            torch.matmul(A, Bs[0].t(), out=ob)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g):
+                for B in Bs:
+                    torch.matmul(A, B.t(), out=ob)
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            rows.append(f"      torch.matmul on a bf16 copy, T= 64 (library reference): {e0.elapsed_time(e1) * 1e3 / R:8.1f} us")
+            del Bs
+        del ws
     assert int(status.item()) == 0
 
 

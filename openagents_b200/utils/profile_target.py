@@ -31,8 +31,11 @@ def main():
         N, K, t = (28672, 4096, GgmlType.Q4_K) if case == "qgemm64" else (128256, 4096, GgmlType.Q6_K)
         w = _rand_q(N, K, t)
         x = torch.randn(64, K, device=DEV).bfloat16()
-        y = torch.zeros((64, N), device=DEV)
-        fn = lambda: ops.qgemm(w, x, 64, y, N, epi=ops.QEPI_ADD, split_k=0, status=status)
+        y = torch.zeros((64, N // 2), dtype=torch.bfloat16, device=DEV) if case == "qgemm64" else torch.zeros((64, N), device=DEV)
+        if case == "qgemm64":      # gate/up projection with the SwiGLU epilogue, the largest matrix of a layer
+            fn = lambda: ops.qgemm(w, x, 64, out_bf16=y, ldo=N // 2, epi=ops.QEPI_SWIGLU, status=status)
+        else:
+            fn = lambda: ops.qgemm(w, x, 64, out_f32=y, epi=ops.QEPI_STORE, status=status)
     elif case == "gemm":
         M, N, K = 2048, 28672, 4096
         A, B = torch.randn(M, K, device=DEV).bfloat16(), torch.randn(N, K, device=DEV).bfloat16()

@@ -142,3 +142,29 @@ def test_repack_roundtrip_and_orders():
     L = torch.stack((qs & 0xF, qs >> 4), 2).reshape(-1, 256).long()
     assert torch.equal(el, L)
     assert tc.X8_POS == (0, 2, 4, 6, 1, 3, 5, 7)
+
+
+def test_corrupt_headers_are_errors_not_crashes(tmp_path):
+    """Header counts and tensor extents are checked against the file size with overflow-safe arithmetic."""
+    import struct
+    from openagents_b200.gguf import GGUFFile
+
+    def write(name, body):
+        p = tmp_path / name
+        p.write_bytes(b"GGUF" + struct.pack("<I", 3) + body)
+        return str(p)
+
+    # counts far beyond what the file could hold
+    with pytest.raises(Exception, match="counts exceed|malformed|truncated"):
+        GGUFFile(write("huge_counts.gguf", struct.pack("<QQ", 2 ** 60, 0) + b"\0" * 64))
+    with pytest.raises(Exception, match="counts exceed|malformed|truncated"):
+        GGUFFile(write("huge_kv.gguf", struct.pack("<QQ", 0, 2 ** 61) + b"\0" * 64))
+    # one tensor whose dimensions multiply past 64 bits
+    name = b"t"
+    info = struct.pack("<Q", len(name)) + name + struct.pack("<I", 2) + struct.pack("<QQ", 2 ** 40, 2 ** 40) + struct.pack("<IQ", 0, 0)
+    with pytest.raises(Exception, match="impossible element count|past the end"):
+        GGUFFile(write("overflow_dims.gguf", struct.pack("<QQ", 1, 0) + info + b"\0" * 64))
+    # an offset chosen so that offset + size wraps around
+    info = struct.pack("<Q", len(name)) + name + struct.pack("<I", 1) + struct.pack("<Q", 32) + struct.pack("<IQ", 0, 2 ** 64 - 64)
+    with pytest.raises(Exception, match="past the end"):
+        GGUFFile(write("wrap_offset.gguf", struct.pack("<QQ", 1, 0) + info + b"\0" * 256))

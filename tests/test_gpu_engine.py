@@ -127,3 +127,38 @@ def test_device_side_decode_loop_matches_stepwise(tmp_path):
             outs.append(eng.decode_steps(ids, first, 20).cpu().long())
     assert torch.equal(outs[0], outs[1])
     assert eng.pool.length(10) == len(prompts[0]) + 20
+
+
+def test_backend_samples_on_the_device(tmp_path):
+    """The serving backend's step: greedy rows take the engine's fused arg-max, the others the device top-k / top-p
+    kernel; four bytes per sequence come back.  Sampled ids must lie in the oracle's top-k, and a seeded request repeats."""
+    from openagents_b200.serve.backend import CudaBackend
+    from openagents_b200.serve.generation import ByteTokenizer, SamplingParams, Scheduler
+    cfg = TINY_LLAMA.with_(vocab=1000)
+    p = str(tmp_path / "t.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 5), PLAN_Q8_0)
+    cfg2, W = load_gguf_float(p)
+    be = CudaBackend.from_gguf(p, max_num_seqs=8, max_ctx=256, max_tokens=256)
+    prompt = list(range(20, 45))
+    ref = llama_forward(cfg2, W, torch.tensor(prompt), KVCacheRef(cfg.n_layers))[-1]
+    be.begin(1, prompt)
+    be.begin(2, prompt)
+    hot = SamplingParams(temperature=0.9, top_k=5, top_p=1.0)
+    ids = be.step([1, 2], [prompt, prompt], [SamplingParams(), hot], [0.0, 0.6])
+    assert be.last_d2h_bytes == 8
+    assert ids[0] == int(ref.argmax()) and ids[1] in ref.topk(5).indices.tolist()
+    ids2 = be.step([1, 2], [[ids[0]], [ids[1]]], [SamplingParams(), hot], [0.0, 0.1])
+    assert len(ids2) == 2 and be.last_d2h_bytes == 8
+    be.end(1)
+    be.end(2)
+    # through the scheduler: a seeded sampled request repeats token for token
+    outs = []
+    for _ in range(2):
+        sch = Scheduler(be, ByteTokenizer(cfg.vocab), max_num_seqs=4)
+        r = sch.submit(prompt, SamplingParams(max_tokens=12, temperature=0.8, top_k=8, seed=7))
+        g = sch.submit(prompt[:10], SamplingParams(max_tokens=12))
+        sch.run_until_done([r, g])
+        assert r.finish_reason in ("length", "stop") and g.finish_reason in ("length", "stop")
+        outs.append(r.output)
+    assert outs[0] == outs[1] and sch.stats["d2h_bytes"] > 0
+    be.engine.check_status()

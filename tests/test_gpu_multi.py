@@ -166,6 +166,24 @@ def _tp_engine(rank, world, path):
         got = full_logits(logits)
         assert (got - ref).abs().max().item() < 0.08 * scale, (step, (got - ref).abs().max().item())
         toks = ref.argmax(-1).tolist()
+    # a 12-sequence decode batch: fused-dequant GEMMs with the slot all-reduce (eager, then replayed from a graph)
+    many = [torch.randint(0, cfg.vocab, (4 + b % 3,), generator=g) for b in range(12)]
+    ids = list(range(5, 17))
+    for b in ids:
+        eng.begin(b)
+    logits, nxt = eng.forward_tokens(ids, [p.tolist() for p in many])
+    caches = [KVCacheRef(cfg.n_layers) for _ in range(12)]
+    ref = torch.stack([llama_forward(cfg, W, many[b], caches[b])[-1] for b in range(12)])
+    got = full_logits(logits)
+    assert (got - ref).abs().max().item() < 0.08 * scale, (got - ref).abs().max().item()
+    toks = ref.argmax(-1).tolist()
+    for step in range(3):
+        logits, nxt = eng.decode(ids, toks, use_graph=(step > 0))
+        ref = torch.stack([llama_forward(cfg, W, torch.tensor([toks[b]]), caches[b])[-1] for b in range(12)])
+        got = full_logits(logits)
+        assert (got - ref).abs().max().item() < 0.08 * scale, (step, (got - ref).abs().max().item())
+        assert nxt.tolist() == got.argmax(-1).tolist()
+        toks = ref.argmax(-1).tolist()
     eng.check_status()
     assert comm.heap.status() == (0, 0)
 

@@ -76,3 +76,64 @@ def test_stage_decode_batch():
         pool.stage_decode(torch.tensor([1234], dtype=torch.int64).data_ptr(), 1, 8, True, *ptrs)
     with pytest.raises(ValueError):
         pool.stage_decode(*args[:2], 1, True, *ptrs)
+
+
+def test_publish_covers_the_whole_sequence_and_hits_compare_tokens():
+    """A page is registered under the tokens it really holds: publishing a continued sequence takes the full token
+    list, and a lookup whose tokens differ from the registered page's is not a hit."""
+    p = KVPool(32, 16)
+    turn1 = list(range(100, 140))                  # 40 tokens
+    p.begin(1, turn1)
+    p.extend(1, 40)
+    p.publish(1, turn1)
+    gen = list(range(500, 508))                    # 8 generated tokens, then a second turn of 16
+    turn2 = list(range(700, 716))
+    p.extend(1, 8 + 16)
+    p.publish(1, turn1 + gen + turn2)              # 64 tokens: pages 2 and 3 are registered under their true contents
+    assert p.begin(2, turn1 + gen + turn2 + [1]) == 64
+    assert p.begin(3, turn2 * 4 + [1]) == 0        # the new turn alone is not a prefix of anything cached
+    # a list longer than the sequence is cut to what the sequence holds
+    p.begin(4)
+    p.extend(4, 16)
+    p.publish(4, list(range(900, 948)))
+    assert p.begin(5, list(range(900, 948)) + [1]) == 16
+
+
+def test_truncate_unregisters_the_partial_page_and_copies_a_shared_one():
+    p = KVPool(32, 16)
+    A = list(range(200, 248))                      # three full pages
+    p.begin(1, A)
+    p.extend(1, 48)
+    p.publish(1, A)
+    assert p.truncate(1, 20) is None               # sole owner: page 1 stays, leaves the index
+    assert len(p.pages(1)) == 2
+    assert p.begin(2, A + [1]) == 16               # only page 0 can still be shared
+    p.end(2)
+    # shared partial page: the truncating sequence gets its own copy, the other keeps the original
+    B = list(range(300, 348))
+    p.begin(3, B)
+    p.extend(3, 48)
+    p.publish(3, B)
+    assert p.begin(4, B + [7]) == 48
+    p.extend(4, 1)
+    before = p.pages(3)
+    cow = p.truncate(4, 40)
+    assert cow is not None and cow[0] == before[2] and cow[1] not in before
+    assert p.pages(4)[2] == cow[1] and p.pages(3) == before
+    assert p.begin(5, B + [9]) == 48               # sequence 3's pages are still registered and intact
+    with pytest.raises(ValueError):
+        p.truncate(4, 1000)
+
+
+def test_stage_decode_is_all_or_nothing():
+    import torch
+    pool = KVPool(3, 16)
+    for sid in (1, 2):
+        pool.begin(sid)
+        pool.extend(sid, 16)                       # both sit on a page boundary; one page is left
+    seq = torch.tensor([1, 2], dtype=torch.int64)
+    pos, slot, ctx = (torch.zeros(2, dtype=torch.int32) for _ in range(3))
+    table = torch.zeros((2, 4), dtype=torch.int32)
+    with pytest.raises(MemoryError):
+        pool.stage_decode(seq.data_ptr(), 2, 4, True, pos.data_ptr(), slot.data_ptr(), ctx.data_ptr(), table.data_ptr())
+    assert pool.length(1) == 16 and pool.length(2) == 16 and pool.free_pages == 1      # nothing grew

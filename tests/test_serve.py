@@ -183,3 +183,122 @@ def test_manifests_and_payout_split(gguf_path):
     assert len(mf.structural_errors(whole)) >= 2
     with pytest.raises(ValueError):
         mf.payout_split(mf.sharded_run_receipt("sha256:m", 32, stages, "mismatch"), 10)
+
+
+# ---------------------------------------------------------------- scheduler: failures stay with their request
+
+class _FakeBackend:
+    """Scripted backend: counts calls, serves arg-max ``(last token + 1) % 50``, fails where told to."""
+    name = "fake"
+
+    def __init__(self, max_context=64, fail_seq=None):
+        from openagents_b200.models.config import TINY_LLAMA
+        self.cfg = TINY_LLAMA.with_(vocab=512)
+        self._max, self.fail_seq = max_context, fail_seq
+        self.open, self.ended, self.batches, self.published = {}, [], [], {}
+        self.last_d2h_bytes = 0
+
+    @property
+    def max_context(self):
+        return self._max
+
+    def begin(self, seq_id, prompt):
+        self.open[seq_id] = 0
+        return 0
+
+    def step(self, seq_ids, new_tokens, params, uniforms):
+        if self.fail_seq is not None and self.fail_seq in seq_ids:
+            raise MemoryError("KV cache is out of pages")
+        self.batches.append(list(seq_ids))
+        for s, t in zip(seq_ids, new_tokens):
+            self.open[s] += len(t)
+        self.last_d2h_bytes = 4 * len(seq_ids)
+        return [(t[-1] + 1) % 50 for t in new_tokens]
+
+    def publish(self, seq_id, tokens):
+        self.published[seq_id] = list(tokens)
+
+    def end(self, seq_id):
+        self.ended.append(seq_id)
+        self.open.pop(seq_id, None)
+
+
+def test_failed_request_does_not_block_the_queue():
+    from openagents_b200.serve.generation import RequestRejected
+    be = _FakeBackend(max_context=32)
+    sch = Scheduler(be, ByteTokenizer(512), max_num_seqs=4, prefill_chunk=64)
+    with pytest.raises(RequestRejected):            # longer than the context window: refused at the door
+        sch.submit(list(range(1, 30)), SamplingParams(max_tokens=8))
+    assert not sch.waiting and sch.stats["rejected"] == 1
+    bad = sch.submit([1, 2, 3], SamplingParams(max_tokens=4))
+    good = sch.submit([4, 5, 6], SamplingParams(max_tokens=4))
+    be.fail_seq = 1                                  # the first sequence the scheduler opens
+    sch.run_until_done([bad, good], max_steps=50)
+    assert bad.finish_reason == "error" and isinstance(bad.error, MemoryError)
+    assert good.finish_reason == "length" and good.output == [7, 8, 9, 10]
+    assert 1 in be.ended and not sch.waiting and not sch.running and sch.stats["errors"] == 1
+    later = sch.submit([9], SamplingParams(max_tokens=2))     # and the scheduler keeps serving
+    sch.run_until_done([later], max_steps=10)
+    assert later.output == [10, 11]
+
+
+def test_prefill_is_batched_and_sessions_publish_their_whole_history():
+    be = _FakeBackend()
+    sch = Scheduler(be, ByteTokenizer(512), max_num_seqs=8, prefill_chunk=64)
+    reqs = [sch.submit([10 + i, 11 + i, 12 + i], SamplingParams(max_tokens=3)) for i in range(4)]
+    sch.step()
+    assert be.batches[0] == [1, 2, 3, 4]             # four prompts shared one forward call
+    assert sch.stats["prefill_seqs_sum"] / sch.stats["prefill_calls"] == 4
+    sch.run_until_done(reqs, max_steps=20)
+    assert sch.stats["batch_size_sum"] / sch.stats["steps"] == 4 and sch.stats["d2h_bytes"] > 0
+    first = sch.submit([1, 2], SamplingParams(max_tokens=2), keep_sequence=True)
+    sch.run_until_done([first])
+    turn2 = sch.submit([30, 31], SamplingParams(max_tokens=2), seq_id=first.seq_id, keep_sequence=True, history=[1, 2, 3])
+    sch.run_until_done([turn2])
+    assert be.published[first.seq_id] == [1, 2, 3, 30, 31]      # earlier turns + the new one, never the new turn alone
+
+
+def test_concurrent_http_requests_share_decode_batches(gguf_path):
+    model = ServedModel("tiny", CpuBackend.from_gguf(gguf_path), None, max_num_seqs=8)
+    state = ServerState([model])
+    httpd = serve(state, "127.0.0.1", 0)
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    base = f"http://127.0.0.1:{httpd.server_address[1]}"
+    out = [None] * 8
+
+    def one(i):
+        body = {"messages": [{"role": "user", "content": f"question number {i}"}], "max_tokens": 64, "temperature": 0, "stream": True}
+        out[i] = _post(base + "/v1/chat/completions", body)
+
+    ts = [threading.Thread(target=one, args=(i,)) for i in range(8)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(timeout=300)
+    httpd.shutdown()
+    assert all(o is not None and o[0] == 200 and b"[DONE]" in o[1] for o in out)
+    s = model.sched.stats
+    assert s["batch_size_sum"] / s["steps"] > 4, s      # the eight streams decoded together, not one after another
+    assert state.ledger.total() > 0 and len(state.ledger.rows) == 8
+    model.close()
+
+
+def test_over_long_prompt_is_rejected_and_server_keeps_working(server):
+    base, state = server
+    long_text = "x" * (state.default.backend.cfg.context + 10)
+    code, raw = _post(base + "/v1/chat/completions", {"messages": [{"role": "user", "content": long_text}], "max_tokens": 4})
+    assert code == 400 and json.loads(raw)["error"]["type"] == "context_length_exceeded"
+    code, raw = _post(base + "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3, "temperature": 0})
+    assert code == 200 and json.loads(raw)["usage"]["completion_tokens"] <= 3
+
+
+def test_sampling_on_host_matches_its_definition():
+    from openagents_b200.serve.backend import sample_row
+    logits = torch.tensor([0.1, 3.0, 2.5, -1.0, 2.9])
+    assert sample_row(logits, SamplingParams(temperature=0.0), 0.7) == 1
+    p = SamplingParams(temperature=1.0, top_k=3, top_p=1.0)
+    probs = torch.softmax(torch.tensor([3.0, 2.9, 2.5]), 0)          # candidates 1, 4, 2 in that order
+    assert sample_row(logits, p, 0.0) == 1
+    assert sample_row(logits, p, float(probs[0]) + 1e-3) == 4
+    assert sample_row(logits, p, 0.999) == 2
+    assert sample_row(logits, SamplingParams(temperature=1.0, top_k=3, top_p=0.2), 0.999) == 1    # top-p keeps only the best

@@ -58,4 +58,18 @@ def test_noalloc_sampler_rejects_oversize_and_bad_arguments():
     assert f(x.data_ptr(), 64, 128256, 1.0, 4, 1.0, x.data_ptr(), o.data_ptr(), st) == -1     # 8.2M floats > 2M
     assert f(x.data_ptr(), 1, 8, 1.0, 0, 1.0, x.data_ptr(), o.data_ptr(), st) == -2
     assert f(x.data_ptr(), 0, 8, 1.0, 1, 1.0, x.data_ptr(), o.data_ptr(), st) == -2
+    assert f(x.data_ptr(), 1, 8, 1.0, 9, 1.0, x.data_ptr(), o.data_ptr(), st) == -2            # more candidates than entries
+
+
+def test_noalloc_sampler_gives_a_defined_id_for_rows_without_finite_logits():
+    f = _fn()
+    V = 4096
+    logits = torch.full((2, V), float("nan"), device="cuda")
+    logits[1] = float("-inf")
+    logits[1, 77] = 0.5                      # one finite entry: it must win whatever top_k says
+    u = torch.rand(2, device="cuda")
+    out = torch.full((2,), -1, dtype=torch.int32, device="cuda")
+    rc = f(logits.data_ptr(), 2, V, 1.0, 8, 1.0, u.data_ptr(), out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0 and out.tolist() == [0, 77]
     torch.cuda.synchronize()
