@@ -346,7 +346,10 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, in
 // that issues the MMAs spends about 540 cycles per K block on a narrow tile (measured with clock64 stamps: some 55
 // per tcgen05.mma, the rest on the barrier wait, the fence and the commit), more than the tensor core needs for
 // four narrow MMAs (220 cycles at N = 64), and the producer thread 420; fewer, larger stages halve that overhead.
-template <int BN, int STAGES, int AROWS, int KSUB>
+// MN = true: both operands are given MN-major (A as [K][M], B as [K][N], row-major): the form of dW = dy^T x, where dy
+// and x are read as they lie in memory instead of through transposed copies.  A stage then holds, per operand,
+// 64-column blocks of [64 k rows][128 bytes] (one TMA box each), which the MMA reads through MN-major descriptors.
+template <int BN, int STAGES, int AROWS, int KSUB, bool MN = false>
 __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
                                                          const __grid_constant__ CUtensorMap tmB,
                                                          const GemmEpi epi, int M, int N, int K, int splits,
@@ -452,17 +455,26 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(smem_u32(empty + s), ph ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(smem_u32(full + s), A_BYTES + B_BYTES);
+          if constexpr (MN) {                   // coordinates are (mn, k): 64-column blocks of 64 k rows
 #pragma unroll
-          for (int u = 0; u < KSUB; u++) {      // a block past the end of K is filled with zeros by the TMA unit
-            tma_load_2d(smem_u32(sA + s * A_BYTES + u * A_SUB), &tmA, smem_u32(full + s), kb * BKS + u * BK, m0);
-            tma_load_2d(smem_u32(sB + s * B_BYTES + u * B_SUB), &tmB, smem_u32(full + s), kb * BKS + u * BK, b_row);
+            for (int hb = 0; hb < BM / 64; hb++)
+              tma_load_2d(smem_u32(sA + s * A_BYTES + hb * 8192), &tmA, smem_u32(full + s), m0 + hb * 64, kb * BK);
+#pragma unroll
+            for (int hb = 0; hb < BN / 64; hb++)
+              tma_load_2d(smem_u32(sB + s * B_BYTES + hb * 8192), &tmB, smem_u32(full + s), b_row + hb * 64, kb * BK);
+          } else {
+#pragma unroll
+            for (int u = 0; u < KSUB; u++) {      // a block past the end of K is filled with zeros by the TMA unit
+              tma_load_2d(smem_u32(sA + s * A_BYTES + u * A_SUB), &tmA, smem_u32(full + s), kb * BKS + u * BK, m0);
+              tma_load_2d(smem_u32(sB + s * B_BYTES + u * B_SUB), &tmB, smem_u32(full + s), kb * BKS + u * BK, b_row);
+            }
           }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = idesc_bf16(BM, BN);
+      constexpr uint32_t idesc = idesc_bf16(BM, BN) | (MN ? ((1u << 15) | (1u << 16)) : 0u);   // bits 15 / 16: A / B MN-major
       uint32_t it = 0, tcount = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < n_tiles && ok; item += gridDim.x) {
@@ -478,13 +490,22 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(smem_u32(full + s), ph, abort_flag)) { ok = false; break; }
           tc_fence_after();
-#pragma unroll
-          for (int u = 0; u < KSUB; u++) {
-            const uint64_t ad = smem_desc_sw128(smem_u32(sA + s * A_BYTES + u * A_SUB));
-            const uint64_t bd = smem_desc_sw128(smem_u32(sB + s * B_BYTES + u * B_SUB));
+          if constexpr (MN) {
+            // 64-column blocks 8192 bytes apart, 8-row groups along K 1024 bytes apart; a K step of 16 rows is 2048 bytes on
+            const uint64_t ad = smem_desc_sw128_mn(smem_u32(sA + s * A_BYTES), 8192);
+            const uint64_t bd = smem_desc_sw128_mn(smem_u32(sB + s * B_BYTES), 8192);
 #pragma unroll
             for (int k = 0; k < BK / 16; k++)
-              umma_bf16(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb != kb0 || u != 0 || k != 0) ? 1u : 0u);
+              umma_bf16(d_tmem, ad + 128 * k, bd + 128 * k, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int u = 0; u < KSUB; u++) {
+              const uint64_t ad = smem_desc_sw128(smem_u32(sA + s * A_BYTES + u * A_SUB));
+              const uint64_t bd = smem_desc_sw128(smem_u32(sB + s * B_BYTES + u * B_SUB));
+#pragma unroll
+              for (int k = 0; k < BK / 16; k++)
+                umma_bf16(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb != kb0 || u != 0 || k != 0) ? 1u : 0u);
+            }
           }
           umma_commit(smem_u32(empty + s));
         }
@@ -741,7 +762,7 @@ static bool gemm_deep_enabled() {      // B200_GEMM_DEEP=0: measurement aid, the
   return on == 1;
 }
 
-template <int BN, int STAGES, int AROWS = 128, int KSUB = 1>
+template <int BN, int STAGES, int AROWS = 128, int KSUB = 1, bool MN = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpi& e, int M, int N, int K,
                        int splits, int* status, cudaStream_t st) {
   // AROWS = 64: no tile list (never grouped); the last stage's 128-row operand read runs 8 KB past its A tile and
@@ -749,7 +770,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmE
   constexpr size_t smem = 1024 + (size_t)STAGES * KSUB * (AROWS * BK * 2 + BN * BK * 2) + (2 * STAGES + 6) * 8 + 4 * 32 * 32 * 4 +
                           (AROWS == 128 ? kMaxLiveTiles * 4 : 0);
   static_assert(smem <= 232448, "shared memory per CTA");
-  auto kern = gemm_bf16_kernel<BN, STAGES, AROWS, KSUB>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, AROWS, KSUB, MN>;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -768,8 +789,26 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
                             void* out_bf16, int ldc, const float* bias, const float* resid_f32,
                             const void* resid_bf16, int act, int accumulate, int tile_n, int split_k, int* status,
                             int sym_mode, const SymTable* sym, size_t sym_off, int rows_per_rank, int wait_ready,
-                            int ag_rows_per_rank, int ag_epoch, cudaStream_t st) {
-  if (M <= 0 || N <= 0 || K <= 0 || (lda % 8) || (ldb % 8) || (K % 8)) return B200_ERR_BAD_ARG;
+                            int ag_rows_per_rank, int ag_epoch, int mn_major, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0 || (lda % 8) || (ldb % 8) || (!mn_major && (K % 8))) return B200_ERR_BAD_ARG;
+  if (mn_major) {
+    // D[M][N] = sum_k A[k][m] * B[k][n]: A is [K][M] (row stride lda), B is [K][N] (row stride ldb).  Plain epilogues only.
+    if (sym_mode != SYM_NONE || ag_rows_per_rank || tile_n < 0 || split_k > 1 || act == ACT_SWIGLU_PAIR || (M % 8) || (N % 8))
+      return B200_ERR_BAD_ARG;
+    if ((out_bf16 && (ldc % 8)) || (out_f32 && (ldc % 4)) || (N % 4)) return B200_ERR_BAD_ARG;
+    CUtensorMap ta, tb;
+    int rc = make_tmap_2d(&ta, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, 64, true);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tb, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, 64, true);
+    if (rc) return rc;
+    GemmEpi e = {};
+    e.out_f32 = out_f32; e.out_bf16 = (__nv_bfloat16*)out_bf16; e.bias = bias; e.resid_f32 = resid_f32;
+    e.resid_bf16 = (const __nv_bfloat16*)resid_bf16; e.ldc = ldc; e.act = act; e.accumulate = accumulate; e.rows_per_rank = 1;
+    const long t256 = (long)((N + 255) / 256) * ((M + 127) / 128);
+    if ((tile_n == 256 || (tile_n == 0 && N >= 256 && t256 >= 148)))
+      return launch_gemm<256, 4, 128, 1, true>(ta, tb, e, M, N, K, 1, status, st);
+    return launch_gemm<128, 6, 128, 1, true>(ta, tb, e, M, N, K, 1, status, st);
+  }
   if ((out_bf16 && (ldc % 8)) || (out_f32 && (ldc % 4))) return B200_ERR_BAD_ARG;
   if (N % 4) return B200_ERR_BAD_ARG;
   if (sym_mode != SYM_NONE && (!sym || (ldc % 4) || (sym_off % 16))) return B200_ERR_BAD_ARG;

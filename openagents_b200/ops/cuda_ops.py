@@ -39,7 +39,7 @@ _SIGS = {
     "b200_attn_prefill": [_P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
     "b200_attn_prefill_tc05": [_P, _P, _P, _P, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
     "b200_gemm_bf16": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int,
-                       _P, c_int, _P, c_size_t, c_int, c_int, c_int, c_int, _P],
+                       _P, c_int, _P, c_size_t, c_int, c_int, c_int, c_int, c_int, _P],
     "b200_moe_gemm": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P, c_int, _P, _P, _P, c_size_t, _P, _P],
     "b200_moe_route_dispatch": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_size_t, c_size_t, c_size_t, c_size_t,
                                 _P, _P, _P, _P, _P],
@@ -209,12 +209,15 @@ def attn_prefill_tc05(q16, kc, vc, page_table, q_start, q_len, ctx_len, n_seqs, 
 
 def gemm_bf16(A, B, M, N, K, lda=None, ldb=None, out_f32=None, out_bf16=None, ldc=None, bias=None, resid_f32=None,
               resid_bf16=None, act=ACT_NONE, accumulate=False, tile_n=0, status=None, sym_mode=SYM_NONE, sym=None,
-              sym_off=0, rows_per_rank=0, split_k=0, wait_ready=False, ag_rows_per_rank=0, ag_epoch=0):
+              sym_off=0, rows_per_rank=0, split_k=0, wait_ready=False, ag_rows_per_rank=0, ag_epoch=0, mn_major=False):
     """D[M][N] = A[M][K] @ B[N][K]^T with fused epilogue (see ``gemm_tc05.cu``).  ``ag_rows_per_rank`` > 0: the rows
-    of A are all-gathered by push (``rmsnorm_allgather``) and each tile waits for its owners' counter to reach ``ag_epoch``."""
-    _check(lib().b200_gemm_bf16(_p(A), _p(B), M, N, K, lda or K, ldb or K, _p(out_f32), _p(out_bf16), ldc or N,
+    of A are all-gathered by push (``rmsnorm_allgather``) and each tile waits for its owners' counter to reach ``ag_epoch``.
+    ``mn_major``: the operands are given as A [K][M] and B [K][N] (row strides ``lda`` / ``ldb``), i.e. D = A^T B: the weight
+    gradient dW = dy^T x straight from dy and x, without transposed copies."""
+    _check(lib().b200_gemm_bf16(_p(A), _p(B), M, N, K, lda or (M if mn_major else K), ldb or (N if mn_major else K), _p(out_f32), _p(out_bf16), ldc or N,
                                 _p(bias), _p(resid_f32), _p(resid_bf16), act, int(accumulate), tile_n, split_k, _p(status),
-                                sym_mode, _sym(sym), sym_off, rows_per_rank, int(wait_ready), ag_rows_per_rank, ag_epoch, _st()), "gemm_bf16")
+                                sym_mode, _sym(sym), sym_off, rows_per_rank, int(wait_ready), ag_rows_per_rank, ag_epoch,
+                                int(mn_major), _st()), "gemm_bf16")
 
 
 def set_pdl(on: bool):

@@ -19,6 +19,8 @@ _SIGS = {
     "b200_gelu_bwd": [_P, _P, c_size_t, _P],
     "b200_bias_grad": [_P, _P, c_int, c_int, _P],
     "b200_ce_fused": [_P, _P, _P, c_float, c_int, c_int, c_int, _P],
+    "b200_attn_train_fwd": [_P, _P, _P, c_int, c_int, c_int, c_int, _P],
+    "b200_attn_train_bwd": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "b200_zero_reduce_norm": [_P, c_size_t, c_size_t, c_size_t, _P, _P, _P],
     "b200_zero_adamw_gather": [_P, c_size_t, c_size_t, c_size_t, _P, _P, _P, _P, _P, c_float, c_float, c_float, c_float,
                                c_float, c_float, c_float, c_float, c_size_t, _P],
@@ -72,6 +74,17 @@ def bias_grad(dy, gb):
 def ce_fused(logits, targets, loss, scale, V):
     M, ldl = logits.shape
     _check(lib().b200_ce_fused(_p(logits), _p(targets), _p(loss), scale, M, V, ldl, _st()), "ce_fused")
+
+
+def attn_train_fwd(qkv, o, lse, B, T, H, hd):
+    """Causal attention forward on the fused projection output ``qkv`` [B*T, 3*H*hd] bf16 (read in place) ->
+    ``o`` [B*T, H*hd] bf16 and ``lse`` [B, H, T] fp32 (see ``attn_train.cu``)."""
+    _check(lib().b200_attn_train_fwd(_p(qkv), _p(o), _p(lse), B, T, H, hd, _st()), "attn_train_fwd")
+
+
+def attn_train_bwd(qkv, o, d_o, lse, dsum, dqkv, B, T, H, hd):
+    """Backward of :func:`attn_train_fwd`: ``dqkv`` [B*T, 3*H*hd] bf16 from ``d_o``; ``dsum`` [B, H, T] fp32 is working space."""
+    _check(lib().b200_attn_train_bwd(_p(qkv), _p(o), _p(d_o), _p(lse), _p(dsum), _p(dqkv), B, T, H, hd, _st()), "attn_train_bwd")
 
 
 def zero_reduce_norm(table, grad_off, lo, n, gshard, norm2):

@@ -8,9 +8,11 @@ order, so "decay or not" is a single index comparison inside the optimizer kerne
 Linear layers run on the tcgen05 GEMM in its K-major x K-major form:
     forward   y  = x  W^T         A = x [M,K],     B = W  [N,K]
     backward  dx = dy W           A = dy [M,N],    B = W^T [K,N]   (transposed copy, refreshed per step)
-              dW += dy^T x        A = dy^T [N,M],  B = x^T [K,M]   (accumulated in fp32 in the epilogue)
-The attention core currently calls torch's fused scaled-dot-product attention for its forward and
-backward inside training; the serving path uses this package's own attention kernels.
+              dW += dy^T x        both operands MN-major: dy [M,N] and x [M,K] are read as they lie in memory
+                                  (the reduction runs over their rows); accumulated in fp32 in the epilogue
+The attention core is this package's flash-attention kernel pair (``csrc/kernels/attn_train.cu``): the forward reads
+the fused QKV projection in place and saves one log-sum-exp per row, the backward writes dQ, dK and dV straight into
+the gradient of that projection.  No autograd graph is built anywhere in this file.
 """
 from __future__ import annotations
 
@@ -18,7 +20,6 @@ import math
 from dataclasses import dataclass
 
 import torch
-import torch.nn.functional as F
 
 from ..models.config import ModelConfig
 from ..models.weights import TensorSpec, init_tensor, tensor_specs
@@ -97,6 +98,7 @@ class GPT2Model:
         L = cfg.n_layers
         self.act = [dict(x_in=torch.empty((M, d), **bf), ln1=torch.empty((M, d), **bf), mean1=torch.empty(M, **f32),
                          rstd1=torch.empty(M, **f32), qkv=torch.empty((M, 3 * d), **bf), attn=torch.empty((M, d), **bf),
+                         lse=torch.empty((micro_batch, cfg.n_heads, seq_len), **f32),
                          x_mid=torch.empty((M, d), **bf), ln2=torch.empty((M, d), **bf), mean2=torch.empty(M, **f32),
                          rstd2=torch.empty(M, **f32), h=torch.empty((M, f), **bf), a=torch.empty((M, f), **bf))
                     for _ in range(L)]
@@ -110,8 +112,8 @@ class GPT2Model:
         self.d_a = torch.empty((M, f), **bf)
         self.d_d = torch.empty((M, d), **bf)
         self.d_qkv = torch.empty((M, 3 * d), **bf)
-        self.tA = torch.empty(max(f, 3 * d, self.Vp) * M, **bf)     # transposed dy
-        self.tB = torch.empty(max(max(f, 3 * d) * M, d * self.Vp), **bf)   # transposed activation / tied embedding
+        self.dsum = torch.empty((micro_batch, cfg.n_heads, seq_len), **f32)     # attention backward: rowsum(dO * O)
+        self.tB = torch.empty(d * self.Vp, **bf)   # transposed tied embedding (dx of the LM head)
         self.kernel_launches = 0
 
     # ---- helpers
@@ -137,12 +139,7 @@ class GPT2Model:
         W = self.p[wname]
         N, K = W.shape
         M = dy.shape[0]
-        dyT = self.tA[: N * M].view(N, M)
-        xT = self.tB[: K * M].view(K, M)
-        ops.transpose_bf16(dy, dyT)
-        ops.transpose_bf16(x, xT)
-        self.kernel_launches += 2
-        self._gemm(dyT, xT, N, K, M, out_f32=self.g[wname], accumulate=True)
+        self._gemm(dy, x, N, K, M, lda=dy.stride(0), ldb=x.stride(0), out_f32=self.g[wname], accumulate=True, mn_major=True)
         if bname:
             tops.bias_grad(dy, self.g[bname])
             self.kernel_launches += 1
@@ -158,19 +155,13 @@ class GPT2Model:
         x = self.act[0]["x_in"]
         tops.embed_fwd(ids, self.p["token_embd.weight"], self.p["position_embd.weight"], x, T)
         self.kernel_launches += 1
-        attn_saved = []
         for i, a in enumerate(self.act):
             pre = f"blk.{i}."
             x = a["x_in"]
             tops.layernorm_fwd(x, self.vec[pre + "attn_norm.weight"], self.vec[pre + "attn_norm.bias"], cfg.norm_eps,
                                a["ln1"], a["mean1"], a["rstd1"])
             self._linear_fwd(a["ln1"], pre + "attn_qkv.weight", pre + "attn_qkv.bias", a["qkv"])
-            qkv = a["qkv"].view(self.B, T, 3, H, hd).permute(2, 0, 3, 1, 4)       # [3, B, H, T, hd]
-            q, k, v = (t.detach().requires_grad_(True) for t in (qkv[0], qkv[1], qkv[2]))
-            with torch.enable_grad():
-                o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-            attn_saved.append((q, k, v, o))
-            a["attn"].view(self.B, T, H, hd).copy_(o.detach().permute(0, 2, 1, 3))
+            tops.attn_train_fwd(a["qkv"], a["attn"], a["lse"], self.B, T, H, hd)
             self._linear_fwd(a["attn"], pre + "attn_output.weight", pre + "attn_output.bias", a["x_mid"], resid=x)
             tops.layernorm_fwd(a["x_mid"], self.vec[pre + "ffn_norm.weight"], self.vec[pre + "ffn_norm.bias"],
                                cfg.norm_eps, a["ln2"], a["mean2"], a["rstd2"])
@@ -190,11 +181,7 @@ class GPT2Model:
         # ---- backward
         dlog = self.logits
         # tied embedding: d wte += dlogits^T lnf ; d lnf = dlogits wte
-        dlT = self.tA[: self.Vp * M].view(self.Vp, M)
-        lnfT = self.tB[: d * M].view(d, M)
-        ops.transpose_bf16(dlog, dlT)
-        ops.transpose_bf16(self.lnf, lnfT)
-        self._gemm(dlT, lnfT, self.Vp, d, M, out_f32=self.g["token_embd.weight"], accumulate=True)
+        self._gemm(dlog, self.lnf, self.Vp, d, M, lda=self.Vp, ldb=d, out_f32=self.g["token_embd.weight"], accumulate=True, mn_major=True)
         wteT = self.tB[: d * self.Vp].view(d, self.Vp)
         ops.transpose_bf16(wte, wteT)
         self._gemm(dlog, wteT, M, d, self.Vp, out_bf16=self.d_d)
@@ -212,18 +199,11 @@ class GPT2Model:
                                True, self.g[pre + "ffn_norm.weight"], self.g[pre + "ffn_norm.bias"])
             # attention branch: x_mid = x_in + proj(attn(qkv(ln1(x_in))))
             self._linear_bwd(self.dx, a["attn"], pre + "attn_output.weight", pre + "attn_output.bias", self.d_d)
-            q, k, v, o = attn_saved[i]
-            do = self.d_d.view(self.B, T, H, hd).permute(0, 2, 1, 3)
-            dq, dk, dv = torch.autograd.grad(o, (q, k, v), do)
-            dqkv = self.d_qkv.view(self.B, T, 3, H, hd)
-            dqkv[:, :, 0].copy_(dq.permute(0, 2, 1, 3))
-            dqkv[:, :, 1].copy_(dk.permute(0, 2, 1, 3))
-            dqkv[:, :, 2].copy_(dv.permute(0, 2, 1, 3))
+            tops.attn_train_bwd(a["qkv"], a["attn"], self.d_d, a["lse"], self.dsum, self.d_qkv, self.B, T, H, hd)
             self._linear_bwd(self.d_qkv, a["ln1"], pre + "attn_qkv.weight", pre + "attn_qkv.bias", self.d_d)
             tops.layernorm_bwd(self.d_d, a["x_in"], self.vec[pre + "attn_norm.weight"], a["mean1"], a["rstd1"], self.dx,
                                True, self.g[pre + "attn_norm.weight"], self.g[pre + "attn_norm.bias"])
-            attn_saved[i] = None
-            self.kernel_launches += 3
+            self.kernel_launches += 6
         tops.embed_bwd(ids, self.dx, self.g["token_embd.weight"], self.g["position_embd.weight"], T)
         self.kernel_launches += 1
         return loss

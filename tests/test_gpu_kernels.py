@@ -597,6 +597,65 @@ def test_slot_allreduce_single_rank():
     assert heap.status() == (0, 0)
 
 
+@pytest.mark.parametrize("B,T,H", [(2, 128, 3), (1, 320, 2), (3, 64, 1)])
+def test_attn_train_forward_backward(B, T, H):
+    """Training attention (causal, head size 64) against fp32 softmax attention and its autograd gradients, reading the
+    fused QKV projection in place; run twice: the kernels use no atomics, so the bits must repeat."""
+    from openagents_b200.ops import train_ops as tops
+    hd, d = 64, H * 64
+    qkv = (_randn(B * T, 3 * d, seed=70) * 0.8).bfloat16()
+    d_o = (_randn(B * T, d, seed=71) * 0.5).bfloat16()
+    o = torch.zeros((B * T, d), dtype=torch.bfloat16, device=DEV)
+    lse = torch.zeros((B, H, T), device=DEV)
+    tops.attn_train_fwd(qkv, o, lse, B, T, H, hd)
+    q, k, v = (qkv.float().view(B, T, 3, H, hd)[:, :, i].permute(0, 2, 1, 3).clone().requires_grad_(True) for i in range(3))
+    s = (q @ k.transpose(-1, -2)) / math.sqrt(hd)
+    s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool, device=DEV), 1), float("-inf"))
+    ref = torch.softmax(s, -1) @ v                                     # [B, H, T, hd]
+    got = o.float().view(B, T, H, hd).permute(0, 2, 1, 3)
+    assert torch.allclose(got, ref, atol=2e-2, rtol=2e-2), (got - ref).abs().max().item()
+    assert torch.allclose(lse * math.log(2.0), torch.logsumexp(s, -1), atol=2e-3, rtol=1e-3)
+    ref.backward(d_o.float().view(B, T, H, hd).permute(0, 2, 1, 3))
+    dqkv = torch.zeros_like(qkv)
+    dsum = torch.empty((B, H, T), device=DEV)
+    tops.attn_train_bwd(qkv, o, d_o, lse, dsum, dqkv, B, T, H, hd)
+    g = dqkv.float().view(B, T, 3, H, hd)
+    for i, r in enumerate((q.grad, k.grad, v.grad)):
+        mine = g[:, :, i].permute(0, 2, 1, 3)
+        rel = (mine - r).norm().item() / r.norm().item()
+        assert rel < 2e-2, (i, rel)
+    again = torch.zeros_like(qkv)
+    o2 = torch.zeros_like(o)
+    tops.attn_train_fwd(qkv, o2, lse, B, T, H, hd)
+    tops.attn_train_bwd(qkv, o2, d_o, lse, dsum, again, B, T, H, hd)
+    assert torch.equal(o, o2) and torch.equal(dqkv, again)
+
+
+@pytest.mark.parametrize("M,N,K", [(2304, 768, 2048), (200, 136, 100), (768, 3072, 4096), (50304, 768, 512)])
+def test_gemm_mn_major_operands(M, N, K):
+    """D = A^T B with both operands read as they lie in memory ([K][M] and [K][N]): the weight-gradient GEMM dW = dy^T x.
+    Plain store, fp32 accumulation on top of existing contents, a K that is not a multiple of the 64-row K block."""
+    ops = _ops()
+    A = _randn(K, M, seed=90).bfloat16()
+    B = _randn(K, N, seed=91).bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ref = A.float().t() @ B.float()
+    tol = 4e-3 * math.sqrt(K) + 1e-3
+    out = torch.zeros((M, N), device=DEV)
+    ops.gemm_bf16(A, B, M, N, K, out_f32=out, mn_major=True, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert (out - ref).abs().max().item() < tol, (out - ref).abs().max().item()
+    acc = torch.full((M, N), 0.5, device=DEV)
+    ops.gemm_bf16(A, B, M, N, K, out_f32=acc, accumulate=True, mn_major=True, status=status)
+    assert (acc - ref - 0.5).abs().max().item() < tol
+    # against the K-major path on explicit transposes
+    out2 = torch.zeros((M, N), device=DEV)
+    ops.gemm_bf16(A.t().contiguous(), B.t().contiguous(), M, N, (K + 7) // 8 * 8 if K % 8 == 0 else K, out_f32=out2, status=status) if K % 8 == 0 else None
+    if K % 8 == 0:
+        assert (out2 - out).abs().max().item() < tol
+
+
 def test_stream_triad_probe():
     """The bandwidth probe's triad kernel computes a = b + 3 c (checked inside) and reports a plausible rate."""
     from openagents_b200.utils.bandwidth_probe import stream_triad_gbs

@@ -205,7 +205,7 @@ def _dp_trainer(rank, world, ckpt_dir):
     from openagents_b200.models.config import GPT2_SMALL
     from openagents_b200.train.trainer import TrainConfig, Trainer, synthetic_batch
     dev = torch.device("cuda", rank)
-    m = GPT2_SMALL.with_(n_layers=2, d_model=128, n_heads=4, n_kv_heads=4, head_dim=32, ffn=512, vocab=1000, context=64)
+    m = GPT2_SMALL.with_(n_layers=2, d_model=128, n_heads=2, n_kv_heads=2, head_dim=64, ffn=512, vocab=1000, context=64)
     cfg = TrainConfig(model=m, global_batch=8, micro_batch=4, seq_len=64, lr=1e-3)
     tr = Trainer(cfg, dev, rank, world)
     # the same global batch, split by rank here and taken whole by a one-rank trainer below
@@ -238,7 +238,7 @@ def test_dp2_trainer_matches_single_rank(tmp_path):
     d = str(tmp_path / "ck")
     _run(_dp_trainer, 2, d)
     res = torch.load(d + "/dp_result.pt")
-    m = GPT2_SMALL.with_(n_layers=2, d_model=128, n_heads=4, n_kv_heads=4, head_dim=32, ffn=512, vocab=1000, context=64)
+    m = GPT2_SMALL.with_(n_layers=2, d_model=128, n_heads=2, n_kv_heads=2, head_dim=64, ffn=512, vocab=1000, context=64)
     cfg = TrainConfig(model=m, global_batch=8, micro_batch=4, seq_len=64, lr=1e-3)
     tr = Trainer(cfg, "cuda:0")
     tok, tgt = synthetic_batch(cfg, 2, 0, 0, "cuda:0")

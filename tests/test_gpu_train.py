@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 def _small_cfg():
     from openagents_b200.train.trainer import TrainConfig
-    m = GPT2_SMALL.with_(n_layers=2, d_model=128, n_heads=4, n_kv_heads=4, head_dim=32, ffn=512, vocab=1000, context=64)
+    m = GPT2_SMALL.with_(n_layers=2, d_model=128, n_heads=2, n_kv_heads=2, head_dim=64, ffn=512, vocab=1000, context=64)
     return TrainConfig(model=m, global_batch=4, micro_batch=4, seq_len=64, lr=1e-3, weight_decay=0.1, grad_clip=1.0)
 
 
