@@ -23,9 +23,11 @@ struct SymControl {               // first kSymControlBytes of every heap
   int ticket[kSymChannels];       // CTAs of the current launch that have finished (local)
   int status;                     // last error (B200Status), 0 if none
   int timeouts;                   // number of waits that ran out
-  uint32_t slot_seq;              // slot all-reduces this rank has issued so far (local; see sym_slots_*)
   uint32_t merge_seq;             // arg-max merges this rank has issued so far (local)
+  uint32_t row_seq[64];           // per row of the slot all-reduce: all-reduces this rank has done on that row (local)
+  uint32_t row_flag[64];          // per row: pushes that have landed here, one per rank and all-reduce (written by peers)
 };
+constexpr int kSymSlotRows = 64;
 
 struct SymTable {
   int world, rank, use_mc;
@@ -272,46 +274,41 @@ __device__ __forceinline__ bool sym_wait_rows(const SymTable& T, int owner, uint
 }
 
 // ---- one-shot all-reduce through per-rank slots -------------------------------------------------
-// Decode-time row-parallel projections (a few tokens to a batch of 64) do not add into a shared tensor:
-// every rank STORES its partial result into its own slot of a [2][world][rows][d] fp32 tensor on every
-// rank (multimem.st / peer stores) and bumps flag kSymSlotCh0 + rank everywhere; the kernel that needs
-// the sum (the next RMSNorm) waits for the world flags and adds the slots up in rank order, so every
-// replica computes bit-identical sums.  Nothing waits inside the producer, there is no barrier and no
-// "ready" handshake: slot parity alternates with the sequence number, and a rank can only start writing
-// parity p again after it has consumed the all-reduce in between, which every peer contributed to after
-// it had finished reading parity p.  The sequence number lives in device memory (slot_seq) and is
-// advanced by the producer's last CTA, so the scheme replays unchanged inside a CUDA graph.
-constexpr int kSymSlotCh0 = 16;    // channels 16 .. 16 + kMaxRanks - 1
-constexpr int kSymMergeCh0 = 24;   // channels 24 .. 24 + kMaxRanks - 1 (arg-max merge, same scheme)
+// Decode-time row-parallel projections (a few tokens to a batch of 64) leave their partial result in LOCAL memory,
+// at full single-GPU speed; the kernel that needs the sum (the RMSNorm that follows) is the all-reduce: its CTA for
+// row t pushes this rank's partial row into slot (parity, rank, t) of a [2][world][rows][d] fp32 tensor on every rank
+// (multimem.st / peer stores, 16 bytes per lane), raises row_flag[t] everywhere with one system-scope release,
+// waits until the world has done the same, and adds the slots up in rank order, so every replica computes
+// bit-identical sums.  There is no barrier, no cross-CTA ticket and no "ready" handshake: rows are independent, the
+// sequence number of a row lives in device memory (so the scheme replays unchanged inside a CUDA graph), slot parity
+// alternates with it, and a rank can only write parity p of a row again after it has consumed the all-reduce in
+// between, to which every peer contributed after it had finished reading parity p.
+constexpr int kSymMergeCh0 = 24;   // flag channels 24 .. 24 + kMaxRanks - 1: arg-max merge
 
-// Sequence number of the slot all-reduce this kernel is producing (read after the dependency wait).
-__device__ __forceinline__ uint32_t sym_slots_next_seq(const SymTable& T) {
-  return *(volatile uint32_t*)&sym_ctl(T, T.rank)->slot_seq + 1u;
+// Thread 0 of the CTA that owns row t, after a CTA barrier that follows the CTA's pushes: publish them.
+__device__ __forceinline__ void sym_row_signal(const SymTable& T, int t) {
+  const size_t off = offsetof(SymControl, row_flag) + 4 * (size_t)t;
+  if (T.use_mc) {
+    asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(T.mc_base + off), "r"(1u) : "memory");
+  } else {
+    for (int p = 0; p < T.world; p++)
+      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(T.base[p] + off), "r"(1u) : "memory");
+  }
 }
-// Sequence number of the latest completed producer kernel on this rank (what a consumer waits for).
-__device__ __forceinline__ uint32_t sym_slots_cur_seq(const SymTable& T) {
-  return *(volatile uint32_t*)&sym_ctl(T, T.rank)->slot_seq;
-}
-// Call from every thread of every CTA at the end of the producing kernel.  Each CTA's stores are ordered
-// before its ticket by a system-scope fence; the CTA that takes the last ticket advances the sequence
-// number and raises this rank's flag on every rank.
-__device__ __forceinline__ void sym_slots_signal(const SymTable& T, int n_ctas) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    SymControl* me = sym_ctl(T, T.rank);
-    __threadfence_system();
-    const int done = atomicAdd(&me->ticket[kSymSlotCh0], 1);
-    if (done == n_ctas - 1) {
-      me->ticket[kSymSlotCh0] = 0;
-      me->slot_seq = me->slot_seq + 1u;
-      __threadfence_system();
-      const size_t off = offsetof(SymControl, flag) + 4 * (kSymSlotCh0 + T.rank);
-      if (T.use_mc) {
-        asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(T.mc_base + off), "r"(1u) : "memory");
-      } else {
-        for (int p = 0; p < T.world; p++)
-          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(T.base[p] + off), "r"(1u) : "memory");
-      }
+// One thread: wait until every rank's push number `seq` of row t has landed here.  Returns false (and records the
+// time-out) if the wait ran out.
+__device__ __forceinline__ bool sym_row_wait(const SymTable& T, int t, uint32_t seq) {
+  SymControl* me = sym_ctl(T, T.rank);
+  const uint32_t target = (uint32_t)T.world * seq;
+  const unsigned long long t0 = sym_now_ns();
+  for (uint32_t spin = 0;; ++spin) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(&me->row_flag[t]) : "memory");
+    if ((int32_t)(v - target) >= 0) return true;
+    if ((spin & 63u) == 63u && sym_now_ns() - t0 > T.wait_ns) {
+      me->status = (int)B200_ERR_TIMEOUT_PEER;
+      atomicAdd(&me->timeouts, 1);
+      return false;
     }
   }
 }

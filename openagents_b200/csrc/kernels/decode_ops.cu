@@ -93,16 +93,17 @@ B200_API int b200_embedding(const int* ids, float* out, int T, int D, int type, 
 constexpr int kRmsRegs = 8;
 // sym_mode 1: tensor parallel, all-reduce form: x is replicated in the symmetric heap and peers add into it; the kernel
 //             ends by telling them that this rank has finished reading (see sym_signal_ready).
-// sym_mode 2: tensor parallel, slot form: the row-parallel projection before this norm left every rank's partial
-//             result in per-rank slots (see sym_slots_* in sym.cuh).  The kernel waits for the world flags, adds the
-//             slots to x in rank order (x <- x + sum, written back: x is this rank's private replica) and normalises
-//             the sum.  This is the consumer half of the all-reduce.
+// sym_mode 2: tensor parallel, slot form: this kernel IS the all-reduce.  The row-parallel projection before it left
+//             this rank's partial result in `part` (local, fp32 [T][D]).  The CTA of row t pushes that row into this
+//             rank's slot on every rank, raises the row's flag, waits for the world's pushes, adds the slots to x in
+//             rank order (x <- x + sum, written back: x is this rank's private replica) and normalises the sum.  It
+//             leaves its row of `part` zeroed, because the projection accumulates into it (K splits).  See sym.cuh.
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ g, float eps,
                                                        int D, int8_t* __restrict__ xq, float* __restrict__ xd,
                                                        float* __restrict__ xs16, __nv_bfloat16* __restrict__ hb,
                                                        float* __restrict__ hf, const SymTable sym, int sym_mode,
                                                        float4* __restrict__ zero, int zero_n4, size_t slot_off,
-                                                       int slot_rows) {
+                                                       int slot_rows, float* __restrict__ part) {
   __shared__ float red[32];
   const int t = blockIdx.x;
   float* xr = x + (size_t)t * D;
@@ -121,14 +122,28 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, co
   size_t slot_stride = 0;
   if (sym_mode == 2) {
     __shared__ uint32_t s_seq;
-    if (threadIdx.x < (unsigned)sym.world) {            // one thread per rank flag
-      const uint32_t seq = sym_slots_cur_seq(sym);
-      sym_wait_flag(sym, kSymSlotCh0 + threadIdx.x, seq);  // on a time-out the status word says so; the sum is then wrong, not hung
-      if (threadIdx.x == 0) s_seq = seq;
+    SymControl* me = sym_ctl(sym, sym.rank);
+    if (threadIdx.x == 0) s_seq = *(volatile uint32_t*)&me->row_seq[t] + 1u;
+    __syncthreads();
+    const uint32_t seq = s_seq;
+    slot_stride = (size_t)slot_rows * D;
+    const size_t par_off = (size_t)(seq & 1u) * sym.world * slot_stride + (size_t)t * D;      // in floats
+    // push this rank's partial row, 16 bytes per lane, and leave it zeroed for the next projection
+    float4* pr = (float4*)(part + (size_t)t * D);
+    const size_t dst = slot_off + (par_off + (size_t)sym.rank * slot_stride) * 4;
+    for (int i = threadIdx.x; i < D / 4; i += blockDim.x) {
+      const float4 pv = pr[i];
+      sym_st_all_v4(sym, dst + (size_t)i * 16, make_uint4(__float_as_uint(pv.x), __float_as_uint(pv.y), __float_as_uint(pv.z), __float_as_uint(pv.w)));
+      pr[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     __syncthreads();
-    slot_stride = (size_t)slot_rows * D;
-    slot0 = (const float*)(sym.base[sym.rank] + slot_off) + (size_t)(s_seq & 1u) * sym.world * slot_stride + (size_t)t * D;
+    if (threadIdx.x == 0) {
+      me->row_seq[t] = seq;
+      sym_row_signal(sym, t);
+      sym_row_wait(sym, t, seq);      // on a time-out the status word says so; the sum is then wrong, not hung
+    }
+    __syncthreads();
+    slot0 = (const float*)(sym.base[sym.rank] + slot_off) + par_off;
   }
 #pragma unroll
   for (int k = 0; k < kRmsRegs; k++) {
@@ -191,18 +206,19 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, co
 }
 
 // sym_mode 0: plain.  1: x lives in the symmetric heap and the next row-parallel kernel of every rank will add into
-// it; this kernel then ends by signalling that this rank has read x (see sym.cuh).  2: add the per-rank slots at heap
-// offset slot_off ([2][world][slot_rows][D] fp32) into x first (see the kernel).
+// it; this kernel then ends by signalling that this rank has read x (see sym.cuh).  2: all-reduce this rank's partial
+// rows `part` (fp32 [T][D], local) through the per-rank slots at heap offset slot_off ([2][world][slot_rows][D] fp32)
+// and add the sum into x first (see the kernel).
 // zero / zero_n: an fp32 buffer (16-byte aligned, zero_n a multiple of 4) that the kernel clears on the side.
 B200_API int b200_rmsnorm(float* x, const float* g, float eps, int T, int D, void* xq, float* xd,
                           float* xs16, void* hb, float* hf, const SymTable* sym, int sym_mode, float* zero, long zero_n,
-                          size_t slot_off, int slot_rows, cudaStream_t st) {
+                          size_t slot_off, int slot_rows, float* part, cudaStream_t st) {
   if (D % 32 || (zero && ((zero_n % 4) || ((uintptr_t)zero % 16)))) return B200_ERR_BAD_ARG;
-  if ((sym_mode != 0 && !sym) || sym_mode < 0 || sym_mode > 2 || (sym_mode == 2 && (T > slot_rows || (slot_off % 16)))) return B200_ERR_BAD_ARG;
+  if ((sym_mode != 0 && !sym) || sym_mode < 0 || sym_mode > 2 || (sym_mode == 2 && (T > slot_rows || slot_rows > kSymSlotRows || (slot_off % 16) || !part || (D % 4) || ((uintptr_t)part % 16)))) return B200_ERR_BAD_ARG;
   const int threads = D >= 4096 ? 1024 : D >= 1024 ? 512 : 256;
   return launch_pdl(rmsnorm_kernel, dim3(T), dim3(threads), 0, st, x, g, eps, D, (int8_t*)xq, xd, xs16,
                     (__nv_bfloat16*)hb, hf, sym ? *sym : SymTable{}, sym ? sym_mode : 0, (float4*)zero, zero ? (int)(zero_n / 4) : 0,
-                    slot_off, slot_rows);
+                    slot_off, slot_rows, part);
 }
 
 // Sequence-sharded tensor-parallel prefill: this rank owns rows [row0, row0 + T) of the residual

@@ -13,7 +13,7 @@
 using namespace b200;
 
 enum { WT_Q4KR = 0, WT_Q6KR = 1, WT_Q8R = 2, WT_BF16 = 3 };
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU_Q8 = 2, EPI_SWIGLU_F32 = 3, EPI_ALLREDUCE = 4, EPI_SLOTS = 5 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU_Q8 = 2, EPI_SWIGLU_F32 = 3, EPI_ALLREDUCE = 4 };
 
 struct MatvecArgs {
   const uint8_t* w;     // main plane
@@ -35,12 +35,8 @@ struct MatvecArgs {
   // EPI_ALLREDUCE: this rank's partial products are added into the fp32 tensor at byte offset
   // sym_off ([nb][ldy]) of EVERY rank's symmetric heap, and the kernel ends with a cross-rank
   // barrier, so on completion each replica holds resid + sum of all ranks' partials.
-  // EPI_SLOTS: the partial products are STORED into this rank's slot of the fp32 tensor
-  // [2][world][slot_rows][ldy] at byte offset sym_off of every rank's heap and the kernel ends by raising this rank's
-  // flag; the RMSNorm that follows adds the slots up (see sym_slots_* in sym.cuh).  No barrier, no handshake.
   SymTable sym;
   size_t sym_off;
-  int slot_rows;
   int prefetch;         // bring this CTA's weight rows into L2 before waiting for the previous kernel
   int wait_ready;       // EPI_ALLREDUCE: check the peers' "finished reading" signals before the first add
 };
@@ -179,7 +175,7 @@ __device__ __forceinline__ void matvec_epilogue(const MatvecArgs& a, const float
   const int n = blockIdx.x * R + lane;
   const bool live = lane < R && n < a.N;
   float v = res[lane * B + b];
-  if (a.bias && live && ((a.epi != EPI_ALLREDUCE && a.epi != EPI_SLOTS) || a.sym.rank == 0)) v += a.bias[dual ? 2 * n : n];
+  if (a.bias && live && (a.epi != EPI_ALLREDUCE || a.sym.rank == 0)) v += a.bias[dual ? 2 * n : n];
   if (a.epi == EPI_STORE) {
     if (live) a.y[(size_t)b * a.ldy + n] = v;
     if (dual && live) {
@@ -190,9 +186,6 @@ __device__ __forceinline__ void matvec_epilogue(const MatvecArgs& a, const float
     if (live) a.y[(size_t)b * a.ldy + n] = a.resid[(size_t)b * a.ldy + n] + v;
   } else if (a.epi == EPI_ALLREDUCE) {
     if (live) sym_red_all_f32(a.sym, a.sym_off + ((size_t)b * a.ldy + n) * 4, v);
-  } else if (a.epi == EPI_SLOTS) {
-    const size_t slot = (size_t)(sym_slots_next_seq(a.sym) & 1u) * a.sym.world + a.sym.rank;
-    if (live) sym_st_all_f32(a.sym, a.sym_off + ((slot * a.slot_rows + b) * a.ldy + n) * 4, v);
   } else {
     float u = res[32 * B + lane * B + b];
     if (a.bias && live) u += a.bias[2 * n + 1];
@@ -314,7 +307,6 @@ __global__ void __launch_bounds__(256) matvec_q_kernel(const MatvecArgs a) {
   __syncthreads();
   matvec_epilogue<B, R>(a, res, DUAL);
   if (a.epi == EPI_ALLREDUCE) sym_kernel_end_barrier(a.sym, 0, gridDim.x, a.wait_ready != 0);
-  if (a.epi == EPI_SLOTS) sym_slots_signal(a.sym, gridDim.x);
 }
 
 // bf16 weights [N][K] against fp32 activations.
@@ -381,7 +373,6 @@ __global__ void __launch_bounds__(256) matvec_bf16_kernel(const MatvecArgs a) {
   __syncthreads();
   matvec_epilogue<B>(a, res, DUAL);
   if (a.epi == EPI_ALLREDUCE) sym_kernel_end_barrier(a.sym, 0, gridDim.x, a.wait_ready != 0);
-  if (a.epi == EPI_SLOTS) sym_slots_signal(a.sym, gridDim.x);
 }
 
 template <int WT, int B, bool DUAL, int RW>
@@ -433,7 +424,7 @@ static int dispatch_wt(int wt, const MatvecArgs& a, cudaStream_t st) {
 B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, int nb, const void* xq,
                          const float* xd, const float* xs16, const float* xf, int epi, const float* bias,
                          const float* resid, float* y, int ldy, void* oq, float* od, float* os16,
-                         const SymTable* sym, size_t sym_off, int wait_ready, int slot_rows, cudaStream_t st) {
+                         const SymTable* sym, size_t sym_off, int wait_ready, cudaStream_t st) {
   if (nb < 1 || nb > 8) return B200_ERR_BAD_ARG;
   if (wt == WT_BF16 ? (K % 8 != 0) : (K % 256 != 0 && !(wt == WT_Q8R && K % 32 == 0))) return B200_ERR_BAD_ARG;
   if (epi == EPI_SWIGLU_Q8 && N % 32) return B200_ERR_BAD_ARG;
@@ -441,9 +432,8 @@ B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, in
   a.w = (const uint8_t*)w; a.w2 = (const __half*)w2; a.N = N; a.K = K; a.nb = nb;
   a.xq = (const int8_t*)xq; a.xd = xd; a.xs16 = xs16; a.xf = xf; a.epi = epi; a.bias = bias;
   a.resid = resid; a.y = y; a.ldy = ldy; a.oq = (int8_t*)oq; a.od = od; a.os16 = os16;
-  a.slot_rows = slot_rows;
-  if (epi == EPI_ALLREDUCE || epi == EPI_SLOTS) {
-    if (!sym || (epi == EPI_SLOTS && nb > slot_rows)) return B200_ERR_BAD_ARG;
+  if (epi == EPI_ALLREDUCE) {
+    if (!sym) return B200_ERR_BAD_ARG;
     a.sym = *sym;
     a.sym_off = sym_off;
   } else {

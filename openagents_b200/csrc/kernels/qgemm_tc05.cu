@@ -23,37 +23,35 @@
 // which is also why the issuing loop below works on precomputed descriptor words.
 // Stages hand over through mbarriers; every wait is bounded and reports through `status`.
 //
-// Epilogues: plain store (fp32 and/or bf16), accumulation with `red` (K may be split), SwiGLU over
-// interleaved (gate, up) rows, and the tensor-parallel form that stores the partial tile into this
-// rank's slot on every rank (see sym_slots_* in sym.cuh).
+// Epilogues: plain store (fp32 and/or bf16), accumulation with vector `red` (K may be split; under tensor
+// parallelism the row-parallel projections accumulate this rank's partial result that way and the RMSNorm
+// that follows all-reduces it) and SwiGLU over interleaved (gate, up) rows.
 //
 // GEMM-shaped reference math: apps/openagents.com/workers/api/src/cs336-a2-benchmark-workload.ts:251-292;
 // the quantized formats are the ones the reference serves (docs/muse/muse-glimmer.md:112).
 #include "tc05.cuh"
-#include "../comm/sym.cuh"
 
 using namespace b200;
 using namespace b200::tc;
 
 enum { QW_Q4KR = 0, QW_Q6KR = 1 };
-enum { QEPI_STORE = 0, QEPI_ADD = 1, QEPI_SWIGLU = 2, QEPI_SLOTS = 3 };
+enum { QEPI_STORE = 0, QEPI_ADD = 1, QEPI_SWIGLU = 2 };
 
 struct QGemmArgs {
   const __half* w2;      // Q6_K-R: fp16 d per (row, superblock); unused for Q4_K-R
   float* out_f32;        // [T][ldo] (STORE / ADD), or null
   __nv_bfloat16* out_bf16;   // [T][ldo] (STORE) or [T][ldo] with N / 2 live columns (SWIGLU), or null
-  const float* bias;     // [N] in the row order of W, or null (applied by K split 0; SLOTS: by rank 0)
+  const float* bias;     // [N] in the row order of W, or null (applied by K split 0)
   int ldo, T, N, K;
   int epi;
   int splits, sb_per_split, n_items;
   int* status;
-  SymTable sym;          // SLOTS only
-  size_t slot_off;       // heap offset of the slot tensor [2][world][slot_rows][ldo] fp32
-  int slot_rows;
 };
 
 __device__ __forceinline__ uint32_t bf162_as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 __device__ __forceinline__ __nv_bfloat162 u32_as_bf162(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) { return bf162_as_u32(__floats2bfloat162_rn(lo, hi)); }
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
@@ -273,7 +271,6 @@ __global__ void __launch_bounds__(kQThreads, 1) qgemm_kernel(const __grid_consta
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     uint32_t g = 0, ecount = 0;
     bool ok = true;
-    uint32_t slot_buf = 0;
     bool waited = false;
 
     // epilogue of the item with accumulator number `ec`: this warp takes its lane quarter and 32 of the 64 token columns
@@ -287,7 +284,6 @@ __global__ void __launch_bounds__(kQThreads, 1) qgemm_kernel(const __grid_consta
       if (!waited) {                      // first global write of this thread: the kernel before this one must be complete
         pdl_wait();
         waited = true;
-        if (a.epi == QEPI_SLOTS) slot_buf = (sym_slots_next_seq(a.sym)) & 1u;
       }
       const int n = tile * QBM + row;
       const int t0 = khalf * 32;
@@ -307,28 +303,51 @@ __global__ void __launch_bounds__(kQThreads, 1) qgemm_kernel(const __grid_consta
           const int t = t0 + j + (odd ? 1 : 0);
           if (live && t < a.T) a.out_bf16[(size_t)t * a.ldo + (n >> 1)] = __float2bfloat16(silu(gate) * up);
         }
-      } else if (live) {
+      } else {
+        // Transpose 4 x 4 patches inside each lane quad (four shuffles per four tokens): a lane then holds, for ONE token,
+        // four consecutive output columns, so that a warp instruction moves four rows of 128 contiguous bytes: vector
+        // stores, vector reductions into L2, full packets over NVLink.
         float b = 0.f;
-        if (a.bias && sp == 0 && (a.epi != QEPI_SLOTS || a.sym.rank == 0)) b = a.bias[n];
-        if (a.epi == QEPI_SLOTS) {
-          const size_t base = a.slot_off + ((((size_t)slot_buf * a.sym.world + a.sym.rank) * a.slot_rows) * a.ldo + n) * 4;
+        if (a.bias && live && sp == 0) b = a.bias[n];
+        const int lq = lane & 3, nq = tile * QBM + q * 32 + (lane & ~3);      // first of this lane's four columns
+        const bool quad_live = nq + 3 < a.N && (a.ldo & 3) == 0;
 #pragma unroll
-          for (int j = 0; j < 32; j++) {
-            const int t = t0 + j;
-            if (t < a.T) sym_st_all_f32(a.sym, base + (size_t)t * a.ldo * 4, __uint_as_float(v[j]) + b);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; j++) {
-            const int t = t0 + j;
-            if (t >= a.T) continue;
-            const float x = __uint_as_float(v[j]) + b;
-            const size_t idx = (size_t)t * a.ldo + n;
+        for (int k4 = 0; k4 < 8; k4++) {
+          float c[4] = {__uint_as_float(v[4 * k4]) + b, __uint_as_float(v[4 * k4 + 1]) + b, __uint_as_float(v[4 * k4 + 2]) + b,
+                        __uint_as_float(v[4 * k4 + 3]) + b};
+          float x0 = (lq & 1) ? c[0] : c[1];
+          x0 = __shfl_xor_sync(0xffffffffu, x0, 1);
+          if (lq & 1) c[0] = x0; else c[1] = x0;
+          float x1 = (lq & 1) ? c[2] : c[3];
+          x1 = __shfl_xor_sync(0xffffffffu, x1, 1);
+          if (lq & 1) c[2] = x1; else c[3] = x1;
+          float x2 = (lq & 2) ? c[0] : c[2];
+          x2 = __shfl_xor_sync(0xffffffffu, x2, 2);
+          if (lq & 2) c[0] = x2; else c[2] = x2;
+          float x3 = (lq & 2) ? c[1] : c[3];
+          x3 = __shfl_xor_sync(0xffffffffu, x3, 2);
+          if (lq & 2) c[1] = x3; else c[3] = x3;
+          const int t = t0 + 4 * k4 + lq;          // c[0..3] = columns nq .. nq + 3 of token t
+          if (t >= a.T) continue;
+          const size_t idx = (size_t)t * a.ldo + nq;
+          if (quad_live) {
+            const float4 o = make_float4(c[0], c[1], c[2], c[3]);
             if (a.epi == QEPI_ADD) {
-              asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(a.out_f32 + idx), "f"(x) : "memory");
+              asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(a.out_f32 + idx), "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w) : "memory");
             } else {
-              if (a.out_f32) a.out_f32[idx] = x;
-              if (a.out_bf16) a.out_bf16[idx] = __float2bfloat16(x);
+              if (a.out_f32) *(float4*)(a.out_f32 + idx) = o;
+              if (a.out_bf16) *(uint2*)(a.out_bf16 + idx) = make_uint2(pack2(o.x, o.y), pack2(o.z, o.w));
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              if (nq + e >= a.N) break;
+              if (a.epi == QEPI_ADD) {
+                asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(a.out_f32 + idx + e), "f"(c[e]) : "memory");
+              } else {
+                if (a.out_f32) a.out_f32[idx + e] = c[e];
+                if (a.out_bf16) a.out_bf16[idx + e] = __float2bfloat16(c[e]);
+              }
             }
           }
         }
@@ -423,10 +442,6 @@ __global__ void __launch_bounds__(kQThreads, 1) qgemm_kernel(const __grid_consta
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, 512);
   if (threadIdx.x == 0 && *abort_flag && a.status) atomicExch(a.status, (int)B200_ERR_TIMEOUT_MMA);
-  if (a.epi == QEPI_SLOTS) {
-    if (threadIdx.x == 0) pdl_wait();       // a CTA without items must not signal before the kernel before this one is done
-    sym_slots_signal(a.sym, gridDim.x);
-  }
 }
 
 static int q_sm_count() {
@@ -468,21 +483,15 @@ static int launch_q(const void* w, const void* x, int ldx, QGemmArgs a, cudaStre
 //   QEPI_STORE  out_f32 and/or out_bf16 [T][ldo] = result (+ bias)
 //   QEPI_ADD    out_f32 [T][ldo] += result (+ bias); split_k > 1 allowed (0 = choose)
 //   QEPI_SWIGLU rows of W are (gate_0, up_0, gate_1, ...); out_bf16 [T][ldo] gets silu(gate) * up, N / 2 columns
-//   QEPI_SLOTS  tensor parallel: the partial result goes to slot (parity of the sequence number, this rank) of the
-//               fp32 tensor [2][world][slot_rows][ldo] at heap offset slot_off on EVERY rank; the kernel ends by
-//               signalling, nothing waits (the consumer does: rmsnorm with slots).  T <= 64.
 B200_API int b200_qgemm(int wt, const void* w, const void* w2, int N, int K, const void* x, int ldx, int T, float* out_f32,
-                        void* out_bf16, int ldo, const float* bias, int epi, int split_k, const SymTable* sym,
-                        size_t slot_off, int slot_rows, int* status, cudaStream_t st) {
+                        void* out_bf16, int ldo, const float* bias, int epi, int split_k, int* status, cudaStream_t st) {
   if (K % QSB || (ldx % 8) || T < 1 || N < 1 || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return B200_ERR_BAD_ARG;
   if (wt != QW_Q4KR && wt != QW_Q6KR) return B200_ERR_BAD_ARG;
   if (wt == QW_Q6KR && !w2) return B200_ERR_BAD_ARG;
-  if (epi == QEPI_SWIGLU ? (!out_bf16 || (N & 1)) : epi == QEPI_ADD ? !out_f32 : epi == QEPI_STORE ? (!out_f32 && !out_bf16)
-      : (epi != QEPI_SLOTS || !sym || T > QBN || T > slot_rows || (slot_off % 16)))
+  if (epi == QEPI_SWIGLU ? (!out_bf16 || (N & 1)) : epi == QEPI_ADD ? !out_f32 : (epi != QEPI_STORE || (!out_f32 && !out_bf16)))
     return B200_ERR_BAD_ARG;
   QGemmArgs a = {};
   a.w2 = (const __half*)w2; a.bias = bias; a.ldo = ldo; a.N = N; a.K = K; a.epi = epi; a.status = status;
-  if (epi == QEPI_SLOTS) { a.sym = *sym; a.slot_off = slot_off; a.slot_rows = slot_rows; }
   const int nsb = K / QSB, tiles = (N + QBM - 1) / QBM;
   int splits = 1;
   if (epi == QEPI_ADD) {

@@ -170,9 +170,10 @@ class LlamaEngine:
         self.cfg, self.device = cfg, torch.device(device)
         self.rank, self.world, self.comm = tp_rank, tp_world, comm
         self._use_fence = os.environ.get("B200_TP_FENCE", "0") == "1"
-        # Tensor-parallel decode: "slots" = one-shot all-reduce through per-rank slots, summed by the next norm (no
-        # barrier, no handshake); "allreduce" = the older form (multimem.red into every replica + barrier), kept as a
-        # measurement aid and for weight types the fused-dequant GEMM does not take.
+        # Tensor-parallel decode: "slots" = the row-parallel projections keep their partial result local and the RMSNorm
+        # that follows all-reduces it through per-rank slots (one kernel: push, per-row flags, sum, normalise; no barrier,
+        # no handshake); "allreduce" = the older form (multimem.red into every replica from the projection's epilogue +
+        # barrier), kept as a measurement aid and for weight types the fused-dequant GEMM does not take.
         self.tp_mode = os.environ.get("B200_TP_MODE", "slots")
         if cfg.n_kv_heads % tp_world or cfg.ffn % tp_world:
             raise ValueError("tensor-parallel degree must divide the KV heads and the FFN width")
@@ -308,9 +309,11 @@ class LlamaEngine:
         self._wscratch_elems = max(wmax, self.wout.N * self.wout.K if self.wout.quantized else 0)
         self._wscratch = None
         if self.world > 1:
-            # one-shot all-reduce slots [parity][rank][row][d] and arg-max merge slots [parity][rank][row][2]
+            # one-shot all-reduce: slots [parity][rank][row][d] on every rank, and this rank's partial rows (local, kept
+            # zeroed between uses: the projections accumulate into them)
             self.slot_rows = QGEMM_MAX_TOKENS
             self.slots, self.slots_off = self.comm.alloc_tensor((2, self.world, self.slot_rows, d), torch.float32)
+            self.xpart = torch.zeros((self.slot_rows, d), **f32)
             row_par = [w for l in self.layers for w in (l.wo, l.wdown) if w is not None]
             self.slots_small = self.tp_mode == "slots"
             self.slots_dense = self.slots_small and all(self._qg(w) for w in row_par)
@@ -336,7 +339,7 @@ class LlamaEngine:
 
     @property
     def _slot_arg(self):
-        return (self.comm.heap.table, self.slots_off, self.slot_rows)
+        return (self.comm.heap.table, self.slots_off, self.slot_rows, self.xpart)
 
     # ------------------------------------------------------------------ building blocks
     def _splits(self, B: int, ctx_pages: int) -> int:
@@ -390,10 +393,9 @@ class LlamaEngine:
             if self.world == 1:
                 ops.matvec(L.wo.wt, L.wo.main, L.wo.plane2, L.wo.N, L.wo.K, nb, xq=self.xq, xd=self.xd, xs16=self.xs,
                            xf=self.xf, epi=ops.EPI_RESID, bias=L.bo, resid=x, y=x, ldy=self.d)
-            elif slots:
+            elif slots:      # partial result stays local; the norm below all-reduces it
                 ops.matvec(L.wo.wt, L.wo.main, L.wo.plane2, L.wo.N, L.wo.K, nb, xq=self.xq, xd=self.xd, xs16=self.xs,
-                           xf=self.xf, epi=ops.EPI_SLOTS, bias=L.bo, ldy=self.d, sym=table, sym_off=self.slots_off,
-                           slot_rows=self.slot_rows)
+                           xf=self.xf, epi=ops.EPI_STORE, bias=L.bo if self.rank == 0 else None, y=self.xpart, ldy=self.d)
             else:
                 self.comm.matvec_allreduce(L.wo, nb, self.xq, self.xd, self.xs, self.xf, x, self.d, bias=L.bo, wait_ready=not self._use_fence)
             g8 = L.wgu.quantized
@@ -412,8 +414,7 @@ class LlamaEngine:
                            xs16=self.fs, xf=self.gu, epi=ops.EPI_RESID, resid=x, y=x, ldy=self.d)
             elif slots:
                 ops.matvec(L.wdown.wt, L.wdown.main, L.wdown.plane2, L.wdown.N, L.wdown.K, nb, xq=self.fq, xd=self.fd,
-                           xs16=self.fs, xf=self.gu, epi=ops.EPI_SLOTS, ldy=self.d, sym=table, sym_off=self.slots_off,
-                           slot_rows=self.slot_rows)
+                           xs16=self.fs, xf=self.gu, epi=ops.EPI_STORE, y=self.xpart, ldy=self.d)
             else:
                 self.comm.matvec_allreduce(L.wdown, nb, self.fq, self.fd, self.fs, self.gu, x, self.d, wait_ready=not self._use_fence)
             n += 8
@@ -490,9 +491,9 @@ class LlamaEngine:
 
     def _row_parallel(self, a_bf16, w: QWeight, T: int, x, bias, fused: bool, slots: bool, table):
         """x += a W^T for a row-parallel projection (attention output, FFN down), summed over the tensor-parallel ranks."""
-        if slots:
-            ops.qgemm(w, a_bf16, T, ldo=self.d, bias=bias, epi=ops.QEPI_SLOTS, sym=table, slot_off=self.slots_off,
-                      slot_rows=self.slot_rows, status=self.status)
+        if slots:        # this rank's partial sums stay local (K splits add into the zeroed rows); the next norm all-reduces them
+            ops.qgemm(w, a_bf16, T, out_f32=self.xpart, ldo=self.d, bias=bias if self.rank == 0 else None, epi=ops.QEPI_ADD,
+                      status=self.status)
         elif self.world == 1:
             if fused and self._qg(w):
                 ops.qgemm(w, a_bf16, T, out_f32=x, ldo=self.d, bias=bias, epi=ops.QEPI_ADD, status=self.status)

@@ -14,7 +14,7 @@ import torch
 from .. import _native
 
 WT_Q4KR, WT_Q6KR, WT_Q8R, WT_BF16, WT_MXFP4R = 0, 1, 2, 3, 4
-EPI_STORE, EPI_RESID, EPI_SWIGLU_Q8, EPI_SWIGLU_F32, EPI_ALLREDUCE, EPI_SLOTS = 0, 1, 2, 3, 4, 5
+EPI_STORE, EPI_RESID, EPI_SWIGLU_Q8, EPI_SWIGLU_F32, EPI_ALLREDUCE = 0, 1, 2, 3, 4
 SYM_NONE, SYM_ALLREDUCE, SYM_RSCATTER, SYM_RSCATTER_ROWS = 0, 1, 2, 3
 EMB_F32, EMB_BF16, EMB_Q8R, EMB_Q6KR = 0, 1, 2, 3
 ACT_NONE, ACT_GELU, ACT_SWIGLU_PAIR = 0, 1, 2
@@ -22,7 +22,7 @@ ACT_NONE, ACT_GELU, ACT_SWIGLU_PAIR = 0, 1, 2
 _P = c_void_p
 _SIGS = {
     "b200_embedding": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, c_int, _P],
-    "b200_rmsnorm": [_P, _P, c_float, c_int, c_int, _P, _P, _P, _P, _P, _P, c_int, _P, c_long, c_size_t, c_int, _P],
+    "b200_rmsnorm": [_P, _P, c_float, c_int, c_int, _P, _P, _P, _P, _P, _P, c_int, _P, c_long, c_size_t, c_int, _P, _P],
     "b200_rmsnorm_allgather": [_P, _P, c_float, c_int, c_int, c_int, c_size_t, _P, _P],
     "b200_quantize_x": [_P, c_int, c_int, _P, _P, _P, _P],
     "b200_rope_kv": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, _P, c_int, _P],
@@ -32,7 +32,7 @@ _SIGS = {
     "b200_argmax": [_P, c_int, c_int, _P, _P, c_int, _P, _P],
     "b200_sample_topk": [_P, c_int, c_int, c_float, c_int, c_float, _P, _P, _P, _P],
     "b200_matvec": [c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, _P, _P,
-                    c_size_t, c_int, c_int, _P],
+                    c_size_t, c_int, _P],
     "b200_argmax_merge": [_P, _P, c_int, _P, c_size_t, c_int, _P],
     "b200_attn_decode": [_P, _P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                          _P, _P, _P, _P, _P],
@@ -49,7 +49,7 @@ _SIGS = {
     "b200_dequant_bf16": [c_int, _P, _P, _P, c_size_t, c_int, _P],
     "b200_f32_to_bf16": [_P, _P, c_size_t, _P],
     "b200_transpose_bf16": [_P, _P, c_int, c_int, _P],
-    "b200_qgemm": [c_int, _P, _P, c_int, c_int, _P, c_int, c_int, _P, _P, c_int, _P, c_int, c_int, _P, c_size_t, c_int, _P, _P],
+    "b200_qgemm": [c_int, _P, _P, c_int, c_int, _P, c_int, c_int, _P, _P, c_int, _P, c_int, c_int, _P, _P],
     "b200_decode_advance": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, _P, c_int, _P],
 }
 
@@ -102,18 +102,20 @@ def rmsnorm(x, g, eps, xq=None, xd=None, xs16=None, hb=None, hf=None, signal_sym
     """``signal_sym``: symmetric-heap table; the kernel then ends by telling every rank that this rank has
     finished reading ``x`` (the handshake the fused all-reduce kernels check with ``wait_ready``).
     ``zero``: a contiguous fp32 tensor the kernel clears on the side (the output of a split-K GEMM that follows).
-    ``slots``: ``(table, heap offset, rows)`` of the slot tensor a tensor-parallel row-parallel projection just filled
-    (``EPI_SLOTS`` / ``QEPI_SLOTS``): the kernel waits for every rank's flag, adds the slots into ``x`` (in place) and
-    normalises the sum: the consumer half of the one-shot all-reduce."""
+    ``slots``: ``(table, heap offset, rows, part)``: tensor parallel: ``part`` (fp32 [T, D], local) holds this rank's
+    partial result of the row-parallel projection before this norm; the kernel all-reduces it through the per-rank slot
+    tensor at ``heap offset`` ([2][world][rows][D] fp32 on every rank), adds the sum into ``x`` (in place), normalises
+    it, and leaves ``part`` zeroed."""
     T, D = x.shape
+    part = None
     if slots is not None:
-        table, slot_off, slot_rows = slots
+        table, slot_off, slot_rows, part = slots
         mode = 2
     else:
         table, slot_off, slot_rows = signal_sym, 0, 0
         mode = 1 if signal_sym is not None else 0
     _check(lib().b200_rmsnorm(_p(x), _p(g), eps, T, D, _p(xq), _p(xd), _p(xs16), _p(hb), _p(hf), _sym(table), mode,
-                              _p(zero), zero.numel() if zero is not None else 0, slot_off, slot_rows, _st()), "rmsnorm")
+                              _p(zero), zero.numel() if zero is not None else 0, slot_off, slot_rows, _p(part), _st()), "rmsnorm")
 
 
 def rmsnorm_allgather(x, g, eps, row0, n_rows, hb_off, sym):
@@ -168,12 +170,11 @@ def sample_topk(logits, temperature, top_k, top_p, u, out_id, scratch):
 
 
 def matvec(wt, w, w2, N, K, nb, xq=None, xd=None, xs16=None, xf=None, epi=EPI_STORE, bias=None, resid=None, y=None,
-           ldy=0, oq=None, od=None, os16=None, sym=None, sym_off=0, wait_ready=False, slot_rows=0):
+           ldy=0, oq=None, od=None, os16=None, sym=None, sym_off=0, wait_ready=False):
     """Quantized mat-vec for 1..8 tokens (see ``matvec.cu``).  The SwiGLU epilogues read ``w`` as 2N rows interleaved
-    (gate_0, up_0, gate_1, ...).  ``EPI_SLOTS``: ``sym_off`` is the heap offset of the slot tensor
-    [2][world][slot_rows][ldy]."""
+    (gate_0, up_0, gate_1, ...)."""
     _check(lib().b200_matvec(wt, _p(w), _p(w2), N, K, nb, _p(xq), _p(xd), _p(xs16), _p(xf), epi, _p(bias), _p(resid),
-                             _p(y), ldy, _p(oq), _p(od), _p(os16), _sym(sym), sym_off, int(wait_ready), slot_rows, _st()), "matvec")
+                             _p(y), ldy, _p(oq), _p(od), _p(os16), _sym(sym), sym_off, int(wait_ready), _st()), "matvec")
 
 
 def argmax_merge(out_id, out_val, nb, sym, merge_off, rows):
@@ -244,18 +245,16 @@ def decode_advance(ids, out_ids, pos, slot, seq_lens, page_table, page_size, B, 
            "decode_advance")
 
 
-QEPI_STORE, QEPI_ADD, QEPI_SWIGLU, QEPI_SLOTS = 0, 1, 2, 3
+QEPI_STORE, QEPI_ADD, QEPI_SWIGLU = 0, 1, 2
 
 
-def qgemm(w, x_bf16, T, out_f32=None, out_bf16=None, ldo=None, bias=None, epi=QEPI_STORE, split_k=0, status=None,
-          sym=None, slot_off=0, slot_rows=0):
+def qgemm(w, x_bf16, T, out_f32=None, out_bf16=None, ldo=None, bias=None, epi=QEPI_STORE, split_k=0, status=None):
     """out[T][N] (+)= x[T][K] @ dequant(W)[N][K]^T with the dequantization inside the tcgen05 pipeline
     (``qgemm_tc05.cu``).  ``w`` is a QWeight in Q4_K-R or Q6_K-R; its packed planes are read as they are.
-    ``QEPI_SWIGLU``: rows of ``w`` are (gate, up) pairs, ``out_bf16`` gets N/2 columns.  ``QEPI_SLOTS``: see ``rmsnorm``."""
+    ``QEPI_SWIGLU``: rows of ``w`` are (gate, up) pairs, ``out_bf16`` gets N/2 columns."""
     wt = {WT_Q4KR: 0, WT_Q6KR: 1}[w.wt]
     _check(lib().b200_qgemm(wt, _p(w.main), _p(w.plane2), w.N, w.K, _p(x_bf16), x_bf16.stride(0), T, _p(out_f32), _p(out_bf16),
-                            ldo if ldo is not None else w.N, _p(bias), epi, split_k, _sym(sym), slot_off, slot_rows,
-                            _p(status), _st()), "qgemm")
+                            ldo if ldo is not None else w.N, _p(bias), epi, split_k, _p(status), _st()), "qgemm")
 
 
 # ---------------------------------------------------------------- mixture of experts

@@ -549,21 +549,22 @@ def test_qgemm_swiglu(T, F, K):
 
 
 def test_slot_allreduce_single_rank():
-    """The one-shot all-reduce protocol with a world of one: a mat-vec and a fused-dequant GEMM store their result into
-    the slot of the current parity and raise the flag; the RMSNorm that follows waits for the flag, adds the slot into the
-    residual stream and normalises the sum.  Several rounds, so both parities and the device-side sequence number are
-    exercised; the arg-max merge uses the same scheme."""
+    """The one-shot all-reduce with a world of one: a mat-vec or a fused-dequant GEMM leaves its result in the local
+    partial buffer; the RMSNorm pushes each row into its slot, raises and awaits the row's flag, adds the slots into the
+    residual stream, normalises the sum and leaves the partial rows zeroed.  Several rounds with different row counts, so
+    both parities and the per-row device-side sequence numbers are exercised; the arg-max merge uses the same scheme."""
     from openagents_b200.parallel.symm import SymmHeap
     ops = _ops()
     N, K, rows = 256, 512, 64
     heap = SymmHeap(64 << 20, DEV)
     slots, slots_off = heap.alloc_tensor((2, 1, rows, N), torch.float32)
+    part = torch.zeros((rows, N), device=DEV)
     W = _randn(N, K, seed=46, scale=0.05)
     w = _qweight(W, GgmlType.Q4_K)
     Wd = tc.dequantize(tc.quantize(W, GgmlType.Q4_K), GgmlType.Q4_K, (N, K))
     g = _randn(N, seed=47) * 0.1 + 1.0
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    for rnd, nb in enumerate((1, 3, 40, 64, 2)):
+    for rnd, nb in enumerate((1, 3, 40, 64, 2, 64)):
         x = _randn(nb, K, seed=48 + rnd)
         resid = _randn(nb, N, seed=60 + rnd)
         xres = resid.clone()
@@ -571,19 +572,18 @@ def test_slot_allreduce_single_rank():
             xq, xd, xs = _alloc_q(nb, K)
             ops.quantize_x(x, xq, xd, xs)
             xin = _quant_x(x)[0]
-            ops.matvec(w.wt, w.main, w.plane2, N, K, nb, xq=xq, xd=xd, xs16=xs, xf=x, epi=ops.EPI_SLOTS, ldy=N,
-                       sym=heap.table, sym_off=slots_off, slot_rows=rows)
+            ops.matvec(w.wt, w.main, w.plane2, N, K, nb, xq=xq, xd=xd, xs16=xs, xf=x, epi=ops.EPI_STORE, y=part, ldy=N)
         else:
             xin = x.bfloat16().float()
-            ops.qgemm(w, x.bfloat16(), nb, ldo=N, epi=ops.QEPI_SLOTS, sym=heap.table, slot_off=slots_off, slot_rows=rows,
-                      status=status)
+            ops.qgemm(w, x.bfloat16(), nb, out_f32=part, ldo=N, epi=ops.QEPI_ADD, status=status)
         hf = torch.empty((nb, N), device=DEV)
-        ops.rmsnorm(xres, g, 1e-5, hf=hf, slots=(heap.table, slots_off, rows))
+        ops.rmsnorm(xres, g, 1e-5, hf=hf, slots=(heap.table, slots_off, rows, part))
         torch.cuda.synchronize()
         tot = resid + xin @ Wd.t()
         assert torch.allclose(xres, tot, atol=0.02 * tot.std().item(), rtol=1e-3), rnd
         ref = tot * torch.rsqrt(tot.pow(2).mean(-1, keepdim=True) + 1e-5) * g
         assert torch.allclose(hf, ref, atol=0.03, rtol=1e-2), rnd
+        assert float(part[:nb].abs().max()) == 0.0          # left zeroed for the next projection
     assert int(status.item()) == 0 and heap.status() == (0, 0)
     # arg-max merge with one rank: the ids pass through unchanged, twice (both parities)
     merge, merge_off = heap.alloc_tensor((2, 1, 1024, 2), torch.float32)

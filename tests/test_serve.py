@@ -270,9 +270,12 @@ def test_concurrent_http_requests_share_decode_batches(gguf_path):
         body = {"messages": [{"role": "user", "content": f"question number {i}"}], "max_tokens": 64, "temperature": 0, "stream": True}
         out[i] = _post(base + "/v1/chat/completions", body)
 
+    import time
     ts = [threading.Thread(target=one, args=(i,)) for i in range(8)]
-    for t in ts:
-        t.start()
+    with model.lock:                 # hold the scheduler until every connection has reached its submit
+        for t in ts:
+            t.start()
+        time.sleep(1.0)
     for t in ts:
         t.join(timeout=300)
     httpd.shutdown()
