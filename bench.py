@@ -10,6 +10,12 @@ batch.  The device-timed value replays the engine's self-advancing decode graph 
 autoregression: each step consumes the previous step's arg-max); the end-to-end value calls the
 public ``engine.decode`` once per step with the step's inputs copied from pinned host memory and
 the sampled ids read back.
+
+``vs_baseline`` is this run's value over the same benchmark served by plain PyTorch on the same GPUs right after it
+(``baseline/llama_torch.py``: weights dequantized to bf16, ``torch.matmul``, fused SDPA, NCCL all-reduce, CUDA graph);
+``--impl baseline`` runs only that arm.  ``--impl reference`` reports why the reference repository cannot be run.
+``extra`` also carries the training (GPT-2-small, 3 + 3 steps) and expert-parallel MoE decode throughput on the same
+GPUs, unless ``--extras none``.
 """
 from __future__ import annotations
 
@@ -96,10 +102,14 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     ap.add_argument("--model", default=MODEL)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; marks the run invalid)")
+    ap.add_argument("--extras", default="train,moe", help="side benchmarks reported under extra: comma list of train, moe, or none")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the PyTorch baseline arm (vs_baseline stays null)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
         return
+    if args.impl not in ("b200", "baseline"):
+        raise SystemExit("--impl is one of b200, baseline, reference")
     K, W = args.steps, max(args.warmup, 3)
 
     import torch
@@ -130,11 +140,6 @@ def main():
         comm = TPComm(rank, world, dev, heap_bytes=(4 * P + world) * cfg.d_model * 6 + (64 << 20))
     total_steps = 2 * (K + W) + 8
     max_ctx = P + total_steps + PAGE
-    t0 = time.time()
-    eng = LlamaEngine(cfg, RandomSource(cfg, PLAN_Q4_K, 0, dev), device=dev, max_batch=B + 1, max_ctx=max_ctx,
-                      max_tokens=4 * P, tp_rank=rank, tp_world=world, comm=comm)
-    load_s = time.time() - t0
-
     g = torch.Generator().manual_seed(1234)
     prompts = torch.randint(0, cfg.vocab, (B + 1, P), generator=g)
 
@@ -149,6 +154,32 @@ def main():
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    def baseline_arm(with_clocks: bool):
+        from baseline.llama_torch import run_decode_baseline
+        return run_decode_baseline(cfg, RandomSource(cfg, PLAN_Q4_K, 0, dev), dev, rank, world, B, P, K, W, prompts[:B], barrier,
+                                   max_over_ranks, ClockSampler(local) if with_clocks else None)
+
+    if args.impl == "baseline":
+        r = baseline_arm(True)
+        if rank == 0:
+            print(json.dumps({"impl": "baseline", "metric": f"llama3_8b_q4k_decode_tok_s_bs{B}", "value": round(r["value"], 1),
+                              "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(r["ms_per_step"], 4),
+                              "higher_is_better": True, "scaling": "strong", "vs_baseline": 1.0, "dtype": "bf16", "data": "synthetic",
+                              "config": {"model": cfg.name, "weights": "the product run's Q4_K/Q6_K weights dequantized to bf16",
+                                         "global_batch": B, "seq_len": P, "kv_cache": "contiguous bf16", "parallelism": f"tp{world}",
+                                         "stack": "torch.matmul (cuBLAS) + SDPA + NCCL all-reduce + CUDA graph", "valid": valid},
+                              "clocks": r["clocks"],
+                              "e2e": {"value": round(r["e2e_value"], 1), "unit": "tokens/s", "ms_per_step": round(r["e2e_ms_per_step"], 4),
+                                      "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B},
+                              "gpu_launches": 0, "extra": {"weight_bytes_per_gpu": r["weight_bytes_per_gpu"]}}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    t0 = time.time()
+    eng = LlamaEngine(cfg, RandomSource(cfg, PLAN_Q4_K, 0, dev), device=dev, max_batch=B + 1, max_ctx=max_ctx,
+                      max_tokens=4 * P, tp_rank=rank, tp_world=world, comm=comm)
+    load_s = time.time() - t0
 
     # ---- prefill TTFT: one 2048-token prompt, device time of the whole forward incl. first arg-max
     eng.begin(B)
@@ -261,12 +292,58 @@ def main():
                     {"decode_tok_s": round(B / (slowest * 1e-3), 1), "ms_per_step": round(slowest, 4), "batch_per_gpu": Bl,
                      "parallelism": f"dp{world} (independent replicas)"})
 
+    weight_bytes = eng.weight_bytes()
+    scratch_bytes = 0 if eng._wscratch is None else eng._wscratch.numel() * 2
+    launches_per_step = eng.launches_per_decode
+    del eng
+    if comm is not None:
+        del comm
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+
+    # ---- the same benchmark on plain PyTorch (cuBLAS + SDPA + NCCL), same GPUs, same weights: the baseline arm
+    base, base_err = None, None
+    if not args.no_baseline:
+        try:
+            base = baseline_arm(False)
+        except Exception as e:      # noqa: BLE001 - the product number stands even if the comparison arm fails
+            base_err = f"{type(e).__name__}: {e}"[:200]
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    # ---- side benchmarks on the same GPUs: training throughput and expert-parallel MoE decode
+    extras = {} if args.extras == "none" else {k: None for k in args.extras.split(",") if k}
+    if "train" in extras:
+        try:
+            import bench_train
+            r = bench_train.run(3, 3)
+            extras["train"] = None if r is None else {"train_tok_s": r["value"], "train_ms_per_step": r["ms_per_step"],
+                                                      "train_model_tflops_per_gpu": r["extra"]["model_tflops_per_gpu"],
+                                                      "train_config": r["config"]}
+        except Exception as e:      # noqa: BLE001
+            extras["train"] = {"train_error": f"{type(e).__name__}: {e}"[:200]}
+        gc.collect()
+        torch.cuda.empty_cache()
+    if "moe" in extras:
+        try:
+            import bench_moe
+            margs = argparse.Namespace(gpus=world, steps=16, warmup=4, batch=256, prefill=4096, context=4096, layers=0)
+            r = bench_moe.run(margs)
+            extras["moe"] = None if r is None else {"moe_decode_tok_s": r["value"], "moe_ms_per_step": r["ms_per_step"],
+                                                    "moe_prefill_tok_s": r["extra"]["prefill_tok_s"], "moe_config": r["config"]}
+        except Exception as e:      # noqa: BLE001
+            extras["moe"] = {"moe_error": f"{type(e).__name__}: {e}"[:200]}
+        gc.collect()
+        torch.cuda.empty_cache()
+
     if rank == 0:
         value = B / (dev_ms * 1e-3)
         out = {
             "metric": f"{cfg.name.replace('-shape', '').replace('-', '_').replace('llama_3', 'llama3')}_q4k_decode_tok_s_bs{B}", "value": round(value, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(dev_ms, 4), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None if base is None else round(value / base["value"], 4), "dtype": "bf16",
+            "data": "synthetic",
             "config": {"model": cfg.name, "weights": "Q4_K (embeddings/output Q6_K), seeded N(0,0.02)",
                        "global_batch": B, "seq_len": P, "decode_context": f"{P}+", "kv_cache": "paged fp16, 16-token pages",
                        "parallelism": f"tp{world}", "l2": "inputs larger than L2 (weights + KV cache >> 126 MB)",
@@ -278,7 +355,14 @@ def main():
             "extra": {"decode_tok_s_bs1": round(1.0 / (bs1_ms * 1e-3), 1), "ms_per_step_bs1": round(bs1_ms, 4),
                       "launches_per_step_bs1": launches_bs1, "prefill_ttft_ms": round(ttft_ms, 3),
                       "prefill_tok_s": round(P / (ttft_ms * 1e-3), 1), "load_s": round(load_s, 1),
-                      "weight_bytes_per_gpu": eng.weight_bytes(), **({"replicas": replicas} if replicas else {})},
+                      "weight_bytes_per_gpu": weight_bytes, "prefill_scratch_bytes_per_gpu": scratch_bytes,
+                      "launches_per_step_bs64": launches_per_step,
+                      "baseline": ({"error": base_err} if base is None else
+                                   {"decode_tok_s": round(base["value"], 1), "ms_per_step": round(base["ms_per_step"], 4),
+                                    "e2e_tok_s": round(base["e2e_value"], 1), "weight_bytes_per_gpu": base["weight_bytes_per_gpu"],
+                                    "stack": "torch.matmul (cuBLAS) + SDPA + NCCL all-reduce + CUDA graph"}),
+                      **{k: v for e in extras.values() if e for k, v in e.items()},
+                      **({"replicas": replicas} if replicas else {})},
         }
         print(json.dumps(out))
     if world > 1:

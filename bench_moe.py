@@ -17,16 +17,20 @@ import os
 import time
 
 
-def main():
+def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--batch", type=int, default=256, help="global decode batch")
     ap.add_argument("--prefill", type=int, default=4096)
-    ap.add_argument("--context", type=int, default=128, help="tokens each decode sequence holds before the timed steps")
+    ap.add_argument("--context", type=int, default=4096, help="tokens each decode sequence holds before the timed steps")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; marks the run invalid)")
-    args = ap.parse_args()
+    return ap.parse_args()
+
+
+def run(args) -> dict | None:
+    """The benchmark proper; the process group (when WORLD_SIZE > 1) must already exist.  Returns the record on rank 0."""
     K, W = args.steps, max(args.warmup, 3)
 
     import torch
@@ -39,12 +43,7 @@ def main():
     from openagents_b200.models.weights import PLAN_MOE
 
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
-    torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     cfg, valid = GPT_OSS_20B, True
     if args.layers:
         cfg, valid = cfg.with_(n_layers=args.layers), False
@@ -130,8 +129,10 @@ def main():
     eng.check_status()
     h2d = (eng.h2d_bytes - h2d_before) // K        # counted by the engine from the tensors it copies: ids, pos, slot,
                                                    # lengths every step, page-table rows when a sequence takes a new page
-    if rank == 0:
-        print(json.dumps({
+    if rank != 0:
+        return None
+    if True:
+        return ({
             "metric": "gpt_oss_20b_moe_decode_tok_s_bs256", "value": round(args.batch / dev_ms * 1000, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(dev_ms, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -144,7 +145,22 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B},
             "gpu_launches": launches,
             "extra": {"prefill_ms_per_chunk": round(prefill_ms, 3), "prefill_tok_s": round(P * world / prefill_ms * 1000, 1),
-                      "load_s": round(load_s, 1), "weight_bytes_per_gpu": eng.weight_bytes()}}))
+                      "load_s": round(load_s, 1), "weight_bytes_per_gpu": eng.weight_bytes()}})
+
+
+def main():
+    args = parse()
+    import torch
+    import torch.distributed as dist
+    world, local = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    out = run(args)
+    if out is not None:
+        print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
 

@@ -16,15 +16,9 @@ import json
 import os
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--steps", type=int, default=3)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--global-batch", type=int, default=512)
-    ap.add_argument("--micro-batch", type=int, default=16)
-    ap.add_argument("--seq-len", type=int, default=1024)
-    ap.add_argument("--gpus", type=int, default=1)
-    args = ap.parse_args()
+def run(steps: int, warmup: int, global_batch: int = 512, micro_batch: int = 16, seq_len: int = 1024) -> dict | None:
+    """Time ``steps`` optimizer steps after ``warmup``; the process group (when WORLD_SIZE > 1) must already exist.
+    Returns the result record on rank 0, None elsewhere."""
     import torch
     import torch.distributed as dist
     from bench import ClockSampler
@@ -33,11 +27,8 @@ def main():
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    cfg = TrainConfig(model=GPT2_SMALL, global_batch=args.global_batch, micro_batch=args.micro_batch, seq_len=args.seq_len)
+    cfg = TrainConfig(model=GPT2_SMALL, global_batch=global_batch, micro_batch=micro_batch, seq_len=seq_len)
     tr = Trainer(cfg, dev, rank, world)
     batches = [synthetic_batch(cfg, tr.accum, s, rank, dev) for s in range(2)]
     batches = [(a.pin_memory(), b.pin_memory()) for a, b in batches]
@@ -52,7 +43,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    losses = [step(i) for i in range(args.warmup)]
+    losses = [step(i) for i in range(warmup)]
     tr.check_status()
     n0 = tr.model.kernel_launches
     sampler = ClockSampler(local)
@@ -60,33 +51,54 @@ def main():
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
-        losses.append(step(args.warmup + i))
+    for i in range(steps):
+        losses.append(step(warmup + i))
     e1.record()
     barrier()
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = e0.elapsed_time(e1) / steps
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     tr.check_status()
-    if rank == 0:
-        toks = cfg.global_batch * cfg.seq_len
-        # 6 * params * tokens (matmul FLOPs incl. the tied LM head) + attention 12 * L * T * d per token
-        m = cfg.model
-        flops = 6.0 * (12 * m.n_layers * m.d_model ** 2 + m.vocab * m.d_model) * toks + 12.0 * m.n_layers * cfg.seq_len * m.d_model * toks
-        print(json.dumps({
-            "metric": "gpt2_small_train_tok_s", "value": round(toks / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 2), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"model": m.name, "global_batch": cfg.global_batch, "seq_len": cfg.seq_len, "micro_batch": cfg.micro_batch,
-                       "parallelism": f"dp{world}+zero{cfg.zero_stage}", "optimizer": "AdamW lr 6e-4 betas (0.9,0.95) wd 0.1 clip 1.0",
-                       "timed_region": "includes per-step H2D of token ids from pinned memory and D2H of the loss"},
-            "clocks": clocks, "gpu_launches": tr.model.kernel_launches - n0,
-            "extra": {"model_tflops_per_gpu": round(flops / (ms * 1e-3) / 1e12 / world, 1), "first_loss": round(losses[0], 4),
-                      "last_loss": round(losses[-1], 4),
-                      "h2d_bytes_per_step": 2 * 8 * tr.accum * cfg.micro_batch * cfg.seq_len, "d2h_bytes_per_step": 4 * tr.accum}}))
+    if rank != 0:
+        return None
+    toks = cfg.global_batch * cfg.seq_len
+    # 6 * params * tokens (matmul FLOPs incl. the tied LM head) + attention 12 * L * T * d per token
+    m = cfg.model
+    flops = 6.0 * (12 * m.n_layers * m.d_model ** 2 + m.vocab * m.d_model) * toks + 12.0 * m.n_layers * cfg.seq_len * m.d_model * toks
+    return {
+        "metric": "gpt2_small_train_tok_s", "value": round(toks / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 2), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": m.name, "global_batch": cfg.global_batch, "seq_len": cfg.seq_len, "micro_batch": cfg.micro_batch,
+                   "parallelism": f"dp{world}+zero{cfg.zero_stage}", "optimizer": "AdamW lr 6e-4 betas (0.9,0.95) wd 0.1 clip 1.0",
+                   "timed_region": "includes per-step H2D of token ids from pinned memory and D2H of the loss"},
+        "clocks": clocks, "gpu_launches": tr.model.kernel_launches - n0,
+        "extra": {"model_tflops_per_gpu": round(flops / (ms * 1e-3) / 1e12 / world, 1), "first_loss": round(losses[0], 4),
+                  "last_loss": round(losses[-1], 4),
+                  "h2d_bytes_per_step": 2 * 8 * tr.accum * cfg.micro_batch * cfg.seq_len, "d2h_bytes_per_step": 4 * tr.accum}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--global-batch", type=int, default=512)
+    ap.add_argument("--micro-batch", type=int, default=16)
+    ap.add_argument("--seq-len", type=int, default=1024)
+    ap.add_argument("--gpus", type=int, default=1)
+    args = ap.parse_args()
+    import torch
+    import torch.distributed as dist
+    world, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    out = run(args.steps, max(args.warmup, 3), args.global_batch, args.micro_batch, args.seq_len)
+    if out is not None:
+        print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
 
