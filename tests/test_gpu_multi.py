@@ -250,6 +250,62 @@ def test_dp2_trainer_matches_single_rank(tmp_path):
     assert abs(losses[-1] - sum(res["losses"][-1:]) ) < 0.3
 
 
+# ---------------------------------------------------------------- a rank leaves between steps (two GPUs, no multicast)
+
+def _rank_leaves(rank, world, out_dir):
+    import time
+    import torch.distributed as dist
+    from openagents_b200.parallel.failure import (CollectiveFailure, HeartbeatBoard, PeerLeft, RoundLedger, check_collectives,
+                                                  latest_sealed_checkpoint)
+    from openagents_b200.parallel.symm import SymmHeap
+    from openagents_b200.train import checkpoint as ck
+    dev = torch.device("cuda", rank)
+    heap = SymmHeap(1 << 20, dev, wait_s=0.2, multicast=False)      # plain peer stores: no multicast object holds a rank's memory
+    assert not heap.uses_multicast
+    store = dist.distributed_c10d._get_default_store()
+    board = HeartbeatBoard(store, rank, world, ttl_s=30.0)
+    # step 1: a healthy collective, then rank 0 seals a checkpoint
+    board.beat(1)
+    heap.barrier()
+    torch.cuda.synchronize()
+    assert heap.status() == (0, 0)
+    state = torch.arange(8, dtype=torch.float32)
+    root = out_dir + "/ckpt"
+    if rank == 0:
+        d = root + "/step00000001"
+        files = ck.save_shard(d, 0, state, torch.zeros(8), torch.zeros(8))
+        ck.write_manifest(d, files, run_ref="run.t", window_ref="run.t.w0", step=1, world_size=1, zero_stage=2, n_total=8, shard=8,
+                          term=1, train_config={}, model_config={})
+    if rank == 1:
+        board.leave(2)                      # between steps: none of this rank's kernels or collectives is in flight
+        store.wait(["rank0_done"])          # stays mapped (its memory is a peer's store target) until rank 0 has finished
+        return
+    board.beat(2)
+    deadline = time.time() + 5.0
+    with pytest.raises(PeerLeft):           # found on the host, before any launch
+        while time.time() < deadline:
+            board.check_peers(2)
+            time.sleep(0.02)
+    # a launcher that went ahead anyway: the collective gives up at its limit and reports, the context survives
+    heap.barrier()
+    torch.cuda.synchronize()
+    with pytest.raises(CollectiveFailure) as e:
+        check_collectives(heap, rank)
+    assert e.value.status == 3 and e.value.timeouts == 1
+    assert float((torch.ones(4, device=dev) * 3).sum()) == 12.0
+    ev = RoundLedger("run.t.w0.step2", world).on_failure(1, e.value.status)
+    assert ev["decision"] == "abort_round" and ev["bannedForRound"] == [1]
+    man, master, _, _ = ck.load_full(latest_sealed_checkpoint(root))      # discard the step, back to the sealed state
+    assert man["step"] == 1 and torch.equal(master, state)
+    store.set("rank0_done", "1")
+
+
+def test_rank_leaves_between_steps_two_gpus(tmp_path, monkeypatch):
+    _need(2)
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
+    _run(_rank_leaves, 2, str(tmp_path))
+
+
 # ---------------------------------------------------------------- failure path (one GPU)
 
 def test_wait_times_out_and_context_survives():
