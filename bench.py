@@ -176,8 +176,36 @@ def main():
         if world > 1:
             dist.destroy_process_group()
         return
+    # The model is served from a GGUF FILE: rank 0 writes the seeded Q4_K / Q6_K tensors once (standard block bytes, this
+    # package's C++ writer), every rank then opens the file with the C++ reader and loads its shard from it.
+    gguf_path, gguf_write_s, src, weights_from = None, None, None, "gguf file"
+    try:
+        import tempfile
+        from openagents_b200.gguf import GGUFWriter
+        from openagents_b200.models.qweight import GGUFSource
+        from openagents_b200.models.weights import tensor_specs
+        gguf_path = os.path.join(tempfile.gettempdir(), f"b200_bench_{cfg.name}_{cfg.n_layers}l_q4k.gguf")
+        if rank == 0 and not os.path.exists(gguf_path):
+            tw = time.time()
+            rs = RandomSource(cfg, PLAN_Q4_K, 0, dev)
+            wr = GGUFWriter(gguf_path + ".tmp")
+            for k_, v_ in cfg.to_gguf_metadata().items():
+                wr.add_meta(k_, v_)
+            for spec in tensor_specs(cfg):
+                r_ = rs.get(spec.name)
+                wr.add_tensor_raw(spec.name, int(r_.type), spec.shape, r_.data.cpu().numpy())
+            wr.write()
+            os.replace(gguf_path + ".tmp", gguf_path)
+            gguf_write_s = time.time() - tw
+        barrier()
+        src = GGUFSource(gguf_path, dev)
+    except Exception as e:      # noqa: BLE001 - no room for the file, read-only temp dir, ...: generate the same tensors in memory
+        weights_from = f"generated in memory ({type(e).__name__}: {e})"[:160]
+        if world > 1:
+            dist.barrier()
+        src = RandomSource(cfg, PLAN_Q4_K, 0, dev)
     t0 = time.time()
-    eng = LlamaEngine(cfg, RandomSource(cfg, PLAN_Q4_K, 0, dev), device=dev, max_batch=B + 1, max_ctx=max_ctx,
+    eng = LlamaEngine(cfg, src, device=dev, max_batch=B + 1, max_ctx=max_ctx,
                       max_tokens=4 * P, tp_rank=rank, tp_world=world, comm=comm)
     load_s = time.time() - t0
 
@@ -354,7 +382,9 @@ def main():
             "gpu_launches": launches,
             "extra": {"decode_tok_s_bs1": round(1.0 / (bs1_ms * 1e-3), 1), "ms_per_step_bs1": round(bs1_ms, 4),
                       "launches_per_step_bs1": launches_bs1, "prefill_ttft_ms": round(ttft_ms, 3),
-                      "prefill_tok_s": round(P / (ttft_ms * 1e-3), 1), "load_s": round(load_s, 1),
+                      "prefill_tok_s": round(P / (ttft_ms * 1e-3), 1), "load_s": round(load_s, 1), "weights_from": weights_from,
+                      "gguf_file_bytes": os.path.getsize(gguf_path) if gguf_path and os.path.exists(gguf_path) else None,
+                      "gguf_write_s": None if gguf_write_s is None else round(gguf_write_s, 1),
                       "weight_bytes_per_gpu": weight_bytes, "prefill_scratch_bytes_per_gpu": scratch_bytes,
                       "launches_per_step_bs64": launches_per_step,
                       "baseline": ({"error": base_err} if base is None else

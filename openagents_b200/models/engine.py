@@ -153,10 +153,11 @@ class _Layer:
     window: int
 
 
-def _f32(src: WeightSource, name: str) -> torch.Tensor | None:
+def _f32(src: WeightSource, name: str, device=None) -> torch.Tensor | None:
     if not src.has(name):
         return None
-    return src.get(name).to_float().contiguous()
+    x = src.get(name).to_float().contiguous()
+    return x if device is None else x.to(device)
 
 
 class LlamaEngine:
@@ -210,37 +211,37 @@ class LlamaEngine:
     def _load(self, src: WeightSource):
         cfg, dev = self.cfg, self.device
         emb = src.get("token_embd.weight")
-        self.emb = QWeight.from_raw(emb)
+        self.emb = QWeight.from_raw(emb).to(dev)
         self.emb_type = {ops.WT_Q6KR: ops.EMB_Q6KR, ops.WT_Q8R: ops.EMB_Q8R, ops.WT_BF16: ops.EMB_BF16}.get(self.emb.wt)
         if self.emb_type is None:
             # Q4_K / MXFP4 tables are not gathered directly; keep them as bf16.
-            x = emb.to_float().to(torch.bfloat16).contiguous()
+            x = emb.to_float().to(torch.bfloat16).contiguous().to(dev)
             self.emb = QWeight(ops.WT_BF16, x.shape[0], x.shape[1], x, None, emb.type)
             self.emb_type = ops.EMB_BF16
         self.layers: list[_Layer] = []
         for i in range(cfg.n_layers):
             p = f"blk.{i}."
             q, k, v = (self._shard_rows(src.get(p + n + ".weight")) for n in ("attn_q", "attn_k", "attn_v"))
-            wqkv = QWeight.from_raw(RawTensor.cat_rows([q, k, v]))
+            wqkv = QWeight.from_raw(RawTensor.cat_rows([q, k, v])).to(dev)
             bqkv = None
             if src.has(p + "attn_q.bias"):
-                bqkv = torch.cat([self._shard_rows(src.get(p + n + ".bias")).to_float() for n in ("attn_q", "attn_k", "attn_v")]).contiguous()
-            wo = QWeight.from_raw(self._shard_cols(src.get(p + "attn_output.weight")))
-            bo = _f32(src, p + "attn_output.bias")
-            sinks = _f32(src, p + "attn_sinks.weight")
+                bqkv = torch.cat([self._shard_rows(src.get(p + n + ".bias")).to_float() for n in ("attn_q", "attn_k", "attn_v")]).contiguous().to(dev)
+            wo = QWeight.from_raw(self._shard_cols(src.get(p + "attn_output.weight"))).to(dev)
+            bo = _f32(src, p + "attn_output.bias", dev)
+            sinks = _f32(src, p + "attn_sinks.weight", dev)
             if sinks is not None and self.world > 1:
                 sinks = sinks[self.rank * self.Hq:(self.rank + 1) * self.Hq].contiguous()
             wgu, wdown = self._load_ffn(src, p, i)
-            self.layers.append(_Layer(_f32(src, p + "attn_norm.weight"), wqkv, bqkv, wo, bo, sinks,
-                                      _f32(src, p + "ffn_norm.weight"), wgu, wdown,
+            self.layers.append(_Layer(_f32(src, p + "attn_norm.weight", dev), wqkv, bqkv, wo, bo, sinks,
+                                      _f32(src, p + "ffn_norm.weight", dev), wgu, wdown,
                                       cfg.sliding_window if cfg.layer_uses_window(i) else 0))
-        self.out_norm = _f32(src, "output_norm.weight")
+        self.out_norm = _f32(src, "output_norm.weight", dev)
         out = src.get("token_embd.weight" if cfg.tied_embeddings else "output.weight")
         self.V_local = out.shape[0] // self.world if out.shape[0] % self.world == 0 else out.shape[0]
         self.vocab_sharded = self.world > 1 and out.shape[0] % self.world == 0
         if self.vocab_sharded:
             out = out.rows(self.rank * self.V_local, (self.rank + 1) * self.V_local)
-        self.wout = QWeight.from_raw(out)
+        self.wout = QWeight.from_raw(out).to(dev)
         torch.cuda.synchronize(dev)
 
     def _load_ffn(self, src: WeightSource, p: str, layer: int):
@@ -249,8 +250,8 @@ class LlamaEngine:
         prefill GEMM."""
         g = self._shard_rows(src.get(p + "ffn_gate.weight"))
         u = self._shard_rows(src.get(p + "ffn_up.weight"))
-        return (QWeight.from_raw(RawTensor.interleave_rows(g, u)),
-                QWeight.from_raw(self._shard_cols(src.get(p + "ffn_down.weight"))))
+        return (QWeight.from_raw(RawTensor.interleave_rows(g, u)).to(self.device),
+                QWeight.from_raw(self._shard_cols(src.get(p + "ffn_down.weight"))).to(self.device))
 
     def weight_bytes(self) -> int:
         n = self.wout.nbytes()

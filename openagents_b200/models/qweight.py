@@ -158,6 +158,13 @@ class QWeight:
     def quantized(self) -> bool:
         return self.wt != ops.WT_BF16
 
+    def to(self, device) -> "QWeight":
+        """The same weight with its planes on ``device`` (a source on the host repacks there; the kernels need the GPU)."""
+        if self.main.device == torch.device(device):
+            return self
+        return QWeight(self.wt, self.N, self.K, self.main.to(device), None if self.plane2 is None else self.plane2.to(device),
+                       self.src_type)
+
     def nbytes(self) -> int:
         return self.main.numel() * self.main.element_size() + (0 if self.plane2 is None else self.plane2.numel() * self.plane2.element_size())
 
