@@ -391,21 +391,26 @@ B200_API int b200_rope_kv(const float* qkv, const int* pos, const int* slot, flo
 
 // ------------------------------------------------------------------ SwiGLU / add / bias
 
-// gu fp32 [T][2F] (gate then up) -> bf16 and/or fp32 act [T][F]
-__global__ void swiglu_kernel(const float* __restrict__ gu, int F, __nv_bfloat16* __restrict__ ob,
-                              float* __restrict__ of) {
+// gu fp32 [T][2F] with (gate_i, up_i) in adjacent columns (the row order of the fused gate/up matrix) -> bf16 and/or
+// fp32 act [T][F].  zero_after: gu is cleared behind the read, for a producer that accumulates into it with K splits.
+__global__ void swiglu_kernel(float* __restrict__ gu, int F, __nv_bfloat16* __restrict__ ob, float* __restrict__ of,
+                              int zero_after) {
   pdl_trigger();
   pdl_wait();
   const size_t t = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= F) return;
-  const float v = silu(gu[t * 2 * F + i]) * gu[t * 2 * F + F + i];
+  float2* p = (float2*)(gu + t * 2 * F) + i;
+  const float2 g = *p;
+  if (zero_after) *p = make_float2(0.f, 0.f);
+  const float v = silu(g.x) * g.y;
   if (ob) ob[t * F + i] = __float2bfloat16(v);
   if (of) of[t * F + i] = v;
 }
-B200_API int b200_swiglu(const float* gu, int T, int F, void* ob, float* of, cudaStream_t st) {
+B200_API int b200_swiglu(float* gu, int T, int F, void* ob, float* of, int zero_after, cudaStream_t st) {
+  if ((uintptr_t)gu % 8) return B200_ERR_BAD_ARG;
   dim3 grid((F + 255) / 256, T);
-  return launch_pdl(swiglu_kernel, grid, dim3(256), 0, st, gu, F, (__nv_bfloat16*)ob, of);
+  return launch_pdl(swiglu_kernel, grid, dim3(256), 0, st, gu, F, (__nv_bfloat16*)ob, of, zero_after);
 }
 
 __global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, size_t n) {

@@ -563,13 +563,23 @@ class LlamaEngine:
     def _ffn_dense(self, li: int, L: _Layer, T: int, x, hb_d, hb_f, gu, fused: bool = False, slots: bool = False, table=None) -> int:
         """Feed-forward block on ``hb_d`` (normalised hidden, bf16); adds its output into ``x``.  The gate/up matrix has
         interleaved rows, so SwiGLU runs in the epilogue of its GEMM: no fp32 [T][2F] round trip."""
-        if fused and self._qg(L.wgu):
+        n = 2
+        if fused and self._qg(L.wgu) and (2 * self.F + 127) // 128 >= 74:
             ops.qgemm(L.wgu, hb_d, T, out_bf16=hb_f, ldo=self.F, epi=ops.QEPI_SWIGLU, status=self.status)
+        elif fused and self._qg(L.wgu):
+            # Few row tiles (a tensor-parallel shard): a tile per CTA would leave most SMs idle for the whole K loop, so K is
+            # split, the partial sums add up in fp32 and a small kernel applies SwiGLU (and clears the buffer behind it).
+            if not getattr(self, "_gu_zeroed", False):
+                self.gu.zero_()
+                self._gu_zeroed = True
+            ops.qgemm(L.wgu, hb_d, T, out_f32=gu, ldo=2 * self.F, epi=ops.QEPI_ADD, status=self.status)
+            ops.swiglu(gu, self.F, ob=hb_f, zero_after=True)
+            n = 3
         else:
             ops.gemm_bf16(hb_d, self._dense(L.wgu), T, 2 * self.F, L.wgu.K, lda=hb_d.stride(0), ldb=L.wgu.K, out_bf16=hb_f,
                           ldc=self.F, act=ops.ACT_SWIGLU_PAIR, status=self.status)
         self._row_parallel(hb_f, L.wdown, T, x, None, fused, slots, table)
-        return 2
+        return n
 
     def _head(self, rows: torch.Tensor, nb: int, greedy: bool = True):
         """Final norm + LM head on ``nb`` rows of fp32 hidden state -> logits (and arg-max ids)."""

@@ -27,7 +27,7 @@ _SIGS = {
     "b200_quantize_x": [_P, c_int, c_int, _P, _P, _P, _P],
     "b200_rope_kv": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, _P, c_int, _P],
     "b200_rope_table": [_P, c_int, c_int, c_float, _P],
-    "b200_swiglu": [_P, c_int, c_int, _P, _P, _P],
+    "b200_swiglu": [_P, c_int, c_int, _P, _P, c_int, _P],
     "b200_add_inplace": [_P, _P, c_size_t, _P],
     "b200_argmax": [_P, c_int, c_int, _P, _P, c_int, _P, _P],
     "b200_sample_topk": [_P, c_int, c_int, c_float, c_int, c_float, _P, _P, _P, _P],
@@ -144,9 +144,10 @@ def rope_table(n_pos, hd, theta, device):
     return tab
 
 
-def swiglu(gu, F, ob=None, of=None):
+def swiglu(gu, F, ob=None, of=None, zero_after=False):
+    """``gu`` fp32 [T, 2F] holds (gate_i, up_i) in adjacent columns; writes silu(gate) * up; ``zero_after`` clears ``gu``."""
     T = gu.shape[0]
-    _check(lib().b200_swiglu(_p(gu), T, F, _p(ob), _p(of), _st()), "swiglu")
+    _check(lib().b200_swiglu(_p(gu), T, F, _p(ob), _p(of), int(zero_after), _st()), "swiglu")
 
 
 def add_inplace(x, y):

@@ -412,9 +412,11 @@ def test_swiglu_add_cast_transpose():
     gu = _randn(T, 2 * F, seed=26)
     of = torch.empty((T, F), device=DEV)
     ob = torch.empty((T, F), dtype=torch.bfloat16, device=DEV)
+    ref = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]           # (gate_i, up_i) sit in adjacent columns
     ops.swiglu(gu, F, ob=ob, of=of)
-    ref = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
     assert torch.allclose(of, ref, atol=1e-5, rtol=1e-5) and torch.allclose(ob.float(), ref, atol=2e-2, rtol=1e-2)
+    ops.swiglu(gu, F, ob=ob, zero_after=True)
+    assert torch.allclose(ob.float(), ref, atol=2e-2, rtol=1e-2) and float(gu.abs().max()) == 0.0
     a, b = _randn(1001, seed=27), _randn(1001, seed=28)
     c = a.clone()
     ops.add_inplace(c, b)
