@@ -18,8 +18,8 @@ import torch.nn.functional as F
 
 
 class TorchLlama:
-    def __init__(self, cfg, src, device, rank: int = 0, world: int = 1, max_batch: int = 64, max_ctx: int = 4096):
-        self.cfg, self.dev, self.rank, self.world = cfg, device, rank, world
+    def __init__(self, cfg, src, device, rank: int = 0, world: int = 1, max_batch: int = 64, max_ctx: int = 4096, group=None):
+        self.cfg, self.dev, self.rank, self.world, self.group = cfg, device, rank, world, group
         self.Hq, self.Hkv, self.hd = cfg.n_heads // world, cfg.n_kv_heads // world, cfg.head_dim
         self.F = cfg.ffn // world
         bf = torch.bfloat16
@@ -94,21 +94,21 @@ class TorchLlama:
             o = F.scaled_dot_product_attention(q, kc, vc, attn_mask=mask, enable_gqa=True)
             a = o.transpose(1, 2).reshape(B, T, self.Hq * self.hd) @ wo.t()
             if self.world > 1:
-                dist.all_reduce(a)
+                dist.all_reduce(a, group=self.group)
             x = x + a
             h = self._norm(x, g2)
             gu = h @ wgu.t()
             m = (F.silu(gu[..., : self.F]) * gu[..., self.F:]) @ wd.t()
             if self.world > 1:
-                dist.all_reduce(m)
+                dist.all_reduce(m, group=self.group)
             x = x + m
         logits = self._norm(x[:, -1], self.out_norm) @ self.wout.t()
         val, idx = logits.float().max(-1)
         if self.world > 1:          # vocabulary is sharded: merge the per-shard winners
             vals = [torch.empty_like(val) for _ in range(self.world)]
             ids_ = [torch.empty_like(idx) for _ in range(self.world)]
-            dist.all_gather(vals, val)
-            dist.all_gather(ids_, idx + self.rank * self.V_local)
+            dist.all_gather(vals, val, group=self.group)
+            dist.all_gather(ids_, idx + self.rank * self.V_local, group=self.group)
             vals, ids_ = torch.stack(vals), torch.stack(ids_)
             idx = ids_.gather(0, vals.argmax(0, keepdim=True))[0]
         return idx
@@ -155,10 +155,13 @@ class DecodeGraph:
         self.graph.replay()
 
 
-def run_decode_baseline(cfg, src, dev, rank, world, B, P, K, W, prompts, barrier, max_over_ranks, sampler=None):
+def run_decode_baseline(cfg, src, dev, rank, world, B, P, K, W, prompts, barrier, max_over_ranks, sampler=None, group=None, total_batch=None):
     """Prefill ``B`` prompts of ``P`` tokens (untimed), then time ``K`` greedy decode steps of the whole batch after ``W``
-    warm-up steps.  Returns (tokens/s, ms per step, end-to-end tokens/s with per-step host copies, clocks)."""
-    model = TorchLlama(cfg, src, dev, rank, world, max_batch=B, max_ctx=P + 2 * (K + W) + 16)
+    warm-up steps.  Returns (tokens/s, ms per step, end-to-end tokens/s with per-step host copies, clocks).  ``rank`` /
+    ``world`` / ``group`` describe ONE tensor-parallel replica; with several replicas side by side ``B`` is this replica's
+    share and ``total_batch`` the number of sequences all replicas advance per step."""
+    total_batch = total_batch or B
+    model = TorchLlama(cfg, src, dev, rank, world, max_batch=B, max_ctx=P + 2 * (K + W) + 16, group=group)
     first = torch.zeros(B, dtype=torch.long, device=dev)
     ar = torch.arange(model.max_ctx, device=dev)
     for b0 in range(0, B, 4):
@@ -196,7 +199,7 @@ def run_decode_baseline(cfg, src, dev, rank, world, B, P, K, W, prompts, barrier
         host_ids.copy_(g.out[:, None].cpu())
     torch.cuda.synchronize()
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / K
-    res = {"value": B / (ms * 1e-3), "ms_per_step": ms, "e2e_value": B / (e2e_ms * 1e-3), "e2e_ms_per_step": e2e_ms, "clocks": clocks,
+    res = {"value": total_batch / (ms * 1e-3), "ms_per_step": ms, "e2e_value": total_batch / (e2e_ms * 1e-3), "e2e_ms_per_step": e2e_ms, "clocks": clocks,
            "weight_bytes_per_gpu": model.weight_bytes()}
     del g, model
     torch.cuda.empty_cache()

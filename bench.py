@@ -104,6 +104,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; marks the run invalid)")
     ap.add_argument("--extras", default="train,moe", help="side benchmarks reported under extra: comma list of train, moe, or none")
     ap.add_argument("--no-baseline", action="store_true", help="skip the PyTorch baseline arm (vs_baseline stays null)")
+    ap.add_argument("--tp", type=int, default=0, help="ranks per tensor-parallel replica (0: all ranks up to 4; 8 GPUs then run "
+                    "two replicas of 4, each serving half of the batch)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -134,14 +136,32 @@ def main():
         cfg = cfg.with_(n_layers=args.layers)
         valid = False
     B, P = args.batch, args.prompt_len
+    # Layout: ``dp`` replicas of ``tp`` ranks.  A replica shards the model (tensor parallel, this package's fused kernels
+    # over the symmetric heap) and serves B / dp of the sequences; replicas never talk to each other.  Beyond four ranks
+    # the per-layer all-reduce latency outweighs what a thinner weight shard saves for a model of this size, so eight
+    # GPUs run as two replicas of four unless --tp says otherwise.
+    tp = args.tp if args.tp > 0 else (world if world <= 4 else 4)
+    if world % tp or B % (world // tp):
+        raise SystemExit(f"--tp {tp} does not divide {world} ranks / batch {B}")
+    dp = world // tp
+    tp_rank, replica, Bl = rank % tp, rank // tp, B // dp
+    layout = f"tp{tp}" if dp == 1 else (f"dp{dp}" if tp == 1 else f"dp{dp}xtp{tp}")
+    tp_group = None
+    if world > 1 and dp > 1 and tp > 1:
+        for r0 in range(0, world, tp):          # every rank creates every group, in the same order
+            grp = dist.new_group(list(range(r0, r0 + tp)))
+            if r0 == replica * tp:
+                tp_group = grp
     comm = None
-    if world > 1:    # symmetric heap: the fp32 residual stream and the bf16 all-gathered activations of a prefill chunk
+    if tp > 1:    # symmetric heap: the fp32 residual stream and the bf16 all-gathered activations of a prefill chunk
         from openagents_b200.parallel.tp import TPComm
-        comm = TPComm(rank, world, dev, heap_bytes=(4 * P + world) * cfg.d_model * 6 + (64 << 20))
+        comm = TPComm(tp_rank, tp, dev, heap_bytes=(4 * P + tp) * cfg.d_model * 6 + (64 << 20), group=tp_group)
     total_steps = 2 * (K + W) + 8
     max_ctx = P + total_steps + PAGE
     g = torch.Generator().manual_seed(1234)
     prompts = torch.randint(0, cfg.vocab, (B + 1, P), generator=g)
+    extra_prompt = prompts[B]
+    my_prompts = prompts[replica * Bl:(replica + 1) * Bl]
 
     def barrier():
         if world > 1:
@@ -157,8 +177,8 @@ def main():
 
     def baseline_arm(with_clocks: bool):
         from baseline.llama_torch import run_decode_baseline
-        return run_decode_baseline(cfg, RandomSource(cfg, PLAN_Q4_K, 0, dev), dev, rank, world, B, P, K, W, prompts[:B], barrier,
-                                   max_over_ranks, ClockSampler(local) if with_clocks else None)
+        return run_decode_baseline(cfg, RandomSource(cfg, PLAN_Q4_K, 0, dev), dev, tp_rank, tp, Bl, P, K, W, my_prompts, barrier,
+                                   max_over_ranks, ClockSampler(local) if with_clocks else None, group=tp_group, total_batch=B)
 
     if args.impl == "baseline":
         r = baseline_arm(True)
@@ -167,7 +187,7 @@ def main():
                               "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(r["ms_per_step"], 4),
                               "higher_is_better": True, "scaling": "strong", "vs_baseline": 1.0, "dtype": "bf16", "data": "synthetic",
                               "config": {"model": cfg.name, "weights": "the product run's Q4_K/Q6_K weights dequantized to bf16",
-                                         "global_batch": B, "seq_len": P, "kv_cache": "contiguous bf16", "parallelism": f"tp{world}",
+                                         "global_batch": B, "seq_len": P, "kv_cache": "contiguous bf16", "parallelism": layout,
                                          "stack": "torch.matmul (cuBLAS) + SDPA + NCCL all-reduce + CUDA graph", "valid": valid},
                               "clocks": r["clocks"],
                               "e2e": {"value": round(r["e2e_value"], 1), "unit": "tokens/s", "ms_per_step": round(r["e2e_ms_per_step"], 4),
@@ -205,53 +225,54 @@ def main():
             dist.barrier()
         src = RandomSource(cfg, PLAN_Q4_K, 0, dev)
     t0 = time.time()
-    eng = LlamaEngine(cfg, src, device=dev, max_batch=B + 1, max_ctx=max_ctx,
-                      max_tokens=4 * P, tp_rank=rank, tp_world=world, comm=comm)
+    eng = LlamaEngine(cfg, src, device=dev, max_batch=Bl + 1, max_ctx=max_ctx,
+                      max_tokens=4 * P, tp_rank=tp_rank, tp_world=tp, comm=comm)
     load_s = time.time() - t0
 
     # ---- prefill TTFT: one 2048-token prompt, device time of the whole forward incl. first arg-max
-    eng.begin(B)
-    eng.forward_tokens([B], [prompts[B, :64].tolist()])      # warm the kernels on a short chunk
-    eng.end(B)
+    X = Bl                                                    # the extra sequence used for time-to-first-token and batch 1
+    eng.begin(X)
+    eng.forward_tokens([X], [extra_prompt[:64].tolist()])    # warm the kernels on a short chunk
+    eng.end(X)
     ttft = []
     for rep in range(3):
-        eng.begin(B)
+        eng.begin(X)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        _, nxt1 = eng.forward_tokens([B], [prompts[B].tolist()])
+        _, nxt1 = eng.forward_tokens([X], [extra_prompt.tolist()])
         e1.record()
         barrier()
         ttft.append(max_over_ranks(e0.elapsed_time(e1)))
         if rep < 2:
-            eng.end(B)
+            eng.end(X)
     ttft_ms = min(ttft[1:])
 
     # ---- batch prefill (untimed): 4 sequences per call
     first = []
-    for b0 in range(0, B, 4):
-        ids = list(range(b0, min(B, b0 + 4)))
+    for b0 in range(0, Bl, 4):
+        ids = list(range(b0, min(Bl, b0 + 4)))
         for i in ids:
             eng.begin(i)
-        _, nxt = eng.forward_tokens(ids, [prompts[i].tolist() for i in ids])
+        _, nxt = eng.forward_tokens(ids, [my_prompts[i].tolist() for i in ids])
         first += nxt.tolist()
     eng.check_status()
 
     gpu_index = local
     # ---- bs1 decode (sequence B, already prefilled)
     tok1 = [int(nxt1[0].item())]
-    last = eng.decode_steps([B], tok1, W)[W - 1].clone()
+    last = eng.decode_steps([X], tok1, W)[W - 1].clone()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     marks = {0: e0}
-    eng.decode_steps([B], [int(last[0].item())], K, on_replay=lambda i: marks[i].record() if i in marks else None)
+    eng.decode_steps([X], [int(last[0].item())], K, on_replay=lambda i: marks[i].record() if i in marks else None)
     e1.record()
     barrier()
     bs1_ms = max_over_ranks(e0.elapsed_time(e1)) / K
     launches_bs1 = eng.launches_per_decode
 
     # ---- bs64 decode: device-timed, self-advancing graph
-    seqs = list(range(B))
+    seqs = list(range(Bl))
     hist = eng.decode_steps(seqs, first, W)
     last = hist[W - 1].tolist()
     sampler = ClockSampler(gpu_index)
@@ -282,24 +303,24 @@ def main():
     e2e_ms = max_over_ranks((time.perf_counter() - t_start) * 1e3) / K
     h2d = (eng.h2d_bytes - h2d_before) // K        # counted by the engine from the tensors it copies: ids, pos, slot,
                                                    # lengths every step, page-table rows when a sequence takes a new page
-    d2h = 4 * B
+    h2d, d2h = h2d * world, 4 * Bl * world         # every rank copies its replica's inputs in and reads the ids back
     eng.check_status()
 
     # ---- N > 1, side measurement: the same global batch served by N independent replicas (whole model per GPU,
     # B / N sequences each), the configuration a model that fits one GPU would be deployed in for throughput.
     # The headline stays the tensor-parallel number; a failure here is reported, not raised.
     replicas = None
-    if world > 1 and B % world == 0 and cfg.d_model <= 4096:
-        Bl, rep_ms, err = B // world, -1.0, ""
+    if tp > 1 and B % world == 0 and cfg.d_model <= 4096:
+        Br, rep_ms, err = B // world, -1.0, ""
         try:                       # local work only in here: a rank that fails must not leave the others in a collective
-            rep = LlamaEngine(cfg, RandomSource(cfg, PLAN_Q4_K, 0, dev), device=dev, max_batch=Bl, max_ctx=max_ctx,
+            rep = LlamaEngine(cfg, RandomSource(cfg, PLAN_Q4_K, 0, dev), device=dev, max_batch=Br, max_ctx=max_ctx,
                               max_tokens=P, tp_rank=0, tp_world=1, comm=None)
             firsts = []
-            for i in range(Bl):
+            for i in range(Br):
                 rep.begin(i)
-                _, nx = rep.forward_tokens([i], [prompts[rank * Bl + i].tolist()])
+                _, nx = rep.forward_tokens([i], [prompts[rank * Br + i].tolist()])
                 firsts += nx.tolist()
-            ids_l = list(range(Bl))
+            ids_l = list(range(Br))
             h = rep.decode_steps(ids_l, firsts, W)
             lastl = h[W - 1].tolist()
             torch.cuda.synchronize()
@@ -317,7 +338,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)                 # slowest rank, and whether any rank failed
         slowest, any_failed = float(t[0].item()), float(t[1].item()) > 0
         replicas = ({"error": err or "a rank failed"} if any_failed else
-                    {"decode_tok_s": round(B / (slowest * 1e-3), 1), "ms_per_step": round(slowest, 4), "batch_per_gpu": Bl,
+                    {"decode_tok_s": round(B / (slowest * 1e-3), 1), "ms_per_step": round(slowest, 4), "batch_per_gpu": Br,
                      "parallelism": f"dp{world} (independent replicas)"})
 
     weight_bytes = eng.weight_bytes()
@@ -374,7 +395,7 @@ def main():
             "data": "synthetic",
             "config": {"model": cfg.name, "weights": "Q4_K (embeddings/output Q6_K), seeded N(0,0.02)",
                        "global_batch": B, "seq_len": P, "decode_context": f"{P}+", "kv_cache": "paged fp16, 16-token pages",
-                       "parallelism": f"tp{world}", "l2": "inputs larger than L2 (weights + KV cache >> 126 MB)",
+                       "parallelism": layout, "batch_per_replica": Bl, "l2": "inputs larger than L2 (weights + KV cache >> 126 MB)",
                        "valid": valid},
             "clocks": clocks,
             "e2e": {"value": round(B / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),

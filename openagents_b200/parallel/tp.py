@@ -18,9 +18,13 @@ from .symm import SymmHeap
 
 class TPComm:
     def __init__(self, rank: int, world: int, device, heap_bytes: int = 1 << 30, multicast: bool | None = None,
-                 wait_s: float = 2.0):
+                 wait_s: float = 2.0, group=None):
+        """``group``: the process group of ONE tensor-parallel replica (default: all ranks); ``rank`` / ``world`` are the
+        position and size within it."""
         self.rank, self.world, self.device = rank, world, torch.device(device)
-        self.heap = SymmHeap(heap_bytes, device, wait_s=wait_s, multicast=multicast)
+        self.heap = SymmHeap(heap_bytes, device, group=group, wait_s=wait_s, multicast=multicast)
+        if (self.heap.rank, self.heap.world) != (rank, world):
+            raise ValueError(f"rank {rank}/{world} does not match the group's {self.heap.rank}/{self.heap.world}")
         self._merge = None
 
     def alloc_tensor(self, shape, dtype):

@@ -9,7 +9,10 @@ by itself in seconds.  Cases: qgemm64, qgemm_lm, gemm, matvec, attn_decode, attn
 engine without graphs, for a per-kernel launch list; ``moe_step``: the same for a 2-layer gpt-oss-20b-shape
 expert engine at batch 256; ``moe_ffn``: one expert layer at 4096 tokens; ``gemm_ar64`` / ``gemm_ar2048``: the
 row-parallel GEMM with its fused all-reduce epilogue; ``gemm_ag2048`` / ``gemm_rs2048``: the sequence-sharded prefill
-pair (norm + all-gather push -> GEMM, GEMM -> reduce-scatter); ``zero_adamw``: the sharded optimizer step.
+pair (norm + all-gather push -> GEMM, GEMM -> reduce-scatter); ``zero_adamw``: the sharded optimizer step;
+``attn_train_fwd`` / ``attn_train_bwd``: training attention at GPT-2-small's shape (16 x 1024 tokens, 12 heads of 64);
+``gemm_mn``: the weight-gradient GEMM (both operands read token-major); ``norm_slots``: the RMSNorm that is the tensor-parallel
+all-reduce, 64 rows of 4096 on a one-rank heap.
 """
 from __future__ import annotations
 
@@ -160,6 +163,32 @@ def main():
             A, B = torch.randn(M, K, device=DEV).bfloat16(), torch.randn(d, K, device=DEV).bfloat16()
             fn = lambda: ops.gemm_bf16(A, B, M, d, K, ldc=d, status=status, sym_mode=ops.SYM_RSCATTER_ROWS, sym=table,
                                        sym_off=x_off, rows_per_rank=M)
+    elif case in ("attn_train_fwd", "attn_train_bwd"):
+        from ..ops import train_ops as tops
+        B, T, H, hd = 16, 1024, 12, 64
+        qkv = (torch.randn(B * T, 3 * H * hd, device=DEV) * 0.5).bfloat16()
+        o, d_o, dqkv = (torch.empty((B * T, H * hd), dtype=torch.bfloat16, device=DEV), (torch.randn(B * T, H * hd, device=DEV) * 0.1).bfloat16(),
+                        torch.empty((B * T, 3 * H * hd), dtype=torch.bfloat16, device=DEV))
+        lse, dsum = torch.empty((B, H, T), device=DEV), torch.empty((B, H, T), device=DEV)
+        tops.attn_train_fwd(qkv, o, lse, B, T, H, hd)
+        if case == "attn_train_fwd":
+            fn = lambda: tops.attn_train_fwd(qkv, o, lse, B, T, H, hd)
+        else:
+            fn = lambda: tops.attn_train_bwd(qkv, o, d_o, lse, dsum, dqkv, B, T, H, hd)
+    elif case == "gemm_mn":
+        # dW = dY^T X of GPT-2-small's feed-forward expansion: 3072 x 768 over 16384 tokens, operands as stored
+        M, N, K = 3072, 768, 16384
+        A, B = torch.randn(K, M, device=DEV).bfloat16(), torch.randn(K, N, device=DEV).bfloat16()
+        out = torch.empty((M, N), device=DEV)
+        fn = lambda: ops.gemm_bf16(A, B, M, N, K, out_f32=out, status=status, mn_major=True)
+    elif case == "norm_slots":
+        from ..parallel.symm import SymmHeap
+        rows, d = 64, 4096
+        heap = SymmHeap(64 << 20, DEV)
+        _, slots_off = heap.alloc_tensor((2, 1, rows, d), torch.float32)
+        part, xres, gain = torch.randn(rows, d, device=DEV), torch.randn(rows, d, device=DEV), torch.ones(d, device=DEV)
+        hb = torch.empty((rows, d), dtype=torch.bfloat16, device=DEV)
+        fn = lambda: ops.rmsnorm(xres, gain, 1e-5, hb=hb, slots=(heap.table, slots_off, rows, part))
     elif case == "zero_adamw":
         # sharded AdamW step on GPT-2-small's 124M parameters, one-rank heap: reduce-scatter + norm, then
         # clip + AdamW + bf16 cast + all-gather push
