@@ -563,185 +563,6 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   if (epi.sym_mode != SYM_NONE) sym_kernel_end_barrier(epi.sym, 0, gridDim.x, epi.wait_ready != 0);
 }
 
-// ---------------------------------------------------------------------------------------------------
-// GEMM with at most 64 rows (decode batches): one 256-column output tile per thread-block CLUSTER, the
-// CTAs of the cluster splitting K.  A 256-wide MMA streams 32 KB of weights per 64-wide K block in the
-// time a 64-wide one streams 8 KB, so wide tiles are what keeps a weight-streaming GEMM on the memory
-// roofline; splitting K inside a cluster puts enough CTAs on the job without reducing partial sums
-// through L2 atomics: after its share of K each CTA sends, for every column slice, its partial rows
-// to the slice's owner through distributed shared memory, and each owner adds the S partials of its
-// slice and runs the normal epilogue (bias, activation, residual, fp32 / bf16 stores) on the sums.
-template <int S>
-__global__ void __launch_bounds__(192) gemm_fewrows_cluster_kernel(const __grid_constant__ CUtensorMap tmA,
-                                                                    const __grid_constant__ CUtensorMap tmB,
-                                                                    const GemmEpi epi, int M, int N, int K,
-                                                                    int* __restrict__ status) {
-  constexpr int BN = 256, STAGES = 5, A_BYTES = 64 * BK * 2, B_BYTES = BN * BK * 2;
-  constexpr int SLICE = BN / S;                       // columns each CTA of the cluster finishes
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* sA = smem;
-  uint8_t* sB = smem + STAGES * A_BYTES;
-  uint64_t* bars = (uint64_t*)(sB + STAGES * B_BYTES);
-  uint64_t* full = bars;
-  uint64_t* empty = bars + STAGES;
-  uint64_t* tfull = bars + 2 * STAGES;
-  uint32_t* tmem_holder = (uint32_t*)(bars + 2 * STAGES + 1);
-  volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
-  float* stage = (float*)smem;                        // after the main loop: [S sources][64 rows][SLICE] fp32 = 64 KB
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  uint32_t crank;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
-  const int n0 = (blockIdx.x / S) * BN;
-  const int KB = (K + BK - 1) / BK;
-  const int kps = (KB + S - 1) / S;
-  const int kb0 = min(KB, (int)crank * kps), kb1 = min(KB, kb0 + kps);
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; s++) {
-      mbar_init(smem_u32(full + s), 1);
-      mbar_init(smem_u32(empty + s), 1);
-    }
-    mbar_init(smem_u32(tfull), 1);
-    *abort_flag = 0;
-    fence_barrier_init();
-    tma_prefetch_desc(&tmA);
-    tma_prefetch_desc(&tmB);
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_holder), BN);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_holder;
-  pdl_trigger();
-  pdl_wait();
-
-  if (warp == 0 && lane == 0) {
-    for (int kb = kb0, it = 0; kb < kb1; kb++, it++) {
-      const int s = it % STAGES;
-      if (!mbar_wait(smem_u32(empty + s), ((it / STAGES) & 1) ^ 1, abort_flag)) break;
-      mbar_expect_tx(smem_u32(full + s), A_BYTES + B_BYTES);
-      tma_load_2d(smem_u32(sA + s * A_BYTES), &tmA, smem_u32(full + s), kb * BK, 0);
-      tma_load_2d(smem_u32(sB + s * B_BYTES), &tmB, smem_u32(full + s), kb * BK, n0);
-    }
-  } else if (warp == 1 && lane == 0) {
-    constexpr uint32_t idesc = idesc_bf16(BM, BN);
-    for (int kb = kb0, it = 0; kb < kb1; kb++, it++) {
-      const int s = it % STAGES;
-      if (!mbar_wait(smem_u32(full + s), (it / STAGES) & 1, abort_flag)) break;
-      tc_fence_after();
-      // the 128-row operand read runs 8 KB past the 64-row A tile into the next stage (or the B region): rows 64..127
-      // of the accumulator are never read
-      const uint64_t ad = smem_desc_sw128(smem_u32(sA + s * A_BYTES));
-      const uint64_t bd = smem_desc_sw128(smem_u32(sB + s * B_BYTES));
-#pragma unroll
-      for (int k = 0; k < BK / 16; k++) umma_bf16(tmem_base, ad + 2 * k, bd + 2 * k, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
-      umma_commit(smem_u32(empty + s));
-    }
-    umma_commit(smem_u32(tfull));
-  }
-
-  // ---- K is done: exchange partial tiles inside the cluster, each CTA finishes one column slice
-  auto cluster_sync = []() {
-    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-  };
-  const int q = warp & 3;                               // tensor-memory lane quarter of an epilogue warp
-  bool ok = true;
-  if (warp >= 2) {
-    ok = mbar_wait(smem_u32(tfull), 0, abort_flag);     // this CTA's accumulator is complete, its ring is no longer read
-    ok = __all_sync(0xffffffffu, ok && !*abort_flag);
-    tc_fence_after();
-  }
-  __syncthreads();
-  cluster_sync();                                       // every CTA of the cluster is past its main loop
-  if (warp >= 2 && q < 2 && ok) {                       // rows 0..63 live in lanes 0..63
-    const int row = q * 32 + lane;
-    const uint32_t stage_addr = smem_u32(stage);
-#pragma unroll 1
-    for (int c = 0; c < BN / 32; c++) {
-      uint32_t r[32];
-      if (kb1 > kb0) {
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
-        tmem_ld_wait();
-      } else {                                          // no K block fell to this CTA: its accumulator was never written
-#pragma unroll
-        for (int j = 0; j < 32; j++) r[j] = 0u;
-      }
-      const uint32_t owner = (uint32_t)(c * 32) / SLICE;
-      const uint32_t off = (((uint32_t)crank * 64 + row) * SLICE + (uint32_t)(c * 32) % SLICE) * 4;
-      uint32_t remote;
-      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(stage_addr + off), "r"(owner));
-#pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(remote + j * 4), "r"(r[j]), "r"(r[j + 1]),
-                     "r"(r[j + 2]), "r"(r[j + 3]) : "memory");
-    }
-    tc_fence_before();
-  }
-  cluster_sync();                                       // all partials have landed
-  if (warp >= 2 && ok) {
-    const int t = threadIdx.x - 64;
-    for (int item = t; item < 64 * (SLICE / 32); item += 128) {
-      const int row = item & 63, ch = item >> 6;
-      float acc[32];
-#pragma unroll
-      for (int j = 0; j < 32; j++) acc[j] = 0.f;
-#pragma unroll 1
-      for (int src = 0; src < S; src++) {
-        const float4* p = (const float4*)(stage + ((size_t)(src * 64 + row) * SLICE + ch * 32));
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-          const float4 v = p[j];
-          acc[4 * j] += v.x; acc[4 * j + 1] += v.y; acc[4 * j + 2] += v.z; acc[4 * j + 3] += v.w;
-        }
-      }
-      uint32_t r[32];
-#pragma unroll
-      for (int j = 0; j < 32; j++) r[j] = __float_as_uint(acc[j]);
-      const int n = n0 + (int)crank * SLICE + ch * 32;
-      if (n < N) {
-        if (epi.act == ACT_SWIGLU_PAIR) { if (row < M) epilogue_row_swiglu(epi, row, n, r); }
-        else epilogue_row(epi, row, n, M, N, r, true);
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, BN);
-  if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, (int)B200_ERR_TIMEOUT_MMA);
-}
-
-template <int S>
-static int launch_cluster(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpi& e, int M, int N, int K, int* status,
-                          cudaStream_t st) {
-  constexpr size_t smem = 1024 + 5 * (64 * BK * 2 + 256 * BK * 2) + 16 * 8;
-  auto kern = gemm_fewrows_cluster_kernel<S>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return (int)err;
-    configured = true;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(((N + 255) / 256) * S);
-  cfg.blockDim = dim3(192);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = S; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = b200_pdl_enabled() ? 2 : 1;
-  return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, e, M, N, K, status);
-}
-
 static int sm_count() {
   static int n = 0;
   if (!n) {
@@ -834,22 +655,6 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   const bool red_ok = sym_mode != SYM_NONE ||
                       (out_f32 && !out_bf16 && !resid_bf16 && act == 0 &&
                        ((accumulate && !resid_f32) || (!accumulate && resid_f32 == out_f32)));
-  // tile_n = -2, at most 64 rows: one 256-column tile per thread-block cluster, K split over its CTAs
-  // (gemm_fewrows_cluster_kernel), with the largest cluster that still fits the GPU in one wave.  Opt-in:
-  // measured inside CUDA graphs at 64 rows it is slower than the persistent kernel with K splits added
-  // through L2 (output projection 32.5 us against 14.9, down 50.1 against 28.4, QKV 21.8 against 17.2).
-  int cluster_s = 0;
-  if (tile_n == -2) {
-    if (M > 64 || split_k > 0 || sym_mode != SYM_NONE || ag_rows_per_rank != 0) return B200_ERR_BAD_ARG;
-    tile_n = 0;
-    const int tn = (N + 255) / 256, kbt = (K + BK - 1) / BK;
-    for (int c = 8; c >= 2; c >>= 1)
-      if (tn * c <= 148 && kbt / c >= 4) {
-        cluster_s = c;
-        break;
-      }
-    if (cluster_s) tile_n = 256;       // else: the shape does not suit a cluster, the usual choice below applies
-  }
   if (tile_n == 0) {
     const long tiles256 = (long)((N + 255) / 256) * tiles_m, tiles128 = (long)((N + 127) / 128) * tiles_m;
     if (M <= 64 && !swap) {
@@ -865,7 +670,7 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
     }
   }
   CUtensorMap ta, tb;
-  const bool few_rows = M <= 64 && (gemm_deep_enabled() || cluster_s);      // 64-row A box, deeper pipeline
+  const bool few_rows = M <= 64 && gemm_deep_enabled();      // 64-row A box, deeper pipeline
   int rc = make_tmap_2d(&ta, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, few_rows ? 64 : BM, BK, true);
   if (rc) return rc;
   rc = make_tmap_2d(&tb, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, (uint32_t)tile_n, BK, true);
@@ -875,7 +680,7 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
   e.resid_bf16 = (const __nv_bfloat16*)resid_bf16; e.ldc = ldc; e.act = act; e.accumulate = accumulate;
   e.sym_mode = sym_mode; e.rows_per_rank = rows_per_rank > 0 ? rows_per_rank : 1; e.sym_off = sym_off;
   const long n_out_tiles = (long)((N + tile_n - 1) / tile_n) * tiles_m;
-  const bool two_k = few_rows && !cluster_s && tile_n != 256;      // two K blocks per stage (narrow tiles)
+  const bool two_k = few_rows && tile_n != 256;      // two K blocks per stage (narrow tiles)
   const int k_unit = two_k ? 2 * BK : BK, min_per_split = two_k ? 4 : 8;
   const int KBt = (K + k_unit - 1) / k_unit;                       // K in the kernel's stage units
   int splits = 1;
@@ -898,14 +703,6 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, int M, int N, int K, i
     e.sym = *sym;
   } else {
     e.sym = SymTable{};
-  }
-  if (cluster_s) {
-    e.splitk_red = 0;
-    switch (cluster_s) {
-      case 8: return launch_cluster<8>(ta, tb, e, M, N, K, status, st);
-      case 4: return launch_cluster<4>(ta, tb, e, M, N, K, status, st);
-      case 2: return launch_cluster<2>(ta, tb, e, M, N, K, status, st);
-    }
   }
   switch (tile_n) {
     case 256: return few_rows ? launch_gemm<256, 5, 64>(ta, tb, e, M, N, K, splits, status, st)

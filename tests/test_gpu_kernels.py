@@ -662,36 +662,3 @@ def test_stream_triad_probe():
     """The bandwidth probe's triad kernel computes a = b + 3 c (checked inside) and reports a plausible rate."""
     from openagents_b200.utils.bandwidth_probe import stream_triad_gbs
     assert stream_triad_gbs(DEV, n=1 << 24) > 200.0
-
-
-@pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (48, 6144, 4096), (33, 520, 2112), (64, 768, 768), (1, 4096, 14336)])
-def test_gemm_fewrows_cluster(M, N, K):
-    """``tile_n=-2``, at most 64 rows: one 256-column tile per thread-block cluster, K split over its CTAs and reduced through
-    distributed shared memory (cluster sizes 8, 4, 8 with an empty last share, 2, 8).  Plain store with bias into
-    fp32 + bf16, in-place residual, accumulation, and the same result as the persistent kernel."""
-    ops = _ops()
-    A = _randn(M, K, seed=51).bfloat16()
-    B = _randn(N, K, seed=52, scale=0.05).bfloat16()
-    bias = _randn(N, seed=53)
-    status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    ref = A.float() @ B.float().t()
-    tol = 2e-3 * math.sqrt(K) * 0.05 + 1e-3
-    out = torch.zeros((M, N), device=DEV)
-    outb = torch.zeros((M, N), dtype=torch.bfloat16, device=DEV)
-    ops.gemm_bf16(A, B, M, N, K, out_f32=out, out_bf16=outb, bias=bias, tile_n=-2, status=status)
-    torch.cuda.synchronize()
-    assert int(status.item()) == 0
-    assert (out - (ref + bias)).abs().max().item() < tol, (out - (ref + bias)).abs().max().item()
-    assert torch.allclose(outb.float(), ref + bias, atol=3e-2, rtol=2e-2)
-    resid = _randn(M, N, seed=54)
-    x = resid.clone()
-    ops.gemm_bf16(A, B, M, N, K, out_f32=x, resid_f32=x, ldc=N, tile_n=-2, status=status)           # in-place residual add
-    assert (x - (ref + resid)).abs().max().item() < tol
-    acc = resid.clone()
-    ops.gemm_bf16(A, B, M, N, K, out_f32=acc, accumulate=True, bias=bias, tile_n=-2, status=status)
-    assert (acc - (ref + resid + bias)).abs().max().item() < tol
-    old = torch.zeros((M, N), device=DEV)
-    ops.gemm_bf16(A, B, M, N, K, out_f32=old, bias=bias, status=status)                    # the library's own choice: the persistent kernel
-    torch.cuda.synchronize()
-    assert int(status.item()) == 0
-    assert (old - out).abs().max().item() < tol
