@@ -21,6 +21,9 @@ LIB = PKG / "_lib"
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=default", "--expt-relaxed-constexpr"]
+# measurement builds: B200_NVCC_DEFINES="QGEMM_STAMPS" compiles the in-kernel cycle counters (part of the flag digest, so
+# switching it on or off rebuilds)
+NVCC_FLAGS += ["-D" + d for d in os.environ.get("B200_NVCC_DEFINES", "").replace(",", " ").split()]
 CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-fopenmp", "-Wall", "-Wno-unused-function"]
 
 

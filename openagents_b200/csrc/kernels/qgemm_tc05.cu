@@ -130,6 +130,18 @@ constexpr int kAS = 3;                             // operand stages in tensor m
 // moment the SMs then read different slices of the activations, instead of all of them pulling the same few L2 lines.
 __device__ __forceinline__ int rot_sb(int sb0, int sb1, int i) { const int n = sb1 - sb0; return sb0 + (i + (int)blockIdx.x) % n; }
 
+// Build with -DQGEMM_STAMPS to have CTA 0's MMA thread add up, over all launches: [0] cycles spent waiting for operands,
+// [1] cycles spent issuing, [2] cycles from an item's first stage to the retirement of its last, [3] stages counted in [2].
+// `b200_qgemm_stamps(out, reset)` copies the four counters out.  Not compiled by default.
+#ifdef QGEMM_STAMPS
+__device__ long long g_qgemm_stamps[4];
+#define QSTAMP_T0() long long _qs = clock64()
+#define QSTAMP_ADD(i) do { const long long _qn = clock64(); if (blockIdx.x == 0) g_qgemm_stamps[i] += _qn - _qs; _qs = _qn; } while (0)
+#else
+#define QSTAMP_T0() do { } while (0)
+#define QSTAMP_ADD(i) do { } while (0)
+#endif
+
 template <int WT> struct QTraits { static constexpr int RAWB = WT == QW_Q4KR ? 144 : 208; static constexpr int RS = WT == QW_Q4KR ? 6 : 4; };
 
 // tcgen05.mma (TS form) with the shared-memory descriptor given as its two 32-bit halves: the issuing thread adds
@@ -249,9 +261,14 @@ __global__ void __launch_bounds__(kQThreads, 1) qgemm_kernel(const __grid_consta
         if (!mbar_wait(smem_u32(tempty + acc), ((tcount >> 1) & 1) ^ 1, abort_flag)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * QBN;
+#ifdef QGEMM_STAMPS
+        const long long item_t0 = clock64();
+#endif
         for (int i = 0; i < n_st; i++, g++) {
           const uint32_t s = g % kAS, ph = (g / kAS) & 1;
+          QSTAMP_T0();
           if (!mbar_wait(smem_u32(a_full + s), ph, abort_flag) || !mbar_wait(smem_u32(x_full + s), ph, abort_flag)) { ok = false; break; }
+          QSTAMP_ADD(0);                  // cycles this thread waited for the stage's operands
           tc_fence_after();
           const uint32_t a_tmem = tmem_base + 128 + s * 128;
           const uint32_t b_lo = b_lo0 + s * (kXStage >> 4);
@@ -260,6 +277,16 @@ __global__ void __launch_bounds__(kQThreads, 1) qgemm_kernel(const __grid_consta
           for (int m = 1; m < 16; m++)     // K block m / 4 (8 KB apart in shared memory, 32 columns apart in tensor memory), K step m % 4
             umma_ts_lohi(d_tmem, a_tmem + (m >> 2) * 32 + (m & 3) * 8, b_lo + (m >> 2) * ((QBN * 128) >> 4) + (m & 3) * 2, b_hi, idesc, 1u);
           umma_commit(smem_u32(done + s));
+          QSTAMP_ADD(1);                  // cycles to issue the stage's 16 MMAs and the commit
+#ifdef QGEMM_STAMPS
+          // retire time of a stage: with the operands of the NEXT stage already there (wait above near zero), the gap
+          // between two stages' `done` barriers is what the tensor core needed for 16 MMAs
+          if (blockIdx.x == 0 && i + 1 == n_st) {
+            mbar_wait(smem_u32(done + s), ph, abort_flag);
+            g_qgemm_stamps[2] += clock64() - item_t0;
+            g_qgemm_stamps[3] += n_st;
+          }
+#endif
         }
         umma_commit(smem_u32(tfull + acc));      // released even after a failed wait; the flag says why
       }
@@ -517,3 +544,14 @@ B200_API int b200_qgemm(int wt, const void* w, const void* w2, int N, int K, con
   }
   return 0;
 }
+
+#ifdef QGEMM_STAMPS
+B200_API int b200_qgemm_stamps(long long* out, int reset) {
+  int rc = (int)cudaMemcpyFromSymbol(out, g_qgemm_stamps, sizeof(long long) * 4);
+  if (rc == 0 && reset) {
+    const long long z[4] = {0, 0, 0, 0};
+    rc = (int)cudaMemcpyToSymbol(g_qgemm_stamps, z, sizeof(z));
+  }
+  return rc;
+}
+#endif

@@ -24,6 +24,7 @@ from .. import _native
 from ..ops import cuda_ops as ops
 from .config import ModelConfig
 from .qweight import QWeight, RawTensor, WeightSource
+from ..utils.nvtx import nvtx_method
 
 PAGE = 16
 MATVEC_MAX_TOKENS = 8
@@ -490,6 +491,7 @@ class LlamaEngine:
             self._slots_pending = slots      # decode: the final norm takes the last sum
         return n
 
+    @nvtx_method("tp.row_parallel(all_reduce)")
     def _row_parallel(self, a_bf16, w: QWeight, T: int, x, bias, fused: bool, slots: bool, table):
         """x += a W^T for a row-parallel projection (attention output, FFN down), summed over the tensor-parallel ranks."""
         if slots:        # this rank's partial sums stay local (K splits add into the zeroed rows); the next norm all-reduces them
@@ -503,6 +505,7 @@ class LlamaEngine:
         else:
             self.comm.gemm_allreduce(a_bf16, self._dense(w), T, x, bias=bias, status=self.status, wait_ready=not self._use_fence)
 
+    @nvtx_method("tp.prefill_layers(reduce_scatter+all_gather)")
     def _layers_seq_sharded(self, T: int, n_seqs: int, max_q: int):
         """Prefill with the residual stream sharded by rows over the tensor-parallel ranks.  Per layer:
         norm + all-gather push -> QKV GEMM (waits tile by tile for the rows' owners) -> attention on this
@@ -680,6 +683,7 @@ class LlamaEngine:
             self._stg["last_batch"] = None        # page lists changed: the decode fast path must resend its rows
 
     @torch.no_grad()
+    @nvtx_method("engine.prefill")
     def forward_tokens(self, seq_ids: list[int], new_tokens: list[list[int]], greedy: bool = True):
         """Append ``new_tokens[b]`` to sequence ``seq_ids[b]`` and return the logits of each
         sequence's last new token ([B, V] view, valid until the next call) and their arg-max."""
@@ -752,6 +756,7 @@ class LlamaEngine:
         return self._stg
 
     @torch.no_grad()
+    @nvtx_method("engine.decode_step")
     def decode(self, seq_ids: list[int], tokens: list[int], use_graph: bool = True):
         """One decode step: append one token per sequence, return (logits view, arg-max ids)."""
         if not use_graph:
@@ -794,6 +799,7 @@ class LlamaEngine:
         return self.logits[:B], self.out_ids[:B]
 
     @torch.no_grad()
+    @nvtx_method("engine.decode_steps")
     def decode_steps(self, seq_ids: list[int], tokens: list[int], n_steps: int, on_replay=None):
         """``n_steps`` greedy decode steps with the autoregression kept on the device: one upload,
         ``n_steps`` graph replays (each ends by turning its arg-max into the next step's input),

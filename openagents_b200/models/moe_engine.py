@@ -33,6 +33,7 @@ from ..parallel.tp import TPComm
 from .config import ModelConfig
 from .engine import LlamaEngine, _Layer
 from .qweight import WeightSource
+from ..utils.nvtx import nvtx_method
 
 
 @dataclass
@@ -114,6 +115,7 @@ class MoEEngine(LlamaEngine):
         if self.ep_world > 1:
             self.ep.heap.barrier(ch=2)
 
+    @nvtx_method("moe.dispatch+experts+combine")
     def _ffn_dense(self, li: int, L: _Layer, T: int, x, hb_d, hb_f, gu, fused: bool = False, slots: bool = False, table=None) -> int:
         ex, heap = self.experts[li], self.ep.heap
         par = li & 1

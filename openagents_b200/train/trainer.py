@@ -28,6 +28,7 @@ from ..models.config import GPT2_SMALL, ModelConfig
 from ..models.weights import TensorSpec, init_tensor, tensor_specs
 from ..ops import train_ops as tops
 from ..parallel.symm import SymmHeap
+from ..utils.nvtx import nvtx_method
 from .gpt2 import GPT2Model, padded_vocab, param_layout
 
 
@@ -103,6 +104,7 @@ class Trainer:
         return c.lr
 
     # ---- one optimizer step over `accum` micro-batches.  tokens/targets: [accum, micro_batch, seq_len]
+    @nvtx_method("train.forward_backward")
     def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         losses = []
         for a in range(self.accum):
@@ -110,6 +112,7 @@ class Trainer:
         self.optimizer_step()
         return torch.stack(losses).mean()
 
+    @nvtx_method("train.optimizer_step(reduce_scatter+adamw+all_gather)")
     def optimizer_step(self):
         c, T = self.cfg, self.heap.table
         self.step_count += 1

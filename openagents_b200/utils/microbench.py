@@ -191,6 +191,14 @@ def bench_qgemm(rows):
             gbs = ws[0].nbytes() / s_ / 1e9
             rows.append(f"qgemm {name:8s} N={N:6d} K={K:5d} {t.name} {mode:6s} T={T:3d}: {s_*1e6:8.1f} us  {gbs:6.0f} GB/s packed "
                         f"({gbs/hbm:4.2f} of {tag} HBM)")
+            stamps = getattr(ops.lib(), "b200_qgemm_stamps", None) if hasattr(ops, "lib") else None
+            if stamps is not None:       # library built with B200_NVCC_DEFINES=QGEMM_STAMPS: CTA 0's MMA thread, summed over the launches above
+                import ctypes
+                buf = (ctypes.c_longlong * 4)()
+                stamps(buf, 1)
+                if buf[3]:
+                    rows.append(f"      MMA thread of CTA 0: {buf[2] / buf[3]:7.0f} cycles per 256-wide K stage (16 MMAs) from first wait to "
+                                f"retirement; waiting for operands {buf[0] / buf[3]:6.0f}, issuing {buf[1] / buf[3]:6.0f} cycles per stage")
         if name != "lm_head":
             Bs = [torch.randn(N, K, device=DEV).bfloat16() for _ in range(R)]
             A = torch.randn(64, K, device=DEV).bfloat16()

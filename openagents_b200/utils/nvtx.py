@@ -29,3 +29,19 @@ def nvtx_range(name: str):
         yield
     finally:
         torch.cuda.nvtx.range_pop()
+
+
+def nvtx_method(name: str):
+    """Decorator form: the function runs inside a range called ``name``.  With the marks off it returns the function
+    itself, so a decorated hot-path method costs nothing extra."""
+    def wrap(fn):
+        if not _ON:
+            return fn
+        import functools
+
+        @functools.wraps(fn)
+        def inner(*a, **kw):
+            with nvtx_range(name):
+                return fn(*a, **kw)
+        return inner
+    return wrap
