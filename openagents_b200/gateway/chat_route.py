@@ -10,6 +10,14 @@ registered adapters; 8. re-frame the answer (JSON, or server-sent events for ``s
 usage against the pricing table and the key's balance; 10. build the telemetry record and return the
 compact telemetry block on the response.
 
+Caller-funded requests (``x-openagents-provider`` / ``x-openagents-provider-key`` headers, or a provider key attached
+to the account) go to an adapter built for that key, are never debited and are acknowledged in the
+``x-openagents-byok`` response header (chat-completions-routes.ts:221-223, 254-312, 2786-2812); the billing
+disclosure on the receipt says which of receipt-backed / zero-charge / no-debit applied (:1533-1553).  Model gating
+comes from a table (``ModelGate``): premium models need an entitled key, internal models an allow-listed account, and a
+model nobody can serve is refused before any spend check (:2586-2600, 3019-3025).  With ``platform_funded=False`` only
+caller-funded or no-meter traffic is dispatched (:3043-3065).  Every answered request lands in the served-token ledger.
+
 Adapters here: ``LocalEngineAdapter`` answers from an in-process ``ServerState`` (this engine, whole-model
 lane) and produces the serving receipt with exact-greedy parity itself; the ``openagents-network`` adapter
 from ``fabric`` does the same over HTTP to a node.
@@ -39,9 +47,67 @@ class GatewayError(Exception):
 
 class ApiKey:
     def __init__(self, key: str, account: str, balance_msat: int = 0, allowed_models: tuple | None = None, max_inflight: int = 4,
-                 byok: dict | None = None):
+                 byok: dict | None = None, premium: bool = False, no_meter: bool = False):
         self.key, self.account, self.balance_msat, self.allowed_models = key, account, balance_msat, allowed_models
         self.max_inflight, self.inflight, self.byok = max_inflight, 0, byok or {}
+        self.premium, self.no_meter = premium, no_meter      # entitled to premium models; operator-owned capacity, never debited
+
+
+BYOK_PROVIDER_HEADER = "x-openagents-provider"
+BYOK_PROVIDER_KEY_HEADER = "x-openagents-provider-key"
+BYOK_ACK_HEADER = "x-openagents-byok"
+BYOK_PROVIDERS = ("openrouter",)
+
+
+class ByokState:
+    """``absent`` | ``accepted`` (provider, api_key, source = request | account) | ``invalid`` (reason)."""
+
+    def __init__(self, tag: str, provider: str | None = None, api_key: str | None = None, source: str | None = None, reason: str | None = None):
+        self.tag, self.provider, self.api_key, self.source, self.reason = tag, provider, api_key, source, reason
+
+    def __repr__(self):        # the key never reaches a log line
+        return f"ByokState({self.tag}, provider={self.provider}, source={self.source})"
+
+
+def _key_shape_ok(raw) -> bool:
+    return isinstance(raw, str) and 8 <= len(raw.strip()) <= 512 and raw.strip() == raw and not any(c.isspace() or c == "," for c in raw)
+
+
+def resolve_byok(headers: dict | None) -> ByokState:
+    """Per-request caller funding from the two headers (names compared case-insensitively)."""
+    h = {str(k).lower(): v for k, v in (headers or {}).items()}
+    provider = (h.get(BYOK_PROVIDER_HEADER) or "").strip().lower()
+    raw = h.get(BYOK_PROVIDER_KEY_HEADER)
+    if not provider and raw is None:
+        return ByokState("absent")
+    if provider not in BYOK_PROVIDERS:
+        return ByokState("invalid", reason=f"Only {BYOK_PROVIDER_HEADER}: {' | '.join(BYOK_PROVIDERS)} is supported for BYOK.")
+    if not _key_shape_ok(raw):
+        return ByokState("invalid", reason=f"{BYOK_PROVIDER_KEY_HEADER} must be a single valid API key value.")
+    return ByokState("accepted", provider, raw, "request")
+
+
+def byok_response_headers(state: ByokState, routed: bool) -> dict:
+    if state.tag == "absent":
+        return {}
+    return {BYOK_ACK_HEADER: "invalid" if state.tag == "invalid" else ("routed" if routed else "accepted")}
+
+
+class ModelGate:
+    """One row of the model gating table."""
+
+    def __init__(self, model: str, premium: bool = False, internal_only: bool = False, servable: bool = True, alias_of: str | None = None):
+        self.model, self.premium, self.internal_only, self.servable, self.alias_of = model, premium, internal_only, servable, alias_of
+
+
+def billing_disclosure(zero_charge: bool, receipt_ref: str | None, byok: bool) -> dict:
+    if zero_charge:
+        return {"mode": "zero_charge", "receipt_required": False}
+    if receipt_ref is not None:
+        return {"mode": "receipt_backed", "receipt_required": True}
+    if byok:
+        return {"mode": "no_debit", "reason": "caller_provider_key", "receipt_required": False}
+    return {"mode": "no_debit", "reason": "operator_exempt_or_unmetered", "receipt_required": False}
 
 
 class LocalEngineAdapter:
@@ -72,12 +138,22 @@ class LocalEngineAdapter:
 
 class ChatGateway:
     def __init__(self, registry: ProviderRegistry, keys: list[ApiKey], pricing: PricingTable | None = None, plan=None, now=time.time,
-                 sleep=lambda ms: None, default_price_msat_per_token: tuple[int, int] = (1, 4)):
+                 sleep=lambda ms: None, default_price_msat_per_token: tuple[int, int] = (1, 4), gates: list[ModelGate] | None = None,
+                 internal_accounts: tuple = (), byok_adapter_factory=None, resolve_account_byok=None, ledger=None,
+                 platform_funded: bool = True):
+        """``gates``: the model gating table (a model without a row is not gated).  ``byok_adapter_factory(provider,
+        api_key)`` builds the adapter a caller-funded request is sent to; ``resolve_account_byok(account)`` returns
+        ``(provider, api_key)`` for an account with an attached provider key, or None.  ``ledger``: a
+        ``ServedTokensLedger``.  ``platform_funded=False``: only caller-funded or no-meter keys are served."""
         self.registry, self.pricing, self.plan, self.now, self.sleep = registry, pricing, plan, now, sleep
         self.keys = {k.key: k for k in keys}
         self.default_price = default_price_msat_per_token
         self.lock = threading.Lock()
         self.telemetry: list[dict] = []
+        self.gates = {g.model: g for g in (gates or [])}
+        self.internal_accounts = frozenset(internal_accounts)
+        self.byok_adapter_factory, self.resolve_account_byok = byok_adapter_factory, resolve_account_byok
+        self.ledger, self.platform_funded = ledger, platform_funded
 
     # ---- steps
     def authenticate(self, authorization: str | None) -> ApiKey:
@@ -115,30 +191,73 @@ class ChatGateway:
         return usage.prompt_tokens * pi + usage.completion_tokens * po
 
     # ---- the route
-    def handle(self, authorization: str | None, body, session: str | None = None) -> tuple[int, dict | list[str]]:
+    def handle(self, authorization: str | None, body, session: str | None = None, headers: dict | None = None) -> tuple[int, dict | list[str]]:
         """Returns (status, JSON object) or, for ``stream``, (200, list of SSE frames)."""
+        status, _, out = self.handle_with_headers(authorization, body, session, headers)
+        return status, out
+
+    def handle_with_headers(self, authorization: str | None, body, session: str | None = None, headers: dict | None = None):
+        """As ``handle`` plus the response headers (the caller-funding acknowledgement)."""
         t0 = self.now()
+        byok = ByokState("absent")
         try:
             key = self.authenticate(authorization)
+            byok = resolve_byok(headers)
+            if byok.tag == "invalid":
+                return 400, byok_response_headers(byok, False), {"error": {"message": byok.reason, "type": "invalid_byok_provider_key",
+                                                                           "code": "invalid_byok_provider_key"}}
+            if byok.tag == "absent":       # request headers win and stay ephemeral; else a key attached to the account
+                attached = None
+                if self.resolve_account_byok is not None:
+                    try:
+                        attached = self.resolve_account_byok(key.account)
+                    except Exception:      # noqa: BLE001 - a failing lookup means "no attached key", never a failed request
+                        attached = None
+                if attached is None and key.byok.get("provider") and key.byok.get("api_key"):
+                    attached = (key.byok["provider"], key.byok["api_key"])
+                if attached is not None and attached[0] in BYOK_PROVIDERS and _key_shape_ok(attached[1]):
+                    byok = ByokState("accepted", attached[0], attached[1], "account")
             with self.lock:
                 if key.inflight >= key.max_inflight:
                     raise GatewayError(429, "fair_share_exceeded", "too many requests in flight for this key")
                 key.inflight += 1
             try:
-                return self._handle(key, body, session, t0)
+                status, out = self._handle(key, body, session, t0, byok)
+                return status, byok_response_headers(byok, status == 200), out
             finally:
                 with self.lock:
                     key.inflight -= 1
         except GatewayError as e:
-            return e.status, e.body()
+            return e.status, byok_response_headers(byok, False), e.body()
 
-    def _handle(self, key: ApiKey, body, session, t0):
-        body = self.decode_body(body)
-        model = body["model"].strip()
+    def gate(self, key: ApiKey, model: str) -> str:
+        """Model gating: returns the model id to route (aliases resolved) or raises.  Servability comes first: a model
+        nobody can serve is never the caller's balance or allow-list problem."""
+        g = self.gates.get(model)
+        if g is not None and g.alias_of:
+            model, g = g.alias_of, self.gates.get(g.alias_of)
+        if g is not None and not g.servable:
+            raise GatewayError(503, "model_unavailable", f"{model!r} has no serving lane right now")
         if key.allowed_models is not None and model not in key.allowed_models:
             raise GatewayError(403, "model_not_allowed", f"this key may not use {model!r}")
-        if key.balance_msat <= 0 and not key.byok:
-            raise GatewayError(402, "insufficient_balance", "the key has no balance")
+        if g is not None and g.internal_only and key.account not in self.internal_accounts:
+            raise GatewayError(403, "model_not_allowed", f"{model!r} is limited to internal accounts")
+        if g is not None and g.premium and not (key.premium or key.account in self.internal_accounts):
+            raise GatewayError(403, "premium_model_requires_entitlement", f"{model!r} needs a premium entitlement")
+        return model
+
+    def _handle(self, key: ApiKey, body, session, t0, byok: ByokState | None = None):
+        byok = byok or ByokState("absent")
+        body = self.decode_body(body)
+        requested = body["model"].strip()
+        model = self.gate(key, requested)
+        caller_paid = byok.tag == "accepted"
+        if not caller_paid and not key.no_meter:
+            if not self.platform_funded:
+                raise GatewayError(503, "platform_funding_unavailable",
+                                   "Platform-funded inference is unavailable. Configure a supported BYOK provider account.")
+            if key.balance_msat <= 0:
+                raise GatewayError(402, "insufficient_balance", "the key has no balance")
         layout = pc.assemble_stable_prompt_layout([(m, m.get("stable_kind")) for m in body["messages"]])
         messages = tuple({"role": m["role"], "content": m["content"]} for m in layout["messages"])
         affinity_raw = pc.derive_cache_affinity_key(key.account, session)
@@ -148,20 +267,40 @@ class ChatGateway:
         plan = self.plan(model) if self.plan else select_adapter_plan(model, self.pricing)
         events = []
         t_dispatch = self.now()
+        registry = self.registry
+        if caller_paid:                  # the caller's own provider account answers; no overflow onto platform capacity
+            if self.byok_adapter_factory is None:
+                raise GatewayError(503, "byok_provider_unavailable", f"no adapter is configured for provider {byok.provider!r}")
+            adapter = self.byok_adapter_factory(byok.provider, byok.api_key)
+            registry = ProviderRegistry()
+            registry.register(adapter)
+            plan = [adapter.id]
         try:
-            d = dispatch_with_overflow(request, lambda a, r: a.complete(r), self.registry, plan=plan, sleep=self.sleep, telemetry=events.append)
+            d = dispatch_with_overflow(request, lambda a, r: a.complete(r), registry, plan=plan, sleep=self.sleep, telemetry=events.append)
         except InferenceAdapterError as e:
             status = e.http_status if e.http_status in (400, 404, 429) else (503 if e.retryable else 502)
             raise GatewayError(status, e.kind, e.reason)
         t_done = self.now()
-        out = d.value
+        out = d.value if isinstance(d.value, tuple) else (d.value, {})      # an external adapter returns the bare result
         result, receipt = out[0], out[1]
         paid = out[2] if len(out) > 2 else None
         price = self.price_msat(result.served_model if self.pricing and self.pricing.lookup(result.served_model) else model, result.usage)
-        if not key.byok:
+        debited = not caller_paid and not key.no_meter
+        if debited:
             with self.lock:
                 key.balance_msat -= price
+        else:
+            price = 0
         rid = "chatcmpl-" + uuid.uuid4().hex[:24]
+        receipt_ref = f"receipt.inference.{rid}" if debited and price > 0 else None
+        billing = billing_disclosure(zero_charge=debited and price == 0, receipt_ref=receipt_ref, byok=caller_paid)
+        if self.ledger is not None:      # the ledger is a projection of the answer: it never fails the request
+            try:
+                self.ledger.record(rid, model, result.usage.prompt_tokens, result.usage.completion_tokens, account_ref=key.account,
+                                   adapter_id=d.adapter_id, demand_kind="internal" if key.account in self.internal_accounts else "external",
+                                   served_model=result.served_model)
+            except Exception:            # noqa: BLE001
+                pass
         record = rt.build_record(
             request_id=rid, requested_model=model, served_model=result.served_model, route=d.adapter_id, provider=d.adapter_id,
             request_class="interactive_stream" if request.stream else "async_job", prompt_tokens=result.usage.prompt_tokens,
@@ -182,7 +321,8 @@ class ChatGateway:
             usage["prompt_tokens_details"] = {"cached_tokens": result.usage.cached_prompt_tokens}
         ext = {"telemetry": rt.block_from_record(record, f"telemetry.{rid}"), "receipt": receipt, "route": d.adapter_id,
                "overflow_count": d.overflow_count, "stable_prefix_hash": layout["stablePrefixHash"], "price_msat": price,
-               "clears_paid_traffic": paid}
+               "clears_paid_traffic": paid, "billing": billing, "receipt_ref": receipt_ref,
+               "requested_model": requested}
         created = int(t_done)
         if request.stream:
             frames = []

@@ -93,3 +93,87 @@ def test_refusals(state):
     status, out = gw.handle("Bearer k1", dict(BODY, model="qwen-unknown"))
     assert status in (404, 502, 503) and gw.keys["k1"].inflight == 0
     assert gw.quote("qwen-tiny", 100, 50) == {"model": "qwen-tiny", "maxPriceMsat": 300} and rt.FIREWORKS in [m["id"] for m in gw.models()["data"]]
+
+
+class _Echo:
+    """An external provider reached with the caller's own key."""
+
+    def __init__(self, provider, api_key):
+        self.id, self.api_key, self.calls = f"byok-{provider}", api_key, 0
+
+    def complete(self, request):
+        self.calls += 1
+        return fb.InferenceResult("echo:" + request.messages[-1]["content"], "stop", request.model, fb.InferenceUsage(5, 3, 8))
+
+
+def test_caller_funded_request_is_routed_not_debited_and_acknowledged(state):
+    from openagents_b200.gateway.observability import ServedTokensLedger
+    made = []
+
+    def factory(provider, api_key):
+        made.append(_Echo(provider, api_key))
+        return made[-1]
+
+    reg = fb.ProviderRegistry()
+    reg.register(cr.LocalEngineAdapter(state, model_alias={"qwen-tiny": "tiny"}))
+    ledger = ServedTokensLedger()
+    gw = cr.ChatGateway(reg, [cr.ApiKey("k", "acct", 0)], byok_adapter_factory=factory, ledger=ledger, platform_funded=False)
+    hdr = {"X-OpenAgents-Provider": "OpenRouter", "x-openagents-provider-key": "sk-or-0123456789abcdef"}
+    status, rh, out = gw.handle_with_headers("Bearer k", BODY, headers=hdr)
+    assert status == 200 and rh == {cr.BYOK_ACK_HEADER: "routed"} and made[0].calls == 1 and made[0].api_key == "sk-or-0123456789abcdef"
+    ext = out["openagents"]
+    assert ext["route"] == "byok-openrouter" and ext["price_msat"] == 0 and gw.keys["k"].balance_msat == 0
+    assert ext["billing"] == {"mode": "no_debit", "reason": "caller_provider_key", "receipt_required": False} and ext["receipt_ref"] is None
+    assert ledger.total() == 8 and list(ledger.rows.values())[0]["adapterId"] == "byok-openrouter"
+    assert "sk-or" not in repr(cr.resolve_byok(hdr))                                   # the key never prints
+    # unsupported provider / malformed key: 400 with the acknowledgement header, nothing dispatched
+    for bad in ({"x-openagents-provider": "acme", "x-openagents-provider-key": "sk-or-0123456789abcdef"},
+                {"x-openagents-provider": "openrouter", "x-openagents-provider-key": "two keys"},
+                {"x-openagents-provider-key": "sk-or-0123456789abcdef"}):
+        status, rh, out = gw.handle_with_headers("Bearer k", BODY, headers=bad)
+        assert status == 400 and rh == {cr.BYOK_ACK_HEADER: "invalid"} and out["error"]["code"] == "invalid_byok_provider_key"
+    assert len(made) == 1
+    # without caller funding the platform does not pay
+    status, rh, out = gw.handle_with_headers("Bearer k", BODY)
+    assert status == 503 and out["error"]["code"] == "platform_funding_unavailable" and rh == {}
+    # a key attached to the account is used when the request carries none; request headers win over it
+    gw.resolve_account_byok = lambda account: ("openrouter", "sk-or-attached-000000") if account == "acct" else None
+    status, rh, out = gw.handle_with_headers("Bearer k", BODY)
+    assert status == 200 and rh == {cr.BYOK_ACK_HEADER: "routed"} and made[-1].api_key == "sk-or-attached-000000"
+    status, rh, out = gw.handle_with_headers("Bearer k", BODY, headers=hdr)
+    assert made[-1].api_key == "sk-or-0123456789abcdef"
+    # a resolver that throws means "no attached key"
+    def boom(account):
+        raise RuntimeError("db down")
+    gw.resolve_account_byok = boom
+    assert gw.handle("Bearer k", BODY)[0] == 503
+
+
+def test_model_gating_table_and_billing_modes(state):
+    from openagents_b200.gateway.observability import ServedTokensLedger
+    reg = fb.ProviderRegistry()
+    reg.register(cr.LocalEngineAdapter(state, model_alias={"qwen-tiny": "tiny", "qwen-pro": "tiny", "qwen-lab": "tiny"}))
+    gates = [cr.ModelGate("qwen-pro", premium=True), cr.ModelGate("qwen-lab", internal_only=True), cr.ModelGate("qwen-dead", servable=False),
+             cr.ModelGate("qwen-latest", alias_of="qwen-pro")]
+    ledger = ServedTokensLedger()
+    keys = [cr.ApiKey("plain", "a1", 10_000), cr.ApiKey("prem", "a2", 10_000, premium=True), cr.ApiKey("ops", "ops1", 0, no_meter=True),
+            cr.ApiKey("broke", "a3", 0)]
+    gw = cr.ChatGateway(reg, keys, gates=gates, internal_accounts=("ops1",), ledger=ledger, plan=lambda m: ["openagents-network"])
+    body = lambda m: {**BODY, "model": m}
+    assert gw.handle("Bearer plain", body("qwen-pro"))[1]["error"]["code"] == "premium_model_requires_entitlement"
+    assert gw.handle("Bearer plain", body("qwen-latest"))[1]["error"]["code"] == "premium_model_requires_entitlement"      # alias resolves first
+    assert gw.handle("Bearer plain", body("qwen-lab"))[1]["error"]["code"] == "model_not_allowed"
+    # servability is checked before balance: a dead model is a 503 even for a key without balance
+    assert gw.handle("Bearer broke", body("qwen-dead")) [0] == 503
+    assert gw.handle("Bearer broke", body("qwen-tiny"))[1]["error"]["code"] == "insufficient_balance"
+    status, out = gw.handle("Bearer prem", body("qwen-latest"))
+    assert status == 200 and out["openagents"]["requested_model"] == "qwen-latest"
+    assert out["openagents"]["billing"] == {"mode": "receipt_backed", "receipt_required": True}
+    assert out["openagents"]["receipt_ref"].startswith("receipt.inference.chatcmpl-")
+    # operator-owned capacity: internal account, never debited, demand labelled internal in the ledger
+    status, out = gw.handle("Bearer ops", body("qwen-lab"))
+    assert status == 200 and out["openagents"]["billing"]["reason"] == "operator_exempt_or_unmetered" and out["openagents"]["price_msat"] == 0
+    kinds = sorted(r["demandKind"] for r in ledger.rows.values())
+    assert kinds == ["external", "internal"]
+    # a model without a row is not gated
+    assert gw.handle("Bearer plain", body("qwen-tiny"))[0] == 200
