@@ -124,6 +124,7 @@ class ServerState:
         self.responses: dict[str, tuple[str, str]] = {}     # response id -> (session id, text)
         self.reasoning_budget, self.mesh_coordination = reasoning_budget, mesh_coordination
         self.started = time.time()
+        self.allow_shutdown = False
         self.ttft = Histogram([0.005, 0.01, 0.025, 0.05, 0.1, 0.25, 0.5, 1, 2.5, 5, 10])
         self.itl = Histogram([0.0005, 0.001, 0.002, 0.005, 0.01, 0.02, 0.05, 0.1, 0.25])
         self.lock = threading.Lock()
@@ -297,6 +298,12 @@ def make_handler(state: ServerState):
             body = self._body()
             if body is None:
                 return self._err(400, "request body must be a JSON object")
+            if path == "/admin/shutdown":          # only with --allow-shutdown: lets a launcher or a test stop all ranks cleanly
+                if not state.allow_shutdown:
+                    return self._err(404, "not found", "not_found")
+                self._json(200, {"stopping": True})
+                threading.Thread(target=self.server.shutdown, daemon=True).start()
+                return None
             try:
                 model = state.model(body.get("model"))
             except KeyError:
@@ -491,6 +498,7 @@ def parse_args(argv=None):
     ap.add_argument("--kv-page-size", type=int, default=_flag_env("kv-page-size", 16))
     ap.add_argument("--max-num-seqs", type=int, default=_flag_env("max-num-seqs", 64))
     ap.add_argument("--max-ctx", type=int, default=_flag_env("max-ctx", 4096))
+    ap.add_argument("--allow-shutdown", action="store_true", help="accept POST /admin/shutdown (stops every rank between steps)")
     a = ap.parse_args(argv)
     if a.tp > 1 and a.ep > 1:
         ap.error("--tp and --ep cannot be combined")
@@ -502,8 +510,9 @@ def parse_args(argv=None):
 def run_server(a, **parallel):
     state = build_state(a.model, a.backend, a.max_num_seqs, a.kv_page_size, a.max_ctx, a.reasoning_budget, a.mesh_coordination,
                         **parallel)
+    state.allow_shutdown = bool(getattr(a, "allow_shutdown", False))
     httpd = serve(state, a.host, a.port)
-    print(json.dumps({"event": "listening", "host": a.host, "port": a.port, "models": list(state.models),
+    print(json.dumps({"event": "listening", "host": a.host, "port": httpd.server_address[1], "models": list(state.models),
                       "execution_engine": ENGINE_NAME, "tp": a.tp, "ep": a.ep}), flush=True)
     try:
         httpd.serve_forever()

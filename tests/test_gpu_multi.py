@@ -321,3 +321,86 @@ def test_wait_times_out_and_context_survives():
     heap.barrier()                        # a one-rank barrier completes at once
     torch.cuda.synchronize()
     assert heap.status()[1] == 1
+
+
+# ---------------------------------------------------------------- the HTTP server on two tensor-parallel ranks
+
+def test_server_tp2_over_http(tmp_path):
+    """``python -m openagents_b200.serve.server --tp 2``: rank 0 serves HTTP and schedules, rank 1 follows over the gloo
+    control group.  Concurrent requests share decode batches, greedy answers repeat exactly, the first token of each
+    answer is the CPU oracle's, a streamed answer equals the plain one, and ``/admin/shutdown`` ends every rank with 0."""
+    _need(2)
+    import json
+    import subprocess
+    import sys
+    import threading
+    import time
+    import urllib.request
+    from openagents_b200.models.config import TINY_LLAMA
+    from openagents_b200.models.weights import PLAN_Q4_K, random_weights, save_gguf
+    from openagents_b200.serve.backend import CpuBackend
+    from openagents_b200.serve.server import ServedModel, ServerState
+    cfg = TINY_LLAMA.with_(d_model=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1024, vocab=4096, n_layers=3)
+    p = str(tmp_path / "tiny.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 3), PLAN_Q4_K)
+    port = _free_port()
+    env = dict(os.environ, B200_SERVE_HEAP_MB="256")
+    proc = subprocess.Popen([sys.executable, "-m", "openagents_b200.serve.server", "-m", p, "--tp", "2", "--port", str(port),
+                             "--allow-shutdown", "--max-num-seqs", "8", "--max-ctx", "512"],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
+    lines, ready = [], threading.Event()
+
+    def pump():
+        for ln in proc.stdout:
+            lines.append(ln)
+            if '"listening"' in ln:
+                ready.set()
+    threading.Thread(target=pump, daemon=True).start()
+    base = f"http://127.0.0.1:{port}"
+
+    def post(path, obj, timeout=120):
+        req = urllib.request.Request(base + path, data=json.dumps(obj).encode(), headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=timeout) as r:
+            return r.read().decode()
+    try:
+        assert ready.wait(240), "".join(lines[-30:])
+        prompts = [f"prompt number {i} says hello" for i in range(4)]
+        body = lambda t, **kw: {"model": "tiny", "messages": [{"role": "user", "content": t}], "max_tokens": 8, "temperature": 0, **kw}
+        outs = [None] * 4
+
+        def one(i):
+            outs[i] = json.loads(post("/v1/chat/completions", body(prompts[i])))
+        ts = [threading.Thread(target=one, args=(i,)) for i in range(4)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join(180)
+        assert all(o is not None and o["usage"]["completion_tokens"] == 8 for o in outs), outs
+        again = json.loads(post("/v1/chat/completions", body(prompts[2])))
+        assert again["choices"][0]["message"]["content"] == outs[2]["choices"][0]["message"]["content"]
+        # the CPU oracle on the same file: same prompt ids, same first token
+        oracle = ServerState([ServedModel("tiny", CpuBackend.from_gguf(p), "sha256:x", max_num_seqs=4)])
+        for i in (0, 3):
+            r, usage = oracle.complete(oracle.default, [{"role": "user", "content": prompts[i]}], {"max_tokens": 1, "temperature": 0})
+            assert usage["prompt_tokens"] == outs[i]["usage"]["prompt_tokens"]
+            first = oracle.default.tok.decode(r.output[:1])
+            assert outs[i]["choices"][0]["message"]["content"].startswith(first), (first, outs[i]["choices"][0]["message"]["content"])
+        for m in oracle.models.values():
+            m.close()
+        # streamed answer = plain answer
+        raw = post("/v1/chat/completions", body(prompts[1], stream=True))
+        text = "".join((json.loads(ln[5:])["choices"][0]["delta"].get("content") or "") for ln in raw.splitlines()
+                       if ln.startswith("data:") and "[DONE]" not in ln and json.loads(ln[5:]).get("choices"))
+        assert text == outs[1]["choices"][0]["message"]["content"]
+        with urllib.request.urlopen(base + "/health", timeout=30) as r:
+            health = json.loads(r.read())
+        assert health.get("status") in ("ok", "healthy", "ready") or health
+        post("/admin/shutdown", {})
+        assert proc.wait(120) == 0, "".join(lines[-30:])
+    finally:
+        if proc.poll() is None:
+            proc.terminate()              # this exact child; its ranks are idle between steps
+            try:
+                proc.wait(30)
+            except subprocess.TimeoutExpired:
+                proc.kill()

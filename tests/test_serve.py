@@ -305,3 +305,20 @@ def test_sampling_on_host_matches_its_definition():
     assert sample_row(logits, p, float(probs[0]) + 1e-3) == 4
     assert sample_row(logits, p, 0.999) == 2
     assert sample_row(logits, SamplingParams(temperature=1.0, top_k=3, top_p=0.2), 0.999) == 1    # top-p keeps only the best
+
+
+def test_shutdown_route_is_off_unless_allowed(gguf_path):
+    model = ServedModel("tiny", CpuBackend.from_gguf(gguf_path), mf.artifact_digest(gguf_path), max_num_seqs=2)
+    state = ServerState([model])
+    httpd = serve(state, "127.0.0.1", 0)
+    t = threading.Thread(target=httpd.serve_forever, daemon=True)
+    t.start()
+    url = f"http://127.0.0.1:{httpd.server_address[1]}"
+    status, _ = _post(url + "/admin/shutdown", {})
+    assert status == 404 and t.is_alive()
+    state.allow_shutdown = True
+    status, body = _post(url + "/admin/shutdown", {})
+    assert status == 200 and json.loads(body)["stopping"] is True
+    t.join(10)
+    assert not t.is_alive()
+    model.close()
