@@ -170,8 +170,36 @@ def tokenizer_from_metadata(meta: dict, vocab_size: int):
     return VocabTokenizer(tokens, eos)
 
 
-def render_chat(messages: list[dict]) -> str:
+def render_chat(messages: list[dict], template: str | None = None, bos_token: str = "", eos_token: str = "", tools=None, **kwargs) -> str:
+    """The prompt text for a list of chat messages.  ``template``: a GGUF ``tokenizer.chat_template`` that the caller has
+    ADMITTED (digest allowlist); it is rendered in an immutable sandbox (no attribute access to Python internals, no
+    mutation of the inputs) with the variables model templates expect (``messages``, ``add_generation_prompt``,
+    ``bos_token``, ``eos_token``, ``tools``, plus ``kwargs`` such as ``reasoning_effort``).  A template that fails to
+    render falls back to the built-in layout rather than failing the request."""
+    if template:
+        try:
+            return _compiled_template(template).render(messages=[dict(m) for m in messages], add_generation_prompt=True,
+                                                       bos_token=bos_token, eos_token=eos_token, tools=tools, **kwargs)
+        except Exception:      # noqa: BLE001 - template errors (undefined names, raise_exception) must not take a request down
+            pass
     return "".join(f"<|{m.get('role', 'user')}|>\n{m.get('content', '')}\n" for m in messages) + "<|assistant|>\n"
+
+
+_TEMPLATES: dict[str, object] = {}
+
+
+def _compiled_template(template: str):
+    t = _TEMPLATES.get(template)
+    if t is None:
+        from jinja2.sandbox import ImmutableSandboxedEnvironment
+
+        def raise_exception(msg):
+            raise ValueError(msg)
+        env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True)
+        env.globals["raise_exception"] = raise_exception
+        env.globals["strftime_now"] = lambda fmt: time.strftime(fmt)
+        t = _TEMPLATES[template] = env.from_string(template)
+    return t
 
 
 @dataclass

@@ -51,6 +51,8 @@ class ServedModel:
         self.chat_template = chat_template          # a GGUF chat template admitted by the digest allowlist, or None
         self.sched = Scheduler(backend, self.tok, max_num_seqs=max_num_seqs, prefill_chunk=prefill_chunk)
         self.cv = threading.Condition()              # guards the scheduler and the backend
+        self.waiters = 0                             # handler threads that want the lock (see _loop)
+        self._wl = threading.Lock()
         self.created = int(time.time())
         self.closed = False
         self.thread = threading.Thread(target=self._loop, name=f"sched-{model_id}", daemon=True)
@@ -70,6 +72,13 @@ class ServedModel:
                     return
                 with nvtx_range("scheduler.step"):
                     self.sched.step()
+                # Python locks are not fair: a loop that re-takes the lock at once can starve the handler threads that
+                # want to enqueue, and their requests would miss the running batch.  While any handler is waiting, give
+                # the lock away (bounded: a few milliseconds per step at most).
+                for _ in range(8):
+                    if not self.waiters:
+                        break
+                    self.cv.wait(timeout=0.001)
 
     def close(self):
         with self.cv:
@@ -78,10 +87,16 @@ class ServedModel:
         self.thread.join(timeout=5)
 
     def submit(self, prompt_ids, params, seq_id=None, keep=False, on_token=None, on_done=None, history=None) -> Request:
-        with self.cv:
-            r = self.sched.submit(prompt_ids, params, seq_id=seq_id, keep_sequence=keep, on_token=on_token, on_done=on_done,
-                                  history=history)
-            self.cv.notify_all()
+        with self._wl:
+            self.waiters += 1
+        try:
+            with self.cv:
+                r = self.sched.submit(prompt_ids, params, seq_id=seq_id, keep_sequence=keep, on_token=on_token, on_done=on_done,
+                                      history=history)
+                self.cv.notify_all()
+        finally:
+            with self._wl:
+                self.waiters -= 1
         return r
 
     def generate(self, prompt_ids, params, seq_id=None, keep=False, on_token=None, history=None) -> Request:
@@ -148,7 +163,14 @@ class ServerState:
                                 top_k=int(body.get("top_k") or 0),
                                 stop=tuple(body["stop"]) if isinstance(body.get("stop"), list) else ((body["stop"],) if body.get("stop") else ()),
                                 seed=body.get("seed"))
-        ids = model.tok.encode(render_chat(messages))
+        tok = model.tok
+        toks = getattr(tok, "tokens", None)
+
+        def special(i):
+            return toks[i] if toks is not None and isinstance(i, int) and 0 <= i < len(toks) else ""
+        ids = tok.encode(render_chat(messages, model.chat_template, bos_token=special(getattr(tok, "bos_id", None)),
+                                     eos_token=special(getattr(tok, "eos_id", None)), tools=body.get("tools"),
+                                     **(body.get("chat_template_kwargs") if isinstance(body.get("chat_template_kwargs"), dict) else {})))
         with nvtx_range("serve.complete"):
             if session is None:
                 r = model.generate(ids, params, on_token=on_token)

@@ -322,3 +322,30 @@ def test_shutdown_route_is_off_unless_allowed(gguf_path):
     t.join(10)
     assert not t.is_alive()
     model.close()
+
+
+def test_admitted_chat_template_is_rendered_in_a_sandbox(gguf_path, monkeypatch):
+    from openagents_b200.control.node_bridge import template_admitted, template_digest
+    from openagents_b200.serve.generation import render_chat
+    tpl = ("{{ bos_token }}{% for m in messages %}<|start|>{{ m['role'] }}\\n{{ m['content'] }}<|end|>\\n{% endfor %}"
+           "{% if add_generation_prompt %}<|start|>assistant\\n{% endif %}{% if reasoning_effort is defined %}[{{ reasoning_effort }}]{% endif %}")
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}]
+    out = render_chat(msgs, tpl, bos_token="<s>", reasoning_effort="low")
+    assert out == "<s><|start|>system\\nbe brief<|end|>\\n<|start|>user\\nhi<|end|>\\n<|start|>assistant\\n[low]"
+    builtin = render_chat(msgs)
+    assert builtin.endswith("<|assistant|>\n") and render_chat(msgs, None) == builtin
+    # the sandbox: no reaching into Python internals, no mutation of the request; a failing template falls back
+    assert render_chat(msgs, "{{ messages.__class__.__mro__ }}") == builtin
+    assert render_chat(msgs, "{% set _ = messages.append({'role': 'x'}) %}{{ messages | length }}") == builtin and len(msgs) == 2
+    assert render_chat(msgs, "{{ raise_exception('only user/assistant roles') }}") == builtin
+    # the server renders a template only when its digest is admitted
+    assert not template_admitted(tpl)
+    monkeypatch.setenv("B200_CHAT_TEMPLATE_ALLOW", template_digest(tpl))
+    assert template_admitted(tpl)
+    model = ServedModel("tiny", CpuBackend.from_gguf(gguf_path), mf.artifact_digest(gguf_path), max_num_seqs=2, chat_template=tpl)
+    state = ServerState([model])
+    r1, u1 = state.complete(model, msgs, {"max_tokens": 2})
+    model.chat_template = None
+    r2, u2 = state.complete(model, msgs, {"max_tokens": 2})
+    assert u1["prompt_tokens"] != u2["prompt_tokens"]            # different prompt text reached the tokenizer
+    model.close()
