@@ -166,11 +166,13 @@ class LlamaEngine:
 
     def __init__(self, cfg: ModelConfig, src: WeightSource, device="cuda", max_batch: int = 64,
                  max_ctx: int = 4096, n_pages: int | None = None, tp_rank: int = 0, tp_world: int = 1,
-                 max_tokens: int = 4096, comm=None):
+                 max_tokens: int = 4096, comm=None, canaries: bool | None = None):
         if cfg.arch not in self.ARCHS:
             raise ValueError(f"{type(self).__name__} serves {self.ARCHS} models, not {cfg.arch!r}")
         self.cfg, self.device = cfg, torch.device(device)
         self.rank, self.world, self.comm = tp_rank, tp_world, comm
+        self.canaries = (os.environ.get("B200_CANARY", "0") == "1") if canaries is None else bool(canaries)
+        self._guards: dict[str, tuple[torch.Tensor, int]] = {}
         self._use_fence = os.environ.get("B200_TP_FENCE", "0") == "1"
         # Tensor-parallel decode: "slots" = the row-parallel projections keep their partial result local and the RMSNorm
         # that follows all-reduces it through per-rank slots (one kernel: push, per-row flags, sum, normalise; no barrier,
@@ -261,6 +263,40 @@ class LlamaEngine:
         return n
 
     # ------------------------------------------------------------------ workspaces
+    _GUARD_BYTES, _GUARD_FILL = 256, 0xA5
+
+    def _ws(self, name: str, shape, dtype, zero: bool = False) -> torch.Tensor:
+        """One workspace tensor.  With canaries on (``B200_CANARY=1`` or ``canaries=True``) it sits between two 256-byte
+        guard zones of a known byte, and ``check_canaries`` tells which guards a kernel has written into: the
+        substitute for a memory checker on the engine's own buffers."""
+        n = 1
+        for v in shape:
+            n *= int(v)
+        if not self.canaries:
+            return (torch.zeros if zero else torch.empty)(tuple(shape), dtype=dtype, device=self.device)
+        G = self._GUARD_BYTES
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        body_bytes = (nbytes + G - 1) // G * G
+        raw = torch.full((G + body_bytes + G,), self._GUARD_FILL, dtype=torch.uint8, device=self.device)
+        body = raw[G: G + nbytes].view(dtype).view(*shape)
+        if zero:
+            body.zero_()
+        self._guards[name] = (raw, nbytes)
+        return body
+
+    def check_canaries(self) -> list[str]:
+        """Names of the workspaces whose guard zones no longer hold the fill byte (empty list: all intact, or canaries
+        off).  ``name:before`` / ``name:after`` says on which side the stray write landed."""
+        bad = []
+        G = self._GUARD_BYTES
+        torch.cuda.synchronize(self.device) if self.device.type == "cuda" else None
+        for name, (raw, nbytes) in self._guards.items():
+            if not bool((raw[:G] == self._GUARD_FILL).all()):
+                bad.append(name + ":before")
+            if not bool((raw[G + nbytes:] == self._GUARD_FILL).all()):
+                bad.append(name + ":after")
+        return bad
+
     def _alloc(self):
         dev, T = self.device, self.max_tokens
         f32 = dict(dtype=torch.float32, device=dev)
@@ -274,36 +310,38 @@ class LlamaEngine:
             self.hbfull, self.hbfull_off = self.comm.alloc_tensor((T + self.world, d), torch.bfloat16)
             self._ag_epoch = 0
         else:
-            self.x = torch.empty((T, d), **f32)
-        self.qkv = torch.empty((T, self.qkv_dim), **f32)
-        self.q32 = torch.empty((max(self.max_batch, 1), qd), **f32)
-        self.q16 = torch.empty((T, qd), dtype=torch.float16, device=dev)
-        self.hb = torch.empty((T, max(d, qd, F)), dtype=torch.bfloat16, device=dev)
-        self.hb2 = torch.empty((T, F), dtype=torch.bfloat16, device=dev)
-        self.gu = torch.empty((T, 2 * F), **f32)
-        self.logits = torch.empty((self.max_batch, self.V_local), **f32)
+            self.x = self._ws("x", (T, d), torch.float32)
+        i8, i32, bf, f16, f32t = torch.int8, torch.int32, torch.bfloat16, torch.float16, torch.float32
+        ws = self._ws
+        self.qkv = ws("qkv", (T, self.qkv_dim), f32t)
+        self.q32 = ws("q32", (max(self.max_batch, 1), qd), f32t)
+        self.q16 = ws("q16", (T, qd), f16)
+        self.hb = ws("hb", (T, max(d, qd, F)), bf)
+        self.hb2 = ws("hb2", (T, F), bf)
+        self.gu = ws("gu", (T, 2 * F), f32t)
+        self.logits = ws("logits", (self.max_batch, self.V_local), f32t)
         kmax = max(d, qd, F)
         nb = MATVEC_MAX_TOKENS
-        self.xq = torch.empty((nb, kmax), dtype=torch.int8, device=dev)
-        self.xd = torch.empty((nb, kmax // 32 + 1), **f32)
-        self.xs = torch.empty((nb, kmax // 16 + 2), **f32)
-        self.xf = torch.empty((nb, kmax), **f32)
+        self.xq = ws("xq", (nb, kmax), i8)
+        self.xd = ws("xd", (nb, kmax // 32 + 1), f32t)
+        self.xs = ws("xs", (nb, kmax // 16 + 2), f32t)
+        self.xf = ws("xf", (nb, kmax), f32t)
         # second activation set: a kernel never writes the buffers it is still reading
-        self.fq = torch.empty((nb, kmax), dtype=torch.int8, device=dev)
-        self.fd = torch.empty((nb, kmax // 32 + 1), **f32)
-        self.fs = torch.empty((nb, kmax // 16 + 2), **f32)
-        self.ids = torch.zeros(T, dtype=torch.int32, device=dev)
-        self.pos = torch.zeros(T, dtype=torch.int32, device=dev)
-        self.slot = torch.zeros(T, dtype=torch.int32, device=dev)
-        self.page_table = torch.zeros((self.max_batch, self.max_pages), dtype=torch.int32, device=dev)
-        self.seq_lens = torch.zeros(self.max_batch, dtype=torch.int32, device=dev)
-        self.q_start = torch.zeros(self.max_batch, dtype=torch.int32, device=dev)
-        self.q_len = torch.zeros(self.max_batch, dtype=torch.int32, device=dev)
-        self.out_ids = torch.zeros(self.max_batch, dtype=torch.int32, device=dev)
-        self.out_val = torch.zeros(self.max_batch, **f32)
+        self.fq = ws("fq", (nb, kmax), i8)
+        self.fd = ws("fd", (nb, kmax // 32 + 1), f32t)
+        self.fs = ws("fs", (nb, kmax // 16 + 2), f32t)
+        self.ids = ws("ids", (T,), i32, zero=True)
+        self.pos = ws("pos", (T,), i32, zero=True)
+        self.slot = ws("slot", (T,), i32, zero=True)
+        self.page_table = ws("page_table", (self.max_batch, self.max_pages), i32, zero=True)
+        self.seq_lens = ws("seq_lens", (self.max_batch,), i32, zero=True)
+        self.q_start = ws("q_start", (self.max_batch,), i32, zero=True)
+        self.q_len = ws("q_len", (self.max_batch,), i32, zero=True)
+        self.out_ids = ws("out_ids", (self.max_batch,), i32, zero=True)
+        self.out_val = ws("out_val", (self.max_batch,), f32t, zero=True)
         self.max_splits = 64
-        self.attn_scratch = torch.empty(ops.attn_decode_scratch_floats(self.max_batch, self.Hq, self.Hkv, self.hd, self.max_splits), **f32)
-        self.attn_counters = torch.zeros(self.max_batch * self.Hkv, dtype=torch.int32, device=dev)
+        self.attn_scratch = ws("attn_scratch", (ops.attn_decode_scratch_floats(self.max_batch, self.Hq, self.Hkv, self.hd, self.max_splits),), f32t)
+        self.attn_counters = ws("attn_counters", (self.max_batch * self.Hkv,), i32, zero=True)
         self.argmax_scratch = ops.argmax_scratch(self.max_batch, dev)
         self.rope_tab = ops.rope_table(self.max_pages * PAGE, self.hd, self.cfg.rope_theta, dev)
         wmax = max(max(l.wqkv.N * l.wqkv.K, l.wo.N * l.wo.K, *((l.wgu.N * l.wgu.K, l.wdown.N * l.wdown.K) if l.wgu is not None else ()))
@@ -315,7 +353,7 @@ class LlamaEngine:
             # zeroed between uses: the projections accumulate into them)
             self.slot_rows = QGEMM_MAX_TOKENS
             self.slots, self.slots_off = self.comm.alloc_tensor((2, self.world, self.slot_rows, d), torch.float32)
-            self.xpart = torch.zeros((self.slot_rows, d), **f32)
+            self.xpart = self._ws("xpart", (self.slot_rows, d), torch.float32, zero=True)
             row_par = [w for l in self.layers for w in (l.wo, l.wdown) if w is not None]
             self.slots_small = self.tp_mode == "slots"
             self.slots_dense = self.slots_small and all(self._qg(w) for w in row_par)

@@ -100,10 +100,10 @@ class MoEEngine(LlamaEngine):
         self.recv_w, self.recv_w_off = heap.alloc_tensor((self.E_local * self.cap,), torch.float32)
         self.counts, self.counts_off = heap.alloc_tensor((2, self.E_local), torch.int32)
         self.counts.zero_()
-        self.hf32 = torch.empty((T, d), dtype=torch.float32, device=dev)      # normalised hidden in fp32, for the router
-        self.hmid = torch.empty((self.E_local * self.cap, f), dtype=torch.bfloat16, device=dev)
-        self.topk_ids = torch.zeros((T, self.top_k), dtype=torch.int32, device=dev)
-        self.topk_w = torch.zeros((T, self.top_k), dtype=torch.float32, device=dev)
+        self.hf32 = self._ws("hf32", (T, d), torch.float32)                    # normalised hidden in fp32, for the router
+        self.hmid = self._ws("hmid", (self.E_local * self.cap, f), torch.bfloat16)
+        self.topk_ids = self._ws("topk_ids", (T, self.top_k), torch.int32, zero=True)
+        self.topk_w = self._ws("topk_w", (T, self.top_k), torch.float32, zero=True)
         self.moe_status = self.status
 
     # ------------------------------------------------------------------ forward

@@ -407,6 +407,11 @@ def make_handler(state: ServerState):
 
                 r, usage = state.complete(model, msgs, body, on_token=on_token)
                 finish = r.finish_reason
+                if pending:                  # bytes held back as an incomplete UTF-8 sequence: the answer ends here, send them
+                    tail = model.tok.decode(pending)
+                    pending.clear()
+                    if tail:
+                        emit(tail)
                 if splitter:
                     for d in splitter.flush():
                         chunk({**base, "choices": [{"index": 0, "delta": d, "finish_reason": None}]})

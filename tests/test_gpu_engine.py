@@ -162,3 +162,37 @@ def test_backend_samples_on_the_device(tmp_path):
         outs.append(r.output)
     assert outs[0] == outs[1] and sch.stats["d2h_bytes"] > 0
     be.engine.check_status()
+
+
+def test_workspace_canaries_stay_intact(tmp_path):
+    """Every engine workspace between guard zones of a known byte: after prefill at the workspace's full token count,
+    mat-vec decode, batched fused-dequant decode (eager and from a graph) and the device-side decode loop, no kernel
+    has written a byte outside its buffers; and a deliberate stray write on the host is reported."""
+    from openagents_b200.models.engine import LlamaEngine
+    from openagents_b200.models.qweight import GGUFSource
+    cfg = TINY_LLAMA.with_(d_model=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1024, vocab=4096, n_layers=2)
+    p = str(tmp_path / "q4k.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 5), PLAN_Q4_K)
+    src = GGUFSource(p, "cuda")
+    eng = LlamaEngine(src.cfg, src, max_batch=16, max_ctx=256, max_tokens=192, canaries=True)
+    assert len(eng._guards) > 20 and eng.check_canaries() == []
+    g = torch.Generator().manual_seed(4)
+    ids = list(range(12))
+    for b in ids:
+        eng.begin(b)
+    # 12 x 16 = 192 tokens: the prefill fills the token workspaces to the last row
+    _, nxt = eng.forward_tokens(ids, [torch.randint(0, cfg.vocab, (16,), generator=g).tolist() for _ in ids])
+    toks = nxt.tolist()
+    for step in range(3):
+        _, nxt = eng.decode(ids, toks, use_graph=(step > 0))
+        toks = nxt.tolist()
+    eng.decode_steps(ids, toks, 4)
+    _, nxt = eng.decode([0, 1], toks[:2])                 # mat-vec path
+    eng.decode_steps([3], [5], 3)
+    eng.check_status()
+    assert eng.check_canaries() == []
+    raw, nbytes = eng._guards["gu"]
+    raw[eng._GUARD_BYTES + nbytes + 3] = 0                 # one byte past the end of `gu`
+    raw_q, _ = eng._guards["qkv"]
+    raw_q[eng._GUARD_BYTES - 1] = 7                        # one byte before the start of `qkv`
+    assert sorted(eng.check_canaries()) == ["gu:after", "qkv:before"]

@@ -349,3 +349,26 @@ def test_admitted_chat_template_is_rendered_in_a_sandbox(gguf_path, monkeypatch)
     r2, u2 = state.complete(model, msgs, {"max_tokens": 2})
     assert u1["prompt_tokens"] != u2["prompt_tokens"]            # different prompt text reached the tokenizer
     model.close()
+
+
+def test_stream_flushes_bytes_held_back_as_incomplete_utf8(gguf_path):
+    """A model that ends on a byte which starts a multi-byte character: the streamed text equals the plain answer."""
+    class _Tail(CpuBackend):
+        def step(self, seq_ids, new_tokens, params, uniforms):
+            out = super().step(seq_ids, new_tokens, params, uniforms)
+            return [0xE2 for _ in out]                    # first byte of a three-byte sequence, never completed
+    be = _Tail.from_gguf(gguf_path)
+    model = ServedModel("tiny", be, None, max_num_seqs=2)
+    state = ServerState([model])
+    httpd = serve(state, "127.0.0.1", 0)
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    base = f"http://127.0.0.1:{httpd.server_address[1]}"
+    body = {"messages": [{"role": "user", "content": "x"}], "max_tokens": 3, "temperature": 0}
+    _, plain = _post(base + "/v1/chat/completions", body)
+    _, raw = _post(base + "/v1/chat/completions", {**body, "stream": True})
+    text = "".join((json.loads(ln[5:])["choices"][0]["delta"].get("content") or "") for ln in raw.decode().splitlines()
+                   if ln.startswith("data:") and "[DONE]" not in ln)
+    want = json.loads(plain)["choices"][0]["message"]["content"]
+    assert want and text == want
+    httpd.shutdown()
+    model.close()
