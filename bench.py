@@ -342,7 +342,7 @@ def main():
                      "parallelism": f"dp{world} (independent replicas)"})
 
     weight_bytes = eng.weight_bytes()
-    scratch_bytes = 0 if eng._wscratch is None else eng._wscratch.numel() * 2
+    scratch_bytes = eng.scratch_bytes()
     launches_per_step = eng.launches_per_decode
     del eng
     if comm is not None:

@@ -346,8 +346,15 @@ class LlamaEngine:
         self.rope_tab = ops.rope_table(self.max_pages * PAGE, self.hd, self.cfg.rope_theta, dev)
         wmax = max(max(l.wqkv.N * l.wqkv.K, l.wo.N * l.wo.K, *((l.wgu.N * l.wgu.K, l.wdown.N * l.wdown.K) if l.wgu is not None else ()))
                    for l in self.layers)
-        self._wscratch_elems = max(wmax, self.wout.N * self.wout.K if self.wout.quantized else 0)
-        self._wscratch = None
+        # bf16 expansion space for prefill GEMMs: the largest layer matrix (the LM head too only when the fused-dequant GEMM
+        # does not take its type).  Two buffers when the expansion of the next matrix runs beside the current GEMM.
+        self._wscratch_elems = max(wmax, self.wout.N * self.wout.K if (self.wout.quantized and not self._qg(self.wout)) else 0)
+        self._wbufs: list[torch.Tensor | None] = [None, None]
+        self._pf = None                      # (weight, buffer index, ready event) of the expansion in flight on the side stream
+        self._pf_stream = None
+        self._pf_on = os.environ.get("B200_DEQUANT_OVERLAP", "1") == "1"
+        order = [w for l in self.layers for w in (l.wqkv, l.wo, l.wgu, l.wdown) if w is not None and w.wt != ops.WT_BF16]
+        self._pf_next = {id(a): b for a, b in zip(order, order[1:])}
         if self.world > 1:
             # one-shot all-reduce: slots [parity][rank][row][d] on every rank, and this rank's partial rows (local, kept
             # zeroed between uses: the projections accumulate into them)
@@ -366,16 +373,45 @@ class LlamaEngine:
         """Whether the fused-dequant GEMM takes this weight."""
         return w is not None and w.wt in (ops.WT_Q4KR, ops.WT_Q6KR) and w.K % 256 == 0
 
+    def scratch_bytes(self) -> int:
+        return sum(b.numel() * 2 for b in self._wbufs if b is not None)
+
+    def _wbuf(self, i: int, w: QWeight) -> torch.Tensor:
+        if self._wbufs[i] is None:
+            self._wbufs[i] = torch.empty(self._wscratch_elems, dtype=torch.bfloat16, device=self.device)
+        return self._wbufs[i][: w.N * w.K].view(w.N, w.K)
+
     def _dense(self, w: QWeight) -> torch.Tensor:
-        """bf16 [N][K] form of a weight for the bf16 tensor-core GEMM (prefill): the matrix itself when it is stored
-        in bf16, else its expansion into the one scratch buffer all quantized matrices share.  The expansion kernel
-        and the GEMM run in stream order, so the buffer is free again when the next matrix needs it."""
+        """bf16 [N][K] form of a weight for the bf16 tensor-core GEMM (prefill): the matrix itself when it is stored in
+        bf16, else its expansion into a scratch buffer.  The expansion is memory-bound and the GEMM compute-bound, so while
+        the GEMM on this matrix runs, the NEXT matrix of the layer walk is expanded into the other buffer on a side stream
+        (events order the two; ``B200_DEQUANT_OVERLAP=0`` or a stream capture in progress falls back to one buffer in
+        stream order)."""
         if w.wt == ops.WT_BF16:
             return w.main
-        if self._wscratch is None:
-            self._wscratch = torch.empty(self._wscratch_elems, dtype=torch.bfloat16, device=self.device)
-        out = self._wscratch[: w.N * w.K].view(w.N, w.K)
-        return w.dequant_into(out)
+        main = torch.cuda.current_stream(self.device)
+        pf, self._pf = self._pf, None
+        if pf is not None:
+            main.wait_event(pf[2])                       # whatever the side stream was writing is complete before we go on
+        overlap = self._pf_on and self.device.type == "cuda" and not torch.cuda.is_current_stream_capturing()
+        if pf is not None and pf[0] is w:
+            b, out = pf[1], self._wbuf(pf[1], w)
+        else:
+            b = 0
+            out = w.dequant_into(self._wbuf(0, w))
+        nxt = self._pf_next.get(id(w)) if overlap else None
+        if nxt is not None:
+            if self._pf_stream is None:
+                self._pf_stream = torch.cuda.Stream(self.device)
+            free = torch.cuda.Event()
+            free.record(main)                            # the GEMM that last read the other buffer is before this point
+            self._pf_stream.wait_event(free)
+            with torch.cuda.stream(self._pf_stream):
+                nxt.dequant_into(self._wbuf(1 - b, nxt))
+                ready = torch.cuda.Event()
+                ready.record(self._pf_stream)
+            self._pf = (nxt, 1 - b, ready)
+        return out
 
     @property
     def _slot_arg(self):
@@ -637,7 +673,7 @@ class LlamaEngine:
         else:
             hb = self.hb.view(-1)[: nb * self.d].view(nb, self.d)
             ops.rmsnorm(rows, self.out_norm, cfg.norm_eps, hb=hb, slots=slots)
-            if nb <= QGEMM_MAX_TOKENS and self._qg(self.wout):
+            if self._qg(self.wout):          # any row count: the kernel is launched once per 64 rows
                 ops.qgemm(self.wout, hb, nb, out_f32=self.logits, ldo=self.V_local, epi=ops.QEPI_STORE, status=self.status)
             else:
                 self._gemm(hb, self.wout, nb, out_f32=self.logits)
