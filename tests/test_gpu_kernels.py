@@ -449,6 +449,21 @@ def test_train_ops_match_torch():
     tops.layernorm_bwd(dy, x, g, mean, rstd, dx, True, dg, db)
     assert torch.allclose(dx.float(), xr.grad + 0.5, atol=6e-2, rtol=3e-2)
     assert torch.allclose(dg, gr.grad, atol=0.15, rtol=2e-2) and torch.allclose(db, br.grad, atol=0.15, rtol=2e-2)
+    # rows wider than the register-resident limit (1024) and a row count that is not a multiple of the warps per CTA
+    M2, D2 = 37, 1280
+    x2, dy2 = _randn(M2, D2, seed=70).bfloat16(), _randn(M2, D2, seed=71).bfloat16()
+    g2, b2 = (_randn(D2, seed=72) * 0.1 + 1.0), _randn(D2, seed=73) * 0.1
+    y2, mean2, rstd2 = torch.empty_like(x2), torch.empty(M2, device=DEV), torch.empty(M2, device=DEV)
+    tops.layernorm_fwd(x2, g2, b2, 1e-5, y2, mean2, rstd2)
+    xr2, gr2, br2 = x2.float().requires_grad_(True), g2.clone().requires_grad_(True), b2.clone().requires_grad_(True)
+    ref2 = torch.nn.functional.layer_norm(xr2, (D2,), gr2, br2, 1e-5)
+    assert torch.allclose(y2.float(), ref2, atol=3e-2, rtol=2e-2)
+    ref2.backward(dy2.float())
+    dx2 = torch.zeros((M2, D2), dtype=torch.bfloat16, device=DEV)
+    dg2, db2 = torch.zeros(D2, device=DEV), torch.zeros(D2, device=DEV)
+    tops.layernorm_bwd(dy2, x2, g2, mean2, rstd2, dx2, False, dg2, db2)
+    assert torch.allclose(dx2.float(), xr2.grad, atol=6e-2, rtol=3e-2)
+    assert torch.allclose(dg2, gr2.grad, atol=0.15, rtol=2e-2) and torch.allclose(db2, br2.grad, atol=0.15, rtol=2e-2)
     # GELU
     h = _randn(M, F_, seed=34).bfloat16()
     a = torch.empty_like(h)
