@@ -10,7 +10,7 @@
 
 using namespace b200;
 
-__global__ void sym_barrier_kernel(const SymTable T, int ch) {
+__global__ void sym_barrier_kernel(const __grid_constant__ SymTable T, int ch) {
   if (threadIdx.x == 0) sym_barrier_thread(T, ch);
 }
 B200_API int b200_sym_barrier(const SymTable* T, int ch, cudaStream_t st) {
@@ -20,7 +20,7 @@ B200_API int b200_sym_barrier(const SymTable* T, int ch, cudaStream_t st) {
 
 // In-place all-reduce (sum) of n fp32 values at `off`: rank r sums slice r over all ranks and
 // broadcasts it.  n must be a multiple of 4.
-__global__ void sym_all_reduce_kernel(const SymTable T, size_t off, size_t n, int ch) {
+__global__ void sym_all_reduce_kernel(const __grid_constant__ SymTable T, size_t off, size_t n, int ch) {
   const size_t n4 = n / 4;
   const size_t per = (n4 + T.world - 1) / T.world;
   const size_t lo = per * T.rank, hi = min(n4, lo + per);
@@ -41,7 +41,7 @@ B200_API int b200_sym_all_reduce_f32(const SymTable* T, size_t off, size_t n, in
 }
 
 // All-gather: every rank's `bytes` at src_off land at dst_off + rank * bytes on every rank.
-__global__ void sym_all_gather_kernel(const SymTable T, size_t src_off, size_t dst_off, size_t bytes, int ch) {
+__global__ void sym_all_gather_kernel(const __grid_constant__ SymTable T, size_t src_off, size_t dst_off, size_t bytes, int ch) {
   const uint4* src = (const uint4*)(T.base[T.rank] + src_off);
   const size_t n = bytes / 16;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
@@ -58,7 +58,7 @@ B200_API int b200_sym_all_gather(const SymTable* T, size_t src_off, size_t dst_o
 }
 
 // Reduce-scatter (sum): out[i] on rank r = sum over ranks p of in_p[r * n + i], fp32, n per rank.
-__global__ void sym_reduce_scatter_kernel(const SymTable T, size_t in_off, size_t out_off, size_t n, int ch) {
+__global__ void sym_reduce_scatter_kernel(const __grid_constant__ SymTable T, size_t in_off, size_t out_off, size_t n, int ch) {
   float4* out = (float4*)(T.base[T.rank] + out_off);
   const size_t n4 = n / 4;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x)
@@ -76,7 +76,7 @@ B200_API int b200_sym_reduce_scatter_f32(const SymTable* T, size_t in_off, size_
 
 // All-to-all: chunk p (bytes) of this rank's source goes to dst_off + rank * bytes on rank p: one
 // direct peer write per destination, every peer being one hop through the switch.
-__global__ void sym_all_to_all_kernel(const SymTable T, size_t src_off, size_t dst_off, size_t bytes, int ch) {
+__global__ void sym_all_to_all_kernel(const __grid_constant__ SymTable T, size_t src_off, size_t dst_off, size_t bytes, int ch) {
   const size_t n = bytes / 16;
   for (int p = 0; p < T.world; p++) {
     const int dst = (T.rank + p) % T.world;   // stagger destinations across ranks
@@ -99,7 +99,7 @@ B200_API int b200_sym_all_to_all(const SymTable* T, size_t src_off, size_t dst_o
 // A wait on a flag nothing sets: exercises the timeout path on one GPU without involving a peer.
 // The kernel returns after `wait_ns`, records the status in the control block and leaves the
 // context usable.
-__global__ void sym_wait_unset_flag_kernel(const SymTable T, int ch) {
+__global__ void sym_wait_unset_flag_kernel(const __grid_constant__ SymTable T, int ch) {
   if (threadIdx.x == 0) {
     SymTable solo = T;
     solo.world = 2;            // expects two arrivals, only this rank will ever arrive

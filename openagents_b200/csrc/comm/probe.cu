@@ -20,7 +20,7 @@ __global__ void __launch_bounds__(256) stream_triad_kernel(float4* __restrict__ 
 
 // mode 0: pull (load from peer, store locally); 1: push (load locally, store to peer);
 // 2: broadcast push (load locally, one multimem store reaches every replica; needs multicast)
-__global__ void __launch_bounds__(256) peer_copy_kernel(const SymTable T, int peer, size_t src_off, size_t dst_off,
+__global__ void __launch_bounds__(256) peer_copy_kernel(const __grid_constant__ SymTable T, int peer, size_t src_off, size_t dst_off,
                                                         size_t n16, int mode) {
   const char* src = (mode == 0 ? T.base[peer] : T.base[T.rank]) + src_off;
   char* dst = (mode == 1 ? T.base[peer] : T.base[T.rank]) + dst_off;

@@ -17,7 +17,7 @@
 using namespace b200;
 
 // grads: fp32 [n_total] at grad_off in every heap.  This rank owns [lo, lo + n).  n % 4 == 0.
-__global__ void zero_reduce_norm_kernel(const SymTable T, size_t grad_off, size_t lo, size_t n,
+__global__ void zero_reduce_norm_kernel(const __grid_constant__ SymTable T, size_t grad_off, size_t lo, size_t n,
                                         float* __restrict__ gshard, float* __restrict__ norm2_out) {
   __shared__ float red[32];
   const float inv = 1.f / (float)T.world;
@@ -48,7 +48,7 @@ struct AdamArgs {
 };
 
 // norm2: sum over ALL ranks of the shard squared norms (fp32 scalar, device memory).
-__global__ void zero_adamw_gather_kernel(const SymTable T, size_t param_off, size_t lo, size_t n,
+__global__ void zero_adamw_gather_kernel(const __grid_constant__ SymTable T, size_t param_off, size_t lo, size_t n,
                                          const float* __restrict__ gshard, float* __restrict__ master,
                                          float* __restrict__ m, float* __restrict__ v,
                                          const float* __restrict__ norm2, const AdamArgs a) {

@@ -101,7 +101,7 @@ constexpr int kRmsRegs = 8;
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ g, float eps,
                                                        int D, int8_t* __restrict__ xq, float* __restrict__ xd,
                                                        float* __restrict__ xs16, __nv_bfloat16* __restrict__ hb,
-                                                       float* __restrict__ hf, const SymTable sym, int sym_mode,
+                                                       float* __restrict__ hf, const __grid_constant__ SymTable sym, int sym_mode,
                                                        float4* __restrict__ zero, int zero_n4, size_t slot_off,
                                                        int slot_rows, float* __restrict__ part) {
   __shared__ float red[32];
@@ -229,7 +229,7 @@ B200_API int b200_rmsnorm(float* x, const float* g, float eps, int T, int D, voi
 // the kernel that produces the data.
 __global__ void __launch_bounds__(512) rmsnorm_allgather_kernel(const float* __restrict__ x, const float* __restrict__ g,
                                                                 float eps, int D, int row0, int n_rows, size_t hb_off,
-                                                                const SymTable sym) {
+                                                                const __grid_constant__ SymTable sym) {
   __shared__ float red[32];
   pdl_trigger();
   pdl_wait();
@@ -493,7 +493,7 @@ B200_API int b200_argmax(const float* logits, int T, int V, int* out_id, float* 
 // the world flags and picks the best pair (highest value, lowest id on ties) from identical data, so all ranks
 // agree.  One CTA, one launch; slot parity and sequence number work as in the slot all-reduce (sym.cuh).
 __global__ void __launch_bounds__(1024) argmax_merge_kernel(int* __restrict__ out_id, const float* __restrict__ out_val, int nb,
-                                                            const SymTable sym, size_t merge_off, int rows) {
+                                                            const __grid_constant__ SymTable sym, size_t merge_off, int rows) {
   __shared__ uint32_t s_seq;
   pdl_trigger();
   pdl_wait();

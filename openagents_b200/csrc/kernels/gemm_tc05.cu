@@ -192,10 +192,11 @@ __device__ __forceinline__ void epilogue_col(const GemmEpi& e, int n, int t0, in
   if (n >= n_cols) return;
   const bool sym = e.sym_mode != SYM_NONE;
   const float b = (e.bias && first_split && (!sym || e.sym.rank == 0)) ? e.bias[n] : 0.f;
-#pragma unroll 4
+  // fully unrolled with a predicate per row: an index that is not a compile-time constant would put r[] on the stack
+#pragma unroll
   for (int j = 0; j < 32; j++) {
     const int t = t0 + j;
-    if (t >= n_rows) break;
+    if (t >= n_rows) continue;
     float x = __uint_as_float(r[j]) + b;
     if (sym) {
       const int owner = e.sym_mode != SYM_ALLREDUCE ? t / e.rows_per_rank : 0;
@@ -232,7 +233,9 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, in
   const bool full = n0 + 32 <= N;
   if (e.splitk_red && e.sym_mode == SYM_NONE) {
     const bool add_bias = e.bias && first_split;
-    for (int j = 0; j < 32 && n0 + j < N; j += 4) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      if (n0 + j >= N) continue;
       float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
       if (add_bias) {
         const float4 b = *(const float4*)(e.bias + n0 + j);
@@ -260,7 +263,9 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, in
         else sym_red_to_f32x4(e.sym, owner, off + j * 4, o);
       }
     } else {
-      for (int j = 0; j < 32 && n0 + j < N; j++) {
+#pragma unroll
+      for (int j = 0; j < 32; j++) {
+        if (n0 + j >= N) continue;
         const float x = v[j] + (add_bias ? e.bias[n0 + j] : 0.f);
         if (e.sym_mode == SYM_ALLREDUCE) sym_red_all_f32(e.sym, off + j * 4, x);
         else sym_red_to_f32(e.sym, owner, off + j * 4, x);
@@ -322,7 +327,9 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, in
       }
     }
   } else {
-    for (int j = 0; j < 32 && n0 + j < N; j++) {
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+      if (n0 + j >= N) continue;
       float x = v[j];
       if (e.bias) x += e.bias[n0 + j];
       if (e.act == ACT_GELU) x = gelu_tanh(x);
