@@ -220,7 +220,7 @@ __device__ __forceinline__ void epilogue_col(const GemmEpi& e, int n, int t0, in
 }
 
 __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, int M, int N, const uint32_t (&r)[32],
-                                             bool first_split) {
+                                             bool first_split, const float* bias_s = nullptr) {
   if (e.transposed) {
     epilogue_col(e, m, n0, M, N, r, first_split);
     return;
@@ -274,10 +274,11 @@ __device__ __forceinline__ void epilogue_row(const GemmEpi& e, int m, int n0, in
     return;
   }
   if (full) {
-    if (e.bias) {
+    if (e.bias) {      // bias_s: this chunk's 32 values staged in shared memory by the warp (broadcast reads)
+      const float* bp = bias_s ? bias_s : e.bias + n0;
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
-        const float4 b = *(const float4*)(e.bias + n0 + j);
+        const float4 b = *(const float4*)(bp + j);
         v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
       }
     }
@@ -546,17 +547,36 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         ready_checked = true;
       }
       const int m = m0 + q * 32 + lane;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + (uint32_t)(c * 32), r);
-        tmem_ld_wait();
-        if (n0 + c * 32 < N) {
-          if (epi.moe_mode == 2) epilogue_chunk_combine(epi, stage, m0 + q * 32, live_end, n0 + c * 32, N, r);
-          else if (epi.moe_mode == 1 || epi.act == ACT_SWIGLU_PAIR) { if (m < live_end) epilogue_row_swiglu(epi, m, n0 + c * 32, r); }
-          else if (red_path) epilogue_chunk_red(epi, stage, m0 + q * 32, n0 + c * 32, live_end, N, r, sp == 0);
-          else epilogue_row(epi, m, n0 + c * 32, live_end, N, r, sp == 0);
+      const bool plain = !(epi.moe_mode == 2 || epi.moe_mode == 1 || epi.act == ACT_SWIGLU_PAIR || red_path || epi.transposed);
+      const bool stage_bias = plain && epi.bias != nullptr;
+      if (stage_bias) {              // the tile's bias values, once per tile, into this warp's staging area
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < BN / 32; j++) {
+          const int n = n0 + j * 32 + lane;
+          stage[j * 32 + lane] = n < N ? epi.bias[n] : 0.f;
         }
+        __syncwarp();
+      }
+      auto process = [&](int c, const uint32_t (&r)[32]) {
+        if (n0 + c * 32 >= N) return;
+        if (epi.moe_mode == 2) epilogue_chunk_combine(epi, stage, m0 + q * 32, live_end, n0 + c * 32, N, r);
+        else if (epi.moe_mode == 1 || epi.act == ACT_SWIGLU_PAIR) { if (m < live_end) epilogue_row_swiglu(epi, m, n0 + c * 32, r); }
+        else if (red_path) epilogue_chunk_red(epi, stage, m0 + q * 32, n0 + c * 32, live_end, N, r, sp == 0);
+        else epilogue_row(epi, m, n0 + c * 32, live_end, N, r, sp == 0, stage_bias ? stage + c * 32 : nullptr);
+      };
+      // two register buffers: the tensor-memory load of the next 32 columns is in flight while this chunk is finished
+      const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      uint32_t ra[32], rb[32];
+      tmem_ld32(t_addr, ra);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c += 2) {
+        tmem_ld_wait();
+        tmem_ld32(t_addr + (uint32_t)((c + 1) * 32), rb);
+        process(c, ra);
+        tmem_ld_wait();
+        if (c + 2 < BN / 32) tmem_ld32(t_addr + (uint32_t)((c + 2) * 32), ra);
+        process(c + 1, rb);
       }
       tc_fence_before();
       __syncwarp();
