@@ -1,0 +1,106 @@
+"""Private-deployment contracts: policy resolution, install before pull, per-request routing, exact local metering and
+evaluation receipts, run against a model served by this package's CPU backend."""
+import pytest
+
+from openagents_b200.control import reactor as rx
+from openagents_b200.models.config import TINY_LLAMA
+from openagents_b200.models.weights import PLAN_Q8_0, random_weights, save_gguf
+from openagents_b200.serve.backend import CpuBackend
+from openagents_b200.serve.server import ServedModel, ServerState
+
+T0 = "2026-07-04T14:10:00.000Z"
+
+
+def _catalog():
+    return rx.model_catalog("catalog.reactor.v1", [
+        rx.model_provenance("model.us.open", "Acme Labs", "US", "apache-2.0", "permissive"),
+        rx.model_provenance("model.cn.open", "Dragon AI", "CN", "apache-2.0", "permissive"),
+        rx.model_provenance("model.us.distilled", "Acme Labs", "US", "mit", "permissive",
+                            distillation_lineage=[{"developer": "Dragon AI", "originJurisdiction": "CN", "disclosure": "reported"}]),
+        rx.model_provenance("model.eu.research", "Uni", "EU", "cc-by-nc-4.0", "research_only", training_data_disclosure="full"),
+    ], T0)
+
+
+def test_policy_resolution_reasons_and_empty_set():
+    cat = _catalog()
+    pol = rx.model_policy("policy.us_only", "v3", "owner.acme", {"allowOriginJurisdictions": ["US"], "allowLicenseClasses": ["permissive"],
+                                                                 "blockDevelopers": [" dragon ai "], "enforceDistillationLineageJurisdiction": True})
+    d = rx.resolve_model_policy(cat, pol, T0, "decision.1")
+    by = {m["modelRef"]: m for m in d["modelDecisions"]}
+    assert d["status"] == "conforming_models" and d["conformingModelRefs"] == ["model.us.open"] and d["refusal"] is None
+    assert by["model.cn.open"]["reasonRefs"] == ["reactor.policy.origin_not_allowed", "reactor.policy.developer_blocked"]
+    assert by["model.us.distilled"]["reasonRefs"] == ["reactor.policy.lineage_origin_not_allowed"]      # the ancestor decides
+    assert set(by["model.eu.research"]["reasonRefs"]) == {"reactor.policy.origin_not_allowed", "reactor.policy.license_class_not_allowed"}
+    # without lineage enforcement the distilled model conforms
+    lax = rx.model_policy("policy.us_only", "v4", "owner.acme", {"allowOriginJurisdictions": ["US"]})
+    assert rx.resolve_model_policy(cat, lax, T0, "d2")["conformingModelRefs"] == ["model.us.open", "model.us.distilled"]
+    none = rx.model_policy("policy.none", "v1", "owner.acme", {"allowOriginJurisdictions": ["JP"]})
+    d3 = rx.resolve_model_policy(cat, none, T0, "d3")
+    assert d3["status"] == "refused_empty_set" and d3["refusal"]["reason"] == "no_conforming_models"
+
+
+def test_install_then_route_and_policy_tightening_takes_effect_per_request():
+    cat = _catalog()
+    pol = rx.model_policy("policy.us_only", "v3", "owner.acme", {"allowOriginJurisdictions": ["US"]})
+    prof = rx.node_model_profile("node.rx3.1", "model.us.open", "US Open 8B", pol, model_artifact_refs=["artifact.gguf.sha256:abc"])
+    assert prof["servingLane"] == "psionic" and prof["gateway"]["phoneHomeAllowedInServingPath"] is False and prof["exactLocalMeteringRequired"]
+    inst = rx.provision_model(cat, pol, prof, "install", ["artifact.gguf.sha256:abc"], T0, "d.install", "receipt.install.1")
+    assert inst["status"] == "installed" and inst["weightsPullAuthorization"] == "authorized" and inst["refusal"] is None
+    r = rx.route_request(cat, pol, prof, inst, "model.us.open", "req.1", T0, "d.route.1")
+    assert r["status"] == "routed" and r["routedModelRef"] == "model.us.open" and r["servingPathNetwork"] == "offline_once_provisioned"
+    # a request for another model than the profile's; a refused install; a policy changed after install
+    assert rx.route_request(cat, pol, prof, inst, "model.cn.open", "req.2", T0, "d.route.2")["status"] == "refused_profile_mismatch"
+    bad_prof = rx.node_model_profile("node.rx3.2", "model.cn.open", "CN Open", pol)
+    bad = rx.provision_model(cat, pol, bad_prof, "install", [], T0, "d.install2", "receipt.install.2")
+    assert bad["status"] == "refused_policy" and bad["weightsPullAuthorization"] == "refused_before_pull"
+    assert bad["refusal"]["reason"] == "policy_nonconforming_model" and "reactor.policy.origin_not_allowed" in bad["refusal"]["blockerRefs"]
+    assert rx.route_request(cat, pol, bad_prof, bad, "model.cn.open", "req.3", T0, "d.route.3")["status"] == "refused_not_installed"
+    ghost = rx.node_model_profile("node.rx3.3", "model.unknown", "Ghost", pol)
+    assert rx.provision_model(cat, pol, ghost, "install", [], T0, "d", "r")["refusal"]["reason"] == "model_not_in_catalog"
+    v4 = rx.model_policy("policy.us_only", "v4", "owner.acme", {"allowOriginJurisdictions": ["US"], "blockDevelopers": ["Acme Labs"]})
+    late = rx.route_request(cat, v4, prof, inst, "model.us.open", "req.4", T0, "d.route.4")
+    assert late["status"] == "refused_profile_mismatch" and "blocker.reactor.router.policy_binding_mismatch" in late["blockerRefs"]
+    assert "reactor.policy.developer_blocked" in late["blockerRefs"]
+    with pytest.raises(rx.ContractError):
+        rx.node_model_profile("n", "m", "d", pol, serving_lane="other")
+
+
+def test_metering_and_evaluation_against_a_served_model(tmp_path):
+    cfg = TINY_LLAMA.with_(vocab=512, d_model=64, n_heads=2, n_kv_heads=1, head_dim=32, ffn=128)
+    p = str(tmp_path / "tiny.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 0), PLAN_Q8_0)
+    model = ServedModel("model.us.open", CpuBackend.from_gguf(p), None, max_num_seqs=2)
+    state = ServerState([model])
+    cat = _catalog()
+    pol = rx.model_policy("policy.us_only", "v3", "owner.acme", {"allowOriginJurisdictions": ["US"]})
+    prof = rx.node_model_profile("node.rx3.1", "model.us.open", "US Open", pol)
+    r, usage = state.complete(model, [{"role": "user", "content": "hello"}], {"max_tokens": 4})
+    m = rx.local_token_metering_receipt(prof, "model.us.open", "req.1", "receipt.meter.1", T0, usage)
+    assert m["usageTruth"] == "exact" and m["totalTokens"] == usage["total_tokens"] == m["promptTokens"] + 4 and m["localOnly"] and m["blockerRefs"] == []
+    nm = rx.local_token_metering_receipt(prof, "model.us.open", "req.2", "receipt.meter.2", T0, None)
+    assert nm["usageTruth"] == "not_measured" and nm["totalTokens"] is None and nm["blockerRefs"][0] == "blocker.reactor.local_metering.not_measured"
+    with pytest.raises(rx.ContractError):
+        rx.local_token_metering_receipt(prof, "m", "r", "x", T0, {"prompt_tokens": 3, "completion_tokens": 4, "total_tokens": 8})
+    # the harness this lane owns, run on the served model: what the model answers is what gets scored
+    answer = model.tok.decode(state.complete(model, [{"role": "user", "content": "q1"}], {"max_tokens": 3})[0].output)
+    complete = lambda prompt: model.tok.decode(state.complete(model, [{"role": "user", "content": prompt}], {"max_tokens": 3})[0].output)
+    meas = rx.run_task_class_eval(complete, [{"prompt": "q1", "expected": answer}, {"prompt": "q1", "expected": "\x00never\x00"}])
+    assert meas == {"state": "measured", "score": 0.5, "sampleCount": 2, "scoreUnit": "exact_match", "executionTarget": "rx3_served_model"}
+    e1 = rx.model_eval_receipt(cat, "model.us.open", "extraction", "receipt.eval.1", T0, meas)
+    e2 = rx.model_eval_receipt(cat, "model.us.open", "drafting", "receipt.eval.2", T0, {"state": "not_measured", "reasonRef": "reason.no_dataset"})
+    assert e1["capabilityCopyAllowed"] and e1["runnerOwner"] == "psionic" and e1["score"] == 0.5
+    assert not e2["capabilityCopyAllowed"] and e2["executionTarget"] == "not_measured" and e2["score"] is None
+    mat = rx.eval_coverage_matrix(cat, [e1, e2], "matrix.1", T0)
+    assert len(mat["cells"]) == 4 * 4 and sum(c["measurementState"] == "measured" for c in mat["cells"]) == 1
+    sel = rx.select_capability_copy_eval_refs("model.us.open", ["extraction", "drafting"], [e1, e2], T0, "d.copy")
+    assert sel["status"] == "blocked_not_measured" and sel["allowedEvalRefs"] == ["receipt.eval.1"] and "task_class:drafting" in sel["blockerRefs"]
+    assert rx.select_capability_copy_eval_refs("model.us.open", ["extraction"], [e1], T0, "d")["status"] == "allowed"
+    for bad in ({"state": "measured", "score": 1.5, "sampleCount": 2, "scoreUnit": "f1", "executionTarget": "rx3_served_model"},
+                {"state": "measured", "score": 0.5, "sampleCount": 0, "scoreUnit": "f1", "executionTarget": "rx3_served_model"}):
+        with pytest.raises(rx.ContractError):
+            rx.model_eval_receipt(cat, "model.us.open", "extraction", "r", T0, bad)
+    with pytest.raises(rx.ContractError):
+        rx.model_eval_receipt(cat, "model.nope", "extraction", "r", T0, meas)
+    with pytest.raises(rx.ContractError):
+        rx.eval_coverage_matrix(cat, [e1, dict(e1, receiptRef="dup")], "m", T0)
+    model.close()
