@@ -215,3 +215,117 @@ def owner_armed_rollout(recommendation: dict, owner_arm_ref: str | None) -> dict
             "canApplyLiveFlags": ready, "ownerArmRef": owner_arm_ref if ready else None, "blockers": blockers,
             "applicationPlan": {"applyMode": "owner_armed_manual", "selection": recommendation["selection"],
                                 "engineFlags": recommendation["selection"]["engineFlags"]} if ready else None}
+
+
+# ---------------------------------------------------------------- measured side: actual levers, live sweep, report
+THROUGHPUT_REPORT_SCHEMA = "openagents.gym.throughput_report.v1"
+THROUGHPUT_SAMPLE_SCHEMA = "openagents.gym.throughput_sample.v1"
+
+
+def lever_actual_from_status(status_model: dict, expectation: dict, quantization_gate: str = "not_checked") -> dict:
+    """What the engine reports about itself (one entry of ``/psionic/management/status`` ``models``) in the shape of a
+    lever expectation, with the KV headroom gate evaluated on the page counts it reports
+    (inference/gym/throughput.ts:81-101).  ``lever_mismatches`` compares the two."""
+    lv, kv = status_model.get("levers", {}), status_model.get("kv", {})
+    free = (100.0 * kv["pages_free"] / kv["pages_total"]) if kv.get("pages_total") else NOT_MEASURED
+    gate = expectation["kvHeadroomGate"]
+    kv_status = "not_checked" if free == NOT_MEASURED else ("passed" if free >= gate["minFreeKvCachePercent"] else "failed")
+    spec_on = lv.get("speculation", "none") != "none"
+    return {"label": expectation["label"], "maxNumSeqs": lv.get("max_num_seqs"), "enablePrefixCaching": bool(lv.get("prefix_caching")),
+            "enableChunkedPrefill": bool(lv.get("chunked_prefill")),
+            "lowBatchSpeculativeDecoding": ({"policy": "enabled_below_batch", "maxBatchSize": 4, "mode": lv["speculation"]} if spec_on
+                                            else {"policy": "disabled", "maxBatchSize": 1, "mode": "none"}),
+            "quantization": {**expectation["quantization"], "gateStatus": quantization_gate},
+            "kvHeadroomGate": {**gate, "observedFreeKvCachePercent": free, "gateStatus": kv_status}}
+
+
+def lever_mismatches(expectation: dict, actual: dict) -> list[str]:
+    out = [k for k in ("maxNumSeqs", "enablePrefixCaching", "enableChunkedPrefill") if expectation[k] != actual[k]]
+    if expectation["lowBatchSpeculativeDecoding"]["policy"] != actual["lowBatchSpeculativeDecoding"]["policy"]:
+        out.append("lowBatchSpeculativeDecoding")
+    if actual["kvHeadroomGate"]["gateStatus"] == "failed":
+        out.append("kvHeadroomGate")
+    if actual["quantization"]["gateStatus"] == "failed":
+        out.append("quantizationQualityGate")
+    return out
+
+
+def run_throughput_sweep(base_url: str, model: str, concurrency_ramp=(1, 2, 4, 8), samples_per_concurrency: int = 4, max_tokens: int = 32,
+                         prompt: str = "Write one sentence about rivers.", lane: str = "psionic", engine: str = "openagents_b200",
+                         timeout_s: float = 300.0, actual_levers: dict | None = None) -> list[dict]:
+    """Drive an OpenAI-compatible server: for each concurrency c, ``samples_per_concurrency`` rounds of c simultaneous
+    streamed requests; every request becomes one sample (time to first token, wall clock, perceived tokens/s, mean
+    inter-token gap, completion tokens from the terminal usage frame)."""
+    import json
+    import threading
+    import time
+    import urllib.error
+    import urllib.request
+    samples = []
+
+    def one(c, idx, barrier):
+        body = {"model": model, "messages": [{"role": "user", "content": f"{prompt} ({c}.{idx})"}], "max_tokens": max_tokens, "temperature": 0,
+                "stream": True}
+        req = urllib.request.Request(base_url.rstrip("/") + "/chat/completions", data=json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json"})
+        rec = {"schemaVersion": THROUGHPUT_SAMPLE_SCHEMA, "lane": lane, "engine": engine, "modelRef": model, "concurrency": c, "sampleIndex": idx,
+               "status": "failed", "ttftMs": NOT_MEASURED, "totalWallClockMs": NOT_MEASURED, "perceivedTps": NOT_MEASURED,
+               "interTokenLatencyMs": NOT_MEASURED, "completionTokens": NOT_MEASURED, "speculationMode": "none",
+               "speculationAcceptanceRate": NOT_MEASURED}
+        if actual_levers is not None:
+            rec["actualThroughputLevers"] = actual_levers
+        barrier.wait()
+        t0 = time.perf_counter()
+        try:
+            stamps, usage = [], None
+            with urllib.request.urlopen(req, timeout=timeout_s) as r:
+                for raw in r:
+                    line = raw.decode().strip()
+                    if not line.startswith("data:") or line.endswith("[DONE]"):
+                        continue
+                    ev = json.loads(line[5:])
+                    usage = ev.get("usage") or usage
+                    if any((ch.get("delta") or {}).get("content") for ch in ev.get("choices") or []):
+                        stamps.append(time.perf_counter())
+            t1 = time.perf_counter()
+            n = (usage or {}).get("completion_tokens")
+            rec.update(status="ok", totalWallClockMs=(t1 - t0) * 1e3, completionTokens=n if isinstance(n, int) else NOT_MEASURED)
+            if stamps:
+                rec["ttftMs"] = (stamps[0] - t0) * 1e3
+            if isinstance(n, int) and n > 0 and t1 > t0:
+                rec["perceivedTps"] = n / (t1 - t0)
+                if stamps and n > 1:
+                    rec["interTokenLatencyMs"] = (t1 - stamps[0]) * 1e3 / (n - 1)
+        except urllib.error.HTTPError as e:
+            rec.update(status="quota_limited" if e.code == 429 else "failed", errorClass=f"http_{e.code}")
+        except Exception as e:      # noqa: BLE001
+            rec["errorClass"] = type(e).__name__
+        samples.append(rec)
+
+    for c in concurrency_ramp:
+        for rnd in range(samples_per_concurrency):
+            barrier = threading.Barrier(c)
+            ts = [threading.Thread(target=one, args=(c, rnd * c + i, barrier)) for i in range(c)]
+            for t in ts:
+                t.start()
+            for t in ts:
+                t.join(timeout_s)
+    return sorted(samples, key=lambda s: (s["concurrency"], s["sampleIndex"]))
+
+
+def throughput_report(target: dict, samples: list[dict], concurrency_ramp, samples_per_concurrency: int, expectation: dict | None = None,
+                      actual: dict | None = None, degradation_threshold_multiplier: float = 2.0, prompt_profile: str = "short_chat") -> dict:
+    """The typed report (inference/gym/throughput.ts:143-162, 1682-): environment, per-concurrency points, where latency
+    degrades, the best aggregate rate, and the expected-vs-actual lever check."""
+    pts = concurrency_points(samples)
+    best = max((p for p in pts if p["aggregateTps"] is not None), key=lambda p: p["aggregateTps"], default=None)
+    mism = lever_mismatches(expectation, actual) if expectation and actual else []
+    return {"schemaVersion": THROUGHPUT_REPORT_SCHEMA, "publicSafe": True,
+            "environment": {"schemaVersion": "openagents.gym.throughput_environment.v1", "environmentRef": "throughput-concurrency",
+                            "target": target, "promptProfile": prompt_profile, "concurrencyRamp": list(concurrency_ramp),
+                            "samplesPerConcurrency": samples_per_concurrency, "degradationThresholdMultiplier": degradation_threshold_multiplier,
+                            "serving": {"speculationMode": "none"}},
+            "points": pts, "degradation": degradation_point(pts, degradation_threshold_multiplier),
+            "bestAggregate": None if best is None else {"concurrency": best["concurrency"], "aggregateTps": best["aggregateTps"]},
+            "levers": {"expected": expectation, "actual": actual, "mismatches": mism},
+            "sampleCount": len(samples), "okSampleCount": sum(s["status"] == "ok" for s in samples)}

@@ -231,7 +231,9 @@ class ServerState:
                 "mesh_coordination": self.mesh_coordination, "reasoning_budget": self.reasoning_budget,
                 "models": [{"id": m.id, "backend": m.backend.name, "architecture": m.backend.cfg.arch,
                             "artifact_digest": m.artifact_digest, "kv": m.backend.kv_stats(),
-                            "topology": m.backend.topology(), "scheduler": dict(m.sched.stats)} for m in self.models.values()],
+                            "topology": m.backend.topology(), "scheduler": dict(m.sched.stats),
+                            "levers": {"max_num_seqs": m.sched.max_num_seqs, "prefix_caching": True, "chunked_prefill": True,
+                                       "prefill_chunk": m.sched.prefill_chunk, "speculation": "none"}} for m in self.models.values()],
                 "sessions": len(self.sessions), "tokens_served": self.ledger.public_projection(),
                 "serving_rate": self.rate_monitor.tick()["classification"]}
 
