@@ -329,3 +329,40 @@ def throughput_report(target: dict, samples: list[dict], concurrency_ramp, sampl
             "bestAggregate": None if best is None else {"concurrency": best["concurrency"], "aggregateTps": best["aggregateTps"]},
             "levers": {"expected": expectation, "actual": actual, "mismatches": mism},
             "sampleCount": len(samples), "okSampleCount": sum(s["status"] == "ok" for s in samples)}
+
+
+def main(argv=None) -> int:
+    """``python -m openagents_b200.gateway.benchmark --base-url http://127.0.0.1:8080 --model <id>``: live sweep against
+    a running server, one JSON line per concurrency and a closing summary line."""
+    import argparse
+    import json
+    import urllib.request
+    ap = argparse.ArgumentParser(prog="b200-throughput-sweep")
+    ap.add_argument("--base-url", default="http://127.0.0.1:8080")
+    ap.add_argument("--model", required=True)
+    ap.add_argument("--ramp", default="1,8,32,64")
+    ap.add_argument("--samples", type=int, default=2)
+    ap.add_argument("--max-tokens", type=int, default=128)
+    ap.add_argument("--prompt", default="Tell me a long story about a river and a mountain.")
+    a = ap.parse_args(argv)
+    base = a.base_url.rstrip("/")
+    ramp = tuple(int(x) for x in a.ramp.split(","))
+    st = next(m for m in json.loads(urllib.request.urlopen(base + "/psionic/management/status").read())["models"] if m["id"] == a.model)
+    exp = lever_expectation(st["levers"]["max_num_seqs"], speculation_below_batch=None)
+    act = lever_actual_from_status(st, exp)
+    run_throughput_sweep(base + "/v1", a.model, concurrency_ramp=(min(8, max(ramp)),), samples_per_concurrency=1, max_tokens=16)     # warm-up
+    samples = run_throughput_sweep(base + "/v1", a.model, ramp, a.samples, a.max_tokens, a.prompt, actual_levers=act)
+    rep = throughput_report({"lane": "psionic", "engine": "openagents_b200", "modelRef": a.model}, samples, ramp, a.samples, exp, act)
+    for p in rep["points"]:
+        wall = p["totalWallClockMs"]["mean"]
+        done = p["completionTokens"]["mean"]
+        print(json.dumps({"concurrency": p["concurrency"], "ok": p["okSamples"], "of": p["totalSamples"],
+                          "per_request_tok_s": p["perceivedTps"]["mean"], "aggregate_tok_s": p["aggregateTps"],
+                          "round_wall_ms": wall, "completion_tokens": done, "ttft_p50_ms": p["ttftMs"]["p50"]}))
+    print(json.dumps({"best": rep["bestAggregate"], "degradation": rep["degradation"], "lever_mismatches": rep["levers"]["mismatches"],
+                      "kv_headroom": act["kvHeadroomGate"]}))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -502,8 +502,13 @@ def build_state(model_paths: list[str], backend: str = "cuda", max_num_seqs: int
     return ServerState(models, reasoning_budget, mesh_coordination)
 
 
+class _Server(ThreadingHTTPServer):
+    # the default listen backlog of 5 resets connections when a few dozen clients connect in the same instant
+    request_queue_size = 1024
+
+
 def serve(state: ServerState, host: str = "127.0.0.1", port: int = 8080) -> ThreadingHTTPServer:
-    httpd = ThreadingHTTPServer((host, port), make_handler(state))
+    httpd = _Server((host, port), make_handler(state))
     httpd.daemon_threads = True
     return httpd
 
