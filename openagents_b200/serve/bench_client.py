@@ -93,10 +93,12 @@ class MemorySampler:
         self._thread = threading.Thread(target=self._run, daemon=True)
 
     def _run(self):
-        while not self._stop.wait(self.period):
+        while True:                      # first sample at once, so that a run shorter than the period still has one
             kib = self.probe(self.pid)
             if kib:
                 self.samples_kib.append(kib)
+            if self._stop.wait(self.period):
+                return
 
     def start(self):
         self._thread.start()

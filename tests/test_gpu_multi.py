@@ -398,8 +398,11 @@ def test_server_tp2_over_http(tmp_path):
         from openagents_b200.serve.bench_client import run_benchmark
         rep = run_benchmark(base + "/v1", "local", "tiny", "tp2-test", repetitions=1, only=("exact_instruction", "multi_turn_memory", "structured_json"),
                             max_tokens=12, server_pid=proc.pid)
-        assert len(rep["results"]) == 3 and all(r["http_status"] == 200 and r["ttft_seconds"] is not None for r in rep["results"])
-        assert all(v["ok"] == 1 and v["decode_tok_s_median"] for v in rep["summary"].values()) and rep["memory"]["peak_rss_kib"] > 0
+        # (a random model over the byte tokenizer may emit no printable text, so time-to-first-token can be unmeasured;
+        # the status, the exact usage and the memory sampler are what is checked)
+        assert len(rep["results"]) == 3 and all(r["http_status"] == 200 and r["total_seconds"] > 0 for r in rep["results"])
+        assert all((r["usage"] or {}).get("completion_tokens") == 12 for r in rep["results"])
+        assert all(v["ok"] == 1 for v in rep["summary"].values()) and rep["memory"]["peak_rss_kib"] > 0
         post("/admin/shutdown", {})
         assert proc.wait(120) == 0, "".join(lines[-30:])
     finally:
