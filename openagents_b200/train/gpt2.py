@@ -147,7 +147,9 @@ class GPT2Model:
             self._gemm(dy, self.wT[wname], M, K, N, out_bf16=dx_out)
 
     # ---- forward + backward of one micro-batch; returns the mean loss (device scalar)
-    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, loss_scale: float = 1.0):
+    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, loss_scale: float = 1.0, on_bucket=None):
+        """``on_bucket(i)`` is called right after the backward of layer ``i`` has been enqueued (its weight gradients are then
+        final for this micro-batch) and ``on_bucket(None)`` at the very end (embeddings, norms and biases)."""
         cfg, M, T, d = self.cfg, self.M, self.T, self.cfg.d_model
         H, hd = cfg.n_heads, cfg.head_dim
         ids = tokens.reshape(-1).to(torch.int32)
@@ -204,6 +206,10 @@ class GPT2Model:
             tops.layernorm_bwd(self.d_d, a["x_in"], self.vec[pre + "attn_norm.weight"], a["mean1"], a["rstd1"], self.dx,
                                True, self.g[pre + "attn_norm.weight"], self.g[pre + "attn_norm.bias"])
             self.kernel_launches += 6
+            if on_bucket is not None:
+                on_bucket(i)
         tops.embed_bwd(ids, self.dx, self.g["token_embd.weight"], self.g["position_embd.weight"], T)
         self.kernel_launches += 1
+        if on_bucket is not None:
+            on_bucket(None)
         return loss

@@ -47,6 +47,7 @@ class TrainConfig:
     total_steps: int = 0             # 0 = constant learning rate after warm-up
     seed: int = 0
     zero_stage: int = 2
+    overlap_grad_reduce: bool = True  # reduce-scatter each layer's gradients while the backward of the layers below it runs
 
 
 class Trainer:
@@ -78,6 +79,19 @@ class Trainer:
         self.model.refresh_param_views()
         self.grads.zero_()
         self.last_grad_norm = float("nan")
+        # gradient buckets: one per layer (its weight matrices are contiguous in the flat buffer), the rest at the end
+        self._layer_ranges = []
+        for i in range(m.n_layers):
+            mine = [sl for sl in self.slots if sl.name.startswith(f"blk.{i}.") and sl.decay]
+            lo_i, hi_i = min(sl.offset for sl in mine), max(sl.offset + (sl.numel + 63) // 64 * 64 for sl in mine)
+            if any(lo_i <= sl.offset < hi_i and sl not in mine for sl in self.slots):
+                self._layer_ranges = []          # layout is not layer-contiguous: one bucket for everything
+                break
+            self._layer_ranges.append((lo_i, hi_i))
+        if any(a[1] != b[0] for a, b in zip(self._layer_ranges, self._layer_ranges[1:])):
+            self._layer_ranges = []              # the "rest" bucket assumes the layers lie back to back
+        self._comm_stream = None
+        self._reduced = False
 
     # ---- initialisation: every rank draws the same seeded values and keeps its shard as master
     def _init_params(self):
@@ -108,18 +122,56 @@ class Trainer:
     def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         losses = []
         for a in range(self.accum):
-            losses.append(self.model.forward_backward(tokens[a], targets[a], loss_scale=1.0 / self.accum))
+            hook = None
+            if a == self.accum - 1 and self.cfg.overlap_grad_reduce and self._layer_ranges and self.device.type == "cuda":
+                self.norm2.zero_()
+                hook = self._bucket_ready
+            losses.append(self.model.forward_backward(tokens[a], targets[a], loss_scale=1.0 / self.accum, on_bucket=hook))
         self.optimizer_step()
         return torch.stack(losses).mean()
+
+    # ---- bucketed gradient reduce-scatter, overlapped with backward
+    def _reduce_range(self, lo: int, hi: int):
+        """This rank's part of the flat range [lo, hi): cross-rank barrier (everyone's gradients for the range are final),
+        then the fused reduce-scatter + mean + squared norm on the intersection with this rank's shard.  Every rank
+        launches both kernels for every range, also with an empty intersection, so the barrier counts stay in step."""
+        a, b = max(lo, self.lo), min(hi, self.lo + self.shard)
+        n = max(0, b - a)
+        self.heap.barrier(ch=3)
+        off = (a - self.lo) if n else 0
+        tops.zero_reduce_norm(self.heap.table, self.grad_off, a if n else self.lo, n, self.gshard[off:], self.norm2)
+        self.model.kernel_launches += 2
+
+    def _bucket_ready(self, layer):
+        main = torch.cuda.current_stream(self.device)
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(self.device)
+        ev = torch.cuda.Event()
+        ev.record(main)
+        self._comm_stream.wait_event(ev)
+        with torch.cuda.stream(self._comm_stream):
+            if layer is not None:
+                self._reduce_range(*self._layer_ranges[layer])
+            else:                                   # everything outside the layer buckets: embeddings, norms, biases, padding
+                first, last = self._layer_ranges[0][0], self._layer_ranges[-1][1]
+                self._reduce_range(0, first)
+                self._reduce_range(last, self.n_total)
+                done = torch.cuda.Event()
+                done.record(self._comm_stream)
+                main.wait_event(done)
+                self._reduced = True
 
     @nvtx_method("train.optimizer_step(reduce_scatter+adamw+all_gather)")
     def optimizer_step(self):
         c, T = self.cfg, self.heap.table
         self.step_count += 1
         t = self.step_count
-        self.norm2.zero_()
-        self.heap.barrier(ch=3)                       # every rank's gradients are complete
-        tops.zero_reduce_norm(T, self.grad_off, self.lo, self.shard, self.gshard, self.norm2)
+        if self._reduced:                             # the buckets were reduced while backward ran
+            self._reduced = False
+        else:
+            self.norm2.zero_()
+            self.heap.barrier(ch=3)                   # every rank's gradients are complete
+            tops.zero_reduce_norm(T, self.grad_off, self.lo, self.shard, self.gshard, self.norm2)
         if self.world > 1:
             self.heap.all_reduce_f32(self.norm_off, 4, ch=3)
         tops.zero_adamw_gather(T, self.param_off, self.lo, self.shard, self.gshard, self.master, self.m, self.v,
