@@ -758,14 +758,16 @@ class LlamaEngine:
 
     @torch.no_grad()
     @nvtx_method("engine.prefill")
-    def forward_tokens(self, seq_ids: list[int], new_tokens: list[list[int]], greedy: bool = True):
+    def forward_tokens(self, seq_ids: list[int], new_tokens: list[list[int]], greedy: bool = True, all_positions: bool = False):
         """Append ``new_tokens[b]`` to sequence ``seq_ids[b]`` and return the logits of each
-        sequence's last new token ([B, V] view, valid until the next call) and their arg-max."""
+        sequence's last new token ([B, V] view, valid until the next call) and their arg-max.  ``all_positions``: the
+        logits and arg-max of EVERY new token instead ([T, V], in feeding order): what verifying a speculated
+        continuation needs; T is then limited by the logits workspace (``max_batch`` rows)."""
         B = len(seq_ids)
         staged = self._stage_batch(seq_ids, new_tokens)
         ids, pos, slot, q_start, q_len, ctx, table = staged
         T = len(ids)
-        if T > self.max_tokens or B > self.max_batch:
+        if T > self.max_tokens or B > self.max_batch or (all_positions and T > self.max_batch):
             raise ValueError("batch exceeds the engine's workspace")
         self._upload(*staged)
         self._embed(T)
@@ -775,6 +777,9 @@ class LlamaEngine:
             self._layers_small(T, pages)
         else:
             self._layers_dense(T, decode, B, max(q_len), pages)
+        if all_positions:
+            self._head(self.x[:T], T, greedy)
+            return self.logits[:T], self.out_ids[:T]
         if decode:
             rows = self.x[:B]
         else:

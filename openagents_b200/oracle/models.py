@@ -23,6 +23,12 @@ class KVCacheRef:
     def length(self) -> int:
         return 0 if self.k[0] is None else self.k[0].shape[0]
 
+    def truncate(self, n: int):
+        """Keep the first ``n`` positions (a rejected speculative tail is dropped)."""
+        for i in range(len(self.k)):
+            if self.k[i] is not None:
+                self.k[i], self.v[i] = self.k[i][:n], self.v[i][:n]
+
 
 def _lin(x, w, b=None):
     y = x @ w.t()

@@ -36,6 +36,20 @@ class Backend:
 
     last_d2h_bytes = 0
 
+    # ---- speculative decoding support (optional): a backend that implements all three can verify drafted tokens
+    supports_verify = False
+
+    def verify(self, seq_id: int, tokens: list[int]) -> list[int]:
+        """Append ``tokens`` and return the greedy prediction after EACH of them (``len(tokens)`` ids)."""
+        raise NotImplementedError
+
+    def truncate(self, seq_id: int, new_len: int):
+        """Forget the sequence's positions from ``new_len`` on."""
+        raise NotImplementedError
+
+    def seq_len(self, seq_id: int) -> int:
+        raise NotImplementedError
+
     @property
     def max_context(self) -> int | None:
         """Longest sequence (prompt + generated) the backend can hold, or None when it does not know."""
@@ -104,6 +118,19 @@ class CpuBackend(Backend):
 
     def end(self, seq_id):
         self.caches.pop(seq_id, None)
+
+    supports_verify = True
+
+    @torch.no_grad()
+    def verify(self, seq_id, tokens):
+        from ..oracle.models import llama_forward
+        return llama_forward(self.cfg, self.W, torch.tensor(tokens, dtype=torch.long), self.caches[seq_id]).float().argmax(-1).tolist()
+
+    def truncate(self, seq_id, new_len):
+        self.caches[seq_id].truncate(new_len)
+
+    def seq_len(self, seq_id):
+        return self.caches[seq_id].length
 
     @property
     def max_context(self):
@@ -194,6 +221,19 @@ class CudaBackend(Backend):
 
     def end(self, seq_id):
         self.engine.end(seq_id)
+
+    supports_verify = True
+
+    def verify(self, seq_id, tokens):
+        _, ids = self.engine.forward_tokens([seq_id], [list(tokens)], all_positions=True)
+        self.last_d2h_bytes = 4 * len(tokens)
+        return ids[: len(tokens)].tolist()
+
+    def truncate(self, seq_id, new_len):
+        self.engine.truncate(seq_id, new_len)
+
+    def seq_len(self, seq_id):
+        return self.engine.pool.length(seq_id)
 
     @property
     def max_context(self):

@@ -55,6 +55,19 @@ class LeaderBackend(Backend):
     def end(self, seq_id):
         return self._call("end", seq_id)
 
+    @property
+    def supports_verify(self):
+        return self.inner.supports_verify
+
+    def verify(self, seq_id, tokens):
+        return self._call("verify", seq_id, list(tokens))
+
+    def truncate(self, seq_id, new_len):
+        return self._call("truncate", seq_id, new_len)
+
+    def seq_len(self, seq_id):
+        return self.inner.seq_len(seq_id)          # host-side bookkeeping, identical on every rank
+
     def shutdown(self):
         _announce(self.group, ("stop", ()))
 

@@ -217,6 +217,34 @@ class SamplingParams:
 
 
 @dataclass
+class SpeculationConfig:
+    """Low-batch speculative decoding by n-gram lookup in the sequence's own tokens (prompt-lookup drafting): when at
+    most ``max_batch`` sequences are decoding, a greedy request whose last ``ngram`` tokens occurred before proposes the
+    up to ``draft`` tokens that followed them; one forward over last token + draft verifies all of them and yields one
+    more token, the rejected tail is cut from the KV cache.  The output is exactly the greedy output.  The lever the
+    gateway's throughput report calls ``lowBatchSpeculativeDecoding`` (inference/gym/throughput.ts:49-55, 114-135:
+    ``enabled_below_batch``, ``maxBatchSize`` 4, mode ``n_gram``)."""
+    mode: str = "n_gram"
+    max_batch: int = 4
+    ngram: int = 3
+    draft: int = 4
+    min_ngram: int = 2
+
+
+def ngram_draft(context: list[int], ngram: int, draft: int, min_ngram: int = 2) -> list[int]:
+    """The tokens that followed the most recent earlier occurrence of the context's last n tokens (longest n first)."""
+    L = len(context)
+    for n in range(min(ngram, L - 1), min_ngram - 1, -1):
+        tail = context[L - n:]
+        for start in range(L - n - 1, -1, -1):
+            if context[start: start + n] == tail:
+                out = context[start + n: start + n + draft]
+                if out:
+                    return out
+    return []
+
+
+@dataclass
 class Request:
     request_id: str
     prompt: list[int]
@@ -262,15 +290,21 @@ class Scheduler:
     a lock and runs ``step`` on its scheduling thread)."""
 
     def __init__(self, backend: Backend, tokenizer, max_num_seqs: int = 64, prefill_chunk: int = 2048,
-                 now=time.perf_counter):
+                 now=time.perf_counter, speculation: SpeculationConfig | None = None):
         self.backend, self.tok, self.max_num_seqs, self.prefill_chunk, self.now = backend, tokenizer, max_num_seqs, prefill_chunk, now
+        self.speculation = speculation if (speculation and speculation.mode == "n_gram" and getattr(backend, "supports_verify", False)) else None
         self.waiting: list[Request] = []
         self.running: list[Request] = []
         self._seq_ids = itertools.count(1)
         self._req_ids = itertools.count(1)
         self.stats = {"requests": 0, "prompt_tokens": 0, "completion_tokens": 0, "cached_prompt_tokens": 0, "steps": 0,
                       "batch_size_sum": 0, "prefill_calls": 0, "prefill_seqs_sum": 0, "errors": 0, "rejected": 0,
-                      "d2h_bytes": 0}
+                      "d2h_bytes": 0, "spec_steps": 0, "spec_drafted": 0, "spec_accepted": 0}
+
+    @property
+    def speculation_acceptance_rate(self) -> float | None:
+        d = self.stats["spec_drafted"]
+        return self.stats["spec_accepted"] / d if d else None
 
     @property
     def has_work(self) -> bool:
@@ -412,6 +446,14 @@ class Scheduler:
             progressed += len(batch)
         # ---- one decode step for everyone who has a token to feed
         dec = [r for r in self.running if r.next_token is not None]
+        if dec and self.speculation is not None and len(dec) <= self.speculation.max_batch:
+            rest = []
+            for r in dec:
+                if r.params.greedy and self._speculate(r):
+                    progressed += 1
+                else:
+                    rest.append(r)
+            dec = rest
         if dec:
             toks = self._sample_batch(dec, [r.seq_id for r in dec], [[r.next_token] for r in dec])
             self.stats["steps"] += 1
@@ -421,6 +463,53 @@ class Scheduler:
                     self._accept(r, tok)
             progressed += len(dec)
         return progressed
+
+    def _speculate(self, r: Request) -> bool:
+        """Draft, verify and accept for one greedy request; False when there was nothing to draft (the request then takes
+        the normal decode step).  On a backend error the request is finished with that error, like in any other step."""
+        sp, be = self.speculation, self.backend
+        room = r.params.max_tokens - len(r.output) - 1            # drafts we could still emit before the bonus token
+        limit = getattr(be, "max_context", None)
+        try:
+            base = be.seq_len(r.seq_id)
+        except Exception:      # noqa: BLE001
+            return False
+        if limit is not None:
+            room = min(room, limit - base - 2)
+        if room < 1:
+            return False
+        draft = ngram_draft(r.history + r.prompt + r.output, sp.ngram, min(sp.draft, room), sp.min_ngram)
+        if not draft:
+            return False
+        try:
+            preds = be.verify(r.seq_id, [r.next_token] + draft)
+            self.stats["d2h_bytes"] += getattr(be, "last_d2h_bytes", 0)
+        except Exception as e:      # noqa: BLE001
+            self._finish(r, "error", e)
+            return True
+        k = len(draft)
+        n_acc = 0
+        while n_acc < k and draft[n_acc] == preds[n_acc]:
+            n_acc += 1
+        self.stats["spec_steps"] += 1
+        self.stats["spec_drafted"] += k
+        self.stats["spec_accepted"] += n_acc
+        self.stats["steps"] += 1
+        self.stats["batch_size_sum"] += 1
+        i_last = n_acc
+        for i, tok in enumerate(draft[:n_acc] + [preds[n_acc]]):
+            self._accept(r, tok)
+            if r.state == "finished":
+                i_last = i
+                break
+        keep = base + 1 + i_last                  # the fed token plus the accepted tokens whose successors were used
+        if keep < base + 1 + k and (r.state != "finished" or (r.keep_sequence and r.finish_reason not in ("error", "cancelled"))):
+            try:
+                be.truncate(r.seq_id, keep)
+            except Exception as e:      # noqa: BLE001
+                if r.state != "finished":
+                    self._finish(r, "error", e)
+        return True
 
     def run_until_done(self, reqs: list[Request], max_steps: int = 1_000_000):
         for _ in range(max_steps):

@@ -45,11 +45,11 @@ class ServedModel:
     others are decoding join the same decode batch (continuous batching across connections)."""
 
     def __init__(self, model_id: str, backend, artifact_digest: str | None, tokenizer=None, max_num_seqs: int = 64,
-                 prefill_chunk: int = 2048, chat_template: str | None = None):
+                 prefill_chunk: int = 2048, chat_template: str | None = None, speculation=None):
         self.id, self.backend, self.artifact_digest = model_id, backend, artifact_digest
         self.tok = tokenizer or ByteTokenizer(backend.cfg.vocab)
         self.chat_template = chat_template          # a GGUF chat template admitted by the digest allowlist, or None
-        self.sched = Scheduler(backend, self.tok, max_num_seqs=max_num_seqs, prefill_chunk=prefill_chunk)
+        self.sched = Scheduler(backend, self.tok, max_num_seqs=max_num_seqs, prefill_chunk=prefill_chunk, speculation=speculation)
         self.cv = threading.Condition()              # guards the scheduler and the backend
         self.waiters = 0                             # handler threads that want the lock (see _loop)
         self._wl = threading.Lock()
@@ -233,7 +233,9 @@ class ServerState:
                             "artifact_digest": m.artifact_digest, "kv": m.backend.kv_stats(),
                             "topology": m.backend.topology(), "scheduler": dict(m.sched.stats),
                             "levers": {"max_num_seqs": m.sched.max_num_seqs, "prefix_caching": True, "chunked_prefill": True,
-                                       "prefill_chunk": m.sched.prefill_chunk, "speculation": "none"}} for m in self.models.values()],
+                                       "prefill_chunk": m.sched.prefill_chunk,
+                                       "speculation": m.sched.speculation.mode if m.sched.speculation else "none",
+                                       "speculation_acceptance_rate": m.sched.speculation_acceptance_rate}} for m in self.models.values()],
                 "sessions": len(self.sessions), "tokens_served": self.ledger.public_projection(),
                 "serving_rate": self.rate_monitor.tick()["classification"]}
 
@@ -477,7 +479,7 @@ def load_tokenizer(path: str, vocab_size: int):
 def build_state(model_paths: list[str], backend: str = "cuda", max_num_seqs: int = 64, kv_page_size: int = 16,
                 max_ctx: int = 4096, reasoning_budget: int = 0, mesh_coordination: str = "disabled",
                 device="cuda:0", tp_rank: int = 0, tp_world: int = 1, ep_rank: int = 0, ep_world: int = 1, comm=None,
-                control_group=None) -> ServerState:
+                control_group=None, speculation=None) -> ServerState:
     """``tp_world`` / ``ep_world`` > 1: this process is rank 0 of a tensor- or expert-parallel group whose other ranks
     run ``serve.distributed.follower_loop``; every engine call is first announced to them over ``control_group``."""
     from ..receipts.manifests import artifact_digest
@@ -498,7 +500,8 @@ def build_state(model_paths: list[str], backend: str = "cuda", max_num_seqs: int
             b = LeaderBackend(b, control_group)
         mid = p.rsplit("/", 1)[-1].removesuffix(".gguf")
         tok, tpl = load_tokenizer(p, b.cfg.vocab)
-        models.append(ServedModel(mid, b, artifact_digest(p), tokenizer=tok, max_num_seqs=max_num_seqs, chat_template=tpl))
+        models.append(ServedModel(mid, b, artifact_digest(p), tokenizer=tok, max_num_seqs=max_num_seqs, chat_template=tpl,
+                                  speculation=speculation))
     return ServerState(models, reasoning_budget, mesh_coordination)
 
 
@@ -532,6 +535,9 @@ def parse_args(argv=None):
     ap.add_argument("--kv-page-size", type=int, default=_flag_env("kv-page-size", 16))
     ap.add_argument("--max-num-seqs", type=int, default=_flag_env("max-num-seqs", 64))
     ap.add_argument("--max-ctx", type=int, default=_flag_env("max-ctx", 4096))
+    ap.add_argument("--speculation", default=_flag_env("speculation", "none"), choices=["none", "n_gram"],
+                    help="low-batch speculative decoding: n-gram drafts verified in one forward (greedy requests only)")
+    ap.add_argument("--speculation-max-batch", type=int, default=_flag_env("speculation-max-batch", 4))
     ap.add_argument("--allow-shutdown", action="store_true", help="accept POST /admin/shutdown (stops every rank between steps)")
     a = ap.parse_args(argv)
     if a.tp > 1 and a.ep > 1:
@@ -542,8 +548,12 @@ def parse_args(argv=None):
 
 
 def run_server(a, **parallel):
+    spec = None
+    if getattr(a, "speculation", "none") == "n_gram":
+        from .generation import SpeculationConfig
+        spec = SpeculationConfig(max_batch=a.speculation_max_batch)
     state = build_state(a.model, a.backend, a.max_num_seqs, a.kv_page_size, a.max_ctx, a.reasoning_budget, a.mesh_coordination,
-                        **parallel)
+                        speculation=spec, **parallel)
     state.allow_shutdown = bool(getattr(a, "allow_shutdown", False))
     httpd = serve(state, a.host, a.port)
     print(json.dumps({"event": "listening", "host": a.host, "port": httpd.server_address[1], "models": list(state.models),

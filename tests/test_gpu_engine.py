@@ -196,3 +196,40 @@ def test_workspace_canaries_stay_intact(tmp_path):
     raw_q, _ = eng._guards["qkv"]
     raw_q[eng._GUARD_BYTES - 1] = 7                        # one byte before the start of `qkv`
     assert sorted(eng.check_canaries()) == ["gu:after", "qkv:before"]
+
+
+def test_speculative_decoding_matches_greedy_on_the_engine(tmp_path):
+    """N-gram drafts verified by one multi-token forward with logits at every position, rejected tails cut from the
+    paged cache: the tokens are exactly those of plain greedy decoding, also across a second turn on the same sequence."""
+    from openagents_b200.serve.backend import CudaBackend
+    from openagents_b200.serve.generation import ByteTokenizer, SamplingParams, Scheduler, SpeculationConfig
+    cfg = TINY_LLAMA.with_(d_model=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1024, vocab=4096, n_layers=2)
+    p = str(tmp_path / "q4k.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 9), PLAN_Q4_K)
+    prompt = list(b"abcabcabcabc the cat sat on the mat the cat sat on")
+    outs = {}
+    for name, spec in (("plain", None), ("spec", SpeculationConfig(max_batch=4, ngram=3, draft=4))):
+        be = CudaBackend.from_gguf(p, max_num_seqs=8, max_ctx=512, max_tokens=512)
+        sch = Scheduler(be, ByteTokenizer(be.cfg.vocab), max_num_seqs=4, speculation=spec)
+        r = sch.submit(prompt, SamplingParams(max_tokens=48), keep_sequence=True)
+        sch.run_until_done([r])
+        feed = [r.output[-1]] + list(b" again")
+        r2 = sch.submit(feed, SamplingParams(max_tokens=16), seq_id=r.seq_id, keep_sequence=True, history=prompt + r.output[:-1])
+        sch.run_until_done([r2])
+        outs[name] = (r.output, r2.output)
+        be.engine.check_status()
+        if spec:
+            assert sch.stats["spec_steps"] > 0
+            print("speculation:", {k: v for k, v in sch.stats.items() if k.startswith("spec")}, "steps", sch.stats["steps"])
+    assert outs["spec"] == outs["plain"]
+    # the verify call itself: predictions at every position equal stepping one token at a time
+    be = CudaBackend.from_gguf(p, max_num_seqs=8, max_ctx=512, max_tokens=512)
+    be.begin(1, prompt)
+    be.begin(2, prompt)
+    be.forward([1, 2], [prompt[:-5], prompt[:-5]])
+    tail = prompt[-5:]
+    all_at_once = be.verify(1, tail)
+    one_by_one = [be.step([2], [[t]], [SamplingParams()], [0.0])[0] for t in tail]
+    assert all_at_once == one_by_one and be.seq_len(1) == len(prompt)
+    be.truncate(1, len(prompt) - 3)
+    assert be.seq_len(1) == len(prompt) - 3 and be.verify(1, tail[2:]) == all_at_once[2:]

@@ -372,3 +372,37 @@ def test_stream_flushes_bytes_held_back_as_incomplete_utf8(gguf_path):
     assert want and text == want
     httpd.shutdown()
     model.close()
+
+
+def test_ngram_speculation_gives_exactly_the_greedy_output(gguf_path):
+    """Prompt-lookup drafts verified in one forward: same tokens as plain greedy decoding, fewer steps, KV rolled back
+    after rejected tails (a second turn on the same session still matches), stop conditions honoured mid-draft."""
+    from openagents_b200.serve.generation import SpeculationConfig, ngram_draft
+    assert ngram_draft([1, 2, 3, 4, 5, 1, 2, 3], 3, 4) == [4, 5, 1, 2] and ngram_draft([1, 2, 3], 3, 4) == []
+    prompt = list(b"abcabcabcabc the cat sat on the mat the cat sat on")
+    outs, steps = {}, {}
+    for name, spec in (("plain", None), ("spec", SpeculationConfig(max_batch=4, ngram=3, draft=4))):
+        be = CpuBackend.from_gguf(gguf_path)
+        sch = Scheduler(be, ByteTokenizer(be.cfg.vocab), max_num_seqs=4, speculation=spec)
+        r = sch.submit(prompt, SamplingParams(max_tokens=40), keep_sequence=True)
+        sch.run_until_done([r])
+        # a second turn on the same sequence: only correct if the KV cache holds exactly the accepted tokens
+        feed = [r.output[-1]] + list(b" again")
+        r2 = sch.submit(feed, SamplingParams(max_tokens=12), seq_id=r.seq_id, keep_sequence=True, history=prompt + r.output[:-1])
+        sch.run_until_done([r2])
+        outs[name], steps[name] = (r.output, r2.output, r.finish_reason), sch.stats["steps"]
+        if spec:
+            st = sch.stats
+            assert st["spec_steps"] > 0 and st["spec_drafted"] >= st["spec_accepted"] >= 0
+            held = lambda q: len(q.output) - (1 if q.finish_reason == "length" else 0)      # an end-of-sequence token was sampled from the last output's forward
+            assert be.seq_len(r.seq_id) == len(prompt) + held(r) + len(feed) + held(r2)
+            rate = sch.speculation_acceptance_rate
+            assert rate is not None and 0.0 <= rate <= 1.0
+    assert outs["spec"] == outs["plain"]
+    assert steps["spec"] <= steps["plain"]
+    # sampling requests and large batches never speculate
+    be = CpuBackend.from_gguf(gguf_path)
+    sch = Scheduler(be, ByteTokenizer(be.cfg.vocab), max_num_seqs=8, speculation=SpeculationConfig(max_batch=1))
+    rs = [sch.submit(prompt, SamplingParams(max_tokens=6)) for _ in range(2)] + [sch.submit(prompt, SamplingParams(max_tokens=6, temperature=0.8, seed=1))]
+    sch.run_until_done(rs)
+    assert sch.stats["spec_steps"] == 0
