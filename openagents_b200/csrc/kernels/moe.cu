@@ -45,42 +45,70 @@ __global__ void __launch_bounds__(256) moe_route_dispatch_kernel(const MoeDispat
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const __nv_bfloat16* hr = a.h + (size_t)t * a.d;
 
-  // Router logits: warp w takes experts w, w + 8, ...
+  // Router logits: warp w takes experts w, w + 8, ... FOUR at a time (the hidden row is read once per group and four
+  // weight rows stream beside it, so a warp has five independent loads in flight per step instead of two).
   const float* hfr = a.hf ? a.hf + (size_t)t * a.d : nullptr;
-  for (int e = w; e < a.E; e += 8) {
-    const float* wr = a.wr + (size_t)e * a.d;
-    float acc = 0.f;
+  for (int e0 = w; e0 < a.E; e0 += 32) {
+    const float* wr[4];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 4; j++) wr[j] = a.wr + (size_t)min(e0 + 8 * j, a.E - 1) * a.d;
+#pragma unroll 2
     for (int i = lane * 2; i < a.d; i += 64) {
       const float2 x = hfr ? *(const float2*)(hfr + i) : __bfloat1622float2(*(const __nv_bfloat162*)(hr + i));
-      const float2 y = *(const float2*)(wr + i);
-      acc += x.x * y.x + x.y * y.y;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float2 y = *(const float2*)(wr[j] + i);
+        acc[j] += x.x * y.x + x.y * y.y;
+      }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) s_logit[e] = acc + (a.br ? a.br[e] : 0.f);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float v = warp_sum(acc[j]);
+      const int e = e0 + 8 * j;
+      if (lane == 0 && e < a.E) s_logit[e] = v + (a.br ? a.br[e] : 0.f);
+    }
   }
   __syncthreads();
 
-  if (tid == 0) {
-    // top-k by repeated arg-max (lowest index wins ties), then softmax over the k winners
-    float vals[kMoeMaxTopK];
+  if (w == 0) {
+    // top-k by repeated arg-max over the warp (lowest index wins ties), softmax over the k winners, then lane k claims
+    // a row in its expert's receive buffer: the k remote atomics are in flight together instead of one after another
+    float mine[(kMoeMaxExperts + 31) / 32];
+#pragma unroll
+    for (int j = 0; j < (kMoeMaxExperts + 31) / 32; j++) mine[j] = lane + 32 * j < a.E ? s_logit[lane + 32 * j] : -INFINITY;
+    float my_val = 0.f;
+    int my_sel = 0;
+    float mx = 0.f, sum = 0.f;
     for (int k = 0; k < a.top_k; k++) {
       float best = -INFINITY;
-      int bi = 0;
-      for (int e = 0; e < a.E; e++)
-        if (s_logit[e] > best) { best = s_logit[e]; bi = e; }
-      vals[k] = best;
-      s_sel[k] = bi;
-      s_logit[bi] = -INFINITY;
+      int bi = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < (kMoeMaxExperts + 31) / 32; j++)
+        if (mine[j] > best) { best = mine[j]; bi = lane + 32 * j; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      if (bi == 0x7fffffff) bi = 0;              // a row without a finite logit
+      if (k == 0) mx = best;
+      const float ex = __expf(best - mx);
+      sum += ex;
+      if (lane == k) { my_val = ex; my_sel = bi; }
+#pragma unroll
+      for (int j = 0; j < (kMoeMaxExperts + 31) / 32; j++)
+        if (lane + 32 * j == bi) mine[j] = -INFINITY;
     }
-    const float mx = vals[0];
-    float sum = 0.f;
-    for (int k = 0; k < a.top_k; k++) { vals[k] = __expf(vals[k] - mx); sum += vals[k]; }
-    for (int k = 0; k < a.top_k; k++) {
-      s_w[k] = vals[k] / sum;
-      if (a.topk_ids) a.topk_ids[(size_t)t * a.top_k + k] = s_sel[k];
-      if (a.topk_w) a.topk_w[(size_t)t * a.top_k + k] = s_w[k];
-      // claim a row in the owner's receive buffer
-      const int owner = s_sel[k] / a.E_local, el = s_sel[k] % a.E_local;
+    if (lane < a.top_k) {
+      const int k = lane;
+      const float wgt = my_val / sum;
+      s_sel[k] = my_sel;
+      s_w[k] = wgt;
+      if (a.topk_ids) a.topk_ids[(size_t)t * a.top_k + k] = my_sel;
+      if (a.topk_w) a.topk_w[(size_t)t * a.top_k + k] = wgt;
+      const int owner = my_sel / a.E_local, el = my_sel % a.E_local;
       unsigned slot;
       asm volatile("atom.relaxed.sys.global.add.u32 %0, [%1], %2;" : "=r"(slot)
                    : "l"(a.sym.base[owner] + a.counts_off + (size_t)el * 4), "r"(1u) : "memory");
@@ -93,7 +121,7 @@ __global__ void __launch_bounds__(256) moe_route_dispatch_kernel(const MoeDispat
         int* meta = (int*)(base + a.recv_meta_off) + ((size_t)el * a.C + slot) * 2;
         asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(meta), "r"(a.sym.rank), "r"(t) : "memory");
         asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"((float*)(base + a.recv_w_off) + (size_t)el * a.C + slot),
-                     "f"(s_w[k]) : "memory");
+                     "f"(wgt) : "memory");
       }
     }
   }
