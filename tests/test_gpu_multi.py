@@ -325,10 +325,11 @@ def test_wait_times_out_and_context_survives():
 
 # ---------------------------------------------------------------- the HTTP server on two tensor-parallel ranks
 
-def test_server_tp2_over_http(tmp_path):
-    """``python -m openagents_b200.serve.server --tp 2``: rank 0 serves HTTP and schedules, rank 1 follows over the gloo
-    control group.  Concurrent requests share decode batches, greedy answers repeat exactly, the first token of each
-    answer is the CPU oracle's, a streamed answer equals the plain one, and ``/admin/shutdown`` ends every rank with 0."""
+def _serve_two_ranks(p, flag):
+    """``python -m openagents_b200.serve.server --tp 2`` / ``--ep 2``: rank 0 serves HTTP and schedules, rank 1 follows
+    over the gloo control group.  Concurrent requests share decode batches, greedy answers repeat exactly, the first token
+    of each answer is the CPU oracle's, a streamed answer equals the plain one, the benchmark client runs against it, and
+    ``/admin/shutdown`` ends every rank with 0."""
     _need(2)
     import json
     import subprocess
@@ -340,12 +341,9 @@ def test_server_tp2_over_http(tmp_path):
     from openagents_b200.models.weights import PLAN_Q4_K, random_weights, save_gguf
     from openagents_b200.serve.backend import CpuBackend
     from openagents_b200.serve.server import ServedModel, ServerState
-    cfg = TINY_LLAMA.with_(d_model=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1024, vocab=4096, n_layers=3)
-    p = str(tmp_path / "tiny.gguf")
-    save_gguf(p, cfg, random_weights(cfg, 3), PLAN_Q4_K)
     port = _free_port()
     env = dict(os.environ, B200_SERVE_HEAP_MB="256")
-    proc = subprocess.Popen([sys.executable, "-m", "openagents_b200.serve.server", "-m", p, "--tp", "2", "--port", str(port),
+    proc = subprocess.Popen([sys.executable, "-m", "openagents_b200.serve.server", "-m", p, flag, "2", "--port", str(port),
                              "--allow-shutdown", "--max-num-seqs", "8", "--max-ctx", "512"],
                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
     lines, ready = [], threading.Event()
@@ -365,7 +363,8 @@ def test_server_tp2_over_http(tmp_path):
     try:
         assert ready.wait(240), "".join(lines[-30:])
         prompts = [f"prompt number {i} says hello" for i in range(4)]
-        body = lambda t, **kw: {"model": "tiny", "messages": [{"role": "user", "content": t}], "max_tokens": 8, "temperature": 0, **kw}
+        name = os.path.basename(p).removesuffix(".gguf")
+        body = lambda t, **kw: {"model": name, "messages": [{"role": "user", "content": t}], "max_tokens": 8, "temperature": 0, **kw}
         outs = [None] * 4
 
         def one(i):
@@ -379,7 +378,7 @@ def test_server_tp2_over_http(tmp_path):
         again = json.loads(post("/v1/chat/completions", body(prompts[2])))
         assert again["choices"][0]["message"]["content"] == outs[2]["choices"][0]["message"]["content"]
         # the CPU oracle on the same file: same prompt ids, same first token
-        oracle = ServerState([ServedModel("tiny", CpuBackend.from_gguf(p), "sha256:x", max_num_seqs=4)])
+        oracle = ServerState([ServedModel(name, CpuBackend.from_gguf(p), "sha256:x", max_num_seqs=4)])
         for i in (0, 3):
             r, usage = oracle.complete(oracle.default, [{"role": "user", "content": prompts[i]}], {"max_tokens": 1, "temperature": 0})
             assert usage["prompt_tokens"] == outs[i]["usage"]["prompt_tokens"]
@@ -396,7 +395,7 @@ def test_server_tp2_over_http(tmp_path):
             assert json.loads(r.read())["status"] == "ok"
         # the benchmark client against the two-rank server: three streamed scenarios, one repetition, memory sampled
         from openagents_b200.serve.bench_client import run_benchmark
-        rep = run_benchmark(base + "/v1", "local", "tiny", "tp2-test", repetitions=1, only=("exact_instruction", "multi_turn_memory", "structured_json"),
+        rep = run_benchmark(base + "/v1", "local", name, "two-rank-test", repetitions=1, only=("exact_instruction", "multi_turn_memory", "structured_json"),
                             max_tokens=12, server_pid=proc.pid)
         # (a random model over the byte tokenizer may emit no printable text, so time-to-first-token can be unmeasured;
         # the status, the exact usage and the memory sampler are what is checked)
@@ -412,3 +411,18 @@ def test_server_tp2_over_http(tmp_path):
                 proc.wait(30)
             except subprocess.TimeoutExpired:
                 proc.kill()
+
+
+def test_server_tp2_over_http(tmp_path):
+    from openagents_b200.models.config import TINY_LLAMA
+    from openagents_b200.models.weights import PLAN_Q4_K, random_weights, save_gguf
+    cfg = TINY_LLAMA.with_(d_model=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1024, vocab=4096, n_layers=3)
+    p = str(tmp_path / "tiny.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 3), PLAN_Q4_K)
+    _serve_two_ranks(p, "--tp")
+
+
+def test_server_ep2_over_http(tmp_path):
+    """The expert-parallel engine behind the same server: experts sharded over two ranks, attention replicated."""
+    from test_gpu_moe import _make
+    _serve_two_ranks(_make(tmp_path), "--ep")
