@@ -117,13 +117,17 @@ class GPT2Model:
         self.kernel_launches = 0
 
     # ---- helpers
-    def refresh_param_views(self):
-        """Call after every optimizer step: fp32 vector copies and transposed matrices."""
-        for n, v in self.vec.items():
-            v.copy_(self.p[n])
+    def refresh_param_views(self, chunk=None):
+        """Call after every optimizer step: fp32 vector copies and transposed matrices.  ``chunk``: only the views of one
+        parameter chunk (``"rest"``: every vector; an int: that layer's transposed matrices), so that a chunked parameter
+        all-gather can refresh each chunk's views right behind it."""
+        if chunk is None or chunk == "rest":
+            for n, v in self.vec.items():
+                v.copy_(self.p[n])
         for n, t in self.wT.items():
-            ops.transpose_bf16(self.p[n], t)
-            self.kernel_launches += 1
+            if chunk is None or (isinstance(chunk, int) and n.startswith(f"blk.{chunk}.")) or (chunk == "rest" and not n.startswith("blk.")):
+                ops.transpose_bf16(self.p[n], t)
+                self.kernel_launches += 1
 
     def _gemm(self, A, B, M, N, K, **kw):
         ops.gemm_bf16(A, B, M, N, K, status=self.status, **kw)
@@ -147,19 +151,25 @@ class GPT2Model:
             self._gemm(dy, self.wT[wname], M, K, N, out_bf16=dx_out)
 
     # ---- forward + backward of one micro-batch; returns the mean loss (device scalar)
-    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, loss_scale: float = 1.0, on_bucket=None):
+    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, loss_scale: float = 1.0, on_bucket=None, before_layer=None):
         """``on_bucket(i)`` is called right after the backward of layer ``i`` has been enqueued (its weight gradients are then
-        final for this micro-batch) and ``on_bucket(None)`` at the very end (embeddings, norms and biases)."""
+        final for this micro-batch) and ``on_bucket(None)`` at the very end (embeddings, norms and biases).
+        ``before_layer("rest")`` is called before anything reads a parameter and ``before_layer(i)`` before layer ``i``'s
+        forward (the trainer waits there for that chunk of the parameter all-gather)."""
         cfg, M, T, d = self.cfg, self.M, self.T, self.cfg.d_model
         H, hd = cfg.n_heads, cfg.head_dim
         ids = tokens.reshape(-1).to(torch.int32)
         tg = targets.reshape(-1).to(torch.int32)
         x = self.act[0]["x_in"]
+        if before_layer is not None:
+            before_layer("rest")
         tops.embed_fwd(ids, self.p["token_embd.weight"], self.p["position_embd.weight"], x, T)
         self.kernel_launches += 1
         for i, a in enumerate(self.act):
             pre = f"blk.{i}."
             x = a["x_in"]
+            if before_layer is not None:
+                before_layer(i)
             tops.layernorm_fwd(x, self.vec[pre + "attn_norm.weight"], self.vec[pre + "attn_norm.bias"], cfg.norm_eps,
                                a["ln1"], a["mean1"], a["rstd1"])
             self._linear_fwd(a["ln1"], pre + "attn_qkv.weight", pre + "attn_qkv.bias", a["qkv"])

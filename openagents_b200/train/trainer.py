@@ -48,6 +48,7 @@ class TrainConfig:
     seed: int = 0
     zero_stage: int = 2
     overlap_grad_reduce: bool = True  # reduce-scatter each layer's gradients while the backward of the layers below it runs
+    overlap_param_gather: bool = True  # AdamW + parameter all-gather in per-layer chunks; the next forward waits chunk by chunk
 
 
 class Trainer:
@@ -92,6 +93,7 @@ class Trainer:
             self._layer_ranges = []              # the "rest" bucket assumes the layers lie back to back
         self._comm_stream = None
         self._reduced = False
+        self._param_ready: dict = {}        # chunk -> event: its updated parameters (and their views) are on every rank
 
     # ---- initialisation: every rank draws the same seeded values and keeps its shard as master
     def _init_params(self):
@@ -126,9 +128,24 @@ class Trainer:
             if a == self.accum - 1 and self.cfg.overlap_grad_reduce and self._layer_ranges and self.device.type == "cuda":
                 self.norm2.zero_()
                 hook = self._bucket_ready
-            losses.append(self.model.forward_backward(tokens[a], targets[a], loss_scale=1.0 / self.accum, on_bucket=hook))
+            wait = self._wait_chunk if (a == 0 and self._param_ready) else None
+            losses.append(self.model.forward_backward(tokens[a], targets[a], loss_scale=1.0 / self.accum, on_bucket=hook, before_layer=wait))
+            if a == 0:
+                self._sync_params()                  # whatever the first forward did not wait for (nothing, normally)
         self.optimizer_step()
         return torch.stack(losses).mean()
+
+    # ---- chunked parameter all-gather, overlapped with the next forward
+    def _wait_chunk(self, key):
+        ev = self._param_ready.pop(key, None)
+        if ev is not None:
+            torch.cuda.current_stream(self.device).wait_event(ev)
+
+    def _sync_params(self):
+        """Make the current stream wait for every outstanding parameter chunk (checkpointing, evaluation, the end of the
+        first micro-batch)."""
+        for key in list(self._param_ready):
+            self._wait_chunk(key)
 
     # ---- bucketed gradient reduce-scatter, overlapped with backward
     def _reduce_range(self, lo: int, hi: int):
@@ -174,9 +191,37 @@ class Trainer:
             tops.zero_reduce_norm(T, self.grad_off, self.lo, self.shard, self.gshard, self.norm2)
         if self.world > 1:
             self.heap.all_reduce_f32(self.norm_off, 4, ch=3)
-        tops.zero_adamw_gather(T, self.param_off, self.lo, self.shard, self.gshard, self.master, self.m, self.v,
-                               self.norm2, self.lr_at(t - 1), c.betas[0], c.betas[1], c.eps, c.weight_decay,
-                               1.0 - c.betas[0] ** t, 1.0 - c.betas[1] ** t, c.grad_clip, self.decay_end)
+        args = (self.lr_at(t - 1), c.betas[0], c.betas[1], c.eps, c.weight_decay, 1.0 - c.betas[0] ** t, 1.0 - c.betas[1] ** t,
+                c.grad_clip, self.decay_end)
+        if c.overlap_param_gather and self._layer_ranges and self.device.type == "cuda":
+            # The update runs chunk by chunk on the side stream, in the order the next forward needs the parameters:
+            # embeddings, norms and biases first, then layer 0, 1, ...  Each chunk's kernel ends with the cross-rank barrier,
+            # so its event means "every rank's share of this chunk has arrived here"; the forward waits per chunk.
+            main = torch.cuda.current_stream(self.device)
+            if self._comm_stream is None:
+                self._comm_stream = torch.cuda.Stream(self.device)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            self._comm_stream.wait_event(ev)
+            first, last = self._layer_ranges[0][0], self._layer_ranges[-1][1]
+            chunks = [("rest", [(0, first), (last, self.n_total)])] + [(i, [r]) for i, r in enumerate(self._layer_ranges)]
+            with torch.cuda.stream(self._comm_stream):
+                for key, ranges in chunks:
+                    for lo, hi in ranges:
+                        a, b = max(lo, self.lo), min(hi, self.lo + self.shard)
+                        n = max(0, b - a)
+                        off = (a - self.lo) if n else 0
+                        tops.zero_adamw_gather(T, self.param_off, a if n else self.lo, n, self.gshard[off:], self.master[off:],
+                                               self.m[off:], self.v[off:], self.norm2, *args)
+                        self.model.kernel_launches += 1
+                    self.model.refresh_param_views(key)
+                    done = torch.cuda.Event()
+                    done.record(self._comm_stream)
+                    self._param_ready[key] = done
+            self.grads.zero_()
+            self.model.kernel_launches += 2 + (1 if self.world > 1 else 0)
+            return
+        tops.zero_adamw_gather(T, self.param_off, self.lo, self.shard, self.gshard, self.master, self.m, self.v, self.norm2, *args)
         self.grads.zero_()
         self.model.refresh_param_views()
         self.model.kernel_launches += 3 + (1 if self.world > 1 else 0)
@@ -185,6 +230,7 @@ class Trainer:
         return float(torch.sqrt(self.norm2[0]).item())
 
     def check_status(self):
+        self._sync_params()
         s = int(self.model.status.item())
         if s:
             raise RuntimeError(f"a GEMM wait timed out (status {s})")
@@ -194,6 +240,7 @@ class Trainer:
 
     # ---- full-precision state for checkpoints (gathered with NCCL: not a hot path)
     def gather_master(self) -> torch.Tensor:
+        self._sync_params()
         if self.world == 1:
             return self.master.clone()
         parts = [torch.empty_like(self.master) for _ in range(self.world)]
@@ -216,6 +263,7 @@ class Trainer:
         """Every rank writes its shard files; rank 0 (the commit authority) writes the manifest."""
         import dataclasses
         from . import checkpoint as ck
+        self._sync_params()
         torch.cuda.synchronize(self.device)
         mine = ck.save_shard(ckpt_dir, self.rank, self.master, self.m, self.v)
         files = dict(mine)
