@@ -13,7 +13,7 @@
 using namespace b200;
 
 enum { WT_Q4KR = 0, WT_Q6KR = 1, WT_Q8R = 2, WT_BF16 = 3 };
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU_Q8 = 2, EPI_SWIGLU_F32 = 3, EPI_ALLREDUCE = 4 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU_Q8 = 2, EPI_SWIGLU_F32 = 3, EPI_ALLREDUCE = 4, EPI_ROPE_KV = 5 };
 
 struct MatvecArgs {
   const uint8_t* w;     // main plane
@@ -39,6 +39,18 @@ struct MatvecArgs {
   size_t sym_off;
   int prefetch;         // bring this CTA's weight rows into L2 before waiting for the previous kernel
   int wait_ready;       // EPI_ALLREDUCE: check the peers' "finished reading" signals before the first add
+  // EPI_ROPE_KV: the matrix is the fused QKV projection of a model whose rotary pairs are ADJACENT rows (2j, 2j + 1).
+  // The epilogue rotates q and k by the token's position, writes q (scaled) to q_out [nb][Hq * hd] and k / v as fp16
+  // into the token's slot of the paged cache [page][Hkv][page_size][hd]: the separate rotary kernel's work.
+  const int* pos;       // [nb]
+  const int* slot;      // [nb] cache slot of the token (page * page_size + offset), < 0: do not write the cache
+  const float2* tab;    // [tab_len][hd / 2] (cos, sin)
+  int tab_len;
+  float* q_out;
+  __half* kc;
+  __half* vc;
+  int Hq, Hkv, hd, page_size;
+  float q_scale, theta;
 };
 
 __device__ __forceinline__ int dp4a(uint32_t a, uint32_t b, int c) {
@@ -176,6 +188,38 @@ __device__ __forceinline__ void matvec_epilogue(const MatvecArgs& a, const float
   const bool live = lane < R && n < a.N;
   float v = res[lane * B + b];
   if (a.bias && live && (a.epi != EPI_ALLREDUCE || a.sym.rank == 0)) v += a.bias[dual ? 2 * n : n];
+  if (a.epi == EPI_ROPE_KV) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, 1);      // the pair's partner row sits in the neighbouring lane
+    if (!live) return;
+    const int qd = a.Hq * a.hd, kd = a.Hkv * a.hd, half = a.hd >> 1;
+    const int s = a.slot[b];
+    const int page = s >= 0 ? s / a.page_size : 0, off = s >= 0 ? s % a.page_size : 0;
+    if (n >= qd + kd) {
+      if (s >= 0) {
+        const int e = n - qd - kd, kh = e / a.hd, c = e % a.hd;
+        a.vc[(((size_t)page * a.Hkv + kh) * a.page_size + off) * a.hd + c] = __float2half(v);
+      }
+      return;
+    }
+    const int h = n / a.hd, e = n % a.hd, j = e >> 1;
+    const int p = a.pos[b];
+    float cs, sn;
+    if (a.tab && p >= 0 && p < a.tab_len) {
+      const float2 t = a.tab[(size_t)p * half + j];
+      cs = t.x;
+      sn = t.y;
+    } else {                       // outside the table: double precision, as the table was built
+      const double inv = exp2(-2.0 * (double)j / (double)a.hd * log2((double)a.theta));
+      double snd, csd;
+      sincos((double)p * inv, &snd, &csd);
+      sn = (float)snd;
+      cs = (float)csd;
+    }
+    const float r = (e & 1) ? other * sn + v * cs : v * cs - other * sn;
+    if (h < a.Hq) a.q_out[(size_t)b * qd + n] = r * a.q_scale;
+    else if (s >= 0) a.kc[(((size_t)page * a.Hkv + (h - a.Hq)) * a.page_size + off) * a.hd + e] = __float2half(r);
+    return;
+  }
   if (a.epi == EPI_STORE) {
     if (live) a.y[(size_t)b * a.ldy + n] = v;
     if (dual && live) {
@@ -421,27 +465,9 @@ static int dispatch_wt(int wt, const MatvecArgs& a, cudaStream_t st) {
 // wt: weight layout; nb: tokens (1..8).  For the SwiGLU epilogues `w` holds 2N rows, interleaved
 // (gate_0, up_0, gate_1, ...: the order the GEMMs' SwiGLU epilogues pair rows in, so one copy of the matrix
 // serves every batch size) and N is the width of one of them; a bias is interleaved the same way.
-B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, int nb, const void* xq,
-                         const float* xd, const float* xs16, const float* xf, int epi, const float* bias,
-                         const float* resid, float* y, int ldy, void* oq, float* od, float* os16,
-                         const SymTable* sym, size_t sym_off, int wait_ready, cudaStream_t st) {
-  if (nb < 1 || nb > 8) return B200_ERR_BAD_ARG;
-  if (wt == WT_BF16 ? (K % 8 != 0) : (K % 256 != 0 && !(wt == WT_Q8R && K % 32 == 0))) return B200_ERR_BAD_ARG;
-  if (epi == EPI_SWIGLU_Q8 && N % 32) return B200_ERR_BAD_ARG;
-  MatvecArgs a;
-  a.w = (const uint8_t*)w; a.w2 = (const __half*)w2; a.N = N; a.K = K; a.nb = nb;
-  a.xq = (const int8_t*)xq; a.xd = xd; a.xs16 = xs16; a.xf = xf; a.epi = epi; a.bias = bias;
-  a.resid = resid; a.y = y; a.ldy = ldy; a.oq = (int8_t*)oq; a.od = od; a.os16 = os16;
-  if (epi == EPI_ALLREDUCE) {
-    if (!sym) return B200_ERR_BAD_ARG;
-    a.sym = *sym;
-    a.sym_off = sym_off;
-  } else {
-    a.sym = SymTable{};
-    a.sym_off = 0;
-  }
+static int run_matvec(int wt, MatvecArgs& a, cudaStream_t st) {
+  const int nb = a.nb, epi = a.epi;
   a.prefetch = b200_prefetch_enabled();
-  a.wait_ready = wait_ready;
   const bool dual = epi == EPI_SWIGLU_Q8 || epi == EPI_SWIGLU_F32;
   const int B = nb <= 1 ? 1 : nb <= 2 ? 2 : nb <= 4 ? 4 : 8;
   if (dual) {
@@ -458,4 +484,47 @@ B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, in
     case 4: return dispatch_wt<4, false>(wt, a, st);
     default: return dispatch_wt<8, false>(wt, a, st);
   }
+}
+
+B200_API int b200_matvec(int wt, const void* w, const void* w2, int N, int K, int nb, const void* xq,
+                         const float* xd, const float* xs16, const float* xf, int epi, const float* bias,
+                         const float* resid, float* y, int ldy, void* oq, float* od, float* os16,
+                         const SymTable* sym, size_t sym_off, int wait_ready, cudaStream_t st) {
+  if (nb < 1 || nb > 8 || epi == EPI_ROPE_KV) return B200_ERR_BAD_ARG;
+  if (wt == WT_BF16 ? (K % 8 != 0) : (K % 256 != 0 && !(wt == WT_Q8R && K % 32 == 0))) return B200_ERR_BAD_ARG;
+  if (epi == EPI_SWIGLU_Q8 && N % 32) return B200_ERR_BAD_ARG;
+  MatvecArgs a = {};
+  a.w = (const uint8_t*)w; a.w2 = (const __half*)w2; a.N = N; a.K = K; a.nb = nb;
+  a.xq = (const int8_t*)xq; a.xd = xd; a.xs16 = xs16; a.xf = xf; a.epi = epi; a.bias = bias;
+  a.resid = resid; a.y = y; a.ldy = ldy; a.oq = (int8_t*)oq; a.od = od; a.os16 = os16;
+  if (epi == EPI_ALLREDUCE) {
+    if (!sym) return B200_ERR_BAD_ARG;
+    a.sym = *sym;
+    a.sym_off = sym_off;
+  } else {
+    a.sym = SymTable{};
+    a.sym_off = 0;
+  }
+  a.wait_ready = wait_ready;
+  return run_matvec(wt, a, st);
+}
+
+// The fused QKV projection of 1-8 tokens with the rotary embedding and the paged-cache write in its epilogue
+// (adjacent-pair rotary layout only).  N = (Hq + 2 Hkv) * hd rows; q_out [nb][Hq * hd] fp32, scaled by q_scale;
+// kc / vc fp16 [n_pages][Hkv][page_size][hd]; slot[b] < 0 skips the cache write of token b.
+B200_API int b200_matvec_rope_kv(int wt, const void* w, const void* w2, int K, int nb, const void* xq, const float* xd,
+                                 const float* xs16, const float* xf, const float* bias, const int* pos, const int* slot,
+                                 const void* tab, int tab_len, float* q_out, void* kc, void* vc, int Hq, int Hkv, int hd,
+                                 int page_size, float theta, float q_scale, cudaStream_t st) {
+  if (nb < 1 || nb > 8 || Hq < 1 || Hkv < 1 || hd < 2 || (hd & 1) || page_size < 1 || !pos || !slot || !q_out || !kc || !vc)
+    return B200_ERR_BAD_ARG;
+  if (wt == WT_BF16 ? (K % 8 != 0) : (K % 256 != 0 && !(wt == WT_Q8R && K % 32 == 0))) return B200_ERR_BAD_ARG;
+  MatvecArgs a = {};
+  a.w = (const uint8_t*)w; a.w2 = (const __half*)w2; a.N = (Hq + 2 * Hkv) * hd; a.K = K; a.nb = nb;
+  a.xq = (const int8_t*)xq; a.xd = xd; a.xs16 = xs16; a.xf = xf; a.epi = EPI_ROPE_KV; a.bias = bias;
+  a.sym = SymTable{};
+  a.pos = pos; a.slot = slot; a.tab = (const float2*)tab; a.tab_len = tab ? tab_len : 0; a.q_out = q_out;
+  a.kc = (__half*)kc; a.vc = (__half*)vc; a.Hq = Hq; a.Hkv = Hkv; a.hd = hd; a.page_size = page_size;
+  a.q_scale = q_scale; a.theta = theta;
+  return run_matvec(wt, a, st);
 }

@@ -200,6 +200,7 @@ class LlamaEngine:
         self.h2d_bytes = 0                              # host-to-device bytes copied by decode() so far
         self.prefill_tc05 = os.environ.get("B200_PREFILL_TC05", "1") == "1"     # tcgen05 prefill attention (head size 128)
         self.seq_shard = os.environ.get("B200_TP_SEQ_SHARD", "1") == "1"        # sequence-sharded tensor-parallel prefill
+        self.fuse_rope = os.environ.get("B200_FUSE_ROPE", "1") == "1"          # small-batch path: rotary + cache write in the QKV mat-vec
         self.attn_target_ctas = int(os.environ.get("B200_ATTN_CTAS", 0))   # split-K attention: CTAs to aim for (0: built-in rule)
 
     # ------------------------------------------------------------------ weights
@@ -457,10 +458,16 @@ class LlamaEngine:
             ops.rmsnorm(x, L.attn_norm, cfg.norm_eps, xq=self.xq if q8 else None, xd=self.xd, xs16=self.xs,
                         hf=None if q8 else self.xf, signal_sym=None if slots else self._sig,
                         slots=self._slot_arg if slots and li > 0 else None)
-            ops.matvec(L.wqkv.wt, L.wqkv.main, L.wqkv.plane2, L.wqkv.N, L.wqkv.K, nb, xq=self.xq, xd=self.xd,
-                       xs16=self.xs, xf=self.xf, epi=ops.EPI_STORE, bias=L.bqkv, y=self.qkv, ldy=self.qkv_dim)
-            ops.rope_kv(self.qkv[:nb], self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv,
-                        self.hd, PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd), table=self.rope_tab)
+            if style == 0 and self.fuse_rope:      # rotary pairs are adjacent rows: rotate and write the cache in the epilogue
+                ops.matvec_rope_kv(L.wqkv, nb, self.pos, self.slot, self.q32, self.kc[li], self.vc[li], self.Hq, self.Hkv, self.hd,
+                                   PAGE, cfg.rope_theta, 1.0 / math.sqrt(self.hd), xq=self.xq, xd=self.xd, xs16=self.xs, xf=self.xf,
+                                   bias=L.bqkv, table=self.rope_tab)
+                n -= 1
+            else:
+                ops.matvec(L.wqkv.wt, L.wqkv.main, L.wqkv.plane2, L.wqkv.N, L.wqkv.K, nb, xq=self.xq, xd=self.xd,
+                           xs16=self.xs, xf=self.xf, epi=ops.EPI_STORE, bias=L.bqkv, y=self.qkv, ldy=self.qkv_dim)
+                ops.rope_kv(self.qkv[:nb], self.pos, self.slot, self.q32, None, self.kc[li], self.vc[li], self.Hq, self.Hkv,
+                            self.hd, PAGE, cfg.rope_theta, style, 1.0 / math.sqrt(self.hd), table=self.rope_tab)
             oq8 = L.wo.quantized
             ops.attn_decode(self.q32, self.kc[li], self.vc[li], self.page_table, self.seq_lens, nb, self.Hq, self.Hkv,
                             self.hd, window=L.window, S=S, sinks=L.sinks, out_f32=None if oq8 else self.xf,

@@ -31,6 +31,8 @@ _SIGS = {
     "b200_add_inplace": [_P, _P, c_size_t, _P],
     "b200_argmax": [_P, c_int, c_int, _P, _P, c_int, _P, _P],
     "b200_sample_topk": [_P, c_int, c_int, c_float, c_int, c_float, _P, _P, _P, _P],
+    "b200_matvec_rope_kv": [c_int, _P, _P, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int,
+                            c_int, c_float, c_float, _P],
     "b200_matvec": [c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, _P, _P,
                     c_size_t, c_int, _P],
     "b200_argmax_merge": [_P, _P, c_int, _P, c_size_t, c_int, _P],
@@ -176,6 +178,16 @@ def matvec(wt, w, w2, N, K, nb, xq=None, xd=None, xs16=None, xf=None, epi=EPI_ST
     (gate_0, up_0, gate_1, ...)."""
     _check(lib().b200_matvec(wt, _p(w), _p(w2), N, K, nb, _p(xq), _p(xd), _p(xs16), _p(xf), epi, _p(bias), _p(resid),
                              _p(y), ldy, _p(oq), _p(od), _p(os16), _sym(sym), sym_off, int(wait_ready), _st()), "matvec")
+
+
+def matvec_rope_kv(w, nb, pos, slot, q_out, kc, vc, Hq, Hkv, hd, page_size, theta, q_scale, xq=None, xd=None, xs16=None, xf=None,
+                   bias=None, table=None):
+    """The fused QKV projection of ``nb`` <= 8 tokens with the rotary embedding (adjacent-pair layout) and the paged-cache
+    write in its epilogue: replaces ``matvec(..., EPI_STORE)`` + ``rope_kv`` on the small-batch decode path.  ``w``: a
+    ``QWeight`` with (Hq + 2 Hkv) * hd rows."""
+    _check(lib().b200_matvec_rope_kv(w.wt, _p(w.main), _p(w.plane2), w.K, nb, _p(xq), _p(xd), _p(xs16), _p(xf), _p(bias), _p(pos),
+                                     _p(slot), _p(table), 0 if table is None else table.shape[0], _p(q_out), _p(kc), _p(vc), Hq, Hkv,
+                                     hd, page_size, theta, q_scale, _st()), "matvec_rope_kv")
 
 
 def argmax_merge(out_id, out_val, nb, sym, merge_off, rows):

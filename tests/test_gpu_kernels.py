@@ -677,3 +677,40 @@ def test_stream_triad_probe():
     """The bandwidth probe's triad kernel computes a = b + 3 c (checked inside) and reports a plausible rate."""
     from openagents_b200.utils.bandwidth_probe import stream_triad_gbs
     assert stream_triad_gbs(DEV, n=1 << 24) > 200.0
+
+
+@pytest.mark.parametrize("t,nb,hd", [(GgmlType.Q4_K, 1, 128), (GgmlType.Q4_K, 3, 64), (GgmlType.Q6_K, 4, 128), (GgmlType.Q8_0, 2, 64),
+                                     (GgmlType.BF16, 1, 64)])
+def test_matvec_with_rotary_and_cache_write(t, nb, hd):
+    """The fused QKV projection with the rotary embedding and the paged-cache write in its epilogue equals the plain
+    mat-vec followed by the rotary kernel (same sums, same table; the two compilations may contract the rotation into
+    fused multiply-adds differently, hence a last-bit tolerance), including a position beyond the table, a
+    token that writes no cache, a bias, and a matrix small enough for the 8-row CTAs."""
+    ops = _ops()
+    Hq, Hkv, K = 4, 2, 512
+    N = (Hq + 2 * Hkv) * hd
+    W = _randn(N, K, seed=90, scale=0.05)
+    w = _qweight(W, t)
+    bias = _randn(N, seed=91) * 0.1
+    x = _randn(nb, K, seed=92)
+    xq, xd, xs = _alloc_q(nb, K)
+    ops.quantize_x(x, xq, xd, xs)
+    pos = torch.tensor([5, 1023, 9000, 0][:nb], dtype=torch.int32, device=DEV)      # 9000 is beyond the table
+    slot = torch.tensor([3, 17, -1, 40][:nb], dtype=torch.int32, device=DEV)         # -1 writes no cache
+    tab = ops.rope_table(8192, hd, 500000.0, DEV)
+    scale = 1.0 / math.sqrt(hd)
+    # reference: two kernels
+    y = torch.empty((nb, N), device=DEV)
+    ops.matvec(w.wt, w.main, w.plane2, N, K, nb, xq=xq, xd=xd, xs16=xs, xf=x, epi=ops.EPI_STORE, bias=bias, y=y, ldy=N)
+    kc0 = torch.zeros((4, Hkv, 16, hd), dtype=torch.float16, device=DEV)
+    vc0 = torch.zeros_like(kc0)
+    q0 = torch.zeros((nb, Hq * hd), device=DEV)
+    ops.rope_kv(y, pos, slot, q0, None, kc0, vc0, Hq, Hkv, hd, 16, 500000.0, 0, scale, table=tab)
+    # fused
+    kc1, vc1, q1 = torch.zeros_like(kc0), torch.zeros_like(kc0), torch.zeros_like(q0)
+    ops.matvec_rope_kv(w, nb, pos, slot, q1, kc1, vc1, Hq, Hkv, hd, 16, 500000.0, scale, xq=xq, xd=xd, xs16=xs, xf=x, bias=bias, table=tab)
+    torch.cuda.synchronize()
+    assert torch.allclose(q1, q0, atol=1e-6, rtol=1e-5) and torch.equal(vc1, vc0)
+    assert torch.allclose(kc1.float(), kc0.float(), atol=2e-3, rtol=2e-3)
+    assert float(q0.abs().max()) > 0 and float(kc0.abs().max()) > 0
+    assert torch.equal(kc1 == 0, kc0 == 0)                    # exactly the same cache slots were written
