@@ -52,8 +52,11 @@ class TrainConfig:
 
 
 class Trainer:
-    def __init__(self, cfg: TrainConfig, device, rank: int = 0, world: int = 1, multicast: bool | None = None):
-        self.cfg, self.rank, self.world = cfg, rank, world
+    def __init__(self, cfg: TrainConfig, device, rank: int = 0, world: int = 1, multicast: bool | None = None, group=None):
+        """``group``: the process group of this trainer's data-parallel ranks (default: all ranks).  A job that runs several
+        independent replicas (local-update training) gives each replica its own group; ``rank`` / ``world`` are the position
+        and size within it."""
+        self.cfg, self.rank, self.world, self.group = cfg, rank, world, group
         self.device = torch.device(device)
         m = cfg.model
         if cfg.global_batch % (world * cfg.micro_batch):
@@ -65,7 +68,9 @@ class Trainer:
         self.shard = self.n_total // world
         self.lo = rank * self.shard
         heap_bytes = self.n_total * (2 + 4) + (1 << 20)
-        self.heap = SymmHeap(heap_bytes, self.device, multicast=multicast)
+        self.heap = SymmHeap(heap_bytes, self.device, group=group, multicast=multicast)
+        if (self.heap.rank, self.heap.world) != (rank, world):
+            raise ValueError(f"rank {rank}/{world} does not match the group's {self.heap.rank}/{self.heap.world}")
         self.params, self.param_off = self.heap.alloc_tensor((self.n_total,), torch.bfloat16)
         self.grads, self.grad_off = self.heap.alloc_tensor((self.n_total,), torch.float32)
         self.norm2, self.norm_off = self.heap.alloc_tensor((4,), torch.float32)
@@ -226,6 +231,20 @@ class Trainer:
         self.model.refresh_param_views()
         self.model.kernel_launches += 3 + (1 if self.world > 1 else 0)
 
+    def set_master(self, shard: torch.Tensor):
+        """Install new fp32 parameters for this rank's shard (an outer optimizer step, a reloaded aggregate) and rebuild
+        the bf16 working copy on every rank.  Not a hot path: the gather uses the process group."""
+        self._sync_params()
+        self.master.copy_(shard.to(self.master.dtype))
+        mine = self.master.to(torch.bfloat16)
+        if self.world == 1:
+            self.params[: self.shard].copy_(mine)
+        else:
+            parts = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(parts, mine, group=self.group)
+            self.params.copy_(torch.cat(parts))
+        self.model.refresh_param_views()
+
     def grad_norm(self) -> float:
         return float(torch.sqrt(self.norm2[0]).item())
 
@@ -244,7 +263,7 @@ class Trainer:
         if self.world == 1:
             return self.master.clone()
         parts = [torch.empty_like(self.master) for _ in range(self.world)]
-        dist.all_gather(parts, self.master)
+        dist.all_gather(parts, self.master, group=self.group)
         return torch.cat(parts)
 
     def named_master(self) -> dict[str, torch.Tensor]:
@@ -269,7 +288,7 @@ class Trainer:
         files = dict(mine)
         if self.world > 1:
             gathered = [None] * self.world
-            dist.all_gather_object(gathered, mine)
+            dist.all_gather_object(gathered, mine, group=self.group)
             files = {}
             for g in gathered:
                 files.update(g)
@@ -280,7 +299,7 @@ class Trainer:
                                     world_size=self.world, zero_stage=self.cfg.zero_stage, n_total=self.n_total,
                                     shard=self.shard, term=term, train_config=tc_, model_config=self.cfg.model.as_dict())
         if self.world > 1:
-            dist.barrier()
+            dist.barrier(group=self.group)
         return man
 
     def load_checkpoint(self, ckpt_dir: str) -> dict:
@@ -300,7 +319,7 @@ class Trainer:
         self.model.refresh_param_views()
         torch.cuda.synchronize(self.device)
         if self.world > 1:
-            dist.barrier()
+            dist.barrier(group=self.group)
         return man
 
     def export_gguf(self, path: str, plan=None):

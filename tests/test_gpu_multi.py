@@ -32,7 +32,9 @@ def _entry(rank, world, port, fn, args):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    from datetime import timedelta
+    # a short collective timeout: a rank that fails an assertion must not leave the others waiting for ten minutes
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank), timeout=timedelta(seconds=120))
     try:
         fn(rank, world, *args)
         torch.cuda.synchronize()
@@ -426,3 +428,44 @@ def test_server_ep2_over_http(tmp_path):
     """The expert-parallel engine behind the same server: experts sharded over two ranks, attention replicated."""
     from test_gpu_moe import _make
     _serve_two_ranks(_make(tmp_path), "--ep")
+
+
+# ---------------------------------------------------------------- local-update (DiLoCo) rounds over two replicas
+
+def _diloco_worker(rank, world, out):
+    import torch.distributed as dist
+    from openagents_b200.models.config import GPT2_SMALL
+    from openagents_b200.train.diloco import DilocoConfig, DilocoReplica
+    from openagents_b200.train.trainer import TrainConfig, Trainer, synthetic_batch
+    dev = torch.device("cuda", rank)
+    groups = [dist.new_group([r]) for r in range(world)]          # every rank creates every group
+    m = GPT2_SMALL.with_(n_layers=2, d_model=128, n_heads=2, n_kv_heads=2, head_dim=64, ffn=512, vocab=1000, context=64)
+    cfg = TrainConfig(model=m, global_batch=4, micro_batch=4, seq_len=64, lr=1e-3)
+    tr = Trainer(cfg, dev, rank=0, world=1, group=groups[rank])   # a whole model per replica, no gradient traffic between them
+    rep = DilocoReplica(tr, DilocoConfig(inner_steps=3, outer_lr=0.7, outer_momentum=0.9, min_participants=2), f"replica.{rank}")
+    tok, tgt = synthetic_batch(cfg, 1, 7, rank, dev)               # one fixed batch per replica, different between replicas
+    batches = [(tok.to(dev), tgt.to(dev))] * 3
+    losses, same = [], True
+    for rnd in range(3):
+        rec = rep.run_round(batches)
+        mine = tr.master.clone()
+        other = mine.clone()
+        dist.broadcast(other, 0)
+        same = same and rec["sealed"] and rec["participants"] == 2 and rec["localSteps"] == 3 and torch.equal(mine, other) \
+            and torch.equal(tr.params[: tr.shard], tr.master.bfloat16())
+        losses.append(rec["meanLocalLoss"])
+    tr.check_status()
+    # every rank takes the same decision (a rank that raised alone would leave the other in a collective)
+    verdict = torch.tensor([1.0 if same else 0.0, losses[0], losses[-1]], device=dev)
+    dist.all_reduce(verdict)
+    assert float(verdict[0]) == world, "replicas diverged or a round was not sealed"
+    assert float(verdict[2]) < float(verdict[1]), (float(verdict[1]), float(verdict[2]))
+    if rank == 0:
+        torch.save({"losses": losses, "history": rep.history}, out + "/diloco.pt")
+
+
+def test_diloco_two_replicas(tmp_path):
+    _need(2)
+    _run(_diloco_worker, 2, str(tmp_path))
+    r = torch.load(tmp_path / "diloco.pt")
+    assert len(r["history"]) == 3 and r["history"][-1]["baseCheckpoint"] == "checkpoint.round.2"
