@@ -4,7 +4,7 @@
 
 Each case sets up one kernel on a problem that is larger than L2 but holds well under a gigabyte on
 the device, launches it a few times and exits, so a capture with ``ncu -k regex:<kernel> -c 1`` ends
-by itself in seconds.  Cases: qgemm64, qgemm_lm, gemm, matvec, attn_decode, attn_prefill, attn_prefill_tc05, and
+by itself in seconds.  Cases: qgemm64, qgemm_lm, gemm, gemm_k768, matvec, attn_decode, attn_prefill, attn_prefill_tc05, and
 ``step64`` / ``step1``: whole decode steps (batch 64 / 1, context 2048) of a 4-layer Llama-3-8B-shape
 engine without graphs, for a per-kernel launch list; ``moe_step``: the same for a 2-layer gpt-oss-20b-shape
 expert engine at batch 256; ``moe_ffn``: one expert layer at 4096 tokens; ``gemm_ar64`` / ``gemm_ar2048``: the
@@ -39,8 +39,8 @@ def main():
             fn = lambda: ops.qgemm(w, x, 64, out_bf16=y, ldo=N // 2, epi=ops.QEPI_SWIGLU, status=status)
         else:
             fn = lambda: ops.qgemm(w, x, 64, out_f32=y, epi=ops.QEPI_STORE, status=status)
-    elif case == "gemm":
-        M, N, K = 2048, 28672, 4096
+    elif case in ("gemm", "gemm_k768"):
+        M, N, K = (2048, 28672, 4096) if case == "gemm" else (16384, 3072, 768)      # prefill gate/up; GPT-2 feed-forward expansion
         A, B = torch.randn(M, K, device=DEV).bfloat16(), torch.randn(N, K, device=DEV).bfloat16()
         out = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
         fn = lambda: ops.gemm_bf16(A, B, M, N, K, out_bf16=out, tile_n=256, status=status)
