@@ -250,6 +250,8 @@ class Request:
     prompt: list[int]
     params: SamplingParams
     seq_id: int = -1
+    spec_proposed: int = 0            # speculated tokens offered to the verifier / accepted by it, for this request
+    spec_accepted: int = 0
     state: str = "waiting"            # waiting | prefill | running | finished
     prefilled: int = 0
     cached_prompt_tokens: int = 0
@@ -494,6 +496,8 @@ class Scheduler:
         self.stats["spec_steps"] += 1
         self.stats["spec_drafted"] += k
         self.stats["spec_accepted"] += n_acc
+        r.spec_proposed += k
+        r.spec_accepted += n_acc
         self.stats["steps"] += 1
         self.stats["batch_size_sum"] += 1
         i_last = n_acc

@@ -192,6 +192,10 @@ class ServerState:
                 session.pending = r.output[-1:] if r.output else []
         usage = {"prompt_tokens": len(ids), "completion_tokens": len(r.output), "total_tokens": len(ids) + len(r.output),
                  "prompt_tokens_details": {"cached_tokens": r.cached_prompt_tokens}}
+        if model.sched.speculation is not None:      # disclosed per request, in the gateway's speculation-metadata shape
+            from ..gateway.metadata import speculation_metadata
+            usage["speculation"] = speculation_metadata(model.sched.speculation.mode, active=r.spec_proposed > 0,
+                                                        proposed=r.spec_proposed, accepted=r.spec_accepted)
         self.ledger.record(r.request_id + "." + uuid.uuid4().hex[:8], model.id, len(ids), len(r.output),
                            account_ref=str(body.get("user") or "account.anonymous"), adapter_id=ENGINE_NAME,
                            demand_kind=str(body.get("demand_kind") or "unlabeled"))

@@ -406,3 +406,18 @@ def test_ngram_speculation_gives_exactly_the_greedy_output(gguf_path):
     rs = [sch.submit(prompt, SamplingParams(max_tokens=6)) for _ in range(2)] + [sch.submit(prompt, SamplingParams(max_tokens=6, temperature=0.8, seed=1))]
     sch.run_until_done(rs)
     assert sch.stats["spec_steps"] == 0
+
+
+def test_speculation_is_disclosed_per_request(gguf_path):
+    from openagents_b200.serve.generation import SpeculationConfig
+    model = ServedModel("tiny", CpuBackend.from_gguf(gguf_path), None, max_num_seqs=2, speculation=SpeculationConfig())
+    state = ServerState([model])
+    msgs = [{"role": "user", "content": "abcabcabcabc the cat sat on the mat the cat sat on"}]
+    r, usage = state.complete(model, msgs, {"max_tokens": 24})
+    sp = usage["speculation"]
+    assert sp["mode"] == "n_gram" and sp["draftTokensProposed"] == r.spec_proposed and sp["draftTokensAccepted"] == r.spec_accepted
+    assert state.status()["models"][0]["levers"]["speculation"] == "n_gram"
+    plain = ServedModel("tiny2", CpuBackend.from_gguf(gguf_path), None, max_num_seqs=2)
+    assert "speculation" not in ServerState([plain]).complete(plain, msgs, {"max_tokens": 4})[1]
+    model.close()
+    plain.close()
