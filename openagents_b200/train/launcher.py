@@ -7,6 +7,9 @@ rendezvous on 127.0.0.1); each worker then builds the trainer, walks the run/win
 (plan -> active -> seal -> reconcile) around its steps and, at the end of a window, writes a
 checkpoint whose seal descriptor goes through the durable-seal predicate.
 
+``--sync-profile diloco`` makes every rank a replica of its own (local-update rounds: ``--inner-steps`` optimizer steps
+per round, then one outer step over all replicas; one window per round).
+
 Flags follow the trainer contract (``--zero-stage --global-batch --seq-len --lr --betas --wd --clip
 --ckpt-dir --resume``); the run/window semantics are the reference's
 (apps/openagents.com/workers/api/src/training-run-window-authority.ts:43-56, 219-231).
@@ -42,6 +45,13 @@ def parse(argv=None):
     ap.add_argument("--max-allowed-stale", type=int, default=5)
     ap.add_argument("--master-port", type=int, default=29517)
     ap.add_argument("--log-jsonl", default="")
+    ap.add_argument("--sync-profile", default="sync", choices=["sync", "diloco"],
+                    help="sync: every step is data-parallel over all ranks; diloco: every rank is a replica that takes "
+                         "--inner-steps local steps per round, then one outer step over all replicas")
+    ap.add_argument("--inner-steps", type=int, default=16)
+    ap.add_argument("--outer-lr", type=float, default=0.7)
+    ap.add_argument("--outer-momentum", type=float, default=0.9)
+    ap.add_argument("--min-participants", type=int, default=1)
     return ap.parse_args(argv)
 
 
@@ -65,6 +75,8 @@ def worker(args):
     cfg = TrainConfig(model=model, global_batch=args.global_batch, micro_batch=args.micro_batch, seq_len=args.seq_len,
                       lr=args.lr, betas=tuple(args.betas), weight_decay=args.wd, grad_clip=args.clip, seed=args.seed,
                       zero_stage=args.zero_stage)
+    if args.sync_profile == "diloco":
+        return diloco_worker(args, cfg, dev, rank, world)
     tr = Trainer(cfg, dev, rank, world)
     if args.resume:
         man = tr.load_checkpoint(args.resume)
@@ -122,13 +134,62 @@ def worker(args):
         dist.destroy_process_group()
 
 
+def diloco_worker(args, cfg, dev, rank, world):
+    """Local-update rounds: one replica per rank (its own trainer and optimizer state, a ``world``-th of the global batch),
+    one window per round; rank 0 prints the round records and the window's coordination tags."""
+    import dataclasses
+    import torch
+    import torch.distributed as dist
+    from ..control import run_window as rw
+    from .diloco import DilocoConfig, DilocoReplica
+    from .trainer import Trainer, synthetic_batch
+    if cfg.global_batch % world:
+        raise SystemExit("--global-batch must be a multiple of the number of replicas")
+    rcfg = dataclasses.replace(cfg, global_batch=cfg.global_batch // world)
+    groups = [dist.new_group([r]) for r in range(world)] if world > 1 else [None]
+    tr = Trainer(rcfg, dev, rank=0, world=1, group=groups[rank])
+    dcfg = DilocoConfig(inner_steps=args.inner_steps, outer_lr=args.outer_lr, outer_momentum=args.outer_momentum,
+                        min_participants=min(args.min_participants, world))
+    rep = DilocoReplica(tr, dcfg, f"replica.rank{rank}")
+    auth = rw.Authority()
+    run = auth.plan_run("promise.local.train.diloco", max_allowed_stale=args.max_allowed_stale)
+    auth.advance_run(run.run_ref, "active")
+    done = 0
+    while done < args.steps:
+        n = min(args.inner_steps, args.steps - done)
+        w = auth.plan_window(run.run_ref, done, done + n)
+        auth.activate_window(w.window_ref)
+        auth.claim_lease(w.window_ref, f"worker.rank{rank}")
+        batches = []
+        for i in range(n):
+            tok, tgt = synthetic_batch(rcfg, tr.accum, done + i, rank, dev)
+            batches.append((tok.pin_memory().to(dev, non_blocking=True), tgt.pin_memory().to(dev, non_blocking=True)))
+        t0 = time.perf_counter()
+        tags = dcfg.window_tags(rep.round_index, rep.base_checkpoint)
+        rec = rep.run_round(batches)
+        torch.cuda.synchronize(dev)
+        dt = time.perf_counter() - t0
+        tr.check_status()
+        done += n
+        if rank == 0:
+            print(json.dumps({"event": "round", **rec, "round_s": round(dt, 4), "windowRef": w.window_ref, "replicas": world,
+                              "tokens_per_s": round(rec["tokensAllReplicas"] / dt, 1), "windowTags": tags}), flush=True)
+        auth.seal_window(w.window_ref, rw.SealMetadata(verification_overhead={"verificationSeconds": 0.0, "trainingSeconds": dt}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main(argv=None):
+    if "RANK" in os.environ and os.environ.get("B200_TRAIN_ARGV"):      # a worker started by the re-execution below
+        return worker(parse(json.loads(os.environ["B200_TRAIN_ARGV"])))
     args = parse(argv)
     if args.nproc > 1 and "RANK" not in os.environ:
+        # The worker's flags travel in the environment: torch.distributed.run parses abbreviations of its own options
+        # (``--nproc`` matches ``--nproc-per-node``) even behind the module name.
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.nproc}",
                "--master-addr", "127.0.0.1", "--master-port", str(args.master_port), "-m", "openagents_b200.train.launcher"]
-        cmd += sys.argv[1:] if argv is None else list(argv)
-        raise SystemExit(subprocess.call(cmd))
+        env = dict(os.environ, B200_TRAIN_ARGV=json.dumps(sys.argv[1:] if argv is None else list(argv)))
+        raise SystemExit(subprocess.call(cmd, env=env))
     worker(args)
 
 

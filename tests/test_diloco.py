@@ -93,3 +93,26 @@ def test_two_replicas_stay_identical_and_converge(tmp_path):
     assert a["last"]["sealed"] is False and b["last"]["sealed"] is False and a["last"]["participants"] == 1
     assert torch.equal(a["master"], b["master"]) and bool(torch.isfinite(a["master"]).all())
     assert a["rounds"] == 7 and a["base"] == "checkpoint.round.6"                     # the base did not advance in the unsealed round
+
+
+def test_launcher_flags_travel_in_the_environment(monkeypatch):
+    """``--nproc N`` re-executes under torch.distributed.run, whose parser would read ``--nproc`` as an abbreviation of its
+    own option if the worker's flags followed the module name; they go through the environment instead."""
+    import json
+    from openagents_b200.train import launcher as L
+    seen = {}
+    monkeypatch.setattr(L.subprocess, "call", lambda cmd, env=None: seen.update(cmd=cmd, env=env) or 0)
+    monkeypatch.delenv("RANK", raising=False)
+    with pytest.raises(SystemExit) as e:
+        L.main(["--nproc", "2", "--sync-profile", "diloco", "--inner-steps", "4", "--steps", "8"])
+    assert e.value.code == 0
+    assert seen["cmd"][-2:] == ["-m", "openagents_b200.train.launcher"] and "--nproc-per-node=2" in seen["cmd"]
+    assert "127.0.0.1" in seen["cmd"] and "--nproc" not in seen["cmd"]
+    argv = json.loads(seen["env"]["B200_TRAIN_ARGV"])
+    assert argv == ["--nproc", "2", "--sync-profile", "diloco", "--inner-steps", "4", "--steps", "8"]
+    got = {}
+    monkeypatch.setattr(L, "worker", lambda args: got.update(profile=args.sync_profile, inner=args.inner_steps, steps=args.steps))
+    monkeypatch.setenv("RANK", "1")
+    monkeypatch.setenv("B200_TRAIN_ARGV", seen["env"]["B200_TRAIN_ARGV"])
+    L.main([])
+    assert got == {"profile": "diloco", "inner": 4, "steps": 8}
