@@ -369,6 +369,7 @@ def main():
             r = bench_train.run(3, 3)
             extras["train"] = None if r is None else {"train_tok_s": r["value"], "train_ms_per_step": r["ms_per_step"],
                                                       "train_model_tflops_per_gpu": r["extra"]["model_tflops_per_gpu"],
+                                                      "train_vs_torch_arm": r["vs_baseline"], "train_torch_arm": r["extra"]["baseline"],
                                                       "train_config": r["config"]}
         except Exception as e:      # noqa: BLE001
             extras["train"] = {"train_error": f"{type(e).__name__}: {e}"[:200]}

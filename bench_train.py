@@ -16,9 +16,11 @@ import json
 import os
 
 
-def run(steps: int, warmup: int, global_batch: int = 512, micro_batch: int = 16, seq_len: int = 1024) -> dict | None:
+def run(steps: int, warmup: int, global_batch: int = 512, micro_batch: int = 16, seq_len: int = 1024, baseline: bool = True) -> dict | None:
     """Time ``steps`` optimizer steps after ``warmup``; the process group (when WORLD_SIZE > 1) must already exist.
-    Returns the result record on rank 0, None elsewhere."""
+    ``baseline``: afterwards time the same model, batch and optimizer on plain PyTorch (``baseline/gpt2_torch.py``: autocast,
+    SDPA, fused AdamW, DDP) on the same GPUs and report the ratio as ``vs_baseline``.  Returns the result record on rank 0,
+    None elsewhere."""
     import torch
     import torch.distributed as dist
     from bench import ClockSampler
@@ -62,6 +64,28 @@ def run(steps: int, warmup: int, global_batch: int = 512, micro_batch: int = 16,
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     tr.check_status()
+    launches = tr.model.kernel_launches - n0
+    accum = tr.accum
+    base = None
+    if baseline:
+        del tr
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            from baseline.gpt2_torch import run_train_baseline
+            b = run_train_baseline(cfg.model, dev, rank, world, batches, accum, max(1, min(steps, 2)), 2, lr=cfg.lr, betas=cfg.betas,
+                                   wd=cfg.weight_decay, clip=cfg.grad_clip, barrier=barrier)
+            bms = b["ms_per_step"]
+            if world > 1:
+                t = torch.tensor([bms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                bms = float(t.item())
+            base = {"tok_s": round(cfg.global_batch * cfg.seq_len / (bms * 1e-3), 1), "ms_per_step": round(bms, 2),
+                    "last_loss": round(b["losses"][-1], 4),
+                    "stack": "torch.nn + bf16 autocast + SDPA + fused AdamW" + (" + DDP (NCCL)" if world > 1 else "")}
+        except Exception as e:      # noqa: BLE001 - the product number stands even if the comparison arm fails
+            base = {"error": f"{type(e).__name__}: {e}"[:200]}
     if rank != 0:
         return None
     toks = cfg.global_batch * cfg.seq_len
@@ -71,14 +95,16 @@ def run(steps: int, warmup: int, global_batch: int = 512, micro_batch: int = 16,
     return {
         "metric": "gpt2_small_train_tok_s", "value": round(toks / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
         "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 2), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": (round(toks / (ms * 1e-3) / base["tok_s"], 4) if base and "tok_s" in base else None),
+        "dtype": "bf16", "data": "synthetic",
         "config": {"model": m.name, "global_batch": cfg.global_batch, "seq_len": cfg.seq_len, "micro_batch": cfg.micro_batch,
                    "parallelism": f"dp{world}+zero{cfg.zero_stage}", "optimizer": "AdamW lr 6e-4 betas (0.9,0.95) wd 0.1 clip 1.0",
                    "timed_region": "includes per-step H2D of token ids from pinned memory and D2H of the loss"},
-        "clocks": clocks, "gpu_launches": tr.model.kernel_launches - n0,
+        "clocks": clocks, "gpu_launches": launches,
         "extra": {"model_tflops_per_gpu": round(flops / (ms * 1e-3) / 1e12 / world, 1), "first_loss": round(losses[0], 4),
                   "last_loss": round(losses[-1], 4),
-                  "h2d_bytes_per_step": 2 * 8 * tr.accum * cfg.micro_batch * cfg.seq_len, "d2h_bytes_per_step": 4 * tr.accum}}
+                  "h2d_bytes_per_step": 2 * 8 * accum * cfg.micro_batch * cfg.seq_len, "d2h_bytes_per_step": 4 * accum,
+                  "baseline": base}}
 
 
 def main():
@@ -89,6 +115,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=16)
     ap.add_argument("--seq-len", type=int, default=1024)
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--no-baseline", action="store_true", help="skip the plain-PyTorch comparison arm that runs after the timed steps")
     args = ap.parse_args()
     import torch
     import torch.distributed as dist
@@ -96,7 +123,7 @@ def main():
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    out = run(args.steps, max(args.warmup, 3), args.global_batch, args.micro_batch, args.seq_len)
+    out = run(args.steps, max(args.warmup, 3), args.global_batch, args.micro_batch, args.seq_len, baseline=not args.no_baseline)
     if out is not None:
         print(json.dumps(out))
     if world > 1:
