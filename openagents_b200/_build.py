@@ -34,7 +34,7 @@ def _sources(sub: str, exts: tuple[str, ...]) -> list[Path]:
 
 def host_sources() -> list[Path]:
     out = []
-    for sub in ("gguf", "kv", "host"):
+    for sub in ("gguf", "kv", "data", "host"):
         if (CSRC / sub).is_dir():
             out += _sources(sub, (".cpp",))
     return out

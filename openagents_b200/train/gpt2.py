@@ -151,8 +151,11 @@ class GPT2Model:
             self._gemm(dy, self.wT[wname], M, K, N, out_bf16=dx_out)
 
     # ---- forward + backward of one micro-batch; returns the mean loss (device scalar)
-    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, loss_scale: float = 1.0, on_bucket=None, before_layer=None):
-        """``on_bucket(i)`` is called right after the backward of layer ``i`` has been enqueued (its weight gradients are then
+    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, loss_scale: float = 1.0, on_bucket=None, before_layer=None,
+                         denom: float | None = None):
+        """``denom``: with masked targets (negative ids contribute neither loss nor gradient) the caller passes the number of
+        unmasked targets the loss is averaged over; the return value is then this micro-batch's share ``sum / denom``.
+        ``on_bucket(i)`` is called right after the backward of layer ``i`` has been enqueued (its weight gradients are then
         final for this micro-batch) and ``on_bucket(None)`` at the very end (embeddings, norms and biases).
         ``before_layer("rest")`` is called before anything reads a parameter and ``before_layer(i)`` before layer ``i``'s
         forward (the trainer waits there for that chunk of the parameter all-gather)."""
@@ -186,9 +189,9 @@ class GPT2Model:
                            self.lnf, self.meanf, self.rstdf)
         wte = self.p["token_embd.weight"]
         self._gemm(self.lnf, wte, M, self.Vp, d, out_bf16=self.logits)
-        tops.ce_fused(self.logits, tg, self.loss_rows, loss_scale / M, cfg.vocab)     # logits now hold dlogits
+        tops.ce_fused(self.logits, tg, self.loss_rows, loss_scale / M if denom is None else 1.0 / denom, cfg.vocab)     # logits now hold dlogits
         self.kernel_launches += 2
-        loss = self.loss_rows.mean()
+        loss = self.loss_rows.mean() if denom is None else self.loss_rows.sum() / denom
 
         # ---- backward
         dlog = self.logits

@@ -45,6 +45,8 @@ def parse(argv=None):
     ap.add_argument("--max-allowed-stale", type=int, default=5)
     ap.add_argument("--master-port", type=int, default=29517)
     ap.add_argument("--log-jsonl", default="")
+    ap.add_argument("--data", nargs="*", default=[], help="token shards (data.write_token_shard); default: synthetic uniform ids")
+    ap.add_argument("--data-raw-width", type=int, default=0, choices=[0, 2, 4], help="read files without a shard header as raw ids of this width")
     ap.add_argument("--sync-profile", default="sync", choices=["sync", "diloco"],
                     help="sync: every step is data-parallel over all ranks; diloco: every rank is a replica that takes "
                          "--inner-steps local steps per round, then one outer step over all replicas")
@@ -87,6 +89,15 @@ def worker(args):
     auth.advance_run(run.run_ref, "active")
     wsteps = args.window_steps or args.steps
     log = open(args.log_jsonl, "a") if (args.log_jsonl and rank == 0) else None
+    loader = None
+    if args.data:
+        from ..data import BatchLoader, TokenDataset
+        ds = TokenDataset(args.data, cfg.seq_len, args.data_raw_width)
+        # the sampler is a function of the batch index, so a resumed run continues the stream at its step count
+        loader = BatchLoader(ds, tr.accum, cfg.micro_batch, rank, world, seed=cfg.seed, start_batch=tr.step_count)
+        if rank == 0:
+            print(json.dumps({"event": "data", "shards": len(args.data), "tokens": ds.tokens, "windows": ds.windows,
+                              "batchesPerEpoch": loader.batches_per_epoch}))
     step0 = tr.step_count
     done = 0
     while done < args.steps:
@@ -96,10 +107,17 @@ def worker(args):
         auth.claim_lease(w.window_ref, f"worker.rank{rank}")
         t_train = 0.0
         for _ in range(n):
-            tok, tgt = synthetic_batch(cfg, tr.accum, tr.step_count, rank, dev)
-            tok, tgt = tok.pin_memory().to(dev, non_blocking=True), tgt.pin_memory().to(dev, non_blocking=True)
+            n_valid = None
+            if loader is not None:
+                tok, tgt, nv, _ = loader.next()
+                n_valid = nv if nv < tok.numel() else None           # only masked data changes the normalisation
+                # the slot goes back to the loader at the next call, after this step's loss has been read (a stream sync)
+                tok, tgt = tok.to(dev, non_blocking=True), tgt.to(dev, non_blocking=True)
+            else:
+                tok, tgt = synthetic_batch(cfg, tr.accum, tr.step_count, rank, dev)
+                tok, tgt = tok.pin_memory().to(dev, non_blocking=True), tgt.pin_memory().to(dev, non_blocking=True)
             t0 = time.perf_counter()
-            loss = tr.train_step(tok, tgt)
+            loss = tr.train_step(tok, tgt, n_valid)
             lv = float(loss.item())
             dt = time.perf_counter() - t0
             t_train += dt

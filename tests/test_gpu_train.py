@@ -80,3 +80,54 @@ def test_loss_decreases_and_optimizer_matches_adamw():
         losses.append(tr.train_step(tok, tgt).item())
     assert losses[-1] < losses[0] - 0.5 and losses[0] < math.log(cfg.model.vocab) + 0.5
     tr.check_status()
+
+
+def test_masked_targets_match_oracle_and_loader_feeds_the_trainer(tmp_path):
+    """Instruction-tuning shape: half of the targets masked (-1), loss and gradients averaged over the rest; then batches
+    from token shards through the prefetching loader."""
+    import numpy as np
+    from openagents_b200.data import BatchLoader, TokenDataset, write_token_shard
+    from openagents_b200.oracle.models import gpt2_forward
+    from openagents_b200.train.trainer import Trainer, synthetic_batch
+    cfg = _small_cfg()
+    tr = Trainer(cfg, "cuda:0")
+    tok, tgt = synthetic_batch(cfg, 1, 0, 0, "cuda:0")
+    tok, tgt = tok.cuda(), tgt.cuda()
+    keep = torch.rand(tgt.shape, device="cuda", generator=torch.Generator("cuda").manual_seed(1)) < 0.5
+    tgt = torch.where(keep, tgt, torch.full_like(tgt, -1))
+    n_valid = int(keep.sum())
+    loss = tr.model.forward_backward(tok[0], tgt[0], denom=float(n_valid))
+    tr.check_status()
+    W = {}
+    for sl in tr.slots:
+        x = tr.params[sl.offset: sl.offset + sl.numel].view(*sl.shape).float()
+        if sl.name == "token_embd.weight":
+            x = x[: cfg.model.vocab]
+        W[sl.name] = x.clone().requires_grad_(True)
+    logits = gpt2_forward(cfg.model, W, tok[0].long())
+    ref = torch.nn.functional.cross_entropy(logits.view(-1, cfg.model.vocab), tgt[0].reshape(-1).long(), ignore_index=-1)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 2e-2
+    for sl in tr.slots:
+        g = tr.grads[sl.offset: sl.offset + sl.numel].view(*sl.shape)
+        if sl.name == "token_embd.weight":
+            g = g[: cfg.model.vocab]
+        r = W[sl.name].grad
+        assert (g - r).norm().item() / (r.norm().item() + 1e-12) < 0.08, sl.name
+    tr.grads.zero_()
+
+    # a periodic token stream with the odd positions masked: learnable, and n_valid is half of every batch
+    period = np.arange(37) * 13 % 1000
+    stream = np.tile(period, 400)
+    mask = (np.arange(stream.size) % 2).astype(np.uint8)
+    write_token_shard(tmp_path / "a.b2tk", stream[:9000], mask[:9000])
+    write_token_shard(tmp_path / "b.b2tk", stream[9000:], mask[9000:])
+    ds = TokenDataset([tmp_path / "a.b2tk", tmp_path / "b.b2tk"], cfg.seq_len)
+    ld = BatchLoader(ds, tr.accum, cfg.micro_batch, seed=3)
+    losses = []
+    for _ in range(30):
+        t, g, nv, _ = ld.next()
+        assert t.is_pinned() and nv == t.numel() // 2
+        losses.append(tr.train_step(t.cuda(non_blocking=True), g.cuda(non_blocking=True), nv).item())
+    tr.check_status()
+    assert losses[0] > 5.0 and losses[-1] < losses[0] - 2.0, losses
