@@ -47,6 +47,14 @@ def parse(argv=None):
     ap.add_argument("--log-jsonl", default="")
     ap.add_argument("--data", nargs="*", default=[], help="token shards (data.write_token_shard); default: synthetic uniform ids")
     ap.add_argument("--data-raw-width", type=int, default=0, choices=[0, 2, 4], help="read files without a shard header as raw ids of this width")
+    ap.add_argument("--lane", default="pretrain", choices=["pretrain", "sft"],
+                    help="sft: instruction tuning on --sft-records (JSON lines of {messages: [...]}) with the assistant-token mask, "
+                         "cosine schedule and a checkpoint/resume drill; prints the lane report")
+    ap.add_argument("--sft-records", default="")
+    ap.add_argument("--sft-merges", type=int, default=512, help="merges of the byte-level BPE trained on the records")
+    ap.add_argument("--sft-repeat", type=int, default=0, help="tile the packed corpus this many times (0 = enough for the run)")
+    ap.add_argument("--checkpoint-at", type=int, default=0, help="step of the resume drill (0 = a third of the run)")
+    ap.add_argument("--report", default="", help="write the lane report here as JSON")
     ap.add_argument("--sync-profile", default="sync", choices=["sync", "diloco"],
                     help="sync: every step is data-parallel over all ranks; diloco: every rank is a replica that takes "
                          "--inner-steps local steps per round, then one outer step over all replicas")
@@ -79,6 +87,8 @@ def worker(args):
                       zero_stage=args.zero_stage)
     if args.sync_profile == "diloco":
         return diloco_worker(args, cfg, dev, rank, world)
+    if args.lane == "sft":
+        return sft_worker(args, cfg, dev, rank, world)
     tr = Trainer(cfg, dev, rank, world)
     if args.resume:
         man = tr.load_checkpoint(args.resume)
@@ -193,6 +203,48 @@ def diloco_worker(args, cfg, dev, rank, world):
             print(json.dumps({"event": "round", **rec, "round_s": round(dt, 4), "windowRef": w.window_ref, "replicas": world,
                               "tokens_per_s": round(rec["tokensAllReplicas"] / dt, 1), "windowTags": tags}), flush=True)
         auth.seal_window(w.window_ref, rw.SealMetadata(verification_overhead={"verificationSeconds": 0.0, "trainingSeconds": dt}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def sft_worker(args, cfg, dev, rank, world):
+    """Instruction tuning on a file of chat records: tokenizer, masked shard, the run and its resume drill."""
+    import dataclasses
+    import tempfile
+    import torch.distributed as dist
+    from ..data import BatchLoader, ByteBpe, TokenDataset
+    from . import sft
+    from .trainer import Trainer
+    if not args.sft_records:
+        raise SystemExit("--lane sft needs --sft-records")
+    with open(args.sft_records) as f:
+        records = [json.loads(line) for line in f if line.strip()]
+    text = "\n".join(m["content"] for r in records for m in r["messages"]).encode()
+    tok = ByteBpe.train(text, args.sft_merges, special=sft.SPECIAL_TOKENS)
+    if tok.vocab_size > cfg.model.vocab:
+        raise SystemExit(f"the tokenizer has {tok.vocab_size} ids, the model {cfg.model.vocab}")
+    corpus = sft.build_corpus(records, tok, os.path.basename(args.sft_records))
+    cfg = dataclasses.replace(cfg, total_steps=args.steps)
+    work = args.ckpt_dir or tempfile.mkdtemp(prefix="b200_sft_")
+    os.makedirs(work, exist_ok=True)
+    shard = os.path.join(work, "sft.b2tk")
+    accum = cfg.global_batch // (cfg.micro_batch * world)
+    need = (cfg.global_batch * cfg.seq_len + 1) * 2
+    repeat = args.sft_repeat or max(1, -(-need // len(corpus.ids)))
+    if rank == 0:
+        sft.pack(corpus, shard, repeat)
+    if world > 1:
+        dist.barrier()
+    ds = TokenDataset(shard, cfg.seq_len)
+    rep = sft.run_lane(lambda: Trainer(cfg, dev, rank, world),
+                       lambda start: BatchLoader(ds, accum, cfg.micro_batch, rank, world, seed=cfg.seed, start_batch=start),
+                       steps=args.steps, checkpoint_at=args.checkpoint_at or max(1, args.steps // 3), ckpt_dir=os.path.join(work, "drill"),
+                       corpus_manifest=corpus.manifest, device=dev)
+    if rank == 0:
+        print(json.dumps(rep))
+        if args.report:
+            with open(args.report, "w") as f:
+                json.dump(rep, f, indent=1)
     if world > 1:
         dist.destroy_process_group()
 

@@ -131,3 +131,28 @@ def test_masked_targets_match_oracle_and_loader_feeds_the_trainer(tmp_path):
         losses.append(tr.train_step(t.cuda(non_blocking=True), g.cuda(non_blocking=True), nv).item())
     tr.check_status()
     assert losses[0] > 5.0 and losses[-1] < losses[0] - 2.0, losses
+
+
+def test_sft_lane_on_the_trainer_with_resume_drill(tmp_path):
+    """The instruction-tuning lane end to end on the GPU trainer: masked shard, cosine schedule, checkpoint at step 3, a fresh
+    trainer resumed from it; the restored state is bit-identical and the resumed losses agree with the uninterrupted run."""
+    import dataclasses
+    from openagents_b200.data import BatchLoader, ByteBpe, TokenDataset
+    from openagents_b200.train import sft
+    from openagents_b200.train.trainer import Trainer
+    records = [{"messages": [{"role": "user", "content": f"What is {a} plus {b}?"}, {"role": "assistant", "content": f"It is {a + b}."}]}
+               for a in range(6) for b in range(6)]
+    text = "\n".join(m["content"] for r in records for m in r["messages"]).encode()
+    tok = ByteBpe.train(text, 64, special=sft.SPECIAL_TOKENS)
+    corpus = sft.build_corpus(records, tok, "sums@v1")
+    sft.pack(corpus, tmp_path / "sft.b2tk", repeat=3)
+    cfg = dataclasses.replace(_small_cfg(), total_steps=9, lr=3e-3)
+    assert tok.vocab_size <= cfg.model.vocab
+    ds = TokenDataset(tmp_path / "sft.b2tk", cfg.seq_len)
+    rep = sft.run_lane(lambda: Trainer(cfg, "cuda:0"), lambda start: BatchLoader(ds, 1, cfg.micro_batch, seed=2, start_batch=start),
+                       steps=9, checkpoint_at=3, ckpt_dir=str(tmp_path / "drill"), corpus_manifest=corpus.manifest, device="cuda:0",
+                       loss_tolerance=2e-2)
+    d = rep["resumeDrill"]
+    assert rep["lossImproved"] and rep["lastLoss"] < rep["firstLoss"] - 0.5, rep["stepReceipts"]
+    assert d["restoredStateBitExact"] and d["sameBatchesAfterResume"] and d["postResumeLossesAgree"], d
+    assert all(0 < r["trainableTokens"] < 4 * 64 for r in rep["stepReceipts"])
