@@ -50,6 +50,14 @@ class Backend:
     def seq_len(self, seq_id: int) -> int:
         raise NotImplementedError
 
+    # ---- scoring support (optional): log-probabilities of given continuations (evaluation packs, ``logprobs``)
+    supports_score = False
+
+    def score(self, seq_id: int, tokens: list[int], targets: list[int]) -> list[float]:
+        """Append ``tokens``; natural-log probability of ``targets[i]`` as the token after ``tokens[i]`` (a negative target
+        yields 0.0).  ``len(targets) == len(tokens)``."""
+        raise NotImplementedError
+
     @property
     def max_context(self) -> int | None:
         """Longest sequence (prompt + generated) the backend can hold, or None when it does not know."""
@@ -125,6 +133,16 @@ class CpuBackend(Backend):
     def verify(self, seq_id, tokens):
         from ..oracle.models import llama_forward
         return llama_forward(self.cfg, self.W, torch.tensor(tokens, dtype=torch.long), self.caches[seq_id]).float().argmax(-1).tolist()
+
+    supports_score = True
+
+    @torch.no_grad()
+    def score(self, seq_id, tokens, targets):
+        from ..oracle.models import llama_forward
+        lp = torch.log_softmax(llama_forward(self.cfg, self.W, torch.tensor(tokens, dtype=torch.long), self.caches[seq_id]).double(), -1)
+        t = torch.tensor(targets, dtype=torch.long)
+        out = lp.gather(1, t.clamp(min=0).unsqueeze(1)).squeeze(1)
+        return torch.where(t >= 0, out, torch.zeros_like(out)).tolist()
 
     def truncate(self, seq_id, new_len):
         self.caches[seq_id].truncate(new_len)
@@ -228,6 +246,21 @@ class CudaBackend(Backend):
         _, ids = self.engine.forward_tokens([seq_id], [list(tokens)], all_positions=True)
         self.last_d2h_bytes = 4 * len(tokens)
         return ids[: len(tokens)].tolist()
+
+    supports_score = True
+
+    def score(self, seq_id, tokens, targets):
+        # logits of every position fit the workspace ``max_batch`` rows at a time
+        out, step = [], self.engine.max_batch
+        for lo in range(0, len(tokens), step):
+            chunk = list(tokens[lo: lo + step])
+            logits, _ = self.engine.forward_tokens([seq_id], [chunk], all_positions=True)
+            full = self._full_rows(logits[: len(chunk)]).float()
+            t = torch.tensor(targets[lo: lo + step], dtype=torch.long).pin_memory().to(full.device, non_blocking=True)
+            lp = torch.log_softmax(full, -1).gather(1, t.clamp(min=0).unsqueeze(1)).squeeze(1)
+            out.append(torch.where(t >= 0, lp, torch.zeros_like(lp)))
+        self.last_d2h_bytes = 4 * len(tokens)
+        return torch.cat(out).cpu().tolist() if out else []
 
     def truncate(self, seq_id, new_len):
         self.engine.truncate(seq_id, new_len)

@@ -65,6 +65,13 @@ class LeaderBackend(Backend):
     def truncate(self, seq_id, new_len):
         return self._call("truncate", seq_id, new_len)
 
+    @property
+    def supports_score(self):
+        return self.inner.supports_score
+
+    def score(self, seq_id, tokens, targets):
+        return self._call("score", seq_id, list(tokens), list(targets))
+
     def seq_len(self, seq_id):
         return self.inner.seq_len(seq_id)          # host-side bookkeeping, identical on every rank
 

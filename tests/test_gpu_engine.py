@@ -233,3 +233,38 @@ def test_speculative_decoding_matches_greedy_on_the_engine(tmp_path):
     assert all_at_once == one_by_one and be.seq_len(1) == len(prompt)
     be.truncate(1, len(prompt) - 3)
     assert be.seq_len(1) == len(prompt) - 3 and be.verify(1, tail[2:]) == all_at_once[2:]
+
+
+def test_scoring_on_the_engine_matches_the_cpu_backend(tmp_path):
+    """Log-probabilities of given continuations (evaluation packs): the engine's multi-position logits against the fp32 CPU
+    backend on the same quantized file, in chunks longer than the logits workspace, and a multiple-choice item that reuses
+    the context's keys and values through ``truncate``."""
+    from openagents_b200.eval import multiple_choice
+    from openagents_b200.serve.backend import CpuBackend, CudaBackend
+    from openagents_b200.serve.generation import ByteTokenizer
+    cfg = TINY_LLAMA.with_(d_model=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1024, vocab=4096, n_layers=2)
+    p = str(tmp_path / "q8.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 4), PLAN_Q8_0)
+    gpu = CudaBackend.from_gguf(p, max_num_seqs=8, max_ctx=512, max_tokens=512)
+    cpu = CpuBackend.from_gguf(p)
+    free0 = gpu.kv_stats()["pages_free"]
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, cfg.vocab, (151,), generator=g).tolist()          # more than two chunks of 64 rows
+    feed, tgt = toks[:-1], toks[1:]
+    tgt[7] = -1
+    gpu.begin(1, feed)
+    cpu.begin(1, feed)
+    a, b = gpu.score(1, feed, tgt), cpu.score(1, feed, tgt)
+    gpu.engine.check_status()
+    assert a[7] == 0.0 and gpu.seq_len(1) == 150
+    worst = max(abs(x - y) for x, y in zip(a, b))
+    assert worst < 0.15, worst                                                   # bf16 activations against fp32
+    assert abs(sum(a) - sum(b)) / 150 < 0.02
+    gpu.end(1)
+    cpu.end(1)
+    items = [{"context": "the cat sat on the", "choices": [" mat", " moon and stars", " q"], "answer": 0}]
+    tok = ByteTokenizer(cfg.vocab)
+    rg, rc = multiple_choice(gpu, items, tok), multiple_choice(cpu, items, tok)
+    gpu.engine.check_status()
+    assert all(abs(x - y) < 0.1 for x, y in zip(rg["picks"][0]["scores"], rc["picks"][0]["scores"]))
+    assert gpu.kv_stats()["pages_free"] == free0                                 # every sequence was closed
