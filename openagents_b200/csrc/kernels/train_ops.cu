@@ -363,8 +363,11 @@ B200_API int b200_bias_grad(const void* dy, float* gb, int M, int N, cudaStream_
 // its gradient is zero).  Per row: loss = logsumexp - logit[target]; dlogits = (softmax - onehot) *
 // scale, written in place over the logits.  One CTA per row; 16-byte accesses; maximum and sum in ONE pass
 // (running maximum per thread, rescaled sums), so a row is read twice and written once.
+// row_scale (optional): one factor per row that replaces `scale` (preference optimisation weights every sequence's rows by
+// a signed coefficient).  write_grad = 0 stops after the loss: the logits stay as they are, so the caller can derive the
+// row factors from the losses and call again.
 __global__ void __launch_bounds__(512) ce_fused_kernel(bf16* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ loss,
-                                                       float scale, int V, int ldl) {
+                                                       float scale, const float* __restrict__ row_scale, int write_grad, int V, int ldl) {
   __shared__ float red[32];
   const size_t row = blockIdx.x;
   bf16* l = logits + row * ldl;
@@ -392,9 +395,10 @@ __global__ void __launch_bounds__(512) ce_fused_kernel(bf16* __restrict__ logits
   const int tgt = targets[row];
   const float lse = gmx + __logf(se);
   if (threadIdx.x == 0) loss[row] = tgt >= 0 ? lse - __bfloat162float(l[tgt]) : 0.f;
+  if (!write_grad) return;
   __syncthreads();                       // the target logit is read before anyone overwrites it
   const float inv = 1.f / se;
-  const float sc = tgt >= 0 ? scale : 0.f;   // a negative target masks the position
+  const float sc = tgt >= 0 ? (row_scale ? row_scale[row] : scale) : 0.f;   // a negative target masks the position
   for (int i = threadIdx.x * 8; i < ldl; i += blockDim.x * 8) {
     float f[8];
     unpack8(*(const uint4*)(l + i), f);
@@ -407,6 +411,12 @@ __global__ void __launch_bounds__(512) ce_fused_kernel(bf16* __restrict__ logits
 B200_API int b200_ce_fused(void* logits, const int* targets, float* loss, float scale, int M, int V, int ldl,
                            cudaStream_t st) {
   if (ldl % 8) return B200_ERR_BAD_ARG;
-  ce_fused_kernel<<<M, 512, 0, st>>>((bf16*)logits, targets, loss, scale, V, ldl);
+  ce_fused_kernel<<<M, 512, 0, st>>>((bf16*)logits, targets, loss, scale, nullptr, 1, V, ldl);
+  return (int)cudaGetLastError();
+}
+B200_API int b200_ce_fused_rows(void* logits, const int* targets, float* loss, const float* row_scale, int write_grad, int M, int V, int ldl,
+                                cudaStream_t st) {
+  if (ldl % 8 || (write_grad && !row_scale)) return B200_ERR_BAD_ARG;
+  ce_fused_kernel<<<M, 512, 0, st>>>((bf16*)logits, targets, loss, 0.f, row_scale, write_grad, V, ldl);
   return (int)cudaGetLastError();
 }

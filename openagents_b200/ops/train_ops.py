@@ -19,6 +19,7 @@ _SIGS = {
     "b200_gelu_bwd": [_P, _P, c_size_t, _P],
     "b200_bias_grad": [_P, _P, c_int, c_int, _P],
     "b200_ce_fused": [_P, _P, _P, c_float, c_int, c_int, c_int, _P],
+    "b200_ce_fused_rows": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "b200_attn_train_fwd": [_P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "b200_attn_train_bwd": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "b200_zero_reduce_norm": [_P, c_size_t, c_size_t, c_size_t, _P, _P, _P],
@@ -74,6 +75,13 @@ def bias_grad(dy, gb):
 def ce_fused(logits, targets, loss, scale, V):
     M, ldl = logits.shape
     _check(lib().b200_ce_fused(_p(logits), _p(targets), _p(loss), scale, M, V, ldl, _st()), "ce_fused")
+
+
+def ce_fused_rows(logits, targets, loss, row_scale, V):
+    """Per-row losses only (``row_scale`` None: the logits are left untouched) or losses + gradients scaled row by row."""
+    M, ldl = logits.shape
+    _check(lib().b200_ce_fused_rows(_p(logits), _p(targets), _p(loss), _p(row_scale) if row_scale is not None else None,
+                                    int(row_scale is not None), M, V, ldl, _st()), "ce_fused_rows")
 
 
 def attn_train_fwd(qkv, o, lse, B, T, H, hd):

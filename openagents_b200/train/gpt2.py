@@ -152,8 +152,12 @@ class GPT2Model:
 
     # ---- forward + backward of one micro-batch; returns the mean loss (device scalar)
     def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, loss_scale: float = 1.0, on_bucket=None, before_layer=None,
-                         denom: float | None = None):
-        """``denom``: with masked targets (negative ids contribute neither loss nor gradient) the caller passes the number of
+                         denom: float | None = None, backward: bool = True, row_scale_fn=None):
+        """``backward=False``: forward only; returns a copy of the per-token losses ``-log p(target)`` [M] (0 where masked).
+        ``row_scale_fn(loss_rows) -> (row_scale [M] fp32, reported loss)``: objectives that weight every token's log-likelihood
+        gradient by a factor that depends on the losses themselves (preference optimisation): the losses are computed first
+        with the logits left intact, the function runs on the device, then the gradient is written with those factors.
+        ``denom``: with masked targets (negative ids contribute neither loss nor gradient) the caller passes the number of
         unmasked targets the loss is averaged over; the return value is then this micro-batch's share ``sum / denom``.
         ``on_bucket(i)`` is called right after the backward of layer ``i`` has been enqueued (its weight gradients are then
         final for this micro-batch) and ``on_bucket(None)`` at the very end (embeddings, norms and biases).
@@ -189,9 +193,19 @@ class GPT2Model:
                            self.lnf, self.meanf, self.rstdf)
         wte = self.p["token_embd.weight"]
         self._gemm(self.lnf, wte, M, self.Vp, d, out_bf16=self.logits)
-        tops.ce_fused(self.logits, tg, self.loss_rows, loss_scale / M if denom is None else 1.0 / denom, cfg.vocab)     # logits now hold dlogits
-        self.kernel_launches += 2
-        loss = self.loss_rows.mean() if denom is None else self.loss_rows.sum() / denom
+        if not backward:
+            tops.ce_fused_rows(self.logits, tg, self.loss_rows, None, cfg.vocab)
+            self.kernel_launches += 2
+            return self.loss_rows.clone()
+        if row_scale_fn is not None:
+            tops.ce_fused_rows(self.logits, tg, self.loss_rows, None, cfg.vocab)
+            row_scale, loss = row_scale_fn(self.loss_rows)
+            tops.ce_fused_rows(self.logits, tg, self.loss_rows, row_scale.contiguous(), cfg.vocab)     # logits now hold dlogits
+            self.kernel_launches += 3
+        else:
+            tops.ce_fused(self.logits, tg, self.loss_rows, loss_scale / M if denom is None else 1.0 / denom, cfg.vocab)     # logits now hold dlogits
+            self.kernel_launches += 2
+            loss = self.loss_rows.mean() if denom is None else self.loss_rows.sum() / denom
 
         # ---- backward
         dlog = self.logits

@@ -47,9 +47,11 @@ def parse(argv=None):
     ap.add_argument("--log-jsonl", default="")
     ap.add_argument("--data", nargs="*", default=[], help="token shards (data.write_token_shard); default: synthetic uniform ids")
     ap.add_argument("--data-raw-width", type=int, default=0, choices=[0, 2, 4], help="read files without a shard header as raw ids of this width")
-    ap.add_argument("--lane", default="pretrain", choices=["pretrain", "sft"],
+    ap.add_argument("--lane", default="pretrain", choices=["pretrain", "sft", "dpo"],
                     help="sft: instruction tuning on --sft-records (JSON lines of {messages: [...]}) with the assistant-token mask, "
                          "cosine schedule and a checkpoint/resume drill; prints the lane report")
+    ap.add_argument("--dpo-pairs", default="", help="--lane dpo: JSON lines of {messages, chosen, rejected}")
+    ap.add_argument("--beta", type=float, default=0.1, help="--lane dpo: strength of the implicit reward")
     ap.add_argument("--sft-records", default="")
     ap.add_argument("--sft-merges", type=int, default=512, help="merges of the byte-level BPE trained on the records")
     ap.add_argument("--sft-repeat", type=int, default=0, help="tile the packed corpus this many times (0 = enough for the run)")
@@ -89,6 +91,8 @@ def worker(args):
         return diloco_worker(args, cfg, dev, rank, world)
     if args.lane == "sft":
         return sft_worker(args, cfg, dev, rank, world)
+    if args.lane == "dpo":
+        return dpo_worker(args, cfg, dev, rank, world)
     tr = Trainer(cfg, dev, rank, world)
     if args.resume:
         man = tr.load_checkpoint(args.resume)
@@ -245,6 +249,58 @@ def sft_worker(args, cfg, dev, rank, world):
         if args.report:
             with open(args.report, "w") as f:
                 json.dump(rep, f, indent=1)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def dpo_worker(args, cfg, dev, rank, world):
+    """Preference optimisation on a file of pairs: every step takes the next ``global_batch / 2`` pairs (cycling), the
+    reference log-probabilities are computed once with the starting weights."""
+    import torch
+    import torch.distributed as dist
+    from ..data import ByteBpe
+    from . import dpo, sft
+    from .trainer import Trainer
+    if not args.dpo_pairs:
+        raise SystemExit("--lane dpo needs --dpo-pairs")
+    with open(args.dpo_pairs) as f:
+        pairs = [json.loads(line) for line in f if line.strip()]
+    text = "\n".join([m["content"] for p in pairs for m in p["messages"]] + [p[k] for p in pairs for k in ("chosen", "rejected")]).encode()
+    tok = ByteBpe.train(text, args.sft_merges, special=sft.SPECIAL_TOKENS)
+    if tok.vocab_size > cfg.model.vocab:
+        raise SystemExit(f"the tokenizer has {tok.vocab_size} ids, the model {cfg.model.vocab}")
+    tr = Trainer(cfg, dev, rank, world)
+    if args.resume:
+        tr.load_checkpoint(args.resume)
+    d = dpo.DpoTrainer(tr, beta=args.beta)
+    P = cfg.micro_batch // 2                       # pairs per micro-batch on this rank
+    per_step = P * tr.accum * world
+
+    def batch(step):
+        toks, tgts = [], []
+        for a in range(tr.accum):
+            at = step * per_step + (a * world + rank) * P
+            t, g, _ = dpo.build_preference_batch([pairs[(at + i) % len(pairs)] for i in range(P)], tok, cfg.seq_len)
+            toks.append(t)
+            tgts.append(g)
+        return torch.stack(toks).pin_memory().to(dev, non_blocking=True), torch.stack(tgts).pin_memory().to(dev, non_blocking=True)
+
+    distinct = min(args.steps, -(-len(pairs) // per_step))
+    refs = {}
+    for s in range(distinct):                      # before the first update: the starting weights are the reference policy
+        t, g = batch(s)
+        refs[s] = d.reference_logps(t, g)
+    for s in range(args.steps):
+        t, g = batch(s % distinct)
+        t0 = time.perf_counter()
+        loss = float(d.train_step(t, g, refs[s % distinct]).item())
+        dt = time.perf_counter() - t0
+        if rank == 0:
+            print(json.dumps({"event": "step", "step": tr.step_count, "pair_loss": round(loss, 5), "reward_accuracy": round(d.reward_accuracy(), 4),
+                              "grad_norm": round(tr.grad_norm(), 5), "step_s": round(dt, 4), "pairs_per_s": round(per_step / dt, 1)}), flush=True)
+    tr.check_status()
+    if args.ckpt_dir:
+        tr.save_checkpoint(os.path.join(args.ckpt_dir, f"step{tr.step_count:08d}"))
     if world > 1:
         dist.destroy_process_group()
 

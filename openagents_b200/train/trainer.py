@@ -126,10 +126,12 @@ class Trainer:
 
     # ---- one optimizer step over `accum` micro-batches.  tokens/targets: [accum, micro_batch, seq_len]
     @nvtx_method("train.forward_backward")
-    def train_step(self, tokens: torch.Tensor, targets: torch.Tensor, n_valid: int | None = None) -> torch.Tensor:
+    def train_step(self, tokens: torch.Tensor, targets: torch.Tensor, n_valid: int | None = None, row_scale_fns=None) -> torch.Tensor:
         """``tokens`` / ``targets``: ``[accum, micro_batch, seq_len]`` on the device.  ``n_valid``: when some targets are
         masked (negative), the number of unmasked targets in this rank's batch; the loss and its gradient are then the mean
-        over those (per rank; ranks are averaged as usual)."""
+        over those (per rank; ranks are averaged as usual).  ``row_scale_fns``: one function per micro-batch for objectives
+        whose per-token gradient weights depend on the losses (``GPT2Model.forward_backward``); each returns its share of
+        the step's loss, and the shares are summed."""
         losses = []
         denom = None if n_valid is None else float(max(1, n_valid))
         for a in range(self.accum):
@@ -138,11 +140,12 @@ class Trainer:
                 self.norm2.zero_()
                 hook = self._bucket_ready
             wait = self._wait_chunk if (a == 0 and self._param_ready) else None
-            losses.append(self.model.forward_backward(tokens[a], targets[a], loss_scale=1.0 / self.accum, on_bucket=hook, before_layer=wait, denom=denom))
+            losses.append(self.model.forward_backward(tokens[a], targets[a], loss_scale=1.0 / self.accum, on_bucket=hook, before_layer=wait, denom=denom,
+                                                      row_scale_fn=row_scale_fns[a] if row_scale_fns else None))
             if a == 0:
                 self._sync_params()                  # whatever the first forward did not wait for (nothing, normally)
         self.optimizer_step()
-        return torch.stack(losses).mean() if denom is None else torch.stack(losses).sum()
+        return torch.stack(losses).mean() if (denom is None and not row_scale_fns) else torch.stack(losses).sum()
 
     # ---- chunked parameter all-gather, overlapped with the next forward
     def _wait_chunk(self, key):

@@ -156,3 +156,53 @@ def test_sft_lane_on_the_trainer_with_resume_drill(tmp_path):
     assert rep["lossImproved"] and rep["lastLoss"] < rep["firstLoss"] - 0.5, rep["stepReceipts"]
     assert d["restoredStateBitExact"] and d["sameBatchesAfterResume"] and d["postResumeLossesAgree"], d
     assert all(0 < r["trainableTokens"] < 4 * 64 for r in rep["stepReceipts"])
+
+
+def test_dpo_gradients_match_autograd_and_preferences_are_learned():
+    """Preference optimisation through the fused cross-entropy's per-row factors: gradients against autograd of the pair loss on
+    the fp32 oracle, then a few steps on fixed pairs (the loss falls below ln 2, every pair ends up ranked correctly)."""
+    import dataclasses
+    import math
+    from openagents_b200.data import ByteBpe
+    from openagents_b200.oracle.models import gpt2_forward
+    from openagents_b200.train import dpo, sft
+    from openagents_b200.train.trainer import Trainer
+    cfg = dataclasses.replace(_small_cfg(), lr=2e-3, weight_decay=0.0)
+    tok = ByteBpe.train(b"What is the capital? Paris. London. red green blue yes no maybe", 10, special=sft.SPECIAL_TOKENS)
+    pairs = [{"messages": [{"role": "user", "content": f"Question {i}: red or blue?"}], "chosen": "red " * (1 + i % 2), "rejected": "blue"} for i in range(2)]
+    tokens, targets, _ = dpo.build_preference_batch(pairs, tok, cfg.seq_len)
+    assert tokens.shape[0] == cfg.micro_batch
+    tokens, targets = tokens[None].cuda(), targets[None].cuda()
+    tr = Trainer(cfg, "cuda:0")
+    d = dpo.DpoTrainer(tr, beta=0.5)
+    ref = d.reference_logps(tokens, targets)
+    tr.check_status()
+    assert ref.shape == (1, 4) and bool((ref < 0).all())
+    shifted = ref + torch.tensor([[0.3, -0.2, 0.1, 0.4]], device="cuda")          # margins away from zero, so both signs of factor matter
+    stats = {}
+    loss = tr.model.forward_backward(tokens[0], targets[0], row_scale_fn=lambda rows: dpo.dpo_row_scales(rows, shifted[0], 0.5, 2, stats))
+    tr.check_status()
+    W = {}
+    for sl in tr.slots:
+        x = tr.params[sl.offset: sl.offset + sl.numel].view(*sl.shape).float()
+        if sl.name == "token_embd.weight":
+            x = x[: cfg.model.vocab]
+        W[sl.name] = x.clone().requires_grad_(True)
+    logits = gpt2_forward(cfg.model, W, tokens[0].long())
+    nll = torch.nn.functional.cross_entropy(logits.view(-1, cfg.model.vocab), targets[0].reshape(-1).long(), ignore_index=-1, reduction="none")
+    pol = -nll.view(4, -1).sum(1)
+    m = 0.5 * ((pol[:2] - shifted[0, :2]) - (pol[2:] - shifted[0, 2:]))
+    want = torch.nn.functional.softplus(-m).mean()
+    want.backward()
+    assert abs(loss.item() - want.item()) < 2e-2
+    for sl in tr.slots:
+        g = tr.grads[sl.offset: sl.offset + sl.numel].view(*sl.shape)
+        if sl.name == "token_embd.weight":
+            g = g[: cfg.model.vocab]
+        r = W[sl.name].grad
+        assert (g - r).norm().item() / (r.norm().item() + 1e-12) < 0.08, sl.name
+    tr.grads.zero_()
+    losses = [d.train_step(tokens, targets, ref).item() for _ in range(25)]
+    tr.check_status()
+    assert abs(losses[0] - math.log(2.0)) < 0.05                                  # policy == reference: every margin is zero
+    assert losses[-1] < 0.35 and d.reward_accuracy() == 1.0, losses
