@@ -206,3 +206,38 @@ def test_dpo_gradients_match_autograd_and_preferences_are_learned():
     tr.check_status()
     assert abs(losses[0] - math.log(2.0)) < 0.05                                  # policy == reference: every margin is zero
     assert losses[-1] < 0.35 and d.reward_accuracy() == 1.0, losses
+
+
+def test_launcher_lanes_from_files(tmp_path, capsys):
+    """``b200-train`` end to end on files: pre-training from prepared shards (and a resumed run continuing the data stream), the
+    instruction-tuning lane and the preference lane."""
+    import json
+    from openagents_b200.data.__main__ import main as data_main
+    from openagents_b200.train.launcher import main as train_main
+    (tmp_path / "c.txt").write_text("\n\n".join(f"Document {i} tells of river {i % 7}, its boats, mills and the grain market of town {i}." for i in range(400)))
+    assert data_main(["prepare", "--text", str(tmp_path / "c.txt"), "--out", str(tmp_path / "d"), "--merges", "64", "--no-refine"]) == 0
+    capsys.readouterr()
+    common = ["--layers", "2", "--global-batch", "8", "--micro-batch", "4", "--seq-len", "64", "--lr", "1e-3"]
+    shards = [str(p) for p in sorted((tmp_path / "d").glob("train-*.b2tk"))]
+    train_main(common + ["--steps", "4", "--data", *shards, "--ckpt-dir", str(tmp_path / "ck")])
+    recs = [json.loads(x) for x in capsys.readouterr().out.splitlines() if x.startswith("{")]
+    steps = [r for r in recs if r.get("event") == "step"]
+    assert recs[0]["event"] == "data" and len(steps) == 4 and steps[-1]["loss"] < steps[0]["loss"]
+    train_main(common + ["--steps", "1", "--data", *shards, "--resume", str(tmp_path / "ck" / "step00000004")])
+    recs = [json.loads(x) for x in capsys.readouterr().out.splitlines() if x.startswith("{")]
+    assert [r["step"] for r in recs if r.get("event") == "step"] == [5]
+    with open(tmp_path / "chat.jsonl", "w") as f:
+        for a in range(5):
+            for b in range(5):
+                f.write(json.dumps({"messages": [{"role": "user", "content": f"What is {a} plus {b}?"}, {"role": "assistant", "content": f"It is {a + b}."}]}) + "\n")
+    train_main(common + ["--lane", "sft", "--steps", "6", "--sft-records", str(tmp_path / "chat.jsonl"), "--sft-merges", "32", "--ckpt-dir", str(tmp_path / "sft"),
+                         "--report", str(tmp_path / "sft.json")])
+    capsys.readouterr()
+    rep = json.loads((tmp_path / "sft.json").read_text())
+    assert rep["completedSteps"] == 6 and rep["lossImproved"] and rep["resumeDrill"]["restoredStateBitExact"] and rep["resumeDrill"]["checkpointAtStep"] == 2
+    with open(tmp_path / "pairs.jsonl", "w") as f:
+        for i in range(6):
+            f.write(json.dumps({"messages": [{"role": "user", "content": f"Pick a colour, number {i}."}], "chosen": "red", "rejected": "blue"}) + "\n")
+    train_main(common + ["--lane", "dpo", "--steps", "6", "--dpo-pairs", str(tmp_path / "pairs.jsonl"), "--sft-merges", "16", "--beta", "0.5"])
+    steps = [json.loads(x) for x in capsys.readouterr().out.splitlines() if x.startswith("{")]
+    assert len(steps) == 6 and abs(steps[0]["pair_loss"] - 0.693) < 0.05 and steps[-1]["pair_loss"] < steps[0]["pair_loss"]
