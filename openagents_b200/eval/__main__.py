@@ -41,7 +41,7 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
 
     from ..data import TokenDataset
-    from ..serve.backend import CpuBackend, CudaBackend
+    from ..serve.backend import open_backend
     from ..serve.server import load_tokenizer
     from .pack import EvalPack, eval_run_evidence, run_pack
 
@@ -49,11 +49,8 @@ def main(argv=None) -> int:
         with open(path) as f:
             return [json.loads(x) for x in f if x.strip()]
 
-    if args.backend == "cpu":
-        backend = CpuBackend.from_gguf(args.model)
-    else:
-        backend = CudaBackend.from_gguf(args.model, device=args.device, max_num_seqs=4, max_ctx=max(args.seq_len, 512) + 64,
-                                        max_tokens=max(args.seq_len, 512) + 64)
+    backend = open_backend(args.model, args.backend, args.device, max_num_seqs=4, max_ctx=max(args.seq_len, 512) + 64,
+                           max_tokens=max(args.seq_len, 512) + 64)
     tok, _ = load_tokenizer(args.model, backend.cfg.vocab)
     tasks = []
     if args.heldout:

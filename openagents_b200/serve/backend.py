@@ -288,3 +288,21 @@ class CudaBackend(Backend):
         t["placementDigest"] = (e.placement_digest() if hasattr(e, "placement_digest") else
                                 "sha256:" + hashlib.sha256(repr(sorted(t.items(), key=lambda kv: kv[0])).encode()).hexdigest())
         return t
+
+
+def open_backend(path: str, backend: str = "cuda", device="cuda:0", **engine_args) -> Backend:
+    """The backend for a GGUF file by its architecture: the paged engine (or the fp32 oracle) for the llama and gpt-oss
+    families, the recompute backends for GPT-2-shape checkpoints."""
+    from ..gguf import GGUFFile
+    with GGUFFile(path) as f:
+        arch = f.metadata.get("general.architecture")
+    if arch == "gpt2":
+        from .gpt2_backend import Gpt2CpuBackend, Gpt2CudaBackend
+        if backend == "cpu":
+            return Gpt2CpuBackend.from_gguf(path)
+        if max(engine_args.get("tp_world", 1), engine_args.get("ep_world", 1)) > 1:
+            raise ValueError("GPT-2-shape checkpoints are served on one GPU")
+        return Gpt2CudaBackend.from_gguf(path, device=device, rows=min(8, engine_args.get("max_num_seqs", 8)))
+    if backend == "cpu":
+        return CpuBackend.from_gguf(path)
+    return CudaBackend.from_gguf(path, device=device, **engine_args)

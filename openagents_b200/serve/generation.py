@@ -153,9 +153,36 @@ class BpeTokenizer:
         return buf.decode("utf-8", "replace")
 
 
+class ByteBpeTokenizer:
+    """The native byte-level BPE (``data.bpe.ByteBpe``) behind the serving tokenizer interface.  End of sequence is the
+    end-of-turn marker when the vocabulary has one (instruction-tuned checkpoints), else ``<|endoftext|>``."""
+
+    def __init__(self, spec_json: str, vocab_size: int):
+        from ..data.bpe import ByteBpe
+        self.bpe = ByteBpe.from_json(spec_json)
+        if self.bpe.vocab_size > vocab_size:
+            raise ValueError("the tokenizer has more ids than the model")
+        self.vocab_size = vocab_size
+        ids = self.bpe.special_ids
+        self.eos_id = ids.get("<|end|>", ids.get("<|endoftext|>", vocab_size - 1))
+        self.bos_id = None
+
+    def encode(self, text: str) -> list[int]:
+        return self.bpe.encode(text)
+
+    def decode(self, ids) -> str:
+        return self.bpe.decode([i for i in ids if 0 <= i < self.bpe.vocab_size])
+
+    def decode_bytes(self, ids) -> bytes:
+        return self.bpe.decode_bytes([i for i in ids if 0 <= i < self.bpe.vocab_size])
+
+
 def tokenizer_from_metadata(meta: dict, vocab_size: int):
     """The tokenizer a GGUF file describes: byte-level BPE when it carries merges, greedy longest match over the token
     list when it only has tokens, raw bytes when it has neither (synthetic models)."""
+    own = meta.get("tokenizer.b200.byte_bpe")
+    if own:                                        # a checkpoint tuned by this framework carries the tokenizer it was tuned with
+        return ByteBpeTokenizer(own if isinstance(own, str) else bytes(own).decode(), vocab_size)
     tokens = meta.get("tokenizer.ggml.tokens")
     if not tokens:
         return ByteTokenizer(vocab_size)

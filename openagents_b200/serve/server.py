@@ -487,18 +487,15 @@ def build_state(model_paths: list[str], backend: str = "cuda", max_num_seqs: int
     """``tp_world`` / ``ep_world`` > 1: this process is rank 0 of a tensor- or expert-parallel group whose other ranks
     run ``serve.distributed.follower_loop``; every engine call is first announced to them over ``control_group``."""
     from ..receipts.manifests import artifact_digest
-    from .backend import CpuBackend, CudaBackend
+    from .backend import open_backend
     if backend not in ("cpu", "cuda"):
         raise ValueError("--backend accepts cpu or cuda")
     if kv_page_size != 16:
         raise ValueError("the paged KV cache uses 16-token pages")
     models = []
     for p in model_paths:
-        if backend == "cpu":
-            b = CpuBackend.from_gguf(p)
-        else:
-            b = CudaBackend.from_gguf(p, device=device, max_num_seqs=max_num_seqs, max_ctx=max_ctx, tp_rank=tp_rank,
-                                      tp_world=tp_world, comm=comm, ep_rank=ep_rank, ep_world=ep_world)
+        b = open_backend(p, backend, device, max_num_seqs=max_num_seqs, max_ctx=max_ctx, tp_rank=tp_rank,
+                         tp_world=tp_world, comm=comm, ep_rank=ep_rank, ep_world=ep_world)
         if max(tp_world, ep_world) > 1:
             from .distributed import LeaderBackend
             b = LeaderBackend(b, control_group)

@@ -75,8 +75,9 @@ def param_layout(cfg: ModelConfig, align: int = 64) -> tuple[list[ParamSlot], in
 class GPT2Model:
     """Holds views into the flat buffers and runs forward/backward for one micro-batch."""
 
-    def __init__(self, cfg: ModelConfig, params_bf16: torch.Tensor, grads_f32: torch.Tensor, slots: list[ParamSlot],
+    def __init__(self, cfg: ModelConfig, params_bf16: torch.Tensor, grads_f32: torch.Tensor | None, slots: list[ParamSlot],
                  micro_batch: int, seq_len: int):
+        """``grads_f32`` None: forward only (inference on the training kernels); no gradient views, no backward scratch."""
         self.cfg, self.B, self.T = cfg, micro_batch, seq_len
         self.M = micro_batch * seq_len
         self.dev = params_bf16.device
@@ -84,7 +85,8 @@ class GPT2Model:
         self.p, self.g = {}, {}
         for s in slots:
             self.p[s.name] = params_bf16[s.offset: s.offset + s.numel].view(*s.shape)
-            self.g[s.name] = grads_f32[s.offset: s.offset + s.numel].view(*s.shape)
+            if grads_f32 is not None:
+                self.g[s.name] = grads_f32[s.offset: s.offset + s.numel].view(*s.shape)
         self.slots = slots
         d, f, M = cfg.d_model, cfg.ffn, self.M
         bf = dict(dtype=torch.bfloat16, device=self.dev)
@@ -93,7 +95,7 @@ class GPT2Model:
         self.vec = {n: torch.empty(s.shape, **f32) for n, s in ((s.name, s) for s in slots) if len(s.shape) == 1}
         # transposed weight copies for dx = dy W
         self.wT = {s.name: torch.empty((s.shape[1], s.shape[0]), **bf) for s in slots
-                   if len(s.shape) == 2 and s.name.startswith("blk.")}
+                   if len(s.shape) == 2 and s.name.startswith("blk.") and grads_f32 is not None}
         self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
         L = cfg.n_layers
         self.act = [dict(x_in=torch.empty((M, d), **bf), ln1=torch.empty((M, d), **bf), mean1=torch.empty(M, **f32),
@@ -107,6 +109,9 @@ class GPT2Model:
         self.meanf, self.rstdf = torch.empty(M, **f32), torch.empty(M, **f32)
         self.logits = torch.empty((M, self.Vp), **bf)
         self.loss_rows = torch.empty(M, **f32)
+        self.kernel_launches = 0
+        if grads_f32 is None:
+            return
         # backward scratch
         self.dx = torch.empty((M, d), **bf)
         self.d_a = torch.empty((M, f), **bf)

@@ -329,12 +329,14 @@ class Trainer:
             dist.barrier(group=self.group)
         return man
 
-    def export_gguf(self, path: str, plan=None):
-        """Save the trained model through the same GGUF writer the serving loader reads."""
+    def export_gguf(self, path: str, plan=None, tokenizer=None):
+        """Save the trained model through the same GGUF writer the serving loader reads.  ``tokenizer``: a ``data.bpe.ByteBpe``;
+        its definition travels in the file's metadata so that the server tokenizes exactly as the training data was."""
         from ..models.weights import PLAN_BF16, save_gguf
         named = self.named_master()
         if self.rank == 0:
-            save_gguf(path, self.cfg.model, {k: v.cpu() for k, v in named.items()}, plan or PLAN_BF16)
+            extra = {"tokenizer.b200.byte_bpe": tokenizer.to_json()} if tokenizer is not None else None
+            save_gguf(path, self.cfg.model, {k: v.cpu() for k, v in named.items()}, plan or PLAN_BF16, extra_meta=extra)
 
 
 def synthetic_batch(cfg: TrainConfig, accum: int, step: int, rank: int, device):

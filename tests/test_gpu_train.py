@@ -241,3 +241,55 @@ def test_launcher_lanes_from_files(tmp_path, capsys):
     train_main(common + ["--lane", "dpo", "--steps", "6", "--dpo-pairs", str(tmp_path / "pairs.jsonl"), "--sft-merges", "16", "--beta", "0.5"])
     steps = [json.loads(x) for x in capsys.readouterr().out.splitlines() if x.startswith("{")]
     assert len(steps) == 6 and abs(steps[0]["pair_loss"] - 0.693) < 0.05 and steps[-1]["pair_loss"] < steps[0]["pair_loss"]
+
+
+def test_gpt2_checkpoint_is_served_on_the_training_kernels(tmp_path):
+    """A trained GPT-2-shape checkpoint through the serving interface on the GPU (recompute on the trainer's forward kernels)
+    against the fp32 oracle backend; then the same backend over a live trainer's buffers (on-policy sampling)."""
+    from openagents_b200.data import ByteBpe
+    from openagents_b200.serve.backend import open_backend
+    from openagents_b200.serve.generation import SamplingParams, Scheduler
+    from openagents_b200.serve.gpt2_backend import Gpt2CudaBackend
+    from openagents_b200.serve.server import load_tokenizer
+    from openagents_b200.train.trainer import Trainer, synthetic_batch
+    cfg = _small_cfg()
+    tr = Trainer(cfg, "cuda:0")
+    tok, tgt = synthetic_batch(cfg, tr.accum, 0, 0, "cuda:0")
+    tok, tgt = tok.cuda(), tgt.cuda()
+    for _ in range(3):
+        tr.train_step(tok, tgt)
+    bpe = ByteBpe.train(b"the cat sat on the mat " * 8, 20, special=["<|end|>"])
+    path = str(tmp_path / "tuned.gguf")
+    tr.export_gguf(path, tokenizer=bpe)
+    gpu, cpu = open_backend(path, "cuda", max_num_seqs=4), open_backend(path, "cpu")
+    assert type(gpu).__name__ == "Gpt2CudaBackend" and gpu.max_context == 64
+    seqs = {1: [5, 17, 200, 3, 42, 42, 9], 2: [7] * 30, 3: [999, 0, 1], 4: [11, 12], 5: [400, 500, 600, 700]}       # five sequences: two groups of rows
+    for b in (gpu, cpu):
+        for s, t in seqs.items():
+            b.begin(s, t)
+    a = gpu.forward(list(seqs), list(seqs.values()))
+    b = cpu.forward(list(seqs), list(seqs.values()))
+    assert a.shape == b.shape == (5, cfg.model.vocab)
+    assert (a - b).abs().max().item() < 0.08 * b.abs().max().item() + 0.05
+    la, lb = gpu.score(1, [8, 9, 10], [9, 10, -1]), cpu.score(1, [8, 9, 10], [9, 10, -1])
+    assert la[2] == 0.0 and max(abs(x - y) for x, y in zip(la, lb)) < 0.1
+    gpu.truncate(1, 7)
+    assert gpu.seq_len(1) == 7 and len(gpu.verify(1, [8, 9])) == 2
+    loaded, _ = load_tokenizer(path, cfg.model.vocab)
+    sch = Scheduler(open_backend(path, "cuda", max_num_seqs=4), loaded, max_num_seqs=4)
+    reqs = [sch.submit(loaded.encode("the cat"), SamplingParams(max_tokens=6)) for _ in range(3)]
+    sch.run_until_done(reqs)
+    assert all(1 <= len(r.output) <= 6 for r in reqs) and reqs[0].output == reqs[1].output        # greedy: same prompt, same answer
+    # on-policy: the backend reads the trainer's own buffers, so an optimizer step changes what it samples from
+    live = Gpt2CudaBackend.over_trainer(tr)
+    live.begin(1, [1, 2, 3])
+    before = live.forward([1], [[1, 2, 3]])
+    ref = open_backend(path, "cpu")
+    ref.begin(1, [1, 2, 3])
+    assert (before - ref.forward([1], [[1, 2, 3]])).abs().max().item() < 0.1
+    for _ in range(3):
+        tr.train_step(tok, tgt)
+    live.truncate(1, 0)
+    after = live.forward([1], [[1, 2, 3]])
+    assert (after - before).abs().max().item() > 1e-3
+    tr.check_status()
