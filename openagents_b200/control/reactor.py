@@ -13,7 +13,7 @@ Restates packages/reactor-contracts/src/index.ts: lanes and profiles :61-156, po
 receipts :258-333, evaluation :336-390, policy resolution :1106-1225, provisioning :1242-1305, routing :1317-1391, metering
 :1396-1444, harness profile :1454-1468, evaluation receipts and coverage :1476-1680.  Records are plain dicts with the
 reference's field names; ``ContractError`` replaces schema-decoding failures.  The need-to-know corpus rules and the
-data-liberation pipeline of that package are not ML and are not restated.
+data-liberation pipeline of that package are in ``control.reactor_data``.
 """
 from __future__ import annotations
 
