@@ -11,7 +11,8 @@ MEASURED evaluations.  The evaluation harness is owned by this engine's lane.
 
 Restates packages/reactor-contracts/src/index.ts: lanes and profiles :61-156, policy :194-255, install / route / metering
 receipts :258-333, evaluation :336-390, policy resolution :1106-1225, provisioning :1242-1305, routing :1317-1391, metering
-:1396-1444, harness profile :1454-1468, evaluation receipts and coverage :1476-1680.  Records are plain dicts with the
+:1396-1444, harness profile :1454-1468, evaluation receipts and coverage :1476-1680, air-gapped update bundles and
+install operations :1675-1811.  Records are plain dicts with the
 reference's field names; ``ContractError`` replaces schema-decoding failures.  The need-to-know corpus rules and the
 data-liberation pipeline of that package are in ``control.reactor_data``.
 """
@@ -317,3 +318,70 @@ def select_capability_copy_eval_refs(model_ref: str, task_class_refs, receipts: 
     return {"schemaVersion": "openagents.reactor.capability_copy_eval_decision.v1", "allowedEvalRefs": allowed, "blockerRefs": blockers,
             "decidedAt": decided_at, "decisionRef": decision_ref, "modelRef": model_ref, "sourceRefs": _unique([*allowed, *source_refs]),
             "status": "allowed" if not blockers else "blocked_not_measured", "taskClassRefs": tasks}
+
+
+# ---------------------------------------------------------------- air-gapped updates (index.ts:405-447 types, :1675-1811 builders)
+AIRGAP_VERIFIER_REF = "openagents_b200.control.reactor.verify_airgap_bundle"
+AIRGAP_PUBLIC_KEY_REF = "keys/release-pubkey.json"
+
+
+def airgap_update_bundle_manifest(profile: dict, bundle_ref: str, bundle_version: str, artifact_sha256: str, policy_ref: str, policy_version: str,
+                                  signature_kid: str, signature_ref: str, created_at: str, public_key_ref: str = AIRGAP_PUBLIC_KEY_REF,
+                                  verifier_ref: str = AIRGAP_VERIFIER_REF, source_refs=()) -> dict:
+    """What travels on the medium beside the artifact: which model for which node profile under which policy version, the
+    artifact's SHA-256, and where the detached ed25519 signature and its public key are.  Never needs a callback."""
+    _need(len(artifact_sha256) == 64 and all(c in "0123456789abcdef" for c in artifact_sha256), "reactor.airgap.artifact_sha256")
+    return {"schemaVersion": "openagents.reactor.airgap_update_bundle_manifest.v1", "artifactSha256": artifact_sha256, "bundleRef": bundle_ref,
+            "bundleVersion": bundle_version, "callbackRequired": False, "createdAt": created_at, "modelRef": profile["modelRef"],
+            "nodeProfileRef": profile["nodeProfileRef"], "policyRef": policy_ref, "policyVersion": policy_version, "publicKeyRef": public_key_ref,
+            "signatureAlg": "ed25519", "signatureKid": signature_kid, "signatureRef": signature_ref,
+            "sourceRefs": _unique([profile["nodeProfileRef"], signature_ref, public_key_ref, verifier_ref, *source_refs]), "verifierRef": verifier_ref}
+
+
+def verify_airgap_bundle(bundle: dict, artifact: bytes, signature: bytes, public_key: bytes) -> list[str]:
+    """Offline check of a bundle on the node: the artifact hashes to what the manifest says and the detached signature over
+    that digest verifies under the given ed25519 public key (32 raw bytes).  Returns blocker refs (empty = verified)."""
+    import hashlib
+    out = []
+    if hashlib.sha256(artifact).hexdigest() != bundle["artifactSha256"]:
+        out.append("blocker.reactor.airgap_update.artifact_digest_mismatch")
+    try:
+        from cryptography.exceptions import InvalidSignature
+        from cryptography.hazmat.primitives.asymmetric.ed25519 import Ed25519PublicKey
+        try:
+            Ed25519PublicKey.from_public_bytes(public_key).verify(signature, bytes.fromhex(bundle["artifactSha256"]))
+        except (InvalidSignature, ValueError):
+            out.append("blocker.reactor.airgap_update.signature_invalid")
+    except ImportError:                                      # no ed25519 implementation on this node: fail closed
+        out.append("blocker.reactor.airgap_update.signature_unverifiable")
+    return out
+
+
+def install_ops_receipt(action: str, bundle: dict, catalog: dict, policy: dict, profile: dict, decided_at: str, receipt_ref: str,
+                        rollback_from_bundle_ref: str | None = None, rollback_to_bundle_ref: str | None = None, verification_blockers=(),
+                        source_refs=()) -> dict:
+    """Fresh install, upgrade or rollback from a bundle: the bundle must be bound to this profile and this policy version, the
+    policy is re-validated against the catalogue at install time (a model the policy no longer admits is refused before any
+    weights move), and the offline verification (``verify_airgap_bundle``) must have found nothing."""
+    _need(action in ("fresh_install", "upgrade", "rollback"), "reactor.install_ops.unknown_action")
+    inst = provision_model(catalog, policy, profile, "install" if action == "fresh_install" else "upgrade",
+                           [bundle["bundleRef"], f"sha256:{bundle['artifactSha256']}"], decided_at, f"{receipt_ref}.policy_decision",
+                           f"{receipt_ref}.model_install", [bundle["bundleRef"], *source_refs])
+    blockers = list(verification_blockers)
+    if bundle.get("callbackRequired") is not False:
+        blockers.append("blocker.reactor.airgap_update.callback_required")
+    if not (bundle["nodeProfileRef"] == profile["nodeProfileRef"] and bundle["modelRef"] == profile["modelRef"]):
+        blockers.append("blocker.reactor.airgap_update.profile_binding_mismatch")
+    if not (bundle["policyRef"] == policy["policyRef"] and bundle["policyVersion"] == policy["version"]):
+        blockers.append("blocker.reactor.airgap_update.policy_binding_mismatch")
+    if inst["status"] != "installed":
+        blockers += ["blocker.reactor.install_ops.policy_revalidation_failed", *(inst["refusal"] or {}).get("blockerRefs", [])]
+    blockers = _unique(blockers)
+    rb = action == "rollback"
+    return {"schemaVersion": "openagents.reactor.install_ops_receipt.v1", "action": action, "blockerRefs": blockers, "bundleRef": bundle["bundleRef"],
+            "decidedAt": decided_at, "modelInstallReceiptRef": inst["receiptRef"], "modelRef": profile["modelRef"], "nodeProfileRef": profile["nodeProfileRef"],
+            "policyDecisionRef": inst["policyDecisionRef"], "policyRef": policy["policyRef"], "policyVersion": policy["version"], "receiptRef": receipt_ref,
+            "rollbackFromBundleRef": rollback_from_bundle_ref if rb else None, "rollbackToBundleRef": (rollback_to_bundle_ref or bundle["bundleRef"]) if rb else None,
+            "sourceRefs": _unique([bundle["bundleRef"], bundle["signatureRef"], inst["receiptRef"], inst["policyDecisionRef"], *source_refs]),
+            "status": "refused" if blockers else "succeeded",
+            "verificationRefs": _unique([bundle["verifierRef"], bundle["publicKeyRef"], bundle["signatureRef"], inst["policyDecisionRef"]])}

@@ -104,3 +104,42 @@ def test_metering_and_evaluation_against_a_served_model(tmp_path):
     with pytest.raises(rx.ContractError):
         rx.eval_coverage_matrix(cat, [e1, dict(e1, receiptRef="dup")], "m", T0)
     model.close()
+
+
+def test_airgap_bundle_is_verified_offline_and_install_ops_revalidates_policy():
+    import hashlib
+    from cryptography.hazmat.primitives import serialization
+    from cryptography.hazmat.primitives.asymmetric.ed25519 import Ed25519PrivateKey
+    cat = _catalog()
+    pol = rx.model_policy("policy.us_only", "v3", "owner.acme", {"allowOriginJurisdictions": ["US"]})
+    prof = rx.node_model_profile("node.rx3.1", "model.us.open", "US Open 8B", pol)
+    artifact = b"weights and runtime" * 100
+    digest = hashlib.sha256(artifact).hexdigest()
+    key = Ed25519PrivateKey.generate()
+    pub = key.public_key().public_bytes(serialization.Encoding.Raw, serialization.PublicFormat.Raw)
+    sig = key.sign(bytes.fromhex(digest))
+    b = rx.airgap_update_bundle_manifest(prof, "bundle.rx3.2026_07", "2026.07.1", digest, "policy.us_only", "v3", "kid.release.1", "sig.bundle.2026_07", T0)
+    assert b["callbackRequired"] is False and b["signatureAlg"] == "ed25519" and b["modelRef"] == "model.us.open"
+    assert rx.verify_airgap_bundle(b, artifact, sig, pub) == []
+    assert rx.verify_airgap_bundle(b, artifact + b"x", sig, pub) == ["blocker.reactor.airgap_update.artifact_digest_mismatch"]
+    assert rx.verify_airgap_bundle(b, artifact, sig[:-1] + bytes([sig[-1] ^ 1]), pub) == ["blocker.reactor.airgap_update.signature_invalid"]
+    ok = rx.install_ops_receipt("fresh_install", b, cat, pol, prof, T0, "receipt.ops.1", verification_blockers=rx.verify_airgap_bundle(b, artifact, sig, pub))
+    assert ok["status"] == "succeeded" and ok["blockerRefs"] == [] and ok["rollbackToBundleRef"] is None and "sig.bundle.2026_07" in ok["verificationRefs"]
+    rb = rx.install_ops_receipt("rollback", b, cat, pol, prof, T0, "receipt.ops.2", rollback_from_bundle_ref="bundle.rx3.2026_08")
+    assert rb["status"] == "succeeded" and rb["rollbackFromBundleRef"] == "bundle.rx3.2026_08" and rb["rollbackToBundleRef"] == "bundle.rx3.2026_07"
+    # the policy moved on since the bundle was cut; a bundle for another node; a tampered artifact; a model the policy refuses
+    v4 = rx.model_policy("policy.us_only", "v4", "owner.acme", {"allowOriginJurisdictions": ["US"]})
+    prof4 = rx.node_model_profile("node.rx3.1", "model.us.open", "US Open 8B", v4)
+    stale = rx.install_ops_receipt("upgrade", b, cat, v4, prof4, T0, "receipt.ops.3")
+    assert stale["status"] == "refused" and stale["blockerRefs"] == ["blocker.reactor.airgap_update.policy_binding_mismatch"]
+    other = rx.node_model_profile("node.rx3.9", "model.us.open", "US Open 8B", pol)
+    assert "blocker.reactor.airgap_update.profile_binding_mismatch" in rx.install_ops_receipt("upgrade", b, cat, pol, other, T0, "receipt.ops.4")["blockerRefs"]
+    tampered = rx.install_ops_receipt("upgrade", b, cat, pol, prof, T0, "receipt.ops.5", verification_blockers=rx.verify_airgap_bundle(b, b"other", sig, pub))
+    assert tampered["status"] == "refused" and tampered["blockerRefs"] == ["blocker.reactor.airgap_update.artifact_digest_mismatch"]
+    cn = rx.node_model_profile("node.rx3.2", "model.cn.open", "CN Open", pol)
+    bcn = rx.airgap_update_bundle_manifest(cn, "bundle.cn", "1", digest, "policy.us_only", "v3", "kid", "sig.cn", T0)
+    refused = rx.install_ops_receipt("fresh_install", bcn, cat, pol, cn, T0, "receipt.ops.6")
+    assert refused["status"] == "refused" and "blocker.reactor.install_ops.policy_revalidation_failed" in refused["blockerRefs"]
+    assert "reactor.policy.origin_not_allowed" in refused["blockerRefs"]
+    with pytest.raises(rx.ContractError):
+        rx.airgap_update_bundle_manifest(prof, "b", "1", "nothex", "p", "v", "k", "s", T0)
