@@ -85,6 +85,27 @@ def verify_freivalds_merkle(payload: dict, challenge_ref: str = "challenge.local
                    {"fieldModulus": p, "rowOpeningCount": len(openings)})
 
 
+def freivalds_check_cuda(left, right, claimed, r, p: int = DEFAULT_MODULUS, exact: bool = False, device="cuda:0") -> dict:
+    """The arithmetic of ``verify_freivalds_merkle`` on the GPU for matrices too large to check comfortably on the host:
+    ``A (B r) == C r (mod p)`` with three exact mat-vecs and, with ``exact``, the full product.  Inputs are integer arrays
+    of residues in ``[0, p)``; the answer is bit-identical to the host check (``matvec_mod`` / ``matmul_mod``)."""
+    import torch
+    from ..ops import cuda_ops as ops
+    if not 2 <= p <= 2 ** 31 - 1:
+        raise ValueError("the device check needs a modulus below 2^31")
+    A, B, C, rv = (torch.as_tensor(np.asarray(a, dtype=np.int64)).to(torch.int32).to(device).contiguous() for a in (left, right, claimed, r))
+    if A.shape[1] != B.shape[0] or C.shape != (A.shape[0], B.shape[1]) or rv.numel() != C.shape[1]:
+        return {"verified": False, "code": "DimensionMismatch", "mismatchedRows": None}
+    lhs = ops.modp_matvec(A, ops.modp_matvec(B, rv, p), p)
+    rhs = ops.modp_matvec(C, rv, p)
+    bad = int(ops.count_mismatch(lhs, rhs).item())
+    out = {"verified": bad == 0, "code": None if bad == 0 else "FreivaldsMismatch", "mismatchedRows": bad}
+    if exact and bad == 0:
+        cells = int(ops.count_mismatch(ops.modp_matmul(A, B, p), C).item())
+        out.update(verified=cells == 0, code=None if cells == 0 else "FreivaldsMismatch", mismatchedCells=cells)
+    return out
+
+
 def verify_deterministic_recompute(payload: dict, challenge_ref: str = "challenge.local") -> Verdict:
     expected = payload.get("expectedDigestRef", payload.get("outputDigestRef"))
     actual = payload.get("recomputedDigestRef")

@@ -53,6 +53,9 @@ _SIGS = {
     "b200_transpose_bf16": [_P, _P, c_int, c_int, _P],
     "b200_qgemm": [c_int, _P, _P, c_int, c_int, _P, c_int, c_int, _P, _P, c_int, _P, c_int, c_int, _P, _P],
     "b200_decode_advance": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, _P, c_int, _P],
+    "b200_modp_matvec": [_P, _P, _P, c_int, c_int, ctypes.c_uint, _P],
+    "b200_modp_matmul": [_P, _P, _P, c_int, c_int, c_int, ctypes.c_uint, _P],
+    "b200_count_mismatch": [_P, _P, c_size_t, _P, _P],
 }
 
 _lib = None
@@ -292,3 +295,25 @@ def moe_gemm(A, B, groups, group_rows, N, K, counts, mode, out_bf16=None, ldc=0,
 
 def moe_zero(t):
     _check(lib().b200_moe_zero(_p(t), t.numel(), _st()), "moe_zero")
+
+
+# ---- exact arithmetic over a prime field (training verification): residues are int32 tensors with values in [0, p), p < 2^31
+def modp_matvec(A, x, p: int):
+    rows, cols = A.shape
+    y = torch.empty(rows, dtype=torch.int32, device=A.device)
+    _check(lib().b200_modp_matvec(_p(A), _p(x), _p(y), rows, cols, p, _st()), "modp_matvec")
+    return y
+
+
+def modp_matmul(A, B, p: int):
+    n, k = A.shape
+    m = B.shape[1]
+    C = torch.empty((n, m), dtype=torch.int32, device=A.device)
+    _check(lib().b200_modp_matmul(_p(A), _p(B), _p(C), n, k, m, p, _st()), "modp_matmul")
+    return C
+
+
+def count_mismatch(a, b) -> torch.Tensor:
+    out = torch.zeros(1, dtype=torch.int32, device=a.device)
+    _check(lib().b200_count_mismatch(_p(a), _p(b), a.numel(), _p(out), _st()), "count_mismatch")
+    return out

@@ -714,3 +714,36 @@ def test_matvec_with_rotary_and_cache_write(t, nb, hd):
     assert torch.allclose(kc1.float(), kc0.float(), atol=2e-3, rtol=2e-3)
     assert float(q0.abs().max()) > 0 and float(kc0.abs().max()) > 0
     assert torch.equal(kc1 == 0, kc0 == 0)                    # exactly the same cache slots were written
+
+
+def test_freivalds_arithmetic_on_the_device_is_exact():
+    """The prime-field kernels of training verification against the host arithmetic: bit-identical mat-vec and product, a
+    correct product verifies, a single wrong cell is caught by the random challenge, a compensated error only by the exact check."""
+    import numpy as np
+    from openagents_b200.control.verification import DEFAULT_MODULUS, freivalds_check_cuda, matmul_mod, matvec_mod
+    ops = _ops()
+    p = DEFAULT_MODULUS
+    rng = np.random.default_rng(0)
+    n, k, m = 70, 533, 45
+    A, B = rng.integers(0, p, (n, k)), rng.integers(0, p, (k, m))
+    A[0, :] = p - 1                                           # the largest residues: products near 2^62
+    B[:, 0] = p - 1
+    r = rng.integers(0, p, m)
+    C = matmul_mod(A, B, p)
+    dev = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int64)).to(torch.int32).cuda()
+    assert np.array_equal(ops.modp_matvec(dev(B), dev(r), p).cpu().numpy().astype(np.int64), matvec_mod(B, r, p))
+    assert np.array_equal(ops.modp_matmul(dev(A), dev(B), p).cpu().numpy().astype(np.int64), C)
+    assert freivalds_check_cuda(A, B, C, r, p, exact=True) == {"verified": True, "code": None, "mismatchedRows": 0, "mismatchedCells": 0}
+    wrong = C.copy()
+    wrong[3, 7] = (wrong[3, 7] + 1) % p
+    got = freivalds_check_cuda(A, B, wrong, r, p)
+    assert got["verified"] is False and got["mismatchedRows"] == 1 and got["code"] == "FreivaldsMismatch"
+    # an error the challenge cannot see (it lies in the null space of r): only the exact product catches it
+    r2 = r.copy()
+    r2[5] = 0
+    sneaky = C.copy()
+    sneaky[9, 5] = (sneaky[9, 5] + 12345) % p
+    assert freivalds_check_cuda(A, B, sneaky, r2, p)["verified"] is True
+    ex = freivalds_check_cuda(A, B, sneaky, r2, p, exact=True)
+    assert ex["verified"] is False and ex["mismatchedCells"] == 1
+    assert freivalds_check_cuda(A, B[:-1], C, r, p)["code"] == "DimensionMismatch"
