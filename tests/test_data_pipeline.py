@@ -133,3 +133,32 @@ def test_bpe_with_pieces_and_special_tokens():
     assert again.encode("The lazy fox") == bpe.encode("The lazy fox")
     with pytest.raises(ValueError):
         ByteBpe([(300, 1)])
+
+
+def test_native_bpe_equals_the_plain_loop_on_random_low_entropy_text():
+    """Small alphabets make overlapping pairs ("aaaa"), ties and merges of merges common: the incremental trainer and the
+    rank-ordered encoder must still agree with the loop that recounts every pair after every merge."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=150, deadline=None)
+    @given(st.binary(min_size=0, max_size=120).map(lambda b: bytes(97 + (x % 3) for x in b)), st.integers(min_value=0, max_value=25))
+    def check(data, merges):
+        want = bpe_train(data, merges)
+        bpe = ByteBpe.train(data, merges, pieces="none")
+        assert bpe.merges == [(a, b) for a, b, _ in want["merges"]]
+        assert bpe.encode(data) == want["tokenIds"]
+        assert bpe.decode_bytes(bpe.encode(data)) == data
+
+    check()
+
+
+def test_loader_with_every_slot_and_thread_count_delivers_the_same_stream(tmp_path):
+    paths, _ = _shards(tmp_path, sizes=(3000,))
+    ds = TokenDataset(paths, seq_len=8)
+    ref = None
+    for slots, threads in ((2, 1), (2, 4), (3, 2), (5, 3), (8, 8)):
+        ld = BatchLoader(ds, accum=1, micro_batch=5, seed=4, slots=slots, threads=threads, pin=False)
+        got = [ld.next()[0].clone() for _ in range(40)]
+        ld.close()
+        ref = ref or got
+        assert all(torch.equal(a, b) for a, b in zip(got, ref)), (slots, threads)
