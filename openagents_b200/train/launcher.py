@@ -39,6 +39,10 @@ def parse(argv=None):
     ap.add_argument("--betas", type=float, nargs=2, default=(0.9, 0.95))
     ap.add_argument("--wd", type=float, default=0.1)
     ap.add_argument("--clip", type=float, default=1.0)
+    ap.add_argument("--schedule", default="cosine", choices=["cosine", "wsd", "constant"], help="learning-rate schedule over --total-steps")
+    ap.add_argument("--total-steps", type=int, default=0, help="length of the schedule (0 = constant after warm-up)")
+    ap.add_argument("--warmup-steps", type=int, default=0)
+    ap.add_argument("--decay-fraction", type=float, default=0.2, help="wsd: share of the run spent decaying")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--ckpt-dir", default="")
     ap.add_argument("--resume", default="")
@@ -86,7 +90,8 @@ def worker(args):
         model = model.with_(n_layers=args.layers)
     cfg = TrainConfig(model=model, global_batch=args.global_batch, micro_batch=args.micro_batch, seq_len=args.seq_len,
                       lr=args.lr, betas=tuple(args.betas), weight_decay=args.wd, grad_clip=args.clip, seed=args.seed,
-                      zero_stage=args.zero_stage)
+                      zero_stage=args.zero_stage, schedule=args.schedule, total_steps=args.total_steps, warmup_steps=args.warmup_steps,
+                      decay_fraction=args.decay_fraction)
     if args.sync_profile == "diloco":
         return diloco_worker(args, cfg, dev, rank, world)
     if args.lane == "sft":

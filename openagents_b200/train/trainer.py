@@ -45,10 +45,35 @@ class TrainConfig:
     grad_clip: float = 1.0
     warmup_steps: int = 0
     total_steps: int = 0             # 0 = constant learning rate after warm-up
+    schedule: str = "cosine"         # cosine | wsd (warm-up, stable, then a linear decay over the last decay_fraction of the run) | constant
+    decay_fraction: float = 0.2      # wsd: share of total_steps spent decaying
+    min_lr_ratio: float = 0.1        # floor of both schedules, as a share of lr
     seed: int = 0
     zero_stage: int = 2
     overlap_grad_reduce: bool = True  # reduce-scatter each layer's gradients while the backward of the layers below it runs
     overlap_param_gather: bool = True  # AdamW + parameter all-gather in per-layer chunks; the next forward waits chunk by chunk
+
+
+def lr_schedule(c: TrainConfig, step: int) -> float:
+    """Learning rate of optimizer step ``step`` (0-based).  ``cosine``: linear warm-up, then half a cosine from ``lr`` to the
+    floor over the rest of ``total_steps``.  ``wsd`` (warm-up / stable / decay, the one-delta schedule ablation the reference
+    dispatched: training-ablation-derisking-ledger.ts:290-310): constant ``lr`` until the last ``decay_fraction`` of the run,
+    then linear to the floor, which lets a run be extended or branched from any point of the stable phase."""
+    if c.schedule not in ("cosine", "wsd", "constant"):
+        raise ValueError(f"unknown schedule {c.schedule!r}")
+    if c.warmup_steps and step < c.warmup_steps:
+        return c.lr * (step + 1) / c.warmup_steps
+    if not c.total_steps or c.schedule == "constant":
+        return c.lr
+    floor = c.min_lr_ratio
+    if c.schedule == "wsd":
+        start = c.total_steps - max(1, int(round(c.total_steps * c.decay_fraction)))
+        if step < start:
+            return c.lr
+        t = min(1.0, (step - start + 1) / max(1, c.total_steps - start))
+        return c.lr * (1.0 - (1.0 - floor) * t)
+    t = min(1.0, (step - c.warmup_steps) / max(1, c.total_steps - c.warmup_steps))
+    return c.lr * (floor + (1.0 - floor) * 0.5 * (1.0 + math.cos(math.pi * t)))
 
 
 class Trainer:
@@ -116,13 +141,7 @@ class Trainer:
         del full
 
     def lr_at(self, step: int) -> float:
-        c = self.cfg
-        if c.warmup_steps and step < c.warmup_steps:
-            return c.lr * (step + 1) / c.warmup_steps
-        if c.total_steps:
-            t = min(1.0, (step - c.warmup_steps) / max(1, c.total_steps - c.warmup_steps))
-            return c.lr * (0.1 + 0.9 * 0.5 * (1.0 + math.cos(math.pi * t)))
-        return c.lr
+        return lr_schedule(self.cfg, step)
 
     # ---- one optimizer step over `accum` micro-batches.  tokens/targets: [accum, micro_batch, seq_len]
     @nvtx_method("train.forward_backward")

@@ -121,3 +121,17 @@ def test_lane_report_and_resume_drill(tmp_path):
     assert rep["corpus"]["manifestDigest"] == c.manifest["manifestDigest"] and rep["reportDigest"].startswith("sha256:")
     with pytest.raises(ValueError):
         sft.run_lane(lambda: None, lambda s: None, steps=4, checkpoint_at=4, ckpt_dir="x", corpus_manifest=c.manifest)
+
+
+def test_trainer_schedules_cosine_wsd_constant():
+    from openagents_b200.train.trainer import TrainConfig, lr_schedule
+    cos = TrainConfig(lr=1.0, warmup_steps=2, total_steps=10)
+    assert [round(lr_schedule(cos, s), 4) for s in (0, 1, 2, 6, 10, 50)] == [0.5, 1.0, 1.0, 0.55, 0.1, 0.1]
+    assert lr_schedule(cos, 6) == pytest.approx(sft.cosine_lr(6, 10, 1.0, 1000, warmup_steps=2))
+    wsd = TrainConfig(lr=1.0, warmup_steps=2, total_steps=20, schedule="wsd", decay_fraction=0.25)
+    lrs = [lr_schedule(wsd, s) for s in range(22)]
+    assert lrs[0] == 0.5 and all(x == 1.0 for x in lrs[1:15]) and lrs[15] < 1.0 and lrs[19] == pytest.approx(0.1) and lrs[21] == pytest.approx(0.1)
+    assert all(a > b for a, b in zip(lrs[14:19], lrs[15:20]))                      # strictly decreasing through the decay phase
+    assert lr_schedule(TrainConfig(lr=2.0, total_steps=10, schedule="constant"), 7) == 2.0 and lr_schedule(TrainConfig(lr=2.0), 99) == 2.0
+    with pytest.raises(ValueError):
+        lr_schedule(TrainConfig(schedule="step"), 0)
