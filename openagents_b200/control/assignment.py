@@ -198,3 +198,82 @@ def run_local_inference_assignment(lease_obj, model_rows, complete, post, now=ti
     run.progress("closeout-submitted", "Closeout submitted.", tokens_so_far=total, last_event="closeout")
     return {"accepted": True, "closeout": run.closeout("accepted", receipt_refs=receipts, result_refs=[digest],
                                                        summary_refs=[f"summary.tokens.exact.{total}"]), "usage": usage}
+
+
+# ---------------------------------------------------------------- executor-trace assignments (assignment.ts:678-790)
+TASSADAR_TRACE_JOB_KINDS = ("tassadar_executor_trace", "tassadar_executor_trace_homework")      # packages/tassadar-executor/src/lane.ts:4-6
+
+
+def tassadar_payload_from(assignment) -> dict | None:
+    """The embedded workload of an executor-trace lease, or None when the lease is something else.  The dispatch renames
+    the model's ``seed_writes`` to ``initialChannelWrites`` so that it passes the public-projection scanner; the executor's
+    own field name is restored here."""
+    if not isinstance(assignment, dict) or assignment.get("kind") not in TASSADAR_TRACE_JOB_KINDS:
+        return None
+    t = assignment.get("tassadar")
+    if not isinstance(t, dict) or "model" not in t or not isinstance(t.get("steps"), list):
+        return None
+    model = t["model"]
+    if isinstance(model, dict) and "seed_writes" not in model and "initialChannelWrites" in model:
+        model = {k: v for k, v in model.items() if k != "initialChannelWrites"}
+        model["seed_writes"] = t["model"]["initialChannelWrites"]
+        t = {**t, "model": model}
+    return t
+
+
+def execute_tassadar_assignment(lease: dict, now=time.time) -> dict | None:
+    """Run the lease's digest-pinned numeric-model workload on this node and report what it computed: accepted when the
+    trace digest equals the dispatched expectation (or none was given), rejected on a mismatch or when the executor refuses
+    the model.  Exact-replay verification is a validator's job on another device; this only reports."""
+    import hashlib
+    from ..oracle import tassadar as tz
+    payload = tassadar_payload_from(lease.get("codingAssignment"))
+    if payload is None:
+        return None
+
+    def ref(prefix, text):
+        return f"{prefix}.{hashlib.sha256(text.encode()).hexdigest()[:24]}"
+
+    run_ref = ref("run.pylon.tassadar_executor_trace", f"{lease['leaseRef']}:{payload.get('fixtureId', 'workload')}:{_iso(now())}")
+    try:
+        trace = tz.execute_numeric_model(payload["model"], payload["steps"])
+    except Exception as e:      # noqa: BLE001 - a typed refusal of the model (window overflow, malformed wiring) becomes a rejected closeout
+        fail = ref("proof.pylon.tassadar_executor_trace.refused", f"{lease['leaseRef']}:{type(e).__name__}:{e}")
+        return {"artifactRefs": [], "blockerRefs": ["blocker.assignment.tassadar_execution_refused"], "buildRefs": [run_ref],
+                "message": "Tassadar executor-trace workload refused with a typed execution error.", "previewRefs": [], "proofRefs": [fail],
+                "resultRefs": ["result.tassadar_poc.execution_refused"], "runRefs": [run_ref], "status": "rejected",
+                "summaryRefs": ["summary.tassadar_poc.execution_refused"], "testRefs": [fail]}
+    out = tz.collect_interpreter_outputs(trace["stepOutputs"])
+    digest = trace["traceDigest"]
+    want = payload.get("expectedTraceDigest")
+    ok = want is None or want == digest
+    halted = "true" if out["halted"] else "false"
+    proof = ref("proof.pylon.tassadar_executor_trace", f"{lease['assignmentRef']}:{digest}:{trace['stepCount']}")
+    msg = (f"Tassadar executor-trace workload executed: {trace['stepCount']} steps, halted={halted}, {len(out['outputs'])} output(s), trace digest "
+           f"{digest[:16]}... matches the dispatched expectation." if ok else
+           "Tassadar executor-trace workload executed but the trace digest does not match the dispatched expectation.")
+    return {"artifactRefs": [f"artifact.tassadar_poc.trace_digest.{digest}"], "blockerRefs": [] if ok else ["blocker.assignment.tassadar_trace_digest_mismatch"],
+            "buildRefs": [run_ref], "message": bounded_progress_message(msg), "previewRefs": [], "proofRefs": [proof],
+            "resultRefs": [f"result.tassadar_poc.trace_digest.{digest}", f"result.tassadar_poc.step_count.{trace['stepCount']}", f"result.tassadar_poc.halted.{halted}"],
+            "runRefs": [run_ref], "status": "accepted" if ok else "rejected",
+            "summaryRefs": ["summary.tassadar_poc.trace_digest_match" if ok else "summary.tassadar_poc.trace_digest_mismatch"], "testRefs": [proof]}
+
+
+def run_tassadar_assignment(lease_obj, post, now=time.time, node_capability_refs=()) -> dict:
+    """Lease -> admission (the executor capability must be advertised WITH its self-test receipt) -> accept -> run -> closeout."""
+    from ..oracle import tassadar as tz
+    lease = decode_lease(lease_obj)
+    run = AssignmentRun(lease, post, now)
+    adm = compute_admission(lease, [], now(), node_capability_refs)
+    if tz.CAPABILITY_REF in lease["capabilityRefs"] and not tz.has_receipted_capability(list(node_capability_refs)):
+        adm = {**adm, "admitted": False, "blockerRefs": unique_refs([*adm["blockerRefs"], "blocker.assignment.tassadar_capability_unreceipted"])}
+    acc = run.accept(adm)
+    if not acc["accepted"]:
+        return {"accepted": False, "acceptance": acc}
+    run.progress("running", "Executor-trace workload started.", last_event="runtime_started")
+    res = execute_tassadar_assignment(lease, now)
+    if res is None:
+        return {"accepted": True, "closeout": run.closeout("rejected", extra_blockers=["blocker.assignment.tassadar_payload_missing"])}
+    run.progress("proof-ready", res["message"], artifact_refs=res["artifactRefs"], proof_refs=res["proofRefs"], last_event="trace_digest_ready")
+    return {"accepted": True, "execution": res,
+            "closeout": run.closeout(res["status"], result_refs=res["resultRefs"], summary_refs=res["summaryRefs"], extra_blockers=res["blockerRefs"])}

@@ -101,3 +101,39 @@ def test_full_loop_on_the_local_model_server(tmp_path):
     n = len(sent)
     assert run.closeout("accepted") is first and len(sent) == n          # idempotent
     model.close()
+
+
+def test_executor_trace_assignment_runs_the_pinned_workload():
+    import json
+    import os
+    from openagents_b200.control import assignment as asg
+    from openagents_b200.oracle import tassadar as tz
+    g = json.load(open(os.path.join(os.path.dirname(__file__), "data", "tassadar_loop_sum_golden.json")))
+    model = dict(g["model"])
+    transit = {k: v for k, v in model.items() if k != "seed_writes"}
+    transit["initialChannelWrites"] = model["seed_writes"]
+    receipt = tz.run_self_test({"fixtureId": "loop_sum", "model": g["model"], "steps": g["steps"], "expectedTraceDigest": g["expectedTraceDigest"],
+                                "expectedModelDigest": "0" * 64})
+    caps = [tz.CAPABILITY_REF, receipt["receiptRef"]]
+
+    def lease(expected, kind="tassadar_executor_trace", m=transit):
+        return {"schema": asg.LEASE_SCHEMA, "assignmentRef": "assignment.tz.1", "leaseRef": "lease.tz.1", "goal": "replay the pinned workload",
+                "paymentMode": "no-spend", "capabilityRefs": [tz.CAPABILITY_REF], "expiresAt": "2099-01-01T00:00:00Z",
+                "codingAssignment": {"kind": kind, "tassadar": {"fixtureId": "loop_sum", "model": m, "steps": g["steps"], **({"expectedTraceDigest": expected} if expected else {})}}}
+    posts = []
+    out = asg.run_tassadar_assignment(lease(g["expectedTraceDigest"]), lambda k, b: posts.append((k, b)), node_capability_refs=caps)
+    assert out["accepted"] and out["closeout"]["status"] == "accepted" and out["closeout"]["blockerRefs"] == []
+    assert f"result.tassadar_poc.trace_digest.{g['expectedTraceDigest']}" in out["closeout"]["resultRefs"]
+    assert out["execution"]["summaryRefs"] == ["summary.tassadar_poc.trace_digest_match"] and [k for k, _ in posts] == ["acceptance", "progress", "progress", "closeout"]
+    bad = asg.run_tassadar_assignment(lease("0" * 64), lambda k, b: None, node_capability_refs=caps)
+    assert bad["closeout"]["status"] == "rejected" and bad["closeout"]["blockerRefs"] == ["blocker.assignment.tassadar_trace_digest_mismatch"]
+    assert bad["closeout"]["payoutClaimAllowed"] is False
+    # the capability without its self-test receipt is not admitted; another kind of lease is not this runner's
+    unreceipted = asg.run_tassadar_assignment(lease(None), lambda k, b: None, node_capability_refs=[tz.CAPABILITY_REF])
+    assert not unreceipted["accepted"] and "blocker.assignment.tassadar_capability_unreceipted" in unreceipted["acceptance"]["blockerRefs"]
+    assert asg.tassadar_payload_from({"kind": "coding", "tassadar": {}}) is None
+    assert asg.tassadar_payload_from(lease(None)["codingAssignment"])["model"]["seed_writes"] == model["seed_writes"]
+    broken = dict(transit)
+    broken.pop(next(k for k in broken if k not in ("initialChannelWrites", "graph_digest")))
+    refused = asg.execute_tassadar_assignment(asg.decode_lease(lease(None, m=broken)))
+    assert refused["status"] == "rejected" and refused["blockerRefs"] == ["blocker.assignment.tassadar_execution_refused"]
