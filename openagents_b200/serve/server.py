@@ -99,6 +99,37 @@ class ServedModel:
                 self.waiters -= 1
         return r
 
+    _score_ids = 1 << 50
+
+    def token_logprobs(self, context_ids, output_ids) -> list[float]:
+        """Natural-log probability of each generated token given everything before it: one extra forward over
+        ``context + output`` in a sequence of its own, between two scheduler steps (the ``logprobs`` option of a completed,
+        non-streamed request)."""
+        if not getattr(self.backend, "supports_score", False):
+            raise RequestRejected(f"the {self.backend.name} backend cannot report log-probabilities")
+        if not output_ids:
+            return []
+        ctx, out = list(context_ids), list(output_ids)
+        feed = ctx + out[:-1]
+        targets = [-1] * (len(ctx) - 1) + out
+        with self._wl:
+            self.waiters += 1
+            ServedModel._score_ids += 1
+            sid = ServedModel._score_ids
+        try:
+            with self.cv:
+                cached = self.backend.begin(sid, feed)
+                try:
+                    if cached:
+                        self.backend.truncate(sid, 0)
+                    lp = self.backend.score(sid, feed, targets)
+                finally:
+                    self.backend.end(sid)
+        finally:
+            with self._wl:
+                self.waiters -= 1
+        return lp[len(ctx) - 1:]
+
     def generate(self, prompt_ids, params, seq_id=None, keep=False, on_token=None, history=None) -> Request:
         """Blocking completion.  ``on_token`` is called on THIS thread (tokens cross from the scheduling thread through
         a queue), so a slow client socket never stalls the decode loop."""
@@ -385,6 +416,9 @@ def make_handler(state: ServerState):
                      json.dumps(m.get("tool_calls") or m.get("content") or "")} for m in msgs]
             cid = "chatcmpl-" + uuid.uuid4().hex[:24]
             created = int(time.time())
+            want_lp = bool(body.get("logprobs"))
+            if want_lp and (body.get("stream") or int(body.get("top_logprobs") or 0) > 0):
+                return self._err(400, "logprobs are reported for non-streamed completions, for the chosen tokens only (top_logprobs must be 0)")
             if body.get("stream"):
                 self.send_response(200)
                 self.send_header("Content-Type", "text/event-stream")
@@ -437,8 +471,18 @@ def make_handler(state: ServerState):
                 return self._err(422, str(e), e.kind)
             if finish == "stop":
                 finish = r.finish_reason
+            choice = {"index": 0, "message": msg, "finish_reason": finish}
+            if want_lp:
+                try:
+                    lps = model.token_logprobs(list(r.history) + list(r.prompt), r.output)
+                except RequestRejected as e:
+                    return self._err(400, str(e))
+                dec = getattr(model.tok, "decode_bytes", None)
+                choice["logprobs"] = {"content": [{"token": model.tok.decode([t]), "logprob": lp,
+                                                   "bytes": list(dec([t])) if dec else list(model.tok.decode([t]).encode()), "top_logprobs": []}
+                                                  for t, lp in zip(r.output, lps)]}
             self._json(200, {"id": cid, "object": "chat.completion", "created": created, "model": model.id,
-                             "choices": [{"index": 0, "message": msg, "finish_reason": finish}], "usage": usage,
+                             "choices": [choice], "usage": usage,
                              "timings": {"ttft_ms": None if r.ttft_s is None else round(r.ttft_s * 1e3, 3),
                                          "predicted_per_second": (len(r.output) - 1) / (r.t_done - r.t_first_token)
                                          if r.t_done and r.t_first_token and len(r.output) > 1 and r.t_done > r.t_first_token else None}})

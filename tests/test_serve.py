@@ -421,3 +421,35 @@ def test_speculation_is_disclosed_per_request(gguf_path):
     assert "speculation" not in ServerState([plain]).complete(plain, msgs, {"max_tokens": 4})[1]
     model.close()
     plain.close()
+
+
+def test_logprobs_of_the_chosen_tokens(server, gguf_path):
+    """``logprobs: true`` on a non-streamed completion: one extra forward scores the generated tokens; a greedy token's
+    log-probability is the maximum of its distribution, and the values equal a direct computation on the oracle."""
+    import math
+    import torch
+    from openagents_b200.oracle.models import llama_forward
+    base, state = server
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 5, "logprobs": True}
+    code, raw = _post(base + "/v1/chat/completions", body)
+    assert code == 200, raw
+    c = json.loads(raw)["choices"][0]
+    rows = c["logprobs"]["content"]
+    assert 1 <= len(rows) <= 5 and all(r["logprob"] <= 0.0 and r["top_logprobs"] == [] and isinstance(r["bytes"], list) for r in rows)
+    m = state.models["tiny"] if isinstance(state.models, dict) else state.models[0]
+    from openagents_b200.serve.generation import render_chat
+    prompt = m.tok.encode(render_chat(body["messages"], m.chat_template))
+    be = m.backend
+    out_ids, feed = [], list(prompt)
+    logits = llama_forward(be.cfg, be.W, torch.tensor(feed), None).double()
+    for r in rows:
+        lp = torch.log_softmax(logits[-1], -1)
+        nxt = int(lp.argmax())
+        assert r["logprob"] == pytest.approx(float(lp[nxt]), abs=1e-4) and math.isfinite(r["logprob"])
+        out_ids.append(nxt)
+        feed.append(nxt)
+        logits = llama_forward(be.cfg, be.W, torch.tensor(feed), None).double()
+    assert be.kv_stats()["sequences"] == 0
+    assert _post(base + "/v1/chat/completions", {**body, "stream": True})[0] == 400
+    assert _post(base + "/v1/chat/completions", {**body, "top_logprobs": 3})[0] == 400
+    assert "logprobs" not in json.loads(_post(base + "/v1/chat/completions", {**body, "logprobs": False})[1])["choices"][0]
