@@ -430,6 +430,8 @@ def test_logprobs_of_the_chosen_tokens(server, gguf_path):
     import torch
     from openagents_b200.oracle.models import llama_forward
     base, state = server
+    m0 = state.models["tiny"] if isinstance(state.models, dict) else state.models[0]
+    open_before = m0.backend.kv_stats()["sequences"]          # sessions of earlier tests may still hold theirs
     body = {"model": "tiny", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 5, "logprobs": True}
     code, raw = _post(base + "/v1/chat/completions", body)
     assert code == 200, raw
@@ -449,7 +451,7 @@ def test_logprobs_of_the_chosen_tokens(server, gguf_path):
         out_ids.append(nxt)
         feed.append(nxt)
         logits = llama_forward(be.cfg, be.W, torch.tensor(feed), None).double()
-    assert be.kv_stats()["sequences"] == 0
+    assert be.kv_stats()["sequences"] == open_before        # the scoring sequence was closed
     assert _post(base + "/v1/chat/completions", {**body, "stream": True})[0] == 400
     assert _post(base + "/v1/chat/completions", {**body, "top_logprobs": 3})[0] == 400
     assert "logprobs" not in json.loads(_post(base + "/v1/chat/completions", {**body, "logprobs": False})[1])["choices"][0]
