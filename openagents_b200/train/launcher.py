@@ -49,6 +49,8 @@ def parse(argv=None):
     ap.add_argument("--max-allowed-stale", type=int, default=5)
     ap.add_argument("--master-port", type=int, default=29517)
     ap.add_argument("--log-jsonl", default="")
+    ap.add_argument("--export-gguf", default="", help="write the final weights as a GGUF file the server and the evaluator load")
+    ap.add_argument("--tokenizer", default="", help="tokenizer.json of the data preparation; travels inside the exported file")
     ap.add_argument("--data", nargs="*", default=[], help="token shards (data.write_token_shard); default: synthetic uniform ids")
     ap.add_argument("--data-raw-width", type=int, default=0, choices=[0, 2, 4], help="read files without a shard header as raw ids of this width")
     ap.add_argument("--lane", default="pretrain", choices=["pretrain", "sft", "dpo"],
@@ -167,8 +169,20 @@ def worker(args):
             pass
     if log:
         log.close()
+    if args.export_gguf:
+        _export(tr, args, rank)
     if world > 1:
         dist.destroy_process_group()
+
+
+def _export(tr, args, rank, tokenizer=None):
+    if tokenizer is None and args.tokenizer:
+        from ..data import ByteBpe
+        with open(args.tokenizer) as f:
+            tokenizer = ByteBpe.from_json(f.read())
+    tr.export_gguf(args.export_gguf, tokenizer=tokenizer)
+    if rank == 0:
+        print(json.dumps({"event": "exported", "path": args.export_gguf, "tokenizer": tokenizer is not None}))
 
 
 def diloco_worker(args, cfg, dev, rank, world):
@@ -248,7 +262,8 @@ def sft_worker(args, cfg, dev, rank, world):
     rep = sft.run_lane(lambda: Trainer(cfg, dev, rank, world),
                        lambda start: BatchLoader(ds, accum, cfg.micro_batch, rank, world, seed=cfg.seed, start_batch=start),
                        steps=args.steps, checkpoint_at=args.checkpoint_at or max(1, args.steps // 3), ckpt_dir=os.path.join(work, "drill"),
-                       corpus_manifest=corpus.manifest, device=dev)
+                       corpus_manifest=corpus.manifest, device=dev,
+                       on_finished=(lambda tr: _export(tr, args, rank, tokenizer=tok)) if args.export_gguf else None)
     if rank == 0:
         print(json.dumps(rep))
         if args.report:

@@ -157,10 +157,11 @@ def _run_steps(trainer, loader, n: int, device):
 
 
 def run_lane(make_trainer, make_loader, steps: int, checkpoint_at: int, ckpt_dir: str, corpus_manifest: dict, device="cpu",
-             run_id: str = "b200-instruct-sft-smoke", loss_tolerance: float = 5e-3) -> dict:
+             run_id: str = "b200-instruct-sft-smoke", loss_tolerance: float = 5e-3, on_finished=None) -> dict:
     """``make_trainer()`` -> an object with ``train_step(tokens, targets, n_valid)``, ``step_count``, ``save_checkpoint(dir)``,
     ``load_checkpoint(dir)`` and the flat state tensors ``master`` / ``m`` / ``v``; ``make_loader(start_batch)`` -> a
-    ``data.BatchLoader``.  Returns the lane report."""
+    ``data.BatchLoader``.  ``on_finished(trainer)`` is called with the trainer of the uninterrupted run after its last step
+    (export the tuned weights there).  Returns the lane report."""
     if not 0 < checkpoint_at < steps:
         raise ValueError("checkpoint_at must lie inside the run")
     tr = make_trainer()
@@ -171,6 +172,8 @@ def run_lane(make_trainer, make_loader, steps: int, checkpoint_at: int, ckpt_dir
     rest = _run_steps(tr, ld, steps - checkpoint_at, device)
     ld.close()
     straight = first + rest
+    if on_finished is not None:
+        on_finished(tr)
     del tr, ld                                  # the first trainer's device memory is free before the second is built
     # the drill: a fresh trainer, the checkpoint, the same stream from the same batch
     tr2 = make_trainer()

@@ -231,10 +231,17 @@ def test_launcher_lanes_from_files(tmp_path, capsys):
             for b in range(5):
                 f.write(json.dumps({"messages": [{"role": "user", "content": f"What is {a} plus {b}?"}, {"role": "assistant", "content": f"It is {a + b}."}]}) + "\n")
     train_main(common + ["--lane", "sft", "--steps", "6", "--sft-records", str(tmp_path / "chat.jsonl"), "--sft-merges", "32", "--ckpt-dir", str(tmp_path / "sft"),
-                         "--report", str(tmp_path / "sft.json")])
+                         "--report", str(tmp_path / "sft.json"), "--export-gguf", str(tmp_path / "tuned.gguf")])
     capsys.readouterr()
     rep = json.loads((tmp_path / "sft.json").read_text())
     assert rep["completedSteps"] == 6 and rep["lossImproved"] and rep["resumeDrill"]["restoredStateBitExact"] and rep["resumeDrill"]["checkpointAtStep"] == 2
+    # the tuned checkpoint carries its tokenizer and goes straight into the evaluator on the GPU backend
+    from openagents_b200.eval.__main__ import main as eval_main
+    (tmp_path / "em.jsonl").write_text(json.dumps({"prompt": "<|user|>\nWhat is 1 plus 1?<|end|>\n<|assistant|>\n", "answer": "It is 2."}) + "\n")
+    rc = eval_main(["--model", str(tmp_path / "tuned.gguf"), "--backend", "cuda", "--exact", str(tmp_path / "em.jsonl"), "--max-new-tokens", "8",
+                    "--gate", "em.exactMatch:>=:0:optional"])
+    d = json.loads(capsys.readouterr().out.splitlines()[-1])
+    assert rc == 0 and d["backend"] == "cuda" and d["tasks"]["em"]["items"] == 1
     with open(tmp_path / "pairs.jsonl", "w") as f:
         for i in range(6):
             f.write(json.dumps({"messages": [{"role": "user", "content": f"Pick a colour, number {i}."}], "chosen": "red", "rejected": "blue"}) + "\n")
