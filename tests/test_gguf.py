@@ -168,3 +168,29 @@ def test_corrupt_headers_are_errors_not_crashes(tmp_path):
     info = struct.pack("<Q", len(name)) + name + struct.pack("<I", 1) + struct.pack("<Q", 32) + struct.pack("<IQ", 0, 2 ** 64 - 64)
     with pytest.raises(Exception, match="past the end"):
         GGUFFile(write("wrap_offset.gguf", struct.pack("<QQ", 1, 0) + info + b"\0" * 256))
+
+
+def test_command_line_inspect_quantize_digest(tmp_path, capsys):
+    import json
+    from openagents_b200.gguf.__main__ import main
+    from openagents_b200.models.config import TINY_LLAMA
+    from openagents_b200.models.weights import PLAN_BF16, load_gguf_float, random_weights, save_gguf
+    cfg = TINY_LLAMA.with_(vocab=512, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512)
+    src, dst = str(tmp_path / "a.gguf"), str(tmp_path / "b.gguf")
+    save_gguf(src, cfg, random_weights(cfg, 0), PLAN_BF16, extra_meta={"tokenizer.b200.byte_bpe": '{"schema": "x"}', "general.author": "someone"})
+    assert main(["inspect", src]) == 0
+    a = json.loads(capsys.readouterr().out)
+    assert a["architecture"] == "llama" and a["tokenizer"] == "b200-byte-bpe" and list(a["byType"]) == ["BF16"] or "F32" in a["byType"]
+    assert a["bitsPerWeight"] >= 16.0 and a["shape"]["block_count"] == cfg.n_layers
+    assert main(["quantize", src, dst, "--plan", "q4_k"]) == 0
+    q = json.loads(capsys.readouterr().out)
+    assert 0.0 < q["worstRelativeRmsError"] < 0.12 and q["tensorBytes"] < a["tensorBytes"] / 2.5
+    assert "tokenizer.b200.byte_bpe" in q["keptMetadataKeys"] and "general.author" in q["keptMetadataKeys"]
+    assert {r["to"] for r in q["tensors"]} >= {"Q4_K", "Q6_K"}
+    main(["inspect", dst])
+    b = json.loads(capsys.readouterr().out)
+    assert b["bitsPerWeight"] < 7.0 and b["tokenizer"] == "b200-byte-bpe" and b["shape"] == a["shape"]
+    c2, w2 = load_gguf_float(dst)
+    assert c2.d_model == 256 and set(w2) == set(random_weights(cfg, 0))
+    main(["digest", dst])
+    assert json.loads(capsys.readouterr().out)["artifactDigest"].startswith("sha256:")
