@@ -35,7 +35,7 @@ from . import tools as tooling
 from .generation import (CHAT_TEMPLATE_DIGEST, ByteTokenizer, Request, RequestRejected, SamplingParams, Scheduler,
                          VocabTokenizer, render_chat, tokenizer_from_metadata)
 
-ENDPOINTS = ["/health", "/v1/models", "/v1/chat/completions", "/v1/responses", "/v1/sessions", "/v1/serve",
+ENDPOINTS = ["/health", "/v1/models", "/v1/completions", "/v1/chat/completions", "/v1/responses", "/v1/sessions", "/v1/serve",
              "/psionic/management/status", "/metrics"]
 
 
@@ -372,6 +372,8 @@ def make_handler(state: ServerState):
             try:
                 if path == "/v1/chat/completions":
                     return self._chat(model, body)
+                if path == "/v1/completions":
+                    return self._completions(model, body)
                 if path == "/v1/responses":
                     return self._responses(model, body)
                 if path == "/v1/serve":
@@ -398,6 +400,56 @@ def make_handler(state: ServerState):
             except Exception as e:      # surface engine errors as a typed, non-retryable failure
                 return self._err(500, f"{type(e).__name__}: {e}", "engine_error")
             self._err(404, f"no route {path}", "not_found")
+
+        def _completions(self, model, body):
+            """Text completion on a raw prompt (no chat template): ``prompt`` is a string or a list of token ids; ``echo`` returns
+            the prompt in front of the completion; ``logprobs`` (any value but null / false) adds the tokens, their log-probabilities
+            (the first prompt token has none) and text offsets; ``max_tokens: 0`` with ``echo`` scores a text without generating,
+            which is how evaluation harnesses compute log-likelihoods.  Not streamed."""
+            prompt = body.get("prompt")
+            if isinstance(prompt, list) and len(prompt) == 1 and isinstance(prompt[0], (str, list)):
+                prompt = prompt[0]
+            if isinstance(prompt, str):
+                ids = model.tok.encode(prompt)
+            elif isinstance(prompt, list) and prompt and all(isinstance(t, int) and 0 <= t < model.backend.cfg.vocab for t in prompt):
+                ids = list(prompt)
+            else:
+                return self._err(400, "prompt must be a non-empty string or a list of token ids (one prompt per request)")
+            if not ids:
+                return self._err(400, "the prompt is empty")
+            if body.get("stream"):
+                return self._err(400, "text completions are not streamed; use /v1/chat/completions")
+            echo, want_lp = bool(body.get("echo")), body.get("logprobs") not in (None, False)
+            n_new = body.get("max_tokens")
+            n_new = 16 if n_new is None else int(n_new)
+            if n_new < 0 or (n_new == 0 and not echo):
+                return self._err(400, "max_tokens must be positive (0 is allowed together with echo)")
+            out, finish = [], "length"
+            if n_new > 0:
+                params = SamplingParams(max_tokens=n_new, temperature=float(body.get("temperature") or 0.0), top_p=float(body.get("top_p") or 1.0),
+                                        top_k=int(body.get("top_k") or 0),
+                                        stop=tuple(body["stop"]) if isinstance(body.get("stop"), list) else ((body["stop"],) if body.get("stop") else ()),
+                                        seed=body.get("seed"))
+                r = model.generate(ids, params)
+                out, finish = list(r.output), r.finish_reason or "stop"
+            shown = (ids if echo else []) + out
+            choice = {"index": 0, "text": model.tok.decode(shown), "finish_reason": finish, "logprobs": None}
+            if want_lp:
+                scored = ids + out
+                lps = model.token_logprobs(scored[:1], scored[1:]) if len(scored) > 1 else []
+                lps = [None] + lps                                     # nothing precedes the first token
+                lps = lps if echo else lps[len(ids):]
+                pieces = [model.tok.decode([t]) for t in shown]
+                offsets, at = [], 0
+                for piece in pieces:
+                    offsets.append(at)
+                    at += len(piece)
+                choice["logprobs"] = {"tokens": pieces, "token_ids": shown, "token_logprobs": lps, "text_offset": offsets, "top_logprobs": None}
+            usage = {"prompt_tokens": len(ids), "completion_tokens": len(out), "total_tokens": len(ids) + len(out)}
+            state.ledger.record("cmpl." + uuid.uuid4().hex[:12], model.id, len(ids), len(out), account_ref=str(body.get("user") or "account.anonymous"),
+                                adapter_id=ENGINE_NAME, demand_kind=str(body.get("demand_kind") or "unlabeled"))
+            self._json(200, {"id": "cmpl-" + uuid.uuid4().hex[:24], "object": "text_completion", "created": int(time.time()), "model": model.id,
+                             "choices": [choice], "usage": usage})
 
         def _chat(self, model, body):
             msgs = body.get("messages")

@@ -455,3 +455,31 @@ def test_logprobs_of_the_chosen_tokens(server, gguf_path):
     assert _post(base + "/v1/chat/completions", {**body, "stream": True})[0] == 400
     assert _post(base + "/v1/chat/completions", {**body, "top_logprobs": 3})[0] == 400
     assert "logprobs" not in json.loads(_post(base + "/v1/chat/completions", {**body, "logprobs": False})[1])["choices"][0]
+
+
+def test_text_completions_with_echo_and_logprobs(server):
+    """``/v1/completions``: generation on a raw prompt, and ``max_tokens: 0`` + ``echo`` + ``logprobs`` as a scoring call (the
+    log-likelihood request of evaluation harnesses), checked against the oracle."""
+    import torch
+    from openagents_b200.oracle.models import llama_forward
+    base, state = server
+    m = state.models["tiny"] if isinstance(state.models, dict) else state.models[0]
+    code, raw = _post(base + "/v1/completions", {"model": "tiny", "prompt": "abc", "max_tokens": 4})
+    c = json.loads(raw)
+    assert code == 200 and c["object"] == "text_completion" and c["usage"] == {"prompt_tokens": 3, "completion_tokens": c["usage"]["completion_tokens"], "total_tokens": 3 + c["usage"]["completion_tokens"]}
+    assert c["choices"][0]["logprobs"] is None and 1 <= c["usage"]["completion_tokens"] <= 4
+    code, raw = _post(base + "/v1/completions", {"model": "tiny", "prompt": "hello world", "max_tokens": 0, "echo": True, "logprobs": 1})
+    s = json.loads(raw)["choices"][0]
+    ids = m.tok.encode("hello world")
+    want = torch.log_softmax(llama_forward(m.backend.cfg, m.backend.W, torch.tensor(ids), None).double(), -1)
+    assert code == 200 and s["text"] == "hello world" and s["logprobs"]["token_ids"] == ids and s["logprobs"]["token_logprobs"][0] is None
+    for i in range(1, len(ids)):
+        assert s["logprobs"]["token_logprobs"][i] == pytest.approx(float(want[i - 1, ids[i]]), abs=1e-4)
+    assert s["logprobs"]["text_offset"] == list(range(len(ids))) and s["logprobs"]["tokens"][:2] == ["h", "e"]
+    # generation + logprobs without echo: only the new tokens are listed; token ids as the prompt
+    code, raw = _post(base + "/v1/completions", {"model": "tiny", "prompt": ids, "max_tokens": 3, "logprobs": True})
+    g = json.loads(raw)["choices"][0]
+    assert code == 200 and len(g["logprobs"]["token_logprobs"]) == len(g["logprobs"]["token_ids"]) <= 3 and all(x <= 0 for x in g["logprobs"]["token_logprobs"])
+    for bad in ({"prompt": ""}, {"prompt": [["a"], ["b"]]}, {"prompt": "x", "max_tokens": 0}, {"prompt": "x", "stream": True}, {"prompt": [10 ** 9]}):
+        assert _post(base + "/v1/completions", {"model": "tiny", **bad})[0] == 400
+    assert "/v1/completions" in json.loads(_get(base + "/health")[1])["endpoints"]
