@@ -483,3 +483,25 @@ def test_text_completions_with_echo_and_logprobs(server):
     for bad in ({"prompt": ""}, {"prompt": [["a"], ["b"]]}, {"prompt": "x", "max_tokens": 0}, {"prompt": "x", "stream": True}, {"prompt": [10 ** 9]}):
         assert _post(base + "/v1/completions", {"model": "tiny", **bad})[0] == 400
     assert "/v1/completions" in json.loads(_get(base + "/health")[1])["endpoints"]
+
+
+def test_remote_scorers_agree_with_the_in_process_ones(server, tmp_path):
+    import numpy as np
+    from openagents_b200.data import TokenDataset, write_token_shard
+    from openagents_b200.eval import multiple_choice, perplexity
+    from openagents_b200.eval.remote import loglikelihood, multiple_choice_http, perplexity_http
+    base, state = server
+    m = state.models["tiny"] if isinstance(state.models, dict) else state.models[0]
+    items = [{"context": "the cat", "choices": [" sat", " flew away"], "answer": 0}]
+    with m.lock:
+        local = multiple_choice(m.backend, items, m.tok)
+    remote = multiple_choice_http(base, "tiny", items, m.tok)
+    assert remote["picks"][0]["scores"] == pytest.approx(local["picks"][0]["scores"], abs=1e-4) and remote["accuracy"] == local["accuracy"]
+    assert loglikelihood(base, "tiny", [1, 2, 3], [4, 5]) < 0
+    write_token_shard(tmp_path / "v.b2tk", np.random.default_rng(3).integers(0, 500, 80))
+    ds = TokenDataset(tmp_path / "v.b2tk", seq_len=16)
+    r = perplexity_http(base, "tiny", ds, max_windows=2)
+    with m.lock:
+        l = perplexity(m.backend, ds, max_windows=2)
+    # a window of 16 inputs and its final target is 17 ids on the wire: the same 16 predictions the in-process scorer makes
+    assert r["targets"] == l["targets"] == 2 * 16 and r["loss"] == pytest.approx(l["loss"], abs=1e-4)
