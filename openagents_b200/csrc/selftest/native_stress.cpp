@@ -1,11 +1,11 @@
 // A stress program for the host-side native code, meant to be built with a sanitizer:
 //
-//   g++ -std=c++17 -O1 -g -fsanitize=thread            native_stress.cpp ../data/token_data.cpp ../data/bpe.cpp ../kv/kv_alloc.cpp -pthread
-//   g++ -std=c++17 -O1 -g -fsanitize=address,undefined native_stress.cpp ../data/token_data.cpp ../data/bpe.cpp ../kv/kv_alloc.cpp -pthread
+//   g++ -std=c++17 -O1 -g -fsanitize=thread            native_stress.cpp ../data/*.cpp ../kv/kv_alloc.cpp ../gguf/*.cpp -pthread -fopenmp
+//   g++ -std=c++17 -O1 -g -fsanitize=address,undefined native_stress.cpp ../data/*.cpp ../kv/kv_alloc.cpp ../gguf/*.cpp -pthread -fopenmp
 //
 // Thread sanitizer: the loader's worker threads, its ring of slots and the consumer (data races, lock order).  Address and
 // undefined-behaviour sanitizers: the shard reader's bounds, the BPE trainer's and encoder's containers, the KV page pool
-// under a random sequence of begin / extend / publish / truncate / end.  The program also checks the results it can check
+// under a random sequence of begin / extend / publish / truncate / end, and the GGUF reader on thousands of damaged files.  The program also checks the results it can check
 // (every batch equals the windows the sampler names; an encoded text decodes to itself; the pool returns every page).
 // Exit code 0 = all checks passed.
 #include <cstdint>
@@ -37,6 +37,21 @@ void b200_bpe_train_free(void*);
 void* b200_bpe_encoder(const int32_t* merges, int n_merges);
 int64_t b200_bpe_encode(void*, const uint8_t* text, uint64_t n, int mode, int32_t* out, uint64_t cap);
 void b200_bpe_encoder_free(void*);
+void* b200_gguf_open(const char* path);
+const char* b200_gguf_error(void*);
+void b200_gguf_close(void*);
+const char* b200_gguf_meta_json(void*);
+uint64_t b200_gguf_n_tensors(void*);
+const char* b200_gguf_tensor_name(void*, uint64_t i);
+uint64_t b200_gguf_tensor_nbytes(void*, uint64_t i);
+const void* b200_gguf_tensor_data(void*, uint64_t i);
+void* b200_gguf_writer_new(const char* path, uint32_t alignment);
+void b200_gguf_writer_kv_u32(void*, const char* key, uint32_t v);
+void b200_gguf_writer_kv_str(void*, const char* key, const char* v, uint64_t n);
+void b200_gguf_writer_kv_str_array(void*, const char* key, const char* blob, const uint64_t* lens, uint64_t n);
+int b200_gguf_writer_tensor(void*, const char* name, uint32_t type, uint32_t ndim, const uint64_t* dims, const void* data);
+int b200_gguf_writer_finish(void*);
+void b200_gguf_writer_free(void*);
 void* b200_kv_create(int32_t n_pages, int32_t page_size);
 void b200_kv_destroy(void*);
 int32_t b200_kv_free_pages(void*);
@@ -196,6 +211,79 @@ static void kv_stress() {
   b200_kv_destroy(p);
 }
 
+// A valid file, then thousands of damaged copies (flipped bytes, overwritten 64-bit counts, cut tails): the reader must either
+// refuse with an error or hand out tensors that lie inside the mapping; every byte it hands out is read here so that the
+// address sanitizer sees an out-of-range pointer.
+static void gguf_fuzz(const std::string& dir) {
+  const std::string good = dir + "/good.gguf", bad = dir + "/bad.gguf";
+  std::vector<float> w0(64 * 8), w1(32);
+  for (auto& x : w0) x = (float)(rnd() % 100) / 10.f;
+  for (auto& x : w1) x = 1.f;
+  void* w = b200_gguf_writer_new(good.c_str(), 32);
+  b200_gguf_writer_kv_str(w, "general.architecture", "llama", 5);
+  b200_gguf_writer_kv_u32(w, "llama.block_count", 2);
+  const char blob[] = "abcde";
+  const uint64_t lens[3] = {1, 2, 2};
+  b200_gguf_writer_kv_str_array(w, "tokenizer.ggml.tokens", blob, lens, 3);
+  const uint64_t d0[2] = {64, 8}, d1[1] = {32};
+  CHECK(b200_gguf_writer_tensor(w, "blk.0.w", 0, 2, d0, w0.data()) == 0);        // type 0: F32
+  CHECK(b200_gguf_writer_tensor(w, "norm", 0, 1, d1, w1.data()) == 0);
+  CHECK(b200_gguf_writer_finish(w) == 0);
+  b200_gguf_writer_free(w);
+  std::vector<uint8_t> bytes;
+  {
+    FILE* f = std::fopen(good.c_str(), "rb");
+    CHECK(f != nullptr);
+    uint8_t buf[4096];
+    size_t n;
+    while (f && (n = std::fread(buf, 1, sizeof buf, f)) > 0) bytes.insert(bytes.end(), buf, buf + n);
+    if (f) std::fclose(f);
+  }
+  CHECK(bytes.size() > 64 * 8 * 4);
+  int opened = 0, refused = 0;
+  for (int iter = 0; iter < 3000; iter++) {
+    std::vector<uint8_t> m = bytes;
+    const int kind = (int)(rnd() % 4);
+    const size_t header = m.size() - (64 * 8 + 32) * 4;          // most damage goes where the structure is
+    if (kind == 0) {
+      for (int k = 0; k < 1 + (int)(rnd() % 4); k++) m[rnd() % header] ^= (uint8_t)(1u << (rnd() % 8));
+    } else if (kind == 1) {
+      const size_t at = rnd() % (header - 8);
+      const uint64_t v = (rnd() % 3 == 0) ? ~0ull : (rnd() % 3 == 0 ? (1ull << 62) : rnd());
+      std::memcpy(m.data() + at, &v, 8);
+    } else if (kind == 2) {
+      m.resize(rnd() % m.size());
+    } else {
+      const size_t at = rnd() % header;
+      m[at] = (uint8_t)rnd();
+      m.resize(header + rnd() % (m.size() - header));
+    }
+    FILE* f = std::fopen(bad.c_str(), "wb");
+    if (!f) continue;
+    if (!m.empty()) std::fwrite(m.data(), 1, m.size(), f);
+    std::fclose(f);
+    void* r = b200_gguf_open(bad.c_str());
+    if (b200_gguf_error(r) != nullptr) {
+      refused++;
+    } else {
+      opened++;
+      volatile uint64_t sink = std::strlen(b200_gguf_meta_json(r));
+      const uint64_t nt = b200_gguf_n_tensors(r);
+      CHECK(nt < 1000);
+      for (uint64_t i = 0; i < nt; i++) {
+        sink += std::strlen(b200_gguf_tensor_name(r, i));
+        const uint8_t* p = (const uint8_t*)b200_gguf_tensor_data(r, i);
+        const uint64_t nb = b200_gguf_tensor_nbytes(r, i);
+        for (uint64_t k = 0; k < nb; k += 61) sink += p[k];
+        if (nb) sink += p[nb - 1];
+      }
+      (void)sink;
+    }
+    b200_gguf_close(r);
+  }
+  CHECK(refused > 100 && opened > 10);                          // both outcomes were exercised
+}
+
 int main(int argc, char** argv) {
   if (argc < 2) {
     std::fprintf(stderr, "usage: native_stress <scratch directory>\n");
@@ -204,6 +292,7 @@ int main(int argc, char** argv) {
   loader_stress(argv[1]);
   bpe_stress();
   kv_stress();
+  gguf_fuzz(argv[1]);
   std::printf("native stress: %d failed checks\n", failures);
   return failures ? 1 : 0;
 }
