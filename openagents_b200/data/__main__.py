@@ -3,8 +3,8 @@
     python -m openagents_b200.data prepare --text corpus/*.txt --out data/run1 --merges 8192 --val-fraction 0.01
     python -m openagents_b200.data traces --in served.jsonl --out sft_records.jsonl
 
-``prepare`` treats every input file as documents separated by blank lines (or one JSON object with a ``text`` field per line
-for ``.jsonl``), runs the refinery, trains a byte-level BPE on the refined text (or loads ``--tokenizer``), writes
+``prepare`` treats every input file as documents separated by blank lines (one JSON object with a ``text`` field per line for
+``.jsonl``; the HTML responses of ``.warc`` / ``.warc.gz`` crawl files and ``.html`` files go through the text extractor), runs the refinery, trains a byte-level BPE on the refined text (or loads ``--tokenizer``), writes
 ``train-*.b2tk`` / ``val.b2tk`` with an end-of-text id between documents, and a manifest with every stage's counters.
 """
 from __future__ import annotations
@@ -19,6 +19,15 @@ import sys
 def _read_documents(paths) -> list[str]:
     texts = []
     for p in paths:
+        if p.endswith((".warc", ".warc.gz")):                     # crawl files: HTML responses -> extracted text
+            from .extract import warc_to_documents
+            texts += ["\n".join(d["lines"]) for d in warc_to_documents(p)]
+            continue
+        if p.endswith((".html", ".htm")):
+            from .extract import html_to_text
+            with open(p, "rb") as f:
+                texts.append(html_to_text(f.read()))
+            continue
         with open(p, encoding="utf-8", errors="replace") as f:
             if p.endswith(".jsonl"):
                 texts += [json.loads(line)["text"] for line in f if line.strip()]
@@ -33,6 +42,13 @@ def prepare(args) -> dict:
     from .refinery import STAGES, documents_from_texts, refine
     texts = _read_documents(args.text)
     docs, report = refine(documents_from_texts(texts), stages=() if args.no_refine else STAGES, seed=args.seed, max_line_repeats=args.max_line_repeats)
+    for flag, stage in ((args.language_id, "language_id"), (args.quality_classifier, "quality_classifier")):
+        if flag:                                                  # MODEL.json:LABEL[:MIN_CONFIDENCE]
+            from .classifiers import HashedNgramClassifier, classifier_stage
+            parts = flag.split(":")
+            docs, rep = classifier_stage(docs, HashedNgramClassifier.load(parts[0]), parts[1], float(parts[2]) if len(parts) > 2 else 0.5, stage=stage)
+            report["stages"].append({"stage": stage, "stats": rep, "documentsAfter": len(docs)})
+            report["outputDocuments"] = len(docs)
     bodies = ["\n".join(d["lines"]) for d in docs]
     if not bodies:
         raise SystemExit("the refinery kept no document")
@@ -93,6 +109,8 @@ def main(argv=None) -> int:
     p.add_argument("--shard-tokens", type=int, default=100_000_000)
     p.add_argument("--max-line-repeats", type=int, default=1)
     p.add_argument("--no-refine", action="store_true")
+    p.add_argument("--language-id", default="", help="MODEL.json:LABEL[:MIN_CONFIDENCE] keeps the documents a hashed n-gram classifier assigns to LABEL")
+    p.add_argument("--quality-classifier", default="", help="same form, for a learned quality filter")
     p.add_argument("--seed", default="refinery")
     t = sub.add_parser("traces")
     t.add_argument("--in", dest="inp", required=True)
