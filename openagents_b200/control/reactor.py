@@ -12,7 +12,7 @@ MEASURED evaluations.  The evaluation harness is owned by this engine's lane.
 Restates packages/reactor-contracts/src/index.ts: lanes and profiles :61-156, policy :194-255, install / route / metering
 receipts :258-333, evaluation :336-390, policy resolution :1106-1225, provisioning :1242-1305, routing :1317-1391, metering
 :1396-1444, harness profile :1454-1468, evaluation receipts and coverage :1476-1680, air-gapped update bundles and
-install operations :1675-1811.  Records are plain dicts with the
+install operations :1675-1811, the dog-food run :1813-1949, the improvement ladder :789-910.  Records are plain dicts with the
 reference's field names; ``ContractError`` replaces schema-decoding failures.  The need-to-know corpus rules and the
 data-liberation pipeline of that package are in ``control.reactor_data``.
 """
@@ -385,3 +385,133 @@ def install_ops_receipt(action: str, bundle: dict, catalog: dict, policy: dict, 
             "sourceRefs": _unique([bundle["bundleRef"], bundle["signatureRef"], inst["receiptRef"], inst["policyDecisionRef"], *source_refs]),
             "status": "refused" if blockers else "succeeded",
             "verificationRefs": _unique([bundle["verifierRef"], bundle["publicKeyRef"], bundle["signatureRef"], inst["policyDecisionRef"]])}
+
+
+# ---------------------------------------------------------------- dog-food run and the improvement ladder (index.ts:449-481, :789-910, :1813-1949)
+IMPROVEMENT_STAGES = ("distill_to_fit", "flywheel_training", "harness_evolution")
+HARNESS_MECHANISMS = ("context_fidelity", "deliverable_landing", "loop_robustness", "tool_call_repair")
+
+
+def _policy_is_single_origin_with_lineage(policy: dict) -> bool:
+    c = policy["constraints"]
+    return bool(c.get("enforceDistillationLineageJurisdiction")) and len(c.get("allowOriginJurisdictions") or []) == 1
+
+
+def dogfood_run_receipt(profile: dict, policy: dict, install_ops: dict, refused_install_ops: dict, route_receipts: list[dict], metering_receipts: list[dict],
+                        workload_ref: str, case_study_ref: str, window_started_at: str, window_ended_at: str, generated_at: str, receipt_ref: str,
+                        source_refs=()) -> dict:
+    """One measured internal run of a private deployment, from its receipts: the node is a dog-food placement bound to a
+    strict policy (one allowed origin jurisdiction, lineage enforced), the served model was installed through install-ops, a
+    non-conforming model was REFUSED by the same policy before any pull, every request was routed under that policy and has
+    an exact local metering receipt.  Anything else blocks; the receipt never authorises an external claim."""
+    b = []
+    if profile.get("placement") != "dogfood":
+        b.append("blocker.reactor.dogfood.node_not_dogfood_placement")
+    if not (profile["policyRef"] == policy["policyRef"] and profile["policyVersion"] == policy["version"]):
+        b.append("blocker.reactor.dogfood.profile_policy_binding_mismatch")
+    if not _policy_is_single_origin_with_lineage(policy):
+        b.append("blocker.reactor.dogfood.strict_single_origin_policy_missing")
+    if install_ops["status"] != "succeeded":
+        b.append("blocker.reactor.dogfood.install_ops_not_succeeded")
+    if not (install_ops["nodeProfileRef"] == profile["nodeProfileRef"] and install_ops["modelRef"] == profile["modelRef"]
+            and install_ops["policyRef"] == policy["policyRef"] and install_ops["policyVersion"] == policy["version"]):
+        b.append("blocker.reactor.dogfood.install_ops_binding_mismatch")
+    if refused_install_ops["status"] != "refused":
+        b.append("blocker.reactor.dogfood.nonconforming_pull_not_refused")
+    if "blocker.reactor.install_ops.policy_revalidation_failed" not in refused_install_ops["blockerRefs"]:
+        b.append("blocker.reactor.dogfood.nonconforming_pull_not_policy_refused")
+    if refused_install_ops["modelRef"] == profile["modelRef"]:
+        b.append("blocker.reactor.dogfood.refused_model_matches_served_model")
+    for r in route_receipts:
+        if r["status"] != "routed":
+            b += ["blocker.reactor.dogfood.route_not_routed", *r["blockerRefs"]]
+        if not (r["nodeProfileRef"] == profile["nodeProfileRef"] and r["policyRef"] == policy["policyRef"] and r["policyVersion"] == policy["version"]):
+            b.append("blocker.reactor.dogfood.route_binding_mismatch")
+    for m in metering_receipts:
+        if not (m["nodeProfileRef"] == profile["nodeProfileRef"] and m["policyRef"] == policy["policyRef"] and m["policyVersion"] == policy["version"]):
+            b.append("blocker.reactor.dogfood.metering_binding_mismatch")
+        if not (m["measurementState"] == "measured" and m["usageTruth"] == "exact" and m["totalTokens"] is not None):
+            b.append("blocker.reactor.dogfood.local_metering_not_exact")
+    requests = _unique([r["requestRef"] for r in route_receipts])
+    metered = {m["requestRef"] for m in metering_receipts}
+    b += [f"blocker.reactor.dogfood.missing_metering:{q}" for q in requests if q not in metered]
+    b = _unique(b)
+    c = policy["constraints"]
+    return {"schemaVersion": "openagents.reactor.dogfood_run_receipt.v1", "blockerRefs": b, "caseStudyWriteupRef": case_study_ref, "externalClaimFlipAllowed": False,
+            "externalPilotAuthorized": False, "generatedAt": generated_at, "installOpsReceiptRef": install_ops["receiptRef"],
+            "localMeteringReceiptRefs": [m["receiptRef"] for m in metering_receipts], "measuredWindowStartedAt": window_started_at,
+            "measuredWindowEndedAt": window_ended_at, "nodeProfileRef": profile["nodeProfileRef"], "placement": profile.get("placement"),
+            "policyConstraintRefs": _unique([*[f"constraint.origin_jurisdiction:{j}" for j in c.get("allowOriginJurisdictions") or []],
+                                             "constraint.distillation_lineage_jurisdiction:" + ("enforced" if c.get("enforceDistillationLineageJurisdiction") else "not_enforced")]),
+            "policyDecisionReceiptRefs": _unique([install_ops["policyDecisionRef"], refused_install_ops["policyDecisionRef"], *[r["policyDecisionRef"] for r in route_receipts]]),
+            "policyRef": policy["policyRef"], "policyVersion": policy["version"], "publicSafe": True, "receiptRef": receipt_ref,
+            "refusedNonconformingInstallOpsReceiptRef": refused_install_ops["receiptRef"], "refusedNonconformingModelRef": refused_install_ops["modelRef"],
+            "requestRefs": requests, "routeDecisionRefs": [r["decisionRef"] for r in route_receipts],
+            "sourceRefs": _unique([profile["nodeProfileRef"], policy["policyRef"], install_ops["receiptRef"], refused_install_ops["receiptRef"], case_study_ref,
+                                   *[r["decisionRef"] for r in route_receipts], *[m["receiptRef"] for m in metering_receipts], *source_refs]),
+            "status": "refused" if b else "completed", "totalMeasuredTokens": sum(m["totalTokens"] or 0 for m in metering_receipts),
+            "workloadRef": workload_ref, "workloadTruth": "internal_openagents"}
+
+
+def improvement_ladder_plan(plan_ref: str, design_doc_ref: str, generated_at: str, stages=IMPROVEMENT_STAGES, source_refs=()) -> dict:
+    _need(all(s in IMPROVEMENT_STAGES for s in stages) and len(stages) > 0, "reactor.improvement_ladder.unknown_stage")
+    return {"schemaVersion": "openagents.reactor.improvement_ladder_plan_receipt.v1", "boundaryRequirement": "customer_premises_or_regulated_private",
+            "capabilityClaimsAuthorized": False, "consentRequired": True, "customerDataUsed": False, "customerWeightsOwnerRequired": True,
+            "designDocRef": design_doc_ref, "generatedAt": generated_at, "planRef": plan_ref, "sourceRefs": _unique([design_doc_ref, *source_refs]),
+            "stages": list(stages)}
+
+
+def harness_evolution_receipt(model_ref: str, policy: dict, mechanism_class: str, baseline_harness_ref: str, candidate_harness_ref: str,
+                              baseline_score_bps: int, candidate_score_bps: int, acceptance_threshold_bps: int, dataset_snapshot_ref: str,
+                              eval_delta_ref: str, receipt_ref: str, generated_at: str, transfer_labels=(), source_refs=()) -> dict:
+    """A change of ONE harness mechanism (no weight changes), accepted only when the evaluated gain reaches the threshold."""
+    _need(mechanism_class in HARNESS_MECHANISMS, "reactor.harness_evolution.unknown_mechanism")
+    delta = int(candidate_score_bps) - int(baseline_score_bps)
+    return {"schemaVersion": "openagents.reactor.harness_evolution_dogfood_receipt.v1", "acceptanceThresholdBps": acceptance_threshold_bps,
+            "accepted": delta >= acceptance_threshold_bps, "baselineHarnessRef": baseline_harness_ref, "baselineScoreBps": baseline_score_bps,
+            "candidateHarnessRef": candidate_harness_ref, "candidateScoreBps": candidate_score_bps, "costObjectiveIncluded": True, "customerDataUsed": False,
+            "datasetSnapshotRef": dataset_snapshot_ref, "deltaBps": delta, "evalDeltaRef": eval_delta_ref, "generatedAt": generated_at,
+            "mechanismClass": mechanism_class, "modelRef": model_ref, "oneMechanismOnly": True, "optimizerRef": "mutalisk", "policyRef": policy["policyRef"],
+            "policyVersion": policy["version"], "receiptRef": receipt_ref, "runnerRef": "psionic",
+            "sourceRefs": _unique([baseline_harness_ref, candidate_harness_ref, dataset_snapshot_ref, eval_delta_ref, *source_refs]),
+            "stage": "harness_evolution", "transferLabels": list(transfer_labels), "weightChangesAllowed": False, "workloadTruth": "internal_openagents_dogfood"}
+
+
+def distill_to_fit_receipt(catalog: dict, policy: dict, source_model_ref: str, candidate_artifact_ref: str, distillation_run_ref: str,
+                           baseline_quality_bps: int, candidate_quality_bps: int, baseline_cost_micro_usd_per_1k: int, candidate_cost_micro_usd_per_1k: int,
+                           max_quality_loss_bps: int, dataset_snapshot_ref: str, input_distribution_capture_ref: str, eval_delta_ref: str,
+                           receipt_ref: str, generated_at: str, source_refs=()) -> dict:
+    """A smaller model distilled from a served one (``train.distill``): accepted for internal use when the SOURCE model still conforms to
+    the policy at this moment, the candidate is cheaper, and the evaluated quality loss stays within the bound.  The router swap stays a
+    separate, evaluation-gated step; this receipt never authorises it."""
+    pd = resolve_model_policy(catalog, policy, generated_at, f"{receipt_ref}.policy_decision", [source_model_ref, *source_refs])
+    md = _decision_for(pd, source_model_ref)
+    conforms = md is not None and md["status"] == "conforming"
+    _need(baseline_cost_micro_usd_per_1k > 0, "reactor.distill_to_fit.baseline_cost")
+    dq = int(candidate_quality_bps) - int(baseline_quality_bps)
+    cost_red = round((baseline_cost_micro_usd_per_1k - candidate_cost_micro_usd_per_1k) / baseline_cost_micro_usd_per_1k * 10_000)
+    gate = conforms and cost_red > 0 and dq >= -abs(max_quality_loss_bps)
+    return {"schemaVersion": "openagents.reactor.distill_to_fit_dogfood_receipt.v1", "acceptedForDogfood": gate,
+            "baselineCostPer1kTokensMicrousd": baseline_cost_micro_usd_per_1k, "baselineQualityScoreBps": baseline_quality_bps,
+            "candidateArtifactRef": candidate_artifact_ref, "candidateCostPer1kTokensMicrousd": candidate_cost_micro_usd_per_1k,
+            "candidateModelClass": "smaller_distilled_model", "candidateQualityScoreBps": candidate_quality_bps, "costReductionBps": cost_red,
+            "customerDataUsed": False, "datasetSnapshotRef": dataset_snapshot_ref, "distillationRunRef": distillation_run_ref, "evalDeltaRef": eval_delta_ref,
+            "generatedAt": generated_at, "inputDistributionCaptureRef": input_distribution_capture_ref, "policyRef": policy["policyRef"],
+            "policyRevalidated": True, "policyVersion": policy["version"], "qualityDeltaBps": dq, "receiptRef": receipt_ref, "routeSwapAuthorized": False,
+            "routerSwapGate": "eval_gated_rx3_router", "routerSwapGateStatus": "passed" if gate else "blocked", "runnerRef": "psionic",
+            "sourceModelConformsToPolicy": conforms, "sourceModelRef": source_model_ref,
+            "sourceRefs": _unique([source_model_ref, candidate_artifact_ref, distillation_run_ref, dataset_snapshot_ref, eval_delta_ref, pd["decisionRef"], *source_refs]),
+            "stage": "distill_to_fit", "workloadTruth": "internal_openagents_dogfood"}
+
+
+def improvement_ladder_dogfood_receipt(plan: dict, harness: dict, distill: dict, receipt_ref: str, generated_at: str, source_refs=()) -> dict:
+    b = []
+    if "harness_evolution" in plan["stages"] and not harness["accepted"]:
+        b.append("blocker.reactor.improvement_ladder.harness_evolution_not_accepted")
+    if "distill_to_fit" in plan["stages"] and not distill["acceptedForDogfood"]:
+        b.append("blocker.reactor.improvement_ladder.distill_to_fit_not_accepted")
+    return {"schemaVersion": "openagents.reactor.improvement_ladder_dogfood_receipt.v1", "blockerRefs": b, "capabilityClaimsAuthorized": False,
+            "customerDataUsed": False, "distillToFitReceiptRef": distill["receiptRef"], "externalClaimFlipAllowed": False, "generatedAt": generated_at,
+            "harnessEvolutionReceiptRef": harness["receiptRef"], "planRef": plan["planRef"], "receiptRef": receipt_ref,
+            "sourceRefs": _unique([plan["planRef"], harness["receiptRef"], distill["receiptRef"], *source_refs]),
+            "status": "blocked_for_public_claims" if b else "completed_internal", "workloadTruth": "internal_openagents_dogfood"}

@@ -143,3 +143,57 @@ def test_airgap_bundle_is_verified_offline_and_install_ops_revalidates_policy():
     assert "reactor.policy.origin_not_allowed" in refused["blockerRefs"]
     with pytest.raises(rx.ContractError):
         rx.airgap_update_bundle_manifest(prof, "b", "1", "nothex", "p", "v", "k", "s", T0)
+
+
+def _dogfood_parts():
+    cat = _catalog()
+    pol = rx.model_policy("policy.us_only", "v3", "owner.acme", {"allowOriginJurisdictions": ["US"], "enforceDistillationLineageJurisdiction": True})
+    prof = rx.node_model_profile("node.dogfood.1", "model.us.open", "US Open 8B", pol, placement="dogfood")
+    b = rx.airgap_update_bundle_manifest(prof, "bundle.1", "1", "ab" * 32, "policy.us_only", "v3", "kid", "sig.1", T0)
+    ops = rx.install_ops_receipt("fresh_install", b, cat, pol, prof, T0, "receipt.ops.ok")
+    cn = rx.node_model_profile("node.dogfood.1", "model.cn.open", "CN Open", pol, placement="dogfood")
+    bcn = rx.airgap_update_bundle_manifest(cn, "bundle.cn", "1", "cd" * 32, "policy.us_only", "v3", "kid", "sig.cn", T0)
+    refused = rx.install_ops_receipt("fresh_install", bcn, cat, pol, cn, T0, "receipt.ops.refused")
+    inst = rx.provision_model(cat, pol, prof, "install", ["bundle.1"], T0, "d.i", "receipt.install")
+    routes = [rx.route_request(cat, pol, prof, inst, "model.us.open", f"req.{i}", T0, f"d.route.{i}") for i in range(2)]
+    meters = [rx.local_token_metering_receipt(prof, "model.us.open", f"req.{i}", f"receipt.meter.{i}", T0,
+                                              {"prompt_tokens": 10 + i, "completion_tokens": 5, "total_tokens": 15 + i}) for i in range(2)]
+    return cat, pol, prof, ops, refused, routes, meters
+
+
+def test_dogfood_run_receipt_needs_every_receipt_to_line_up():
+    cat, pol, prof, ops, refused, routes, meters = _dogfood_parts()
+    kw = dict(workload_ref="workload.leadgen", case_study_ref="doc.case_study", window_started_at=T0, window_ended_at=T0, generated_at=T0, receipt_ref="receipt.dogfood.1")
+    r = rx.dogfood_run_receipt(prof, pol, ops, refused, routes, meters, **kw)
+    assert r["status"] == "completed" and r["blockerRefs"] == [] and r["totalMeasuredTokens"] == 31 and r["refusedNonconformingModelRef"] == "model.cn.open"
+    assert r["externalClaimFlipAllowed"] is False and "constraint.distillation_lineage_jurisdiction:enforced" in r["policyConstraintRefs"]
+    r2 = rx.dogfood_run_receipt(prof, pol, ops, refused, routes, meters[:1], **kw)
+    assert r2["status"] == "refused" and r2["blockerRefs"] == ["blocker.reactor.dogfood.missing_metering:req.1"]
+    lax = rx.model_policy("policy.us_only", "v3", "owner.acme", {"allowOriginJurisdictions": ["US", "EU"]})
+    r3 = rx.dogfood_run_receipt(prof, lax, ops, ops, routes, meters, **kw)          # no strict policy; the "refused" pull actually succeeded
+    assert {"blocker.reactor.dogfood.strict_single_origin_policy_missing", "blocker.reactor.dogfood.nonconforming_pull_not_refused",
+            "blocker.reactor.dogfood.refused_model_matches_served_model"} <= set(r3["blockerRefs"])
+    prem = rx.node_model_profile("node.dogfood.1", "model.us.open", "US Open 8B", pol)
+    assert "blocker.reactor.dogfood.node_not_dogfood_placement" in rx.dogfood_run_receipt(prem, pol, ops, refused, routes, meters, **kw)["blockerRefs"]
+
+
+def test_improvement_ladder_receipts():
+    cat, pol, *_ = _dogfood_parts()
+    plan = rx.improvement_ladder_plan("plan.ladder.1", "doc.design", T0)
+    assert plan["stages"] == list(rx.IMPROVEMENT_STAGES) and plan["consentRequired"] and not plan["capabilityClaimsAuthorized"]
+    h = rx.harness_evolution_receipt("model.us.open", pol, "tool_call_repair", "harness.v1", "harness.v2", 6100, 6450, 300, "dataset.snap.1", "eval.delta.1", "receipt.h.1", T0)
+    assert h["accepted"] and h["deltaBps"] == 350 and h["weightChangesAllowed"] is False and h["oneMechanismOnly"] is True
+    assert not rx.harness_evolution_receipt("model.us.open", pol, "loop_robustness", "a", "b", 6100, 6200, 300, "d", "e", "r", T0)["accepted"]
+    d = rx.distill_to_fit_receipt(cat, pol, "model.us.open", "artifact.student.gguf", "run.distill.1", 8000, 7850, 900, 300, 200, "dataset.snap.1", "capture.prompts.1",
+                                  "eval.delta.2", "receipt.d.1", T0)
+    assert d["acceptedForDogfood"] and d["costReductionBps"] == 6667 and d["qualityDeltaBps"] == -150 and d["routerSwapGateStatus"] == "passed" and not d["routeSwapAuthorized"]
+    worse = rx.distill_to_fit_receipt(cat, pol, "model.us.open", "a", "r", 8000, 7000, 900, 300, 200, "d", "c", "e", "receipt.d.2", T0)
+    assert not worse["acceptedForDogfood"] and worse["routerSwapGateStatus"] == "blocked"
+    from_cn = rx.distill_to_fit_receipt(cat, pol, "model.cn.open", "a", "r", 8000, 8000, 900, 300, 200, "d", "c", "e", "receipt.d.3", T0)
+    assert not from_cn["acceptedForDogfood"] and from_cn["sourceModelConformsToPolicy"] is False       # a teacher the policy refuses taints the student
+    done = rx.improvement_ladder_dogfood_receipt(plan, h, d, "receipt.ladder.1", T0)
+    assert done["status"] == "completed_internal" and done["blockerRefs"] == [] and done["externalClaimFlipAllowed"] is False
+    blocked = rx.improvement_ladder_dogfood_receipt(plan, h, worse, "receipt.ladder.2", T0)
+    assert blocked["status"] == "blocked_for_public_claims" and blocked["blockerRefs"] == ["blocker.reactor.improvement_ladder.distill_to_fit_not_accepted"]
+    with pytest.raises(rx.ContractError):
+        rx.harness_evolution_receipt("m", pol, "magic", "a", "b", 1, 2, 1, "d", "e", "r", T0)

@@ -135,3 +135,39 @@ def test_trainer_schedules_cosine_wsd_constant():
     assert lr_schedule(TrainConfig(lr=2.0, total_steps=10, schedule="constant"), 7) == 2.0 and lr_schedule(TrainConfig(lr=2.0), 99) == 2.0
     with pytest.raises(ValueError):
         lr_schedule(TrainConfig(schedule="step"), 0)
+
+
+def test_distillation_records_from_a_teacher_backend_feed_the_lane(tmp_path):
+    """Sequence-level distillation: the teacher (the fp32 CPU backend here) answers captured prompts through the scheduler, the
+    answers become chat records, the student's lane trains on them; both are then scored on the same items."""
+    from openagents_b200.models.config import ModelConfig
+    from openagents_b200.models.weights import random_weights
+    from openagents_b200.serve.backend import CpuBackend
+    from openagents_b200.train import distill
+    text = " ".join(m["content"] for r in RECORDS for m in r["messages"]).encode()
+    tok = ByteBpe.train(text * 3, 30, special=sft.SPECIAL_TOKENS)
+
+    class Tok:                                   # the serving tokenizer interface over the same BPE
+        eos_id = tok.special_ids["<|end|>"]
+        vocab_size = 400
+        encode, decode = staticmethod(tok.encode), staticmethod(lambda ids: tok.decode([i for i in ids if i < tok.vocab_size]))
+    cfg = ModelConfig(name="teacher", arch="llama", vocab=400, d_model=32, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=8, ffn=64, context=256)
+    teacher = CpuBackend(cfg, {k: v.float() for k, v in random_weights(cfg, 3).items()})
+    prompts = ["What is two plus two?", "Name a colour.", "Say hello."]
+    recs, man = distill.teacher_records(teacher, Tok, prompts, max_new_tokens=6)
+    assert man["prompts"] == 3 and man["records"] + man["dropped"] == 3 and man["records"] >= 1 and man["inputDistributionDigest"].startswith("sha256:")
+    assert all(r["messages"][-1]["role"] == "assistant" and r["messages"][-1]["content"] and "<|end|>" not in r["messages"][-1]["content"] for r in recs)
+    again, man2 = distill.teacher_records(teacher, Tok, prompts, max_new_tokens=6)
+    assert man2["recordsDigest"] == man["recordsDigest"]                      # greedy teacher: the capture is reproducible
+    many, man3 = distill.teacher_records(teacher, Tok, prompts[:1], max_new_tokens=6, answers_per_prompt=4, temperature=1.0, seed=5)
+    assert man3["answersPerPrompt"] == 4 and 1 <= man3["records"] <= 4
+    # the student lane consumes the records unchanged
+    c = sft.build_corpus(recs, tok, "distilled@v1")
+    sft.pack(c, tmp_path / "d.b2tk", repeat=40)
+    ds = TokenDataset(tmp_path / "d.b2tk", seq_len=16)
+    rep = sft.run_lane(lambda: TinyTrainer(tok.vocab_size, 6), lambda start: BatchLoader(ds, 1, 4, seed=1, start_batch=start, pin=False),
+                       steps=6, checkpoint_at=2, ckpt_dir=str(tmp_path / "ck"), corpus_manifest=c.manifest)
+    assert rep["lossImproved"] and rep["corpus"]["datasetIdentity"] == "distilled@v1"
+    q = distill.quality_delta(teacher, teacher, Tok, Tok, [{"prompt": sft.generation_prompt([{"role": "user", "content": prompts[0]}]),
+                                                            "answer": recs[0]["messages"][-1]["content"]}], max_new_tokens=6)
+    assert q["qualityDeltaBps"] == 0 and q["baselineQualityScoreBps"] == q["candidateQualityScoreBps"] and q["items"] == 1
