@@ -90,6 +90,31 @@ class HeartbeatBoard:
         if stale:
             raise PeerLeft(stale, "stopped reporting")
 
+    def wait_peers(self, step: int, timeout_s: float = 5.0, poll_s: float = 0.01, sleep=time.sleep):
+        """The strict form of ``check_peers``: return only once every peer has posted its heartbeat FOR ``step`` (ranks post it
+        before they launch the step, so this is a host-side rendezvous through the store).  A peer that says it left raises
+        ``PeerLeft`` at once, a peer that does not reach ``step`` within ``timeout_s`` raises it as "stopped reporting".  With
+        ``check_peers`` alone a peer that is one step behind and about to leave passes the check, and its departure is then only
+        noticed by the collective's own timeout."""
+        deadline = self.now() + timeout_s
+        while True:
+            gone, behind = [], []
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                hb = self.read(r)
+                if hb is not None and hb.get("state") != "alive":
+                    gone.append(r)
+                elif hb is None or hb["step"] < step:
+                    behind.append(r)
+            if gone:
+                raise PeerLeft(gone, "left the job")
+            if not behind:
+                return
+            if self.now() > deadline:
+                raise PeerLeft(behind, "stopped reporting")
+            sleep(poll_s)
+
 
 @dataclass
 class RoundLedger:

@@ -106,22 +106,14 @@ def _gloo_worker(rank, world, port, mode, out_dir):
     events = []
     try:
         for step in range(1, 6):
+            if mode == "leave" and rank == 1 and step == 4:
+                board.leave(step)            # between steps: nothing of this rank is in flight; it never announces step 4 as alive
+                break
             board.beat(step)
             dist.barrier() if step == 1 else None
-            if mode == "leave" and rank == 1 and step == 4:
-                board.leave(step)            # between steps: nothing of this rank is in flight
-                break
             try:
                 if step > 1:
-                    deadline = time.time() + 2.0          # peers post their heartbeat before they launch; give them a moment
-                    while True:
-                        try:
-                            board.check_peers(step)
-                            break
-                        except PeerLeft as e:
-                            if e.reason == "left the job" and all(board.read(p) is not None for p in e.peers) or time.time() > deadline:
-                                raise
-                            time.sleep(0.02)
+                    board.wait_peers(step, timeout_s=5.0)     # peers post their heartbeat before they launch: a rendezvous on the host
                 if mode == "never_joins" and rank == 1 and step == 4:
                     time.sleep(6.0)          # alive, heartbeat posted, but never enters the collective
                     break
@@ -166,3 +158,38 @@ def test_gloo_rank_failure_is_detected_and_step_is_discarded(tmp_path, mode):
     assert r["step"] == 2 and torch.equal(r["restored"], torch.full((8,), 6.0))       # two steps of (1 + 2)
     assert torch.equal(r["state_before"], torch.full((8,), 9.0))                       # step 3 had completed, step 4 never did
     assert r["preserved"][0] == ["step1.rank0", "step2.rank0", "step3.rank0"] and 1 not in r["preserved"]
+
+
+def test_wait_peers_is_a_rendezvous_on_the_step():
+    """The strict pre-launch check: a peer one step behind is waited for, a peer that left raises at once, a peer that never
+    arrives raises when the time is up."""
+    from openagents_b200.parallel.failure import HeartbeatBoard, PeerLeft
+
+    class Store(dict):
+        def set(self, k, v):
+            self[k] = v
+
+        def check(self, keys):
+            return all(k in self for k in keys)
+
+    store, clock = Store(), [0.0]
+    a, b = (HeartbeatBoard(store, r, 2, now=lambda: clock[0]) for r in (0, 1))
+    a.beat(3)
+    b.beat(2)
+    polls = []
+
+    def sleep(dt):                      # the peer posts its step-3 heartbeat while rank 0 is polling
+        polls.append(dt)
+        clock[0] += dt
+        if len(polls) == 3:
+            b.beat(3)
+    a.wait_peers(3, timeout_s=1.0, sleep=sleep)
+    assert len(polls) == 3
+    a.check_peers(4)                    # the lenient check lets a peer be one step behind ...
+    with pytest.raises(PeerLeft) as e:  # ... the strict one does not, and says so when the time is up
+        a.wait_peers(4, timeout_s=0.5, sleep=lambda dt: clock.__setitem__(0, clock[0] + dt))
+    assert e.value.reason == "stopped reporting" and e.value.peers == [1]
+    b.leave(4)
+    with pytest.raises(PeerLeft) as e:
+        a.wait_peers(4, timeout_s=100.0, sleep=lambda dt: (_ for _ in ()).throw(AssertionError("must not wait for a peer that left")))
+    assert e.value.reason == "left the job"
