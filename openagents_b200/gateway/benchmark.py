@@ -18,6 +18,7 @@ Reference: inference/benchmark/matrix.ts:38-54 (lanes), :60-65 (engines), :122-1
 """
 from __future__ import annotations
 
+import json
 import math
 
 from .metadata import NOT_MEASURED
@@ -329,6 +330,173 @@ def throughput_report(target: dict, samples: list[dict], concurrency_ramp, sampl
             "bestAggregate": None if best is None else {"concurrency": best["concurrency"], "aggregateTps": best["aggregateTps"]},
             "levers": {"expected": expectation, "actual": actual, "mismatches": mism},
             "sampleCount": len(samples), "okSampleCount": sum(s["status"] == "ok" for s in samples)}
+
+
+# ---------------------------------------------------------------- matrix runner and report
+# (inference/benchmark/runner.ts:30-202 run set and skipping rules; report.ts:104-272 group metrics, :550-700 report and its
+# decision-grade rule, :702-720 public-safety scan; lane-seam.ts for the seam a runner samples through)
+BENCHMARK_REPORT_SCHEMA = "openagents.khala.benchmark-report.v1"
+_FORBIDDEN_REPORT_KEYS = ("prompt\"", "completion\"", "message", "content", "account", "apikey", "api_key", "cacheaffinitykey", "pricemsat", "margin",
+                          "mnemonic", "secret")
+
+
+class FixtureLaneSeam:
+    """Deterministic samples derived from the cell and the sample index: exercises the harness and the report math, measures
+    nothing (``can_spend`` False, so a report built from it is never decision grade)."""
+    id, can_spend = "fixture", False
+
+    def sample(self, cell: dict, index: int) -> dict:
+        import zlib
+        h = zlib.crc32(f"{cell['cellId']}:{index}".encode())
+        shape = cell["shape"]
+        out = max(1, shape["outputTokens"])
+        gen_ms = out * (8 + h % 7)
+        verified = cell["verificationExpectation"] != "none"
+        return {"promptTokens": shape["inputTokens"], "completionTokens": out, "totalTokens": shape["inputTokens"] + out,
+                "cachedInputTokens": shape["cacheablePrefixTokens"], "ttftMs": 40 + h % 60, "generationWallClockMs": gen_ms,
+                "totalWallClockMs": 40 + h % 60 + gen_ms, "executedVerdict": ("passed" if h % 4 else "failed") if verified else "not_executed",
+                "verificationClass": cell["verificationExpectation"] if verified else "none", "costBasisMsat": (shape["inputTokens"] + 3 * out) * (1 + h % 3),
+                "toolCallsAttempted": 2 if "coding" in cell["workload"] else 0, "toolCallsSucceeded": (2 if h % 5 else 1) if "coding" in cell["workload"] else 0}
+
+
+class HttpLaneSeam:
+    """A real seam over an OpenAI-compatible endpoint (this package's server, or any other): one streamed chat completion per
+    sample, sized by the cell's shape; tokens from the usage object, TTFT and wall clock measured here.  ``verify(cell, text)``
+    (optional) grades the answer; ``cost_msat(prompt_tokens, completion_tokens)`` (optional) prices it.  ``lanes``: which matrix
+    lanes this endpoint answers for."""
+    id, can_spend = "real", True
+
+    def __init__(self, base_url: str, model: str, lanes=("khala",), verify=None, cost_msat=None, api_key: str | None = None, timeout: float = 300.0):
+        self.base_url, self.model, self.lanes, self.verify, self.cost_msat, self.api_key, self.timeout = base_url, model, set(lanes), verify, cost_msat, api_key, timeout
+
+    def can_execute_fixture_only_lane(self, lane: str) -> bool:
+        return lane in self.lanes
+
+    def sample(self, cell: dict, index: int) -> dict:
+        from ..serve.bench_client import streamed_chat
+        shape = cell["shape"]
+        words = max(1, shape["inputTokens"] // 2)
+        prefix = ("stable shared preamble " * (shape["cacheablePrefixTokens"] // 6 + 1))[: shape["cacheablePrefixTokens"] * 2] if shape["cacheablePrefixTokens"] else ""
+        prompt = prefix + " ".join(f"w{(index * 7919 + i) % 997}" for i in range(words))
+        scenario = {"name": cell["cellId"], "messages": [{"role": "user", "content": prompt}], "max_tokens": max(1, shape["outputTokens"]),
+                    "reasoning_effort": cell["sampling"].get("reasoningEffort", "low"), "expected": ""}
+        r = streamed_chat(self.base_url.rstrip("/") + ("" if self.base_url.rstrip("/").endswith("/v1") else "/v1"), self.api_key or "none", self.model,
+                          scenario, index)
+        if r.get("error") or r.get("http_status") != 200:
+            raise RuntimeError(f"lane request failed: {r.get('http_status')} {r.get('error')}")
+        usage = r.get("usage") or {}
+        out = {"promptTokens": usage.get("prompt_tokens"), "completionTokens": usage.get("completion_tokens"), "totalTokens": usage.get("total_tokens"),
+               "cachedInputTokens": (usage.get("prompt_tokens_details") or {}).get("cached_tokens"),
+               "ttftMs": None if r.get("ttft_seconds") is None else r["ttft_seconds"] * 1e3, "totalWallClockMs": r["total_seconds"] * 1e3,
+               "generationWallClockMs": None if r.get("ttft_seconds") is None else (r["total_seconds"] - r["ttft_seconds"]) * 1e3,
+               "executedVerdict": "not_executed", "verificationClass": "none"}
+        if self.verify is not None and cell["verificationExpectation"] != "none":
+            out["executedVerdict"], out["verificationClass"] = ("passed" if self.verify(cell, r.get("visible_output", "")) else "failed"), cell["verificationExpectation"]
+        if self.cost_msat is not None and isinstance(out["promptTokens"], int) and isinstance(out["completionTokens"], int):
+            out["costBasisMsat"] = int(self.cost_msat(out["promptTokens"], out["completionTokens"]))
+        return out
+
+
+def _skip_reason(cell: dict, seam) -> str | None:
+    if cell["laneAvailability"] == "not_yet_available":
+        return f"lane_not_yet_available:{cell['lane']}"
+    if cell["laneAvailability"] == "fixture_only" and seam.can_spend and not getattr(seam, "can_execute_fixture_only_lane", lambda lane: False)(cell["lane"]):
+        return f"lane_fixture_only:{cell['lane']}"
+    return None
+
+
+def run_benchmark(config: dict, seam, served=()) -> dict:
+    """Expand the matrix and sample every executable cell ``samplesPerCell`` times through ``seam``; a cell whose lane cannot be
+    executed is recorded once with the reason.  Every executed sample becomes a request-telemetry record."""
+    from .request_telemetry import build_record
+    cells = expand_matrix(config, served)
+    runs, executed, skipped = [], 0, 0
+    for cell in cells:
+        why = _skip_reason(cell, seam)
+        if why is not None:
+            skipped += 1
+            runs.append({"cellId": cell["cellId"], "cell": cell, "sampleIndex": 0, "record": None, "clientSurface": None, "skippedReason": why})
+            continue
+        executed += 1
+        for i in range(max(1, int(cell["samplesPerCell"]))):
+            smp = seam.sample(cell, i)
+            model = (cell.get("targetProfile") or {}).get("modelRef") or f"{cell['lane']}/{cell['engine']}"
+            rec = build_record(request_id=f"bench:{config['id']}:{cell['cellId']}:s{i}", requested_model=model, served_model=model, route=cell["workload"],
+                               provider=cell["lane"], request_class="batch" if cell["transport"] == "batch" else ("verifier_run" if cell["workload"] == "verifier-run" else "interactive_stream"),
+                               prompt_tokens=smp.get("promptTokens"), completion_tokens=smp.get("completionTokens"), total_tokens=smp.get("totalTokens"),
+                               cached_input_tokens=smp.get("cachedInputTokens"), ttft_ms=smp.get("ttftMs") if cell["transport"] == "streaming" else None,
+                               total_wall_clock_ms=smp.get("totalWallClockMs"), generation_wall_clock_ms=smp.get("generationWallClockMs"),
+                               verification_class=smp.get("verificationClass", "none"), executed_verdict=smp.get("executedVerdict", "not_executed"),
+                               cost_basis_msat=smp.get("costBasisMsat"), fallback_reason=None)
+            surface = {"toolCallsAttempted": smp["toolCallsAttempted"], "toolCallsSucceeded": smp.get("toolCallsSucceeded", 0)} if "toolCallsAttempted" in smp else None
+            runs.append({"cellId": cell["cellId"], "cell": cell, "sampleIndex": i, "record": rec, "clientSurface": surface, "skippedReason": None})
+    return {"configId": config["id"], "seamId": seam.id, "seamCanSpend": bool(seam.can_spend), "runs": runs, "cellsExpanded": len(cells),
+            "cellsExecuted": executed, "cellsSkipped": skipped}
+
+
+def _latency(values) -> dict:
+    v = [x for x in values if isinstance(x, (int, float)) and not isinstance(x, bool)]
+    return {"p50": percentile(v, 50), "p90": percentile(v, 90), "p99": percentile(v, 99), "mean": (sum(v) / len(v)) if v else None, "sampleCount": len(v)}
+
+
+def _group(runs: list[dict]) -> dict:
+    from .request_telemetry import is_measured
+    first = runs[0]["cell"]
+    done = [r for r in runs if r["record"] is not None]
+    attempted = accepted = calls = calls_ok = tin = tout = ttot = cost = 0
+    cache = []
+    for r in done:
+        rec = r["record"]
+        if rec["executedVerdict"] != "not_executed":
+            attempted += 1
+            accepted += rec["executedVerdict"] == "passed"
+        tin += rec["promptTokens"] if is_measured(rec["promptTokens"]) else 0
+        tout += rec["completionTokens"] if is_measured(rec["completionTokens"]) else 0
+        ttot += rec["totalTokens"] if is_measured(rec["totalTokens"]) else 0
+        cost += rec["costBasisMsat"] if is_measured(rec["costBasisMsat"]) else 0
+        if r["clientSurface"]:
+            calls += r["clientSurface"]["toolCallsAttempted"]
+            calls_ok += r["clientSurface"]["toolCallsSucceeded"]
+        if is_measured(rec["cachedInputTokens"]) and is_measured(rec["promptTokens"]) and rec["promptTokens"] > 0:
+            cache.append(rec["cachedInputTokens"] / rec["promptTokens"])
+    wall = _latency([r["record"]["totalWallClockMs"] for r in done])
+    return {"lane": first["lane"], "engine": first["engine"], "candidateRef": first["candidateRef"], "workload": first["workload"],
+            "laneAvailability": first["laneAvailability"], "syntheticOnly": all(r["cell"]["shape"]["provenance"] == "synthetic" for r in runs),
+            "executedSamples": len(done), "skippedSamples": len(runs) - len(done), "inputTokens": tin, "outputTokens": tout, "totalTokens": ttot,
+            "ttftMs": _latency([r["record"]["ttftMs"] for r in done]), "totalWallClockMs": wall,
+            "perceivedTps": _latency([r["record"]["perceivedTps"] for r in done]), "interTokenLatencyMs": _latency([r["record"]["interTokenLatencyMs"] for r in done]),
+            "meanWallClockMs": wall["mean"], "wallClockSamples": wall["sampleCount"],
+            "cacheHitRate": (sum(cache) / len(cache)) if cache else None, "verificationRate": None if attempted == 0 else accepted / attempted,
+            "acceptedOutcomes": accepted, "attemptedVerifications": attempted, "toolCallSuccessRate": None if calls == 0 else calls_ok / calls,
+            "toolCallsAttempted": calls, "toolCallsSucceeded": calls_ok, "costPerAcceptedOutcomeMsat": None if accepted == 0 else cost / accepted,
+            "totalCostBasisMsat": cost}
+
+
+def build_benchmark_report(run_set: dict) -> dict:
+    """One group per (lane, engine, candidate, workload) in first-seen target order.  Decision grade only when the seam measures
+    real lanes AND no group ran on synthetic-only traffic; otherwise the report says in words what it is."""
+    buckets: dict[tuple, list] = {}
+    for r in run_set["runs"]:
+        c = r["cell"]
+        buckets.setdefault((c["lane"], c["engine"], c["candidateRef"], c["workload"]), []).append(r)
+    order = list(dict.fromkeys((k[0], k[1], k[2]) for k in buckets))
+    groups = [_group(buckets[(*t, w)]) for t in order for w in WORKLOADS if (*t, w) in buckets]
+    decision = bool(run_set["seamCanSpend"]) and not any(g["syntheticOnly"] for g in groups)
+    notice = "" if decision else ("REAL MEASUREMENT, NOT DECISION-GRADE: the numbers are measurements of the executed lanes, but a group used synthetic traffic or no "
+                                  "comparator ran." if run_set["seamId"] == "real" else
+                                  "ILLUSTRATIVE ONLY: produced by the deterministic fixture lane; these numbers exercise the harness, they measure nothing.")
+    report = {"schemaVersion": BENCHMARK_REPORT_SCHEMA, "configId": run_set["configId"], "seamId": run_set["seamId"], "decisionGrade": decision,
+              "illustrativeNotice": notice, "cellsExpanded": run_set["cellsExpanded"], "cellsExecuted": run_set["cellsExecuted"],
+              "cellsSkipped": run_set["cellsSkipped"], "groups": groups}
+    report["publicSafe"] = check_report_public_safety(report)["safe"]
+    return report
+
+
+def check_report_public_safety(report: dict) -> dict:
+    """A report carries counts, latencies and refs: no prompt or completion text, no account or key material, no prices."""
+    text = json.dumps({k: v for k, v in report.items() if k != "illustrativeNotice"}).lower()
+    bad = [k for k in _FORBIDDEN_REPORT_KEYS if k in text]
+    return {"safe": not bad, "violations": bad}
 
 
 def main(argv=None) -> int:
