@@ -117,3 +117,30 @@ def test_a5_rollouts_grading_and_dpo():
     assert c.dpo_pair_loss(0.1, -1.0, -1.0, -1.0, -1.0) == pytest.approx(np.log(2))
     assert c.dpo_pair_loss(0.5, -1.0, -5.0, -2.0, -2.0) < np.log(2) < c.dpo_pair_loss(0.5, -5.0, -1.0, -2.0, -2.0)
     assert c.softplus(800.0) == 800.0 and c.softplus(-800.0) == 0.0
+
+
+def test_a1_published_run_is_reproduced():
+    """The reference's published two-device run (seeded from its tokenizer shard digest): the initial parameter state digest is
+    reproduced bit for bit (seeded stream, initialisation and the JSON number format of the digest), and the validation-loss curve
+    to a few units in the last place (the vectorised forward sums in another order than the reference's scalar loops, which is
+    also why later state digests are not expected to match)."""
+    cfg = c.A1Config()
+    p0 = c.reference_initial_parameters(cfg, c.PUBLISHED_SEED_DIGEST_HEX)
+    assert p0.size == 2244 and c.reference_state_digest(c.PUBLISHED_SEED_DIGEST_HEX, 0, p0) == c.PUBLISHED_INITIAL_STATE_DIGEST_HEX
+    r = c.run_training(cfg, seed_digest_hex=c.PUBLISHED_SEED_DIGEST_HEX)
+    got = [s["validationLoss"] for s in r["steps"]]
+    assert len(got) == 7 and all(abs(a - b) < 1e-12 for a, b in zip(got, c.PUBLISHED_VALIDATION_LOSSES)), got
+    assert got[0] > 3.4657359027997265 > got[1]                       # the run's budget: below ln(32) after the first step
+    perm = c.reference_permutation(f"cs336_a1.real_grad.structure.{c.PUBLISHED_SEED_DIGEST_HEX}", 32)
+    assert sorted(perm) == list(range(32))
+    seqs = c.reference_sequences(cfg, c.PUBLISHED_SEED_DIGEST_HEX, "train:0", 48)
+    follows = sum(int(perm[a] == b) for s in seqs for a, b in zip(s[:-1], s[1:])) / (48 * 16)
+    assert 0.8 < follows < 0.95                                       # structure bias 0.85 (+ uniform draws that happen to agree)
+
+
+def test_js_number_formatting_matches_json_stringify():
+    cases = {0.1: "0.1", 1e-7: "1e-7", 1.5e-7: "1.5e-7", 0.000001: "0.000001", 123456789012345680000.0: "123456789012345680000", 1e21: "1e+21",
+             -0.14433756729740643: "-0.14433756729740643", 1.0: "1", 100.0: "100", 2.5e-10: "2.5e-10", 1234.5: "1234.5", 5e-324: "5e-324",
+             0.00001234: "0.00001234", 0.0: "0", -0.0: "0", 1.7976931348623157e308: "1.7976931348623157e+308", 4294967296.0: "4294967296"}
+    for x, want in cases.items():
+        assert c.js_number(x) == want, (x, c.js_number(x), want)
