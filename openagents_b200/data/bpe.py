@@ -56,6 +56,7 @@ class ByteBpe:
         self.merges, self.pieces, self.special = [tuple(m) for m in merges], pieces, list(special or [])
         arr = np.asarray(self.merges, dtype=np.int32).reshape(-1, 2)
         self._h = _lib().b200_bpe_encoder(arr.ctypes.data if len(arr) else None, len(arr))
+        self._free = _lib().b200_bpe_encoder_free          # bound now: module globals may be gone when __del__ runs at shutdown
         if not self._h:
             raise ValueError("a merge names an id that does not exist yet")
         self.vocab: list[bytes] = [bytes([i]) for i in range(256)]
@@ -127,5 +128,5 @@ class ByteBpe:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            _lib().b200_bpe_encoder_free(self._h)
+            self._free(self._h)
             self._h = None

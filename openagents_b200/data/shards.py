@@ -76,6 +76,7 @@ class TokenDataset:
         paths = [str(p) for p in ([paths] if isinstance(paths, (str, Path)) else paths)]
         arr = (_cp * len(paths))(*[p.encode() for p in paths])
         self._h = _lib().b200_tokds_open(arr, len(paths), seq_len, raw_width)
+        self._free = _lib().b200_tokds_close               # bound now: module globals may be gone when __del__ runs at shutdown
         err = _lib().b200_tokds_error(self._h)
         if err:
             msg = err.decode()
@@ -97,7 +98,7 @@ class TokenDataset:
 
     def close(self):
         if getattr(self, "_h", None):
-            _lib().b200_tokds_close(self._h)
+            self._free(self._h)
             self._h = None
 
     def __del__(self):
@@ -116,11 +117,11 @@ class BatchLoader:
         rows = accum * micro_batch
         lib = _lib()
         self._h = lib.b200_loader_create(ds._h, rows, rank, world, seed, start_batch, int(shuffle), threads)
+        self._free = lib.b200_loader_destroy
         err = lib.b200_loader_error(self._h)
         if err:
             msg = err.decode()
-            lib.b200_loader_destroy(self._h)
-            self._h = None
+            self.close()
             raise ValueError(msg)
         pin = torch.cuda.is_available() if pin is None else pin
         self._bufs = []
@@ -159,7 +160,7 @@ class BatchLoader:
 
     def close(self):
         if getattr(self, "_h", None):
-            _lib().b200_loader_destroy(self._h)
+            self._free(self._h)
             self._h = None
 
     def __del__(self):

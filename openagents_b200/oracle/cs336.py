@@ -337,8 +337,9 @@ def _run_training_reference_seeded(c: A1Config, seed: str) -> dict:
 FIELD_MODULUS = 2 ** 31 - 1
 
 
-def bpe_train(data: bytes, n_merges: int = 24) -> dict:
-    """Byte-level BPE: repeatedly merge the most frequent adjacent pair (ties: lowest pair)."""
+def bpe_train(data: bytes, n_merges: int = 24, min_count: int = 1) -> dict:
+    """Byte-level BPE: repeatedly merge the most frequent adjacent pair (ties: lowest pair); stops when the best pair occurs
+    fewer than ``min_count`` times."""
     ids = list(data)
     merges = []
     for k in range(n_merges):
@@ -348,6 +349,8 @@ def bpe_train(data: bytes, n_merges: int = 24) -> dict:
         if not counts:
             break
         best = max(counts.items(), key=lambda kv: (kv[1], -kv[0][0], -kv[0][1]))[0]
+        if counts[best] < min_count:
+            break
         new_id = 256 + k
         merges.append((best[0], best[1], new_id))
         out, i = [], 0
@@ -361,6 +364,29 @@ def bpe_train(data: bytes, n_merges: int = 24) -> dict:
         ids = out
     digest = hashlib.sha256(json_bytes({"merges": merges, "tokenCount": len(ids)})).hexdigest()
     return {"merges": merges, "tokenIds": ids, "digestHex": digest}
+
+
+# the reference's committed four-line corpus and merge budget (cs336-a1-homework-workload.ts:22-29); its shard digest is the seed
+# of the published A1 / A3 runs
+A1_DEMO_CORPUS = "\n".join(["one day a little robot found a shiny coin on the floor", "the robot gave the coin to a small bird and the bird sang",
+                            "they walked to the lake and watched the slow boats together", "the bird said thank you and the robot beeped a happy song"])
+A1_MERGE_BUDGET = 24
+
+
+def tokenizer_shard(corpus: str = A1_DEMO_CORPUS, merge_budget: int = A1_MERGE_BUDGET) -> dict:
+    """The tokenizer shard of the homework workload (:132-169): byte-level BPE that stops early when the best pair occurs only
+    once, committed by SHA-256 over the merge table and the final token stream."""
+    data = corpus.encode()
+    r = bpe_train(data, merge_budget, min_count=2)
+    body = {"corpusByteLength": len(data), "mergeBudget": merge_budget, "merges": [list(m) for m in r["merges"]], "tokens": r["tokenIds"]}
+    return {"digestHex": hashlib.sha256(json_bytes_ordered(body)).hexdigest(), "mergeCount": len(r["merges"]), "tokenCount": len(r["tokenIds"]),
+            "vocabularySize": 256 + len(r["merges"])}
+
+
+def json_bytes_ordered(obj) -> bytes:
+    """``JSON.stringify`` of an object whose keys are already in insertion order."""
+    import json
+    return json.dumps(obj, separators=(",", ":")).encode()
 
 
 def json_bytes(obj) -> bytes:

@@ -144,3 +144,16 @@ def test_js_number_formatting_matches_json_stringify():
              0.00001234: "0.00001234", 0.0: "0", -0.0: "0", 1.7976931348623157e308: "1.7976931348623157e+308", 4294967296.0: "4294967296"}
     for x, want in cases.items():
         assert c.js_number(x) == want, (x, c.js_number(x), want)
+
+
+def test_a1_tokenizer_shard_digest_is_the_published_seed():
+    """The reference's committed corpus through the BPE gives the shard digest that seeds its published runs; the native trainer
+    learns the same merges."""
+    from openagents_b200.data import ByteBpe
+    shard = c.tokenizer_shard()
+    assert shard["digestHex"] == c.PUBLISHED_SEED_DIGEST_HEX
+    assert shard == {"digestHex": c.PUBLISHED_SEED_DIGEST_HEX, "mergeCount": 24, "tokenCount": 127, "vocabularySize": 280}
+    native = ByteBpe.train(c.A1_DEMO_CORPUS.encode(), 24, pieces="none")
+    assert native.merges == [(a, b) for a, b, _ in c.bpe_train(c.A1_DEMO_CORPUS.encode(), 24)["merges"]]
+    assert len(native.encode(c.A1_DEMO_CORPUS)) == 127
+    assert c.tokenizer_shard("abcdefg", 24)["mergeCount"] == 0           # no pair occurs twice: nothing is merged
