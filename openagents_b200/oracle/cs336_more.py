@@ -288,7 +288,7 @@ def run_refinery_stage(stage: str, shard_digest_hex: str, document_count: int = 
     docs = build_synthetic_corpus(shard_digest_hex, document_count, lines_per_document)
     body, stats = {"pii_masking": pii_masking, "exact_line_dedup": exact_line_dedup, "gopher_rules": gopher_rules,
                    "minhash_dedup": lambda d: minhash_dedup(d, shard_digest_hex)}[stage](docs)
-    digest = sha256_json({"outputBody": body, "shardDigestHex": shard_digest_hex, "stage": stage, "stats": stats, "workloadRef": A4_WORKLOAD_REF})
+    digest = sha256_json({"output": body, "shardDigestHex": shard_digest_hex, "stage": stage, "stats": stats, "workloadRef": A4_WORKLOAD_REF})
     return {"stage": stage, "inputDocumentCount": len(docs), "stats": stats, "outputDigestHex": digest, "workloadRef": A4_WORKLOAD_REF}
 
 

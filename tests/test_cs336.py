@@ -157,3 +157,26 @@ def test_a1_tokenizer_shard_digest_is_the_published_seed():
     assert native.merges == [(a, b) for a, b, _ in c.bpe_train(c.A1_DEMO_CORPUS.encode(), 24)["merges"]]
     assert len(native.encode(c.A1_DEMO_CORPUS)) == 127
     assert c.tokenizer_shard("abcdefg", 24)["mergeCount"] == 0           # no pair occurs twice: nothing is merged
+
+
+def test_a4_and_a5_published_digests_are_reproduced():
+    """The refinery stages and the roll-out / grading stages, seeded from the tokenizer shard digest like the reference's paid runs,
+    give the output digests and counts those runs published (apps/openagents.com/docs/2026-06-11-cs336-a4-data-refinery-workload-and-
+    admission-evidence.md:69-74, 2026-06-11-cs336-a5-rollout-grading-paid-evidence.md:74-79)."""
+    from openagents_b200.oracle import cs336_more as m
+    seed = c.PUBLISHED_SEED_DIGEST_HEX
+    a4 = {"pii_masking": ("0e8f05fc4ab90be1", {"maskedEmails": 62, "maskedPhones": 62, "maskedIpv4": 62, "maskedTotal": 186}),
+          "gopher_rules": ("ce6843a936165413", {"inputDocuments": 64, "keptDocuments": 56, "rejectedLowAlphaRatio": 5, "rejectedSymbolHeavy": 3}),
+          "exact_line_dedup": ("ee9cc8600064add3", {"inputLines": 384, "removedLines": 181, "uniqueLines": 203}),
+          "minhash_dedup": ("5719cb8f68e5e5b2", {"inputDocuments": 64, "removedDocuments": 16, "confirmedNearDuplicatePairs": 16, "nearDuplicateClusters": 48})}
+    for stage, (prefix, counts) in a4.items():
+        r = m.run_refinery_stage(stage, seed)
+        assert r["outputDigestHex"].startswith(prefix), (stage, r["outputDigestHex"])
+        assert {k: r["stats"][k] for k in counts} == counts
+    a5 = {"split_a": ("136c47278a947675", "9eb8041009e49735", 83, 4), "split_b": ("9e888bdce419bcbb", "d7554d7274b75a95", 69, 8)}
+    for split, (rollout_prefix, grading_prefix, correct, unparseable) in a5.items():
+        rb = m.run_rollout_batch(seed, split)
+        assert rb["outputDigestHex"].startswith(rollout_prefix) and len(rb["rollouts"]) == 128
+        g = m.grade_rollouts(rb["rollouts"], m.build_tasks(seed, split), split)
+        assert g["outputDigestHex"].startswith(grading_prefix) and round(g["accuracy"] * 128) == correct
+        assert g["stats"].get("unparseableCount", g["stats"].get("unparseable")) == unparseable
