@@ -111,3 +111,33 @@ def test_capability_envelope_needs_a_verified_self_test():
     assert ts.strip_unreceipted_capability(refs) == ["capability.other"]
     assert ts.strip_unreceipted_capability(["capability.other", r["receiptRef"]]) == ["capability.other"]
     assert ts.strip_unreceipted_capability(refs + [r["receiptRef"]]) == refs + [r["receiptRef"]]
+
+
+def _reference_fixtures():
+    """The reference's own fixture files, when its tree sits beside this repository (or where ``OPENAGENTS_REFERENCE_TREE`` points)."""
+    import os
+    root = Path(os.environ.get("OPENAGENTS_REFERENCE_TREE") or Path(__file__).resolve().parents[2] / "reference")
+    d = root / "packages" / "tassadar-executor" / "fixtures"
+    return d if (d / "tassadar-compiled-program-corpus-v1.json").exists() else None
+
+
+@pytest.mark.skipif(_reference_fixtures() is None, reason="the reference tree is not beside this repository")
+def test_every_reference_fixture_replays_digest_for_digest():
+    """The compiled-program corpus (backward-branch sum, multiply-add, load/store round trip, factorial countdown, stack comparison
+    ladder), the loop-sum fixture and the dense-weight module: trace digest, final row, emitted outputs and halt flag all equal what
+    the reference's fixture generator recorded."""
+    d = _reference_fixtures()
+    corpus = json.loads((d / "tassadar-compiled-program-corpus-v1.json").read_text())
+    assert corpus["programCount"] == len(corpus["fixtures"]) >= 5
+    for fx in corpus["fixtures"] + [json.loads((d / "tassadar-poc-loop-sum-v1.json").read_text())]:
+        tr = ts.execute_numeric_model(fx["model"], fx["steps"])
+        out = ts.collect_interpreter_outputs(tr["stepOutputs"])
+        assert tr["traceDigest"] == fx["expectedTraceDigest"], fx["fixtureId"]
+        assert list(tr["stepOutputs"][-1]) == fx["expectedFinalRow"] and out["outputs"] == fx["expectedOutputs"], fx["fixtureId"]
+        if "halted" in fx:
+            assert out["halted"] == fx["halted"]
+        verdict = ts.verify_full_replay(fx["model"], fx["steps"], fx["expectedTraceDigest"], "validator.local")
+        assert verdict["outcome"] == "verified" and verdict["rejection"] is None
+    dense = json.loads((d / "tassadar-dense-weight-module-v1.json").read_text())
+    tr = ts.execute_dense_module(dense["denseModule"], dense["steps"])
+    assert tr["traceDigest"] == dense["expectedTraceDigest"] and list(tr["stepOutputs"][-1]) == dense["expectedFinalRow"]
