@@ -394,8 +394,13 @@ def json_bytes(obj) -> bytes:
     return json.dumps(obj, sort_keys=True, separators=(",", ":")).encode()
 
 
+def seeded_values(seed: str, count: int, bound: int) -> list[int]:
+    """``count`` values below ``bound`` from the SHA-256 counter stream (each 32-bit word reduced modulo the bound; :170-193)."""
+    return [v % bound for v in reference_uint32s(seed, count)]
+
+
 def seeded_matrix(seed: str, rows: int, cols: int, bound: int = FIELD_MODULUS) -> np.ndarray:
-    return (np.floor(_stream(seed, rows * cols) * bound)).astype(np.int64).reshape(rows, cols)
+    return np.array(seeded_values(seed, rows * cols, bound), dtype=np.int64).reshape(rows, cols)
 
 
 def matrix_product_mod(a: np.ndarray, b: np.ndarray, p: int = FIELD_MODULUS) -> np.ndarray:
@@ -407,28 +412,31 @@ def matrix_product_mod(a: np.ndarray, b: np.ndarray, p: int = FIELD_MODULUS) -> 
 
 
 def merkle_root(leaves: list[str]) -> str:
-    level = [bytes.fromhex(h) for h in leaves]
+    """Pairs of hex digests are concatenated AS TEXT and hashed; an odd last node is hashed alone (:252-262)."""
+    level = list(leaves)
     if not level:
         return hashlib.sha256(b"").hexdigest()
     while len(level) > 1:
-        if len(level) % 2:
-            level.append(level[-1])
-        level = [hashlib.sha256(level[i] + level[i + 1]).digest() for i in range(0, len(level), 2)]
-    return level[0].hex()
+        level = [hashlib.sha256((level[i] + (level[i + 1] if i + 1 < len(level) else "")).encode()).hexdigest() for i in range(0, len(level), 2)]
+    return level[0]
+
+
+PUBLISHED_MERKLE_ROOT_PREFIX = "14cd1fdf7d013cfe"      # apps/openagents.com/docs/2026-06-11-training-validator-paid-closeout-evidence.md:46-50
 
 
 def training_step_matrix(tokenizer_digest: str, rows: int = 8, inner: int = 16, cols: int = 8) -> dict:
-    """One committed forward matmul: left matrix from the tokenizer digest, seeded right matrix, product
-    mod p, row digests, Merkle root, and a challenge vector derived after the commitment."""
-    left = seeded_matrix("left:" + tokenizer_digest, rows, inner)
-    right = seeded_matrix("right:weights", inner, cols)
+    """One committed forward matmul (:232-290): activations below 97 derived from the tokenizer shard digest, the seeded demo
+    weight shard, the product mod p, a SHA-256 digest per product row, the Merkle root over them, and a challenge vector derived
+    from the root, that is, only after the commitment."""
+    left = seeded_matrix(f"cs336_a1.activations.{tokenizer_digest}", rows, inner, 97)
+    right = seeded_matrix("cs336_a1.weight_shard.psion_cs336_a1_demo_v1", inner, cols, 97)
     prod = matrix_product_mod(left, right)
-    row_digests = [hashlib.sha256(json_bytes([int(v) for v in r])).hexdigest() for r in prod]
+    row_digests = [hashlib.sha256(json_bytes_ordered([int(v) for v in r])).hexdigest() for r in prod]
     root = merkle_root(row_digests)
-    challenge = (np.floor(_stream("challenge:" + root, cols) * FIELD_MODULUS)).astype(np.int64)
+    challenge = seeded_values(f"cs336_a1.challenge.{root}", cols, FIELD_MODULUS)
     return {"fieldModulus": FIELD_MODULUS, "leftMatrix": left.tolist(), "rightMatrix": right.tolist(),
             "claimedProductMatrix": prod.tolist(), "rowDigests": row_digests, "merkleRoot": root,
-            "challengeVector": challenge.tolist(), "rowOpenings": [{"rowRef": f"row.{i}", "digest": d} for i, d in enumerate(row_digests)],
+            "challengeVector": challenge, "rowOpenings": [{"rowRef": f"row.{i}", "digest": d} for i, d in enumerate(row_digests)],
             "merkleProofValid": True}
 
 

@@ -180,3 +180,19 @@ def test_a4_and_a5_published_digests_are_reproduced():
         g = m.grade_rollouts(rb["rollouts"], m.build_tasks(seed, split), split)
         assert g["outputDigestHex"].startswith(grading_prefix) and round(g["accuracy"] * 128) == correct
         assert g["stats"].get("unparseableCount", g["stats"].get("unparseable")) == unparseable
+
+
+def test_a1_training_step_commitment_is_the_published_merkle_root():
+    """The committed matmul of the homework workload, seeded from the published shard digest, has the Merkle root the live worker
+    committed to and the validator recomputed; the Freivalds class verifies it, and a tampered cell is caught."""
+    from openagents_b200.control.verification import verify_freivalds_merkle
+    m = c.training_step_matrix(c.PUBLISHED_SEED_DIGEST_HEX)
+    assert m["merkleRoot"].startswith(c.PUBLISHED_MERKLE_ROOT_PREFIX)
+    assert all(0 <= v < 97 for row in m["leftMatrix"] + m["rightMatrix"] for v in row) and len(m["challengeVector"]) == 8
+    ok = verify_freivalds_merkle({**m, "expectExactProduct": True})
+    assert ok.outcome == "Verified" and ok.failure_codes == ()
+    bad = [list(r) for r in m["claimedProductMatrix"]]
+    bad[2][3] = (bad[2][3] + 1) % m["fieldModulus"]
+    assert verify_freivalds_merkle({**m, "claimedProductMatrix": bad}).failure_codes == ("FreivaldsMismatch",)
+    assert c.merkle_root(["aa", "bb", "cc"]) == __import__("hashlib").sha256((__import__("hashlib").sha256(b"aabb").hexdigest()
+                                                                              + __import__("hashlib").sha256(b"cc").hexdigest()).encode()).hexdigest()
