@@ -132,10 +132,13 @@ def run_sweep_cell(compute_budget_flops: float, rank: int, shard_digest_hex: str
         O -= LEARNING_RATE * np.outer(err, x)
         I[ctx] -= LEARNING_RATE * grad_ctx
     final = _eval_loss(I, O, eval_scope)
-    body = {"computeBudgetFlops": compute_budget_flops, "finalLoss": repr(final), "initialLoss": repr(initial),
-            "parameterCount": n_params, "rank": rank, "shardDigestHex": shard_digest_hex, "tokenCount": tokens,
-            "trainedDataUnits": trained, "workloadRef": A3_WORKLOAD_REF}
-    return {**body, "finalLoss": final, "initialLoss": initial, "outputDigestHex": sha256_json(body)}
+    # the committed body (:352-363): losses with 17 significant digits; a run cut short for a test also commits to where it stopped
+    body = {"computeBudgetFlops": compute_budget_flops, "finalLoss": format(final, ".17g"), "initialLoss": format(initial, ".17g"),
+            "parameterCount": n_params, "rank": rank, "shardDigestHex": shard_digest_hex, "tokenCount": tokens}
+    if max_tokens is not None:
+        body["trainedDataUnits"] = trained
+    body["workloadRef"] = A3_WORKLOAD_REF
+    return {**body, "trainedDataUnits": trained, "finalLoss": final, "initialLoss": initial, "outputDigestHex": sha256_json(body)}
 
 
 # ---------------------------------------------------------------- A4
