@@ -24,7 +24,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xcompiler",
 # measurement builds: B200_NVCC_DEFINES="QGEMM_STAMPS" compiles the in-kernel cycle counters (part of the flag digest, so
 # switching it on or off rebuilds)
 NVCC_FLAGS += ["-D" + d for d in os.environ.get("B200_NVCC_DEFINES", "").replace(",", " ").split()]
-CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-fopenmp", "-Wall", "-Wno-unused-function"]
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-fopenmp", "-Wall", "-Wno-unused-function", "-ffp-contract=off"]
 
 
 def _sources(sub: str, exts: tuple[str, ...]) -> list[Path]:
@@ -34,7 +34,7 @@ def _sources(sub: str, exts: tuple[str, ...]) -> list[Path]:
 
 def host_sources() -> list[Path]:
     out = []
-    for sub in ("gguf", "kv", "data", "host"):
+    for sub in ("gguf", "kv", "data", "oracle", "host"):
         if (CSRC / sub).is_dir():
             out += _sources(sub, (".cpp",))
     return out

@@ -537,3 +537,56 @@ def dpo_pair_loss(beta: float, pol_chosen: float, pol_rejected: float, ref_chose
     """-log sigmoid(r_chosen - r_rejected) written with softplus."""
     margin = dpo_implicit_reward(beta, pol_chosen, ref_chosen) - dpo_implicit_reward(beta, pol_rejected, ref_rejected)
     return softplus(-margin)
+
+
+# ---- the same run with the reference's ORDER of floating-point operations (native; csrc/oracle/a1_ordered.cpp)
+PUBLISHED_FINAL_STATE_DIGEST_HEX = "bda8a9edba1c18da74e4c138d66da65888d3fe51f9ae4538b9046f7d701bdbb3"
+
+
+def _ordered_lib():
+    import ctypes
+    from .. import _native
+    lib = _native.host()
+    if not getattr(lib, "_a1_ready", False):
+        dp, ip = ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_int32)
+        lib.b200_a1_shard_gradient.argtypes, lib.b200_a1_shard_gradient.restype = [ctypes.c_int] * 4 + [dp, ip, ctypes.c_int, dp], ctypes.c_double
+        lib.b200_a1_mean_loss.argtypes, lib.b200_a1_mean_loss.restype = [ctypes.c_int] * 4 + [dp, ip, ctypes.c_int], ctypes.c_double
+        lib.b200_a1_sgd_step.argtypes, lib.b200_a1_sgd_step.restype = [ctypes.c_uint64, dp, ctypes.POINTER(dp), ctypes.c_int, ctypes.c_double, dp], None
+        lib.b200_a1_det_exp.argtypes, lib.b200_a1_det_exp.restype = [ctypes.c_double], ctypes.c_double
+        lib.b200_a1_det_ln.argtypes, lib.b200_a1_det_ln.restype = [ctypes.c_double], ctypes.c_double
+        lib._a1_ready = True
+    return lib
+
+
+def reference_shard_gradient_digest(seed_digest_hex: str, step: int, shard: int, grad: np.ndarray) -> str:
+    label = f"cs336_a1.real_grad.shard_gradient.{seed_digest_hex}.step_{step}.shard_{shard}"
+    return hashlib.sha256(('{"label":"' + label + '","values":[' + ",".join(js_number(float(v)) for v in grad) + "]}").encode()).hexdigest()
+
+
+def run_training_ordered(c: A1Config = A1Config(), seed_digest_hex: str = PUBLISHED_SEED_DIGEST_HEX) -> dict:
+    """The reference trajectory digest for digest: scalar loops in the reference's order with its deterministic exp and ln."""
+    import ctypes
+    lib = _ordered_lib()
+    dp, ip = ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_int32)
+    dims = (c.d_model, c.d_ff, c.vocabulary_size, c.sequence_length)
+    params = np.ascontiguousarray(reference_initial_parameters(c, seed_digest_hex))
+    train = [np.ascontiguousarray(reference_sequences(c, seed_digest_hex, f"train:{s}", c.train_sequences_per_shard), dtype=np.int32) for s in range(c.shard_count)]
+    val = np.ascontiguousarray(reference_sequences(c, seed_digest_hex, "val", c.validation_sequence_count), dtype=np.int32)
+
+    def vloss(p):
+        return float(lib.b200_a1_mean_loss(*dims, p.ctypes.data_as(dp), val.ctypes.data_as(ip), len(val)))
+    steps = [{"step": 0, "validationLoss": vloss(params), "stateDigest": reference_state_digest(seed_digest_hex, 0, params)}]
+    for step in range(c.step_count):
+        grads, shard_losses = [], []
+        for t in train:
+            g = np.zeros_like(params)
+            shard_losses.append(float(lib.b200_a1_shard_gradient(*dims, params.ctypes.data_as(dp), t.ctypes.data_as(ip), len(t), g.ctypes.data_as(dp))))
+            grads.append(g)
+        nxt = np.zeros_like(params)
+        arr = (dp * len(grads))(*[g.ctypes.data_as(dp) for g in grads])
+        lib.b200_a1_sgd_step(params.size, params.ctypes.data_as(dp), arr, len(grads), c.learning_rate, nxt.ctypes.data_as(dp))
+        digests = [reference_shard_gradient_digest(seed_digest_hex, step, s, g) for s, g in enumerate(grads)]
+        params = nxt
+        steps.append({"step": step + 1, "validationLoss": vloss(params), "stateDigest": reference_state_digest(seed_digest_hex, step + 1, params),
+                      "gradientDigests": digests, "shardLosses": shard_losses})
+    return {"parameterCount": int(params.size), "steps": steps, "finalParams": params}

@@ -196,3 +196,24 @@ def test_a1_training_step_commitment_is_the_published_merkle_root():
     assert verify_freivalds_merkle({**m, "claimedProductMatrix": bad}).failure_codes == ("FreivaldsMismatch",)
     assert c.merkle_root(["aa", "bb", "cc"]) == __import__("hashlib").sha256((__import__("hashlib").sha256(b"aabb").hexdigest()
                                                                               + __import__("hashlib").sha256(b"cc").hexdigest()).encode()).hexdigest()
+
+
+def test_a1_ordered_oracle_reproduces_the_published_run_digest_for_digest():
+    """The native oracle keeps the reference's order of floating-point operations and its deterministic exp / ln: the seven
+    validation losses of the published two-device run are equal to the last bit and the merged final state has the published
+    SHA-256 digest.  The vectorised oracle agrees with it to rounding."""
+    import numpy as np
+    r = c.run_training_ordered()
+    assert [s["validationLoss"] for s in r["steps"]] == list(c.PUBLISHED_VALIDATION_LOSSES)
+    assert r["steps"][0]["stateDigest"] == c.PUBLISHED_INITIAL_STATE_DIGEST_HEX
+    assert r["steps"][-1]["stateDigest"] == c.PUBLISHED_FINAL_STATE_DIGEST_HEX
+    assert all(len(s["gradientDigests"]) == 2 and s["gradientDigests"][0] != s["gradientDigests"][1] for s in r["steps"][1:])
+    v = c.run_training(c.A1Config(), seed_digest_hex=c.PUBLISHED_SEED_DIGEST_HEX)
+    assert np.abs(v["finalParams"] - r["finalParams"]).max() < 1e-12
+    lib = c._ordered_lib()
+    import math
+    for x in (-3.7, -0.1, 0.0, 0.5, 2.0, 11.3):
+        assert abs(lib.b200_a1_det_exp(x) - math.exp(x)) <= 4e-15 * math.exp(x)
+    for x in (1e-9, 0.3, 1.0, 1.5, 2.0, 77.7):
+        assert abs(lib.b200_a1_det_ln(x) - math.log(x)) <= 1e-15 * max(1.0, abs(math.log(x)))
+    assert lib.b200_a1_det_exp(-701.0) == 0.0 and lib.b200_a1_det_ln(1.0) == 0.0
