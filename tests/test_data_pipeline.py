@@ -162,3 +162,16 @@ def test_loader_with_every_slot_and_thread_count_delivers_the_same_stream(tmp_pa
         ld.close()
         ref = ref or got
         assert all(torch.equal(a, b) for a, b in zip(got, ref)), (slots, threads)
+
+
+def test_loader_ring_protocol_is_checked_on_every_interleaving():
+    """The slot ring of the loader as a model: safe and live on every interleaving of 2 slots x 2 workers x 5 batches and of
+    3 slots x 3 workers x 5 batches; the two broken variants are caught (out-of-order delivery; the ring stalls)."""
+    from openagents_b200.data.loader_model import check_loader_ring
+    for slots, workers in ((2, 2), (3, 3), (2, 3)):
+        r = check_loader_ring(slots, workers, 5)
+        assert r["safety"].ok and r["safety"].states > 100, r["safety"]
+        assert r["every_batch_is_delivered"].ok
+        bad = r["mutation_worker_ignores_expected_batch"]
+        assert not bad.ok and bad.violated in ("invariant delivered_in_order_exactly_once", "invariant one_filler_per_slot") and bad.trace
+        assert not r["mutation_release_keeps_expected_batch"].ok
