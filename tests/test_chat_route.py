@@ -177,3 +177,47 @@ def test_model_gating_table_and_billing_modes(state):
     assert kinds == ["external", "internal"]
     # a model without a row is not gated
     assert gw.handle("Bearer plain", body("qwen-tiny"))[0] == 200
+
+
+def test_gateway_reaches_a_live_model_server_across_the_process_boundary(tmp_path):
+    """The whole serving call stack with the hop that is a process boundary in production: gateway route -> lane plan ->
+    admitted network adapter (registration + heartbeat + payout snapshot) -> serve wire contract over the HTTP transport with a
+    bearer token -> this package's model server (``/v1/serve``: tokenize, prefill, decode, a second greedy decode for parity) ->
+    normalised response, stage-count and parity gates, receipt, metering.  A node that stops heart-beating is refused before
+    any request leaves."""
+    import threading
+    import time
+    from datetime import datetime, timezone
+    from openagents_b200.serve.server import serve
+    cfg = TINY_LLAMA.with_(vocab=512, d_model=64, n_heads=2, n_kv_heads=1, head_dim=32, ffn=128)
+    p = str(tmp_path / "tiny.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 0), PLAN_Q8_0)
+    live = ServerState([ServedModel("qwen-tiny", CpuBackend.from_gguf(p), mf.artifact_digest(p), max_num_seqs=4)])
+    httpd = serve(live, "127.0.0.1", 0)
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    try:
+        now = [time.time()]
+        hb = [datetime.fromtimestamp(now[0], timezone.utc).strftime("%Y-%m-%dT%H:%M:%SZ")]
+        snap = lambda: fb.ServingSnapshot("pylon.b200.1", "active", ("capability.serve.qwen-tiny",), ("lane.openagents-network",), hb[0], "healthy", True, "spark.target.1")
+        transport = fb.make_http_transport(f"http://127.0.0.1:{httpd.server_address[1]}/v1/serve", "node-bearer-token")
+        adapter = fb.OpenAgentsNetworkAdapter(dispatch=fb.dispatch_psionic_serve(transport),
+                                              admission=lambda: fb.decide_admission(snap(), "capability.serve.qwen-tiny", int(now[0] * 1000)))
+        reg = fb.ProviderRegistry()
+        reg.register(_Failing(rt.FIREWORKS, fb.InferenceAdapterError(rt.FIREWORKS, "rate_limited", "429", True, 429)))
+        reg.register(adapter)
+        gw = cr.ChatGateway(reg, [cr.ApiKey("k1", "acct1", balance_msat=10_000)])
+        status, out = gw.handle("Bearer k1", json.dumps(BODY))
+        assert status == 200, out
+        ext = out["openagents"]
+        assert ext["route"] == "openagents-network" and ext["receipt"]["parityVerified"] is True and ext["receipt"]["sharded"] is False
+        assert out["usage"]["completion_tokens"] == 8 and gw.keys["k1"].balance_msat == 10_000 - ext["price_msat"]
+        stats = live.model("qwen-tiny").sched.stats
+        assert stats["requests"] >= 2                                  # the answer and its parity replay ran on the server
+        # the node goes quiet: the admission gate refuses before dispatch, nothing reaches the server, the caller gets a typed failure
+        served_before = stats["requests"]
+        now[0] += 600
+        status, out = gw.handle("Bearer k1", json.dumps(BODY))
+        assert status >= 400 and "heartbeat_stale" in json.dumps(out)
+        assert live.model("qwen-tiny").sched.stats["requests"] == served_before
+    finally:
+        httpd.shutdown()
