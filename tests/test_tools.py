@@ -153,3 +153,58 @@ def test_server_tool_calls_non_stream_and_stream():
         assert json.loads(text)["choices"][0]["message"]["content"] == answer
     finally:
         httpd.shutdown()
+
+
+def test_attach_client_doctor_smoke_and_tool_loop_against_a_live_server(tmp_path, capsys):
+    """The local attach path: base-URL resolution, the health and model-row contract, a smoke completion, and a completion with a
+    tool loop whose records carry digests and lengths only."""
+    import threading
+    from openagents_b200.models.config import TINY_LLAMA
+    from openagents_b200.models.weights import PLAN_Q8_0, random_weights, save_gguf
+    from openagents_b200.receipts import manifests as mf
+    from openagents_b200.serve import attach_client as ac
+    from openagents_b200.serve.backend import CpuBackend
+    from openagents_b200.serve.server import ServedModel, ServerState, serve
+    assert ac.resolve_base_url("http://a/v1/", {}) == "http://a/v1"
+    assert ac.resolve_base_url(None, {"PROBE_PSIONIC_BASE_URL": "http://c/v1", "PYLON_PSIONIC_BASE_URL": "http://b/v1"}) == "http://b/v1"
+    assert ac.resolve_base_url(None, {"PROBE_PSIONIC_BASE_URL": "http://c/v1"}) == "http://c/v1" and ac.resolve_base_url(None, {}) == ac.DEFAULT_BASE_URL
+    assert ac.admit_model_row({"id": "m", "artifact_digest": "sha256:" + "a" * 64})["admitted"]
+    assert ac.admit_model_row({"id": "m", "manifest_ref": "manifest.models.m.v1"})["admitted"]
+    assert not ac.admit_model_row({"id": "m", "artifact_digest": "md5:abc", "manifest_ref": "/home/me/m.json"})["admitted"]
+    cfg = TINY_LLAMA.with_(vocab=512, d_model=64, n_heads=2, n_kv_heads=1, head_dim=32, ffn=128)
+    p = str(tmp_path / "tiny.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 0), PLAN_Q8_0)
+    httpd = serve(ServerState([ServedModel("tiny", CpuBackend.from_gguf(p), mf.artifact_digest(p), max_num_seqs=4)]), "127.0.0.1", 0)
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    try:
+        base = f"http://127.0.0.1:{httpd.server_address[1]}/v1"
+        c = ac.AttachClient(base)
+        d = c.doctor()
+        assert d["ok"] and d["executionEngine"] == "b200" and d["models"][0]["admitted"] and d["models"][0]["artifactDigest"].startswith("sha256:")
+        s = c.smoke()
+        assert s["ok"] and s["model"] == "tiny" and 1 <= s["usage"]["completion_tokens"] <= 4
+        assert ac.main(["doctor", "--base-url", base]) == 0 and json.loads(capsys.readouterr().out)["ok"]
+        LlmRequest, GenerationOptions = tl.LlmRequest, tl.GenerationOptions
+        req = LlmRequest("tiny", [{"role": "user", "content": "secret question 12345"}], options=GenerationOptions(max_tokens=6, temperature=0))
+        out = c.complete(req)
+        assert out["steps"] == 1 and out["usage"]["completion_tokens"] >= 1
+        text = json.dumps({k: out[k] for k in ("redactedTranscript", "toolCallReceipts")})
+        assert "secret question" not in text and out["redactedTranscript"][0] == {"role": "user", "contentChars": 21, "contentDigest": out["redactedTranscript"][0]["contentDigest"], "toolCalls": 0}
+        streamed = c.complete(req, stream=True)
+        assert streamed["message"]["content"] == out["message"]["content"]          # greedy: the streamed answer is the same
+    finally:
+        httpd.shutdown()
+    down = ac.AttachClient("http://127.0.0.1:1/v1", timeout_s=2).doctor()
+    assert not down["ok"] and down["blockerRefs"] == ["blocker.attach.server_unreachable"]
+    # a tool loop against a scripted server: receipts carry digests, a failing tool is marked
+    script = [{"choices": [{"message": {"role": "assistant", "content": None, "tool_calls": [
+                  {"id": "c1", "type": "function", "function": {"name": "add", "arguments": '{"a": 2, "b": 3}'}},
+                  {"id": "c2", "type": "function", "function": {"name": "boom", "arguments": "{}"}}]}}], "usage": {"prompt_tokens": 5, "completion_tokens": 7}},
+              {"choices": [{"message": {"role": "assistant", "content": "five"}}], "usage": {"prompt_tokens": 9, "completion_tokens": 1}}]
+    fake = ac.AttachClient("http://unused/v1")
+    fake._complete_once = lambda body, stream: script.pop(0)
+    r = fake.complete(LlmRequest("m", [{"role": "user", "content": "2+3?"}], tools=[{"name": "add", "parameters": {}}]), {"add": lambda a, b: a + b, "boom": lambda: 1 / 0})
+    assert r["message"]["content"] == "five" and r["steps"] == 2 and r["usage"] == {"prompt_tokens": 14, "completion_tokens": 8, "total_tokens": 22}
+    rec = {x["tool"]: x for x in r["toolCallReceipts"]}
+    assert rec["add"]["resultDigest"].startswith("sha256:") and rec["add"]["failed"] is False and rec["boom"]["failed"] is True
+    assert '"b": 3' not in json.dumps(r["toolCallReceipts"]).replace("\\", "")
