@@ -217,3 +217,34 @@ def test_a1_ordered_oracle_reproduces_the_published_run_digest_for_digest():
     for x in (1e-9, 0.3, 1.0, 1.5, 2.0, 77.7):
         assert abs(lib.b200_a1_det_ln(x) - math.log(x)) <= 1e-15 * max(1.0, abs(math.log(x)))
     assert lib.b200_a1_det_exp(-701.0) == 0.0 and lib.b200_a1_det_ln(1.0) == 0.0
+
+
+def test_a1_recompute_and_aggregation_digests():
+    """A shard gradient recomputed from the same inputs has the same digest and a 1e-9 nudge of one parameter changes it; the
+    aggregated state is the hand-computed mean step, digest for digest."""
+    import ctypes
+    import numpy as np
+    cfg = c.A1Config()
+    seed = c.PUBLISHED_SEED_DIGEST_HEX
+    lib = c._ordered_lib()
+    dp, ip = ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_int32)
+    dims = (cfg.d_model, cfg.d_ff, cfg.vocabulary_size, cfg.sequence_length)
+    p0 = np.ascontiguousarray(c.reference_initial_parameters(cfg, seed))
+    shards = [np.ascontiguousarray(c.reference_sequences(cfg, seed, f"train:{s}", cfg.train_sequences_per_shard), dtype=np.int32) for s in range(2)]
+
+    def grad(params, s):
+        g = np.zeros_like(params)
+        lib.b200_a1_shard_gradient(*dims, params.ctypes.data_as(dp), shards[s].ctypes.data_as(ip), len(shards[s]), g.ctypes.data_as(dp))
+        return g
+    g0, g0_again = grad(p0, 0), grad(p0, 0)
+    assert c.reference_shard_gradient_digest(seed, 0, 0, g0) == c.reference_shard_gradient_digest(seed, 0, 0, g0_again)
+    nudged = p0.copy()
+    nudged[100] += 1e-9
+    assert c.reference_shard_gradient_digest(seed, 0, 0, grad(nudged, 0)) != c.reference_shard_gradient_digest(seed, 0, 0, g0)
+    g1 = grad(p0, 1)
+    nxt = np.zeros_like(p0)
+    arr = (dp * 2)(g0.ctypes.data_as(dp), g1.ctypes.data_as(dp))
+    lib.b200_a1_sgd_step(p0.size, p0.ctypes.data_as(dp), arr, 2, cfg.learning_rate, nxt.ctypes.data_as(dp))
+    by_hand = np.array([p - (cfg.learning_rate * (a + b)) / 2 for p, a, b in zip(p0.tolist(), g0.tolist(), g1.tolist())])
+    assert c.reference_state_digest(seed, 1, nxt) == c.reference_state_digest(seed, 1, by_hand)
+    assert c.reference_state_digest(seed, 1, nxt) == c.run_training_ordered()["steps"][1]["stateDigest"]
