@@ -316,8 +316,12 @@ def dpo_worker(args, cfg, dev, rank, world):
         loss = float(d.train_step(t, g, refs[s % distinct]).item())
         dt = time.perf_counter() - t0
         if rank == 0:
-            print(json.dumps({"event": "step", "step": tr.step_count, "pair_loss": round(loss, 5), "reward_accuracy": round(d.reward_accuracy(), 4),
-                              "grad_norm": round(tr.grad_norm(), 5), "step_s": round(dt, 4), "pairs_per_s": round(per_step / dt, 1)}), flush=True)
+            rec = {"event": "step", "step": tr.step_count, "pair_loss": round(loss, 5), "reward_accuracy": round(d.reward_accuracy(), 4),
+                   "grad_norm": round(tr.grad_norm(), 5), "step_s": round(dt, 4), "pairs_per_s": round(per_step / dt, 1)}
+            print(json.dumps(rec), flush=True)
+            if args.log_jsonl:
+                with open(args.log_jsonl, "a") as f:
+                    f.write(json.dumps(rec) + "\n")
     tr.check_status()
     if args.ckpt_dir:
         tr.save_checkpoint(os.path.join(args.ckpt_dir, f"step{tr.step_count:08d}"))
@@ -325,9 +329,43 @@ def dpo_worker(args, cfg, dev, rank, world):
         dist.destroy_process_group()
 
 
+def run_manifest(path: str, work_dir: str | None = None) -> int:
+    """Zero-touch: validate the assignment, pin its inputs, run it with the flags it stands for, write the receipts."""
+    import tempfile
+    from . import assignment_manifest as am
+    with open(path) as f:
+        m = json.load(f)
+    work = work_dir or tempfile.mkdtemp(prefix="b200_assignment_")
+    os.makedirs(work, exist_ok=True)
+    blockers = am.validate(m) or am.verify_inputs(m)
+    t0 = time.time()
+    status = "refused" if blockers else "succeeded"
+    if not blockers:
+        try:
+            main(am.launcher_argv(m, work))
+        except SystemExit as e:
+            status = "succeeded" if e.code in (0, None) else "failed"
+        except Exception as e:      # noqa: BLE001 - whatever ended the run goes into the receipt, not up the stack
+            status, blockers = "failed", [f"blocker.training_assignment.run_failed.{type(e).__name__}"]
+    out = am.receipts(m if isinstance(m, dict) and "budget" in m else {"budget": {"maxWallSeconds": 1}, "batch": {"global": 0, "seqLen": 0}, "assignmentId": "unknown",
+                                                                        "runRef": "run.unknown", "manifestDigest": "sha256:" + "0" * 64},
+                      work, status, time.time() - t0)
+    out["blockerRefs"] = blockers
+    with open(os.path.join(work, "receipts.json"), "w") as f:
+        json.dump(out, f, indent=1)
+    print(json.dumps({"event": "assignment_closed", "status": out["workerReceipt"]["status"], "workDir": work, "blockerRefs": blockers,
+                      "receiptDigest": out["workerReceipt"]["receiptDigest"]}))
+    return 0 if out["workerReceipt"]["status"] == "succeeded" else 3
+
+
 def main(argv=None):
     if "RANK" in os.environ and os.environ.get("B200_TRAIN_ARGV"):      # a worker started by the re-execution below
         return worker(parse(json.loads(os.environ["B200_TRAIN_ARGV"])))
+    raw = list(sys.argv[1:] if argv is None else argv)
+    if "--manifest" in raw:                                              # the zero-touch path: every other flag comes from the manifest
+        i = raw.index("--manifest")
+        wd = raw[raw.index("--work-dir") + 1] if "--work-dir" in raw else None
+        raise SystemExit(run_manifest(raw[i + 1], wd))
     args = parse(argv)
     if args.nproc > 1 and "RANK" not in os.environ:
         # The worker's flags travel in the environment: torch.distributed.run parses abbreviations of its own options
