@@ -75,3 +75,43 @@ def test_receipts_take_the_tuning_lane_report(tmp_path):
     (work / "lane_report.json").write_text(json.dumps({"stepReceipts": [{"step": 1, "loss": 5.0, "batch": 0, "trainableTokens": 9}, {"step": 2, "loss": 4.5, "batch": 1, "trainableTokens": 9}]}))
     r = am.receipts(m, str(work), "succeeded", 3.0)
     assert r["evidence"]["lastStep"] == 2 and r["evidence"]["lastLoss"] == 4.5 and r["evidence"]["outputs"]["laneReport"]["sha256"].startswith("sha256:")
+
+
+def test_accepted_assignment_runs_the_launcher_and_closes(tmp_path, capsys, monkeypatch):
+    """The success path with the GPU worker replaced by a stand-in that does what a worker does to the run directory."""
+    from openagents_b200.train import launcher
+    d = _files(tmp_path)
+    m = am.make_manifest("assignment.pre.3", "pretrain", [{"role": "shard", "path": str(d / "train-00000.b2tk")}], steps=3, layers=2, global_batch=8, micro_batch=4, seq_len=64)
+    (d / "m.json").write_text(json.dumps(m))
+    seen = {}
+
+    def fake_worker(args):
+        seen["args"] = args
+        os.makedirs(os.path.join(args.ckpt_dir, "step00000003"), exist_ok=True)
+        with open(os.path.join(args.ckpt_dir, "step00000003", "manifest.json"), "w") as f:
+            json.dump({"checkpointDigestRef": "sha256:" + "cd" * 32, "step": 3}, f)
+        with open(args.log_jsonl, "a") as f:
+            for i in range(1, args.steps + 1):
+                f.write(json.dumps({"event": "step", "step": i, "loss": 11.0 - i}) + "\n")
+        with open(args.export_gguf, "wb") as f:
+            f.write(b"GGUF")
+    monkeypatch.setattr(launcher, "worker", fake_worker)
+    with pytest.raises(SystemExit) as e:
+        launcher.main(["--manifest", str(d / "m.json"), "--work-dir", str(d / "work")])
+    assert e.value.code == 0
+    a = seen["args"]
+    assert a.steps == 3 and a.layers == 2 and a.data == [str(d / "train-00000.b2tk")] and a.global_batch == 8 and a.seq_len == 64
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["status"] == "succeeded" and line["blockerRefs"] == []
+    out = json.loads((d / "work" / "receipts.json").read_text())
+    assert out["workerReceipt"]["status"] == "succeeded" and out["evidence"]["lastStep"] == 3 and out["evidence"]["outputs"]["gguf"]["bytes"] == 4
+    assert out["trainingWorkerReceipt"]["checkpointDigest"] == "sha256:" + "cd" * 32 and out["trainingWorkerReceipt"]["tokensProcessed"] == 3 * 8 * 64
+
+    def failing_worker(args):
+        raise RuntimeError("device lost")
+    monkeypatch.setattr(launcher, "worker", failing_worker)
+    with pytest.raises(SystemExit) as e:
+        launcher.main(["--manifest", str(d / "m.json"), "--work-dir", str(d / "work2")])
+    assert e.value.code == 3
+    out = json.loads((d / "work2" / "receipts.json").read_text())
+    assert out["workerReceipt"]["status"] == "failed" and out["blockerRefs"] == ["blocker.training_assignment.run_failed.RuntimeError"]
