@@ -384,9 +384,28 @@ class Scheduler:
             except Exception:       # noqa: BLE001 - closing must not raise out of the scheduling loop
                 pass
         if r.on_done:
-            r.on_done(r)
+            try:
+                r.on_done(r)
+            except Exception:       # noqa: BLE001 - a waiter's callback must not stop the scheduling loop
+                pass
+
+    def fail_all(self, error: Exception):
+        """Finish every queued and running request with ``error``: the last resort of the thread that calls ``step`` when a step
+        raised, so that no caller waits for ever on a request that a broken step left behind."""
+        for r in list(self.running) + list(self.waiting):
+            if r.state != "finished":
+                self._finish(r, "error", error)
 
     def _accept(self, r: Request, tok: int):
+        """Take one sampled token for ``r``.  Whatever goes wrong with this one request (its streaming callback, decoding its
+        text for the stop strings) ends this request with an error and leaves the others, and the scheduling thread, alone."""
+        try:
+            self._accept_token(r, tok)
+        except Exception as e:      # noqa: BLE001
+            if r.state != "finished":
+                self._finish(r, "error", e)
+
+    def _accept_token(self, r: Request, tok: int):
         if r.t_first_token is None:
             r.t_first_token = self.now()
         if tok == self.tok.eos_id:

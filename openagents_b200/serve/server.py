@@ -31,6 +31,7 @@ from .. import ENGINE_NAME, __version__
 from ..gateway.observability import ChatTraceEmitter, RateMonitorConfig, ServedTokensLedger, ServingRateMonitor
 from ..utils.nvtx import nvtx_range
 from ..utils.telemetry import Histogram, measured, not_measured
+from . import request_schema as schema
 from . import tools as tooling
 from .generation import (CHAT_TEMPLATE_DIGEST, ByteTokenizer, Request, RequestRejected, SamplingParams, Scheduler,
                          VocabTokenizer, render_chat, tokenizer_from_metadata)
@@ -70,8 +71,11 @@ class ServedModel:
                     self.cv.wait()
                 if self.closed:
                     return
-                with nvtx_range("scheduler.step"):
-                    self.sched.step()
+                try:
+                    with nvtx_range("scheduler.step"):
+                        self.sched.step()
+                except Exception as e:      # noqa: BLE001 - this thread is the only one that runs the engine: it must outlive any step
+                    self.sched.fail_all(e)
                 # Python locks are not fair: a loop that re-takes the lock at once can starve the handler threads that
                 # want to enqueue, and their requests would miss the running batch.  While any handler is waiting, give
                 # the lock away (bounded: a few milliseconds per step at most).
@@ -189,19 +193,15 @@ class ServerState:
     # ---- one completion, with or without a session
     def complete(self, model: ServedModel, messages: list[dict], body: dict, session: Session | None = None,
                  on_token=None) -> tuple[Request, dict]:
-        params = SamplingParams(max_tokens=int(body.get("max_tokens") or body.get("max_output_tokens") or 128),
-                                temperature=float(body.get("temperature") or 0.0), top_p=float(body.get("top_p") or 1.0),
-                                top_k=int(body.get("top_k") or 0),
-                                stop=tuple(body["stop"]) if isinstance(body.get("stop"), list) else ((body["stop"],) if body.get("stop") else ()),
-                                seed=body.get("seed"))
+        params = schema.sampling_params(body)
         tok = model.tok
         toks = getattr(tok, "tokens", None)
 
         def special(i):
             return toks[i] if toks is not None and isinstance(i, int) and 0 <= i < len(toks) else ""
         ids = tok.encode(render_chat(messages, model.chat_template, bos_token=special(getattr(tok, "bos_id", None)),
-                                     eos_token=special(getattr(tok, "eos_id", None)), tools=body.get("tools"),
-                                     **(body.get("chat_template_kwargs") if isinstance(body.get("chat_template_kwargs"), dict) else {})))
+                                     eos_token=special(getattr(tok, "eos_id", None)), tools=schema.tools(body) or None,
+                                     **schema.template_kwargs(body)))
         with nvtx_range("serve.complete"):
             if session is None:
                 r = model.generate(ids, params, on_token=on_token)
@@ -243,8 +243,11 @@ class ServerState:
 
     def serve_contract(self, model: ServedModel, body: dict) -> dict:
         """The gateway's serve request: greedy decode twice on this engine; parity = same tokens."""
-        msgs = body.get("messages") or []
+        msgs = schema.messages(body.get("messages"))
+        if not isinstance(body.get("passthroughParams"), (dict, type(None))):
+            raise schema.BadRequest("passthroughParams must be an object")
         pp = dict(body.get("passthroughParams") or {})
+        schema.common(pp)
         pp["temperature"] = 0.0
         r1, usage = self.complete(model, msgs, pp)
         parity = False
@@ -311,11 +314,16 @@ def make_handler(state: ServerState):
             self._json(code, {"error": {"message": msg, "type": kind}})
 
         def _body(self):
-            n = int(self.headers.get("Content-Length") or 0)
+            try:
+                n = int(self.headers.get("Content-Length") or 0)
+            except ValueError:
+                return None
+            if n < 0:
+                return None
             raw = self.rfile.read(n) if n else b"{}"
             try:
                 obj = json.loads(raw)
-            except json.JSONDecodeError:
+            except ValueError:            # malformed JSON, or bytes that are not UTF-8
                 return None
             return obj if isinstance(obj, dict) else None
 
@@ -359,6 +367,16 @@ def make_handler(state: ServerState):
             body = self._body()
             if body is None:
                 return self._err(400, "request body must be a JSON object")
+            self._streaming = False
+            try:
+                return self._post(path, body)
+            except Exception as e:      # noqa: BLE001 - a handler that raises would close the connection without an answer
+                if not self._streaming:
+                    return self._err(500, f"{type(e).__name__}: {e}", "engine_error")
+                self.close_connection = True      # the event stream has begun: all that is left is to end it
+                return None
+
+        def _post(self, path, body):
             if path == "/admin/shutdown":          # only with --allow-shutdown: lets a launcher or a test stop all ranks cleanly
                 if not state.allow_shutdown:
                     return self._err(404, "not found", "not_found")
@@ -366,7 +384,10 @@ def make_handler(state: ServerState):
                 threading.Thread(target=self.server.shutdown, daemon=True).start()
                 return None
             try:
+                schema.common(body)
                 model = state.model(body.get("model"))
+            except schema.BadRequest as e:
+                return self._err(400, str(e))
             except KeyError:
                 return self._err(404, f"model {body.get('model')!r} is not served", "model_not_found")
             try:
@@ -387,19 +408,33 @@ def make_handler(state: ServerState):
                     s = state.sessions.get(parts[2])
                     if s is None:
                         return self._err(404, "no such session", "not_found")
-                    msgs = body.get("messages") or [{"role": "user", "content": str(body.get("input", ""))}]
+                    msgs = body.get("messages") or self._input_messages(body)
                     r, usage = state.complete(s.model, msgs, body, session=s)
                     rid = "resp-" + uuid.uuid4().hex[:16]
                     s.responses.append(rid)
                     return self._json(200, {"id": rid, "session": s.id, "output_text": s.model.tok.decode(r.output),
                                             "usage": usage})
+            except schema.BadRequest as e:
+                return self._err(400, str(e))
             except RequestRejected as e:
                 return self._err(400, str(e), "context_length_exceeded")
             except MemoryError as e:
                 return self._err(503, str(e), "kv_cache_exhausted")
             except Exception as e:      # surface engine errors as a typed, non-retryable failure
+                if self._streaming:
+                    raise
                 return self._err(500, f"{type(e).__name__}: {e}", "engine_error")
             self._err(404, f"no route {path}", "not_found")
+
+        @staticmethod
+        def _input_messages(body):
+            """``input`` of the responses routes: a string (one user turn) or a list of messages."""
+            inp = body.get("input")
+            if isinstance(inp, list):
+                return schema.messages(inp, "input")
+            if inp is None or isinstance(inp, str):
+                return [{"role": "user", "content": inp or ""}]
+            raise schema.BadRequest("input must be a string or a list of messages")
 
         def _completions(self, model, body):
             """Text completion on a raw prompt (no chat template): ``prompt`` is a string or a list of token ids; ``echo`` returns
@@ -419,17 +454,14 @@ def make_handler(state: ServerState):
                 return self._err(400, "the prompt is empty")
             if body.get("stream"):
                 return self._err(400, "text completions are not streamed; use /v1/chat/completions")
-            echo, want_lp = bool(body.get("echo")), body.get("logprobs") not in (None, False)
-            n_new = body.get("max_tokens")
-            n_new = 16 if n_new is None else int(n_new)
-            if n_new < 0 or (n_new == 0 and not echo):
+            echo, want_lp = schema.boolean(body, "echo"), body.get("logprobs") not in (None, False)
+            n_new = schema.integer(body, "max_tokens", 0)
+            n_new = 16 if n_new is None else n_new
+            if n_new == 0 and not echo:
                 return self._err(400, "max_tokens must be positive (0 is allowed together with echo)")
             out, finish = [], "length"
             if n_new > 0:
-                params = SamplingParams(max_tokens=n_new, temperature=float(body.get("temperature") or 0.0), top_p=float(body.get("top_p") or 1.0),
-                                        top_k=int(body.get("top_k") or 0),
-                                        stop=tuple(body["stop"]) if isinstance(body.get("stop"), list) else ((body["stop"],) if body.get("stop") else ()),
-                                        seed=body.get("seed"))
+                params = schema.sampling_params(body, max_tokens=n_new)
                 r = model.generate(ids, params)
                 out, finish = list(r.output), r.finish_reason or "stop"
             shown = (ids if echo else []) + out
@@ -452,10 +484,8 @@ def make_handler(state: ServerState):
                              "choices": [choice], "usage": usage})
 
         def _chat(self, model, body):
-            msgs = body.get("messages")
-            if not isinstance(msgs, list) or not msgs:
-                return self._err(400, "messages must be a non-empty list")
-            tools = body.get("tools") or []
+            msgs = schema.messages(body.get("messages"))
+            tools = schema.tools(body)
             try:
                 mode, fname = tooling.normalize_tool_choice(body.get("tool_choice"), tools)
             except tooling.ToolCallError as e:
@@ -472,6 +502,7 @@ def make_handler(state: ServerState):
             if want_lp and (body.get("stream") or int(body.get("top_logprobs") or 0) > 0):
                 return self._err(400, "logprobs are reported for non-streamed completions, for the chosen tokens only (top_logprobs must be 0)")
             if body.get("stream"):
+                self._streaming = True
                 self.send_response(200)
                 self.send_header("Content-Type", "text/event-stream")
                 self.send_header("Cache-Control", "no-cache")
@@ -540,8 +571,7 @@ def make_handler(state: ServerState):
                                          if r.t_done and r.t_first_token and len(r.output) > 1 and r.t_done > r.t_first_token else None}})
 
         def _responses(self, model, body):
-            inp = body.get("input")
-            msgs = inp if isinstance(inp, list) else [{"role": "user", "content": str(inp or "")}]
+            msgs = self._input_messages(body) if body.get("input") is not None or body.get("messages") is None else body["messages"]
             prev = body.get("previous_response_id")
             if prev is not None:
                 if prev not in state.responses:

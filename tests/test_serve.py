@@ -505,3 +505,97 @@ def test_remote_scorers_agree_with_the_in_process_ones(server, tmp_path):
         l = perplexity(m.backend, ds, max_windows=2)
     # a window of 16 inputs and its final target is 17 ids on the wire: the same 16 predictions the in-process scorer makes
     assert r["targets"] == l["targets"] == 2 * 16 and r["loss"] == pytest.approx(l["loss"], abs=1e-4)
+
+
+# ---- mistyped requests: a typed 400 that names the field, never an engine error, a dropped connection or a stuck scheduler
+_M = [{"role": "user", "content": "hi"}]
+_BAD_BODIES = [
+    ("/v1/chat/completions", {"model": ["tiny"]}, "model"),
+    ("/v1/chat/completions", {"model": {"a": 1}}, "model"),
+    ("/v1/chat/completions", {"messages": [[]]}, "messages[0]"),
+    ("/v1/chat/completions", {"messages": [{"role": 5, "content": "x"}]}, "role"),
+    ("/v1/chat/completions", {"messages": [{"role": "user", "content": 3.5}]}, "content"),
+    ("/v1/chat/completions", {"messages": 1e9}, "messages"),
+    ("/v1/chat/completions", {"max_tokens": [1]}, "max_tokens"),
+    ("/v1/chat/completions", {"max_tokens": 3.5}, "max_tokens"),
+    ("/v1/chat/completions", {"max_tokens": "many"}, "max_tokens"),
+    ("/v1/chat/completions", {"max_tokens": -1}, "max_tokens"),
+    ("/v1/chat/completions", {"max_tokens": True}, "max_tokens"),
+    ("/v1/chat/completions", {"temperature": "hot"}, "temperature"),
+    ("/v1/chat/completions", {"temperature": -0.5}, "temperature"),
+    ("/v1/chat/completions", {"top_p": [1, 2]}, "top_p"),
+    ("/v1/chat/completions", {"top_p": 1.5}, "top_p"),
+    ("/v1/chat/completions", {"top_k": {}}, "top_k"),
+    ("/v1/chat/completions", {"seed": ""}, "seed"),
+    ("/v1/chat/completions", {"seed": -1}, "seed"),
+    ("/v1/chat/completions", {"stop": 3.5}, "stop"),
+    ("/v1/chat/completions", {"stop": True}, "stop"),
+    ("/v1/chat/completions", {"stop": [[]]}, "stop"),
+    ("/v1/chat/completions", {"stream": 1e9}, "stream"),
+    ("/v1/chat/completions", {"stream": [1]}, "stream"),
+    ("/v1/chat/completions", {"tools": "hammer"}, "tools"),
+    ("/v1/chat/completions", {"tools": [1]}, "tools"),
+    ("/v1/chat/completions", {"chat_template_kwargs": [1, 2]}, "chat_template_kwargs"),
+    ("/v1/chat/completions", {"chat_template_kwargs": {"messages": []}}, "chat_template_kwargs"),
+    ("/v1/chat/completions", {"top_logprobs": "x"}, "top_logprobs"),
+    ("/v1/chat/completions", {"user": [[]]}, "user"),
+    ("/v1/responses", {"previous_response_id": {}}, "previous_response_id"),
+    ("/v1/responses", {"input": True}, "input"),
+    ("/v1/responses", {"input": [1, 2]}, "input[0]"),
+    ("/v1/completions", {"prompt": 3.5}, "prompt"),
+    ("/v1/completions", {"prompt": "abc", "echo": "yes"}, "echo"),
+    ("/v1/completions", {"prompt": "abc", "max_tokens": [2]}, "max_tokens"),
+    ("/v1/serve", {"messages": True}, "messages"),
+    ("/v1/serve", {"passthroughParams": 7}, "passthroughParams"),
+    ("/v1/serve", {"passthroughParams": {"top_k": []}}, "top_k"),
+]
+
+
+@pytest.mark.parametrize("path,patch,field", _BAD_BODIES, ids=[f"{p.rsplit('/', 1)[-1]}-{json.dumps(b)[:40]}" for p, b, _ in _BAD_BODIES])
+def test_mistyped_request_fields_get_a_typed_400(server, path, patch, field):
+    base, _ = server
+    body = {"model": "tiny", "messages": _M, "max_tokens": 2, **patch}
+    code, raw = _post(base + path, body)
+    err = json.loads(raw)["error"]
+    assert code == 400 and err["type"] == "invalid_request_error" and field in err["message"], (code, raw)
+    code, raw = _post(base + "/v1/chat/completions", {"model": "tiny", "messages": _M, "max_tokens": 2})     # and the server still serves
+    assert code == 200 and json.loads(raw)["usage"]["completion_tokens"] >= 1
+
+
+def test_bodies_that_are_not_json_objects_get_a_400(server):
+    base, _ = server
+    for raw in (b"{", b"[]", b"null", b"\xff\xfe{}", b"12"):
+        req = urllib.request.Request(base + "/v1/chat/completions", data=raw, headers={"Content-Type": "application/json"})
+        with pytest.raises(urllib.error.HTTPError) as e:
+            urllib.request.urlopen(req, timeout=60)
+        assert e.value.code == 400 and json.loads(e.value.read())["error"]["type"] == "invalid_request_error"
+
+
+def test_lenient_spellings_of_valid_requests_are_accepted(server):
+    base, _ = server
+    for patch in ({"max_tokens": 2.0}, {"stop": None}, {"stop": []}, {"stop": ""}, {"top_p": 0}, {"top_k": 0}, {"seed": 7, "temperature": 0.7},
+                  {"stream": None}, {"tools": None}, {"chat_template_kwargs": {"reasoning_effort": "low"}}, {"model": ""}, {"user": "u-1"}):
+        code, raw = _post(base + "/v1/chat/completions", {"model": "tiny", "messages": _M, "max_tokens": 2, **patch})
+        assert code == 200, (patch, raw)
+
+
+def test_scheduling_thread_survives_a_request_it_cannot_process(gguf_path):
+    """Whatever a request does to the scheduler's own bookkeeping (here: a stop entry that is not a string, put past the HTTP
+    checks), that request ends with an error and the next one is served; nothing waits on a dead thread."""
+    model = ServedModel("tiny", CpuBackend.from_gguf(gguf_path), None, max_num_seqs=4)
+    try:
+        with pytest.raises(TypeError):
+            model.generate([1, 2, 3], SamplingParams(max_tokens=3, stop=(3.5,)))
+        assert model.thread.is_alive()
+        ok = model.generate([1, 2, 3], SamplingParams(max_tokens=3))
+        assert len(ok.output) >= 1 and ok.finish_reason in ("length", "stop")
+
+        def boom():
+            raise RuntimeError("step failed")
+        step, model.sched.step = model.sched.step, boom            # a step that raises outright: every waiter is released
+        with pytest.raises(RuntimeError, match="step failed"):
+            model.generate([1, 2, 3], SamplingParams(max_tokens=3))
+        model.sched.step = step
+        assert model.thread.is_alive() and len(model.generate([4, 5], SamplingParams(max_tokens=2)).output) >= 1
+    finally:
+        model.close()
