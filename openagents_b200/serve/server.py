@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import argparse
 import hashlib
+import hmac
 import json
 import os
 import queue
@@ -175,6 +176,7 @@ class ServerState:
         self.reasoning_budget, self.mesh_coordination = reasoning_budget, mesh_coordination
         self.started = time.time()
         self.allow_shutdown = False
+        self.api_key: str | None = None      # when set, every POST route wants "Authorization: Bearer <key>"
         self.ttft = Histogram([0.005, 0.01, 0.025, 0.05, 0.1, 0.25, 0.5, 1, 2.5, 5, 10])
         self.itl = Histogram([0.0005, 0.001, 0.002, 0.005, 0.01, 0.02, 0.05, 0.1, 0.25])
         self.lock = threading.Lock()
@@ -368,6 +370,8 @@ def make_handler(state: ServerState):
             if body is None:
                 return self._err(400, "request body must be a JSON object")
             self._streaming = False
+            if state.api_key and not hmac.compare_digest((self.headers.get("Authorization") or "").encode(), f"Bearer {state.api_key}".encode()):
+                return self._err(401, "send Authorization: Bearer <the server's API key>", "invalid_api_key")
             try:
                 return self._post(path, body)
             except Exception as e:      # noqa: BLE001 - a handler that raises would close the connection without an answer
@@ -665,6 +669,8 @@ def parse_args(argv=None):
     ap.add_argument("--speculation", default=_flag_env("speculation", "none"), choices=["none", "n_gram"],
                     help="low-batch speculative decoding: n-gram drafts verified in one forward (greedy requests only)")
     ap.add_argument("--speculation-max-batch", type=int, default=_flag_env("speculation-max-batch", 4))
+    ap.add_argument("--api-key", default=os.environ.get("B200_API_KEY"),
+                    help="require 'Authorization: Bearer <key>' on every POST route (default: $B200_API_KEY; unset = open, for loopback use)")
     ap.add_argument("--allow-shutdown", action="store_true", help="accept POST /admin/shutdown (stops every rank between steps)")
     a = ap.parse_args(argv)
     if a.tp > 1 and a.ep > 1:
@@ -682,6 +688,7 @@ def run_server(a, **parallel):
     state = build_state(a.model, a.backend, a.max_num_seqs, a.kv_page_size, a.max_ctx, a.reasoning_budget, a.mesh_coordination,
                         speculation=spec, **parallel)
     state.allow_shutdown = bool(getattr(a, "allow_shutdown", False))
+    state.api_key = getattr(a, "api_key", None) or None
     httpd = serve(state, a.host, a.port)
     print(json.dumps({"event": "listening", "host": a.host, "port": httpd.server_address[1], "models": list(state.models),
                       "execution_engine": ENGINE_NAME, "tp": a.tp, "ep": a.ep}), flush=True)
