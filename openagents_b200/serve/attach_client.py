@@ -22,6 +22,7 @@ import os
 import re
 import sys
 import urllib.error
+import urllib.parse
 import urllib.request
 
 from .tools import LlmRequest, ToolCallDeltaAssembler, parse_sse, run_tool_loop
@@ -66,6 +67,32 @@ class AttachClient:
     def _json(self, url: str, body: dict | None = None) -> dict:
         with self._request(url, body) as r:
             return json.loads(r.read())
+
+    # ---- session turns (the routes the local foundation-model bridge of the reference exposes:
+    # packages/apple-fm-runtime/native/foundation-bridge/Sources/foundation-bridge/main.swift:472-494)
+    def create_session(self, model: str | None = None, instructions: str | None = None) -> str:
+        body = {k: v for k, v in (("model", model), ("instructions", instructions)) if v is not None}
+        return self._json(self._root() + "/v1/sessions", body)["id"]
+
+    def stream_turn(self, session_id: str, prompt: str, **options):
+        """Yields ``("snapshot", text_so_far)`` as the answer grows, then ``("completed", {output, model, usage, ...})``.
+        A failure after the stream began arrives as an ``error`` event and is raised here."""
+        url = self._root() + f"/v1/sessions/{urllib.parse.quote(session_id, safe='')}/responses/stream"
+        event = None
+        with self._request(url, {"prompt": prompt, **options}) as r:
+            for line in r:
+                line = line.decode().rstrip("\r\n")
+                if line.startswith("event: "):
+                    event = line[7:]
+                elif line.startswith("data: ") and event:
+                    data = json.loads(line[6:])
+                    if event == "snapshot":
+                        yield ("snapshot", data["content"])
+                    elif event == "completed":
+                        yield ("completed", data)
+                    elif event == "error":
+                        raise RuntimeError(data.get("message") or "the turn failed")
+                    event = None
 
     def doctor(self) -> dict:
         blockers, engine, endpoints, rows = [], None, [], []

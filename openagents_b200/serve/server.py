@@ -25,6 +25,7 @@ import os
 import queue
 import threading
 import time
+import urllib.parse
 import uuid
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 
@@ -37,7 +38,8 @@ from . import tools as tooling
 from .generation import (CHAT_TEMPLATE_DIGEST, ByteTokenizer, Request, RequestRejected, SamplingParams, Scheduler,
                          VocabTokenizer, render_chat, tokenizer_from_metadata)
 
-ENDPOINTS = ["/health", "/v1/models", "/v1/completions", "/v1/chat/completions", "/v1/responses", "/v1/sessions", "/v1/serve",
+ENDPOINTS = ["/health", "/v1/models", "/v1/completions", "/v1/chat/completions", "/v1/responses", "/v1/sessions", "/v1/sessions/{id}/responses",
+             "/v1/sessions/{id}/responses/stream", "/v1/serve",
              "/psionic/management/status", "/metrics"]
 
 
@@ -164,6 +166,7 @@ class Session:
         self.tokens: list[int] = []       # everything the sequence's KV covers, plus the pending tail
         self.pending: list[int] = []      # generated tokens whose K/V have not been written yet
         self.responses: list[str] = []
+        self.instructions: str | None = None   # a system message that opens the session's first turn
         self.created = time.time()
 
 
@@ -405,14 +408,24 @@ def make_handler(state: ServerState):
                     return self._json(200, state.serve_contract(model, body))
                 if path == "/v1/sessions":
                     s = Session("sess-" + uuid.uuid4().hex[:16], model)
+                    s.instructions = schema.string(body, "instructions")
                     state.sessions[s.id] = s
-                    return self._json(200, {"id": s.id, "model": model.id})
+                    return self._json(200, {"id": s.id, "model": model.id, "session": {"id": s.id}})
                 parts = path.strip("/").split("/")
-                if len(parts) == 4 and parts[:2] == ["v1", "sessions"] and parts[3] == "responses":
-                    s = state.sessions.get(parts[2])
+                if len(parts) in (4, 5) and parts[:2] == ["v1", "sessions"] and parts[3] == "responses" and parts[4:] in ([], ["stream"]):
+                    s = state.sessions.get(urllib.parse.unquote(parts[2]))
                     if s is None:
                         return self._err(404, "no such session", "not_found")
-                    msgs = body.get("messages") or self._input_messages(body)
+                    if body.get("messages"):
+                        msgs = body["messages"]
+                    elif body.get("prompt") is not None:           # the shape of a session turn on the local attach path
+                        msgs = [{"role": "user", "content": schema.string(body, "prompt")}]
+                    else:
+                        msgs = self._input_messages(body)
+                    if s.instructions and not s.tokens and not s.pending:      # the session's instructions open its first turn
+                        msgs = [{"role": "system", "content": s.instructions}] + list(msgs)
+                    if parts[4:] == ["stream"]:
+                        return self._session_stream(s, msgs, body)
                     r, usage = state.complete(s.model, msgs, body, session=s)
                     rid = "resp-" + uuid.uuid4().hex[:16]
                     s.responses.append(rid)
@@ -439,6 +452,45 @@ def make_handler(state: ServerState):
             if inp is None or isinstance(inp, str):
                 return [{"role": "user", "content": inp or ""}]
             raise schema.BadRequest("input must be a string or a list of messages")
+
+        def _session_stream(self, sess, msgs, body):
+            """One session turn as server-sent events: a ``snapshot`` event per step whose ``content`` is the answer so far (it
+            grows toward the final text; the last one carries ``finish_reason``), then one ``completed`` event with the output, the
+            model and the usage.  Sent as it is generated (chunked transfer)."""
+            self._streaming = True
+            self.send_response(200)
+            self.send_header("Content-Type", "text/event-stream; charset=utf-8")
+            self.send_header("Cache-Control", "no-cache")
+            self.send_header("Transfer-Encoding", "chunked")
+            self.end_headers()
+
+            def frame(event, obj):
+                data = f"event: {event}\ndata: {json.dumps(obj)}\n\n".encode()
+                self.wfile.write(f"{len(data):x}\r\n".encode() + data + b"\r\n")
+                self.wfile.flush()
+
+            out: list[int] = []
+            sent = [0, ""]                          # snapshots sent, text of the last one
+
+            def on_token(t):
+                out.append(t)
+                text = sess.model.tok.decode(out)
+                if text and not text.endswith("\ufffd") and text != sent[1]:      # hold back incomplete UTF-8 sequences
+                    frame("snapshot", {"sequence": sent[0], "content": text, "output": text, "finish_reason": None})
+                    sent[0], sent[1] = sent[0] + 1, text
+
+            try:
+                r, usage = state.complete(sess.model, msgs, body, session=sess, on_token=on_token)
+            except Exception as e:      # noqa: BLE001 - the stream has begun: the failure is its last event
+                frame("error", {"error": "generation_failed", "message": f"{type(e).__name__}: {e}"})
+                self.wfile.write(b"0\r\n\r\n")
+                return
+            text = sess.model.tok.decode(r.output)
+            frame("snapshot", {"sequence": sent[0], "content": text, "output": text, "finish_reason": r.finish_reason or "stop"})
+            rid = "resp-" + uuid.uuid4().hex[:16]
+            sess.responses.append(rid)
+            frame("completed", {"id": rid, "session": sess.id, "output": text, "content": text, "model": sess.model.id, "usage": usage})
+            self.wfile.write(b"0\r\n\r\n")
 
         def _completions(self, model, body):
             """Text completion on a raw prompt (no chat template): ``prompt`` is a string or a list of token ids; ``echo`` returns

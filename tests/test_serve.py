@@ -599,3 +599,51 @@ def test_scheduling_thread_survives_a_request_it_cannot_process(gguf_path):
         assert model.thread.is_alive() and len(model.generate([4, 5], SamplingParams(max_tokens=2)).output) >= 1
     finally:
         model.close()
+
+
+def test_session_turns_streamed_as_growing_snapshots(server):
+    """``POST /v1/sessions/{id}/responses/stream``: one ``snapshot`` event per step whose content grows toward the answer, then
+    ``completed``; the turn lands in the session exactly like a non-streamed one (same tokens, KV kept for the next turn)."""
+    base, state = server
+
+    def events(raw):
+        out = []
+        for block in raw.decode().split("\n\n"):
+            lines = dict(l.split(": ", 1) for l in block.split("\n") if ": " in l)
+            if "event" in lines:
+                out.append((lines["event"], json.loads(lines["data"])))
+        return out
+
+    sid = json.loads(_post(base + "/v1/sessions", {"model": "tiny", "instructions": "Be brief."})[1])["id"]
+    ref = json.loads(_post(base + "/v1/sessions", {"model": "tiny", "instructions": "Be brief."})[1])["id"]
+    code, raw = _post(base + f"/v1/sessions/{sid}/responses/stream", {"prompt": "hello there", "max_tokens": 6})
+    assert code == 200
+    ev = events(raw)
+    snaps = [d for e, d in ev if e == "snapshot"]
+    assert [e for e, _ in ev][-1] == "completed" and len(snaps) >= 1
+    assert [d["sequence"] for d in snaps] == list(range(len(snaps)))
+    assert all(b["content"].startswith(a["content"]) for a, b in zip(snaps, snaps[1:]))            # each snapshot extends the last
+    assert all(d["finish_reason"] is None for d in snaps[:-1]) and snaps[-1]["finish_reason"] in ("length", "stop")
+    done = ev[-1][1]
+    assert done["output"] == snaps[-1]["content"] == done["content"] and done["model"] == "tiny" and done["usage"]["completion_tokens"] == 6
+    plain = json.loads(_post(base + f"/v1/sessions/{ref}/responses", {"prompt": "hello there", "max_tokens": 6})[1])
+    assert plain["output_text"] == done["output"] and plain["usage"]["prompt_tokens"] == done["usage"]["prompt_tokens"]
+    # the second turn continues the kept sequence on both; the instructions were part of the first turn only
+    code, raw = _post(base + f"/v1/sessions/{sid}/responses/stream", {"prompt": "and then?", "max_tokens": 4})
+    second = events(raw)[-1][1]
+    plain2 = json.loads(_post(base + f"/v1/sessions/{ref}/responses", {"prompt": "and then?", "max_tokens": 4})[1])
+    assert second["output"] == plain2["output_text"] and second["usage"]["prompt_tokens"] == plain2["usage"]["prompt_tokens"] < done["usage"]["prompt_tokens"]
+    assert state.sessions[sid].tokens == state.sessions[ref].tokens
+    assert _post(base + "/v1/sessions/sess-nope/responses/stream", {"prompt": "x"})[0] == 404
+    code, raw = _post(base + f"/v1/sessions/{sid}/responses/stream", {"prompt": 5})
+    assert code == 400 and "prompt" in json.loads(raw)["error"]["message"]
+
+
+def test_attach_client_streams_a_session_turn(server):
+    from openagents_b200.serve.attach_client import AttachClient
+    base, _ = server
+    c = AttachClient(base + "/v1")
+    sid = c.create_session("tiny", instructions="Be brief.")
+    got = list(c.stream_turn(sid, "hello there", max_tokens=5))
+    assert [k for k, _ in got][-1] == "completed" and all(k == "snapshot" for k, _ in got[:-1])
+    assert got[-1][1]["output"] == got[-2][1] and got[-1][1]["usage"]["completion_tokens"] == 5
