@@ -10,7 +10,6 @@ numbers in the weights.
 """
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.distributed as dist

@@ -12,9 +12,8 @@ metadata), :192-216 (manifest), :219-231 (plan request), :260-264 (lease claim).
 from __future__ import annotations
 
 import hashlib
-import json
 import time
-from dataclasses import asdict, dataclass, field
+from dataclasses import dataclass, field
 
 from . import seal as seal_mod
 from .lifecycle import DEFAULT_MAX_ALLOWED_STALE_STEPS

@@ -10,7 +10,7 @@ replication minimum, :51-66 storage classes, :68-99 descriptor, :140-179 predica
 from __future__ import annotations
 
 import re
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 SCHEMA_VERSION = "openagents.training.marathon_operations.durable_checkpoint_seal.v1"
 DIGEST_PATTERN = re.compile(r"^sha256:[a-f0-9]{64}$")

@@ -6,7 +6,7 @@ The presets are the shapes the benchmark configurations name; the server detects
 """
 from __future__ import annotations
 
-from dataclasses import asdict, dataclass, field, replace
+from dataclasses import asdict, dataclass, replace
 
 
 @dataclass(frozen=True)

@@ -5,7 +5,6 @@ A ``WeightSource`` hands out tensors in standard GGUF bytes (so sharding is plai
 """
 from __future__ import annotations
 
-import zlib
 from dataclasses import dataclass
 
 import torch
@@ -14,7 +13,7 @@ from ..gguf import GGUFFile, GgmlType, type_block
 from ..gguf import torch_codecs as tc
 from ..ops import cuda_ops as ops
 from .config import ModelConfig
-from .weights import QuantPlan, TensorSpec, init_tensor, tensor_specs
+from .weights import QuantPlan, init_tensor, tensor_specs
 
 
 @dataclass

@@ -8,10 +8,9 @@ from __future__ import annotations
 import zlib
 from dataclasses import dataclass
 
-import numpy as np
 import torch
 
-from ..gguf import GGUFFile, GGUFWriter, GgmlType, dequantize, quantize, type_block
+from ..gguf import GGUFFile, GGUFWriter, GgmlType, type_block
 from .config import ModelConfig
 
 

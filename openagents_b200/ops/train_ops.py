@@ -1,10 +1,8 @@
 """Python faces of the training-path kernels (``csrc/kernels/train_ops.cu``, ``csrc/comm/zero_adamw.cu``)."""
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_size_t, c_void_p
 
-import torch
 
 from .. import _native
 from .cuda_ops import _check, _p, _st, _sym

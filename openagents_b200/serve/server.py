@@ -32,11 +32,11 @@ from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 from .. import ENGINE_NAME, __version__
 from ..gateway.observability import ChatTraceEmitter, RateMonitorConfig, ServedTokensLedger, ServingRateMonitor
 from ..utils.nvtx import nvtx_range
-from ..utils.telemetry import Histogram, measured, not_measured
+from ..utils.telemetry import Histogram
 from . import request_schema as schema
 from . import tools as tooling
-from .generation import (CHAT_TEMPLATE_DIGEST, ByteTokenizer, Request, RequestRejected, SamplingParams, Scheduler,
-                         VocabTokenizer, render_chat, tokenizer_from_metadata)
+from .generation import (CHAT_TEMPLATE_DIGEST, ByteTokenizer, Request, RequestRejected, Scheduler,
+                         render_chat, tokenizer_from_metadata)
 
 ENDPOINTS = ["/health", "/v1/models", "/v1/completions", "/v1/chat/completions", "/v1/responses", "/v1/sessions", "/v1/sessions/{id}/responses",
              "/v1/sessions/{id}/responses/stream", "/v1/serve",

@@ -21,7 +21,6 @@ from __future__ import annotations
 import hashlib
 import json
 import os
-from dataclasses import asdict
 
 import numpy as np
 import torch

@@ -16,13 +16,12 @@ the gradient of that projection.  No autograd graph is built anywhere in this fi
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 
 import torch
 
 from ..models.config import ModelConfig
-from ..models.weights import TensorSpec, init_tensor, tensor_specs
+from ..models.weights import TensorSpec, tensor_specs
 from ..ops import cuda_ops as ops
 from ..ops import train_ops as tops
 

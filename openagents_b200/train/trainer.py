@@ -18,18 +18,17 @@ in-process reference trajectory); run/window/checkpoint bookkeeping lives in ``c
 from __future__ import annotations
 
 import math
-import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist
 
 from ..models.config import GPT2_SMALL, ModelConfig
-from ..models.weights import TensorSpec, init_tensor, tensor_specs
+from ..models.weights import init_tensor, tensor_specs
 from ..ops import train_ops as tops
 from ..parallel.symm import SymmHeap
 from ..utils.nvtx import nvtx_method
-from .gpt2 import GPT2Model, padded_vocab, param_layout
+from .gpt2 import GPT2Model, param_layout
 
 
 @dataclass

@@ -4,7 +4,6 @@ aggregation and validation, cross-node ``deterministic_recompute`` and ``freival
 queue, signed coordination records, the durable-seal gate (HOLD on a single local copy, SEAL on a replicated one) and
 reconciliation.  The run is the reference's published two-device run, so its digests are known in advance."""
 import ctypes
-import dataclasses
 
 import numpy as np
 
