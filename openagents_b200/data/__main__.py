@@ -15,6 +15,8 @@ import json
 import os
 import sys
 
+from ..utils.cli import cli_entry
+
 
 def _read_documents(paths) -> list[str]:
     texts = []
@@ -97,6 +99,7 @@ def traces(args) -> dict:
     return report
 
 
+@cli_entry("b200-data")
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m openagents_b200.data")
     sub = ap.add_subparsers(dest="cmd", required=True)

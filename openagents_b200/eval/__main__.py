@@ -10,6 +10,8 @@ import json
 import sys
 import time
 
+from ..utils.cli import cli_entry
+
 
 def parse_gate(text: str):
     from .pack import MetricGate
@@ -22,6 +24,7 @@ def parse_gate(text: str):
     return MetricGate(parts[0], parts[1], float(parts[2]), required=flag != "optional", rollback_on_fail=flag == "rollback")
 
 
+@cli_entry("b200-eval")
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m openagents_b200.eval")
     ap.add_argument("--model", required=True, help="GGUF checkpoint")

@@ -36,6 +36,7 @@ import time
 import urllib.parse
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 
+from ..utils.cli import cli_entry
 from .chat_route import ApiKey, ChatGateway, ModelGate
 from .fabric import OpenAgentsNetworkAdapter, ProviderRegistry, dispatch_psionic_serve, make_http_transport
 from .hydralisk import HydraliskAdapter, HydraliskPoolAdapter
@@ -247,6 +248,7 @@ def serve(gw: ChatGateway, host: str = "127.0.0.1", port: int = 8787, admin_key:
     return _Server((host, port), make_handler(gw, admin_key))
 
 
+@cli_entry("b200-gateway")
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="b200-gateway", description=__doc__.split("\n\n")[0])
     ap.add_argument("--config", required=True, help="JSON configuration (keys, nodes, plans, pricing, gates)")

@@ -15,6 +15,8 @@ import sys
 
 import numpy as np
 
+from ..utils.cli import cli_entry
+
 
 def inspect(path: str) -> dict:
     from . import GGUFFile
@@ -65,6 +67,7 @@ def quantize(src: str, dst: str, plan_name: str) -> dict:
             "keptMetadataKeys": sorted(k for k in extra if not k.startswith("tokenizer.ggml.")), "tensors": rows}
 
 
+@cli_entry("b200-gguf")
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m openagents_b200.gguf")
     sub = ap.add_subparsers(dest="cmd", required=True)

@@ -25,6 +25,7 @@ import urllib.error
 import urllib.parse
 import urllib.request
 
+from ..utils.cli import cli_entry
 from .tools import LlmRequest, ToolCallDeltaAssembler, parse_sse, run_tool_loop
 
 DEFAULT_BASE_URL = "http://127.0.0.1:8080/v1"
@@ -170,6 +171,7 @@ class AttachClient:
                 "redactedTranscript": transcript, "toolCallReceipts": receipts}
 
 
+@cli_entry("b200-attach")
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m openagents_b200.serve.attach_client")
     ap.add_argument("command", choices=["doctor", "smoke"])

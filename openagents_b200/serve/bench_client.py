@@ -29,6 +29,8 @@ import urllib.error
 import urllib.request
 from pathlib import Path
 
+from ..utils.cli import cli_entry
+
 BENCH_SCHEMA = "openagents.muse.chat_completions_benchmark.v2"
 PREFLIGHT_SCHEMA = "openagents.pylon.live_serving_preflight_run.v0.1"
 
@@ -262,6 +264,7 @@ def run_preflight(env=None, opener=urllib.request.urlopen, now=None) -> dict:
             "ready": not blockers, "blockerRefs": blockers}
 
 
+@cli_entry("b200-serve-bench")
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="b200-serve-bench")
     sub = ap.add_subparsers(dest="cmd", required=True)

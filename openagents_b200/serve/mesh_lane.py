@@ -23,6 +23,7 @@ import time
 from pathlib import Path
 
 from ..control.coordination import MeshElection
+from ..utils.cli import cli_entry
 
 ROOT_SCHEMA = "b200.mesh_lane.root.v1"
 DIRS = ("config", "identity", "network", "logs", "models", "service")
@@ -189,6 +190,7 @@ class MeshLaneRoot:
                 "sessionGeneration": st["sessionGeneration"], "models": [m["name"] for m in cfg["models"]]}
 
 
+@cli_entry("b200-lane")
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m openagents_b200.serve.mesh_lane")
     sub = ap.add_subparsers(dest="cmd", required=True)

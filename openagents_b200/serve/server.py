@@ -31,6 +31,7 @@ from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 
 from .. import ENGINE_NAME, __version__
 from ..gateway.observability import ChatTraceEmitter, RateMonitorConfig, ServedTokensLedger, ServingRateMonitor
+from ..utils.cli import cli_entry
 from ..utils.nvtx import nvtx_range
 from ..utils.telemetry import Histogram
 from . import request_schema as schema
@@ -753,6 +754,7 @@ def run_server(a, **parallel):
             m.close()
 
 
+@cli_entry("b200-serve")
 def main(argv=None):
     a = parse_args(argv)
     if max(a.tp, a.ep) > 1:

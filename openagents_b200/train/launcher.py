@@ -23,6 +23,8 @@ import subprocess
 import sys
 import time
 
+from ..utils.cli import cli_entry
+
 
 def parse(argv=None):
     ap = argparse.ArgumentParser(prog="b200-train")
@@ -358,6 +360,7 @@ def run_manifest(path: str, work_dir: str | None = None) -> int:
     return 0 if out["workerReceipt"]["status"] == "succeeded" else 3
 
 
+@cli_entry("b200-train")
 def main(argv=None):
     if "RANK" in os.environ and os.environ.get("B200_TRAIN_ARGV"):      # a worker started by the re-execution below
         return worker(parse(json.loads(os.environ["B200_TRAIN_ARGV"])))

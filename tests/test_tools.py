@@ -208,3 +208,21 @@ def test_attach_client_doctor_smoke_and_tool_loop_against_a_live_server(tmp_path
     rec = {x["tool"]: x for x in r["toolCallReceipts"]}
     assert rec["add"]["resultDigest"].startswith("sha256:") and rec["add"]["failed"] is False and rec["boom"]["failed"] is True
     assert '"b": 3' not in json.dumps(r["toolCallReceipts"]).replace("\\", "")
+
+
+def test_command_line_input_errors_are_one_line_and_status_2(tmp_path):
+    """A missing or malformed input ends a command with ``<prog>: error: ...`` on stderr and status 2, not a traceback."""
+    import subprocess
+    import sys
+    bad = tmp_path / "bad.gguf"
+    bad.write_bytes(b"GGUF\x03\x00\x00\x00")
+    cases = [(["openagents_b200.gguf", "inspect", str(bad)], "b200-gguf: error:", "too small"),
+             (["openagents_b200.gguf", "digest", str(tmp_path / "none.gguf")], "b200-gguf: error:", "No such file"),
+             (["openagents_b200.data", "prepare", "--text", str(tmp_path / "none.txt"), "--out", str(tmp_path / "o")], "b200-data: error:", "No such file"),
+             (["openagents_b200.serve.server", "-m", str(bad), "--backend", "cpu"], "b200-serve: error:", "too small")]
+    for argv, head, needle in cases:
+        out = subprocess.run([sys.executable, "-m", *argv], capture_output=True, text=True, timeout=300)
+        assert out.returncode == 2 and out.stderr.strip().startswith(head) and needle in out.stderr and "Traceback" not in out.stderr, (argv, out.stderr)
+    out = subprocess.run([sys.executable, "-m", "openagents_b200.gguf", "inspect", str(bad)], capture_output=True, text=True, timeout=300,
+                         env={**__import__("os").environ, "B200_TRACEBACK": "1"})
+    assert out.returncode == 1 and "Traceback" in out.stderr
