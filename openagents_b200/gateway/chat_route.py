@@ -29,6 +29,7 @@ import threading
 import time
 import uuid
 
+from ..serve import request_schema as schema
 from . import prompt_cache as pc
 from . import request_telemetry as rt
 from .fabric import InferenceAdapterError, InferenceRequest, InferenceResult, InferenceUsage, ProviderRegistry, normalize_serve_response
@@ -121,10 +122,15 @@ class LocalEngineAdapter:
             model = self.state.model(self.alias.get(request.model, request.model))
         except KeyError:
             raise InferenceAdapterError(self.id, "request_rejected", f"model {request.model!r} is not served here", False, 404)
-        greedy = float(request.passthrough_params.get("temperature") or 0.0) == 0.0
-        raw = self.state.serve_contract(model, {"messages": [dict(m) for m in request.messages],
-                                                "passthroughParams": dict(request.passthrough_params),
-                                                "requireExactGreedyParity": greedy})
+        try:
+            greedy = float(request.passthrough_params.get("temperature") or 0.0) == 0.0
+            raw = self.state.serve_contract(model, {"messages": [dict(m) for m in request.messages],
+                                                    "passthroughParams": dict(request.passthrough_params),
+                                                    "requireExactGreedyParity": greedy})
+        except (ValueError, TypeError) as e:        # a request the engine refuses (too long for the context, a mistyped option)
+            raise InferenceAdapterError(self.id, "request_rejected", str(e), False, 400)
+        except MemoryError as e:
+            raise InferenceAdapterError(self.id, "service_overloaded", str(e), True, 503)
         serve = normalize_serve_response(raw)
         if serve is None:
             raise InferenceAdapterError(self.id, "malformed_response", "engine returned a malformed serve response")
@@ -179,8 +185,18 @@ class ChatGateway:
         if not isinstance(msgs, list) or not msgs or not all(isinstance(m, dict) and isinstance(m.get("role"), str) and isinstance(m.get("content"), str) for m in msgs):
             raise GatewayError(400, "invalid_request", "messages must be a non-empty list of {role, content}")
         mt = body.get("max_tokens")
-        if mt is not None and not (isinstance(mt, int) and 1 <= mt <= 131072):
+        if mt is not None and not (isinstance(mt, int) and not isinstance(mt, bool) and 1 <= mt <= 131072):
             raise GatewayError(400, "invalid_request", "max_tokens out of range")
+        try:                             # the checks the model server applies, applied before any lane is tried
+            schema.sampling_fields(body)
+            schema.boolean(body, "stream")
+            schema.tools(body)
+            schema.string(body, "user")
+        except schema.BadRequest as e:
+            raise GatewayError(400, "invalid_request", str(e))
+        for m in msgs:
+            if m.get("stable_kind") is not None and not (isinstance(m["stable_kind"], str) and m["stable_kind"] in pc.STABLE_ORDINAL):
+                raise GatewayError(400, "invalid_request", f"stable_kind must be one of {', '.join(pc.STABLE_ORDINAL)}")
         return body
 
     def price_msat(self, model: str, usage: InferenceUsage) -> int:

@@ -8,8 +8,6 @@ from __future__ import annotations
 
 import math
 
-from .generation import SamplingParams
-
 MAX_STOP_STRINGS = 16
 MAX_SEED = 2 ** 63 - 1
 # names the chat template is always rendered with: a request may add variables (reasoning_effort, ...), not replace these
@@ -81,15 +79,22 @@ def stop_strings(body: dict) -> tuple[str, ...]:
     raise BadRequest(f"stop must be a string or a list of at most {MAX_STOP_STRINGS} strings")
 
 
-def sampling_params(body: dict, default_max_tokens: int = 128, max_tokens: int | None = None) -> SamplingParams:
-    """The sampling options of a request.  ``max_tokens`` (alias ``max_output_tokens``) absent, null or 0 means the default,
-    ``top_p`` 0 or null means 1 (no nucleus cut), ``top_k`` 0 means no cut: the conventions the routes have always had.
+def sampling_fields(body: dict, default_max_tokens: int = 128, max_tokens: int | None = None) -> dict:
+    """The sampling options of a request, checked.  ``max_tokens`` (alias ``max_output_tokens``) absent, null or 0 means the
+    default, ``top_p`` 0 or null means 1 (no nucleus cut), ``top_k`` 0 means no cut: the conventions the routes have always had.
     ``max_tokens`` given as an argument overrides the body (the text-completion route has its own rule for 0)."""
     if max_tokens is None:
         max_tokens = integer(body, "max_tokens", 0) or integer(body, "max_output_tokens", 0) or default_max_tokens
-    return SamplingParams(max_tokens=max_tokens, temperature=number(body, "temperature", 0.0) or 0.0,
-                          top_p=number(body, "top_p", 0.0, 1.0) or 1.0, top_k=integer(body, "top_k", 0, 2 ** 31 - 1) or 0,
-                          stop=stop_strings(body), seed=integer(body, "seed", 0, MAX_SEED))
+    return {"max_tokens": max_tokens, "temperature": number(body, "temperature", 0.0) or 0.0,
+            "top_p": number(body, "top_p", 0.0, 1.0) or 1.0, "top_k": integer(body, "top_k", 0, 2 ** 31 - 1) or 0,
+            "stop": stop_strings(body), "seed": integer(body, "seed", 0, MAX_SEED)}
+
+
+def sampling_params(body: dict, default_max_tokens: int = 128, max_tokens: int | None = None):
+    """``sampling_fields`` as the scheduler's ``SamplingParams`` (imported here, so that this module stays importable without
+    the engine: the gateway applies the same checks in a process that never loads a model)."""
+    from .generation import SamplingParams
+    return SamplingParams(**sampling_fields(body, default_max_tokens, max_tokens))
 
 
 def messages(v, key: str = "messages") -> list[dict]:
@@ -132,7 +137,7 @@ def template_kwargs(body: dict) -> dict:
 def common(body: dict) -> None:
     """Checks shared by every generating route; raises ``BadRequest``."""
     string(body, "model")
-    sampling_params(body)
+    sampling_fields(body)
     boolean(body, "stream")
     tools(body)
     template_kwargs(body)

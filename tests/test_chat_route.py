@@ -221,3 +221,28 @@ def test_gateway_reaches_a_live_model_server_across_the_process_boundary(tmp_pat
         assert live.model("qwen-tiny").sched.stats["requests"] == served_before
     finally:
         httpd.shutdown()
+
+
+@pytest.mark.parametrize("patch,needle", [
+    ({"temperature": True}, "temperature"), ({"temperature": [1]}, "temperature"), ({"top_p": 2}, "top_p"), ({"top_k": 3.5}, "top_k"),
+    ({"seed": "x"}, "seed"), ({"stop": 0}, "stop"), ({"stop": [[]]}, "stop"), ({"stream": 1e9}, "stream"), ({"tools": 3.5}, "tools"),
+    ({"user": [[]]}, "user"), ({"max_tokens": True}, "max_tokens"), ({"max_tokens": 0}, "max_tokens"),
+    ({"messages": [{"role": "user", "content": "hi", "stable_kind": False}]}, "stable_kind"),
+    ({"messages": [{"role": "user", "content": "hi", "stable_kind": "nope"}]}, "stable_kind"),
+])
+def test_mistyped_options_are_refused_at_the_gateway_before_any_lane(state, patch, needle):
+    gw, fw = _gateway(state)
+    before = gw.keys["k1"].balance_msat
+    status, out = gw.handle("Bearer k1", json.dumps({**BODY, **patch}))
+    assert status == 400 and out["error"]["code"] == "invalid_request" and needle in out["error"]["message"], out
+    assert fw.calls == 0 and gw.keys["k1"].balance_msat == before and gw.keys["k1"].inflight == 0
+
+
+def test_engine_refusal_reaches_the_caller_as_a_400_not_an_exception(state):
+    """A request the gateway's own checks pass but the engine refuses (longer than its context window) comes back from the
+    in-process adapter as a typed, non-retryable 400."""
+    gw, _ = _gateway(state)
+    long_text = "word " * 6000
+    status, out = gw.handle("Bearer k1", json.dumps({**BODY, "messages": [{"role": "user", "content": long_text}]}))
+    assert status == 400 and out["error"]["code"] == "request_rejected" and "context" in out["error"]["message"], out
+    assert gw.keys["k1"].inflight == 0
