@@ -41,7 +41,11 @@ def _event(kind: int, content: dict, tags: list) -> dict:
 
 
 def tag_values(event: dict, name: str) -> list:
-    return [t[1:] for t in event["tags"] if t and t[0] == name]
+    """The values of every ``name`` tag.  Events come from relays: anything that is not a list of string lists counts as no tag."""
+    tags = event.get("tags") if isinstance(event, dict) else None
+    if not isinstance(tags, list):
+        return []
+    return [t[1:] for t in tags if isinstance(t, list) and t and t[0] == name and all(isinstance(x, str) for x in t)]
 
 
 def first_tag(event: dict, name: str):
@@ -51,15 +55,21 @@ def first_tag(event: dict, name: str):
 
 def check_event(event: dict) -> list[str]:
     """Missing required tags (unknown tags are never an error)."""
-    need = _REQUIRED.get(event.get("kind"))
+    if not isinstance(event, dict):
+        return ["not_an_event"]
+    kind = event.get("kind")
+    need = _REQUIRED.get(kind) if isinstance(kind, int) and not isinstance(kind, bool) else None
     if need is None:
-        return [f"unknown_kind:{event.get('kind')}"]
+        return [f"unknown_kind:{kind!r}"[:80]]
     errs = [f"missing_tag:{n}" for n in need if first_tag(event, n) is None]
     try:
-        if json.loads(event["content"]).get("schema") != 1:
-            errs.append("content_schema")
-    except (json.JSONDecodeError, AttributeError):
+        body = json.loads(event.get("content")) if isinstance(event.get("content"), str) else None
+    except ValueError:
+        body = None
+    if not isinstance(body, dict):
         errs.append("content_not_json")
+    elif body.get("schema") != 1:
+        errs.append("content_schema")
     return errs
 
 
@@ -112,19 +122,30 @@ def artifact_locator(window: dict, artifact_id: str, role: str, sha256: str, url
 def aggregate_window(window: dict, receipts: list[dict], verdicts: list[dict]) -> dict:
     """Which contributions an aggregate of this window may include and with what weights: same window and
     base checkpoint, an ``accepted`` verdict (by receipt index), and the window's participation floors."""
+    def number(event, name, default, cast):
+        """A numeric tag; one that does not parse counts as ``default`` (a receipt with a garbled weight contributes nothing)."""
+        try:
+            v = cast(first_tag(event, name) or default)
+            return v if v == v and abs(v) != float("inf") else default
+        except (TypeError, ValueError, OverflowError):
+            return default
+
+    if check_event(window) or first_tag(window, "d") is None:
+        raise TrnError("the window record is malformed")
     wid, base = first_tag(window, "d"), first_tag(window, "base_checkpoint")
-    accepted = {tag_values(v, "e")[0][0] for v in verdicts if first_tag(v, "window") == wid and first_tag(v, "status") == "accepted"}
+    accepted = {first_tag(v, "e") for v in verdicts if first_tag(v, "window") == wid and first_tag(v, "status") == "accepted"} - {None}
     admitted, offered = [], 0
     for i, r in enumerate(receipts):
-        if first_tag(r, "window") != wid:
+        if not isinstance(r, dict) or first_tag(r, "window") != wid:
             continue
-        w = int(first_tag(r, "weight") or 0)
+        w = max(0, number(r, "weight", 0, int))
         offered += w
-        if first_tag(r, "base_checkpoint") == base and r.get("id", f"receipt-{i}") in accepted and w > 0:
-            admitted.append({"trainer": tag_values(r, "p")[0][0], "weight": w, "artifact": first_tag(r, "artifact")})
+        rid = r.get("id", f"receipt-{i}")
+        if first_tag(r, "base_checkpoint") == base and isinstance(rid, str) and rid in accepted and w > 0 and first_tag(r, "p") is not None:
+            admitted.append({"trainer": first_tag(r, "p"), "weight": w, "artifact": first_tag(r, "artifact")})
     total = sum(a["weight"] for a in admitted)
-    ok = (len(admitted) >= int(first_tag(window, "min_participants") or 1)
-          and (offered == 0 or total / offered >= float(first_tag(window, "min_weight_fraction") or 0)) and total > 0)
+    ok = (len(admitted) >= max(1, number(window, "min_participants", 1, int))
+          and (offered == 0 or total / offered >= number(window, "min_weight_fraction", 0.0, float)) and total > 0)
     return {"window": wid, "base_checkpoint": base, "aggregation_rule": first_tag(window, "aggregation_rule"), "admitted": admitted,
             "admitted_update_count": len(admitted), "admitted_weight_total": str(total),
             "normalized_weights": [a["weight"] / total for a in admitted] if total else [], "promotion_state": "candidate" if ok else "superseded",

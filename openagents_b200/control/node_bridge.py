@@ -80,7 +80,13 @@ def decode_gepa_candidate_manifest(m) -> dict:
     for k in ("split_refs", "target_suites", "target_failure_families"):
         if not m[k]:
             raise CandidateManifestError(f"{P}.{k}", "must be non-empty")
-    pi, ci, sb = m.get("probe_import") or {}, m.get("benchmark_cloud_import") or {}, m.get("safety_boundary") or {}
+    for k in ("probe_import", "benchmark_cloud_import", "safety_boundary", "components"):
+        if not isinstance(m.get(k), dict):
+            raise CandidateManifestError(f"{P}.{k}", "must be an object")
+    pi, ci, sb = m["probe_import"], m["benchmark_cloud_import"], m["safety_boundary"]
+    for k in ("blueprint_candidate_ref", "loop_policy_candidate_ref", "prompt_candidate_ref", "tool_menu_candidate_ref"):
+        if not isinstance(pi.get(k), str) or not pi[k].strip():
+            raise CandidateManifestError(f"{P}.probe_import.{k}", "must be a non-empty string")
     if pi.get("schema_version") != GEPA_PROBE_IMPORT_SCHEMA or ci.get("schema_version") != GEPA_CLOUD_IMPORT_SCHEMA:
         raise CandidateManifestError(f"{P}.probe_import", "import blocks carry their own schema versions")
     if not ci.get("artifact_contract_refs"):
@@ -93,7 +99,7 @@ def decode_gepa_candidate_manifest(m) -> dict:
         raise CandidateManifestError(f"{P}.safety_boundary", "must inherit runtime authority from the Probe assignment")
     if sb.get("public_claim_upgrade_authority"):
         raise CandidateManifestError(f"{P}.safety_boundary.public_claim_upgrade_authority", "candidate text cannot carry public-claim upgrade authority")
-    comp = m.get("components") or {}
+    comp = m["components"]
     fam = comp.get("failure_family_playbooks")
     if not isinstance(fam, dict) or not fam:
         raise CandidateManifestError(f"{P}.components.failure_family_playbooks", "must be non-empty")
@@ -227,9 +233,11 @@ TASK_MODES = ("coding_agent", "requires_2b")
 
 
 def admission_from_model_rows(rows) -> dict:
-    """rows: [{modelRef, ready}] as listed by the model server (``/v1/models``)."""
+    """rows: [{modelRef, ready}] as listed by the model server (``/v1/models``).  The listing comes over HTTP: anything that is
+    not a row with a string ``modelRef`` is dropped rather than trusted."""
+    rows = [r for r in rows if isinstance(r, dict) and isinstance(r.get("modelRef"), str) and r["modelRef"]] if isinstance(rows, (list, tuple)) else []
     observed = [r["modelRef"] for r in rows]
-    admitted = [r["modelRef"] for r in rows if r.get("ready", True)]
+    admitted = [r["modelRef"] for r in rows if r.get("ready", True) is True]
     return {"rows": list(rows), "observedModelRefs": observed, "admittedModelRefs": admitted,
             "blockerRefs": [] if admitted else ["blocker.psionic_qwen35.qwen35_model_missing"]}
 

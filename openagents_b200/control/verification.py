@@ -69,7 +69,7 @@ def verify_freivalds_merkle(payload: dict, challenge_ref: str = "challenge.local
         codes.append("FieldMismatch")
     if claimed is not None and r.size != claimed.shape[1] and "DimensionMismatch" not in codes:
         codes.append("DimensionMismatch")
-    openings = payload.get("rowOpenings") or []
+    openings = payload.get("rowOpenings") if isinstance(payload.get("rowOpenings"), (list, tuple)) else []
     if len(openings) == 0:
         codes.append("RowOpeningMissing")
     if payload.get("merkleProofValid") is False:
@@ -141,10 +141,10 @@ def verify_exact_trace_replay(payload: dict, challenge_ref: str = "challenge.loc
 def _verify_threshold(class_name: str, payload: dict, challenge_ref: str) -> Verdict:
     obs = payload.get("observedScore")
     thr = payload.get("minimumScore", 1)
-    ok = isinstance(obs, (int, float)) and np.isfinite(obs) and obs >= thr
+    num = lambda x: isinstance(x, (int, float)) and not isinstance(x, bool) and np.isfinite(x)      # noqa: E731
+    ok = num(obs) and num(thr) and obs >= thr
     return Verdict(class_name, "Verified" if ok else "Rejected", () if ok else ("StatisticalThresholdFailed",),
-                   challenge_ref, {"observedScore": obs if isinstance(obs, (int, float)) and np.isfinite(obs) else None,
-                                   "threshold": thr})
+                   challenge_ref, {"observedScore": obs if num(obs) else None, "threshold": thr if num(thr) else None})
 
 
 @dataclass(frozen=True)

@@ -119,6 +119,12 @@ def tools(body: dict) -> list[dict]:
         return []
     if not isinstance(v, list) or not all(isinstance(t, dict) for t in v):
         raise BadRequest("tools must be a list of objects")
+    for i, t in enumerate(v):
+        fn = t.get("function")
+        if t.get("type", "function") != "function" or not isinstance(fn, dict) or not isinstance(fn.get("name"), str) or not fn["name"]:
+            raise BadRequest(f"tools[{i}] must be {{\"type\": \"function\", \"function\": {{\"name\": ..., \"parameters\": ...}}}}")
+        if not isinstance(fn.get("parameters"), (dict, type(None))) or not isinstance(fn.get("description"), (str, type(None))):
+            raise BadRequest(f"tools[{i}].function: parameters must be an object and description a string")
     return v
 
 

@@ -36,9 +36,18 @@ class ToolCallError(Exception):
         self.kind = kind
 
 
+def function_names(tools) -> set:
+    """Names of the well-formed function tools in ``tools`` (entries of any other shape are ignored)."""
+    if not isinstance(tools, (list, tuple)):
+        return set()
+    return {t["function"]["name"] for t in tools
+            if isinstance(t, dict) and t.get("type", "function") == "function" and isinstance(t.get("function"), dict)
+            and isinstance(t["function"].get("name"), str) and t["function"]["name"]}
+
+
 def normalize_tool_choice(choice, tools) -> tuple[str, str | None]:
     """-> (mode, function name) with mode in auto | none | required | named."""
-    names = {t["function"]["name"] for t in tools or [] if t.get("type") == "function" and "function" in t}
+    names = function_names(tools)
     if choice is None:
         return ("auto" if names else "none"), None
     if isinstance(choice, str):
@@ -47,8 +56,9 @@ def normalize_tool_choice(choice, tools) -> tuple[str, str | None]:
         if choice == "required" and not names:
             raise ToolCallError("invalid_tool_choice", "tool_choice required needs tools")
         return choice, None
-    name = (choice.get("function") or {}).get("name") if isinstance(choice, dict) else None
-    if name not in names:
+    fn = choice.get("function") if isinstance(choice, dict) else None
+    name = fn.get("name") if isinstance(fn, dict) else None
+    if not isinstance(name, str) or name not in names:
         raise ToolCallError("invalid_tool_choice", f"tool_choice names an unknown function {name!r}")
     return "named", name
 
@@ -66,7 +76,7 @@ def render_tools_system_message(tools, mode: str, name: str | None) -> dict | No
 
 def parse_tool_calls(text: str, tools=None) -> tuple[str, list[dict]]:
     """-> (text outside the blocks, OpenAI tool_calls).  Malformed blocks and unknown names are dropped into the text."""
-    names = {t["function"]["name"] for t in tools or [] if "function" in t} if tools is not None else None
+    names = function_names(tools) if tools is not None else None
     calls, out, pos = [], [], 0
     for m in _BLOCK.finditer(text):
         try:

@@ -62,8 +62,21 @@ def make_manifest(assignment_id: str, lane: str, inputs: list[dict], steps: int,
     return m
 
 
+def _int(v, lo: int = 1, hi: int | None = None) -> bool:
+    return isinstance(v, int) and not isinstance(v, bool) and v >= lo and (hi is None or v <= hi)
+
+
+def _num(v, lo: float = 0.0) -> bool:
+    return isinstance(v, (int, float)) and not isinstance(v, bool) and v == v and lo <= v < float("inf")
+
+
+SCHEDULES = ("cosine", "wsd", "constant")
+INPUT_ROLES = ("shard", "records", "pairs", "tokenizer")
+
+
 def validate(m) -> list[str]:
-    """Blocker refs (empty = the manifest can be executed here)."""
+    """Blocker refs (empty = the manifest can be executed here).  A manifest arrives from a coordinator: every field the lowering
+    reads is type-checked here, so that a malformed one is refused with a named blocker and never raises further down."""
     b = []
     if not isinstance(m, dict) or m.get("schema") != SCHEMA:
         return ["blocker.training_assignment.schema"]
@@ -71,22 +84,44 @@ def validate(m) -> list[str]:
         b.append("blocker.training_assignment.assignment_id")
     if m.get("lane") not in LANES:
         b.append("blocker.training_assignment.unknown_lane")
-    bud = m.get("budget") or {}
-    if not (isinstance(bud.get("steps"), int) and 0 < bud["steps"] <= 10_000_000 and isinstance(bud.get("maxWallSeconds"), int) and bud["maxWallSeconds"] > 0):
+    bud = m.get("budget") if isinstance(m.get("budget"), dict) else {}
+    if not (_int(bud.get("steps"), 1, 10_000_000) and _int(bud.get("maxWallSeconds"))):
         b.append("blocker.training_assignment.budget")
-    bt = m.get("batch") or {}
-    if not all(isinstance(bt.get(k), int) and bt[k] > 0 for k in ("global", "micro", "seqLen")) or (bt.get("global", 1) % (bt.get("micro", 1) * max(1, m.get("nproc", 1)))):
+    bt = m.get("batch") if isinstance(m.get("batch"), dict) else {}
+    nproc = m.get("nproc", 1)
+    if not _int(nproc, 1, 4096):
+        b.append("blocker.training_assignment.nproc")
+        nproc = 1
+    if not all(_int(bt.get(k)) for k in ("global", "micro", "seqLen")) or bt["global"] % (bt["micro"] * nproc):
         b.append("blocker.training_assignment.batch_geometry")
-    roles = [i.get("role") for i in m.get("inputs") or []]
-    need = {"pretrain": None, "sft": "records", "dpo": "pairs"}.get(m.get("lane"))
-    if need and need not in roles:
+    model = m.get("model") if isinstance(m.get("model"), dict) else {}
+    if not (isinstance(model.get("preset"), str) and _SAFE.match(model["preset"]) and (model.get("layers") is None or _int(model["layers"], 0, 4096))):
+        b.append("blocker.training_assignment.model")
+    opt = m.get("optimizer") if isinstance(m.get("optimizer"), dict) else {}
+    if not (_num(opt.get("lr")) and opt["lr"] > 0 and isinstance(opt.get("schedule"), str) and opt["schedule"] in SCHEDULES
+            and _int(opt.get("warmupSteps"), 0) and _num(opt.get("beta", 0.1))):
+        b.append("blocker.training_assignment.optimizer")
+    if not _int(m.get("seed"), 0, 2 ** 63 - 1):
+        b.append("blocker.training_assignment.seed")
+    if not isinstance(m.get("expectedOutputs"), dict):
+        b.append("blocker.training_assignment.expected_outputs")
+    inputs = m.get("inputs") if isinstance(m.get("inputs"), list) else None
+    if inputs is None or not all(isinstance(i, dict) for i in inputs):
+        b.append("blocker.training_assignment.inputs")
+        inputs = []
+    need = {"pretrain": None, "sft": "records", "dpo": "pairs"}.get(m.get("lane") if isinstance(m.get("lane"), str) else None)
+    if need and need not in [i.get("role") for i in inputs]:
         b.append(f"blocker.training_assignment.missing_input.{need}")
-    for i in m.get("inputs") or []:
-        if not (isinstance(i.get("sha256"), str) and _DIGEST.match(i["sha256"]) and isinstance(i.get("bytes"), int) and isinstance(i.get("path"), str)):
+    for i in inputs:
+        if not (isinstance(i.get("sha256"), str) and _DIGEST.match(i["sha256"]) and _int(i.get("bytes"), 0) and isinstance(i.get("path"), str) and i["path"]
+                and i.get("role") in INPUT_ROLES and isinstance(i.get("ref"), str) and _SAFE.match(i["ref"])):
             b.append("blocker.training_assignment.input_not_pinned")
             break
-    want = m.get("manifestDigest")
-    if want != mf.canonical_digest({k: v for k, v in m.items() if k != "manifestDigest"}):
+    try:
+        digest = mf.canonical_digest({k: v for k, v in m.items() if k != "manifestDigest"})
+    except (TypeError, ValueError):
+        digest = None
+    if digest is None or m.get("manifestDigest") != digest:
         b.append("blocker.training_assignment.manifest_digest_mismatch")
     return b
 
