@@ -242,8 +242,7 @@ def sft_worker(args, cfg, dev, rank, world):
     from .trainer import Trainer
     if not args.sft_records:
         raise SystemExit("--lane sft needs --sft-records")
-    with open(args.sft_records) as f:
-        records = [json.loads(line) for line in f if line.strip()]
+    records = sft.load_records(args.sft_records)
     text = "\n".join(m["content"] for r in records for m in r["messages"]).encode()
     tok = ByteBpe.train(text, args.sft_merges, special=sft.SPECIAL_TOKENS)
     if tok.vocab_size > cfg.model.vocab:
@@ -285,8 +284,7 @@ def dpo_worker(args, cfg, dev, rank, world):
     from .trainer import Trainer
     if not args.dpo_pairs:
         raise SystemExit("--lane dpo needs --dpo-pairs")
-    with open(args.dpo_pairs) as f:
-        pairs = [json.loads(line) for line in f if line.strip()]
+    pairs = sft.load_records(args.dpo_pairs, preference=True)
     text = "\n".join([m["content"] for p in pairs for m in p["messages"]] + [p[k] for p in pairs for k in ("chosen", "rejected")]).encode()
     tok = ByteBpe.train(text, args.sft_merges, special=sft.SPECIAL_TOKENS)
     if tok.vocab_size > cfg.model.vocab:

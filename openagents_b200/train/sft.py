@@ -60,11 +60,48 @@ def generation_prompt(messages) -> str:
     return render_text(messages) + TEMPLATE["roles"]["assistant"] + TEMPLATE["afterRoleMarker"]
 
 
+def check_messages(messages, where: str = "messages", need_assistant: bool = True) -> None:
+    """Raise ``ValueError`` naming ``where`` unless ``messages`` is a list of ``{"role": system|user|assistant|..., "content": str}``."""
+    if not isinstance(messages, list) or not messages:
+        raise ValueError(f"{where}: must be a non-empty list of messages")
+    for i, m in enumerate(messages):
+        if not isinstance(m, dict) or m.get("role") not in TEMPLATE["roles"] or not isinstance(m.get("content"), str):
+            raise ValueError(f"{where}[{i}]: a message is {{\"role\": one of {', '.join(TEMPLATE['roles'])}, \"content\": text}}")
+    if need_assistant and not any(m["role"] == "assistant" and m["content"] for m in messages):
+        raise ValueError(f"{where}: an example needs at least one non-empty assistant message")
+
+
+def load_records(path: str, preference: bool = False) -> list[dict]:
+    """The records of a JSON-lines file (blank lines skipped), each checked: ``{"messages": [...]}`` for instruction tuning,
+    plus non-empty ``chosen`` and ``rejected`` answers for preference pairs (whose messages are the prompt turns only).  A bad
+    line raises ``ValueError`` with the file name and line number."""
+    out = []
+    with open(path, encoding="utf-8") as f:
+        for n, line in enumerate(f, 1):
+            if not line.strip():
+                continue
+            where = f"{path}:{n}"
+            try:
+                rec = json.loads(line)
+            except ValueError as e:
+                raise ValueError(f"{where}: not JSON ({e})") from None
+            if not isinstance(rec, dict):
+                raise ValueError(f"{where}: a record is a JSON object")
+            check_messages(rec.get("messages"), f"{where}: messages", need_assistant=not preference)
+            if preference:
+                for key in ("chosen", "rejected"):
+                    if not isinstance(rec.get(key), str) or not rec[key].strip():
+                        raise ValueError(f"{where}: {key} must be a non-empty string")
+            out.append(rec)
+    if not out:
+        raise ValueError(f"{path}: no records")
+    return out
+
+
 def render_example(messages, tokenizer) -> tuple[list[int], list[int]]:
     """Token ids and the loss mask (1 = trainable).  ``tokenizer.encode`` must map the four markers to single ids
     (``data.bpe.ByteBpe`` with ``special=SPECIAL_TOKENS`` does)."""
-    if not messages or not any(m.get("role") == "assistant" and m.get("content") for m in messages):
-        raise ValueError("an example needs at least one non-empty assistant message")
+    check_messages(messages, "example")
     ids: list[int] = []
     mask: list[int] = []
     for m in messages:
@@ -103,7 +140,9 @@ def build_corpus(records, tokenizer, dataset_identity: str, rights_posture: str 
     all_ids, all_mask, offsets, digests = [], [], [], []
     n = 0
     for rec in records:
-        ids, mask = render_example(rec["messages"], tokenizer)
+        if not isinstance(rec, dict):
+            raise ValueError(f"record {n}: a record is an object with messages")
+        ids, mask = render_example(rec.get("messages"), tokenizer)
         offsets.append(len(all_ids))
         all_ids += ids
         all_mask += mask

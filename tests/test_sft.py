@@ -171,3 +171,31 @@ def test_distillation_records_from_a_teacher_backend_feed_the_lane(tmp_path):
     q = distill.quality_delta(teacher, teacher, Tok, Tok, [{"prompt": sft.generation_prompt([{"role": "user", "content": prompts[0]}]),
                                                             "answer": recs[0]["messages"][-1]["content"]}], max_new_tokens=6)
     assert q["qualityDeltaBps"] == 0 and q["baselineQualityScoreBps"] == q["candidateQualityScoreBps"] and q["items"] == 1
+
+
+def test_record_files_are_checked_line_by_line(tmp_path):
+    """A tuning file is user data: a bad line is reported with the file and the line number, before any training starts."""
+    import json
+    good = {"messages": [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "hello"}]}
+    p = tmp_path / "records.jsonl"
+    p.write_text(json.dumps(good) + "\n\n" + json.dumps(good) + "\n")
+    assert len(sft.load_records(str(p))) == 2
+    cases = [("{not json", "not JSON"), ("[1, 2]", "a record is a JSON object"), ('{"messages": "hi"}', "non-empty list of messages"),
+             ('{"messages": [{"role": "wizard", "content": "x"}]}', r"messages\[0\]"), ('{"messages": [{"role": "user", "content": 5}]}', r"messages\[0\]"),
+             ('{"messages": [5]}', r"messages\[0\]"), ('{"messages": [{"role": "user", "content": "only a question"}]}', "assistant")]
+    for line, needle in cases:
+        p.write_text(json.dumps(good) + "\n" + line + "\n")
+        with pytest.raises(ValueError, match=rf"records\.jsonl:2: .*{needle}"):
+            sft.load_records(str(p))
+    p.write_text("\n\n")
+    with pytest.raises(ValueError, match="no records"):
+        sft.load_records(str(p))
+    pair = {"messages": [{"role": "user", "content": "red or blue?"}], "chosen": "red", "rejected": "blue"}
+    p.write_text(json.dumps(pair) + "\n")
+    assert sft.load_records(str(p), preference=True) == [pair]
+    for patch, needle in (({"chosen": ""}, "chosen"), ({"rejected": 5}, "rejected"), ({"messages": []}, "messages")):
+        p.write_text(json.dumps({**pair, **patch}) + "\n")
+        with pytest.raises(ValueError, match=rf"records\.jsonl:1: .*{needle}"):
+            sft.load_records(str(p), preference=True)
+    with pytest.raises(ValueError, match="record 0"):
+        sft.build_corpus([7], None, "x")
