@@ -47,10 +47,7 @@ def main(argv=None) -> int:
     from ..serve.backend import open_backend
     from ..serve.server import load_tokenizer
     from .pack import EvalPack, eval_run_evidence, run_pack
-
-    def lines(path):
-        with open(path) as f:
-            return [json.loads(x) for x in f if x.strip()]
+    from .scorers import load_items
 
     backend = open_backend(args.model, args.backend, args.device, max_num_seqs=4, max_ctx=max(args.seq_len, 512) + 64,
                            max_tokens=max(args.seq_len, 512) + 64)
@@ -60,9 +57,9 @@ def main(argv=None) -> int:
         tasks.append({"name": "heldout", "kind": "perplexity", "dataset": TokenDataset(args.heldout, args.seq_len, args.raw_width),
                       "max_windows": args.max_windows or None, "shards": len(args.heldout), "seq_len": args.seq_len})
     if args.choices:
-        tasks.append({"name": "mc", "kind": "multiple_choice", "items": lines(args.choices)})
+        tasks.append({"name": "mc", "kind": "multiple_choice", "items": load_items(args.choices, "multiple_choice")})
     if args.exact:
-        tasks.append({"name": "em", "kind": "exact_match", "items": lines(args.exact), "max_new_tokens": args.max_new_tokens,
+        tasks.append({"name": "em", "kind": "exact_match", "items": load_items(args.exact, "exact_match"), "max_new_tokens": args.max_new_tokens,
                       "stop_ids": [tok.eos_id] if getattr(tok, "eos_id", None) is not None else []})
     if not tasks:
         ap.error("nothing to evaluate: give --heldout, --choices or --exact")

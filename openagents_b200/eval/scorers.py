@@ -48,6 +48,41 @@ def perplexity(backend, dataset, max_windows: int | None = None, seq_base: int =
     return out
 
 
+def load_items(path: str, kind: str) -> list[dict]:
+    """The items of a JSON-lines task file, each checked before any model time is spent: ``multiple_choice`` items are
+    ``{"context": text, "choices": [two or more texts], "answer": index}``, ``exact_match`` items ``{"prompt": text, "answer": text}``.
+    A bad line raises ``ValueError`` with the file name and line number."""
+    import json
+    if kind not in ("multiple_choice", "exact_match"):
+        raise ValueError(f"unknown task kind {kind!r}")
+    text = lambda v: isinstance(v, str) and v.strip() != ""      # noqa: E731
+    out = []
+    with open(path, encoding="utf-8") as f:
+        for n, line in enumerate(f, 1):
+            if not line.strip():
+                continue
+            where = f"{path}:{n}"
+            try:
+                it = json.loads(line)
+            except ValueError as e:
+                raise ValueError(f"{where}: not JSON ({e})") from None
+            if not isinstance(it, dict):
+                raise ValueError(f"{where}: an item is a JSON object")
+            if kind == "multiple_choice":
+                ch = it.get("choices")
+                if not text(it.get("context")) or not isinstance(ch, list) or len(ch) < 2 or not all(text(c) for c in ch):
+                    raise ValueError(f"{where}: an item is {{\"context\": text, \"choices\": [two or more texts], \"answer\": index}}")
+                a = it.get("answer")
+                if not isinstance(a, int) or isinstance(a, bool) or not 0 <= a < len(ch):
+                    raise ValueError(f"{where}: answer must be the index of one of the {len(ch)} choices")
+            elif not text(it.get("prompt")) or not isinstance(it.get("answer"), str):
+                raise ValueError(f"{where}: an item is {{\"prompt\": text, \"answer\": text}}")
+            out.append(it)
+    if not out:
+        raise ValueError(f"{path}: no items")
+    return out
+
+
 def multiple_choice(backend, items, tokenizer, length_normalised: bool = True, seq_base: int = 1 << 41) -> dict:
     """``items``: ``{"context": str, "choices": [str, ...], "answer": index}``.  Returns accuracy and the per-item picks."""
     if not (backend.supports_score and backend.supports_verify):

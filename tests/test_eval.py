@@ -136,3 +136,27 @@ def test_command_line_runs_a_pack_on_a_gguf_file(tmp_path, capsys):
     assert rc == 4 and json.loads(capsys.readouterr().out)["decisionState"] == "rollback"
     g = parse_gate("a.b:>=:0.5:rollback")
     assert g.rollback_on_fail and g.required and g.threshold == 0.5
+
+
+def test_task_files_are_checked_line_by_line(tmp_path):
+    import json
+    from openagents_b200.eval.scorers import load_items
+    p = tmp_path / "mc.jsonl"
+    good = {"context": "2 + 2 =", "choices": [" 4", " 5"], "answer": 0}
+    p.write_text(json.dumps(good) + "\n\n" + json.dumps(good) + "\n")
+    assert load_items(str(p), "multiple_choice") == [good, good]
+    for line, needle in (("{oops", "not JSON"), ("7", "JSON object"), (json.dumps({**good, "choices": [" 4"]}), "two or more"), (json.dumps({**good, "answer": 2}), "index of one of the 2"),
+                         (json.dumps({**good, "answer": True}), "index"), (json.dumps({**good, "context": ""}), "context"), (json.dumps({**good, "choices": [" 4", 5]}), "choices")):
+        p.write_text(json.dumps(good) + "\n" + line + "\n")
+        with pytest.raises(ValueError, match=rf"mc\.jsonl:2: .*{needle}"):
+            load_items(str(p), "multiple_choice")
+    p.write_text(json.dumps({"prompt": "Say hi", "answer": "hi"}) + "\n")
+    assert len(load_items(str(p), "exact_match")) == 1
+    p.write_text(json.dumps({"prompt": "Say hi"}) + "\n")
+    with pytest.raises(ValueError, match=r"mc\.jsonl:1: .*prompt"):
+        load_items(str(p), "exact_match")
+    p.write_text("\n")
+    with pytest.raises(ValueError, match="no items"):
+        load_items(str(p), "exact_match")
+    with pytest.raises(ValueError, match="unknown task kind"):
+        load_items(str(p), "essay")
