@@ -243,6 +243,13 @@ class _Server(ThreadingHTTPServer):
     request_queue_size = 1024
     daemon_threads = True
 
+    def handle_error(self, request, client_address):
+        """A client that goes away mid-request is routine, not a traceback on stderr; anything else is still reported."""
+        import sys
+        if isinstance(sys.exc_info()[1], (ConnectionError, TimeoutError)):
+            return
+        super().handle_error(request, client_address)
+
 
 def serve(gw: ChatGateway, host: str = "127.0.0.1", port: int = 8787, admin_key: str | None = None) -> ThreadingHTTPServer:
     return _Server((host, port), make_handler(gw, admin_key))

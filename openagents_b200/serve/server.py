@@ -693,6 +693,13 @@ class _Server(ThreadingHTTPServer):
     # the default listen backlog of 5 resets connections when a few dozen clients connect in the same instant
     request_queue_size = 1024
 
+    def handle_error(self, request, client_address):
+        """A client that goes away mid-request is routine, not a traceback on stderr; anything else is still reported."""
+        import sys
+        if isinstance(sys.exc_info()[1], (ConnectionError, TimeoutError)):
+            return
+        super().handle_error(request, client_address)
+
 
 def serve(state: ServerState, host: str = "127.0.0.1", port: int = 8080) -> ThreadingHTTPServer:
     httpd = _Server((host, port), make_handler(state))

@@ -647,3 +647,69 @@ def test_attach_client_streams_a_session_turn(server):
     got = list(c.stream_turn(sid, "hello there", max_tokens=5))
     assert [k for k, _ in got][-1] == "completed" and all(k == "snapshot" for k, _ in got[:-1])
     assert got[-1][1]["output"] == got[-2][1] and got[-1][1]["usage"]["completion_tokens"] == 5
+
+
+def test_mixed_concurrent_traffic_with_abandoned_streams_leaves_nothing_behind(gguf_path):
+    """Eight clients at once over every generating route, some hanging up in the middle of a stream: every request is answered,
+    no handler or scheduler state is left over (sequences, KV tokens, sessions), and the server still answers afterwards."""
+    import random
+    import socket
+    model = ServedModel("tiny", CpuBackend.from_gguf(gguf_path), None, max_num_seqs=4)
+    state = ServerState([model])
+    httpd = serve(state, "127.0.0.1", 0)
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    port = httpd.server_address[1]
+    base = f"http://127.0.0.1:{port}"
+
+    def abandon(path, body):
+        s = socket.create_connection(("127.0.0.1", port))
+        data = json.dumps(body).encode()
+        s.sendall(f"POST {path} HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\nContent-Length: {len(data)}\r\n\r\n".encode() + data)
+        s.recv(200)
+        s.close()
+
+    problems = []
+
+    def client(i):
+        rnd = random.Random(i)
+        for j in range(8):
+            msgs = [{"role": "user", "content": f"hello {i} {j} " + "x" * rnd.randrange(40)}]
+            try:
+                k = (i + j) % 5
+                if k == 0:
+                    code = _post(base + "/v1/chat/completions", {"messages": msgs, "max_tokens": rnd.randrange(1, 10)})[0]
+                elif k == 1:
+                    code = _post(base + "/v1/chat/completions", {"messages": msgs, "max_tokens": 6, "stream": True})[0]
+                elif k == 2:
+                    abandon("/v1/chat/completions", {"messages": msgs, "max_tokens": 48, "stream": True})
+                    code = 200
+                elif k == 3:
+                    code = _post(base + "/v1/completions", {"prompt": "abc " * 5, "max_tokens": 3, "echo": True, "logprobs": 1})[0]
+                else:
+                    sid = json.loads(_post(base + "/v1/sessions", {})[1])["id"]
+                    _post(base + f"/v1/sessions/{sid}/responses/stream", {"prompt": "hi", "max_tokens": 4})
+                    code = _post(base + f"/v1/sessions/{sid}/responses", {"prompt": "more", "max_tokens": 4})[0]
+                    urllib.request.urlopen(urllib.request.Request(base + f"/v1/sessions/{sid}", method="DELETE"), timeout=60).read()
+                if code != 200:
+                    problems.append((k, code))
+            except Exception as e:      # noqa: BLE001
+                problems.append((i, j, repr(e)))
+
+    try:
+        threads = [threading.Thread(target=client, args=(i,)) for i in range(8)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(timeout=240)
+        assert not any(t.is_alive() for t in threads) and problems == []
+        import time
+        deadline = time.time() + 10               # an abandoned stream is cancelled when its next token cannot be written
+        while time.time() < deadline and (model.sched.running or model.sched.waiting):
+            time.sleep(0.05)
+        assert not model.sched.running and not model.sched.waiting and state.sessions == {}
+        assert model.backend.kv_stats()["sequences"] == 0 and model.backend.kv_stats()["tokens"] == 0
+        assert model.sched.stats["errors"] == 0 and model.thread.is_alive()
+        assert _post(base + "/v1/chat/completions", {"messages": [{"role": "user", "content": "still there?"}], "max_tokens": 2})[0] == 200
+    finally:
+        httpd.shutdown()
+        model.close()

@@ -3,7 +3,6 @@ answer (a verdict, blocker refs, a list of problems) or raise their own declared
 few hundred seeded mutations of a valid record (fields replaced by values of other types, dropped, nested ones mutated in turn)
 and must never leak a TypeError / KeyError / AttributeError from its own bookkeeping."""
 import copy
-import os
 import random
 
 import pytest
