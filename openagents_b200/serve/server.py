@@ -169,6 +169,8 @@ class Session:
         self.responses: list[str] = []
         self.instructions: str | None = None   # a system message that opens the session's first turn
         self.created = time.time()
+        self.last_used = self.created
+        self.busy = 0                          # turns in flight; a busy session is never evicted
 
 
 class ServerState:
@@ -177,6 +179,12 @@ class ServerState:
         self.default = models[0]
         self.sessions: dict[str, Session] = {}
         self.responses: dict[str, tuple[str, str]] = {}     # response id -> (session id, text)
+        # an idle session pins the KV pages of its conversation: sessions are dropped after ``session_ttl_s`` without a turn, the
+        # least recently used ones beyond ``max_sessions``, and as many idle ones as it takes when the KV pool runs out
+        self.max_sessions = int(os.environ.get("B200_SERVE_MAX_SESSIONS", "1024"))
+        self.session_ttl_s = float(os.environ.get("B200_SERVE_SESSION_TTL_S", "1800"))
+        self.sessions_evicted = 0
+        self._sess_lock = threading.Lock()
         self.reasoning_budget, self.mesh_coordination = reasoning_budget, mesh_coordination
         self.started = time.time()
         self.allow_shutdown = False
@@ -196,9 +204,79 @@ class ServerState:
             raise KeyError(name)
         return self.models[name]
 
+    # ---- sessions
+    def add_session(self, s: Session) -> Session:
+        self.reap_sessions()
+        with self._sess_lock:
+            self.sessions[s.id] = s
+        return s
+
+    def drop_session(self, sid: str) -> Session | None:
+        """Forget a session and give its sequence (its KV pages) back; its response ids stop resolving."""
+        with self._sess_lock:
+            s = self.sessions.pop(sid, None)
+            if s is None:
+                return None
+            for rid in s.responses:
+                self.responses.pop(rid, None)
+        if s.seq_id is not None:
+            with s.model.lock:
+                try:
+                    s.model.backend.end(s.seq_id)
+                except Exception:      # noqa: BLE001 - the sequence may already be gone (a failed turn closed it)
+                    pass
+            s.seq_id = None
+        return s
+
+    def reap_sessions(self, need_room: bool = False, now: float | None = None) -> int:
+        """Drop expired sessions and the least recently used ones beyond the cap; with ``need_room`` (the KV pool ran out) also the
+        least recently used idle half of what is left.  Returns how many were dropped."""
+        now = time.time() if now is None else now
+        with self._sess_lock:
+            idle = sorted((s for s in self.sessions.values() if not s.busy), key=lambda s: s.last_used)
+            victims = [s for s in idle if now - s.last_used > self.session_ttl_s]
+            rest = [s for s in idle if s not in victims]
+            over = len(self.sessions) - len(victims) - self.max_sessions + 1
+            if over > 0:
+                victims += rest[:over]
+                rest = rest[over:]
+            if need_room and rest:
+                victims += rest[:max(1, len(rest) // 2)]
+        n = sum(1 for s in victims if self.drop_session(s.id) is not None)
+        self.sessions_evicted += n
+        return n
+
     # ---- one completion, with or without a session
     def complete(self, model: ServedModel, messages: list[dict], body: dict, session: Session | None = None,
                  on_token=None) -> tuple[Request, dict]:
+        """Runs the completion.  When the KV pool is exhausted, idle sessions are evicted; the request itself is tried once more
+        if nothing of it has been seen yet (no token streamed, no earlier turns whose KV the failure just gave up)."""
+        if session is not None:
+            with self._sess_lock:
+                session.busy += 1
+                session.last_used = time.time()
+        fresh = session is None or session.seq_id is None
+        emitted = [0]
+
+        def counted(t):
+            emitted[0] += 1
+            if on_token:
+                on_token(t)
+        try:
+            try:
+                return self._complete(model, messages, body, session, counted)
+            except MemoryError:
+                if self.reap_sessions(need_room=True) == 0 or not fresh or emitted[0]:
+                    raise
+                return self._complete(model, messages, body, session, counted)
+        finally:
+            if session is not None:
+                with self._sess_lock:
+                    session.busy -= 1
+                    session.last_used = time.time()
+
+    def _complete(self, model: ServedModel, messages: list[dict], body: dict, session: Session | None = None,
+                  on_token=None) -> tuple[Request, dict]:
         params = schema.sampling_params(body)
         tok = model.tok
         toks = getattr(tok, "tokens", None)
@@ -223,7 +301,15 @@ class ServerState:
                 except RequestRejected:
                     raise
                 except Exception:
-                    session.seq_id, session.tokens, session.pending = None, [], []     # the scheduler closed the sequence
+                    # a turn that opened the sequence had it closed by the scheduler; a continued sequence is still open and is
+                    # closed here, so that the forgotten conversation does not keep its KV pages
+                    if session.seq_id is not None:
+                        with model.lock:
+                            try:
+                                model.backend.end(session.seq_id)
+                            except Exception:      # noqa: BLE001
+                                pass
+                    session.seq_id, session.tokens, session.pending = None, [], []
                     raise
                 session.tokens += feed + r.output[:-1] if r.output else feed
                 session.pending = r.output[-1:] if r.output else []
@@ -280,7 +366,7 @@ class ServerState:
                                        "prefill_chunk": m.sched.prefill_chunk,
                                        "speculation": m.sched.speculation.mode if m.sched.speculation else "none",
                                        "speculation_acceptance_rate": m.sched.speculation_acceptance_rate}} for m in self.models.values()],
-                "sessions": len(self.sessions), "tokens_served": self.ledger.public_projection(),
+                "sessions": len(self.sessions), "sessions_evicted": self.sessions_evicted, "tokens_served": self.ledger.public_projection(),
                 "serving_rate": self.rate_monitor.tick()["classification"]}
 
     def metrics_text(self) -> str:
@@ -297,6 +383,7 @@ class ServerState:
             for k, v in m.backend.kv_stats().items():
                 out.append(f"b200_kv_{k}{lab} {v}")
         out.append(f"b200_tokens_served_total {self.ledger.total()}")
+        out += [f"b200_sessions {len(self.sessions)}", f"b200_sessions_evicted_total {self.sessions_evicted}"]
         out += self.ttft.prometheus("b200_ttft_seconds") + self.itl.prometheus("b200_inter_token_latency_seconds")
         return "\n".join(out) + "\n"
 
@@ -360,12 +447,10 @@ def make_handler(state: ServerState):
 
         def do_DELETE(self):
             parts = self.path.strip("/").split("/")
-            if len(parts) == 3 and parts[:2] == ["v1", "sessions"] and parts[2] in state.sessions:
-                s = state.sessions.pop(parts[2])
-                if s.seq_id is not None:
-                    with s.model.lock:
-                        s.model.backend.end(s.seq_id)
-                return self._json(200, {"deleted": s.id})
+            if len(parts) == 3 and parts[:2] == ["v1", "sessions"]:
+                s = state.drop_session(urllib.parse.unquote(parts[2]))
+                if s is not None:
+                    return self._json(200, {"deleted": s.id})
             self._err(404, "no such session", "not_found")
 
         def do_POST(self):
@@ -410,7 +495,7 @@ def make_handler(state: ServerState):
                 if path == "/v1/sessions":
                     s = Session("sess-" + uuid.uuid4().hex[:16], model)
                     s.instructions = schema.string(body, "instructions")
-                    state.sessions[s.id] = s
+                    state.add_session(s)
                     return self._json(200, {"id": s.id, "model": model.id, "session": {"id": s.id}})
                 parts = path.strip("/").split("/")
                 if len(parts) in (4, 5) and parts[:2] == ["v1", "sessions"] and parts[3] == "responses" and parts[4:] in ([], ["stream"]):
@@ -631,12 +716,11 @@ def make_handler(state: ServerState):
             msgs = self._input_messages(body) if body.get("input") is not None or body.get("messages") is None else body["messages"]
             prev = body.get("previous_response_id")
             if prev is not None:
-                if prev not in state.responses:
-                    return self._err(404, f"previous_response_id {prev!r} is unknown", "not_found")
-                sess = state.sessions[state.responses[prev][0]]
+                sess = state.sessions.get(state.responses[prev][0]) if prev in state.responses else None
+                if sess is None:
+                    return self._err(404, f"previous_response_id {prev!r} is unknown or its conversation has expired", "not_found")
             else:
-                sess = Session("sess-" + uuid.uuid4().hex[:16], model)
-                state.sessions[sess.id] = sess
+                sess = state.add_session(Session("sess-" + uuid.uuid4().hex[:16], model))
             r, usage = state.complete(sess.model, msgs, body, session=sess)
             rid = "resp-" + uuid.uuid4().hex[:16]
             text = sess.model.tok.decode(r.output)

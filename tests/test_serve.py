@@ -713,3 +713,79 @@ def test_mixed_concurrent_traffic_with_abandoned_streams_leaves_nothing_behind(g
     finally:
         httpd.shutdown()
         model.close()
+
+
+class _LimitedPool:
+    """A CPU backend whose KV pool holds at most ``limit`` sequences (``begin`` beyond that raises ``MemoryError``, as the paged
+    pool does when it is out of pages) and whose ``step`` can be made to fail once."""
+
+    def __init__(self, inner, limit):
+        self.inner, self.limit, self.open, self.fail_next_step = inner, limit, set(), None
+
+    def __getattr__(self, name):
+        return getattr(self.inner, name)
+
+    def begin(self, seq_id, prompt):
+        if len(self.open) >= self.limit:
+            raise MemoryError("KV cache is out of pages")
+        r = self.inner.begin(seq_id, prompt)
+        self.open.add(seq_id)
+        return r
+
+    def end(self, seq_id):
+        self.open.discard(seq_id)
+        return self.inner.end(seq_id)
+
+    def step(self, *a, **kw):
+        if self.fail_next_step is not None:
+            e, self.fail_next_step = self.fail_next_step, None
+            raise e
+        return self.inner.step(*a, **kw)
+
+
+def test_idle_sessions_are_evicted_by_cap_by_age_and_when_the_kv_pool_runs_out(gguf_path):
+    be = _LimitedPool(CpuBackend.from_gguf(gguf_path), limit=3)
+    model = ServedModel("tiny", be, None, max_num_seqs=4)
+    state = ServerState([model])
+    state.max_sessions = 3
+    httpd = serve(state, "127.0.0.1", 0)
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    base = f"http://127.0.0.1:{httpd.server_address[1]}"
+    try:
+        turn = lambda **kw: _post(base + "/v1/responses", {"input": "hello", "max_tokens": 3, **kw})
+        first = json.loads(turn()[1])["id"]
+        ids = [json.loads(turn()[1])["id"] for _ in range(2)]
+        assert len(state.sessions) == 3 and len(be.open) == 3                       # each conversation keeps its sequence
+        # the cap: a fourth conversation pushes the least recently used one out, and its response id stops resolving
+        fourth = json.loads(turn()[1])["id"]
+        assert len(state.sessions) == 3 and len(be.open) == 3 and state.sessions_evicted == 1
+        code, raw = turn(previous_response_id=first)
+        assert code == 404 and "expired" in json.loads(raw)["error"]["message"]
+        assert turn(previous_response_id=ids[1])[0] == 200                           # the others continue
+        # the pool is full of idle conversations: a plain request evicts some of them and is then served
+        state.max_sessions = 100
+        code, raw = _post(base + "/v1/chat/completions", {"messages": [{"role": "user", "content": "room?"}], "max_tokens": 2})
+        assert code == 200 and state.sessions_evicted >= 2 and len(be.open) < 3, raw
+        # age: a conversation idle for longer than the time-to-live goes at the next sweep
+        keep = json.loads(turn()[1])["id"]
+        for s in state.sessions.values():
+            s.last_used -= state.session_ttl_s + 1
+        assert state.reap_sessions() >= 1
+        assert state.sessions == {} and be.open == set() and turn(previous_response_id=keep)[0] == 404
+        assert "b200_sessions_evicted_total" in _get(base + "/metrics")[1].decode()
+        assert json.loads(_get(base + "/psionic/management/status")[1])["sessions_evicted"] == state.sessions_evicted
+        # a later turn that fails closes the sequence it continued (nothing keeps the forgotten conversation's pages)
+        sid = json.loads(_post(base + "/v1/sessions", {})[1])["id"]
+        assert _post(base + f"/v1/sessions/{sid}/responses", {"prompt": "one", "max_tokens": 2})[0] == 200 and len(be.open) == 1
+        be.fail_next_step = RuntimeError("injected engine failure")
+        code, raw = _post(base + f"/v1/sessions/{sid}/responses", {"prompt": "two", "max_tokens": 2})
+        assert code == 500 and "injected" in raw.decode() and be.open == set() and state.sessions[sid].seq_id is None
+        assert _post(base + f"/v1/sessions/{sid}/responses", {"prompt": "three", "max_tokens": 2})[0] == 200      # the session starts over
+        # with nothing left to evict, exhaustion is the typed 503
+        be.limit = 0
+        state.drop_session(sid)
+        code, raw = _post(base + "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "max_tokens": 2})
+        assert code == 503 and json.loads(raw)["error"]["type"] == "kv_cache_exhausted"
+    finally:
+        httpd.shutdown()
+        model.close()
