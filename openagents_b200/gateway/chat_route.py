@@ -155,7 +155,9 @@ class ChatGateway:
         self.keys = {k.key: k for k in keys}
         self.default_price = default_price_msat_per_token
         self.lock = threading.Lock()
-        self.telemetry: list[dict] = []
+        self.telemetry: list[dict] = []                      # the most recent records (at most ``telemetry_keep``)
+        self.telemetry_keep = 10_000
+        self.route_totals: dict[str, list[int]] = {}         # route -> [requests, prompt tokens, completion tokens, msat], since start
         self.gates = {g.model: g for g in (gates or [])}
         self.internal_accounts = frozenset(internal_accounts)
         self.byok_adapter_factory, self.resolve_account_byok = byok_adapter_factory, resolve_account_byok
@@ -331,6 +333,13 @@ class ChatGateway:
             record["quantization"] = engine_quantization("Q4_K") if "q4" in result.served_model.lower() else record["quantization"]
         with self.lock:
             self.telemetry.append(record)
+            if len(self.telemetry) > 2 * self.telemetry_keep:
+                del self.telemetry[: len(self.telemetry) - self.telemetry_keep]
+            tot = self.route_totals.setdefault(d.adapter_id, [0, 0, 0, 0])
+            tot[0] += 1
+            tot[1] += result.usage.prompt_tokens
+            tot[2] += result.usage.completion_tokens
+            tot[3] += price
         usage = {"prompt_tokens": result.usage.prompt_tokens, "completion_tokens": result.usage.completion_tokens,
                  "total_tokens": result.usage.total_tokens}
         if result.usage.cached_prompt_tokens is not None:

@@ -124,6 +124,7 @@ class HydraliskPoolAdapter:
         self.live = {rid: {"inflight": 0, "warm": "unknown", "warmAt": None, "last429": None, "ttft": None, "tps": None, "health": "healthy",
                            "errors": 0} for rid in self.order}
         self.affinity: dict[str, str] = {}
+        self.max_affinity_entries = 100_000        # sessions remembered; the least recently used tenth goes when it is full
         self.last_route: dict | None = None
 
     def states(self) -> list[dict]:
@@ -169,7 +170,11 @@ class HydraliskPoolAdapter:
                 lv.update(errors=0, health="healthy", warm="warm", warmAt=self.now_ms(), ttft=dt,
                           tps=1000.0 * res.usage.completion_tokens / dt)
                 if affinity:
+                    self.affinity.pop(affinity, None)            # re-insert: the map is kept in order of last use
                     self.affinity[affinity] = rid
+                    if len(self.affinity) > self.max_affinity_entries:
+                        for k in list(self.affinity)[: self.max_affinity_entries // 10]:
+                            del self.affinity[k]
             return res
         return run
 

@@ -36,16 +36,42 @@ class ServedTokensLedger:
     serving path: a persistence error is counted and swallowed, because the ledger is a projection of the served
     answer, not its source."""
 
-    def __init__(self, path: str | None = None, now=time.time):
-        self.path, self.now = path, now
+    def __init__(self, path: str | None = None, now=time.time, max_rows_in_memory: int = 100_000):
+        """``max_rows_in_memory``: rows kept for idempotency and inspection.  Totals and the per-minute series behind
+        ``tokens_since`` are running sums, so a server that has answered millions of requests holds a bounded ledger; the file
+        (when there is one) keeps every row.  A duplicate of a row older than the kept window would be counted again."""
+        self.path, self.now, self.max_rows = path, now, max(1, int(max_rows_in_memory))
         self.rows: dict[str, dict] = {}
         self.lock = threading.Lock()
         self.persist_errors = 0
+        self._total, self._count = 0, 0
+        self._minutes: dict[int, int] = {}             # minute index -> tokens recorded in that minute (last 48 h)
+        self._dropped_until = float("-inf")            # recordedAt of the newest row no longer in ``rows``
         if path and os.path.exists(path):
             for line in open(path):
                 if line.strip():
-                    row = json.loads(line)
-                    self.rows[row["idempotencyKey"]] = row
+                    try:
+                        row = json.loads(line)
+                        key = row["idempotencyKey"]
+                        int(row["inputTokens"]), int(row["outputTokens"]), float(row["recordedAt"])
+                    except (ValueError, KeyError, TypeError):
+                        continue                       # a torn last line of a ledger that was being written when the process died
+                    if key not in self.rows:
+                        self._admit(key, row)
+
+    def _admit(self, key: str, row: dict):
+        n = row["inputTokens"] + row["outputTokens"]
+        self.rows[key] = row
+        self._total += n
+        self._count += 1
+        minute = int(row["recordedAt"] // 60)
+        self._minutes[minute] = self._minutes.get(minute, 0) + n
+        if len(self.rows) > self.max_rows:
+            for k in list(self.rows)[: max(1, self.max_rows // 10)]:
+                self._dropped_until = max(self._dropped_until, self.rows.pop(k)["recordedAt"])
+            horizon = minute - 48 * 60
+            for m in [m for m in self._minutes if m < horizon]:
+                del self._minutes[m]
 
     def record(self, request_id: str, model_id: str, input_tokens: int, output_tokens: int, account_ref: str = "account.anonymous",
                adapter_id: str = "psionic", demand_kind: str = "unlabeled", served_model: str | None = None) -> dict:
@@ -60,7 +86,7 @@ class ServedTokensLedger:
         with self.lock:
             if row["idempotencyKey"] in self.rows:
                 return {"inserted": False, "reason": "duplicate"}
-            self.rows[row["idempotencyKey"]] = row
+            self._admit(row["idempotencyKey"], row)
             if self.path:
                 try:
                     with open(self.path, "a") as f:
@@ -71,14 +97,20 @@ class ServedTokensLedger:
 
     def total(self) -> int:
         with self.lock:
-            return sum(r["inputTokens"] + r["outputTokens"] for r in self.rows.values())
+            return self._total
 
     def tokens_since(self, t: float) -> int:
+        """Tokens recorded at or after ``t``: exact from the kept rows while they reach back that far, else from the per-minute
+        series (whole minutes, so up to one minute more than asked)."""
         with self.lock:
-            return sum(r["inputTokens"] + r["outputTokens"] for r in self.rows.values() if r["recordedAt"] >= t)
+            if t > self._dropped_until:
+                return sum(r["inputTokens"] + r["outputTokens"] for r in self.rows.values() if r["recordedAt"] >= t)
+            first = int(t // 60)
+            return sum(n for m, n in self._minutes.items() if m >= first)
 
     def public_projection(self) -> dict:
-        return {"tokensServed": self.total(), "rows": len(self.rows)}
+        with self.lock:
+            return {"tokensServed": self._total, "rows": self._count}
 
 
 @dataclass

@@ -138,14 +138,7 @@ def build_gateway(cfg: dict, opener=None) -> ChatGateway:
 
 def metrics_text(gw: ChatGateway) -> str:
     with gw.lock:
-        recs = list(gw.telemetry)
-    by_route: dict[str, list[int]] = {}
-    for r in recs:
-        row = by_route.setdefault(str(r.get("route")), [0, 0, 0, 0])
-        row[0] += 1
-        for i, k in ((1, "promptTokens"), (2, "completionTokens"), (3, "priceMsat")):
-            if isinstance(r.get(k), (int, float)):         # a figure that was not measured is a marker string, not a number
-                row[i] += int(r[k])
+        by_route = {k: list(v) for k, v in gw.route_totals.items()}
     out = []
     for route, (n, pt, ct, msat) in sorted(by_route.items()):
         lab = f'{{route="{route}"}}'

@@ -246,3 +246,13 @@ def test_engine_refusal_reaches_the_caller_as_a_400_not_an_exception(state):
     status, out = gw.handle("Bearer k1", json.dumps({**BODY, "messages": [{"role": "user", "content": long_text}]}))
     assert status == 400 and out["error"]["code"] == "request_rejected" and "context" in out["error"]["message"], out
     assert gw.keys["k1"].inflight == 0
+
+
+def test_gateway_memory_is_bounded_while_its_counters_stay_exact(state):
+    gw, _ = _gateway(state, keys=[cr.ApiKey("k1", "acct1", balance_msat=10**9, max_inflight=4)])
+    gw.telemetry_keep = 3
+    for _ in range(8):
+        assert gw.handle("Bearer k1", json.dumps({**BODY, "max_tokens": 1}))[0] == 200
+    assert 3 <= len(gw.telemetry) <= 6                                     # trimmed in blocks, never beyond twice the window
+    n, prompt, completion, msat = gw.route_totals["openagents-network"]
+    assert n == 8 and completion == 8 and prompt > 0 and msat == 10**9 - gw.keys["k1"].balance_msat

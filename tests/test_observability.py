@@ -76,3 +76,23 @@ def test_byte_level_bpe_round_trip_and_merge_order():
             "tokenizer.ggml.token_type": [1] * (len(toks) - 1) + [3]}
     assert isinstance(tokenizer_from_metadata(meta, len(toks)), BpeTokenizer)
     assert tokenizer_from_metadata({}, 512).encode("a") == [97]
+
+
+def test_ledger_memory_is_bounded_and_totals_stay_exact(tmp_path):
+    from openagents_b200.gateway.observability import ServedTokensLedger
+    t = [1_000_000.0]
+    path = str(tmp_path / "big.jsonl")
+    led = ServedTokensLedger(path, now=lambda: t[0], max_rows_in_memory=100)
+    for i in range(1000):
+        t[0] += 1.0                                     # one request a second, 3 tokens each
+        assert led.record(f"r{i}", "m", 1, 2)["inserted"]
+    assert len(led.rows) <= 100 and led.total() == 3000 and led.public_projection() == {"tokensServed": 3000, "rows": 1000}
+    assert led.record("r999", "m", 1, 2) == {"inserted": False, "reason": "duplicate"}       # recent keys are still recognised
+    assert led.tokens_since(t[0] - 9.5) == 30                                               # inside the kept rows: exact
+    far = led.tokens_since(t[0] - 600)                                                      # beyond them: per-minute series
+    assert 600 * 3 <= far <= 661 * 3
+    assert led.tokens_since(0) == 3000
+    with open(path, "a") as f:
+        f.write('{"idempotencyKey": "served:torn", "inputTok')                              # the process died mid-write
+    again = ServedTokensLedger(path, now=lambda: t[0], max_rows_in_memory=100)
+    assert again.total() == 3000 and len(again.rows) <= 100 and again.public_projection()["rows"] == 1000
