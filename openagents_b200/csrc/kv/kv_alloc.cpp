@@ -1,6 +1,7 @@
 // Paged KV-cache bookkeeping on the host: a page free-list with reference counts, per-sequence
 // page lists, and a prefix index keyed by a hash chain over full pages of token ids so a new
-// request can share the pages of an earlier one with the same prefix.
+// request can share the pages of an earlier one with the same prefix.  Published pages outlive their
+// last holder (retained, oldest reclaimed first when pages run short), so the earlier request may be over.
 //
 // The reference lists "KV and prefix caches, continuous batching" as model-server infrastructure
 // (docs/muse/muse-glimmer.md:113-114) and derives a cache-affinity key from a canonical prompt
@@ -8,6 +9,8 @@
 // mechanics here are this framework's own.
 #include <cstdint>
 #include <cstring>
+#include <iterator>
+#include <list>
 #include <unordered_map>
 #include <vector>
 
@@ -27,6 +30,13 @@ struct Pool {
   std::vector<int32_t> page_tokens;    // [n_pages][page_size] token ids of a registered page: a hit must match them,
                                        // so a hash collision or a stale registration can never hand out wrong K/V
   std::unordered_map<uint64_t, int32_t> prefix;  // chain hash -> page
+  // Registered pages that no sequence holds any more keep their K/V and their place in the prefix index until the page is
+  // needed: a later prompt with the same prefix (the next turn of a closed conversation, the same system prompt an hour
+  // later) still hits them.  Oldest first; a hit takes the page out again, an allocation that finds the free list empty takes
+  // the oldest one and unregisters it.
+  std::list<int32_t> retained;
+  std::vector<std::list<int32_t>::iterator> retained_at;
+  std::vector<uint8_t> is_retained;
   std::unordered_map<int64_t, Seq> seqs;
   uint64_t hits = 0, lookups = 0;
 };
@@ -54,9 +64,42 @@ void unregister_page(Pool* p, int32_t pg) {
 
 void release_page(Pool* p, int32_t pg) {
   if (--p->refcnt[pg] == 0) {
-    unregister_page(p, pg);
-    p->free_list.push_back(pg);
+    if (p->page_hash[pg]) {             // still a valid prefix page: keep it findable until the page is needed
+      p->retained.push_back(pg);
+      p->retained_at[pg] = std::prev(p->retained.end());
+      p->is_retained[pg] = 1;
+    } else {
+      p->free_list.push_back(pg);
+    }
   }
+}
+
+inline int64_t available(const Pool* p) { return (int64_t)p->free_list.size() + (int64_t)p->retained.size(); }
+
+// A page to write into: a free one, else the longest-unused retained prefix page (which leaves the index).  The caller has
+// checked available() > 0.
+int32_t take_page(Pool* p) {
+  int32_t pg;
+  if (!p->free_list.empty()) {
+    pg = p->free_list.back();
+    p->free_list.pop_back();
+  } else {
+    pg = p->retained.front();
+    p->retained.pop_front();
+    p->is_retained[pg] = 0;
+    unregister_page(p, pg);
+  }
+  p->refcnt[pg] = 1;
+  return pg;
+}
+
+// A prefix hit on a page: one more holder; a retained page is in use again.
+void share_page(Pool* p, int32_t pg) {
+  if (p->is_retained[pg]) {
+    p->retained.erase(p->retained_at[pg]);
+    p->is_retained[pg] = 0;
+  }
+  p->refcnt[pg]++;
 }
 
 }  // namespace
@@ -70,12 +113,16 @@ void* b200_kv_create(int32_t n_pages, int32_t page_size) {
   p->refcnt.assign(n_pages, 0);
   p->page_hash.assign(n_pages, 0);
   p->page_tokens.assign((size_t)n_pages * (size_t)page_size, -1);
+  p->retained_at.assign(n_pages, p->retained.end());
+  p->is_retained.assign(n_pages, 0);
   p->free_list.reserve(n_pages);
   for (int32_t i = n_pages - 1; i >= 0; i--) p->free_list.push_back(i);
   return p;
 }
 void b200_kv_destroy(void* h) { delete (Pool*)h; }
-int32_t b200_kv_free_pages(void* h) { return (int32_t)((Pool*)h)->free_list.size(); }
+// Pages an allocation can take: free ones plus retained prefix pages (which are given up when needed).
+int32_t b200_kv_free_pages(void* h) { return (int32_t)available((Pool*)h); }
+int32_t b200_kv_retained_pages(void* h) { return (int32_t)((Pool*)h)->retained.size(); }
 int32_t b200_kv_total_pages(void* h) { return ((Pool*)h)->n_pages; }
 uint64_t b200_kv_prefix_hits(void* h) { return ((Pool*)h)->hits; }
 uint64_t b200_kv_prefix_lookups(void* h) { return ((Pool*)h)->lookups; }
@@ -99,7 +146,7 @@ int64_t b200_kv_seq_begin(void* h, int64_t seq_id, const int32_t* tokens, int64_
                     sizeof(int32_t) * (size_t)p->page_size) != 0)
       break;                            // same hash, different tokens: not a hit
     p->hits++;
-    p->refcnt[it->second]++;
+    share_page(p, it->second);
     s.pages.push_back(it->second);
     s.chain.push_back(chain);
     s.n_tokens += p->page_size;
@@ -115,13 +162,8 @@ int32_t b200_kv_seq_extend(void* h, int64_t seq_id, int64_t n_new) {
   if (it == p->seqs.end()) return -1;
   Seq& s = it->second;
   int64_t need = (s.n_tokens + n_new + p->page_size - 1) / p->page_size - (int64_t)s.pages.size();
-  if (need > (int64_t)p->free_list.size()) return -2;
-  for (int64_t i = 0; i < need; i++) {
-    int32_t pg = p->free_list.back();
-    p->free_list.pop_back();
-    p->refcnt[pg] = 1;
-    s.pages.push_back(pg);
-  }
+  if (need > available(p)) return -2;
+  for (int64_t i = 0; i < need; i++) s.pages.push_back(take_page(p));
   s.n_tokens += n_new;
   return 0;
 }
@@ -192,7 +234,7 @@ int32_t b200_kv_stage_decode(void* h, const int64_t* seq_ids, int32_t B, int32_t
       if (pages_after > max_pages || (int64_t)s.pages.size() > max_pages) return -3;
       if (pages_after > (int64_t)s.pages.size()) need++;
     }
-    if (need > (int64_t)p->free_list.size()) return -2;
+    if (need > available(p)) return -2;
   }
   for (int32_t b = 0; b < B; b++) {
     auto it = p->seqs.find(seq_ids[b]);
@@ -202,11 +244,8 @@ int32_t b200_kv_stage_decode(void* h, const int64_t* seq_ids, int32_t B, int32_t
     const bool new_page = (p0 + 1 + ps - 1) / ps > (int64_t)s.pages.size();
     if (new_page) {
       if ((int64_t)s.pages.size() + 1 > max_pages) return -3;
-      if (p->free_list.empty()) return -2;
-      int32_t pg = p->free_list.back();
-      p->free_list.pop_back();
-      p->refcnt[pg] = 1;
-      s.pages.push_back(pg);
+      if (available(p) == 0) return -2;
+      s.pages.push_back(take_page(p));
     }
     if ((int64_t)s.pages.size() > max_pages) return -3;
     s.n_tokens = p0 + 1;
@@ -242,10 +281,8 @@ int32_t b200_kv_seq_truncate(void* h, int64_t seq_id, int64_t new_len, int32_t* 
   if (partial) {
     const int32_t pg = s.pages[full];
     if (p->refcnt[pg] > 1) {
-      if (p->free_list.empty()) return -2;
-      const int32_t fresh = p->free_list.back();
-      p->free_list.pop_back();
-      p->refcnt[fresh] = 1;
+      if (available(p) == 0) return -2;
+      const int32_t fresh = take_page(p);
       p->refcnt[pg]--;                  // the other holders keep the original (and its registration)
       s.pages[full] = fresh;
       if (cow_src) *cow_src = pg;

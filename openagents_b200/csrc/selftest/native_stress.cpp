@@ -55,6 +55,8 @@ void b200_gguf_writer_free(void*);
 void* b200_kv_create(int32_t n_pages, int32_t page_size);
 void b200_kv_destroy(void*);
 int32_t b200_kv_free_pages(void*);
+int32_t b200_kv_retained_pages(void*);
+int32_t b200_kv_seq_pages(void*, int64_t, int32_t*, int32_t);
 int32_t b200_kv_total_pages(void*);
 int64_t b200_kv_seq_begin(void*, int64_t seq_id, const int32_t* tokens, int64_t n_tokens);
 int32_t b200_kv_seq_extend(void*, int64_t seq_id, int64_t n_new);
@@ -205,6 +207,22 @@ static void kv_stress() {
       }
     }
     CHECK(b200_kv_free_pages(p) >= 0 && b200_kv_free_pages(p) <= total);
+    if (step % 50 == 0) {
+      // every page is either held by a live sequence (shared pages once) or can be allocated (free, or a retained prefix page):
+      // nothing leaks, and nothing that a sequence holds is also on offer
+      std::vector<uint8_t> held((size_t)total, 0);
+      int32_t n_held = 0, buf[64];
+      for (int64_t id : live) {
+        const int32_t n = b200_kv_seq_pages(p, id, buf, 64);
+        CHECK(n >= 0 && n <= 64);
+        for (int32_t i = 0; i < n; i++) {
+          CHECK(buf[i] >= 0 && buf[i] < total);
+          if (!held[(size_t)buf[i]]) { held[(size_t)buf[i]] = 1; n_held++; }
+        }
+      }
+      CHECK(n_held + b200_kv_free_pages(p) == total);
+      CHECK(b200_kv_retained_pages(p) >= 0 && b200_kv_retained_pages(p) <= b200_kv_free_pages(p));
+    }
   }
   for (int64_t id : live) b200_kv_seq_end(p, id);
   CHECK(b200_kv_free_pages(p) == total);                    // published pages are cached, not leaked: ending every sequence frees them

@@ -40,7 +40,7 @@ class KVPool:
             vp, i64, i32, u64 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_uint64
             P32 = ctypes.POINTER(ctypes.c_int32)
             sig = {"b200_kv_create": ([i32, i32], vp), "b200_kv_destroy": ([vp], None),
-                   "b200_kv_free_pages": ([vp], i32), "b200_kv_total_pages": ([vp], i32),
+                   "b200_kv_free_pages": ([vp], i32), "b200_kv_total_pages": ([vp], i32), "b200_kv_retained_pages": ([vp], i32),
                    "b200_kv_prefix_hits": ([vp], u64), "b200_kv_prefix_lookups": ([vp], u64),
                    "b200_kv_seq_begin": ([vp, i64, P32, i64], i64), "b200_kv_seq_extend": ([vp, i64, i64], i32),
                    "b200_kv_seq_publish": ([vp, i64, P32, i64], None), "b200_kv_seq_len": ([vp, i64], i64),
@@ -128,6 +128,12 @@ class KVPool:
     @property
     def free_pages(self) -> int:
         return self.L.b200_kv_free_pages(self.h)
+
+    @property
+    def retained_pages(self) -> int:
+        """Published pages no sequence holds any more: still in the prefix index, reclaimed (oldest first) when pages run short.
+        They are counted in ``free_pages``."""
+        return self.L.b200_kv_retained_pages(self.h)
 
     @property
     def prefix_stats(self) -> tuple[int, int]:

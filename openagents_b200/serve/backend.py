@@ -276,7 +276,7 @@ class CudaBackend(Backend):
     def kv_stats(self):
         p = self.engine.pool
         hits, lookups = p.prefix_stats
-        return {"pages_total": p.n_pages, "pages_free": p.free_pages, "page_size": p.page_size,
+        return {"pages_total": p.n_pages, "pages_free": p.free_pages, "pages_retained": p.retained_pages, "page_size": p.page_size,
                 "prefix_hits": hits, "prefix_lookups": lookups}
 
     def topology(self):

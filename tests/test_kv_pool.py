@@ -47,8 +47,36 @@ def test_prefix_sharing():
     assert p.pages(2)[:2] == pages1[:2]      # shared pages survive their first owner
     p.end(2)
     p.end(3)
-    assert p.free_pages == 16
-    assert p.begin(4, toks) == 0             # nothing cached once every owner is gone
+    assert p.free_pages == 16                # every page can be allocated again ...
+    assert p.retained_pages == 2             # ... and the two published pages stay findable until their pages are needed
+    assert p.begin(4, toks) == 32 and p.retained_pages == 0 and p.free_pages == 14
+    p.end(4)
+
+
+def test_retained_prefix_pages_are_reclaimed_oldest_first_and_never_hit_stale():
+    """Pages of a closed conversation keep serving prefix hits; an allocation that finds no free page takes the longest-unused
+    retained page, which leaves the index, so a later lookup of that prefix misses instead of reading another sequence's K/V."""
+    p = KVPool(8, 16)
+    a, b = list(range(100, 148)), list(range(200, 248))          # 48 tokens = 3 pages each
+    for sid, toks in ((1, a), (2, b)):
+        assert p.begin(sid, toks) == 0
+        p.extend(sid, 48)
+        p.publish(sid, toks)
+        p.end(sid)                                               # a first, then b: a's pages are the oldest
+    assert p.retained_pages == 6 and p.free_pages == 8
+    assert p.begin(3, None) == 0
+    p.extend(3, 16 * 4)                                          # 2 free pages + the 2 oldest retained ones (a's first two)
+    assert p.retained_pages == 4 and p.free_pages == 4
+    assert p.begin(4, a + [1]) == 0                              # a's chain is broken at its first page: a miss, not stale K/V
+    p.end(4)
+    assert p.begin(5, b + [1]) == 48 and p.retained_pages == 1   # b is intact; the hit takes its pages out of the retained list
+    with pytest.raises(MemoryError):
+        p.extend(5, 16 * 3)                                      # 1 retained + 0 free < 2 more pages needed beyond the partial one
+    p.extend(5, 16)                                              # one more page: the last retained one (a's third) is reclaimed
+    assert p.retained_pages == 0 and p.free_pages == 0
+    p.end(3)
+    p.end(5)
+    assert p.free_pages == 8 and p.retained_pages == 3           # b's published pages are retained again
 
 
 def test_stage_decode_batch():
