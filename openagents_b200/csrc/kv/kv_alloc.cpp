@@ -37,6 +37,7 @@ struct Pool {
   std::list<int32_t> retained;
   std::vector<std::list<int32_t>::iterator> retained_at;
   std::vector<uint8_t> is_retained;
+  bool retain = true;                  // off: a page nobody holds leaves the index at once (prefix hits among live sequences only)
   std::unordered_map<int64_t, Seq> seqs;
   uint64_t hits = 0, lookups = 0;
 };
@@ -64,11 +65,12 @@ void unregister_page(Pool* p, int32_t pg) {
 
 void release_page(Pool* p, int32_t pg) {
   if (--p->refcnt[pg] == 0) {
-    if (p->page_hash[pg]) {             // still a valid prefix page: keep it findable until the page is needed
+    if (p->retain && p->page_hash[pg]) {   // still a valid prefix page: keep it findable until the page is needed
       p->retained.push_back(pg);
       p->retained_at[pg] = std::prev(p->retained.end());
       p->is_retained[pg] = 1;
     } else {
+      unregister_page(p, pg);
       p->free_list.push_back(pg);
     }
   }
@@ -123,6 +125,19 @@ void b200_kv_destroy(void* h) { delete (Pool*)h; }
 // Pages an allocation can take: free ones plus retained prefix pages (which are given up when needed).
 int32_t b200_kv_free_pages(void* h) { return (int32_t)available((Pool*)h); }
 int32_t b200_kv_retained_pages(void* h) { return (int32_t)((Pool*)h)->retained.size(); }
+// Turn retention of published pages on or off; turning it off gives the pages retained so far back.
+void b200_kv_set_retention(void* h, int32_t on) {
+  Pool* p = (Pool*)h;
+  p->retain = on != 0;
+  if (!p->retain) {
+    for (int32_t pg : p->retained) {
+      p->is_retained[pg] = 0;
+      unregister_page(p, pg);
+      p->free_list.push_back(pg);
+    }
+    p->retained.clear();
+  }
+}
 int32_t b200_kv_total_pages(void* h) { return ((Pool*)h)->n_pages; }
 uint64_t b200_kv_prefix_hits(void* h) { return ((Pool*)h)->hits; }
 uint64_t b200_kv_prefix_lookups(void* h) { return ((Pool*)h)->lookups; }

@@ -14,8 +14,8 @@ KV and prefix caches, continuous batching (docs/muse/muse-glimmer.md:110-126).
 from __future__ import annotations
 
 import ctypes
-import os
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -40,7 +40,7 @@ class KVPool:
             vp, i64, i32, u64 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_uint64
             P32 = ctypes.POINTER(ctypes.c_int32)
             sig = {"b200_kv_create": ([i32, i32], vp), "b200_kv_destroy": ([vp], None),
-                   "b200_kv_free_pages": ([vp], i32), "b200_kv_total_pages": ([vp], i32), "b200_kv_retained_pages": ([vp], i32),
+                   "b200_kv_free_pages": ([vp], i32), "b200_kv_total_pages": ([vp], i32), "b200_kv_retained_pages": ([vp], i32), "b200_kv_set_retention": ([vp, i32], None),
                    "b200_kv_prefix_hits": ([vp], u64), "b200_kv_prefix_lookups": ([vp], u64),
                    "b200_kv_seq_begin": ([vp, i64, P32, i64], i64), "b200_kv_seq_extend": ([vp, i64, i64], i32),
                    "b200_kv_seq_publish": ([vp, i64, P32, i64], None), "b200_kv_seq_len": ([vp, i64], i64),
@@ -55,6 +55,13 @@ class KVPool:
         self.h = L.b200_kv_create(n_pages, page_size)
         self.page_size = page_size
         self.n_pages = n_pages
+        # B200_KV_RETAIN=0: published pages leave the prefix index with their last holder, so that a repeated prompt takes the
+        # very same compute path as the first time (bit-exact repeats); the default keeps them until the memory is needed
+        if os.environ.get("B200_KV_RETAIN", "1") == "0":
+            self.set_retention(False)
+
+    def set_retention(self, on: bool):
+        self.L.b200_kv_set_retention(self.h, int(bool(on)))
 
     @staticmethod
     def _arr(tokens):

@@ -101,6 +101,33 @@ def test_prefix_reuse_gives_same_logits(tmp_path):
     assert torch.allclose(l1, l2, atol=2e-2 * l1.std().item())
 
 
+@pytest.mark.kv_retention
+def test_prefix_pages_of_a_closed_sequence_still_serve_hits(tmp_path):
+    """The published pages of a sequence that has ended stay in the prefix index: the same prompt later is prefilled on top of
+    them and gives the same logits (to the tolerance of a different tiling), and they are given up when the pool needs pages."""
+    cfg = TINY_LLAMA.with_(vocab=1000)
+    p = str(tmp_path / "t.gguf")
+    save_gguf(p, cfg, random_weights(cfg, 4), PLAN_Q8_0)
+    eng = _engine(p)
+    prompt = torch.randint(0, 1000, (50,), generator=torch.Generator().manual_seed(5)).tolist()
+    assert eng.begin(1, prompt) == 0
+    l1, _ = eng.forward_tokens([1], [prompt])
+    l1 = l1.clone()
+    eng.pool.publish(1, prompt)
+    free0 = eng.pool.free_pages
+    eng.end(1)
+    assert eng.pool.retained_pages == 3 and eng.pool.free_pages == free0 + 4
+    cached = eng.begin(2, prompt)
+    assert cached == 48 and eng.pool.retained_pages == 0
+    l2, _ = eng.forward_tokens([2], [prompt[cached:]])
+    assert torch.allclose(l1, l2, atol=2e-2 * l1.std().item())
+    eng.end(2)
+    eng.pool.set_retention(False)
+    assert eng.pool.retained_pages == 0 and eng.begin(3, prompt) == 0
+    eng.end(3)
+    eng.check_status()
+
+
 def test_device_side_decode_loop_matches_stepwise(tmp_path):
     """The self-advancing decode graph produces the same ids as one host round trip per step."""
     cfg = TINY_LLAMA.with_(vocab=2048)

@@ -165,3 +165,25 @@ def test_stage_decode_is_all_or_nothing():
     with pytest.raises(MemoryError):
         pool.stage_decode(seq.data_ptr(), 2, 4, True, pos.data_ptr(), slot.data_ptr(), ctx.data_ptr(), table.data_ptr())
     assert pool.length(1) == 16 and pool.length(2) == 16 and pool.free_pages == 1      # nothing grew
+
+
+def test_retention_can_be_switched_off(monkeypatch):
+    toks = list(range(40))
+
+    def closed_conversation(p):
+        p.begin(1, toks)
+        p.extend(1, 40)
+        p.publish(1, toks)
+        p.end(1)
+    p = KVPool(16, 16)
+    closed_conversation(p)
+    assert p.retained_pages == 2
+    p.set_retention(False)                       # switching off gives back what was retained
+    assert p.retained_pages == 0 and p.free_pages == 16 and p.begin(2, toks) == 0
+    p.end(2)
+    closed_conversation(p)
+    assert p.retained_pages == 0 and p.begin(3, toks) == 0
+    monkeypatch.setenv("B200_KV_RETAIN", "0")   # the process-wide default (what bit-exact repeat tests set)
+    q = KVPool(16, 16)
+    closed_conversation(q)
+    assert q.retained_pages == 0 and q.begin(2, toks) == 0
